@@ -1,0 +1,345 @@
+#!/usr/bin/env python
+"""Benchmark of the optimizer-step hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one optimizer step() over the whole parameter set of the workload with
+the gradients already resident in HBM.  Headline workload: Adam (weight decay 0.01) on
+the 12-layer d=768 transformer parameter set, 109 602 816 f32 parameters (28 B/param of
+HBM traffic).  Rank 0 prints ONE JSON line; see README/DESIGN for the meaning of keys.
+
+N > 1 is launched by torch.distributed.run, one rank per GPU: the arena is sharded
+ZeRO-1 style (each rank updates arena/N elements) and step() ends with the NCCL
+all-gather of updated parameters, so `value` is total params / (update + gather) time.
+
+`--impl reference` times the CPU restatement of Volta's own optimizer (oracle/) on the
+host cores on the same workload; Volta is single threaded by construction, so it uses
+one core.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import workloads  # noqa: E402
+
+ADAM_BYTES_PER_PARAM = 28  # read theta, g, m, v (16) + write theta, m, v (12)
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            d = json.load(fh)
+        return dict(hbm_gbs=float(d["hbm_gbs"]), bf16_tflops=float(d["bf16_tflops"]),
+                    bf16_tflops_sustained=float(d.get("bf16_tflops_sustained", d["bf16_tflops"])),
+                    source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.rows = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-i", str(self.gpu_index), "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 9:
+                self.rows.append(parts)
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()  # the exact child we started
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": len(self.rows)}
+        if not self.rows:
+            return out
+        sm = []
+        reasons = set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                out["sm_max_mhz"] = float(r[2])
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
+                                  "sw_power_cap"), r[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        # "under load": the upper half of the samples (idle samples sit at low clocks)
+        if sm:
+            sm.sort()
+            out["sm_mhz"] = statistics.median(sm[len(sm) // 2:])
+        out["reasons"] = sorted(reasons)
+        return out
+
+
+def fill_arena(wl, offsets, arena, arrays):
+    host = np.zeros(arena, np.float32)
+    for o, a in zip(offsets, arrays):
+        host[o:o + a.size] = a.reshape(-1)
+    return host
+
+
+# ---------------------------------------------------------------------------------------------
+# CPU arm: the restatement of Volta's CPU optimizer, one thread (Volta is single threaded)
+# ---------------------------------------------------------------------------------------------
+
+def time_cpu_adam(wl, steps, warmup, max_seconds=25.0):
+    import oracle
+    oracle.build()
+    oracle.set_threads(1)
+    params = wl.make_params()
+    grads = wl.make_grads(1)
+    h = wl.hyper
+    opt = oracle.Adam(params, h["lr"], h["betas"], h["eps"], h["weight_decay"])
+    for _ in range(warmup):
+        opt.step(grads)
+    times = []
+    t_begin = time.perf_counter()
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        opt.step(grads)
+        times.append(time.perf_counter() - t0)
+        if time.perf_counter() - t_begin > max_seconds:
+            break
+    return times
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    wl = workloads.c3_transformer_adam()
+    times = time_cpu_adam(wl, args.steps, min(args.warmup, 1), max_seconds=120.0)
+    sec = sum(times) / len(times)
+    value = wl.total / sec
+    cores = 1
+    line = {
+        "impl": "reference", "metric": "adam_params_per_s", "value": value, "unit": "params/s",
+        "n_gpus": args.gpus, "steps": len(times), "warmup": min(args.warmup, 1), "ms_per_step": sec * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": "c3_transformer_adam: Adam wd=0.01, 157 tensors, 109602816 f32 params",
+                   "host_cores_available": os.cpu_count()},
+        "cpu_baseline": {"value": value, "unit": "params/s", "cores": cores, "kind": "port",
+                         "sample": f"{len(times)} full steps of the whole workload, 1 thread "
+                                   "(Volta's optimizer is single threaded)"},
+        "e2e": {"value": value, "unit": "params/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+# ---------------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------------
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    import volta_b200
+    from volta_b200 import VB_STEP_NO_EXCHANGE, Adam, Engine, PinnedBuffer, Tensor
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run (one rank per GPU)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    eng = Engine(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        idt = torch.zeros(128, dtype=torch.uint8, device=dev)
+        if rank == 0:
+            idt.copy_(torch.frombuffer(bytearray(Engine.unique_id()), dtype=torch.uint8))
+        dist.broadcast(idt, 0)
+        eng.init_comm(bytes(idt.cpu().numpy().tobytes()), rank, world)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        eng.synchronize()
+
+    peaks = load_peaks()
+    wl = workloads.c3_transformer_adam()
+    h = wl.hyper
+    params = wl.make_params()
+    tensors = [Tensor(p, p.shape) for p in params]
+    opt = Adam(tensors, h["lr"], h["betas"], h["eps"], h["weight_decay"], engine=eng)
+    _, _, arena, offsets = opt.arena_layout()
+    grads_pinned = PinnedBuffer(arena)
+    grads_pinned.array[:] = fill_arena(wl, offsets, arena, wl.make_grads(1))
+    params_pinned = PinnedBuffer(arena)
+    opt.upload_arena(1, grads_pinned.array)
+    eng.synchronize()
+
+    stream = torch.cuda.ExternalStream(eng.stream, device=dev)
+
+    def timed_steps(n, flags=0, per_step=False):
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(n + 1)]
+        evs[0].record(stream)
+        for i in range(n):
+            opt.step(flags)
+            if per_step or i == n - 1:
+                evs[i + 1].record(stream)
+        eng.synchronize()
+        total = evs[0].elapsed_time(evs[n])
+        steps_ms = [evs[i].elapsed_time(evs[i + 1]) for i in range(n)] if per_step else None
+        return total, steps_ms
+
+    # ---- device-resident timing: W warm-up steps, then exactly K steps ----
+    for _ in range(args.warmup):
+        opt.step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = eng.launch_count
+    barrier()
+    total_ms, _ = timed_steps(args.steps)
+    barrier()
+    launches = eng.launch_count - launches0
+
+    # the update kernel alone (no exchange), per-launch durations, for the roofline
+    barrier()
+    _, kernel_ms = timed_steps(args.steps, VB_STEP_NO_EXCHANGE, per_step=True)
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+
+    def max_over_ranks(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    total_ms = max_over_ranks(total_ms)
+    kernel_avg_ms = max_over_ranks(sum(kernel_ms) / len(kernel_ms))
+    ms_per_step = total_ms / args.steps
+    value = wl.total / (ms_per_step * 1e-3)
+
+    # ---- end to end through the public API with host buffers ----
+    e2e_steps = max(3, min(args.steps, 10))
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        opt.upload_arena(1, grads_pinned.array)      # host -> device: this step's gradients
+        opt.step()
+        opt.download_arena(0, params_pinned.array)   # device -> host: updated parameters (blocks)
+    barrier()
+    e2e_s = max_over_ranks((time.perf_counter() - t0) / e2e_steps)
+
+    if rank != 0:
+        opt.close()
+        return 0
+
+    owned = arena // world  # elements one launch updates on one rank
+    achieved_gbs = ADAM_BYTES_PER_PARAM * (wl.total / world) / (kernel_avg_ms * 1e-3) / 1e9
+    line = {
+        "metric": "adam_params_per_s", "value": value, "unit": "params/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": "c3_transformer_adam: Adam lr=1e-3 betas=(0.9,0.999) eps=1e-8 wd=0.01, "
+                               "157 tensors, 109602816 f32 params",
+                   "l2": "inputs larger than L2 (1.75 GB of theta/g/m/v per step vs 126 MB)",
+                   "parallelism": f"zero1x{world}" if world > 1 else "single",
+                   "exchange": "nccl all-gather of updated params inside step()" if world > 1 else "none"},
+        "update_only": {"value": wl.total / (kernel_avg_ms * 1e-3), "unit": "params/s",
+                        "ms_per_step": kernel_avg_ms,
+                        "note": "fused update kernel alone, max over ranks"},
+        "roofline": {"bound": "hbm", "achieved": achieved_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": achieved_gbs / peaks["hbm_gbs"], "traffic": None,
+                     "peak_source": peaks["source"], "frac_of_nominal_8tbs": achieved_gbs / 8000.0,
+                     "kernel": "multi_tensor_update_kernel<ADAM>",
+                     "algorithmic_bytes_per_launch": ADAM_BYTES_PER_PARAM * (wl.total // world),
+                     "launch_ms": kernel_avg_ms},
+        "e2e": {"value": wl.total / e2e_s, "unit": "params/s", "h2d_bytes_per_step": arena * 4,
+                "d2h_bytes_per_step": arena * 4, "ms_per_step": e2e_s * 1e3, "steps": e2e_steps},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+    }
+    line["roofline"]["traffic"] = traffic_from_profile()
+
+    if world == 1 and not args.no_cpu_baseline:
+        times = time_cpu_adam(wl, 12, 1, max_seconds=20.0)
+        sec = sum(times) / len(times)
+        line["cpu_baseline"] = {"value": wl.total / sec, "unit": "params/s", "cores": 1, "kind": "port",
+                                "sample": f"{len(times)} full steps of the same workload, 1 thread of "
+                                          f"{os.cpu_count()} host cores (Volta's optimizer is single threaded)",
+                                "ms_per_step": sec * 1e3}
+    opt.close()
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+def traffic_from_profile():
+    """DRAM bytes per launch of the Adam kernel from the committed ncu summary, if present."""
+    path = os.path.join(ROOT, "profiles", "adam_c3_ncu.json")
+    if os.path.exists(path):
+        try:
+            with open(path) as fh:
+                return json.load(fh).get("dram_bytes_per_launch")
+        except (OSError, ValueError):
+            return None
+    return None
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "ours":
+        args.warmup = 3
+    if args.impl == "reference":
+        return run_reference(args)
+    return run_ours(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,242 @@
+/*
+ * volta_b200 — C ABI of the B200 (sm_100a) optimizer-step engine for Volta.
+ *
+ * This is the whole boundary between Volta's optimizer types (Adam / SGD / Muon with
+ * step() and zero_grad()) and the CUDA implementation: plain pointers, sizes and
+ * scalars, no C++ or torch types.  A Rust, C++ or Python host binds exactly these
+ * symbols.  Each declaration names the reference interface (path:line inside
+ * rlarson20/Volta 0.3.0) it stands in for.
+ *
+ * Conventions
+ *  - Every function returns a vb_status (0 = ok).  Nothing aborts, throws or prints;
+ *    vb_last_error() gives the message of the calling thread's last failure.  (Volta's
+ *    own step() panics on invariant violations and silently drops a failed GPU
+ *    dispatch, src/nn/optim/adam.rs:127-129,164; here the caller gets a code.)
+ *  - One engine = one CUDA device + one stream.  All work of an engine is enqueued on
+ *    that stream in call order; calls return without waiting unless stated.  An engine
+ *    and its optimizers are used from one host thread at a time (Volta is single
+ *    threaded: Tensor = Rc<RefCell<_>>, src/tensor.rs:16-23).
+ *  - All tensors are contiguous row-major f32, as Volta's optimizers require
+ *    (src/storage.rs:269-281).
+ *  - There is no CPU fallback: without a usable CUDA device every call fails with
+ *    VB_ERR_CUDA.
+ */
+#ifndef VOLTA_B200_H
+#define VOLTA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum vb_status {
+    VB_OK = 0,
+    VB_ERR_INVALID_ARG = 1, /* null pointer, bad index, size mismatch, bad hyper-parameter */
+    VB_ERR_CUDA = 2,        /* a CUDA runtime/driver call failed (message has the code) */
+    VB_ERR_NCCL = 3,        /* NCCL missing or a collective failed */
+    VB_ERR_TIMEOUT = 4,     /* a bounded device-side wait gave up */
+    VB_ERR_STATE = 5,       /* call not valid in the object's current state */
+    VB_ERR_UNSUPPORTED = 6  /* shape or mode this build does not implement */
+} vb_status;
+
+typedef struct vb_engine vb_engine;
+typedef struct vb_optimizer vb_optimizer;
+
+/* Same field order, types and size (32 bytes) as Volta's OptimizerStepParams
+ * (src/gpu/kernels.rs:42-54), the uniform its WGSL kernel reads
+ * (src/gpu/shaders/optimizer_step.wgsl:8-17).  op: 0 SGD, 1 SGD+momentum, 2 Adam.
+ * beta1 doubles as the momentum coefficient for op 1; t is the time step as f32. */
+typedef struct vb_optimizer_step_params {
+    uint32_t op;
+    float lr;
+    float beta1;
+    float beta2;
+    float t;
+    float eps;
+    float weight_decay;
+    float padding;
+} vb_optimizer_step_params;
+
+/* Newton-Schulz arithmetic of a Muon optimizer. */
+typedef enum vb_ns_mode {
+    /* f32-faithful: sum of squares in the reference's sequential order
+     * (src/nn/optim/muon.rs:58), contraction accurate to f32, operations in the
+     * reference's order.  Target: relative Frobenius error <= 1e-5 per matrix. */
+    VB_NS_F32 = 0,
+    /* bf16 operands on the tcgen05 tensor cores, f32 accumulation in TMEM.
+     * Target: relative Frobenius error <= 2e-2 per matrix. */
+    VB_NS_BF16 = 1
+} vb_ns_mode;
+
+/* Flags of vb_optimizer_step_ex. */
+#define VB_STEP_DEFAULT 0u
+#define VB_STEP_NO_EXCHANGE 1u /* sharded engines: update the owned part only, skip the all-gather / broadcast */
+
+/* ---- library ---------------------------------------------------------------------- */
+
+/* ABI version of this header (major*1000 + minor). */
+int vb_abi_version(void);
+/* Message of the calling thread's most recent failing call ("" if none). */
+const char *vb_last_error(void);
+/* Number of CUDA devices visible (replaces is_gpu_available(), src/gpu/mod.rs:50-60). */
+int vb_device_count(int *count);
+
+/* Pure host planning, no CUDA call: the arena layout (element offset of every tensor,
+ * each on a 128-byte boundary), the arena slice [shard_begin, shard_end) that `rank` of
+ * `world_size` owns, and the chunk table (tensor, offset within tensor, length) that
+ * rank's fused Adam/SGD launch walks on a device with `sm_count` SMs.  Every output
+ * pointer may be NULL; chunk arrays need chunk_capacity >= *n_chunks (query first).
+ * This is exactly the plan vb_adam_create / vb_sgd_create use; it exists so that hosts
+ * and tests can check coverage (every element owned by exactly one rank and one chunk)
+ * without a GPU.  No counterpart in the reference (one dispatch per tensor,
+ * src/gpu/kernels.rs:2077-2078). */
+int vb_plan_layout(int64_t n_tensors, const int64_t *sizes, int world_size, int rank, int sm_count,
+                   int64_t *offsets_out, int64_t *arena_elements, int64_t *shard_begin,
+                   int64_t *shard_end, int64_t *n_chunks, int64_t chunk_capacity,
+                   int64_t *chunk_tensor, int64_t *chunk_offset, int64_t *chunk_len);
+
+/* ---- engine (replaces the process-global wgpu context, src/gpu/mod.rs:30-47) ----- */
+
+int vb_engine_create(int device, vb_engine **out);
+int vb_engine_destroy(vb_engine *engine);
+/* Blocks until everything enqueued so far has run (GpuContext::sync, src/gpu/context.rs:342-382). */
+int vb_engine_synchronize(vb_engine *engine);
+/* The engine's cudaStream_t, for callers that enqueue their own producers of gradients. */
+int vb_engine_stream(vb_engine *engine, void **cuda_stream);
+/* Kernels launched by this engine since creation (bookkeeping for benchmarks). */
+int vb_engine_launch_count(vb_engine *engine, uint64_t *count);
+
+/* Page-locked host memory for upload/download buffers (pinned buffers make the copies
+ * asynchronous and full speed; a pinned upload buffer must stay unchanged until the next
+ * vb_engine_synchronize or download).  Counterpart: the staging buffer pool,
+ * src/gpu/staging_pool.rs. */
+int vb_host_alloc_pinned(void **ptr, size_t bytes);
+int vb_host_free_pinned(void *ptr);
+
+/* Multi-GPU (no counterpart in the reference, which is single-process, README.md:61-62):
+ * one process per GPU; rank 0 makes an id, the host shares its 128 bytes with the other
+ * ranks by any means, every rank calls vb_engine_comm_init.  Optimizers created
+ * afterwards shard their state over the ranks (Adam/SGD: equal slices of the flat
+ * parameter arena; Muon: whole matrices by FLOPs) and exchange updated parameters with
+ * NCCL at the end of step(). */
+int vb_comm_unique_id(void *id128);
+int vb_engine_comm_init(vb_engine *engine, const void *id128, int rank, int world_size);
+int vb_engine_rank(vb_engine *engine, int *rank, int *world_size);
+
+/* ---- optimizer construction ------------------------------------------------------- */
+
+/* Adam::new(params, lr, betas, eps, weight_decay), src/nn/optim/adam.rs:18-60.
+ * sizes[i] = element count of parameter i.  The engine allocates flat device arenas for
+ * parameters, gradients and the moments m, v (zero-initialised, adam.rs:26-47), every
+ * tensor starting on a 128-byte boundary.  t starts at 0. */
+int vb_adam_create(vb_engine *engine, int64_t n_tensors, const int64_t *sizes, float lr,
+                   float beta1, float beta2, float eps, float weight_decay, vb_optimizer **out);
+
+/* SGD::new(params, lr, momentum, weight_decay), src/nn/optim/sgd.rs:28-52.  Velocity is
+ * allocated only when momentum > 0.0 (sgd.rs:30). */
+int vb_sgd_create(vb_engine *engine, int64_t n_tensors, const int64_t *sizes, float lr,
+                  float momentum, float weight_decay, vb_optimizer **out);
+
+/* Muon::new(params, lr, momentum, nesterov, ns_steps), src/nn/optim/muon.rs:19-38.
+ * rows[i], cols[i] are the 2-D view of parameter i that Muon::step derives from its
+ * shape (muon.rs:117-130): (shape[0], product of the rest), or (n, 1) for 1-D.
+ * Newton-Schulz runs only where rows > 1 and cols > 1 (muon.rs:153). */
+int vb_muon_create(vb_engine *engine, int64_t n_tensors, const int64_t *rows, const int64_t *cols,
+                   float lr, float momentum, int nesterov, int ns_steps, int ns_mode,
+                   vb_optimizer **out);
+
+int vb_optimizer_destroy(vb_optimizer *opt);
+
+/* ---- tensors of an optimizer ------------------------------------------------------ */
+
+int vb_optimizer_num_tensors(vb_optimizer *opt, int64_t *n_tensors);
+int vb_optimizer_tensor_size(vb_optimizer *opt, int64_t tensor, int64_t *n_elements);
+/* Sum of all tensor sizes. */
+int vb_optimizer_total_size(vb_optimizer *opt, int64_t *n_elements);
+
+/* Host <-> device copies of one parameter tensor (its `data`, src/tensor.rs:38-46).
+ * n must equal the tensor's size.  Uploads/downloads are enqueued on the engine stream;
+ * download blocks until the data is in `host`. `host` may be pageable or pinned. */
+int vb_optimizer_upload_params(vb_optimizer *opt, int64_t tensor, const float *host, int64_t n);
+int vb_optimizer_download_params(vb_optimizer *opt, int64_t tensor, float *host, int64_t n);
+
+/* Sets the gradient of one tensor from host memory and marks it present
+ * (`p.grad = Some(..)`, src/autograd.rs:140-148). */
+int vb_optimizer_upload_grad(vb_optimizer *opt, int64_t tensor, const float *host, int64_t n);
+int vb_optimizer_download_grad(vb_optimizer *opt, int64_t tensor, float *host, int64_t n);
+
+/* Device addresses (f32, 128-byte aligned) so producers can write gradients / read
+ * parameters in place without staging.  Valid until the optimizer is destroyed. */
+int vb_optimizer_param_ptr(vb_optimizer *opt, int64_t tensor, void **device_ptr);
+int vb_optimizer_grad_ptr(vb_optimizer *opt, int64_t tensor, void **device_ptr);
+
+/* Whole-arena access: all tensors in index order, each padded to a 128-byte boundary.
+ * offsets_out (n_tensors entries, may be NULL) receives each tensor's element offset. */
+int vb_optimizer_arena(vb_optimizer *opt, void **param_arena, void **grad_arena,
+                       int64_t *arena_elements, int64_t *offsets_out);
+/* Copies whole arenas between a host buffer of arena_elements floats and the device
+ * (one transfer instead of one per tensor).  which: 0 params, 1 grads.  Uploading grads
+ * marks every tensor's gradient present. */
+int vb_optimizer_upload_arena(vb_optimizer *opt, int which, const float *host, int64_t n);
+int vb_optimizer_download_arena(vb_optimizer *opt, int which, float *host, int64_t n);
+
+/* Presence of a gradient: step() skips tensors whose gradient is absent
+ * (src/nn/optim/adam.rs:81-84, sgd.rs:75-78, muon.rs:110). */
+int vb_optimizer_set_grad_present(vb_optimizer *opt, int64_t tensor, int present);
+
+/* ---- the hot path ----------------------------------------------------------------- */
+
+/* Adam::step / SGD::step / Muon::step (src/nn/optim/adam.rs:70-95, sgd.rs:69-90,
+ * muon.rs:108-163).  One call updates every tensor whose gradient is present: Adam and
+ * SGD in one fused multi-tensor launch, Muon as momentum/normalise -> Newton-Schulz GEMM
+ * chain -> apply.  Adam's t advances by one per call whether or not any gradient is
+ * present (adam.rs:71).  On a sharded engine the call ends with the parameter exchange.
+ * Work is enqueued; use vb_engine_synchronize or a download to wait. */
+int vb_optimizer_step(vb_optimizer *opt);
+int vb_optimizer_step_ex(vb_optimizer *opt, uint32_t flags);
+
+/* zero_grad(): marks every gradient absent (`grad = None`, src/nn/optim/adam.rs:62-66,
+ * sgd.rs:58-62, muon.rs:40-44).  The gradient arena itself is left as is. */
+int vb_optimizer_zero_grad(vb_optimizer *opt);
+
+/* Hyper-parameters can change between steps (learning-rate schedules). */
+int vb_optimizer_set_lr(vb_optimizer *opt, float lr);
+
+/* ---- optimizer state (private in the reference, src/nn/optim/adam.rs:5-14) -------- */
+
+/* which: 0 = first state (Adam m, SGD velocity, Muon velocity), 1 = Adam v.
+ * On a sharded engine only the owning rank holds a tensor's state: export returns the
+ * owned elements and zeros elsewhere, and reports the owned range. */
+int vb_optimizer_export_state(vb_optimizer *opt, int64_t tensor, int which, float *host, int64_t n,
+                              int64_t *owned_begin, int64_t *owned_end);
+int vb_optimizer_import_state(vb_optimizer *opt, int64_t tensor, int which, const float *host,
+                              int64_t n);
+int vb_optimizer_get_t(vb_optimizer *opt, int64_t *t);
+int vb_optimizer_set_t(vb_optimizer *opt, int64_t t);
+
+/* Muon only: copies the orthogonalised update of the last step for one tensor (the
+ * reference's local `update`, src/nn/optim/muon.rs:139-155) to the host. */
+int vb_muon_download_update(vb_optimizer *opt, int64_t tensor, float *host, int64_t n);
+/* Muon only: tensor-core FLOPs executed by the last step's Newton-Schulz chain. */
+int vb_muon_last_ns_flops(vb_optimizer *opt, double *flops);
+
+/* ---- caller-owned device buffers -------------------------------------------------- */
+
+/* Replaces n_tensors calls of RawTensor::gpu_optimizer_step(params, grads, state1,
+ * state2, &OptimizerStepParams) (src/ops/gpu_ops.rs:495-508, one wgpu dispatch per
+ * tensor, src/gpu/kernels.rs:2016-2086) by one fused launch over caller-owned device
+ * buffers.  params/grads/state1/state2 are host arrays of n_tensors device pointers;
+ * state2 entries (and, for op 0, state1 entries) may be NULL where the op does not use
+ * them.  hp->t is the step number the bias correction uses; it is computed on the host
+ * with the reference's CPU arithmetic (powi, src/nn/optim/adam.rs:188-189), not the
+ * shader's per-thread pow(). */
+int vb_multi_tensor_step(vb_engine *engine, const vb_optimizer_step_params *hp, int64_t n_tensors,
+                         const int64_t *sizes, void *const *params, const void *const *grads,
+                         void *const *state1, void *const *state2);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VOLTA_B200_H */

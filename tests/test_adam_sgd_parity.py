@@ -1,0 +1,303 @@
+"""GPU parity of the fused multi-tensor Adam / SGD path against the CPU oracle.
+
+Tolerances (BASELINE north star): max relative error on params, m and v <= 1e-6 after one
+step and <= 1e-5 after 100 steps.  The kernels are written to be bit-identical to the
+reference's CPU arithmetic, so most cases assert exact equality, which implies both.
+Everything goes through the C ABI (the ctypes mirror in volta_b200.optim).
+"""
+import json
+import os
+
+import numpy as np
+import pytest
+
+from helpers import bits_equal, max_rel_err
+
+pytestmark = pytest.mark.gpu
+
+TOL_ONE_STEP = 1e-6
+TOL_MANY_STEPS = 1e-5
+
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "volta_optimizer_kats.json")
+with open(GOLDEN) as fh:
+    KATS = json.load(fh)
+
+
+def _scalar(t):
+    return float(t.data.reshape(-1)[0])
+
+
+# ---- the reference's own optimizer tests, replayed through the drop-in API ----------------
+
+@pytest.mark.parametrize("case", [c for c in KATS if c["kind"] in ("adam", "sgd")], ids=lambda c: c["name"])
+def test_reference_known_answers(engine, case):
+    """tests/test_optimizers.rs / tests/coverage_fill.rs / src/lib.rs:3102-3119."""
+    from volta_b200 import SGD, Adam, Tensor
+    t = Tensor([case["theta0"]], (1,), True)
+    t.grad = [case["grad"]]
+    if case["kind"] == "adam":
+        opt = Adam([t], case["lr"], tuple(case["betas"]), case["eps"], case["weight_decay"], engine=engine)
+    else:
+        opt = SGD([t], case["lr"], case["momentum"], case["weight_decay"], engine=engine)
+    for step in range(case["steps"]):
+        opt.step()  # the gradient persists across steps, as in test_sgd_no_momentum_simple
+        actual, expected = _scalar(t), case["expected"][step]
+        if "tol_rel" in case:
+            assert abs(actual - expected) <= case["tol_rel"] * abs(expected)
+        else:
+            assert abs(actual - expected) < case["tol_abs"], (actual, expected)
+    opt.close()
+
+
+def test_adam_convergence_convex(engine):
+    """tests/test_optimizers.rs:142-162: minimise (x-3)^2, lr 0.05, 500 steps."""
+    from volta_b200 import Adam, Tensor
+    x = Tensor([0.0], (1,))
+    opt = Adam([x], 0.05, (0.9, 0.999), 1e-8, 0.0, engine=engine)
+    for _ in range(500):
+        opt.zero_grad()
+        x.grad = 2.0 * (x.data - 3.0)
+        opt.step()
+    assert abs(_scalar(x) - 3.0) < 0.05
+    opt.close()
+
+
+def test_sgd_convergence_convex(engine):
+    """tests/test_optimizers.rs:225-245: momentum 0.9, lr 0.05, 500 steps."""
+    from volta_b200 import SGD, Tensor
+    x = Tensor([0.0], (1,))
+    opt = SGD([x], 0.05, 0.9, 0.0, engine=engine)
+    for _ in range(500):
+        opt.zero_grad()
+        x.grad = 2.0 * (x.data - 3.0)
+        opt.step()
+    assert abs(_scalar(x) - 3.0) < 0.05
+    opt.close()
+
+
+# ---- configuration-level parity ------------------------------------------------------------
+
+def _run_both(oracle, engine, wl, steps, check_at=(1,), drop=None):
+    """Runs `steps` steps of workload `wl` on the oracle and on the GPU with identical
+    inputs; returns max relative errors of (params, state1, state2) at the checked steps."""
+    from volta_b200 import SGD, Adam, Tensor
+    params = wl.make_params()
+    ref_params = [p.copy() for p in params]
+    tensors = [Tensor(p, p.shape) for p in params]
+    h = wl.hyper
+    if wl.optimizer == "adam":
+        ref = oracle.Adam(ref_params, h["lr"], h["betas"], h["eps"], h["weight_decay"])
+        opt = Adam(tensors, h["lr"], h["betas"], h["eps"], h["weight_decay"], engine=engine)
+    else:
+        ref = oracle.SGD(ref_params, h["lr"], h["momentum"], h["weight_decay"])
+        opt = SGD(tensors, h["lr"], h["momentum"], h["weight_decay"], engine=engine)
+    out = {}
+    for s in range(1, steps + 1):
+        grads = wl.make_grads(s)
+        if drop is not None:
+            grads = [None if drop(i, s) else g for i, g in enumerate(grads)]
+        opt.zero_grad()
+        for t, g in zip(tensors, grads):
+            if g is not None:
+                t.grad = g
+        opt.step()
+        ref.step(grads)
+        if s in check_at or s == steps:
+            ep = max(max_rel_err(t.data, r) for t, r in zip(tensors, ref_params))
+            exact = all(bits_equal(t.data, r) for t, r in zip(tensors, ref_params))
+            es1 = es2 = 0.0
+            if wl.optimizer == "adam":
+                es1 = max(max_rel_err(opt.state(i, 0), ref.m[i]) for i in range(len(tensors)))
+                es2 = max(max_rel_err(opt.state(i, 1), ref.v[i]) for i in range(len(tensors)))
+                exact = exact and all(bits_equal(opt.state(i, 0), ref.m[i]) and
+                                      bits_equal(opt.state(i, 1), ref.v[i]) for i in range(len(tensors)))
+            elif ref.velocity:
+                es1 = max(max_rel_err(opt.state(i, 0), ref.velocity[i]) for i in range(len(tensors)))
+                exact = exact and all(bits_equal(opt.state(i, 0), ref.velocity[i]) for i in range(len(tensors)))
+            out[s] = (ep, es1, es2, exact)
+    if wl.optimizer == "adam":
+        assert opt.t == ref.t == steps
+    opt.close()
+    return out
+
+
+def test_c1_mlp_adam_100_steps(oracle, engine):
+    import workloads
+    wl = workloads.c1_mlp_adam()
+    res = _run_both(oracle, engine, wl, 100, check_at=(1, 3, 10))
+    assert max(res[1][:3]) <= TOL_ONE_STEP
+    assert max(res[100][:3]) <= TOL_MANY_STEPS
+    assert all(r[3] for r in res.values()), res  # in fact bit-identical at every checked step
+
+
+def test_c2_cnn_sgd_200_steps(oracle, engine):
+    import workloads
+    wl = workloads.c2_cnn_sgd()
+    res = _run_both(oracle, engine, wl, 200, check_at=(1, 100))
+    assert max(res[1][:3]) <= TOL_ONE_STEP
+    assert max(res[200][:3]) <= TOL_MANY_STEPS
+    assert all(r[3] for r in res.values()), res
+
+
+@pytest.mark.parametrize("kind,momentum,wd", [("adam", 0.0, 0.0), ("adam", 0.0, 0.1),
+                                              ("sgd", 0.0, 0.0), ("sgd", 0.0, 0.05),
+                                              ("sgd", 0.9, 0.0), ("sgd", 0.9, 5e-4)])
+def test_ragged_sizes_every_length_1_to_70(oracle, engine, kind, momentum, wd):
+    """Tiny tensors of every length (vector body + scalar tail), all in one launch."""
+    import workloads
+    shapes = [(n,) for n in range(1, 71)] + [(0,), (257,), (4099,), (3, 5, 7)]
+    hyper = dict(lr=1e-2, betas=(0.9, 0.999), eps=1e-8, weight_decay=wd, momentum=momentum)
+    wl = workloads.Workload("ragged_small", kind, shapes, [("normal", 1.0)] * len(shapes), 1e-1, hyper, 5)
+    res = _run_both(oracle, engine, wl, 5)
+    assert all(r[3] for r in res.values()), res
+
+
+def test_missing_gradients_are_skipped_and_t_advances(oracle, engine):
+    """adam.rs:71,81-84: a parameter without a gradient keeps theta, m and v; t still counts."""
+    import workloads
+    shapes = [(1000,), (33,), (5000,), (7,)]
+    hyper = dict(lr=1e-2, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01)
+    wl = workloads.Workload("skip", "adam", shapes, [("normal", 1.0)] * 4, 1e-1, hyper, 6)
+    res = _run_both(oracle, engine, wl, 6, check_at=(1, 2, 3), drop=lambda i, s: (i + s) % 3 == 0)
+    assert all(r[3] for r in res.values()), res
+
+
+def test_c5_ragged_reduced(oracle, engine):
+    """The ragged stress shape law (log-uniform sizes) at a size the oracle finishes quickly:
+    512 tensors in [1, 2^18], lr 3e-4, wd 0.1, 10 steps."""
+    import workloads
+    wl = workloads.c5_ragged_adam(n_tensors=512, max_log2=18, seed=4096)
+    res = _run_both(oracle, engine, wl, 10, check_at=(1,))
+    assert max(res[1][:3]) <= TOL_ONE_STEP and max(res[10][:3]) <= TOL_MANY_STEPS
+    assert all(r[3] for r in res.values()), res
+
+
+def test_c3_full_size_two_steps(oracle, engine):
+    """The 109 602 816-parameter Adam set at full size: two steps, whole-arena comparison."""
+    import workloads
+    from volta_b200 import Adam, Tensor
+    wl = workloads.c3_transformer_adam()
+    assert wl.total == 109_602_816 and len(wl.shapes) == 157
+    params = wl.make_params()
+    ref_params = [p.copy() for p in params]
+    tensors = [Tensor(p, p.shape) for p in params]
+    h = wl.hyper
+    opt = Adam(tensors, h["lr"], h["betas"], h["eps"], h["weight_decay"], engine=engine)
+    ref = oracle.Adam(ref_params, h["lr"], h["betas"], h["eps"], h["weight_decay"])
+    _, _, arena, offsets = opt.arena_layout()
+    host = np.zeros(arena, np.float32)
+    for s in (1, 2):
+        grads = wl.make_grads(s)
+        for o, g in zip(offsets, grads):
+            host[o:o + g.size] = g.reshape(-1)
+        opt.upload_arena(1, host)
+        opt.step()
+        ref.step(grads)
+    opt.download_arena(0, host)
+    for o, r in zip(offsets, ref_params):
+        assert bits_equal(host[o:o + r.size], r)
+    for i in (0, 1, 5, 156):
+        assert bits_equal(opt.state(i, 0), ref.m[i]) and bits_equal(opt.state(i, 1), ref.v[i])
+    # linearity-free size-independent property: padding between tensors stays zero
+    mask = np.ones(arena, bool)
+    for o, r in zip(offsets, ref_params):
+        mask[o:o + r.size] = False
+    assert not host[mask].any()
+    opt.close()
+
+
+def test_state_import_export_and_t(engine, oracle):
+    """Resume: exported m, v, t imported into a fresh optimizer continue bit-identically."""
+    from volta_b200 import Adam, Tensor
+    rng = np.random.default_rng(7)
+    p0 = rng.standard_normal(5000).astype(np.float32)
+    grads = [(rng.standard_normal(5000) * 0.01).astype(np.float32) for _ in range(4)]
+    a = Tensor(p0.copy())
+    opt_a = Adam([a], 1e-3, (0.9, 0.999), 1e-8, 0.01, engine=engine)
+    for g in grads[:2]:
+        a.grad = g
+        opt_a.step()
+    b = Tensor(a.data.copy())
+    opt_b = Adam([b], 1e-3, (0.9, 0.999), 1e-8, 0.01, engine=engine)
+    opt_b.load_state(0, 0, opt_a.state(0, 0))
+    opt_b.load_state(0, 1, opt_a.state(0, 1))
+    opt_b.t = opt_a.t
+    for g in grads[2:]:
+        a.grad = g
+        b.grad = g
+        opt_a.step()
+        opt_b.step()
+    assert bits_equal(a.data, b.data)
+    opt_a.close()
+    opt_b.close()
+
+
+# ---- caller-owned buffers: the per-tensor gpu_optimizer_step seam, fused -------------------
+
+@pytest.mark.parametrize("op", [0, 1, 2])
+def test_multi_tensor_step_on_caller_buffers(oracle, engine, op):
+    """vb_multi_tensor_step on torch-allocated device buffers, including tensors whose
+    addresses are only 4-byte aligned (scalar path)."""
+    import torch
+    from volta_b200 import multi_tensor_step
+    rng = np.random.default_rng(op)
+    sizes = [1, 5, 1024, 4097, 70001, 333]
+    dev = torch.device("cuda:0")
+    pool = torch.zeros(4 * (sum(sizes) + 64 * len(sizes)), device=dev)  # carve misaligned views
+    cursor = 0
+    views = {k: [] for k in "pgab"}
+    host = {k: [] for k in "pgab"}
+    for i, n in enumerate(sizes):
+        for k in "pgab":
+            start = cursor + (i % 4 if k in "pg" else (i + 1) % 4)  # different misalignments
+            v = pool[start:start + n]
+            cursor = start + n + 16
+            cursor += (-cursor) % 4
+            if k == "p":
+                x = rng.standard_normal(n).astype(np.float32)
+            elif k == "g":
+                x = (rng.standard_normal(n) * 0.1).astype(np.float32)
+            else:
+                x = (np.abs(rng.standard_normal(n)) * 0.01).astype(np.float32)
+            v.copy_(torch.from_numpy(x))
+            views[k].append(v)
+            host[k].append(x)
+    torch.cuda.synchronize()
+    lr, b1, b2, eps, wd, t = 1e-2, 0.9, 0.999, 1e-8, 0.01, 7
+    multi_tensor_step(engine, op, sizes, [v.data_ptr() for v in views["p"]],
+                      [v.data_ptr() for v in views["g"]],
+                      [v.data_ptr() for v in views["a"]] if op >= 1 else None,
+                      [v.data_ptr() for v in views["b"]] if op == 2 else None,
+                      lr=lr, beta1=b1, beta2=b2, t=t, eps=eps, weight_decay=wd)
+    engine.synchronize()
+    for i, n in enumerate(sizes):
+        p, g, a, b = (host[k][i].copy() for k in "pgab")
+        if op == 2:
+            o = oracle.Adam([p], lr, (b1, b2), eps, wd)
+            o.m[0][:], o.v[0][:], o.t = a, b, t - 1
+            o.step([g])
+            assert bits_equal(views["a"][i].cpu().numpy(), o.m[0])
+            assert bits_equal(views["b"][i].cpu().numpy(), o.v[0])
+        else:
+            o = oracle.SGD([p], lr, b1 if op == 1 else 0.0, wd)
+            if op == 1:
+                o.velocity[0][:] = a
+            o.step([g])
+            if op == 1:
+                assert bits_equal(views["a"][i].cpu().numpy(), o.velocity[0])
+        assert bits_equal(views["p"][i].cpu().numpy(), p)
+        assert bits_equal(views["g"][i].cpu().numpy(), host["g"][i])  # gradients are read-only
+
+
+def test_errors_are_reported_not_fatal(engine):
+    from volta_b200 import Adam, Tensor, VoltaB200Error, multi_tensor_step
+    t = Tensor(np.zeros(8, np.float32))
+    opt = Adam([t], 1e-3, engine=engine)
+    with pytest.raises(ValueError):
+        t.grad = np.zeros(9, np.float32)
+    with pytest.raises(VoltaB200Error) as ei:
+        opt.load_state(0, 5, np.zeros(8, np.float32))
+    assert ei.value.status == 1
+    with pytest.raises(VoltaB200Error):
+        multi_tensor_step(engine, 2, [8], [0], [0], [0], [0], lr=1e-3, t=1)
+    opt.close()

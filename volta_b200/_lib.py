@@ -1,0 +1,125 @@
+"""ctypes binding of ``libvolta_b200.so`` (the C ABI of ``include/volta_b200.h``).
+
+There is no fallback of any kind: if the shared library is missing or a call fails,
+an exception is raised.  Nothing here computes optimizer arithmetic on the host.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libvolta_b200.so")
+
+STATUS_NAMES = {
+    0: "VB_OK", 1: "VB_ERR_INVALID_ARG", 2: "VB_ERR_CUDA", 3: "VB_ERR_NCCL",
+    4: "VB_ERR_TIMEOUT", 5: "VB_ERR_STATE", 6: "VB_ERR_UNSUPPORTED",
+}
+
+VB_NS_F32 = 0
+VB_NS_BF16 = 1
+VB_STEP_DEFAULT = 0
+VB_STEP_NO_EXCHANGE = 1
+
+
+class VoltaB200Error(RuntimeError):
+    """A C-ABI call returned a non-zero status."""
+
+    def __init__(self, status: int, message: str):
+        super().__init__(f"{STATUS_NAMES.get(status, status)}: {message}")
+        self.status = status
+        self.message = message
+
+
+class StepParams(C.Structure):
+    """Mirror of ``vb_optimizer_step_params`` (Volta's ``OptimizerStepParams``)."""
+
+    _fields_ = [("op", C.c_uint32), ("lr", C.c_float), ("beta1", C.c_float), ("beta2", C.c_float),
+                ("t", C.c_float), ("eps", C.c_float), ("weight_decay", C.c_float),
+                ("padding", C.c_float)]
+
+
+_vp = C.c_void_p
+_i64 = C.c_int64
+_i64p = C.POINTER(C.c_int64)
+_f32p = C.POINTER(C.c_float)
+_vpp = C.POINTER(C.c_void_p)
+
+# name -> argtypes; every function returns int (vb_status) except where noted below.
+SIGNATURES = {
+    "vb_device_count": [C.POINTER(C.c_int)],
+    "vb_plan_layout": [_i64, _i64p, C.c_int, C.c_int, C.c_int, _i64p, _i64p, _i64p, _i64p, _i64p, _i64,
+                       _i64p, _i64p, _i64p],
+    "vb_engine_create": [C.c_int, _vpp],
+    "vb_engine_destroy": [_vp],
+    "vb_engine_synchronize": [_vp],
+    "vb_engine_stream": [_vp, _vpp],
+    "vb_engine_launch_count": [_vp, C.POINTER(C.c_uint64)],
+    "vb_host_alloc_pinned": [_vpp, C.c_size_t],
+    "vb_host_free_pinned": [_vp],
+    "vb_comm_unique_id": [_vp],
+    "vb_engine_comm_init": [_vp, _vp, C.c_int, C.c_int],
+    "vb_engine_rank": [_vp, C.POINTER(C.c_int), C.POINTER(C.c_int)],
+    "vb_adam_create": [_vp, _i64, _i64p, C.c_float, C.c_float, C.c_float, C.c_float, C.c_float, _vpp],
+    "vb_sgd_create": [_vp, _i64, _i64p, C.c_float, C.c_float, C.c_float, _vpp],
+    "vb_muon_create": [_vp, _i64, _i64p, _i64p, C.c_float, C.c_float, C.c_int, C.c_int, C.c_int, _vpp],
+    "vb_optimizer_destroy": [_vp],
+    "vb_optimizer_num_tensors": [_vp, _i64p],
+    "vb_optimizer_tensor_size": [_vp, _i64, _i64p],
+    "vb_optimizer_total_size": [_vp, _i64p],
+    "vb_optimizer_upload_params": [_vp, _i64, _vp, _i64],
+    "vb_optimizer_download_params": [_vp, _i64, _vp, _i64],
+    "vb_optimizer_upload_grad": [_vp, _i64, _vp, _i64],
+    "vb_optimizer_download_grad": [_vp, _i64, _vp, _i64],
+    "vb_optimizer_param_ptr": [_vp, _i64, _vpp],
+    "vb_optimizer_grad_ptr": [_vp, _i64, _vpp],
+    "vb_optimizer_arena": [_vp, _vpp, _vpp, _i64p, _i64p],
+    "vb_optimizer_upload_arena": [_vp, C.c_int, _vp, _i64],
+    "vb_optimizer_download_arena": [_vp, C.c_int, _vp, _i64],
+    "vb_optimizer_set_grad_present": [_vp, _i64, C.c_int],
+    "vb_optimizer_step": [_vp],
+    "vb_optimizer_step_ex": [_vp, C.c_uint32],
+    "vb_optimizer_zero_grad": [_vp],
+    "vb_optimizer_set_lr": [_vp, C.c_float],
+    "vb_optimizer_export_state": [_vp, _i64, C.c_int, _vp, _i64, _i64p, _i64p],
+    "vb_optimizer_import_state": [_vp, _i64, C.c_int, _vp, _i64],
+    "vb_optimizer_get_t": [_vp, _i64p],
+    "vb_optimizer_set_t": [_vp, _i64],
+    "vb_muon_download_update": [_vp, _i64, _vp, _i64],
+    "vb_muon_last_ns_flops": [_vp, C.POINTER(C.c_double)],
+    "vb_multi_tensor_step": [_vp, C.POINTER(StepParams), _i64, _i64p, _vpp, _vpp, _vpp, _vpp],
+}
+OTHER_SYMBOLS = ["vb_abi_version", "vb_last_error"]
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """Loads the shared library (once).  Raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python volta_b200/build.py` "
+            "(nvcc, sm_100a).  volta_b200 has no CPU or PyTorch fallback.")
+    lib = C.CDLL(LIB_PATH)
+    for name, argtypes in SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.argtypes = argtypes
+        fn.restype = C.c_int
+    lib.vb_abi_version.restype = C.c_int
+    lib.vb_abi_version.argtypes = []
+    lib.vb_last_error.restype = C.c_char_p
+    lib.vb_last_error.argtypes = []
+    _lib = lib
+    return lib
+
+
+def check(status: int) -> None:
+    if status != 0:
+        raise VoltaB200Error(status, load().vb_last_error().decode("utf-8", "replace"))
+
+
+def call(name: str, *args) -> None:
+    check(getattr(load(), name)(*args))

@@ -1,0 +1,848 @@
+// C ABI entry points (include/volta_b200.h): engine, optimizer construction, tensor
+// access, step().  The arithmetic lives in multi_tensor.cu (Adam/SGD) and muon.cu.
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <algorithm>
+#include <new>
+
+#include "engine.h"
+
+namespace vb {
+
+static thread_local char g_err[1024] = "";
+
+void set_error(const char *fmt, ...)
+{
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+
+int fail(int code, const char *fmt, ...)
+{
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+constexpr int64_t kTensorAlign = 32;   // elements: every tensor starts on a 128-byte boundary
+constexpr int64_t kShardAlign = 256;   // elements: every rank's slice starts on a 1 KiB boundary
+
+static int64_t round_up(int64_t x, int64_t q) { return (x + q - 1) / q * q; }
+
+static int check_opt(const vb_optimizer *opt)
+{
+    if (!opt || !opt->eng) return fail(VB_ERR_INVALID_ARG, "optimizer handle is null");
+    return VB_OK;
+}
+
+static int check_tensor(const vb_optimizer *opt, int64_t tensor, int64_t n, bool check_n)
+{
+    VB_TRY(check_opt(opt));
+    if (tensor < 0 || tensor >= opt->n_tensors)
+        return fail(VB_ERR_INVALID_ARG, "tensor index %lld out of range [0, %lld)", (long long)tensor,
+                    (long long)opt->n_tensors);
+    if (check_n && n != opt->sizes[tensor])
+        return fail(VB_ERR_INVALID_ARG, "tensor %lld has %lld elements, caller passed %lld",
+                    (long long)tensor, (long long)opt->sizes[tensor], (long long)n);
+    return VB_OK;
+}
+
+static int set_device(const vb_engine *e)
+{
+    VB_CUDA(cudaSetDevice(e->device));
+    return VB_OK;
+}
+
+// ---- pure host planning (no CUDA call): arena layout, rank slices, chunk table ------------
+
+struct Layout {
+    std::vector<int64_t> offsets;
+    int64_t total = 0, arena = 0, shard_begin = 0, shard_end = 0, chunk_len = 0;
+    std::vector<ChunkDesc> chunks;
+};
+
+static void plan_layout(int64_t n_tensors, const int64_t *sizes, int world, int rank, int sm_count,
+                        bool shard, Layout *L)
+{
+    L->offsets.resize((size_t)n_tensors);
+    int64_t off = 0;
+    L->total = 0;
+    for (int64_t i = 0; i < n_tensors; ++i) {
+        L->offsets[(size_t)i] = off;
+        off += round_up(sizes[i], kTensorAlign);
+        L->total += sizes[i];
+    }
+    L->arena = round_up(std::max<int64_t>(off, 1), kShardAlign * world);
+    if (shard) {
+        const int64_t per = L->arena / world;
+        L->shard_begin = per * rank;
+        L->shard_end = L->shard_begin + per;
+    } else {
+        L->shard_begin = 0;
+        L->shard_end = L->arena;
+    }
+    int64_t owned = 0;
+    for (int64_t i = 0; i < n_tensors; ++i) {
+        const int64_t lo = std::max(L->offsets[(size_t)i], L->shard_begin);
+        const int64_t hi = std::min(L->offsets[(size_t)i] + sizes[i], L->shard_end);
+        if (hi > lo) owned += hi - lo;
+    }
+    L->chunk_len = pick_chunk_len(owned, sm_count);
+    L->chunks.clear();
+    for (int64_t i = 0; i < n_tensors; ++i) {
+        const int64_t o = L->offsets[(size_t)i];
+        const int64_t lo = std::max(o, L->shard_begin);
+        const int64_t hi = std::min(o + sizes[i], L->shard_end);
+        for (int64_t b = lo; b < hi; b += L->chunk_len) {
+            ChunkDesc c;
+            c.offset = b - o;
+            c.tensor = (uint32_t)i;
+            c.len = (uint32_t)std::min(L->chunk_len, hi - b);
+            L->chunks.push_back(c);
+        }
+    }
+}
+
+// Allocates the arenas of an optimizer from its layout.
+static int build_arena(vb_optimizer *opt, int n_state_buffers, bool shard_states, Layout *L)
+{
+    vb_engine *e = opt->eng;
+    VB_TRY(set_device(e));
+    plan_layout(opt->n_tensors, opt->sizes.data(), e->world, e->rank, e->sm_count, shard_states, L);
+    opt->offsets = L->offsets;
+    opt->total = L->total;
+    opt->arena = L->arena;
+    opt->shard_begin = L->shard_begin;
+    opt->shard_end = L->shard_end;
+    const size_t arena_bytes = (size_t)opt->arena * sizeof(float);
+    VB_CUDA(cudaMalloc(&opt->d_param, arena_bytes));
+    VB_CUDA(cudaMalloc(&opt->d_grad, arena_bytes));
+    VB_CUDA(cudaMemsetAsync(opt->d_param, 0, arena_bytes, e->stream));
+    VB_CUDA(cudaMemsetAsync(opt->d_grad, 0, arena_bytes, e->stream));
+    opt->state_elems = opt->shard_end - opt->shard_begin;
+    const size_t state_bytes = (size_t)opt->state_elems * sizeof(float);
+    if (n_state_buffers >= 1) {  // Storage::new_zeros, adam.rs:26-47 / sgd.rs:30-41
+        VB_CUDA(cudaMalloc(&opt->d_s1, state_bytes));
+        VB_CUDA(cudaMemsetAsync(opt->d_s1, 0, state_bytes, e->stream));
+    }
+    if (n_state_buffers >= 2) {
+        VB_CUDA(cudaMalloc(&opt->d_s2, state_bytes));
+        VB_CUDA(cudaMemsetAsync(opt->d_s2, 0, state_bytes, e->stream));
+    }
+    opt->present.assign((size_t)std::max<int64_t>(opt->n_tensors, 1), 0);
+    opt->present_on_dev = opt->present;
+    VB_CUDA(cudaMalloc(&opt->d_present, opt->present.size()));
+    VB_CUDA(cudaMemsetAsync(opt->d_present, 0, opt->present.size(), e->stream));
+    return VB_OK;
+}
+
+static int build_chunk_table(vb_optimizer *opt, const Layout &L)
+{
+    vb_engine *e = opt->eng;
+    std::vector<TensorDesc> tds((size_t)std::max<int64_t>(opt->n_tensors, 1));
+    for (int64_t i = 0; i < opt->n_tensors; ++i) {
+        const int64_t off = opt->offsets[(size_t)i];
+        TensorDesc &td = tds[(size_t)i];
+        td.p = opt->d_param + off;
+        td.g = opt->d_grad + off;
+        // state arrays start at shard_begin: bias the pointers so that index i of the
+        // tensor addresses the state of arena element off + i
+        const intptr_t bias = (intptr_t)(off - opt->shard_begin) * (intptr_t)sizeof(float);
+        td.s1 = opt->d_s1 ? (float *)((intptr_t)opt->d_s1 + bias) : nullptr;
+        td.s2 = opt->d_s2 ? (float *)((intptr_t)opt->d_s2 + bias) : nullptr;
+    }
+    opt->n_chunks = (int64_t)L.chunks.size();
+    VB_CUDA(cudaMalloc(&opt->d_tensors, tds.size() * sizeof(TensorDesc)));
+    VB_CUDA(cudaMemcpyAsync(opt->d_tensors, tds.data(), tds.size() * sizeof(TensorDesc),
+                            cudaMemcpyHostToDevice, e->stream));
+    if (!L.chunks.empty()) {
+        VB_CUDA(cudaMalloc(&opt->d_chunks, L.chunks.size() * sizeof(ChunkDesc)));
+        VB_CUDA(cudaMemcpyAsync(opt->d_chunks, L.chunks.data(), L.chunks.size() * sizeof(ChunkDesc),
+                                cudaMemcpyHostToDevice, e->stream));
+    }
+    VB_CUDA(cudaStreamSynchronize(e->stream));  // the host vectors go out of scope
+    return VB_OK;
+}
+
+static int validate_sizes(int64_t n_tensors, const int64_t *sizes)
+{
+    if (n_tensors < 0) return fail(VB_ERR_INVALID_ARG, "n_tensors is negative");
+    if (n_tensors > 0 && !sizes) return fail(VB_ERR_INVALID_ARG, "sizes is null");
+    if (n_tensors > (int64_t)1 << 30) return fail(VB_ERR_INVALID_ARG, "too many tensors");
+    for (int64_t i = 0; i < n_tensors; ++i) {
+        if (sizes[i] < 0) return fail(VB_ERR_INVALID_ARG, "sizes[%lld] is negative", (long long)i);
+        // a chunk's offset/len and Volta's own cap (1e8 elements, src/tensor.rs:125-129)
+        if (sizes[i] > ((int64_t)1 << 40))
+            return fail(VB_ERR_INVALID_ARG, "sizes[%lld] is too large", (long long)i);
+    }
+    return VB_OK;
+}
+
+static void free_optimizer(vb_optimizer *opt)
+{
+    if (!opt) return;
+    if (opt->eng) cudaSetDevice(opt->eng->device);
+    if (opt->muon) destroy_muon_state(opt->muon);
+    cudaFree(opt->d_param);
+    cudaFree(opt->d_grad);
+    cudaFree(opt->d_s1);
+    cudaFree(opt->d_s2);
+    cudaFree(opt->d_tensors);
+    cudaFree(opt->d_chunks);
+    cudaFree(opt->d_present);
+    delete opt;
+}
+
+static int create_elementwise(vb_engine *engine, int kind, int64_t n_tensors, const int64_t *sizes,
+                              int n_states, vb_optimizer **out, vb_optimizer **tmp)
+{
+    if (!engine) return fail(VB_ERR_INVALID_ARG, "engine is null");
+    if (!out) return fail(VB_ERR_INVALID_ARG, "out is null");
+    *out = nullptr;
+    VB_TRY(validate_sizes(n_tensors, sizes));
+    vb_optimizer *opt = new (std::nothrow) vb_optimizer();
+    if (!opt) return fail(VB_ERR_STATE, "out of host memory");
+    *tmp = opt;
+    opt->eng = engine;
+    opt->kind = kind;
+    opt->n_tensors = n_tensors;
+    opt->sizes.assign(sizes, sizes + n_tensors);
+    Layout L;
+    VB_TRY(build_arena(opt, n_states, /*shard_states=*/true, &L));
+    VB_TRY(build_chunk_table(opt, L));
+    return VB_OK;
+}
+
+}  // namespace vb
+
+using namespace vb;
+
+#define VB_API_BEGIN try {
+#define VB_API_END                                                         \
+    }                                                                      \
+    catch (const std::bad_alloc &) { return fail(VB_ERR_STATE, "out of host memory"); } \
+    catch (const std::exception &ex) { return fail(VB_ERR_STATE, "exception: %s", ex.what()); } \
+    catch (...) { return fail(VB_ERR_STATE, "unknown exception"); }
+
+extern "C" {
+
+int vb_abi_version(void) { return 1000; }
+
+const char *vb_last_error(void) { return g_err; }
+
+int vb_device_count(int *count)
+{
+    if (!count) return fail(VB_ERR_INVALID_ARG, "count is null");
+    *count = 0;
+    VB_CUDA(cudaGetDeviceCount(count));
+    return VB_OK;
+}
+
+int vb_plan_layout(int64_t n_tensors, const int64_t *sizes, int world_size, int rank, int sm_count,
+                   int64_t *offsets_out, int64_t *arena_elements, int64_t *shard_begin, int64_t *shard_end,
+                   int64_t *n_chunks, int64_t chunk_capacity, int64_t *chunk_tensor, int64_t *chunk_offset,
+                   int64_t *chunk_len)
+{
+    VB_API_BEGIN
+    VB_TRY(validate_sizes(n_tensors, sizes));
+    if (world_size < 1 || rank < 0 || rank >= world_size || sm_count < 1)
+        return fail(VB_ERR_INVALID_ARG, "rank %d / world_size %d / sm_count %d is not valid", rank, world_size,
+                    sm_count);
+    Layout L;
+    plan_layout(n_tensors, sizes, world_size, rank, sm_count, true, &L);
+    if (offsets_out)
+        for (int64_t i = 0; i < n_tensors; ++i) offsets_out[i] = L.offsets[(size_t)i];
+    if (arena_elements) *arena_elements = L.arena;
+    if (shard_begin) *shard_begin = L.shard_begin;
+    if (shard_end) *shard_end = L.shard_end;
+    if (n_chunks) *n_chunks = (int64_t)L.chunks.size();
+    if (chunk_tensor || chunk_offset || chunk_len) {
+        if (chunk_capacity < (int64_t)L.chunks.size())
+            return fail(VB_ERR_INVALID_ARG, "chunk_capacity %lld is less than the %lld chunks of the plan",
+                        (long long)chunk_capacity, (long long)L.chunks.size());
+        for (size_t c = 0; c < L.chunks.size(); ++c) {
+            if (chunk_tensor) chunk_tensor[c] = L.chunks[c].tensor;
+            if (chunk_offset) chunk_offset[c] = L.chunks[c].offset;
+            if (chunk_len) chunk_len[c] = L.chunks[c].len;
+        }
+    }
+    return VB_OK;
+    VB_API_END
+}
+
+int vb_engine_create(int device, vb_engine **out)
+{
+    VB_API_BEGIN
+    if (!out) return fail(VB_ERR_INVALID_ARG, "out is null");
+    *out = nullptr;
+    int count = 0;
+    VB_CUDA(cudaGetDeviceCount(&count));
+    if (device < 0 || device >= count)
+        return fail(VB_ERR_INVALID_ARG, "device %d out of range (%d visible)", device, count);
+    VB_CUDA(cudaSetDevice(device));
+    cudaDeviceProp prop;
+    VB_CUDA(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10)
+        return fail(VB_ERR_UNSUPPORTED, "device %d is sm_%d%d; this library is built for sm_100a only",
+                    device, prop.major, prop.minor);
+    vb_engine *e = new vb_engine();
+    e->device = device;
+    e->sm_count = prop.multiProcessorCount;
+    cudaError_t err = cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking);
+    if (err != cudaSuccess) {
+        delete e;
+        return fail(VB_ERR_CUDA, "cudaStreamCreate failed: %s", cudaGetErrorString(err));
+    }
+    *out = e;
+    return VB_OK;
+    VB_API_END
+}
+
+int vb_engine_destroy(vb_engine *e)
+{
+    if (!e) return VB_OK;
+    cudaSetDevice(e->device);
+    if (e->stream) cudaStreamSynchronize(e->stream);
+    comm_destroy(e);
+    for (int i = 0; i < 2; ++i) {
+        if (e->h_stage[i]) cudaFreeHost(e->h_stage[i]);
+        if (e->d_stage[i]) cudaFree(e->d_stage[i]);
+        if (e->stage_done[i]) cudaEventDestroy(e->stage_done[i]);
+    }
+    if (e->stream) cudaStreamDestroy(e->stream);
+    delete e;
+    return VB_OK;
+}
+
+int vb_engine_synchronize(vb_engine *e)
+{
+    if (!e) return fail(VB_ERR_INVALID_ARG, "engine is null");
+    VB_CUDA(cudaStreamSynchronize(e->stream));
+    return VB_OK;
+}
+
+int vb_engine_stream(vb_engine *e, void **cuda_stream)
+{
+    if (!e || !cuda_stream) return fail(VB_ERR_INVALID_ARG, "null argument");
+    *cuda_stream = (void *)e->stream;
+    return VB_OK;
+}
+
+int vb_engine_launch_count(vb_engine *e, uint64_t *count)
+{
+    if (!e || !count) return fail(VB_ERR_INVALID_ARG, "null argument");
+    *count = e->launches;
+    return VB_OK;
+}
+
+int vb_comm_unique_id(void *id128)
+{
+    VB_API_BEGIN
+    if (!id128) return fail(VB_ERR_INVALID_ARG, "id128 is null");
+    return comm_unique_id(id128);
+    VB_API_END
+}
+
+int vb_engine_comm_init(vb_engine *e, const void *id128, int rank, int world_size)
+{
+    VB_API_BEGIN
+    if (!e || !id128) return fail(VB_ERR_INVALID_ARG, "null argument");
+    if (world_size < 1 || rank < 0 || rank >= world_size)
+        return fail(VB_ERR_INVALID_ARG, "rank %d / world_size %d is not valid", rank, world_size);
+    if (e->comm) return fail(VB_ERR_STATE, "engine already has a communicator");
+    VB_TRY(set_device(e));
+    return comm_init(e, id128, rank, world_size);
+    VB_API_END
+}
+
+int vb_engine_rank(vb_engine *e, int *rank, int *world_size)
+{
+    if (!e) return fail(VB_ERR_INVALID_ARG, "engine is null");
+    if (rank) *rank = e->rank;
+    if (world_size) *world_size = e->world;
+    return VB_OK;
+}
+
+int vb_host_alloc_pinned(void **ptr, size_t bytes)
+{
+    if (!ptr) return fail(VB_ERR_INVALID_ARG, "ptr is null");
+    *ptr = nullptr;
+    VB_CUDA(cudaHostAlloc(ptr, bytes ? bytes : 1, cudaHostAllocDefault));
+    return VB_OK;
+}
+
+int vb_host_free_pinned(void *ptr)
+{
+    if (ptr) VB_CUDA(cudaFreeHost(ptr));
+    return VB_OK;
+}
+
+int vb_adam_create(vb_engine *engine, int64_t n_tensors, const int64_t *sizes, float lr, float beta1,
+                   float beta2, float eps, float weight_decay, vb_optimizer **out)
+{
+    VB_API_BEGIN
+    vb_optimizer *opt = nullptr;
+    int st = create_elementwise(engine, KIND_ADAM, n_tensors, sizes, 2, out, &opt);
+    if (st != VB_OK) {
+        free_optimizer(opt);
+        return st;
+    }
+    opt->lr = lr;
+    opt->beta1 = beta1;
+    opt->beta2 = beta2;
+    opt->eps = eps;
+    opt->weight_decay = weight_decay;
+    *out = opt;
+    return VB_OK;
+    VB_API_END
+}
+
+int vb_sgd_create(vb_engine *engine, int64_t n_tensors, const int64_t *sizes, float lr, float momentum,
+                  float weight_decay, vb_optimizer **out)
+{
+    VB_API_BEGIN
+    vb_optimizer *opt = nullptr;
+    // sgd.rs:30: velocity only if momentum > 0.0
+    int st = create_elementwise(engine, KIND_SGD, n_tensors, sizes, momentum > 0.0f ? 1 : 0, out, &opt);
+    if (st != VB_OK) {
+        free_optimizer(opt);
+        return st;
+    }
+    opt->lr = lr;
+    opt->momentum = momentum;
+    opt->weight_decay = weight_decay;
+    *out = opt;
+    return VB_OK;
+    VB_API_END
+}
+
+int vb_muon_create(vb_engine *engine, int64_t n_tensors, const int64_t *rows, const int64_t *cols,
+                   float lr, float momentum, int nesterov, int ns_steps, int ns_mode, vb_optimizer **out)
+{
+    VB_API_BEGIN
+    if (!engine) return fail(VB_ERR_INVALID_ARG, "engine is null");
+    if (!out) return fail(VB_ERR_INVALID_ARG, "out is null");
+    *out = nullptr;
+    if (n_tensors < 0 || (n_tensors > 0 && (!rows || !cols)))
+        return fail(VB_ERR_INVALID_ARG, "rows/cols is null or n_tensors negative");
+    if (ns_steps < 0) return fail(VB_ERR_INVALID_ARG, "ns_steps is negative");
+    if (ns_mode != VB_NS_F32 && ns_mode != VB_NS_BF16)
+        return fail(VB_ERR_INVALID_ARG, "unknown ns_mode %d", ns_mode);
+    std::vector<int64_t> sizes((size_t)n_tensors);
+    for (int64_t i = 0; i < n_tensors; ++i) {
+        if (rows[i] < 0 || cols[i] < 0 || (cols[i] > 0 && rows[i] > ((int64_t)1 << 40) / cols[i]))
+            return fail(VB_ERR_INVALID_ARG, "rows/cols of tensor %lld are not valid", (long long)i);
+        sizes[(size_t)i] = rows[i] * cols[i];
+    }
+    vb_optimizer *opt = new vb_optimizer();
+    opt->eng = engine;
+    opt->kind = KIND_MUON;
+    opt->n_tensors = n_tensors;
+    opt->sizes = sizes;
+    opt->rows.assign(rows, rows + n_tensors);
+    opt->cols.assign(cols, cols + n_tensors);
+    opt->lr = lr;
+    opt->momentum = momentum;
+    opt->nesterov = nesterov ? 1 : 0;
+    opt->ns_steps = ns_steps;
+    opt->ns_mode = ns_mode;
+    // Parameters and gradients are whole on every rank; velocity is allocated by
+    // muon_init for the matrices this rank owns.
+    Layout L;
+    int st = build_arena(opt, 0, /*shard_states=*/false, &L);
+    if (st == VB_OK) st = muon_init(opt);
+    if (st != VB_OK) {
+        free_optimizer(opt);
+        return st;
+    }
+    *out = opt;
+    return VB_OK;
+    VB_API_END
+}
+
+int vb_optimizer_destroy(vb_optimizer *opt)
+{
+    if (!opt) return VB_OK;
+    if (opt->eng && opt->eng->stream) {
+        cudaSetDevice(opt->eng->device);
+        cudaStreamSynchronize(opt->eng->stream);
+    }
+    free_optimizer(opt);
+    return VB_OK;
+}
+
+int vb_optimizer_num_tensors(vb_optimizer *opt, int64_t *n)
+{
+    VB_TRY(check_opt(opt));
+    if (!n) return fail(VB_ERR_INVALID_ARG, "null argument");
+    *n = opt->n_tensors;
+    return VB_OK;
+}
+
+int vb_optimizer_tensor_size(vb_optimizer *opt, int64_t tensor, int64_t *n)
+{
+    VB_TRY(check_tensor(opt, tensor, 0, false));
+    if (!n) return fail(VB_ERR_INVALID_ARG, "null argument");
+    *n = opt->sizes[tensor];
+    return VB_OK;
+}
+
+int vb_optimizer_total_size(vb_optimizer *opt, int64_t *n)
+{
+    VB_TRY(check_opt(opt));
+    if (!n) return fail(VB_ERR_INVALID_ARG, "null argument");
+    *n = opt->total;
+    return VB_OK;
+}
+
+static int copy_tensor(vb_optimizer *opt, int64_t tensor, float *dev_base, void *host, int64_t n,
+                       bool to_device)
+{
+    VB_TRY(check_tensor(opt, tensor, n, true));
+    if (n > 0 && !host) return fail(VB_ERR_INVALID_ARG, "host pointer is null");
+    VB_TRY(set_device(opt->eng));
+    if (n == 0) return VB_OK;
+    float *dev = dev_base + opt->offsets[tensor];
+    if (to_device) {
+        VB_CUDA(cudaMemcpyAsync(dev, host, (size_t)n * sizeof(float), cudaMemcpyHostToDevice,
+                                opt->eng->stream));
+    } else {
+        VB_CUDA(cudaMemcpyAsync(host, dev, (size_t)n * sizeof(float), cudaMemcpyDeviceToHost,
+                                opt->eng->stream));
+        VB_CUDA(cudaStreamSynchronize(opt->eng->stream));
+    }
+    return VB_OK;
+}
+
+int vb_optimizer_upload_params(vb_optimizer *opt, int64_t tensor, const float *host, int64_t n)
+{
+    VB_TRY(check_opt(opt));
+    return copy_tensor(opt, tensor, opt->d_param, (void *)host, n, true);
+}
+
+int vb_optimizer_download_params(vb_optimizer *opt, int64_t tensor, float *host, int64_t n)
+{
+    VB_TRY(check_opt(opt));
+    return copy_tensor(opt, tensor, opt->d_param, host, n, false);
+}
+
+int vb_optimizer_upload_grad(vb_optimizer *opt, int64_t tensor, const float *host, int64_t n)
+{
+    VB_TRY(check_opt(opt));
+    VB_TRY(copy_tensor(opt, tensor, opt->d_grad, (void *)host, n, true));
+    opt->present[(size_t)tensor] = 1;
+    return VB_OK;
+}
+
+int vb_optimizer_download_grad(vb_optimizer *opt, int64_t tensor, float *host, int64_t n)
+{
+    VB_TRY(check_opt(opt));
+    return copy_tensor(opt, tensor, opt->d_grad, host, n, false);
+}
+
+int vb_optimizer_param_ptr(vb_optimizer *opt, int64_t tensor, void **p)
+{
+    VB_TRY(check_tensor(opt, tensor, 0, false));
+    if (!p) return fail(VB_ERR_INVALID_ARG, "null argument");
+    *p = opt->d_param + opt->offsets[tensor];
+    return VB_OK;
+}
+
+int vb_optimizer_grad_ptr(vb_optimizer *opt, int64_t tensor, void **p)
+{
+    VB_TRY(check_tensor(opt, tensor, 0, false));
+    if (!p) return fail(VB_ERR_INVALID_ARG, "null argument");
+    *p = opt->d_grad + opt->offsets[tensor];
+    return VB_OK;
+}
+
+int vb_optimizer_arena(vb_optimizer *opt, void **param_arena, void **grad_arena, int64_t *arena_elements,
+                       int64_t *offsets_out)
+{
+    VB_TRY(check_opt(opt));
+    if (param_arena) *param_arena = opt->d_param;
+    if (grad_arena) *grad_arena = opt->d_grad;
+    if (arena_elements) *arena_elements = opt->arena;
+    if (offsets_out)
+        for (int64_t i = 0; i < opt->n_tensors; ++i) offsets_out[i] = opt->offsets[i];
+    return VB_OK;
+}
+
+int vb_optimizer_upload_arena(vb_optimizer *opt, int which, const float *host, int64_t n)
+{
+    VB_TRY(check_opt(opt));
+    if (which != 0 && which != 1) return fail(VB_ERR_INVALID_ARG, "which must be 0 (params) or 1 (grads)");
+    if (n != opt->arena)
+        return fail(VB_ERR_INVALID_ARG, "arena has %lld elements, caller passed %lld", (long long)opt->arena,
+                    (long long)n);
+    if (!host) return fail(VB_ERR_INVALID_ARG, "host pointer is null");
+    VB_TRY(set_device(opt->eng));
+    VB_CUDA(cudaMemcpyAsync(which == 0 ? opt->d_param : opt->d_grad, host, (size_t)n * sizeof(float),
+                            cudaMemcpyHostToDevice, opt->eng->stream));
+    if (which == 1) std::fill(opt->present.begin(), opt->present.end(), (uint8_t)1);
+    return VB_OK;
+}
+
+int vb_optimizer_download_arena(vb_optimizer *opt, int which, float *host, int64_t n)
+{
+    VB_TRY(check_opt(opt));
+    if (which != 0 && which != 1) return fail(VB_ERR_INVALID_ARG, "which must be 0 (params) or 1 (grads)");
+    if (n != opt->arena)
+        return fail(VB_ERR_INVALID_ARG, "arena has %lld elements, caller passed %lld", (long long)opt->arena,
+                    (long long)n);
+    if (!host) return fail(VB_ERR_INVALID_ARG, "host pointer is null");
+    VB_TRY(set_device(opt->eng));
+    VB_CUDA(cudaMemcpyAsync(host, which == 0 ? opt->d_param : opt->d_grad, (size_t)n * sizeof(float),
+                            cudaMemcpyDeviceToHost, opt->eng->stream));
+    VB_CUDA(cudaStreamSynchronize(opt->eng->stream));
+    return VB_OK;
+}
+
+int vb_optimizer_set_grad_present(vb_optimizer *opt, int64_t tensor, int present)
+{
+    VB_TRY(check_tensor(opt, tensor, 0, false));
+    opt->present[(size_t)tensor] = present ? 1 : 0;
+    return VB_OK;
+}
+
+int vb_optimizer_zero_grad(vb_optimizer *opt)
+{
+    VB_TRY(check_opt(opt));
+    std::fill(opt->present.begin(), opt->present.end(), (uint8_t)0);
+    return VB_OK;
+}
+
+int vb_optimizer_set_lr(vb_optimizer *opt, float lr)
+{
+    VB_TRY(check_opt(opt));
+    opt->lr = lr;
+    return VB_OK;
+}
+
+int vb_optimizer_step_ex(vb_optimizer *opt, uint32_t flags)
+{
+    VB_API_BEGIN
+    VB_TRY(check_opt(opt));
+    vb_engine *e = opt->eng;
+    VB_TRY(set_device(e));
+    if (opt->kind == KIND_MUON) return muon_step(opt, flags);
+
+    int op;
+    StepScalars s;
+    if (opt->kind == KIND_ADAM) {
+        opt->t += 1;  // adam.rs:71: before looking at any gradient
+        op = OP_ADAM;
+        s = make_scalars(op, opt->lr, opt->beta1, opt->beta2, opt->eps, opt->weight_decay, opt->t);
+    } else {
+        op = opt->momentum > 0.0f ? OP_SGD_MOMENTUM : OP_SGD;  // sgd.rs:207
+        s = make_scalars(op, opt->lr, opt->momentum, 0.0f, 0.0f, opt->weight_decay, 0);
+    }
+    VB_TRY(sync_present(opt));
+    if (opt->n_chunks > 0) {
+        VB_TRY(launch_multi_tensor(op, opt->d_tensors, opt->d_chunks, opt->n_chunks, opt->d_present, s,
+                                   e->sm_count, e->stream));
+        e->launches += 1;
+    }
+    if (e->world > 1 && !(flags & VB_STEP_NO_EXCHANGE))
+        VB_TRY(comm_all_gather_inplace(e, opt->d_param, opt->arena / e->world));
+    return VB_OK;
+    VB_API_END
+}
+
+int vb_optimizer_step(vb_optimizer *opt) { return vb_optimizer_step_ex(opt, VB_STEP_DEFAULT); }
+
+int vb_optimizer_export_state(vb_optimizer *opt, int64_t tensor, int which, float *host, int64_t n,
+                              int64_t *owned_begin, int64_t *owned_end)
+{
+    VB_API_BEGIN
+    VB_TRY(check_tensor(opt, tensor, n, true));
+    if (n > 0 && !host) return fail(VB_ERR_INVALID_ARG, "host pointer is null");
+    float *state = which == 0 ? opt->d_s1 : which == 1 ? opt->d_s2 : nullptr;
+    if (which != 0 && which != 1) return fail(VB_ERR_INVALID_ARG, "which must be 0 or 1");
+    VB_TRY(set_device(opt->eng));
+    int64_t lo = 0, hi = 0;
+    if (opt->kind == KIND_MUON) {
+        if (which != 0) return fail(VB_ERR_INVALID_ARG, "Muon has one state buffer (velocity)");
+        if (muon_owner(opt, tensor) == opt->eng->rank) hi = n;
+    } else {
+        const int64_t off = opt->offsets[tensor];
+        lo = std::max(off, opt->shard_begin) - off;
+        hi = std::min(off + n, opt->shard_end) - off;
+        if (hi < lo) lo = hi = 0;
+    }
+    if (!state && hi > lo)
+        return fail(VB_ERR_STATE, "this optimizer has no state buffer %d (e.g. SGD without momentum)", which);
+    if (n > 0) memset(host, 0, (size_t)n * sizeof(float));
+    if (hi > lo) {
+        const int64_t arena_pos = opt->offsets[tensor] + lo;
+        VB_CUDA(cudaMemcpyAsync(host + lo, state + (arena_pos - opt->shard_begin),
+                                (size_t)(hi - lo) * sizeof(float), cudaMemcpyDeviceToHost,
+                                opt->eng->stream));
+        VB_CUDA(cudaStreamSynchronize(opt->eng->stream));
+    }
+    if (owned_begin) *owned_begin = lo;
+    if (owned_end) *owned_end = hi;
+    return VB_OK;
+    VB_API_END
+}
+
+int vb_optimizer_import_state(vb_optimizer *opt, int64_t tensor, int which, const float *host, int64_t n)
+{
+    VB_API_BEGIN
+    VB_TRY(check_tensor(opt, tensor, n, true));
+    if (n > 0 && !host) return fail(VB_ERR_INVALID_ARG, "host pointer is null");
+    if (which != 0 && which != 1) return fail(VB_ERR_INVALID_ARG, "which must be 0 or 1");
+    float *state = which == 0 ? opt->d_s1 : opt->d_s2;
+    VB_TRY(set_device(opt->eng));
+    int64_t lo = 0, hi = 0;
+    if (opt->kind == KIND_MUON) {
+        if (which != 0) return fail(VB_ERR_INVALID_ARG, "Muon has one state buffer (velocity)");
+        if (muon_owner(opt, tensor) == opt->eng->rank) hi = n;
+    } else {
+        const int64_t off = opt->offsets[tensor];
+        lo = std::max(off, opt->shard_begin) - off;
+        hi = std::min(off + n, opt->shard_end) - off;
+        if (hi < lo) lo = hi = 0;
+    }
+    if (!state && hi > lo) return fail(VB_ERR_STATE, "this optimizer has no state buffer %d", which);
+    if (hi > lo) {
+        const int64_t arena_pos = opt->offsets[tensor] + lo;
+        VB_CUDA(cudaMemcpyAsync(state + (arena_pos - opt->shard_begin), host + lo,
+                                (size_t)(hi - lo) * sizeof(float), cudaMemcpyHostToDevice,
+                                opt->eng->stream));
+        VB_CUDA(cudaStreamSynchronize(opt->eng->stream));
+    }
+    return VB_OK;
+    VB_API_END
+}
+
+int vb_optimizer_get_t(vb_optimizer *opt, int64_t *t)
+{
+    VB_TRY(check_opt(opt));
+    if (!t) return fail(VB_ERR_INVALID_ARG, "null argument");
+    *t = opt->t;
+    return VB_OK;
+}
+
+int vb_optimizer_set_t(vb_optimizer *opt, int64_t t)
+{
+    VB_TRY(check_opt(opt));
+    if (t < 0 || t > 0x7fffffff) return fail(VB_ERR_INVALID_ARG, "t out of range");
+    opt->t = t;
+    return VB_OK;
+}
+
+int vb_muon_download_update(vb_optimizer *opt, int64_t tensor, float *host, int64_t n)
+{
+    VB_API_BEGIN
+    VB_TRY(check_tensor(opt, tensor, n, true));
+    if (opt->kind != KIND_MUON) return fail(VB_ERR_INVALID_ARG, "not a Muon optimizer");
+    VB_TRY(set_device(opt->eng));
+    return muon_download_update(opt, tensor, host, n);
+    VB_API_END
+}
+
+int vb_muon_last_ns_flops(vb_optimizer *opt, double *flops)
+{
+    VB_TRY(check_opt(opt));
+    if (!flops) return fail(VB_ERR_INVALID_ARG, "null argument");
+    if (opt->kind != KIND_MUON) return fail(VB_ERR_INVALID_ARG, "not a Muon optimizer");
+    return muon_last_flops(opt, flops);
+}
+
+// ---- caller-owned buffers ----------------------------------------------------------------
+
+static int ensure_stage(vb_engine *e, int slot, size_t bytes)
+{
+    if (e->stage_bytes[slot] >= bytes) return VB_OK;
+    size_t cap = std::max<size_t>(bytes, 1 << 16);
+    cap = (cap + 4095) / 4096 * 4096;
+    if (e->h_stage[slot]) VB_CUDA(cudaFreeHost(e->h_stage[slot]));
+    if (e->d_stage[slot]) VB_CUDA(cudaFree(e->d_stage[slot]));
+    e->h_stage[slot] = e->d_stage[slot] = nullptr;
+    e->stage_bytes[slot] = 0;
+    VB_CUDA(cudaHostAlloc(&e->h_stage[slot], cap, cudaHostAllocDefault));
+    VB_CUDA(cudaMalloc(&e->d_stage[slot], cap));
+    if (!e->stage_done[slot]) VB_CUDA(cudaEventCreateWithFlags(&e->stage_done[slot], cudaEventDisableTiming));
+    e->stage_bytes[slot] = cap;
+    return VB_OK;
+}
+
+int vb_multi_tensor_step(vb_engine *e, const vb_optimizer_step_params *hp, int64_t n_tensors,
+                         const int64_t *sizes, void *const *params, const void *const *grads,
+                         void *const *state1, void *const *state2)
+{
+    VB_API_BEGIN
+    if (!e || !hp) return fail(VB_ERR_INVALID_ARG, "null argument");
+    if (hp->op > 2u) return fail(VB_ERR_INVALID_ARG, "op %u is not 0 (SGD), 1 (SGD+momentum) or 2 (Adam)", hp->op);
+    VB_TRY(validate_sizes(n_tensors, sizes));
+    if (n_tensors == 0) return VB_OK;
+    if (!params || !grads) return fail(VB_ERR_INVALID_ARG, "params/grads is null");
+    if (hp->op >= 1 && !state1) return fail(VB_ERR_INVALID_ARG, "state1 is null for op %u", hp->op);
+    if (hp->op == 2 && !state2) return fail(VB_ERR_INVALID_ARG, "state2 is null for Adam");
+    if (hp->op == 2 && !(hp->t >= 1.0f && hp->t <= 2147483648.0f))
+        return fail(VB_ERR_INVALID_ARG, "Adam needs t >= 1");
+    VB_TRY(set_device(e));
+
+    int64_t total = 0;
+    for (int64_t i = 0; i < n_tensors; ++i) {
+        if (sizes[i] == 0) continue;
+        if (!params[i] || !grads[i]) return fail(VB_ERR_INVALID_ARG, "params[%lld] or grads[%lld] is null", (long long)i, (long long)i);
+        if (hp->op >= 1 && !state1[i]) return fail(VB_ERR_INVALID_ARG, "state1[%lld] is null", (long long)i);
+        if (hp->op == 2 && !state2[i]) return fail(VB_ERR_INVALID_ARG, "state2[%lld] is null", (long long)i);
+        if (((uintptr_t)params[i] | (uintptr_t)grads[i]) & 3u)
+            return fail(VB_ERR_INVALID_ARG, "tensor %lld is not 4-byte aligned", (long long)i);
+        total += sizes[i];
+    }
+    const int64_t chunk_len = pick_chunk_len(total, e->sm_count);
+    int64_t n_chunks = 0;
+    for (int64_t i = 0; i < n_tensors; ++i) n_chunks += (sizes[i] + chunk_len - 1) / chunk_len;
+    if (n_chunks == 0) return VB_OK;
+
+    // layout of the staging block: [TensorDesc x n][ChunkDesc x n_chunks][present x n]
+    const size_t td_bytes = (size_t)n_tensors * sizeof(TensorDesc);
+    const size_t ch_off = (td_bytes + 15) / 16 * 16;
+    const size_t ch_bytes = (size_t)n_chunks * sizeof(ChunkDesc);
+    const size_t pr_off = ch_off + ch_bytes;
+    const size_t bytes = pr_off + (size_t)n_tensors;
+    const int slot = e->stage_next;
+    e->stage_next ^= 1;
+    if (e->stage_done[slot]) VB_CUDA(cudaEventSynchronize(e->stage_done[slot]));  // previous user of this slot
+    VB_TRY(ensure_stage(e, slot, bytes));
+    char *h = (char *)e->h_stage[slot];
+    TensorDesc *tds = (TensorDesc *)h;
+    ChunkDesc *chs = (ChunkDesc *)(h + ch_off);
+    uint8_t *pres = (uint8_t *)(h + pr_off);
+    int64_t c = 0;
+    for (int64_t i = 0; i < n_tensors; ++i) {
+        tds[i].p = (float *)params[i];
+        tds[i].g = (const float *)grads[i];
+        tds[i].s1 = state1 ? (float *)state1[i] : nullptr;
+        tds[i].s2 = state2 ? (float *)state2[i] : nullptr;
+        pres[i] = 1;
+        for (int64_t b = 0; b < sizes[i]; b += chunk_len) {
+            chs[c].offset = b;
+            chs[c].tensor = (uint32_t)i;
+            chs[c].len = (uint32_t)std::min(chunk_len, sizes[i] - b);
+            ++c;
+        }
+    }
+    char *d = (char *)e->d_stage[slot];
+    VB_CUDA(cudaMemcpyAsync(d, h, bytes, cudaMemcpyHostToDevice, e->stream));
+    VB_CUDA(cudaEventRecord(e->stage_done[slot], e->stream));
+    const StepScalars s = make_scalars((int)hp->op, hp->lr, hp->beta1, hp->beta2, hp->eps, hp->weight_decay,
+                                       (int64_t)hp->t);
+    VB_TRY(launch_multi_tensor((int)hp->op, (const TensorDesc *)d, (const ChunkDesc *)(d + ch_off), n_chunks,
+                               (const uint8_t *)(d + pr_off), s, e->sm_count, e->stream));
+    e->launches += 1;
+    return VB_OK;
+    VB_API_END
+}
+
+}  // extern "C"

@@ -1,0 +1,98 @@
+// Engine and optimizer objects behind the opaque handles of include/volta_b200.h.
+#pragma once
+
+#include <memory>
+
+#include "vb_internal.h"
+
+namespace vb {
+struct Comm;       // comm.cpp: NCCL communicator (library resolved at run time)
+struct MuonState;  // muon.cu: matrices, work buffers and GEMM schedules of a Muon optimizer
+void destroy_muon_state(MuonState *);
+}  // namespace vb
+
+struct vb_engine {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    int sm_count = 0;
+    uint64_t launches = 0;
+    int rank = 0;
+    int world = 1;
+    vb::Comm *comm = nullptr;
+    // staging for vb_multi_tensor_step (caller-owned buffers): descriptors are written to
+    // pinned host memory and copied to the device on the stream, double buffered.
+    void *h_stage[2] = {nullptr, nullptr};
+    void *d_stage[2] = {nullptr, nullptr};
+    size_t stage_bytes[2] = {0, 0};
+    cudaEvent_t stage_done[2] = {nullptr, nullptr};
+    int stage_next = 0;
+};
+
+enum OptimizerKind { KIND_ADAM = 0, KIND_SGD = 1, KIND_MUON = 2 };
+
+struct vb_optimizer {
+    vb_engine *eng = nullptr;
+    int kind = KIND_ADAM;
+    int64_t n_tensors = 0;
+    std::vector<int64_t> sizes;    // elements per tensor
+    std::vector<int64_t> offsets;  // element offset of each tensor in the arenas
+    std::vector<int64_t> rows, cols;  // Muon's 2-D view
+    int64_t total = 0;             // sum of sizes
+    int64_t arena = 0;             // arena length in elements (padded)
+    // this rank's slice of the arena (Adam/SGD state lives only here)
+    int64_t shard_begin = 0, shard_end = 0;
+
+    float *d_param = nullptr;
+    float *d_grad = nullptr;
+    float *d_s1 = nullptr;  // Adam m / SGD velocity / Muon velocity
+    float *d_s2 = nullptr;  // Adam v
+    int64_t state_elems = 0;
+
+    // hyper-parameters
+    float lr = 0, beta1 = 0, beta2 = 0, eps = 0, weight_decay = 0, momentum = 0;
+    int nesterov = 0, ns_steps = 0, ns_mode = 0;
+    int64_t t = 0;
+
+    // descriptors
+    vb::TensorDesc *d_tensors = nullptr;
+    vb::ChunkDesc *d_chunks = nullptr;
+    int64_t n_chunks = 0;
+    uint8_t *d_present = nullptr;
+    std::vector<uint8_t> present;        // host truth
+    std::vector<uint8_t> present_on_dev; // last copy sent to d_present
+
+    vb::MuonState *muon = nullptr;
+};
+
+namespace vb {
+
+// muon.cu
+int muon_init(vb_optimizer *opt);
+int muon_step(vb_optimizer *opt, uint32_t flags);
+int muon_download_update(vb_optimizer *opt, int64_t tensor, float *host, int64_t n);
+int muon_last_flops(vb_optimizer *opt, double *flops);
+int muon_owner(vb_optimizer *opt, int64_t tensor);
+
+// comm.cpp
+int comm_unique_id(void *id128);
+int comm_init(vb_engine *eng, const void *id128, int rank, int world);
+void comm_destroy(vb_engine *eng);
+int comm_all_gather_inplace(vb_engine *eng, float *base, int64_t elems_per_rank);
+struct BcastItem {
+    float *ptr;
+    int64_t count;
+    int root;
+};
+int comm_group_broadcast(vb_engine *eng, const BcastItem *items, int64_t n_items);
+
+inline int sync_present(vb_optimizer *opt)
+{
+    if (opt->present != opt->present_on_dev) {
+        VB_CUDA(cudaMemcpyAsync(opt->d_present, opt->present.data(), opt->present.size(),
+                                cudaMemcpyHostToDevice, opt->eng->stream));
+        opt->present_on_dev = opt->present;
+    }
+    return VB_OK;
+}
+
+}  // namespace vb

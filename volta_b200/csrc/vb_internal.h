@@ -1,0 +1,79 @@
+// Internal declarations shared by the translation units of libvolta_b200.so.
+// Nothing here is part of the C ABI (include/volta_b200.h).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+#include <vector>
+
+#include "../../include/volta_b200.h"
+
+namespace vb {
+
+// ---- error plumbing -------------------------------------------------------------------
+void set_error(const char *fmt, ...);
+int fail(int code, const char *fmt, ...);
+
+#define VB_CUDA(expr)                                                                       \
+    do {                                                                                    \
+        cudaError_t _e = (expr);                                                            \
+        if (_e != cudaSuccess)                                                              \
+            return ::vb::fail(VB_ERR_CUDA, "%s failed: %s (%d) at %s:%d", #expr,            \
+                              cudaGetErrorString(_e), (int)_e, __FILE__, __LINE__);         \
+    } while (0)
+
+#define VB_TRY(expr)                 \
+    do {                             \
+        int _s = (expr);             \
+        if (_s != VB_OK) return _s;  \
+    } while (0)
+
+// ---- descriptors read by the multi-tensor kernels ------------------------------------
+// One entry per tensor.  For a sharded optimizer s1/s2 are biased so that s1 + i is the
+// state of element i of the tensor for every i this rank owns.
+struct TensorDesc {
+    float *p;
+    const float *g;
+    float *s1;
+    float *s2;
+};
+// One entry per unit of work: `len` consecutive elements of one tensor from `offset`.
+// A chunk never crosses a tensor boundary, so ragged tensor lists load-balance.
+struct ChunkDesc {
+    int64_t offset;
+    uint32_t tensor;
+    uint32_t len;
+};
+
+// Scalars of one step, computed on the host in f32 exactly as the reference does.
+struct StepScalars {
+    float lr;
+    float beta1;            // Adam beta1 / SGD momentum
+    float beta2;
+    float one_minus_beta1;  // 1.0f - beta1   (src/nn/optim/adam.rs:176)
+    float one_minus_beta2;  // 1.0f - beta2   (adam.rs:183)
+    float m_hat_scale;      // 1/(1 - beta1.powi(t))  (adam.rs:188)
+    float v_hat_scale;      // 1/(1 - beta2.powi(t))  (adam.rs:189)
+    float eps;
+    float weight_decay;
+};
+
+enum MultiTensorOp { OP_SGD = 0, OP_SGD_MOMENTUM = 1, OP_ADAM = 2 };
+
+// f32::powi as compiler-rt's __powisf2 computes it (square-and-multiply, exponent bits
+// least significant first, each product rounded to f32).
+float powi_f32(float a, int b);
+StepScalars make_scalars(int op, float lr, float beta1, float beta2, float eps, float wd, int64_t t);
+
+// Launches the fused multi-tensor update over `n_chunks` chunks.  `present` holds one
+// byte per tensor (0 = gradient absent, skip).
+int launch_multi_tensor(int op, const TensorDesc *d_tensors, const ChunkDesc *d_chunks,
+                        int64_t n_chunks, const uint8_t *d_present, const StepScalars &s,
+                        int sm_count, cudaStream_t stream);
+
+// Splits [begin, end) of each tensor into chunks.
+int64_t pick_chunk_len(int64_t total_elements, int sm_count);
+
+}  // namespace vb

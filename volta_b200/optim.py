@@ -1,0 +1,375 @@
+"""Host-side mirror of Volta's optimizer API over the C ABI.
+
+Same names, argument order and meaning as the reference
+(``Adam::new(params, lr, betas, eps, weight_decay)`` src/nn/optim/adam.rs:18-24,
+``SGD::new(params, lr, momentum, weight_decay)`` src/nn/optim/sgd.rs:28,
+``Muon::new(params, lr, momentum, nesterov, ns_steps)`` src/nn/optim/muon.rs:19-25;
+each with ``step()`` and ``zero_grad()``), so a training loop written against Volta reads
+the same here:
+
+    opt = Adam(model_parameters, 1e-3, (0.9, 0.999), 1e-8, 0.0)
+    opt.zero_grad(); ...set p.grad...; opt.step()
+
+All arithmetic runs in the CUDA library; this module only moves bytes and keeps handles.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Iterable, List, Optional, Sequence
+
+import numpy as np
+
+from . import _lib
+from ._lib import VB_NS_BF16, VB_NS_F32, VB_STEP_DEFAULT, VB_STEP_NO_EXCHANGE, VoltaB200Error, call
+
+__all__ = ["Engine", "Tensor", "Adam", "SGD", "Muon", "default_engine", "multi_tensor_step",
+           "VoltaB200Error", "VB_NS_F32", "VB_NS_BF16", "VB_STEP_NO_EXCHANGE"]
+
+
+def _f32(a) -> np.ndarray:
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+class Engine:
+    """One CUDA device + stream (the role of Volta's global GPU context,
+    src/gpu/mod.rs:30-47).  Optionally one rank of a multi-GPU group."""
+
+    def __init__(self, device: int = 0):
+        self._h = C.c_void_p()
+        call("vb_engine_create", int(device), C.byref(self._h))
+        self.device = int(device)
+
+    def close(self) -> None:
+        if getattr(self, "_h", None) is not None and self._h:
+            call("vb_engine_destroy", self._h)
+            self._h = C.c_void_p()
+
+    def synchronize(self) -> None:
+        call("vb_engine_synchronize", self._h)
+
+    @property
+    def stream(self) -> int:
+        """The engine's ``cudaStream_t`` as an integer."""
+        s = C.c_void_p()
+        call("vb_engine_stream", self._h, C.byref(s))
+        return int(s.value or 0)
+
+    @property
+    def launch_count(self) -> int:
+        n = C.c_uint64()
+        call("vb_engine_launch_count", self._h, C.byref(n))
+        return int(n.value)
+
+    @staticmethod
+    def unique_id() -> bytes:
+        buf = C.create_string_buffer(128)
+        call("vb_comm_unique_id", buf)
+        return buf.raw
+
+    def init_comm(self, unique_id: bytes, rank: int, world_size: int) -> None:
+        if len(unique_id) != 128:
+            raise ValueError("unique_id must be 128 bytes")
+        call("vb_engine_comm_init", self._h, C.c_char_p(unique_id), int(rank), int(world_size))
+
+    @property
+    def rank(self) -> int:
+        r, w = C.c_int(), C.c_int()
+        call("vb_engine_rank", self._h, C.byref(r), C.byref(w))
+        return r.value
+
+    @property
+    def world_size(self) -> int:
+        r, w = C.c_int(), C.c_int()
+        call("vb_engine_rank", self._h, C.byref(r), C.byref(w))
+        return w.value
+
+
+_default_engine: Optional[Engine] = None
+
+
+def default_engine() -> Engine:
+    """Process-wide engine on device 0, created on first use."""
+    global _default_engine
+    if _default_engine is None:
+        _default_engine = Engine(0)
+    return _default_engine
+
+
+class PinnedBuffer:
+    """Page-locked float32 host array (``vb_host_alloc_pinned``)."""
+
+    def __init__(self, n: int):
+        self._p = C.c_void_p()
+        call("vb_host_alloc_pinned", C.byref(self._p), max(int(n), 1) * 4)
+        self.array = np.ctypeslib.as_array(C.cast(self._p, C.POINTER(C.c_float)), shape=(int(n),))
+
+    def free(self) -> None:
+        if self._p:
+            self.array = None
+            call("vb_host_free_pinned", self._p)
+            self._p = C.c_void_p()
+
+
+class Tensor:
+    """What Volta's optimizers see of a ``Tensor`` (src/tensor.rs:38-46): a shape, f32
+    ``data`` and an optional ``grad``.  Before an optimizer takes it, the values live in
+    host memory; afterwards they live in the optimizer's device arena, ``data`` reads them
+    back and assigning ``grad`` uploads (``None`` = no gradient)."""
+
+    def __init__(self, data, shape: Optional[Sequence[int]] = None, requires_grad: bool = True):
+        arr = _f32(data)
+        self.shape = tuple(int(s) for s in (shape if shape is not None else arr.shape))
+        if int(np.prod(self.shape, dtype=np.int64)) != arr.size:
+            raise ValueError("shape does not match data")
+        self.requires_grad = requires_grad
+        self._host = arr.reshape(-1).copy()
+        self._host_grad: Optional[np.ndarray] = None
+        self._opt: Optional["_Optimizer"] = None
+        self._index = -1
+
+    @property
+    def size(self) -> int:
+        return int(self._host.size)
+
+    @property
+    def data(self) -> np.ndarray:
+        if self._opt is not None:
+            self._opt._download_params(self._index, self._host)
+        return self._host.reshape(self.shape)
+
+    @data.setter
+    def data(self, value) -> None:
+        arr = _f32(value).reshape(-1)
+        if arr.size != self._host.size:
+            raise ValueError("size mismatch")
+        self._host[:] = arr
+        if self._opt is not None:
+            self._opt._upload_params(self._index, self._host)
+
+    @property
+    def grad(self) -> Optional[np.ndarray]:
+        if self._opt is not None:
+            return self._opt._download_grad(self._index, self.shape)
+        return None if self._host_grad is None else self._host_grad.reshape(self.shape)
+
+    @grad.setter
+    def grad(self, value) -> None:
+        if value is None:
+            self._host_grad = None
+            if self._opt is not None:
+                self._opt._set_present(self._index, False)
+            return
+        arr = _f32(value).reshape(-1)
+        if arr.size != self._host.size:
+            raise ValueError("gradient size mismatch")
+        if self._opt is not None:
+            self._opt._upload_grad(self._index, arr)
+        else:
+            self._host_grad = arr.copy()
+
+
+class _Optimizer:
+    def __init__(self, params: Iterable[Tensor], engine: Optional[Engine]):
+        self.params: List[Tensor] = list(params)
+        for p in self.params:
+            if not isinstance(p, Tensor):
+                raise TypeError("params must be volta_b200.Tensor objects")
+            if p._opt is not None:
+                raise ValueError("a Tensor can belong to one optimizer")
+        self.engine = engine if engine is not None else default_engine()
+        self._h = C.c_void_p()
+        self._present = [False] * len(self.params)
+
+    # -- construction helpers --------------------------------------------------------------
+    def _sizes(self):
+        n = len(self.params)
+        return n, (C.c_int64 * max(n, 1))(*[p.size for p in self.params])
+
+    def _adopt(self) -> None:
+        for i, p in enumerate(self.params):
+            p._opt, p._index = self, i
+            self._upload_params(i, p._host)
+            if p._host_grad is not None:
+                self._upload_grad(i, p._host_grad)
+                p._host_grad = None
+
+    def close(self) -> None:
+        if self._h:
+            for p in self.params:
+                if p._opt is self:
+                    self._download_params(p._index, p._host)
+                    p._opt, p._index = None, -1
+            call("vb_optimizer_destroy", self._h)
+            self._h = C.c_void_p()
+
+    # -- tensor traffic --------------------------------------------------------------------
+    def _upload_params(self, i, arr):
+        call("vb_optimizer_upload_params", self._h, i, arr.ctypes.data_as(C.c_void_p), arr.size)
+
+    def _download_params(self, i, out):
+        call("vb_optimizer_download_params", self._h, i, out.ctypes.data_as(C.c_void_p), out.size)
+
+    def _upload_grad(self, i, arr):
+        call("vb_optimizer_upload_grad", self._h, i, arr.ctypes.data_as(C.c_void_p), arr.size)
+        self._present[i] = True
+
+    def _download_grad(self, i, shape):
+        if not self._present[i]:
+            return None
+        out = np.empty(self.params[i].size, np.float32)
+        call("vb_optimizer_download_grad", self._h, i, out.ctypes.data_as(C.c_void_p), out.size)
+        return out.reshape(shape)
+
+    def _set_present(self, i, present: bool):
+        call("vb_optimizer_set_grad_present", self._h, i, int(present))
+        self._present[i] = bool(present)
+
+    # -- the reference API -----------------------------------------------------------------
+    def step(self, flags: int = VB_STEP_DEFAULT) -> None:
+        """``step()``: one fused update of every parameter that has a gradient."""
+        call("vb_optimizer_step_ex", self._h, int(flags))
+
+    def zero_grad(self) -> None:
+        """``zero_grad()``: every ``grad`` becomes ``None`` (adam.rs:62-66)."""
+        call("vb_optimizer_zero_grad", self._h)
+        self._present = [False] * len(self.params)
+
+    # -- extras (state is private in the reference; exposed for parity checks/resume) ------
+    def set_lr(self, lr: float) -> None:
+        call("vb_optimizer_set_lr", self._h, float(lr))
+
+    def state(self, i: int, which: int = 0) -> np.ndarray:
+        out = np.empty(self.params[i].size, np.float32)
+        lo, hi = C.c_int64(), C.c_int64()
+        call("vb_optimizer_export_state", self._h, i, which, out.ctypes.data_as(C.c_void_p), out.size,
+             C.byref(lo), C.byref(hi))
+        return out
+
+    def state_owned_range(self, i: int, which: int = 0):
+        out = np.empty(self.params[i].size, np.float32)
+        lo, hi = C.c_int64(), C.c_int64()
+        call("vb_optimizer_export_state", self._h, i, which, out.ctypes.data_as(C.c_void_p), out.size,
+             C.byref(lo), C.byref(hi))
+        return int(lo.value), int(hi.value)
+
+    def load_state(self, i: int, which: int, values) -> None:
+        arr = _f32(values).reshape(-1)
+        call("vb_optimizer_import_state", self._h, i, which, arr.ctypes.data_as(C.c_void_p), arr.size)
+
+    @property
+    def t(self) -> int:
+        t = C.c_int64()
+        call("vb_optimizer_get_t", self._h, C.byref(t))
+        return int(t.value)
+
+    @t.setter
+    def t(self, value: int) -> None:
+        call("vb_optimizer_set_t", self._h, int(value))
+
+    # -- whole-arena access (one transfer for all tensors) ---------------------------------
+    def arena_layout(self):
+        """(param_ptr, grad_ptr, arena_elements, offsets[n_tensors])."""
+        n = len(self.params)
+        p, g, e = C.c_void_p(), C.c_void_p(), C.c_int64()
+        offs = (C.c_int64 * max(n, 1))()
+        call("vb_optimizer_arena", self._h, C.byref(p), C.byref(g), C.byref(e), offs)
+        return int(p.value or 0), int(g.value or 0), int(e.value), [int(offs[i]) for i in range(n)]
+
+    def upload_arena(self, which: int, host: np.ndarray) -> None:
+        assert host.dtype == np.float32 and host.flags.c_contiguous
+        call("vb_optimizer_upload_arena", self._h, which, host.ctypes.data_as(C.c_void_p), host.size)
+        if which == 1:
+            self._present = [True] * len(self.params)
+
+    def download_arena(self, which: int, host: np.ndarray) -> None:
+        assert host.dtype == np.float32 and host.flags.c_contiguous
+        call("vb_optimizer_download_arena", self._h, which, host.ctypes.data_as(C.c_void_p), host.size)
+
+    def mark_all_grads_present(self) -> None:
+        for i in range(len(self.params)):
+            if not self._present[i]:
+                self._set_present(i, True)
+
+
+class Adam(_Optimizer):
+    """``Adam::new(params, lr, betas, eps, weight_decay)`` (src/nn/optim/adam.rs:18-60):
+    bias-corrected Adam with L2 weight decay folded into the gradient."""
+
+    def __init__(self, params, lr: float, betas=(0.9, 0.999), eps: float = 1e-8,
+                 weight_decay: float = 0.0, engine: Optional[Engine] = None):
+        super().__init__(params, engine)
+        n, sizes = self._sizes()
+        call("vb_adam_create", self.engine._h, n, sizes, lr, betas[0], betas[1], eps, weight_decay,
+             C.byref(self._h))
+        self._adopt()
+
+
+class SGD(_Optimizer):
+    """``SGD::new(params, lr, momentum, weight_decay)`` (src/nn/optim/sgd.rs:28-52)."""
+
+    def __init__(self, params, lr: float, momentum: float = 0.0, weight_decay: float = 0.0,
+                 engine: Optional[Engine] = None):
+        super().__init__(params, engine)
+        n, sizes = self._sizes()
+        call("vb_sgd_create", self.engine._h, n, sizes, lr, momentum, weight_decay, C.byref(self._h))
+        self._adopt()
+
+
+def muon_dims(shape):
+    """(rows, cols) as Muon::step flattens a shape (src/nn/optim/muon.rs:117-130)."""
+    shape = tuple(int(s) for s in shape)
+    if len(shape) < 2:
+        return (shape[0] if shape else 1), 1
+    cols = 1
+    for s in shape[1:]:
+        cols *= s
+    return shape[0], cols
+
+
+class Muon(_Optimizer):
+    """``Muon::new(params, lr, momentum, nesterov, ns_steps)`` (src/nn/optim/muon.rs:19-38).
+    ``ns_mode`` picks the Newton-Schulz arithmetic: ``VB_NS_F32`` (f32-faithful) or
+    ``VB_NS_BF16`` (tcgen05 bf16 tensor cores)."""
+
+    def __init__(self, params, lr: float, momentum: float, nesterov: bool, ns_steps: int,
+                 ns_mode: int = VB_NS_F32, engine: Optional[Engine] = None):
+        super().__init__(params, engine)
+        n = len(self.params)
+        dims = [muon_dims(p.shape) for p in self.params]
+        rows = (C.c_int64 * max(n, 1))(*[d[0] for d in dims])
+        cols = (C.c_int64 * max(n, 1))(*[d[1] for d in dims])
+        call("vb_muon_create", self.engine._h, n, rows, cols, lr, momentum, int(bool(nesterov)),
+             int(ns_steps), int(ns_mode), C.byref(self._h))
+        self._adopt()
+
+    def last_update(self, i: int) -> np.ndarray:
+        """The orthogonalised update of the last step for parameter ``i``."""
+        out = np.empty(self.params[i].size, np.float32)
+        call("vb_muon_download_update", self._h, i, out.ctypes.data_as(C.c_void_p), out.size)
+        return out.reshape(self.params[i].shape)
+
+    @property
+    def last_ns_flops(self) -> float:
+        f = C.c_double()
+        call("vb_muon_last_ns_flops", self._h, C.byref(f))
+        return float(f.value)
+
+
+def multi_tensor_step(engine: Engine, op: int, sizes: Sequence[int], params: Sequence[int],
+                      grads: Sequence[int], state1: Optional[Sequence[int]] = None,
+                      state2: Optional[Sequence[int]] = None, *, lr: float, beta1: float = 0.0,
+                      beta2: float = 0.0, t: float = 0.0, eps: float = 0.0,
+                      weight_decay: float = 0.0) -> None:
+    """One fused launch over caller-owned device buffers (device addresses as integers):
+    the replacement of per-tensor ``gpu_optimizer_step`` calls (src/ops/gpu_ops.rs:495-508)."""
+    n = len(sizes)
+    hp = _lib.StepParams(op, lr, beta1, beta2, float(t), eps, weight_decay, 0.0)
+    arr_sizes = (C.c_int64 * max(n, 1))(*sizes)
+
+    def ptrs(seq):
+        if seq is None:
+            return None
+        return (C.c_void_p * max(n, 1))(*[(int(x) if x else None) for x in seq])
+
+    call("vb_multi_tensor_step", engine._h, C.byref(hp), n, arr_sizes, ptrs(params), ptrs(grads),
+         ptrs(state1), ptrs(state2))
