@@ -1,0 +1,133 @@
+"""GPU parity of Muon (momentum, normalisation, Newton-Schulz, apply) against the oracle.
+
+Tolerances (BASELINE north star), per matrix, on the Newton-Schulz output ("update"):
+relative Frobenius error <= 1e-5 on the f32 path and <= 2e-2 on the bf16 tensor-core path.
+The oracle's contraction restates matrixmultiply's blocking; the reference itself holds no
+numeric test for Muon, so these compare against the restatement (and, for context, against
+the f64-accumulating variant of the oracle).
+"""
+import numpy as np
+import pytest
+
+from helpers import bits_equal, max_rel_err, rel_frobenius
+
+pytestmark = pytest.mark.gpu
+
+TOL_F32 = 1e-5
+TOL_BF16 = 2e-2
+
+
+def _run(oracle, engine, shapes, steps, ns_mode, lr=0.1, momentum=0.9, nesterov=True, ns_steps=5,
+         grad_std=1e-3, param_std=0.02, seed=0, drop=None, gemm_mode=0):
+    from volta_b200 import Muon, Tensor
+    rng = np.random.default_rng(seed)
+    params = [(rng.standard_normal(s) * param_std).astype(np.float32) for s in shapes]
+    ref_params = [p.copy() for p in params]
+    tensors = [Tensor(p, p.shape) for p in params]
+    opt = Muon(tensors, lr, momentum, nesterov, ns_steps, ns_mode=ns_mode, engine=engine)
+    ref = oracle.Muon(ref_params, lr, momentum, nesterov, ns_steps, gemm_mode=gemm_mode)
+    out = []
+    for s in range(1, steps + 1):
+        grads = [(rng.standard_normal(sh) * grad_std).astype(np.float32) for sh in shapes]
+        if drop is not None:
+            grads = [None if drop(i, s) else g for i, g in enumerate(grads)]
+        opt.zero_grad()
+        for t, g in zip(tensors, grads):
+            if g is not None:
+                t.grad = g
+        opt.step()
+        ref.step(grads)
+        errs = []
+        for i, g in enumerate(grads):
+            if g is None:
+                continue
+            errs.append(rel_frobenius(opt.last_update(i), ref.last_update[i]))
+        out.append(dict(update=max(errs) if errs else 0.0,
+                        weights=max(max_rel_err(t.data, r) for t, r in zip(tensors, ref_params)),
+                        velocity_exact=all(bits_equal(opt.state(i, 0), ref.velocity[i]) for i in range(len(shapes))),
+                        weights_exact=all(bits_equal(t.data, r) for t, r in zip(tensors, ref_params))))
+    opt.close()
+    return out
+
+
+def test_reference_muon_test(engine):
+    """src/nn/optim/muon.rs:172-192: 2x2 parameter, values change and stay below 2.0."""
+    from volta_b200 import VB_NS_F32, Muon, Tensor
+    x = Tensor([1.0, -1.0, 0.5, 0.5], (2, 2), True)
+    x.grad = [0.1, 0.1, -0.1, -0.1]
+    opt = Muon([x], 0.1, 0.9, True, 5, ns_mode=VB_NS_F32, engine=engine)
+    before = x.data.copy()
+    opt.step()
+    after = x.data.copy()
+    assert not np.array_equal(before, after)
+    assert np.all(np.abs(after) < 2.0)
+    opt.close()
+
+
+@pytest.mark.parametrize("shapes", [
+    [(2, 2)], [(48, 32), (32, 48)], [(257, 130), (64, 288), (32, 9)], [(300, 520), (1, 64), (64, 1), (40,)],
+    [(32, 1, 3, 3), (64, 32, 3, 3), (128, 10)],
+])
+def test_f32_path_small_shapes(oracle, engine, shapes):
+    """Odd sizes, conv-shaped 4-D tensors flattened to (out, in*k*k), vectors that skip
+    Newton-Schulz (muon.rs:117-130,153).  The f32 path keeps the oracle's summation order, so
+    beyond the 1e-5 bound the results are expected to be bit-identical."""
+    from volta_b200 import VB_NS_F32
+    res = _run(oracle, engine, shapes, 3, VB_NS_F32)
+    for r in res:
+        assert r["update"] <= TOL_F32, res
+        assert r["velocity_exact"]
+    assert all(r["weights_exact"] for r in res), res
+
+
+@pytest.mark.parametrize("nesterov,ns_steps", [(False, 5), (True, 0), (True, 1), (True, 4)])
+def test_f32_path_variants(oracle, engine, nesterov, ns_steps):
+    from volta_b200 import VB_NS_F32
+    res = _run(oracle, engine, [(96, 160), (200, 72)], 2, VB_NS_F32, nesterov=nesterov, ns_steps=ns_steps)
+    assert all(r["update"] <= TOL_F32 and r["weights_exact"] for r in res), res
+
+
+def test_f32_path_missing_gradients(oracle, engine):
+    from volta_b200 import VB_NS_F32
+    res = _run(oracle, engine, [(64, 64), (100, 30), (17,)], 4, VB_NS_F32, drop=lambda i, s: (i + s) % 2 == 0)
+    assert all(r["weights_exact"] and r["velocity_exact"] for r in res), res
+
+
+def test_f32_path_large_matrix_ordered_norm(oracle, engine):
+    """A 1024 x 1024 matrix: the sequential f32 sum of a million squares is ~5e-4 below the
+    exact sum, so a tree reduction would land ~2.5e-4 away from the reference, 25x outside
+    the 1e-5 bound.  The ordered-sum kernel must reproduce the reference's norm exactly."""
+    from volta_b200 import VB_NS_F32
+    res = _run(oracle, engine, [(1024, 1024)], 1, VB_NS_F32, ns_steps=2)
+    assert res[0]["update"] <= TOL_F32, res
+    assert res[0]["weights_exact"], res
+
+
+def test_ordered_sum_adversarial_values(oracle, engine):
+    """Ties, huge dynamic range, zeros and denormals in the sum of squares: ns_steps = 0 makes
+    the update exactly u / sqrt(sumsq + 1e-8), so equality of the update pins the sum."""
+    from volta_b200 import VB_NS_F32, Muon, Tensor
+    rng = np.random.default_rng(5)
+    n_r, n_c = 96, 512
+    cases = []
+    cases.append(np.full((n_r, n_c), 2.0 ** -6, np.float32))                      # constant: many exact ties
+    x = np.exp2(rng.integers(-20, 3, (n_r, n_c))).astype(np.float32)              # powers of two
+    cases.append(x)
+    x = (rng.standard_normal((n_r, n_c)) * 1e-3).astype(np.float32)
+    x[::7, ::3] = 0.0
+    x[5, 5] = 30.0                                                                 # one huge addend mid-stream
+    cases.append(x)
+    x = (rng.standard_normal((n_r, n_c)) * 1e-20).astype(np.float32)              # squares are denormal / zero
+    cases.append(x)
+    x = np.sort(np.abs(rng.standard_normal((n_r, n_c)).astype(np.float32)).reshape(-1))[::-1].reshape(n_r, n_c).copy()
+    cases.append(x)                                                                # big first, then tiny
+    for g in cases:
+        w = Tensor(np.zeros((n_r, n_c), np.float32))
+        opt = Muon([w], 0.1, 0.0, False, 0, ns_mode=VB_NS_F32, engine=engine)
+        w.grad = g
+        opt.step()
+        wr = np.zeros((n_r, n_c), np.float32)
+        ref = oracle.Muon([wr], 0.1, 0.0, False, 0)
+        ref.step([g])
+        assert bits_equal(opt.last_update(0), ref.last_update[0])
+        opt.close()

@@ -145,28 +145,27 @@ static int build_arena(vb_optimizer *opt, int n_state_buffers, bool shard_states
 static int build_chunk_table(vb_optimizer *opt, const Layout &L)
 {
     vb_engine *e = opt->eng;
-    std::vector<TensorDesc> tds((size_t)std::max<int64_t>(opt->n_tensors, 1));
-    for (int64_t i = 0; i < opt->n_tensors; ++i) {
-        const int64_t off = opt->offsets[(size_t)i];
-        TensorDesc &td = tds[(size_t)i];
-        td.p = opt->d_param + off;
-        td.g = opt->d_grad + off;
-        // state arrays start at shard_begin: bias the pointers so that index i of the
-        // tensor addresses the state of arena element off + i
-        const intptr_t bias = (intptr_t)(off - opt->shard_begin) * (intptr_t)sizeof(float);
-        td.s1 = opt->d_s1 ? (float *)((intptr_t)opt->d_s1 + bias) : nullptr;
-        td.s2 = opt->d_s2 ? (float *)((intptr_t)opt->d_s2 + bias) : nullptr;
+    std::vector<FatChunk> fat(L.chunks.size());
+    for (size_t c = 0; c < L.chunks.size(); ++c) {
+        const ChunkDesc &ch = L.chunks[c];
+        const int64_t pos = opt->offsets[ch.tensor] + ch.offset;  // arena element of the chunk start
+        FatChunk &f = fat[c];
+        f.p = opt->d_param + pos;
+        f.g = opt->d_grad + pos;
+        // state arrays cover only this rank's slice [shard_begin, shard_end)
+        f.s1 = opt->d_s1 ? opt->d_s1 + (pos - opt->shard_begin) : nullptr;
+        f.s2 = opt->d_s2 ? opt->d_s2 + (pos - opt->shard_begin) : nullptr;
+        f.len = ch.len;
+        f.tensor = ch.tensor;
+        f.pad = 0;
     }
-    opt->n_chunks = (int64_t)L.chunks.size();
-    VB_CUDA(cudaMalloc(&opt->d_tensors, tds.size() * sizeof(TensorDesc)));
-    VB_CUDA(cudaMemcpyAsync(opt->d_tensors, tds.data(), tds.size() * sizeof(TensorDesc),
-                            cudaMemcpyHostToDevice, e->stream));
-    if (!L.chunks.empty()) {
-        VB_CUDA(cudaMalloc(&opt->d_chunks, L.chunks.size() * sizeof(ChunkDesc)));
-        VB_CUDA(cudaMemcpyAsync(opt->d_chunks, L.chunks.data(), L.chunks.size() * sizeof(ChunkDesc),
+    opt->n_chunks = (int64_t)fat.size();
+    if (!fat.empty()) {
+        VB_CUDA(cudaMalloc(&opt->d_chunks, fat.size() * sizeof(FatChunk)));
+        VB_CUDA(cudaMemcpyAsync(opt->d_chunks, fat.data(), fat.size() * sizeof(FatChunk),
                                 cudaMemcpyHostToDevice, e->stream));
     }
-    VB_CUDA(cudaStreamSynchronize(e->stream));  // the host vectors go out of scope
+    VB_CUDA(cudaStreamSynchronize(e->stream));  // the host vector goes out of scope
     return VB_OK;
 }
 
@@ -193,7 +192,6 @@ static void free_optimizer(vb_optimizer *opt)
     cudaFree(opt->d_grad);
     cudaFree(opt->d_s1);
     cudaFree(opt->d_s2);
-    cudaFree(opt->d_tensors);
     cudaFree(opt->d_chunks);
     cudaFree(opt->d_present);
     delete opt;
@@ -645,7 +643,9 @@ int vb_optimizer_step_ex(vb_optimizer *opt, uint32_t flags)
     }
     VB_TRY(sync_present(opt));
     if (opt->n_chunks > 0) {
-        VB_TRY(launch_multi_tensor(op, opt->d_tensors, opt->d_chunks, opt->n_chunks, opt->d_present, s,
+        bool all_present = true;
+        for (int64_t i = 0; i < opt->n_tensors && all_present; ++i) all_present = opt->present[(size_t)i] != 0;
+        VB_TRY(launch_multi_tensor(op, opt->d_chunks, opt->n_chunks, opt->d_present, all_present, s,
                                    e->sm_count, e->stream));
         e->launches += 1;
     }
@@ -680,9 +680,10 @@ int vb_optimizer_export_state(vb_optimizer *opt, int64_t tensor, int which, floa
         return fail(VB_ERR_STATE, "this optimizer has no state buffer %d (e.g. SGD without momentum)", which);
     if (n > 0) memset(host, 0, (size_t)n * sizeof(float));
     if (hi > lo) {
-        const int64_t arena_pos = opt->offsets[tensor] + lo;
-        VB_CUDA(cudaMemcpyAsync(host + lo, state + (arena_pos - opt->shard_begin),
-                                (size_t)(hi - lo) * sizeof(float), cudaMemcpyDeviceToHost,
+        const float *src = opt->kind == KIND_MUON
+                               ? muon_velocity_ptr(opt, tensor) + lo
+                               : state + (opt->offsets[tensor] + lo - opt->shard_begin);
+        VB_CUDA(cudaMemcpyAsync(host + lo, src, (size_t)(hi - lo) * sizeof(float), cudaMemcpyDeviceToHost,
                                 opt->eng->stream));
         VB_CUDA(cudaStreamSynchronize(opt->eng->stream));
     }
@@ -712,9 +713,9 @@ int vb_optimizer_import_state(vb_optimizer *opt, int64_t tensor, int which, cons
     }
     if (!state && hi > lo) return fail(VB_ERR_STATE, "this optimizer has no state buffer %d", which);
     if (hi > lo) {
-        const int64_t arena_pos = opt->offsets[tensor] + lo;
-        VB_CUDA(cudaMemcpyAsync(state + (arena_pos - opt->shard_begin), host + lo,
-                                (size_t)(hi - lo) * sizeof(float), cudaMemcpyHostToDevice,
+        float *dst = opt->kind == KIND_MUON ? muon_velocity_ptr(opt, tensor) + lo
+                                            : state + (opt->offsets[tensor] + lo - opt->shard_begin);
+        VB_CUDA(cudaMemcpyAsync(dst, host + lo, (size_t)(hi - lo) * sizeof(float), cudaMemcpyHostToDevice,
                                 opt->eng->stream));
         VB_CUDA(cudaStreamSynchronize(opt->eng->stream));
     }
@@ -805,41 +806,33 @@ int vb_multi_tensor_step(vb_engine *e, const vb_optimizer_step_params *hp, int64
     for (int64_t i = 0; i < n_tensors; ++i) n_chunks += (sizes[i] + chunk_len - 1) / chunk_len;
     if (n_chunks == 0) return VB_OK;
 
-    // layout of the staging block: [TensorDesc x n][ChunkDesc x n_chunks][present x n]
-    const size_t td_bytes = (size_t)n_tensors * sizeof(TensorDesc);
-    const size_t ch_off = (td_bytes + 15) / 16 * 16;
-    const size_t ch_bytes = (size_t)n_chunks * sizeof(ChunkDesc);
-    const size_t pr_off = ch_off + ch_bytes;
-    const size_t bytes = pr_off + (size_t)n_tensors;
+    // staging block: one FatChunk per chunk, built in pinned memory and copied on the stream
+    const size_t bytes = (size_t)n_chunks * sizeof(FatChunk);
     const int slot = e->stage_next;
     e->stage_next ^= 1;
     if (e->stage_done[slot]) VB_CUDA(cudaEventSynchronize(e->stage_done[slot]));  // previous user of this slot
     VB_TRY(ensure_stage(e, slot, bytes));
-    char *h = (char *)e->h_stage[slot];
-    TensorDesc *tds = (TensorDesc *)h;
-    ChunkDesc *chs = (ChunkDesc *)(h + ch_off);
-    uint8_t *pres = (uint8_t *)(h + pr_off);
+    FatChunk *chs = (FatChunk *)e->h_stage[slot];
     int64_t c = 0;
     for (int64_t i = 0; i < n_tensors; ++i) {
-        tds[i].p = (float *)params[i];
-        tds[i].g = (const float *)grads[i];
-        tds[i].s1 = state1 ? (float *)state1[i] : nullptr;
-        tds[i].s2 = state2 ? (float *)state2[i] : nullptr;
-        pres[i] = 1;
         for (int64_t b = 0; b < sizes[i]; b += chunk_len) {
-            chs[c].offset = b;
-            chs[c].tensor = (uint32_t)i;
-            chs[c].len = (uint32_t)std::min(chunk_len, sizes[i] - b);
-            ++c;
+            FatChunk &f = chs[c++];
+            f.p = (float *)params[i] + b;
+            f.g = (const float *)grads[i] + b;
+            f.s1 = (state1 && state1[i]) ? (float *)state1[i] + b : nullptr;
+            f.s2 = (state2 && state2[i]) ? (float *)state2[i] + b : nullptr;
+            f.len = (uint32_t)std::min(chunk_len, sizes[i] - b);
+            f.tensor = (uint32_t)i;
+            f.pad = 0;
         }
     }
-    char *d = (char *)e->d_stage[slot];
-    VB_CUDA(cudaMemcpyAsync(d, h, bytes, cudaMemcpyHostToDevice, e->stream));
+    FatChunk *d = (FatChunk *)e->d_stage[slot];
+    VB_CUDA(cudaMemcpyAsync(d, chs, bytes, cudaMemcpyHostToDevice, e->stream));
     VB_CUDA(cudaEventRecord(e->stage_done[slot], e->stream));
     const StepScalars s = make_scalars((int)hp->op, hp->lr, hp->beta1, hp->beta2, hp->eps, hp->weight_decay,
                                        (int64_t)hp->t);
-    VB_TRY(launch_multi_tensor((int)hp->op, (const TensorDesc *)d, (const ChunkDesc *)(d + ch_off), n_chunks,
-                               (const uint8_t *)(d + pr_off), s, e->sm_count, e->stream));
+    VB_TRY(launch_multi_tensor((int)hp->op, d, n_chunks, nullptr, /*all_present=*/true, s, e->sm_count,
+                               e->stream));
     e->launches += 1;
     return VB_OK;
     VB_API_END

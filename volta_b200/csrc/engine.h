@@ -54,8 +54,7 @@ struct vb_optimizer {
     int64_t t = 0;
 
     // descriptors
-    vb::TensorDesc *d_tensors = nullptr;
-    vb::ChunkDesc *d_chunks = nullptr;
+    vb::FatChunk *d_chunks = nullptr;
     int64_t n_chunks = 0;
     uint8_t *d_present = nullptr;
     std::vector<uint8_t> present;        // host truth
@@ -72,6 +71,8 @@ int muon_step(vb_optimizer *opt, uint32_t flags);
 int muon_download_update(vb_optimizer *opt, int64_t tensor, float *host, int64_t n);
 int muon_last_flops(vb_optimizer *opt, double *flops);
 int muon_owner(vb_optimizer *opt, int64_t tensor);
+float *muon_velocity_ptr(vb_optimizer *opt, int64_t tensor);  // nullptr if not owned
+void plan_muon_owners(int64_t n, const int64_t *rows, const int64_t *cols, int world, int *owner_out);
 
 // comm.cpp
 int comm_unique_id(void *id128);

@@ -2,7 +2,7 @@
 //
 // One launch updates every tensor of an optimizer: the grid strides over a chunk table
 // (fixed-length pieces of tensors, so ragged tensor lists load-balance), each chunk is
-// streamed with 128-bit loads/stores of param / grad / state, and every element is
+// streamed with 256-bit (else 128-bit) loads/stores of param / grad / state, and every element is
 // touched exactly once (HBM traffic = 28 B/param for Adam, 20 B/param for SGD with
 // momentum, 12 B/param for plain SGD).
 //
@@ -18,7 +18,34 @@ namespace vb {
 namespace {
 
 constexpr int kThreads = 256;
-constexpr int kUnroll = 2;  // independent 128-bit transactions per array per thread in flight
+// Launch shape found by sweeping on a B200: 256-bit loads, one vector per array per thread
+// in flight, exactly 3 CTAs of 256 threads per SM.  More resident threads or deeper
+// unrolling put more requests in flight than the HBM controllers like and cost up to 15 %.
+constexpr int kCtasPerSm = 3;
+constexpr int kVecElems = 8;  // floats per 256-bit access
+
+struct alignas(32) Vec8 {
+    float4 lo, hi;
+};
+
+// 256-bit global accesses (sm_100: ld/st.global.v8.f32).  Loads bypass L1: every byte is
+// touched once per step.
+__device__ __forceinline__ Vec8 ld_vec8(const Vec8 *p)
+{
+    Vec8 r;
+    asm volatile("ld.global.L1::no_allocate.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=f"(r.lo.x), "=f"(r.lo.y), "=f"(r.lo.z), "=f"(r.lo.w), "=f"(r.hi.x), "=f"(r.hi.y),
+                   "=f"(r.hi.z), "=f"(r.hi.w)
+                 : "l"(p));
+    return r;
+}
+
+__device__ __forceinline__ void st_vec8(Vec8 *p, const Vec8 &r)
+{
+    asm volatile("st.global.v8.f32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "f"(r.lo.x), "f"(r.lo.y),
+                 "f"(r.lo.z), "f"(r.lo.w), "f"(r.hi.x), "f"(r.hi.y), "f"(r.hi.z), "f"(r.hi.w)
+                 : "memory");
+}
 
 template <int OP>
 __device__ __forceinline__ void update_one(float &p, float g, float &s1, float &s2,
@@ -54,87 +81,107 @@ __device__ __forceinline__ void update_vec(float4 &p, const float4 &g, float4 &a
     update_one<OP>(p.w, g.w, a.w, b.w, s);
 }
 
-template <int OP>
-__global__ void __launch_bounds__(kThreads)
-multi_tensor_update_kernel(const TensorDesc *__restrict__ tensors,
-                           const ChunkDesc *__restrict__ chunks, int64_t n_chunks,
-                           const uint8_t *__restrict__ present, const StepScalars s)
+__device__ __forceinline__ FatChunk load_chunk(const FatChunk *c)
 {
-    constexpr bool kHasS1 = (OP != OP_SGD);
-    constexpr bool kHasS2 = (OP == OP_ADAM);
-
-    for (int64_t c = blockIdx.x; c < n_chunks; c += gridDim.x) {
-        const ChunkDesc ch = chunks[c];
-        if (present[ch.tensor] == 0) continue;  // `grad == None`: adam.rs:81-84, sgd.rs:75-78
-        const TensorDesc td = tensors[ch.tensor];
-        float *__restrict__ p = td.p + ch.offset;
-        const float *__restrict__ g = td.g + ch.offset;
-        float *__restrict__ s1 = kHasS1 ? td.s1 + ch.offset : nullptr;
-        float *__restrict__ s2 = kHasS2 ? td.s2 + ch.offset : nullptr;
-        const uint32_t n = ch.len;
-
-        uintptr_t align_bits = reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g);
-        if (kHasS1) align_bits |= reinterpret_cast<uintptr_t>(s1);
-        if (kHasS2) align_bits |= reinterpret_cast<uintptr_t>(s2);
-
-        uint32_t done = 0;
-        if ((align_bits & 15u) == 0) {
-            const uint32_t n4 = n >> 2;
-            float4 *__restrict__ p4 = reinterpret_cast<float4 *>(p);
-            const float4 *__restrict__ g4 = reinterpret_cast<const float4 *>(g);
-            float4 *__restrict__ a4 = reinterpret_cast<float4 *>(s1);
-            float4 *__restrict__ b4 = reinterpret_cast<float4 *>(s2);
-            for (uint32_t base = 0; base < n4; base += kThreads * kUnroll) {
-                float4 vp[kUnroll], vg[kUnroll], va[kUnroll], vb[kUnroll];
-#pragma unroll
-                for (int u = 0; u < kUnroll; ++u) {
-                    const uint32_t i = base + u * kThreads + threadIdx.x;
-                    if (i < n4) {
-                        vp[u] = __ldcs(p4 + i);
-                        vg[u] = __ldcs(g4 + i);
-                        if (kHasS1) va[u] = __ldcs(a4 + i);
-                        if (kHasS2) vb[u] = __ldcs(b4 + i);
-                    }
-                }
-#pragma unroll
-                for (int u = 0; u < kUnroll; ++u) {
-                    const uint32_t i = base + u * kThreads + threadIdx.x;
-                    if (i < n4) {
-                        update_vec<OP>(vp[u], vg[u], va[u], vb[u], s);
-                        __stcs(p4 + i, vp[u]);
-                        if (kHasS1) __stcs(a4 + i, va[u]);
-                        if (kHasS2) __stcs(b4 + i, vb[u]);
-                    }
-                }
-            }
-            done = n4 << 2;
-        }
-        // ragged tail (n mod 4) or a chunk whose pointers are not 16-byte aligned
-        for (uint32_t i = done + threadIdx.x; i < n; i += kThreads) {
-            float vp = p[i], va = 0.0f, vb = 0.0f;
-            const float vg = g[i];
-            if (kHasS1) va = s1[i];
-            if (kHasS2) vb = s2[i];
-            update_one<OP>(vp, vg, va, vb, s);
-            p[i] = vp;
-            if (kHasS1) s1[i] = va;
-            if (kHasS2) s2[i] = vb;
-        }
-    }
+    // 48 bytes as three 128-bit read-only loads
+    const uint4 *q = reinterpret_cast<const uint4 *>(c);
+    union {
+        uint4 v[3];
+        FatChunk f;
+    } u;
+    u.v[0] = __ldg(q);
+    u.v[1] = __ldg(q + 1);
+    u.v[2] = __ldg(q + 2);
+    return u.f;
 }
 
 template <int OP>
-int occupancy_ctas_per_sm()
+__device__ __forceinline__ void update_chunk(const FatChunk &ch, const StepScalars &s)
 {
-    static int cached = 0;
-    if (cached == 0) {
-        int n = 0;
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, multi_tensor_update_kernel<OP>,
-                                                          kThreads, 0) != cudaSuccess || n < 1)
-            n = 4;
-        cached = n;
+    constexpr bool kHasS1 = (OP != OP_SGD);
+    constexpr bool kHasS2 = (OP == OP_ADAM);
+    float *__restrict__ p = ch.p;
+    const float *__restrict__ g = ch.g;
+    float *__restrict__ s1 = kHasS1 ? ch.s1 : nullptr;
+    float *__restrict__ s2 = kHasS2 ? ch.s2 : nullptr;
+    const uint32_t n = ch.len;
+
+    uintptr_t align_bits = reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g);
+    if (kHasS1) align_bits |= reinterpret_cast<uintptr_t>(s1);
+    if (kHasS2) align_bits |= reinterpret_cast<uintptr_t>(s2);
+
+    uint32_t done = 0;
+    if ((align_bits & 31u) == 0) {
+        const uint32_t n8 = n >> 3;
+        Vec8 *__restrict__ p8 = reinterpret_cast<Vec8 *>(p);
+        const Vec8 *__restrict__ g8 = reinterpret_cast<const Vec8 *>(g);
+        Vec8 *__restrict__ a8 = reinterpret_cast<Vec8 *>(s1);
+        Vec8 *__restrict__ b8 = reinterpret_cast<Vec8 *>(s2);
+        for (uint32_t i = threadIdx.x; i < n8; i += kThreads) {
+            Vec8 vp = ld_vec8(p8 + i), va, vb;
+            const Vec8 vg = ld_vec8(g8 + i);
+            if (kHasS1) va = ld_vec8(a8 + i);
+            if (kHasS2) vb = ld_vec8(b8 + i);
+            update_vec<OP>(vp.lo, vg.lo, va.lo, vb.lo, s);
+            update_vec<OP>(vp.hi, vg.hi, va.hi, vb.hi, s);
+            st_vec8(p8 + i, vp);
+            if (kHasS1) st_vec8(a8 + i, va);
+            if (kHasS2) st_vec8(b8 + i, vb);
+        }
+        done = n8 << 3;
+    } else if ((align_bits & 15u) == 0) {
+        const uint32_t n4 = n >> 2;
+        float4 *__restrict__ p4 = reinterpret_cast<float4 *>(p);
+        const float4 *__restrict__ g4 = reinterpret_cast<const float4 *>(g);
+        float4 *__restrict__ a4 = reinterpret_cast<float4 *>(s1);
+        float4 *__restrict__ b4 = reinterpret_cast<float4 *>(s2);
+        for (uint32_t i = threadIdx.x; i < n4; i += kThreads) {
+            float4 vp = __ldcs(p4 + i), va, vb;
+            const float4 vg = __ldcs(g4 + i);
+            if (kHasS1) va = __ldcs(a4 + i);
+            if (kHasS2) vb = __ldcs(b4 + i);
+            update_vec<OP>(vp, vg, va, vb, s);
+            __stcs(p4 + i, vp);
+            if (kHasS1) __stcs(a4 + i, va);
+            if (kHasS2) __stcs(b4 + i, vb);
+        }
+        done = n4 << 2;
     }
-    return cached;
+    // ragged tail (n mod 8 / n mod 4) or a chunk whose pointers are not 16-byte aligned
+    for (uint32_t i = done + threadIdx.x; i < n; i += kThreads) {
+        float vp = p[i], va = 0.0f, vb = 0.0f;
+        const float vg = g[i];
+        if (kHasS1) va = s1[i];
+        if (kHasS2) vb = s2[i];
+        update_one<OP>(vp, vg, va, vb, s);
+        p[i] = vp;
+        if (kHasS1) s1[i] = va;
+        if (kHasS2) s2[i] = vb;
+    }
+}
+
+// CHECK_PRESENT = false is the common case (every tensor has a gradient): the descriptor of
+// the next chunk is fetched while the current one streams, so no dependent-load latency
+// sits between chunks.  With CHECK_PRESENT the per-tensor flag is looked up as well.
+template <int OP, bool CHECK_PRESENT>
+__global__ void __launch_bounds__(kThreads, kCtasPerSm)
+multi_tensor_update_kernel(const FatChunk *__restrict__ chunks, int64_t n_chunks,
+                           const uint8_t *__restrict__ present, const StepScalars s)
+{
+    int64_t c = blockIdx.x;
+    if (c >= n_chunks) return;
+    FatChunk cur = load_chunk(chunks + c);
+    for (;;) {
+        const int64_t cn = c + gridDim.x;
+        const bool has_next = cn < n_chunks;
+        FatChunk nxt = cur;
+        if (has_next) nxt = load_chunk(chunks + cn);  // in flight while `cur` is processed
+        // `grad == None` -> skip: adam.rs:81-84, sgd.rs:75-78
+        if (!CHECK_PRESENT || present[cur.tensor] != 0) update_chunk<OP>(cur, s);
+        if (!has_next) break;
+        cur = nxt;
+        c = cn;
+    }
 }
 
 }  // namespace
@@ -176,44 +223,42 @@ StepScalars make_scalars(int op, float lr, float beta1, float beta2, float eps, 
 
 int64_t pick_chunk_len(int64_t total_elements, int sm_count)
 {
-    // Enough chunks that every SM sees dozens (small tail), but each long enough to
-    // amortise the descriptor fetch: between 2 Ki and 16 Ki elements, a multiple of
-    // kThreads * 4 * kUnroll so full chunks have no partial vector iteration.
-    const int64_t quantum = kThreads * 4 * kUnroll;
+    // One or two passes of a CTA (256 threads x 8 floats = 2048 elements per pass): short
+    // enough that every CTA walks >100 chunks of a large model (static round-robin then
+    // balances to <1 %), long enough to amortise the 48-byte descriptor.  Measured on B200:
+    // 2 Ki .. 8 Ki elements stream equally fast, longer chunks lose a few percent.
+    const int64_t quantum = kThreads * kVecElems;
     int64_t len = total_elements / ((int64_t)sm_count * 64);
     len = (len + quantum - 1) / quantum * quantum;
     if (len < quantum) len = quantum;
-    if (len > 8 * quantum) len = 8 * quantum;
+    if (len > 2 * quantum) len = 2 * quantum;
     return len;
 }
 
-int launch_multi_tensor(int op, const TensorDesc *d_tensors, const ChunkDesc *d_chunks,
-                        int64_t n_chunks, const uint8_t *d_present, const StepScalars &s,
-                        int sm_count, cudaStream_t stream)
+template <int OP>
+static void launch_op(unsigned grid, const FatChunk *d_chunks, int64_t n_chunks, const uint8_t *d_present,
+                      bool all_present, const StepScalars &s, cudaStream_t stream)
+{
+    if (all_present)
+        multi_tensor_update_kernel<OP, false><<<grid, kThreads, 0, stream>>>(d_chunks, n_chunks, d_present, s);
+    else
+        multi_tensor_update_kernel<OP, true><<<grid, kThreads, 0, stream>>>(d_chunks, n_chunks, d_present, s);
+}
+
+int launch_multi_tensor(int op, const FatChunk *d_chunks, int64_t n_chunks, const uint8_t *d_present,
+                        bool all_present, const StepScalars &s, int sm_count, cudaStream_t stream)
 {
     if (n_chunks <= 0) return VB_OK;
-    int per_sm;
-    switch (op) {
-        case OP_ADAM: per_sm = occupancy_ctas_per_sm<OP_ADAM>(); break;
-        case OP_SGD_MOMENTUM: per_sm = occupancy_ctas_per_sm<OP_SGD_MOMENTUM>(); break;
-        case OP_SGD: per_sm = occupancy_ctas_per_sm<OP_SGD>(); break;
-        default: return fail(VB_ERR_INVALID_ARG, "unknown multi-tensor op %d", op);
-    }
-    int64_t grid = (int64_t)sm_count * per_sm;  // whole waves: a multiple of the SM count
+    if (op != OP_ADAM && op != OP_SGD_MOMENTUM && op != OP_SGD)
+        return fail(VB_ERR_INVALID_ARG, "unknown multi-tensor op %d", op);
+    int64_t grid = (int64_t)sm_count * kCtasPerSm;  // whole waves: a multiple of the SM count
     if (grid > n_chunks) grid = n_chunks;
     switch (op) {
-        case OP_ADAM:
-            multi_tensor_update_kernel<OP_ADAM><<<(unsigned)grid, kThreads, 0, stream>>>(
-                d_tensors, d_chunks, n_chunks, d_present, s);
-            break;
+        case OP_ADAM: launch_op<OP_ADAM>((unsigned)grid, d_chunks, n_chunks, d_present, all_present, s, stream); break;
         case OP_SGD_MOMENTUM:
-            multi_tensor_update_kernel<OP_SGD_MOMENTUM><<<(unsigned)grid, kThreads, 0, stream>>>(
-                d_tensors, d_chunks, n_chunks, d_present, s);
+            launch_op<OP_SGD_MOMENTUM>((unsigned)grid, d_chunks, n_chunks, d_present, all_present, s, stream);
             break;
-        default:
-            multi_tensor_update_kernel<OP_SGD><<<(unsigned)grid, kThreads, 0, stream>>>(
-                d_tensors, d_chunks, n_chunks, d_present, s);
-            break;
+        default: launch_op<OP_SGD>((unsigned)grid, d_chunks, n_chunks, d_present, all_present, s, stream); break;
     }
     VB_CUDA(cudaGetLastError());
     return VB_OK;

@@ -1,12 +1,657 @@
-// Placeholder until the Muon path lands: every entry reports VB_ERR_UNSUPPORTED.
+// Muon::step on the GPU (src/nn/optim/muon.rs:108-163): ownership of matrices, the
+// elementwise kernels (momentum / Nesterov, sum of squares, normalise, apply) and the
+// orchestration of the Newton-Schulz GEMM chain.
+//
+//   K3a  momentum_kernel      v = fma(mu, v, g); u = nesterov ? mu*v + g : v      muon.rs:133-150
+//   K3s  sumsq_ordered_kernel sum of u*u in the reference's left-to-right f32 order muon.rs:58
+//        (VB_NS_F32), or per-chunk partial sums + ordered reduce (VB_NS_BF16)
+//   K3b  normalise_kernel     x = u / sqrt(sumsq + 1e-8)                            muon.rs:59-64
+//   K4/5 Newton-Schulz GEMMs  ns_gemm_f32.cu / ns_gemm_tc.cu                        muon.rs:67-100
+//   K6   apply_kernel         w -= (lr * u) * 0.1                                   muon.rs:158-160
+//
+// Every kernel walks a chunk or tile table over all matrices this rank owns, so a step
+// is a fixed, small number of launches whatever the number of parameters.
+#include <cuda_bf16.h>
+
+#include <algorithm>
+#include <numeric>
+
 #include "engine.h"
+#include "ns_gemm.h"
 
 namespace vb {
-struct MuonState {};
-void destroy_muon_state(MuonState *s) { delete s; }
-int muon_init(vb_optimizer *) { return fail(VB_ERR_UNSUPPORTED, "Muon is not built yet"); }
-int muon_step(vb_optimizer *, uint32_t) { return fail(VB_ERR_UNSUPPORTED, "Muon is not built yet"); }
-int muon_download_update(vb_optimizer *, int64_t, float *, int64_t) { return fail(VB_ERR_UNSUPPORTED, "Muon is not built yet"); }
-int muon_last_flops(vb_optimizer *, double *) { return fail(VB_ERR_UNSUPPORTED, "Muon is not built yet"); }
-int muon_owner(vb_optimizer *, int64_t) { return 0; }
+
+namespace {
+
+constexpr int kEwThreads = 256;
+
+// ---- K3a: momentum (+ Nesterov), optional per-chunk sum of squares ------------------------
+// TensorDesc fields here: p = weights, g = gradient, s1 = velocity, s2 = update buffer.
+template <bool PARTIALS>
+__global__ void __launch_bounds__(kEwThreads)
+momentum_kernel(const TensorDesc *__restrict__ tensors, const ChunkDesc *__restrict__ chunks, int64_t n_chunks,
+                const uint8_t *__restrict__ present, float momentum, int nesterov, float *__restrict__ partials)
+{
+    __shared__ float warp_sums[kEwThreads / 32];
+    for (int64_t c = blockIdx.x; c < n_chunks; c += gridDim.x) {
+        const ChunkDesc ch = chunks[c];
+        if (present[ch.tensor] == 0) continue;
+        const TensorDesc td = tensors[ch.tensor];
+        const float *__restrict__ g = td.g + ch.offset;
+        float *__restrict__ v = td.s1 + ch.offset;
+        float *__restrict__ u = td.s2 + ch.offset;
+        const uint32_t n = ch.len;
+        float local = 0.0f;
+        const uint32_t n4 = n >> 2;  // chunk starts are 16-byte aligned by construction
+        for (uint32_t i = threadIdx.x; i < n4; i += kEwThreads) {
+            const float4 g4 = __ldcs(reinterpret_cast<const float4 *>(g) + i);
+            float4 v4 = __ldcs(reinterpret_cast<const float4 *>(v) + i);
+            float4 u4;
+            v4.x = __fmaf_rn(momentum, v4.x, g4.x);
+            v4.y = __fmaf_rn(momentum, v4.y, g4.y);
+            v4.z = __fmaf_rn(momentum, v4.z, g4.z);
+            v4.w = __fmaf_rn(momentum, v4.w, g4.w);
+            if (nesterov) {
+                u4.x = __fadd_rn(__fmul_rn(momentum, v4.x), g4.x);
+                u4.y = __fadd_rn(__fmul_rn(momentum, v4.y), g4.y);
+                u4.z = __fadd_rn(__fmul_rn(momentum, v4.z), g4.z);
+                u4.w = __fadd_rn(__fmul_rn(momentum, v4.w), g4.w);
+            } else {
+                u4 = v4;
+            }
+            __stcs(reinterpret_cast<float4 *>(v) + i, v4);
+            reinterpret_cast<float4 *>(u)[i] = u4;  // read again soon: keep it in L2
+            if (PARTIALS) local += u4.x * u4.x + u4.y * u4.y + u4.z * u4.z + u4.w * u4.w;
+        }
+        for (uint32_t i = (n4 << 2) + threadIdx.x; i < n; i += kEwThreads) {
+            const float gv = g[i];
+            const float vv = __fmaf_rn(momentum, v[i], gv);
+            const float uv = nesterov ? __fadd_rn(__fmul_rn(momentum, vv), gv) : vv;
+            v[i] = vv;
+            u[i] = uv;
+            if (PARTIALS) local += uv * uv;
+        }
+        if (PARTIALS) {
+            // fixed-shape tree: the result does not depend on timing
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1) local += __shfl_down_sync(0xffffffffu, local, d);
+            if ((threadIdx.x & 31) == 0) warp_sums[threadIdx.x >> 5] = local;
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                float s = 0.0f;
+#pragma unroll
+                for (int w = 0; w < kEwThreads / 32; ++w) s += warp_sums[w];
+                partials[c] = s;
+            }
+            __syncthreads();
+        }
+    }
+}
+
+// Adds each tensor's chunk partials in chunk order (one warp per tensor, lane-strided then
+// a fixed tree: deterministic).  Tensors without chunks keep sumsq = 0.
+__global__ void reduce_partials_kernel(const float *__restrict__ partials, const int64_t *__restrict__ first_chunk,
+                                       const int32_t *__restrict__ ns_tensors, int n_ns, float *__restrict__ sumsq)
+{
+    const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (w >= n_ns) return;
+    const int t = ns_tensors[w];
+    const int64_t lo = first_chunk[t], hi = first_chunk[t + 1];
+    float s = 0.0f;
+    for (int64_t c = lo + (threadIdx.x & 31); c < hi; c += 32) s += partials[c];
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) s += __shfl_down_sync(0xffffffffu, s, d);
+    if ((threadIdx.x & 31) == 0) sumsq[t] = s;
+}
+
+// ---- K3s: order-faithful sum of squares ------------------------------------------------------
+// The reference adds x*x left to right in f32 (muon.rs:58).  With millions of addends that
+// differs from the exact sum by up to a few 1e-3 relative, far more than the 1e-5 parity
+// bound of the f32 path, so the GPU must reproduce the *sequence of roundings*.
+//
+// All addends are >= 0, so the running sum s never decreases.  While s stays inside one
+// binade [2^e, 2^(e+1)) it is k * ulp with ulp = 2^(e-23) and integer k in [2^23, 2^24), and
+//     fl(s + a) = (k + rne(a / ulp)) * ulp,
+// where the round-to-nearest-even of a/ulp = q + f depends on s only through the parity of k
+// (and only when f is exactly 1/2).  So every element is a map  parity -> integer increment,
+// i.e. two numbers, and the composition of such maps is associative: a block composes the
+// maps of thousands of consecutive elements with an ordered tree and applies the result to
+// k in one go.  If the result would leave the binade (k + inc >= 2^24), or s is not a normal
+// number yet, one thread walks the elements with real f32 additions until the exponent of s
+// changes and the block resumes from there; this happens about once per doubling of s.
+struct IncMap {
+    uint32_t even;  // increment (in ulps) when k is even
+    uint32_t odd;   // increment when k is odd
+};
+constexpr uint32_t kIncSat = 1u << 25;  // ">= 2^24": leaves the binade for certain
+
+__device__ __forceinline__ IncMap compose(IncMap a, IncMap b)  // a first, then b
+{
+    IncMap c;
+    const uint32_t b_after_even = (a.even & 1u) ? b.odd : b.even;
+    const uint32_t b_after_odd = ((a.odd + 1u) & 1u) ? b.odd : b.even;
+    c.even = min(a.even + b_after_even, kIncSat);
+    c.odd = min(a.odd + b_after_odd, kIncSat);
+    return c;
+}
+
+__device__ __forceinline__ IncMap element_map(float a, int scale_exp)  // scale_exp = 23 - e
+{
+    IncMap m;
+    const float x = scalbnf(a, scale_exp);  // a / ulp, exact (or 0 / inf on under/overflow)
+    if (!(x < 16777216.0f)) {               // also catches NaN
+        m.even = m.odd = kIncSat;
+        return m;
+    }
+    const float q = floorf(x);
+    const float f = x - q;  // exact
+    const uint32_t qi = (uint32_t)q;
+    const uint32_t up = f > 0.5f ? 1u : 0u;
+    const uint32_t tie = f == 0.5f ? 1u : 0u;
+    m.even = qi + up + (tie & (qi & 1u));          // k even: k+q odd iff q odd -> round up to even
+    m.odd = qi + up + (tie & ((qi & 1u) ^ 1u));    // k odd:  k+q odd iff q even
+    return m;
+}
+
+__device__ __forceinline__ bool binade_ok(float s)
+{
+    const uint32_t e = (__float_as_uint(s) >> 23) & 0xffu;
+    return s > 0.0f && e != 0u && e != 0xffu;  // positive, normal, finite
+}
+
+constexpr int kSeqThreads = 512;
+constexpr int kSeqPerThread = 8;
+constexpr int kSeqChunk = kSeqThreads * kSeqPerThread;
+
+__global__ void __launch_bounds__(kSeqThreads)
+sumsq_ordered_kernel(const TensorDesc *__restrict__ tensors, const int32_t *__restrict__ ns_tensors,
+                     const int64_t *__restrict__ sizes, const uint8_t *__restrict__ present,
+                     float *__restrict__ sumsq)
+{
+    __shared__ float sq[kSeqChunk];
+    __shared__ IncMap warp_maps[kSeqThreads / 32];
+    __shared__ float sh_s;
+    __shared__ int sh_start;
+
+    const int t = ns_tensors[blockIdx.x];
+    if (present[t] == 0) return;
+    const float *__restrict__ x = tensors[t].s2;  // the update buffer
+    const int64_t n = sizes[t];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+    if (tid == 0) sh_s = 0.0f;
+
+    float cur[kSeqPerThread], nxt[kSeqPerThread];
+    auto load = [&](int64_t base, float *dst) {
+        const int64_t i0 = base + (int64_t)tid * kSeqPerThread;
+        if (i0 + kSeqPerThread <= n) {  // tensors start 128-byte aligned: vector loads are aligned
+            const float4 a = *reinterpret_cast<const float4 *>(x + i0);
+            const float4 b = *reinterpret_cast<const float4 *>(x + i0 + 4);
+            dst[0] = a.x; dst[1] = a.y; dst[2] = a.z; dst[3] = a.w;
+            dst[4] = b.x; dst[5] = b.y; dst[6] = b.z; dst[7] = b.w;
+        } else {
+#pragma unroll
+            for (int i = 0; i < kSeqPerThread; ++i) dst[i] = (i0 + i < n) ? x[i0 + i] : 0.0f;
+        }
+    };
+    load(0, cur);
+    for (int64_t base = 0; base < n; base += kSeqChunk) {
+        if (base + kSeqChunk < n) load(base + kSeqChunk, nxt);  // prefetch the next chunk
+        const int cnt = (int)min((int64_t)kSeqChunk, n - base);
+        float a[kSeqPerThread];
+#pragma unroll
+        for (int i = 0; i < kSeqPerThread; ++i) {
+            a[i] = __fmul_rn(cur[i], cur[i]);  // `x * x`, muon.rs:58 (padding squares to 0)
+            sq[tid * kSeqPerThread + i] = a[i];
+        }
+        if (tid == 0) sh_start = 0;
+        __syncthreads();
+        for (;;) {
+            const int start = sh_start;
+            const float s = sh_s;
+            if (start >= cnt) break;
+            const bool ok = binade_ok(s);
+            if (ok) {
+                const int scale_exp = 23 - ((int)((__float_as_uint(s) >> 23) & 0xffu) - 127);
+                IncMap m = {0u, 0u};
+#pragma unroll
+                for (int i = 0; i < kSeqPerThread; ++i) {
+                    const int idx = tid * kSeqPerThread + i;
+                    if (idx >= start && idx < cnt) m = compose(m, element_map(a[i], scale_exp));
+                }
+#pragma unroll
+                for (int d = 1; d < 32; d <<= 1) {
+                    IncMap o;
+                    o.even = __shfl_down_sync(0xffffffffu, m.even, d);
+                    o.odd = __shfl_down_sync(0xffffffffu, m.odd, d);
+                    if ((lane & (2 * d - 1)) == 0) m = compose(m, o);
+                }
+                if (lane == 0) warp_maps[warp] = m;
+            }
+            __syncthreads();
+            if (tid == 0) {
+                float s_new = s;
+                bool advanced = false;
+                if (ok) {
+                    IncMap total = warp_maps[0];
+                    for (int w = 1; w < kSeqThreads / 32; ++w) total = compose(total, warp_maps[w]);
+                    const uint32_t bits = __float_as_uint(s);
+                    const uint32_t k = (bits & 0x7fffffu) | 0x800000u;
+                    const uint32_t inc = (k & 1u) ? total.odd : total.even;
+                    if (k + inc < (1u << 24)) {
+                        s_new = __uint_as_float((bits & 0x7f800000u) | ((k + inc) & 0x7fffffu));
+                        sh_start = cnt;
+                        advanced = true;
+                    }
+                }
+                if (!advanced) {
+                    // walk with real additions until s enters a new binade (or the chunk ends)
+                    int j = start;
+                    while (j < cnt) {
+                        const float nx = __fadd_rn(s_new, sq[j]);
+                        const bool changed = ((__float_as_uint(nx) ^ __float_as_uint(s_new)) >> 23) != 0u;
+                        s_new = nx;
+                        ++j;
+                        if (changed && binade_ok(s_new)) break;
+                    }
+                    sh_start = j;
+                }
+                sh_s = s_new;
+            }
+            __syncthreads();
+        }
+        __syncthreads();  // everyone has left the loop before sq / sh_start are rewritten
+#pragma unroll
+        for (int i = 0; i < kSeqPerThread; ++i) cur[i] = nxt[i];
+    }
+    __syncthreads();
+    if (tid == 0) sumsq[t] = sh_s;
+}
+
+// ---- K3b: normalise ----------------------------------------------------------------------------
+// x = u / sqrt(sumsq + 1e-8) where the norm exceeds 1e-8 (muon.rs:59-64).  F32 mode rewrites
+// the update buffer in place; BF16 mode writes the bf16 operand of the first GEMM.
+template <bool TO_BF16>
+__global__ void __launch_bounds__(kEwThreads)
+normalise_kernel(const TensorDesc *__restrict__ tensors, const ChunkDesc *__restrict__ chunks, int64_t n_chunks,
+                 const uint8_t *__restrict__ present, const uint8_t *__restrict__ is_ns,
+                 const float *__restrict__ sumsq, const float *upd_base, __nv_bfloat16 *__restrict__ xb_base)
+{
+    for (int64_t c = blockIdx.x; c < n_chunks; c += gridDim.x) {
+        const ChunkDesc ch = chunks[c];
+        if (present[ch.tensor] == 0 || is_ns[ch.tensor] == 0) continue;
+        float *u = tensors[ch.tensor].s2 + ch.offset;
+        const float norm = __fsqrt_rn(__fadd_rn(sumsq[ch.tensor], 1e-8f));
+        const bool scale = norm > 1e-8f;
+        const uint32_t n = ch.len;
+        if (TO_BF16) {
+            __nv_bfloat16 *xb = xb_base + (u - upd_base);
+            const uint32_t n4 = n >> 2;
+            for (uint32_t i = threadIdx.x; i < n4; i += kEwThreads) {
+                float4 v = reinterpret_cast<const float4 *>(u)[i];
+                if (scale) {
+                    v.x = __fdiv_rn(v.x, norm); v.y = __fdiv_rn(v.y, norm);
+                    v.z = __fdiv_rn(v.z, norm); v.w = __fdiv_rn(v.w, norm);
+                }
+                __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+                uint2 packed;
+                packed.x = *reinterpret_cast<uint32_t *>(&lo);
+                packed.y = *reinterpret_cast<uint32_t *>(&hi);
+                reinterpret_cast<uint2 *>(xb)[i] = packed;
+            }
+            for (uint32_t i = (n4 << 2) + threadIdx.x; i < n; i += kEwThreads)
+                xb[i] = __float2bfloat16_rn(scale ? __fdiv_rn(u[i], norm) : u[i]);
+        } else {
+            if (!scale) continue;
+            const uint32_t n4 = n >> 2;
+            for (uint32_t i = threadIdx.x; i < n4; i += kEwThreads) {
+                float4 v = reinterpret_cast<const float4 *>(u)[i];
+                v.x = __fdiv_rn(v.x, norm); v.y = __fdiv_rn(v.y, norm);
+                v.z = __fdiv_rn(v.z, norm); v.w = __fdiv_rn(v.w, norm);
+                reinterpret_cast<float4 *>(u)[i] = v;
+            }
+            for (uint32_t i = (n4 << 2) + threadIdx.x; i < n; i += kEwThreads) u[i] = __fdiv_rn(u[i], norm);
+        }
+    }
+}
+
+// ---- K6: apply -----------------------------------------------------------------------------------
+// w -= lr * u * 0.1 (muon.rs:158-160; Rust evaluates (lr * u) * 0.1).  TensorDesc.g here points
+// at the buffer that holds the final update of the tensor.
+__global__ void __launch_bounds__(kEwThreads)
+apply_kernel(const TensorDesc *__restrict__ tensors, const ChunkDesc *__restrict__ chunks, int64_t n_chunks,
+             const uint8_t *__restrict__ present, float lr)
+{
+    for (int64_t c = blockIdx.x; c < n_chunks; c += gridDim.x) {
+        const ChunkDesc ch = chunks[c];
+        if (present[ch.tensor] == 0) continue;
+        float *__restrict__ w = tensors[ch.tensor].p + ch.offset;
+        const float *__restrict__ u = tensors[ch.tensor].g + ch.offset;
+        const uint32_t n = ch.len;
+        const uint32_t n4 = n >> 2;
+        for (uint32_t i = threadIdx.x; i < n4; i += kEwThreads) {
+            float4 wv = __ldcs(reinterpret_cast<const float4 *>(w) + i);
+            const float4 uv = __ldcs(reinterpret_cast<const float4 *>(u) + i);
+            wv.x = __fsub_rn(wv.x, __fmul_rn(__fmul_rn(lr, uv.x), 0.1f));
+            wv.y = __fsub_rn(wv.y, __fmul_rn(__fmul_rn(lr, uv.y), 0.1f));
+            wv.z = __fsub_rn(wv.z, __fmul_rn(__fmul_rn(lr, uv.z), 0.1f));
+            wv.w = __fsub_rn(wv.w, __fmul_rn(__fmul_rn(lr, uv.w), 0.1f));
+            __stcs(reinterpret_cast<float4 *>(w) + i, wv);
+        }
+        for (uint32_t i = (n4 << 2) + threadIdx.x; i < n; i += kEwThreads)
+            w[i] = __fsub_rn(w[i], __fmul_rn(__fmul_rn(lr, u[i]), 0.1f));
+    }
+}
+
+template <typename T>
+int upload(T **d, const std::vector<T> &h, cudaStream_t stream)
+{
+    *d = nullptr;
+    const size_t bytes = std::max<size_t>(h.size(), 1) * sizeof(T);
+    VB_CUDA(cudaMalloc((void **)d, bytes));
+    if (!h.empty()) VB_CUDA(cudaMemcpyAsync(*d, h.data(), h.size() * sizeof(T), cudaMemcpyHostToDevice, stream));
+    return VB_OK;
+}
+
+}  // namespace
+
+struct MuonState {
+    std::vector<int> owner;           // per tensor
+    std::vector<int64_t> local_off;   // per tensor: offset into this rank's buffers, -1 if not owned
+    std::vector<uint8_t> is_ns;       // per tensor: rows > 1 && cols > 1
+    int64_t owned_elems = 0;
+    float *d_upd = nullptr;           // update buffer u / X (f32), owned tensors
+    float *d_xnext = nullptr;         // F32 mode: the other Newton-Schulz buffer
+    float *d_gram = nullptr;          // F32 mode: C = 3I - X^T X per matrix
+    float *d_sumsq = nullptr;         // per tensor
+    float *d_partials = nullptr;      // per chunk (BF16 mode)
+    uint8_t *d_is_ns = nullptr;
+    int64_t *d_sizes = nullptr;
+    int32_t *d_ns_tensors = nullptr;  // owned tensors that run Newton-Schulz
+    int n_ns = 0;
+    int64_t *d_first_chunk = nullptr;
+    TensorDesc *d_desc = nullptr;        // p = w, g = grad, s1 = velocity, s2 = update buffer
+    TensorDesc *d_desc_apply = nullptr;  // p = w, g = final update
+    ChunkDesc *d_chunks = nullptr;
+    int64_t n_chunks = 0;
+    std::vector<float *> final_update;   // per tensor: device pointer of the last step's update
+    // F32 GEMM schedules: [parity] -> gram problems, update problems
+    F32GemmProblem *d_gram_prob[2] = {nullptr, nullptr};
+    F32GemmProblem *d_upd_prob[2] = {nullptr, nullptr};
+    GemmTile *d_gram_tiles = nullptr, *d_upd_tiles = nullptr;
+    int n_gram_tiles = 0, n_upd_tiles = 0;
+    double flops_per_step = 0.0;
+    double last_flops = 0.0;
+};
+
+void destroy_muon_state(MuonState *s)
+{
+    if (!s) return;
+    cudaFree(s->d_upd);
+    cudaFree(s->d_xnext);
+    cudaFree(s->d_gram);
+    cudaFree(s->d_sumsq);
+    cudaFree(s->d_partials);
+    cudaFree(s->d_is_ns);
+    cudaFree(s->d_sizes);
+    cudaFree(s->d_ns_tensors);
+    cudaFree(s->d_first_chunk);
+    cudaFree(s->d_desc);
+    cudaFree(s->d_desc_apply);
+    cudaFree(s->d_chunks);
+    for (int i = 0; i < 2; ++i) {
+        cudaFree(s->d_gram_prob[i]);
+        cudaFree(s->d_upd_prob[i]);
+    }
+    cudaFree(s->d_gram_tiles);
+    cudaFree(s->d_upd_tiles);
+    delete s;
+}
+
+// Whole matrices are owned by one rank: tensors are taken in order of decreasing
+// Newton-Schulz cost (4 * rows * cols^2 FLOPs per iteration, elements for 1-D tensors)
+// and each goes to the rank with the least work so far (ties: lowest rank).
+void plan_muon_owners(int64_t n, const int64_t *rows, const int64_t *cols, int world, int *owner_out)
+{
+    std::vector<int64_t> order((size_t)n);
+    std::iota(order.begin(), order.end(), 0);
+    auto cost = [&](int64_t i) -> double {
+        const double r = (double)rows[i], c = (double)cols[i];
+        return (r > 1 && c > 1) ? 4.0 * r * c * std::min(r, c) : r * c * 1e-3;
+    };
+    std::stable_sort(order.begin(), order.end(), [&](int64_t a, int64_t b) { return cost(a) > cost(b); });
+    std::vector<double> load((size_t)world, 0.0);
+    for (int64_t i : order) {
+        int best = 0;
+        for (int r = 1; r < world; ++r)
+            if (load[(size_t)r] < load[(size_t)best]) best = r;
+        owner_out[i] = best;
+        load[(size_t)best] += cost(i);
+    }
+}
+
+int muon_owner(vb_optimizer *opt, int64_t tensor) { return opt->muon ? opt->muon->owner[(size_t)tensor] : 0; }
+
+float *muon_velocity_ptr(vb_optimizer *opt, int64_t tensor)
+{
+    if (!opt->muon || opt->muon->local_off[(size_t)tensor] < 0) return nullptr;
+    return opt->d_s1 + opt->muon->local_off[(size_t)tensor];
+}
+
+int muon_init(vb_optimizer *opt)
+{
+    vb_engine *e = opt->eng;
+    MuonState *s = new MuonState();
+    opt->muon = s;
+    const int64_t nt = opt->n_tensors;
+    s->owner.assign((size_t)nt, 0);
+    plan_muon_owners(nt, opt->rows.data(), opt->cols.data(), e->world, s->owner.data());
+    s->local_off.assign((size_t)nt, -1);
+    s->is_ns.assign((size_t)std::max<int64_t>(nt, 1), 0);
+    s->final_update.assign((size_t)nt, nullptr);
+    int64_t off = 0, gram_elems = 0;
+    std::vector<int32_t> ns_tensors;
+    std::vector<int64_t> gram_off((size_t)nt, -1);
+    for (int64_t i = 0; i < nt; ++i) {
+        s->is_ns[(size_t)i] = (opt->rows[i] > 1 && opt->cols[i] > 1) ? 1 : 0;  // muon.rs:153
+        if (s->owner[(size_t)i] != e->rank) continue;
+        s->local_off[(size_t)i] = off;
+        off += (opt->sizes[i] + 31) / 32 * 32;
+        if (s->is_ns[(size_t)i] && opt->sizes[i] > 0) {
+            ns_tensors.push_back((int32_t)i);
+            if (opt->rows[i] > 0x7fffffff || opt->cols[i] > 0x7fffffff)
+                return fail(VB_ERR_UNSUPPORTED, "matrix %lld is too large", (long long)i);
+            gram_off[(size_t)i] = gram_elems;
+            gram_elems += (opt->cols[i] * opt->cols[i] + 31) / 32 * 32;
+        }
+    }
+    s->owned_elems = off;
+    s->n_ns = (int)ns_tensors.size();
+    const size_t owned_bytes = (size_t)std::max<int64_t>(off, 1) * sizeof(float);
+    // velocity (muon.rs:26-29) and the update buffer, for owned tensors only
+    VB_CUDA(cudaMalloc(&opt->d_s1, owned_bytes));
+    VB_CUDA(cudaMemsetAsync(opt->d_s1, 0, owned_bytes, e->stream));
+    VB_CUDA(cudaMalloc(&s->d_upd, owned_bytes));
+    VB_CUDA(cudaMemsetAsync(s->d_upd, 0, owned_bytes, e->stream));
+    VB_CUDA(cudaMalloc(&s->d_sumsq, (size_t)std::max<int64_t>(nt, 1) * sizeof(float)));
+    VB_CUDA(cudaMemsetAsync(s->d_sumsq, 0, (size_t)std::max<int64_t>(nt, 1) * sizeof(float), e->stream));
+
+    // element-wise chunk table over owned tensors
+    const int64_t chunk_len = pick_chunk_len(off, e->sm_count);
+    std::vector<TensorDesc> desc((size_t)std::max<int64_t>(nt, 1));
+    std::vector<ChunkDesc> chunks;
+    std::vector<int64_t> first_chunk((size_t)nt + 1, 0);
+    for (int64_t i = 0; i < nt; ++i) {
+        first_chunk[(size_t)i] = (int64_t)chunks.size();
+        TensorDesc &td = desc[(size_t)i];
+        td.p = opt->d_param + opt->offsets[(size_t)i];
+        td.g = opt->d_grad + opt->offsets[(size_t)i];
+        td.s1 = td.s2 = nullptr;
+        if (s->local_off[(size_t)i] < 0) continue;
+        td.s1 = opt->d_s1 + s->local_off[(size_t)i];
+        td.s2 = s->d_upd + s->local_off[(size_t)i];
+        for (int64_t b = 0; b < opt->sizes[i]; b += chunk_len) {
+            ChunkDesc c;
+            c.offset = b;
+            c.tensor = (uint32_t)i;
+            c.len = (uint32_t)std::min(chunk_len, opt->sizes[i] - b);
+            chunks.push_back(c);
+        }
+    }
+    first_chunk[(size_t)nt] = (int64_t)chunks.size();
+    s->n_chunks = (int64_t)chunks.size();
+    VB_TRY(upload(&s->d_desc, desc, e->stream));
+    VB_TRY(upload(&s->d_chunks, chunks, e->stream));
+    VB_TRY(upload(&s->d_first_chunk, first_chunk, e->stream));
+    VB_TRY(upload(&s->d_is_ns, s->is_ns, e->stream));
+    VB_TRY(upload(&s->d_sizes, opt->sizes, e->stream));
+    VB_TRY(upload(&s->d_ns_tensors, ns_tensors, e->stream));
+    VB_CUDA(cudaMalloc(&s->d_partials, (size_t)std::max<int64_t>(s->n_chunks, 1) * sizeof(float)));
+
+    // where the final update of each tensor lives after a step
+    const bool odd = (opt->ns_steps & 1) != 0;
+    std::vector<TensorDesc> desc_apply = desc;
+    if (opt->ns_mode == VB_NS_F32) {
+        VB_CUDA(cudaMalloc(&s->d_xnext, owned_bytes));
+        VB_CUDA(cudaMalloc(&s->d_gram, (size_t)std::max<int64_t>(gram_elems, 1) * sizeof(float)));
+    }
+    for (int64_t i = 0; i < nt; ++i) {
+        if (s->local_off[(size_t)i] < 0) continue;
+        float *fin = s->d_upd + s->local_off[(size_t)i];
+        if (opt->ns_mode == VB_NS_F32 && s->is_ns[(size_t)i] && odd) fin = s->d_xnext + s->local_off[(size_t)i];
+        s->final_update[(size_t)i] = fin;
+        desc_apply[(size_t)i].g = fin;
+    }
+    VB_TRY(upload(&s->d_desc_apply, desc_apply, e->stream));
+
+    // Newton-Schulz schedules
+    s->flops_per_step = 0.0;
+    if (opt->ns_mode == VB_NS_F32) {
+        int bm, bn;
+        f32_gemm_tile_shape(&bm, &bn);
+        std::vector<F32GemmProblem> gram[2], upd[2];
+        std::vector<GemmTile> gram_tiles, upd_tiles;
+        // longest contractions first so the tail of the persistent grid is short
+        std::vector<int32_t> order = ns_tensors;
+        std::stable_sort(order.begin(), order.end(), [&](int32_t a, int32_t b) {
+            return opt->rows[a] * opt->cols[a] > opt->rows[b] * opt->cols[b];
+        });
+        for (int32_t t : order) {
+            const int r = (int)opt->rows[t], c = (int)opt->cols[t];
+            float *buf[2] = {s->d_upd + s->local_off[(size_t)t], s->d_xnext + s->local_off[(size_t)t]};
+            float *gm = s->d_gram + gram_off[(size_t)t];
+            const int pidx = (int)gram[0].size();
+            for (int par = 0; par < 2; ++par) {
+                F32GemmProblem g{};  // xt_x = X^T X, then C = 3I - xt_x   (muon.rs:69-89)
+                g.A = buf[par]; g.B = buf[par]; g.C = gm;
+                g.M = c; g.N = c; g.K = r; g.lda = c; g.ldb = c; g.ldc = c;
+                g.trans_a = 1; g.epilogue = F32_EPI_THREE_I_MINUS; g.tensor = t;
+                gram[par].push_back(g);
+                F32GemmProblem u{};  // X <- 0.5 * (X C)                  (muon.rs:93-99)
+                u.A = buf[par]; u.B = gm; u.C = buf[par ^ 1];
+                u.M = r; u.N = c; u.K = c; u.lda = c; u.ldb = c; u.ldc = c;
+                u.trans_a = 0; u.epilogue = F32_EPI_HALF; u.tensor = t;
+                upd[par].push_back(u);
+            }
+            for (int m0 = 0; m0 < c; m0 += bm)
+                for (int n0 = 0; n0 < c; n0 += bn) gram_tiles.push_back(GemmTile{pidx, m0, n0, 0});
+            for (int m0 = 0; m0 < r; m0 += bm)
+                for (int n0 = 0; n0 < c; n0 += bn) upd_tiles.push_back(GemmTile{pidx, m0, n0, 0});
+            s->flops_per_step += 4.0 * (double)r * (double)c * (double)c * (double)opt->ns_steps;
+        }
+        for (int par = 0; par < 2; ++par) {
+            VB_TRY(upload(&s->d_gram_prob[par], gram[par], e->stream));
+            VB_TRY(upload(&s->d_upd_prob[par], upd[par], e->stream));
+        }
+        VB_TRY(upload(&s->d_gram_tiles, gram_tiles, e->stream));
+        VB_TRY(upload(&s->d_upd_tiles, upd_tiles, e->stream));
+        s->n_gram_tiles = (int)gram_tiles.size();
+        s->n_upd_tiles = (int)upd_tiles.size();
+    } else {
+        return fail(VB_ERR_UNSUPPORTED, "the bf16 tensor-core Newton-Schulz path is not built yet");
+    }
+    VB_CUDA(cudaStreamSynchronize(e->stream));
+    return VB_OK;
+}
+
+int muon_step(vb_optimizer *opt, uint32_t flags)
+{
+    vb_engine *e = opt->eng;
+    MuonState *s = opt->muon;
+    VB_TRY(sync_present(opt));
+    const int ew_grid = (int)std::min<int64_t>(std::max<int64_t>(s->n_chunks, 1), (int64_t)e->sm_count * 8);
+    if (s->n_chunks > 0) {
+        const bool partials = opt->ns_mode == VB_NS_BF16;
+        if (partials)
+            momentum_kernel<true><<<ew_grid, kEwThreads, 0, e->stream>>>(s->d_desc, s->d_chunks, s->n_chunks,
+                                                                          opt->d_present, opt->momentum,
+                                                                          opt->nesterov, s->d_partials);
+        else
+            momentum_kernel<false><<<ew_grid, kEwThreads, 0, e->stream>>>(s->d_desc, s->d_chunks, s->n_chunks,
+                                                                           opt->d_present, opt->momentum,
+                                                                           opt->nesterov, s->d_partials);
+        VB_CUDA(cudaGetLastError());
+        e->launches += 1;
+    }
+    if (s->n_ns > 0) {
+        if (opt->ns_mode == VB_NS_F32) {
+            sumsq_ordered_kernel<<<s->n_ns, kSeqThreads, 0, e->stream>>>(s->d_desc, s->d_ns_tensors, s->d_sizes,
+                                                                        opt->d_present, s->d_sumsq);
+        } else {
+            reduce_partials_kernel<<<(s->n_ns + 3) / 4, 128, 0, e->stream>>>(s->d_partials, s->d_first_chunk,
+                                                                            s->d_ns_tensors, s->n_ns, s->d_sumsq);
+        }
+        VB_CUDA(cudaGetLastError());
+        normalise_kernel<false><<<ew_grid, kEwThreads, 0, e->stream>>>(s->d_desc, s->d_chunks, s->n_chunks,
+                                                                      opt->d_present, s->d_is_ns, s->d_sumsq,
+                                                                      s->d_upd, nullptr);
+        VB_CUDA(cudaGetLastError());
+        e->launches += 2;
+        for (int it = 0; it < opt->ns_steps; ++it) {
+            const int par = it & 1;
+            VB_TRY(launch_ns_gemm_f32(s->d_gram_prob[par], s->d_gram_tiles, s->n_gram_tiles, opt->d_present,
+                                      e->sm_count, e->stream));
+            VB_TRY(launch_ns_gemm_f32(s->d_upd_prob[par], s->d_upd_tiles, s->n_upd_tiles, opt->d_present,
+                                      e->sm_count, e->stream));
+            e->launches += 2;
+        }
+        s->last_flops = s->flops_per_step;
+    }
+    if (s->n_chunks > 0) {
+        apply_kernel<<<ew_grid, kEwThreads, 0, e->stream>>>(s->d_desc_apply, s->d_chunks, s->n_chunks,
+                                                           opt->d_present, opt->lr);
+        VB_CUDA(cudaGetLastError());
+        e->launches += 1;
+    }
+    if (e->world > 1 && !(flags & VB_STEP_NO_EXCHANGE)) {
+        // every matrix from its owner; all ranks must hold the same gradient-presence flags
+        std::vector<BcastItem> items;
+        for (int64_t i = 0; i < opt->n_tensors; ++i)
+            if (opt->present[(size_t)i] && opt->sizes[(size_t)i] > 0)
+                items.push_back(BcastItem{opt->d_param + opt->offsets[(size_t)i], opt->sizes[(size_t)i],
+                                          s->owner[(size_t)i]});
+        VB_TRY(comm_group_broadcast(e, items.data(), (int64_t)items.size()));
+    }
+    return VB_OK;
+}
+
+int muon_download_update(vb_optimizer *opt, int64_t tensor, float *host, int64_t n)
+{
+    MuonState *s = opt->muon;
+    if (s->local_off[(size_t)tensor] < 0)
+        return fail(VB_ERR_STATE, "tensor %lld is owned by rank %d", (long long)tensor, s->owner[(size_t)tensor]);
+    if (n == 0) return VB_OK;
+    if (!host) return fail(VB_ERR_INVALID_ARG, "host pointer is null");
+    VB_CUDA(cudaMemcpyAsync(host, s->final_update[(size_t)tensor], (size_t)n * sizeof(float),
+                            cudaMemcpyDeviceToHost, opt->eng->stream));
+    VB_CUDA(cudaStreamSynchronize(opt->eng->stream));
+    return VB_OK;
+}
+
+int muon_last_flops(vb_optimizer *opt, double *flops)
+{
+    *flops = opt->muon->last_flops;
+    return VB_OK;
+}
+
 }  // namespace vb

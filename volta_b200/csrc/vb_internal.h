@@ -47,6 +47,20 @@ struct ChunkDesc {
     uint32_t len;
 };
 
+// Unit of work of the fused Adam/SGD kernel: `len` consecutive elements of one tensor with
+// the four array addresses resolved on the host, so the kernel needs one 48-byte fetch per
+// chunk and no dependent lookups.
+struct alignas(16) FatChunk {
+    float *p;
+    const float *g;
+    float *s1;
+    float *s2;
+    uint32_t len;
+    uint32_t tensor;
+    uint64_t pad;
+};
+static_assert(sizeof(FatChunk) == 48, "FatChunk is fetched as three 16-byte words");
+
 // Scalars of one step, computed on the host in f32 exactly as the reference does.
 struct StepScalars {
     float lr;
@@ -69,9 +83,8 @@ StepScalars make_scalars(int op, float lr, float beta1, float beta2, float eps, 
 
 // Launches the fused multi-tensor update over `n_chunks` chunks.  `present` holds one
 // byte per tensor (0 = gradient absent, skip).
-int launch_multi_tensor(int op, const TensorDesc *d_tensors, const ChunkDesc *d_chunks,
-                        int64_t n_chunks, const uint8_t *d_present, const StepScalars &s,
-                        int sm_count, cudaStream_t stream);
+int launch_multi_tensor(int op, const FatChunk *d_chunks, int64_t n_chunks, const uint8_t *d_present,
+                        bool all_present, const StepScalars &s, int sm_count, cudaStream_t stream);
 
 // Splits [begin, end) of each tensor into chunks.
 int64_t pick_chunk_len(int64_t total_elements, int sm_count);
