@@ -131,3 +131,93 @@ def test_ordered_sum_adversarial_values(oracle, engine):
         ref.step([g])
         assert bits_equal(opt.last_update(0), ref.last_update[0])
         opt.close()
+
+
+# ---- bf16 tensor-core path (tcgen05) ----------------------------------------------------------
+
+def _bf16_round(x):
+    """float32 -> bfloat16 -> float32, round to nearest even (what the kernels store)."""
+    u = np.ascontiguousarray(x, np.float32).view(np.uint32).astype(np.uint64)
+    u = (u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000
+    return u.astype(np.uint32).view(np.float32)
+
+
+def _ns_bf16_model(x0, steps):
+    """numpy model of the bf16 path: operands rounded to bf16, f32-or-better accumulation,
+    short-side Gram; used to tell a wrong descriptor (O(1) error) from rounding (1e-3)."""
+    r, c = x0.shape
+    x = _bf16_round(x0).astype(np.float64)
+    for it in range(steps):
+        if r >= c:
+            cm = _bf16_round((3.0 * np.eye(c) - x.T @ x).astype(np.float32)).astype(np.float64)
+            nx = 0.5 * (x @ cm)
+        else:
+            cm = _bf16_round((3.0 * np.eye(r) - x @ x.T).astype(np.float32)).astype(np.float64)
+            nx = 0.5 * (cm @ x)
+        x = nx if it == steps - 1 else _bf16_round(nx.astype(np.float32)).astype(np.float64)
+    return x.astype(np.float32)
+
+
+@pytest.mark.parametrize("shape", [(128, 256), (256, 128), (512, 512), (384, 1024), (1024, 384), (200, 72), (72, 200),
+                                   (1032, 264)])
+def test_bf16_path_single_matrix(oracle, engine, shape):
+    """One matrix per launch, tall / wide / square, full and ragged tiles (dims are multiples
+    of 8 but not of the 128 x 256 tile or the 64-wide k block)."""
+    from volta_b200 import VB_NS_BF16, Muon, Tensor
+    rng = np.random.default_rng(sum(shape))
+    g = (rng.standard_normal(shape) * 1e-3).astype(np.float32)
+    w = Tensor(np.zeros(shape, np.float32))
+    opt = Muon([w], 0.1, 0.0, False, 5, ns_mode=VB_NS_BF16, engine=engine)
+    w.grad = g
+    opt.step()
+    got = opt.last_update(0)
+    ref = oracle.newton_schulz(g, 5)
+    x0 = g / np.sqrt(np.float32(np.sum(g.astype(np.float64) ** 2) + 1e-8)).astype(np.float32)
+    model = _ns_bf16_model(x0, 5)
+    assert rel_frobenius(got, model) < 2e-3, (rel_frobenius(got, model), rel_frobenius(got, ref))
+    assert rel_frobenius(got, ref) <= TOL_BF16
+    assert np.allclose(w.data, -(np.float32(0.1) * got) * np.float32(0.1), rtol=0, atol=1e-9)
+    opt.close()
+
+
+def test_bf16_path_mixed_list_three_steps(oracle, engine):
+    """Several matrices in one optimizer (tensor-core shapes, a shape that falls back to the
+    f32 kernels because its rows are not 16-byte aligned in bf16, and a vector), momentum and
+    Nesterov on, three steps."""
+    from volta_b200 import VB_NS_BF16
+    shapes = [(256, 256), (768, 256), (256, 1024), (64, 36), (100,), (512, 128)]
+    res = _run(oracle, engine, shapes, 3, VB_NS_BF16)
+    for r in res:
+        assert r["update"] <= TOL_BF16, res
+        assert r["velocity_exact"]
+
+
+def test_bf16_path_missing_gradients(oracle, engine):
+    from volta_b200 import VB_NS_BF16
+    res = _run(oracle, engine, [(256, 256), (128, 384), (384, 128)], 4, VB_NS_BF16,
+               drop=lambda i, s: (i + s) % 2 == 0)
+    assert all(r["update"] <= TOL_BF16 and r["velocity_exact"] for r in res), res
+
+
+def test_bf16_path_c4_layer_shapes(oracle, engine):
+    """The four matrix shapes of one layer of the Muon benchmark configuration (3072x1024,
+    1024x1024, 4096x1024, 1024x4096) at full size, one step, against the f32 oracle."""
+    from volta_b200 import VB_NS_BF16, Muon, Tensor
+    oracle.set_threads(oracle.max_threads())
+    shapes = [(3072, 1024), (1024, 1024), (4096, 1024), (1024, 4096)]
+    rng = np.random.default_rng(11)
+    grads = [(rng.standard_normal(s) * 1e-3).astype(np.float32) for s in shapes]
+    tensors = [Tensor((rng.standard_normal(s) * 0.02).astype(np.float32)) for s in shapes]
+    opt = Muon(tensors, 0.1, 0.9, True, 5, ns_mode=VB_NS_BF16, engine=engine)
+    for t, g in zip(tensors, grads):
+        t.grad = g
+    opt.step()
+    assert opt.last_ns_flops == sum(4.0 * max(s) * min(s) ** 2 * 5 for s in shapes)
+    for i, (s, g) in enumerate(zip(shapes, grads)):
+        u = np.float32(0.9) * g + g  # first step: v = g, Nesterov update = mu*v + g
+        # short-side form of the reference iteration on the oracle (same mathematics, 4x less
+        # CPU work for the 1024x4096 matrix): NS(X)^T == NS(X^T)
+        ref = oracle.newton_schulz(u, 5) if s[0] >= s[1] else oracle.newton_schulz(np.ascontiguousarray(u.T), 5).T
+        err = rel_frobenius(opt.last_update(i), ref)
+        assert err <= TOL_BF16, (s, err)
+    opt.close()

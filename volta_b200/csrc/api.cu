@@ -514,6 +514,7 @@ static int copy_tensor(vb_optimizer *opt, int64_t tensor, float *dev_base, void 
         VB_CUDA(cudaMemcpyAsync(host, dev, (size_t)n * sizeof(float), cudaMemcpyDeviceToHost,
                                 opt->eng->stream));
         VB_CUDA(cudaStreamSynchronize(opt->eng->stream));
+        if (opt->kind == KIND_MUON) return muon_check_error(opt);
     }
     return VB_OK;
 }

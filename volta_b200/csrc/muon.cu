@@ -6,7 +6,7 @@
 //   K3s  sumsq_ordered_kernel sum of u*u in the reference's left-to-right f32 order muon.rs:58
 //        (VB_NS_F32), or per-chunk partial sums + ordered reduce (VB_NS_BF16)
 //   K3b  normalise_kernel     x = u / sqrt(sumsq + 1e-8)                            muon.rs:59-64
-//   K4/5 Newton-Schulz GEMMs  ns_gemm_f32.cu / ns_gemm_tc.cu                        muon.rs:67-100
+//   K4/5 Newton-Schulz GEMMs  ns_gemm_f32.cu (f32) / ns_gemm_tc.cu (bf16, tcgen05)     muon.rs:67-100
 //   K6   apply_kernel         w -= (lr * u) * 0.1                                   muon.rs:158-160
 //
 // Every kernel walks a chunk or tile table over all matrices this rank owns, so a step
@@ -269,24 +269,25 @@ sumsq_ordered_kernel(const TensorDesc *__restrict__ tensors, const int32_t *__re
 }
 
 // ---- K3b: normalise ----------------------------------------------------------------------------
-// x = u / sqrt(sumsq + 1e-8) where the norm exceeds 1e-8 (muon.rs:59-64).  F32 mode rewrites
-// the update buffer in place; BF16 mode writes the bf16 operand of the first GEMM.
-template <bool TO_BF16>
+// x = u / sqrt(sumsq + 1e-8) where the norm exceeds 1e-8 (muon.rs:59-64).  Per tensor
+// (ns_kind): 1 = rewrite the f32 update buffer in place (operand of the f32 GEMMs, and the
+// final update when ns_steps == 0), 2 = write the bf16 operand of the first tensor-core GEMM.
 __global__ void __launch_bounds__(kEwThreads)
 normalise_kernel(const TensorDesc *__restrict__ tensors, const ChunkDesc *__restrict__ chunks, int64_t n_chunks,
-                 const uint8_t *__restrict__ present, const uint8_t *__restrict__ is_ns,
+                 const uint8_t *__restrict__ present, const uint8_t *__restrict__ ns_kind,
                  const float *__restrict__ sumsq, const float *upd_base, __nv_bfloat16 *__restrict__ xb_base)
 {
     for (int64_t c = blockIdx.x; c < n_chunks; c += gridDim.x) {
         const ChunkDesc ch = chunks[c];
-        if (present[ch.tensor] == 0 || is_ns[ch.tensor] == 0) continue;
+        const int kind = ns_kind[ch.tensor];
+        if (present[ch.tensor] == 0 || kind == 0) continue;
         float *u = tensors[ch.tensor].s2 + ch.offset;
         const float norm = __fsqrt_rn(__fadd_rn(sumsq[ch.tensor], 1e-8f));
         const bool scale = norm > 1e-8f;
         const uint32_t n = ch.len;
-        if (TO_BF16) {
+        const uint32_t n4 = n >> 2;
+        if (kind == 2) {
             __nv_bfloat16 *xb = xb_base + (u - upd_base);
-            const uint32_t n4 = n >> 2;
             for (uint32_t i = threadIdx.x; i < n4; i += kEwThreads) {
                 float4 v = reinterpret_cast<const float4 *>(u)[i];
                 if (scale) {
@@ -303,7 +304,6 @@ normalise_kernel(const TensorDesc *__restrict__ tensors, const ChunkDesc *__rest
                 xb[i] = __float2bfloat16_rn(scale ? __fdiv_rn(u[i], norm) : u[i]);
         } else {
             if (!scale) continue;
-            const uint32_t n4 = n >> 2;
             for (uint32_t i = threadIdx.x; i < n4; i += kEwThreads) {
                 float4 v = reinterpret_cast<const float4 *>(u)[i];
                 v.x = __fdiv_rn(v.x, norm); v.y = __fdiv_rn(v.y, norm);
@@ -358,14 +358,16 @@ int upload(T **d, const std::vector<T> &h, cudaStream_t stream)
 struct MuonState {
     std::vector<int> owner;           // per tensor
     std::vector<int64_t> local_off;   // per tensor: offset into this rank's buffers, -1 if not owned
-    std::vector<uint8_t> is_ns;       // per tensor: rows > 1 && cols > 1
+    std::vector<uint8_t> ns_kind;     // per tensor: 0 no Newton-Schulz, 1 f32 CUDA-core path, 2 bf16 tensor-core path
     int64_t owned_elems = 0;
     float *d_upd = nullptr;           // update buffer u / X (f32), owned tensors
-    float *d_xnext = nullptr;         // F32 mode: the other Newton-Schulz buffer
-    float *d_gram = nullptr;          // F32 mode: C = 3I - X^T X per matrix
+    float *d_xnext = nullptr;         // f32 path: the other Newton-Schulz buffer
+    float *d_gram = nullptr;          // f32 path: C = 3I - X^T X per matrix
+    __nv_bfloat16 *d_xb[2] = {nullptr, nullptr};  // bf16 path: X ping-pong
+    __nv_bfloat16 *d_cb = nullptr;                // bf16 path: C = 3I - Gram per matrix (short side squared)
     float *d_sumsq = nullptr;         // per tensor
-    float *d_partials = nullptr;      // per chunk (BF16 mode)
-    uint8_t *d_is_ns = nullptr;
+    float *d_partials = nullptr;      // per chunk (bf16 mode)
+    uint8_t *d_ns_kind = nullptr;
     int64_t *d_sizes = nullptr;
     int32_t *d_ns_tensors = nullptr;  // owned tensors that run Newton-Schulz
     int n_ns = 0;
@@ -375,11 +377,19 @@ struct MuonState {
     ChunkDesc *d_chunks = nullptr;
     int64_t n_chunks = 0;
     std::vector<float *> final_update;   // per tensor: device pointer of the last step's update
-    // F32 GEMM schedules: [parity] -> gram problems, update problems
+    // f32 GEMM schedules: [parity] -> gram problems, update problems
     F32GemmProblem *d_gram_prob[2] = {nullptr, nullptr};
     F32GemmProblem *d_upd_prob[2] = {nullptr, nullptr};
     GemmTile *d_gram_tiles = nullptr, *d_upd_tiles = nullptr;
     int n_gram_tiles = 0, n_upd_tiles = 0;
+    // tensor-core GEMM schedules: [parity]; the last iteration's update writes the f32 result
+    TcGemmProblem *d_tc_gram[2] = {nullptr, nullptr};
+    TcGemmProblem *d_tc_upd[2] = {nullptr, nullptr};
+    TcGemmProblem *d_tc_upd_final = nullptr;
+    GemmTile *d_tc_gram_tiles = nullptr, *d_tc_upd_tiles = nullptr;
+    int n_tc_gram_tiles = 0, n_tc_upd_tiles = 0;
+    int *d_error = nullptr;
+    int *h_error = nullptr;              // pinned mirror of d_error, refreshed after every step
     double flops_per_step = 0.0;
     double last_flops = 0.0;
 };
@@ -390,9 +400,12 @@ void destroy_muon_state(MuonState *s)
     cudaFree(s->d_upd);
     cudaFree(s->d_xnext);
     cudaFree(s->d_gram);
+    cudaFree(s->d_xb[0]);
+    cudaFree(s->d_xb[1]);
+    cudaFree(s->d_cb);
     cudaFree(s->d_sumsq);
     cudaFree(s->d_partials);
-    cudaFree(s->d_is_ns);
+    cudaFree(s->d_ns_kind);
     cudaFree(s->d_sizes);
     cudaFree(s->d_ns_tensors);
     cudaFree(s->d_first_chunk);
@@ -402,15 +415,22 @@ void destroy_muon_state(MuonState *s)
     for (int i = 0; i < 2; ++i) {
         cudaFree(s->d_gram_prob[i]);
         cudaFree(s->d_upd_prob[i]);
+        cudaFree(s->d_tc_gram[i]);
+        cudaFree(s->d_tc_upd[i]);
     }
+    cudaFree(s->d_tc_upd_final);
     cudaFree(s->d_gram_tiles);
     cudaFree(s->d_upd_tiles);
+    cudaFree(s->d_tc_gram_tiles);
+    cudaFree(s->d_tc_upd_tiles);
+    cudaFree(s->d_error);
+    if (s->h_error) cudaFreeHost(s->h_error);
     delete s;
 }
 
 // Whole matrices are owned by one rank: tensors are taken in order of decreasing
-// Newton-Schulz cost (4 * rows * cols^2 FLOPs per iteration, elements for 1-D tensors)
-// and each goes to the rank with the least work so far (ties: lowest rank).
+// Newton-Schulz cost (4 * long side * short side^2 FLOPs per iteration; elements for 1-D
+// tensors) and each goes to the rank with the least work so far (ties: lowest rank).
 void plan_muon_owners(int64_t n, const int64_t *rows, const int64_t *cols, int world, int *owner_out)
 {
     std::vector<int64_t> order((size_t)n);
@@ -438,6 +458,16 @@ float *muon_velocity_ptr(vb_optimizer *opt, int64_t tensor)
     return opt->d_s1 + opt->muon->local_off[(size_t)tensor];
 }
 
+int muon_check_error(vb_optimizer *opt)
+{
+    MuonState *s = opt->muon;
+    if (s && s->h_error && *s->h_error != 0) {
+        const int code = *s->h_error;
+        return fail(VB_ERR_TIMEOUT, "a Newton-Schulz GEMM kernel gave up waiting on a pipeline barrier (role %d)", code);
+    }
+    return VB_OK;
+}
+
 int muon_init(vb_optimizer *opt)
 {
     vb_engine *e = opt->eng;
@@ -447,22 +477,36 @@ int muon_init(vb_optimizer *opt)
     s->owner.assign((size_t)nt, 0);
     plan_muon_owners(nt, opt->rows.data(), opt->cols.data(), e->world, s->owner.data());
     s->local_off.assign((size_t)nt, -1);
-    s->is_ns.assign((size_t)std::max<int64_t>(nt, 1), 0);
+    s->ns_kind.assign((size_t)std::max<int64_t>(nt, 1), 0);
     s->final_update.assign((size_t)nt, nullptr);
-    int64_t off = 0, gram_elems = 0;
-    std::vector<int32_t> ns_tensors;
-    std::vector<int64_t> gram_off((size_t)nt, -1);
+    int64_t off = 0, gram_elems = 0, cb_elems = 0;
+    std::vector<int32_t> ns_tensors, f32_tensors, tc_tensors;
+    std::vector<int64_t> gram_off((size_t)nt, -1), cb_off((size_t)nt, -1);
     for (int64_t i = 0; i < nt; ++i) {
-        s->is_ns[(size_t)i] = (opt->rows[i] > 1 && opt->cols[i] > 1) ? 1 : 0;  // muon.rs:153
+        const int64_t r = opt->rows[i], c = opt->cols[i];
+        const bool ns = r > 1 && c > 1;  // muon.rs:153
+        if (ns) {
+            // The tensor-core path needs 16-byte aligned bf16 rows for TMA; other shapes of a
+            // bf16-mode optimizer run the (more accurate) f32 path.
+            const bool tc = opt->ns_mode == VB_NS_BF16 && opt->ns_steps > 0 && (r % 8) == 0 && (c % 8) == 0;
+            s->ns_kind[(size_t)i] = tc ? 2 : 1;
+        }
         if (s->owner[(size_t)i] != e->rank) continue;
         s->local_off[(size_t)i] = off;
         off += (opt->sizes[i] + 31) / 32 * 32;
-        if (s->is_ns[(size_t)i] && opt->sizes[i] > 0) {
+        if (ns && opt->sizes[i] > 0) {
+            if (r > 0x7fffffff || c > 0x7fffffff) return fail(VB_ERR_UNSUPPORTED, "matrix %lld is too large", (long long)i);
             ns_tensors.push_back((int32_t)i);
-            if (opt->rows[i] > 0x7fffffff || opt->cols[i] > 0x7fffffff)
-                return fail(VB_ERR_UNSUPPORTED, "matrix %lld is too large", (long long)i);
-            gram_off[(size_t)i] = gram_elems;
-            gram_elems += (opt->cols[i] * opt->cols[i] + 31) / 32 * 32;
+            if (s->ns_kind[(size_t)i] == 2) {
+                tc_tensors.push_back((int32_t)i);
+                const int64_t sh = std::min(r, c);
+                cb_off[(size_t)i] = cb_elems;
+                cb_elems += (sh * sh + 63) / 64 * 64;
+            } else {
+                f32_tensors.push_back((int32_t)i);
+                gram_off[(size_t)i] = gram_elems;
+                gram_elems += (c * c + 31) / 32 * 32;
+            }
         }
     }
     s->owned_elems = off;
@@ -475,6 +519,10 @@ int muon_init(vb_optimizer *opt)
     VB_CUDA(cudaMemsetAsync(s->d_upd, 0, owned_bytes, e->stream));
     VB_CUDA(cudaMalloc(&s->d_sumsq, (size_t)std::max<int64_t>(nt, 1) * sizeof(float)));
     VB_CUDA(cudaMemsetAsync(s->d_sumsq, 0, (size_t)std::max<int64_t>(nt, 1) * sizeof(float), e->stream));
+    VB_CUDA(cudaMalloc(&s->d_error, sizeof(int)));
+    VB_CUDA(cudaMemsetAsync(s->d_error, 0, sizeof(int), e->stream));
+    VB_CUDA(cudaHostAlloc((void **)&s->h_error, sizeof(int), cudaHostAllocDefault));
+    *s->h_error = 0;
 
     // element-wise chunk table over owned tensors
     const int64_t chunk_len = pick_chunk_len(off, e->sm_count);
@@ -503,40 +551,46 @@ int muon_init(vb_optimizer *opt)
     VB_TRY(upload(&s->d_desc, desc, e->stream));
     VB_TRY(upload(&s->d_chunks, chunks, e->stream));
     VB_TRY(upload(&s->d_first_chunk, first_chunk, e->stream));
-    VB_TRY(upload(&s->d_is_ns, s->is_ns, e->stream));
+    VB_TRY(upload(&s->d_ns_kind, s->ns_kind, e->stream));
     VB_TRY(upload(&s->d_sizes, opt->sizes, e->stream));
     VB_TRY(upload(&s->d_ns_tensors, ns_tensors, e->stream));
     VB_CUDA(cudaMalloc(&s->d_partials, (size_t)std::max<int64_t>(s->n_chunks, 1) * sizeof(float)));
 
-    // where the final update of each tensor lives after a step
     const bool odd = (opt->ns_steps & 1) != 0;
-    std::vector<TensorDesc> desc_apply = desc;
-    if (opt->ns_mode == VB_NS_F32) {
+    if (!f32_tensors.empty()) {
         VB_CUDA(cudaMalloc(&s->d_xnext, owned_bytes));
         VB_CUDA(cudaMalloc(&s->d_gram, (size_t)std::max<int64_t>(gram_elems, 1) * sizeof(float)));
     }
+    if (!tc_tensors.empty()) {
+        const size_t xb_bytes = (size_t)std::max<int64_t>(off, 1) * sizeof(__nv_bfloat16);
+        for (int i = 0; i < 2; ++i) {
+            VB_CUDA(cudaMalloc(&s->d_xb[i], xb_bytes));
+            VB_CUDA(cudaMemsetAsync(s->d_xb[i], 0, xb_bytes, e->stream));
+        }
+        VB_CUDA(cudaMalloc(&s->d_cb, (size_t)std::max<int64_t>(cb_elems, 1) * sizeof(__nv_bfloat16)));
+    }
+    // where the final update of each tensor lives after a step
+    std::vector<TensorDesc> desc_apply = desc;
     for (int64_t i = 0; i < nt; ++i) {
         if (s->local_off[(size_t)i] < 0) continue;
         float *fin = s->d_upd + s->local_off[(size_t)i];
-        if (opt->ns_mode == VB_NS_F32 && s->is_ns[(size_t)i] && odd) fin = s->d_xnext + s->local_off[(size_t)i];
+        if (s->ns_kind[(size_t)i] == 1 && odd) fin = s->d_xnext + s->local_off[(size_t)i];
         s->final_update[(size_t)i] = fin;
         desc_apply[(size_t)i].g = fin;
     }
     VB_TRY(upload(&s->d_desc_apply, desc_apply, e->stream));
 
-    // Newton-Schulz schedules
+    // ---- Newton-Schulz schedules ----
     s->flops_per_step = 0.0;
-    if (opt->ns_mode == VB_NS_F32) {
+    auto by_size = [&](int32_t a, int32_t b) { return opt->sizes[(size_t)a] > opt->sizes[(size_t)b]; };
+    if (!f32_tensors.empty()) {
         int bm, bn;
         f32_gemm_tile_shape(&bm, &bn);
         std::vector<F32GemmProblem> gram[2], upd[2];
         std::vector<GemmTile> gram_tiles, upd_tiles;
-        // longest contractions first so the tail of the persistent grid is short
-        std::vector<int32_t> order = ns_tensors;
-        std::stable_sort(order.begin(), order.end(), [&](int32_t a, int32_t b) {
-            return opt->rows[a] * opt->cols[a] > opt->rows[b] * opt->cols[b];
-        });
-        for (int32_t t : order) {
+        // largest matrices first so the tail of the persistent grid is short
+        std::stable_sort(f32_tensors.begin(), f32_tensors.end(), by_size);
+        for (int32_t t : f32_tensors) {
             const int r = (int)opt->rows[t], c = (int)opt->cols[t];
             float *buf[2] = {s->d_upd + s->local_off[(size_t)t], s->d_xnext + s->local_off[(size_t)t]};
             float *gm = s->d_gram + gram_off[(size_t)t];
@@ -567,8 +621,65 @@ int muon_init(vb_optimizer *opt)
         VB_TRY(upload(&s->d_upd_tiles, upd_tiles, e->stream));
         s->n_gram_tiles = (int)gram_tiles.size();
         s->n_upd_tiles = (int)upd_tiles.size();
-    } else {
-        return fail(VB_ERR_UNSUPPORTED, "the bf16 tensor-core Newton-Schulz path is not built yet");
+    }
+    if (!tc_tensors.empty()) {
+        int bm, bn;
+        tc_gemm_tile_shape(&bm, &bn);
+        std::vector<TcGemmProblem> gram[2], upd[2], upd_final;
+        std::vector<GemmTile> gram_tiles, upd_tiles;
+        std::stable_sort(tc_tensors.begin(), tc_tensors.end(), by_size);
+        const int final_par = (opt->ns_steps - 1) & 1;
+        for (int32_t t : tc_tensors) {
+            const int r = (int)opt->rows[t], c = (int)opt->cols[t];
+            const bool tall = r >= c;
+            const int sh = std::min(r, c);
+            __nv_bfloat16 *xb[2] = {s->d_xb[0] + s->local_off[(size_t)t], s->d_xb[1] + s->local_off[(size_t)t]};
+            __nv_bfloat16 *cb = s->d_cb + cb_off[(size_t)t];
+            CUtensorMap map_x[2], map_c;
+            for (int par = 0; par < 2; ++par) VB_TRY(make_bf16_tensor_map(&map_x[par], xb[par], c, r));
+            VB_TRY(make_bf16_tensor_map(&map_c, cb, sh, sh));
+            const int pidx = (int)gram[0].size();
+            for (int par = 0; par < 2; ++par) {
+                // C = 3I - X^T X (tall: both operands are X read with k = row index, "MN-major")
+                // C = 3I - X X^T (wide: both operands are X, K-major)
+                TcGemmProblem g{};
+                g.map_a = map_x[par]; g.map_b = map_x[par];
+                g.M = sh; g.N = sh; g.K = tall ? r : c;
+                g.a_mn_major = tall ? 1 : 0; g.b_mn_major = tall ? 1 : 0;
+                g.epilogue = TC_EPI_THREE_I_MINUS; g.ld_out = sh; g.tensor = t;
+                g.out_bf16 = cb; g.out_f32 = nullptr;
+                gram[par].push_back(g);
+                // X' = 0.5 X C (tall: A = X K-major, B = C which is symmetric)
+                // X' = 0.5 C X (wide: A = C, B = X read with k = row index)
+                TcGemmProblem u{};
+                u.map_a = tall ? map_x[par] : map_c;
+                u.map_b = tall ? map_c : map_x[par];
+                u.M = r; u.N = c; u.K = sh;
+                u.a_mn_major = 0; u.b_mn_major = tall ? 0 : 1;
+                u.epilogue = TC_EPI_HALF; u.ld_out = c; u.tensor = t;
+                u.out_bf16 = xb[par ^ 1]; u.out_f32 = nullptr;
+                upd[par].push_back(u);
+                if (par == final_par) {
+                    u.out_bf16 = nullptr;  // last iteration: the f32 update is the result
+                    u.out_f32 = s->d_upd + s->local_off[(size_t)t];
+                    upd_final.push_back(u);
+                }
+            }
+            for (int m0 = 0; m0 < sh; m0 += bm)
+                for (int n0 = 0; n0 < sh; n0 += bn) gram_tiles.push_back(GemmTile{pidx, m0, n0, 0});
+            for (int m0 = 0; m0 < r; m0 += bm)
+                for (int n0 = 0; n0 < c; n0 += bn) upd_tiles.push_back(GemmTile{pidx, m0, n0, 0});
+            s->flops_per_step += 4.0 * (double)std::max(r, c) * (double)sh * (double)sh * (double)opt->ns_steps;
+        }
+        for (int par = 0; par < 2; ++par) {
+            VB_TRY(upload(&s->d_tc_gram[par], gram[par], e->stream));
+            VB_TRY(upload(&s->d_tc_upd[par], upd[par], e->stream));
+        }
+        VB_TRY(upload(&s->d_tc_upd_final, upd_final, e->stream));
+        VB_TRY(upload(&s->d_tc_gram_tiles, gram_tiles, e->stream));
+        VB_TRY(upload(&s->d_tc_upd_tiles, upd_tiles, e->stream));
+        s->n_tc_gram_tiles = (int)gram_tiles.size();
+        s->n_tc_upd_tiles = (int)upd_tiles.size();
     }
     VB_CUDA(cudaStreamSynchronize(e->stream));
     return VB_OK;
@@ -578,11 +689,12 @@ int muon_step(vb_optimizer *opt, uint32_t flags)
 {
     vb_engine *e = opt->eng;
     MuonState *s = opt->muon;
+    VB_TRY(muon_check_error(opt));
     VB_TRY(sync_present(opt));
     const int ew_grid = (int)std::min<int64_t>(std::max<int64_t>(s->n_chunks, 1), (int64_t)e->sm_count * 8);
+    const bool fast_norm = opt->ns_mode == VB_NS_BF16;
     if (s->n_chunks > 0) {
-        const bool partials = opt->ns_mode == VB_NS_BF16;
-        if (partials)
+        if (fast_norm)
             momentum_kernel<true><<<ew_grid, kEwThreads, 0, e->stream>>>(s->d_desc, s->d_chunks, s->n_chunks,
                                                                           opt->d_present, opt->momentum,
                                                                           opt->nesterov, s->d_partials);
@@ -594,28 +706,38 @@ int muon_step(vb_optimizer *opt, uint32_t flags)
         e->launches += 1;
     }
     if (s->n_ns > 0) {
-        if (opt->ns_mode == VB_NS_F32) {
-            sumsq_ordered_kernel<<<s->n_ns, kSeqThreads, 0, e->stream>>>(s->d_desc, s->d_ns_tensors, s->d_sizes,
-                                                                        opt->d_present, s->d_sumsq);
-        } else {
+        if (fast_norm)
             reduce_partials_kernel<<<(s->n_ns + 3) / 4, 128, 0, e->stream>>>(s->d_partials, s->d_first_chunk,
                                                                             s->d_ns_tensors, s->n_ns, s->d_sumsq);
-        }
+        else
+            sumsq_ordered_kernel<<<s->n_ns, kSeqThreads, 0, e->stream>>>(s->d_desc, s->d_ns_tensors, s->d_sizes,
+                                                                        opt->d_present, s->d_sumsq);
         VB_CUDA(cudaGetLastError());
-        normalise_kernel<false><<<ew_grid, kEwThreads, 0, e->stream>>>(s->d_desc, s->d_chunks, s->n_chunks,
-                                                                      opt->d_present, s->d_is_ns, s->d_sumsq,
-                                                                      s->d_upd, nullptr);
+        normalise_kernel<<<ew_grid, kEwThreads, 0, e->stream>>>(s->d_desc, s->d_chunks, s->n_chunks, opt->d_present,
+                                                               s->d_ns_kind, s->d_sumsq, s->d_upd, s->d_xb[0]);
         VB_CUDA(cudaGetLastError());
         e->launches += 2;
         for (int it = 0; it < opt->ns_steps; ++it) {
             const int par = it & 1;
-            VB_TRY(launch_ns_gemm_f32(s->d_gram_prob[par], s->d_gram_tiles, s->n_gram_tiles, opt->d_present,
-                                      e->sm_count, e->stream));
-            VB_TRY(launch_ns_gemm_f32(s->d_upd_prob[par], s->d_upd_tiles, s->n_upd_tiles, opt->d_present,
-                                      e->sm_count, e->stream));
-            e->launches += 2;
+            const bool last = it == opt->ns_steps - 1;
+            if (s->n_tc_gram_tiles > 0) {
+                VB_TRY(launch_ns_gemm_tc(s->d_tc_gram[par], s->d_tc_gram_tiles, s->n_tc_gram_tiles, opt->d_present,
+                                         s->d_error, e->sm_count, e->stream));
+                VB_TRY(launch_ns_gemm_tc(last ? s->d_tc_upd_final : s->d_tc_upd[par], s->d_tc_upd_tiles,
+                                         s->n_tc_upd_tiles, opt->d_present, s->d_error, e->sm_count, e->stream));
+                e->launches += 2;
+            }
+            if (s->n_gram_tiles > 0) {
+                VB_TRY(launch_ns_gemm_f32(s->d_gram_prob[par], s->d_gram_tiles, s->n_gram_tiles, opt->d_present,
+                                          e->sm_count, e->stream));
+                VB_TRY(launch_ns_gemm_f32(s->d_upd_prob[par], s->d_upd_tiles, s->n_upd_tiles, opt->d_present,
+                                          e->sm_count, e->stream));
+                e->launches += 2;
+            }
         }
         s->last_flops = s->flops_per_step;
+        if (s->n_tc_gram_tiles > 0)
+            VB_CUDA(cudaMemcpyAsync(s->h_error, s->d_error, sizeof(int), cudaMemcpyDeviceToHost, e->stream));
     }
     if (s->n_chunks > 0) {
         apply_kernel<<<ew_grid, kEwThreads, 0, e->stream>>>(s->d_desc_apply, s->d_chunks, s->n_chunks,
@@ -645,7 +767,7 @@ int muon_download_update(vb_optimizer *opt, int64_t tensor, float *host, int64_t
     VB_CUDA(cudaMemcpyAsync(host, s->final_update[(size_t)tensor], (size_t)n * sizeof(float),
                             cudaMemcpyDeviceToHost, opt->eng->stream));
     VB_CUDA(cudaStreamSynchronize(opt->eng->stream));
-    return VB_OK;
+    return muon_check_error(opt);
 }
 
 int muon_last_flops(vb_optimizer *opt, double *flops)

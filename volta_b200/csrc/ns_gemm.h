@@ -3,6 +3,9 @@
 // a tile list (problem, m0, n0) is walked by a persistent grid.
 #pragma once
 
+#include <cuda.h>
+#include <cuda_bf16.h>
+
 #include "vb_internal.h"
 
 namespace vb {
@@ -29,6 +32,28 @@ struct F32GemmProblem {
     int32_t tensor;  // index into the optimizer's gradient-presence bytes
     int32_t pad;
 };
+
+enum TcEpilogue { TC_EPI_THREE_I_MINUS = 0, TC_EPI_HALF = 1 };
+
+// D[M,N] = epilogue( sum_k A[m,k] * B[n,k] ) on the tensor cores, bf16 operands.
+// Each operand is a row-major bf16 matrix described by a TMA tensor map; it is "K-major"
+// when its rows are indexed by m (or n) and "MN-major" when its rows are indexed by k.
+struct alignas(128) TcGemmProblem {
+    CUtensorMap map_a;
+    CUtensorMap map_b;
+    int32_t M, N, K;
+    int32_t a_mn_major, b_mn_major;
+    int32_t epilogue;
+    int32_t ld_out;
+    int32_t tensor;          // index into the optimizer's gradient-presence bytes
+    __nv_bfloat16 *out_bf16; // may be null
+    float *out_f32;          // may be null
+};
+
+int launch_ns_gemm_tc(const TcGemmProblem *d_problems, const GemmTile *d_tiles, int n_tiles,
+                      const uint8_t *d_present, int *d_error_flag, int sm_count, cudaStream_t stream);
+void tc_gemm_tile_shape(int *bm, int *bn);
+int make_bf16_tensor_map(void *map_out, const void *base, int64_t inner, int64_t outer);
 
 int launch_ns_gemm_f32(const F32GemmProblem *d_problems, const GemmTile *d_tiles, int n_tiles,
                        const uint8_t *d_present, int sm_count, cudaStream_t stream);
