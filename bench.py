@@ -274,11 +274,17 @@ def run_ours(args):
     barrier()
     e2e_s = max_over_ranks((time.perf_counter() - t0) / max(e2e_steps, 1))
 
+    opt.close()
+    grads_pinned.free()
+    params_pinned.free()
+    del params, tensors
+
+    # ---- Muon (second headline: Newton-Schulz tensor TFLOP/s), on every rank ----
+    muon = None if args.skip_muon else run_muon(args, eng, world, rank, dev, barrier, max_over_ranks, peaks)
+
     if rank != 0:
-        opt.close()
         return 0
 
-    owned = arena // world  # elements one launch updates on one rank
     achieved_gbs = ADAM_BYTES_PER_PARAM * (wl.total / world) / (kernel_avg_ms * 1e-3) / 1e9
     line = {
         "metric": "adam_params_per_s", "value": value, "unit": "params/s", "n_gpus": world,
@@ -313,21 +319,115 @@ def run_ours(args):
                                 "sample": f"{len(times)} full steps of the same workload, 1 thread of "
                                           f"{os.cpu_count()} host cores (Volta's optimizer is single threaded)",
                                 "ms_per_step": sec * 1e3}
-    opt.close()
+    if muon is not None:
+        line["muon"] = muon
     print(json.dumps(line), flush=True)
     return 0
 
 
+def time_cpu_muon_sample(ns_steps=5):
+    """Oracle Muon step on one 1024 x 1024 matrix, one thread; returns (seconds, flops)."""
+    import oracle
+    oracle.build()
+    oracle.set_threads(1)
+    rng = np.random.default_rng(3)
+    w = (rng.standard_normal((1024, 1024)) * 0.02).astype(np.float32)
+    g = (rng.standard_normal((1024, 1024)) * 1e-3).astype(np.float32)
+    opt = oracle.Muon([w], 0.1, 0.9, True, ns_steps)
+    t0 = time.perf_counter()
+    opt.step([g])
+    return time.perf_counter() - t0, 4.0 * 1024 ** 3 * ns_steps
+
+
+def run_muon(args, eng, world, rank, dev, barrier, max_over_ranks, peaks):
+    """Muon on the 96 matrices of the 24-layer d=1024 configuration: NS TFLOP/s."""
+    import torch
+
+    from volta_b200 import VB_NS_BF16, VB_NS_F32, Muon, Tensor
+
+    wl = workloads.c4_muon()
+    h = wl.hyper
+    params = wl.make_params()
+    grads = wl.make_grads(1)
+    out = {}
+    for mode_name, mode, steps in (("bf16", VB_NS_BF16, max(3, min(args.steps, 20))), ("f32", VB_NS_F32, 2)):
+        if mode_name == "f32" and args.skip_muon_f32:
+            continue
+        tensors = [Tensor(p, p.shape) for p in params]
+        opt = Muon(tensors, h["lr"], h["momentum"], h["nesterov"], h["ns_steps"], ns_mode=mode, engine=eng)
+        _, _, arena, offsets = opt.arena_layout()
+        host = fill_arena(wl, offsets, arena, grads)
+        opt.upload_arena(1, host)
+        del host
+        eng.synchronize()
+        warm = 3 if mode_name == "bf16" else 1
+        for _ in range(warm):
+            opt.step()
+        barrier()
+        eng.set_profiling(True)
+        for ph in ("muon_pre", "muon_ns", "muon_apply", "exchange"):
+            eng.profile(ph)
+        stream = torch.cuda.ExternalStream(eng.stream, device=dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        launches0 = eng.launch_count
+        barrier()
+        e0.record(stream)
+        for _ in range(steps):
+            opt.step()
+        e1.record(stream)
+        eng.synchronize()
+        barrier()
+        step_ms = max_over_ranks(e0.elapsed_time(e1) / steps)
+        ns_ms = max_over_ranks(eng.profile("muon_ns")[0] / steps)
+        pre_ms = eng.profile("muon_pre")[0] / steps
+        apply_ms = eng.profile("muon_apply")[0] / steps
+        exch_ms = eng.profile("exchange")[0] / steps
+        eng.set_profiling(False)
+        flops_rank = opt.last_ns_flops
+        if world > 1:
+            t = torch.tensor([flops_rank], dtype=torch.float64, device=dev)
+            torch.distributed.all_reduce(t)
+            flops_total = float(t.item())
+        else:
+            flops_total = flops_rank
+        tflops = flops_total / (ns_ms * 1e-3) / 1e12
+        peak = peaks["bf16_tflops_sustained"] * world
+        out[mode_name] = {
+            "ns_tflops": tflops, "ns_ms_per_step": ns_ms, "ms_per_step": step_ms,
+            "pre_ms": pre_ms, "apply_ms": apply_ms, "exchange_ms": exch_ms,
+            "params_per_s": wl.total / (step_ms * 1e-3), "steps": steps,
+            "executed_flops_per_step": flops_total,
+            "reference_formulation_flops_per_step": sum(4.0 * r * c * c * h["ns_steps"] for r, c in wl.shapes),
+            "gpu_launches": int(eng.launch_count - launches0),
+        }
+        if mode_name == "bf16":
+            out[mode_name]["roofline"] = {
+                "bound": "tensor", "achieved": tflops, "peak": peak, "unit": "TFLOP/s", "frac": tflops / peak,
+                "peak_source": peaks["source"] + " (cuBLAS bf16 sustained)",
+                "frac_of_burst_peak": tflops / (peaks["bf16_tflops"] * world),
+                "frac_of_nominal_2250": tflops / (2250.0 * world), "traffic": None,
+                "kernel": "ns_gemm_tc_kernel (tcgen05 bf16, 10 launches per step)"}
+        opt.close()
+    out["config"] = {"workload": "c4_muon: 96 matrices (24 x {3072x1024, 1024x1024, 4096x1024, 1024x4096}), "
+                                 "301989888 f32 params, lr=0.1 momentum=0.9 nesterov ns_steps=5"}
+    if world == 1 and not args.no_cpu_baseline:
+        sec, fl = time_cpu_muon_sample(h["ns_steps"])
+        ref_flops = out["bf16"]["reference_formulation_flops_per_step"]
+        out["cpu_baseline"] = {"value": fl / sec / 1e12, "unit": "TFLOP/s", "cores": 1, "kind": "port",
+                               "sample": "one Muon step of one 1024x1024 matrix (21.5 GFLOP), 1 thread; a whole "
+                                         f"step of the workload is {ref_flops / 1e12:.2f} TFLOP in the reference's "
+                                         f"formulation, i.e. ~{ref_flops / fl * sec:.0f} s at this rate (extrapolated)"}
+    return out
+
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of multi_tensor_update_kernel<ADAM>
+# on this workload, from the ncu capture summarised in profiles/adam_c3_multi_tensor_update.md
+NCU_ADAM_C3_DRAM_BYTES_PER_LAUNCH = 3.0138e9
+
+
 def traffic_from_profile():
-    """DRAM bytes per launch of the Adam kernel from the committed ncu summary, if present."""
-    path = os.path.join(ROOT, "profiles", "adam_c3_ncu.json")
-    if os.path.exists(path):
-        try:
-            with open(path) as fh:
-                return json.load(fh).get("dram_bytes_per_launch")
-        except (OSError, ValueError):
-            return None
-    return None
+    return NCU_ADAM_C3_DRAM_BYTES_PER_LAUNCH
 
 
 def main():
@@ -338,6 +438,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true", help="profiling runs: device-resident timing only")
+    ap.add_argument("--skip-muon", action="store_true", help="Adam only")
+    ap.add_argument("--skip-muon-f32", action="store_true", help="skip the (slow) f32 Newton-Schulz timing")
+    ap.add_argument("--only-muon", action="store_true", help="profiling runs: Muon bf16 only")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3

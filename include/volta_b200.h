@@ -108,6 +108,20 @@ int vb_engine_stream(vb_engine *engine, void **cuda_stream);
 /* Kernels launched by this engine since creation (bookkeeping for benchmarks). */
 int vb_engine_launch_count(vb_engine *engine, uint64_t *count);
 
+/* Phase timing for benchmarks (no counterpart in the reference; its SystemMonitor counts
+ * operations with host clocks, src/gpu/system_monitor.rs:31-150).  While profiling is on,
+ * every step brackets its phases with CUDA events on the engine stream.
+ * vb_engine_profile waits for the stream, returns the summed device time and the number
+ * of brackets of one phase since the last query, and clears them. */
+#define VB_PHASE_UPDATE 0    /* fused Adam / SGD launch */
+#define VB_PHASE_MUON_PRE 1  /* Muon momentum, sum of squares, normalise */
+#define VB_PHASE_MUON_NS 2   /* Muon Newton-Schulz GEMM chain */
+#define VB_PHASE_MUON_APPLY 3
+#define VB_PHASE_EXCHANGE 4  /* NCCL all-gather / broadcast */
+#define VB_PHASE_COUNT 5
+int vb_engine_set_profiling(vb_engine *engine, int enabled);
+int vb_engine_profile(vb_engine *engine, int phase, double *total_ms, int64_t *count);
+
 /* Page-locked host memory for upload/download buffers (pinned buffers make the copies
  * asynchronous and full speed; a pinned upload buffer must stay unchanged until the next
  * vb_engine_synchronize or download).  Counterpart: the staging buffer pool,

@@ -35,6 +35,37 @@ constexpr int64_t kShardAlign = 256;   // elements: every rank's slice starts on
 
 static int64_t round_up(int64_t x, int64_t q) { return (x + q - 1) / q * q; }
 
+static cudaEvent_t prof_event(vb_engine *e)
+{
+    cudaEvent_t ev = nullptr;
+    if (!e->prof_free.empty()) {
+        ev = e->prof_free.back();
+        e->prof_free.pop_back();
+    } else if (cudaEventCreate(&ev) != cudaSuccess) {
+        return nullptr;
+    }
+    return ev;
+}
+
+void prof_begin(vb_engine *e, int phase)
+{
+    if (!e->profiling) return;
+    cudaEvent_t ev = prof_event(e);
+    if (!ev) return;
+    cudaEventRecord(ev, e->stream);
+    e->prof_open[phase] = ev;
+}
+
+void prof_end(vb_engine *e, int phase)
+{
+    if (!e->profiling || !e->prof_open[phase]) return;
+    cudaEvent_t ev = prof_event(e);
+    if (!ev) return;
+    cudaEventRecord(ev, e->stream);
+    e->prof_pairs[phase].emplace_back(e->prof_open[phase], ev);
+    e->prof_open[phase] = nullptr;
+}
+
 static int check_opt(const vb_optimizer *opt)
 {
     if (!opt || !opt->eng) return fail(VB_ERR_INVALID_ARG, "optimizer handle is null");
@@ -308,6 +339,14 @@ int vb_engine_destroy(vb_engine *e)
     cudaSetDevice(e->device);
     if (e->stream) cudaStreamSynchronize(e->stream);
     comm_destroy(e);
+    for (int ph = 0; ph < VB_PHASE_COUNT; ++ph) {
+        for (auto &pr : e->prof_pairs[ph]) {
+            cudaEventDestroy(pr.first);
+            cudaEventDestroy(pr.second);
+        }
+        if (e->prof_open[ph]) cudaEventDestroy(e->prof_open[ph]);
+    }
+    for (cudaEvent_t ev : e->prof_free) cudaEventDestroy(ev);
     for (int i = 0; i < 2; ++i) {
         if (e->h_stage[i]) cudaFreeHost(e->h_stage[i]);
         if (e->d_stage[i]) cudaFree(e->d_stage[i]);
@@ -337,6 +376,35 @@ int vb_engine_launch_count(vb_engine *e, uint64_t *count)
     if (!e || !count) return fail(VB_ERR_INVALID_ARG, "null argument");
     *count = e->launches;
     return VB_OK;
+}
+
+int vb_engine_set_profiling(vb_engine *e, int enabled)
+{
+    if (!e) return fail(VB_ERR_INVALID_ARG, "engine is null");
+    e->profiling = enabled != 0;
+    return VB_OK;
+}
+
+int vb_engine_profile(vb_engine *e, int phase, double *total_ms, int64_t *count)
+{
+    VB_API_BEGIN
+    if (!e || !total_ms || !count) return fail(VB_ERR_INVALID_ARG, "null argument");
+    if (phase < 0 || phase >= VB_PHASE_COUNT) return fail(VB_ERR_INVALID_ARG, "unknown phase %d", phase);
+    VB_CUDA(cudaSetDevice(e->device));
+    VB_CUDA(cudaStreamSynchronize(e->stream));
+    double total = 0.0;
+    for (auto &pr : e->prof_pairs[phase]) {
+        float ms = 0.0f;
+        VB_CUDA(cudaEventElapsedTime(&ms, pr.first, pr.second));
+        total += ms;
+        e->prof_free.push_back(pr.first);
+        e->prof_free.push_back(pr.second);
+    }
+    *total_ms = total;
+    *count = (int64_t)e->prof_pairs[phase].size();
+    e->prof_pairs[phase].clear();
+    return VB_OK;
+    VB_API_END
 }
 
 int vb_comm_unique_id(void *id128)
@@ -646,12 +714,17 @@ int vb_optimizer_step_ex(vb_optimizer *opt, uint32_t flags)
     if (opt->n_chunks > 0) {
         bool all_present = true;
         for (int64_t i = 0; i < opt->n_tensors && all_present; ++i) all_present = opt->present[(size_t)i] != 0;
+        prof_begin(e, VB_PHASE_UPDATE);
         VB_TRY(launch_multi_tensor(op, opt->d_chunks, opt->n_chunks, opt->d_present, all_present, s,
                                    e->sm_count, e->stream));
+        prof_end(e, VB_PHASE_UPDATE);
         e->launches += 1;
     }
-    if (e->world > 1 && !(flags & VB_STEP_NO_EXCHANGE))
+    if (e->world > 1 && !(flags & VB_STEP_NO_EXCHANGE)) {
+        prof_begin(e, VB_PHASE_EXCHANGE);
         VB_TRY(comm_all_gather_inplace(e, opt->d_param, opt->arena / e->world));
+        prof_end(e, VB_PHASE_EXCHANGE);
+    }
     return VB_OK;
     VB_API_END
 }

@@ -26,6 +26,11 @@ struct vb_engine {
     size_t stage_bytes[2] = {0, 0};
     cudaEvent_t stage_done[2] = {nullptr, nullptr};
     int stage_next = 0;
+    // optional phase timing (vb_engine_set_profiling): event pairs per phase, summed on query
+    bool profiling = false;
+    std::vector<std::pair<cudaEvent_t, cudaEvent_t>> prof_pairs[VB_PHASE_COUNT];
+    std::vector<cudaEvent_t> prof_free;
+    cudaEvent_t prof_open[VB_PHASE_COUNT] = {};
 };
 
 enum OptimizerKind { KIND_ADAM = 0, KIND_SGD = 1, KIND_MUON = 2 };
@@ -64,6 +69,10 @@ struct vb_optimizer {
 };
 
 namespace vb {
+
+// api.cu: phase timing; no-ops unless profiling is on
+void prof_begin(vb_engine *e, int phase);
+void prof_end(vb_engine *e, int phase);
 
 // muon.cu
 int muon_init(vb_optimizer *opt);

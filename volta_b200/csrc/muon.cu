@@ -693,6 +693,7 @@ int muon_step(vb_optimizer *opt, uint32_t flags)
     VB_TRY(sync_present(opt));
     const int ew_grid = (int)std::min<int64_t>(std::max<int64_t>(s->n_chunks, 1), (int64_t)e->sm_count * 8);
     const bool fast_norm = opt->ns_mode == VB_NS_BF16;
+    prof_begin(e, VB_PHASE_MUON_PRE);
     if (s->n_chunks > 0) {
         if (fast_norm)
             momentum_kernel<true><<<ew_grid, kEwThreads, 0, e->stream>>>(s->d_desc, s->d_chunks, s->n_chunks,
@@ -717,6 +718,8 @@ int muon_step(vb_optimizer *opt, uint32_t flags)
                                                                s->d_ns_kind, s->d_sumsq, s->d_upd, s->d_xb[0]);
         VB_CUDA(cudaGetLastError());
         e->launches += 2;
+        prof_end(e, VB_PHASE_MUON_PRE);
+        prof_begin(e, VB_PHASE_MUON_NS);
         for (int it = 0; it < opt->ns_steps; ++it) {
             const int par = it & 1;
             const bool last = it == opt->ns_steps - 1;
@@ -735,14 +738,18 @@ int muon_step(vb_optimizer *opt, uint32_t flags)
                 e->launches += 2;
             }
         }
+        prof_end(e, VB_PHASE_MUON_NS);
         s->last_flops = s->flops_per_step;
         if (s->n_tc_gram_tiles > 0)
             VB_CUDA(cudaMemcpyAsync(s->h_error, s->d_error, sizeof(int), cudaMemcpyDeviceToHost, e->stream));
     }
+    prof_end(e, VB_PHASE_MUON_PRE);  // no-op if already closed (no Newton-Schulz matrices)
     if (s->n_chunks > 0) {
+        prof_begin(e, VB_PHASE_MUON_APPLY);
         apply_kernel<<<ew_grid, kEwThreads, 0, e->stream>>>(s->d_desc_apply, s->d_chunks, s->n_chunks,
                                                            opt->d_present, opt->lr);
         VB_CUDA(cudaGetLastError());
+        prof_end(e, VB_PHASE_MUON_APPLY);
         e->launches += 1;
     }
     if (e->world > 1 && !(flags & VB_STEP_NO_EXCHANGE)) {
@@ -752,7 +759,9 @@ int muon_step(vb_optimizer *opt, uint32_t flags)
             if (opt->present[(size_t)i] && opt->sizes[(size_t)i] > 0)
                 items.push_back(BcastItem{opt->d_param + opt->offsets[(size_t)i], opt->sizes[(size_t)i],
                                           s->owner[(size_t)i]});
+        prof_begin(e, VB_PHASE_EXCHANGE);
         VB_TRY(comm_group_broadcast(e, items.data(), (int64_t)items.size()));
+        prof_end(e, VB_PHASE_EXCHANGE);
     }
     return VB_OK;
 }

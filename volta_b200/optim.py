@@ -60,6 +60,17 @@ class Engine:
         call("vb_engine_launch_count", self._h, C.byref(n))
         return int(n.value)
 
+    PHASES = {"update": 0, "muon_pre": 1, "muon_ns": 2, "muon_apply": 3, "exchange": 4}
+
+    def set_profiling(self, enabled: bool) -> None:
+        call("vb_engine_set_profiling", self._h, int(bool(enabled)))
+
+    def profile(self, phase: str):
+        """(total device ms, number of brackets) of one phase since the last query."""
+        ms, n = C.c_double(), C.c_int64()
+        call("vb_engine_profile", self._h, self.PHASES[phase], C.byref(ms), C.byref(n))
+        return float(ms.value), int(n.value)
+
     @staticmethod
     def unique_id() -> bytes:
         buf = C.create_string_buffer(128)
