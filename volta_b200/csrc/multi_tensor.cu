@@ -18,10 +18,12 @@ namespace vb {
 namespace {
 
 constexpr int kThreads = 256;
-// Launch shape found by sweeping on a B200: 256-bit loads, one vector per array per thread
-// in flight, exactly 3 CTAs of 256 threads per SM.  More resident threads or deeper
-// unrolling put more requests in flight than the HBM controllers like and cost up to 15 %.
-constexpr int kCtasPerSm = 3;
+// Launch shape found by sweeping on a B200 with realistic (non-zero) data: 256-bit accesses,
+// one vector per array per thread in flight, and exactly 512 resident threads per SM
+// (2 CTAs x 256).  The step runs under the board's power cap: more resident threads or
+// deeper unrolling put more requests in flight than the memory system sustains and cost
+// 5-15 % (768 threads/SM: -7 %, 1024: -6 %, 2048: -15 %).
+constexpr int kCtasPerSm = 2;
 constexpr int kVecElems = 8;  // floats per 256-bit access
 
 struct alignas(32) Vec8 {
