@@ -250,6 +250,32 @@ int vb_multi_tensor_step(vb_engine *engine, const vb_optimizer_step_params *hp, 
                          const int64_t *sizes, void *const *params, const void *const *grads,
                          void *const *state1, void *const *state2);
 
+/* The same fused step for callers that cannot allocate: no counterpart in the reference.
+ *
+ * vb_multi_tensor_step builds its chunk table in device and pinned host memory that it
+ * allocates, and re-allocates when a larger tensor list arrives.  A host that has given all
+ * device memory to its own pool, that must keep the allocator's locks out of its training
+ * loop, or that forbids allocation after start-up cannot make that call.  This entry point
+ * performs no cudaMalloc, cudaHostAlloc, cudaFree or any other allocating call: the chunk
+ * table lives in a fixed 384 KiB device array that is part of the library image (every GPU
+ * that loads the library holds it until the process exits) and is staged through an equally
+ * fixed host array.  Arguments, arithmetic and results are those of vb_multi_tensor_step.
+ *
+ * Limits and rules that follow from the fixed array:
+ *  - at most 8192 chunks: n_tensors <= 8192, and the list must fit in 8192 pieces of at most
+ *    131072 elements (about 1.07e9 elements for large tensors; fewer for many ragged ones).
+ *    Anything larger returns VB_ERR_UNSUPPORTED with a message that says so;
+ *  - all calls on one device share the array and it keeps the last call's table.  The part a
+ *    call uses is rewritten by that call (nothing in it must start at zero).  Calls issued on
+ *    one engine are ordered by its stream; calls from different engines or streams that
+ *    overlap on the GPU race on the table and must be serialised by the caller;
+ *  - the first call on a device also looks up the array's device address; make that first
+ *    call before any stream capture begins. */
+int vb_multi_tensor_step_static(vb_engine *engine, const vb_optimizer_step_params *hp,
+                                int64_t n_tensors, const int64_t *sizes, void *const *params,
+                                const void *const *grads, void *const *state1,
+                                void *const *state2);
+
 #ifdef __cplusplus
 }
 #endif

@@ -90,6 +90,7 @@ SIGNATURES = {
     "vb_muon_download_update": [_vp, _i64, _vp, _i64],
     "vb_muon_last_ns_flops": [_vp, C.POINTER(C.c_double)],
     "vb_multi_tensor_step": [_vp, C.POINTER(StepParams), _i64, _i64p, _vpp, _vpp, _vpp, _vpp],
+    "vb_multi_tensor_step_static": [_vp, C.POINTER(StepParams), _i64, _i64p, _vpp, _vpp, _vpp, _vpp],
 }
 OTHER_SYMBOLS = ["vb_abi_version", "vb_last_error"]
 

@@ -30,6 +30,17 @@ int fail(int code, const char *fmt, ...)
     return code;
 }
 
+int engine_launch_info(vb_engine *e, int *device, int *sm_count, cudaStream_t *stream)
+{
+    if (!e) return fail(VB_ERR_INVALID_ARG, "engine is null");
+    *device = e->device;
+    *sm_count = e->sm_count;
+    *stream = e->stream;
+    return VB_OK;
+}
+
+void engine_count_launch(vb_engine *e) { e->launches += 1; }
+
 constexpr int64_t kTensorAlign = 32;   // elements: every tensor starts on a 128-byte boundary
 constexpr int64_t kShardAlign = 256;   // elements: every rank's slice starts on a 1 KiB boundary
 

@@ -266,4 +266,133 @@ int launch_multi_tensor(int op, const FatChunk *d_chunks, int64_t n_chunks, cons
     return VB_OK;
 }
 
+// ---------------------------------------------------------------------------------------------
+// vb_multi_tensor_step_static: the fused step for callers that must not allocate.
+//
+// vb_multi_tensor_step keeps its chunk table in device and pinned host memory that it
+// allocates (and grows) on demand.  Some hosts cannot tolerate that inside their step: a
+// runtime that has handed all device memory to its own pool, a loop that must not touch the
+// allocator's locks once training has started, a plugin host that forbids allocation after
+// initialisation.  This variant keeps the chunk table in a fixed array that is part of the
+// library image, so a call performs no cudaMalloc / cudaHostAlloc / cudaFree at all: it
+// writes the table into a fixed host array, copies it to the fixed device array on the
+// engine's stream and launches the same kernel as vb_multi_tensor_step.
+//
+// Consequences of the fixed array, all documented in the header:
+//  * capacity: VB_STATIC_MAX_CHUNKS chunks (the chunk length grows with the problem up to
+//    VB_STATIC_MAX_CHUNK_ELEMS elements); larger tensor lists are rejected;
+//  * every GPU that loads the library carries the array (384 KiB) until the process exits;
+//  * all calls on a device share it: two calls that overlap on the GPU (different engines
+//    or streams) race; calls on one engine are ordered by its stream and are safe;
+//  * the first call on a device looks the array's address up (cudaGetSymbolAddress), so
+//    make that first call before starting a stream capture.
+// ---------------------------------------------------------------------------------------------
+
+#define VB_STATIC_MAX_CHUNKS 8192
+#define VB_STATIC_MAX_CHUNK_ELEMS (1 << 17)
+#define VB_STATIC_MAX_DEVICES 64
+
+// The scratch itself.  In host code `g_static_chunk_table` is only a handle for the runtime,
+// not a device address: the address is resolved per device below.
+static __device__ __align__(256) unsigned char g_static_chunk_table[VB_STATIC_MAX_CHUNKS * sizeof(FatChunk)];
+
+namespace {
+
+FatChunk g_static_host_table[VB_STATIC_MAX_CHUNKS];       // staging on the host, equally fixed
+FatChunk *g_static_dev_ptr[VB_STATIC_MAX_DEVICES] = {};   // resolved device address, per device
+
+// Once per device, with that device current.
+int static_table_address(int device, FatChunk **out)
+{
+    if (device < 0 || device >= VB_STATIC_MAX_DEVICES)
+        return fail(VB_ERR_UNSUPPORTED, "device %d is beyond the %d devices the static table supports", device,
+                    VB_STATIC_MAX_DEVICES);
+    if (!g_static_dev_ptr[device]) {
+        void *ptr = nullptr;
+        VB_CUDA(cudaSetDevice(device));
+        VB_CUDA(cudaGetSymbolAddress(&ptr, g_static_chunk_table));
+        if (!ptr) return fail(VB_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
+        g_static_dev_ptr[device] = static_cast<FatChunk *>(ptr);
+    }
+    *out = g_static_dev_ptr[device];
+    return VB_OK;
+}
+
+}  // namespace
 }  // namespace vb
+
+extern "C" int vb_multi_tensor_step_static(vb_engine *engine, const vb_optimizer_step_params *hp, int64_t n_tensors,
+                                           const int64_t *sizes, void *const *params, const void *const *grads,
+                                           void *const *state1, void *const *state2)
+{
+    using namespace vb;
+    int device = 0, sm_count = 0;
+    cudaStream_t stream = nullptr;
+    if (!engine || !hp) return fail(VB_ERR_INVALID_ARG, "null argument");
+    if (engine_launch_info(engine, &device, &sm_count, &stream) != VB_OK) return VB_ERR_INVALID_ARG;
+    if (hp->op > 2u) return fail(VB_ERR_INVALID_ARG, "op %u is not 0 (SGD), 1 (SGD+momentum) or 2 (Adam)", hp->op);
+    if (n_tensors < 0) return fail(VB_ERR_INVALID_ARG, "n_tensors is negative");
+    if (n_tensors == 0) return VB_OK;
+    if (!sizes || !params || !grads) return fail(VB_ERR_INVALID_ARG, "sizes/params/grads is null");
+    if (hp->op >= 1 && !state1) return fail(VB_ERR_INVALID_ARG, "state1 is null for op %u", hp->op);
+    if (hp->op == 2 && !state2) return fail(VB_ERR_INVALID_ARG, "state2 is null for Adam");
+    if (hp->op == 2 && !(hp->t >= 1.0f && hp->t <= 2147483648.0f)) return fail(VB_ERR_INVALID_ARG, "Adam needs t >= 1");
+    if (n_tensors > VB_STATIC_MAX_CHUNKS)
+        return fail(VB_ERR_UNSUPPORTED, "%lld tensors exceed the static table (%d chunks); use vb_multi_tensor_step",
+                    (long long)n_tensors, VB_STATIC_MAX_CHUNKS);
+    int64_t total = 0;
+    for (int64_t i = 0; i < n_tensors; ++i) {
+        if (sizes[i] < 0) return fail(VB_ERR_INVALID_ARG, "sizes[%lld] is negative", (long long)i);
+        if (sizes[i] == 0) continue;
+        if (!params[i] || !grads[i])
+            return fail(VB_ERR_INVALID_ARG, "params[%lld] or grads[%lld] is null", (long long)i, (long long)i);
+        if (hp->op >= 1 && !state1[i]) return fail(VB_ERR_INVALID_ARG, "state1[%lld] is null", (long long)i);
+        if (hp->op == 2 && !state2[i]) return fail(VB_ERR_INVALID_ARG, "state2[%lld] is null", (long long)i);
+        if (((uintptr_t)params[i] | (uintptr_t)grads[i]) & 3u)
+            return fail(VB_ERR_INVALID_ARG, "tensor %lld is not 4-byte aligned", (long long)i);
+        total += sizes[i];
+    }
+    if (total == 0) return VB_OK;
+    // smallest chunk length (doubling from the usual one) whose table fits the fixed array
+    int64_t chunk_len = pick_chunk_len(total, sm_count);
+    int64_t n_chunks = 0;
+    for (;;) {
+        n_chunks = 0;
+        for (int64_t i = 0; i < n_tensors; ++i) n_chunks += (sizes[i] + chunk_len - 1) / chunk_len;
+        if (n_chunks <= VB_STATIC_MAX_CHUNKS) break;
+        if (chunk_len * 2 > VB_STATIC_MAX_CHUNK_ELEMS)
+            return fail(VB_ERR_UNSUPPORTED,
+                        "%lld elements in %lld tensors need %lld chunks of %lld elements; the static table holds %d "
+                        "(use vb_multi_tensor_step, which allocates its table)",
+                        (long long)total, (long long)n_tensors, (long long)n_chunks, (long long)chunk_len,
+                        VB_STATIC_MAX_CHUNKS);
+        chunk_len *= 2;
+    }
+    FatChunk *d_table = nullptr;
+    VB_TRY(static_table_address(device, &d_table));  // first call on this device: resolves the address
+    VB_CUDA(cudaSetDevice(device));
+    int64_t c = 0;
+    for (int64_t i = 0; i < n_tensors; ++i) {
+        for (int64_t b = 0; b < sizes[i]; b += chunk_len) {
+            FatChunk &f = g_static_host_table[c++];
+            f.p = (float *)params[i] + b;
+            f.g = (const float *)grads[i] + b;
+            f.s1 = (state1 && state1[i]) ? (float *)state1[i] + b : nullptr;
+            f.s2 = (state2 && state2[i]) ? (float *)state2[i] + b : nullptr;
+            f.len = (uint32_t)(sizes[i] - b < chunk_len ? sizes[i] - b : chunk_len);
+            f.tensor = (uint32_t)i;
+            f.pad = 0;
+        }
+    }
+    // The used prefix of the device table is rewritten on every call; nothing in it has to
+    // start at zero and entries beyond n_chunks are never read.  The source is ordinary
+    // (pageable) host memory, so the runtime has taken its copy when this call returns and the
+    // host array can be refilled by the next call.
+    VB_CUDA(cudaMemcpyAsync(d_table, g_static_host_table, (size_t)n_chunks * sizeof(FatChunk), cudaMemcpyHostToDevice,
+                            stream));
+    const StepScalars s =
+        make_scalars((int)hp->op, hp->lr, hp->beta1, hp->beta2, hp->eps, hp->weight_decay, (int64_t)hp->t);
+    VB_TRY(launch_multi_tensor((int)hp->op, d_table, n_chunks, nullptr, /*all_present=*/true, s, sm_count, stream));
+    engine_count_launch(engine);
+    return VB_OK;
+}

@@ -86,6 +86,11 @@ StepScalars make_scalars(int op, float lr, float beta1, float beta2, float eps, 
 int launch_multi_tensor(int op, const FatChunk *d_chunks, int64_t n_chunks, const uint8_t *d_present,
                         bool all_present, const StepScalars &s, int sm_count, cudaStream_t stream);
 
+// Device, SM count and stream of an engine / launch bookkeeping, for translation units that
+// do not see the engine's definition (api.cu).
+int engine_launch_info(vb_engine *e, int *device, int *sm_count, cudaStream_t *stream);
+void engine_count_launch(vb_engine *e);
+
 // Splits [begin, end) of each tensor into chunks.
 int64_t pick_chunk_len(int64_t total_elements, int sm_count);
 

@@ -370,9 +370,14 @@ def multi_tensor_step(engine: Engine, op: int, sizes: Sequence[int], params: Seq
                       grads: Sequence[int], state1: Optional[Sequence[int]] = None,
                       state2: Optional[Sequence[int]] = None, *, lr: float, beta1: float = 0.0,
                       beta2: float = 0.0, t: float = 0.0, eps: float = 0.0,
-                      weight_decay: float = 0.0) -> None:
+                      weight_decay: float = 0.0, static_table: bool = False) -> None:
     """One fused launch over caller-owned device buffers (device addresses as integers):
-    the replacement of per-tensor ``gpu_optimizer_step`` calls (src/ops/gpu_ops.rs:495-508)."""
+    the replacement of per-tensor ``gpu_optimizer_step`` calls (src/ops/gpu_ops.rs:495-508).
+
+    ``static_table=True`` takes the entry point that allocates nothing
+    (``vb_multi_tensor_step_static``): same results, but the chunk table sits in a fixed array
+    inside the library, so the tensor list is limited to 8192 chunks and overlapping calls on
+    one GPU must be serialised by the caller."""
     n = len(sizes)
     hp = _lib.StepParams(op, lr, beta1, beta2, float(t), eps, weight_decay, 0.0)
     arr_sizes = (C.c_int64 * max(n, 1))(*sizes)
@@ -382,5 +387,5 @@ def multi_tensor_step(engine: Engine, op: int, sizes: Sequence[int], params: Seq
             return None
         return (C.c_void_p * max(n, 1))(*[(int(x) if x else None) for x in seq])
 
-    call("vb_multi_tensor_step", engine._h, C.byref(hp), n, arr_sizes, ptrs(params), ptrs(grads),
-         ptrs(state1), ptrs(state2))
+    call("vb_multi_tensor_step_static" if static_table else "vb_multi_tensor_step", engine._h, C.byref(hp), n,
+         arr_sizes, ptrs(params), ptrs(grads), ptrs(state1), ptrs(state2))
