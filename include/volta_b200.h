@@ -97,6 +97,13 @@ int vb_plan_layout(int64_t n_tensors, const int64_t *sizes, int world_size, int 
                    int64_t *shard_end, int64_t *n_chunks, int64_t chunk_capacity,
                    int64_t *chunk_tensor, int64_t *chunk_offset, int64_t *chunk_len);
 
+/* Pure host planning, no CUDA call: which rank owns each Muon tensor.  Whole tensors are
+ * taken in order of decreasing Newton-Schulz cost (4 * long side * short side^2 FLOPs per
+ * iteration) and given to the least-loaded rank; this is the assignment vb_muon_create
+ * uses.  No counterpart in the reference (single process). */
+int vb_plan_muon_owners(int64_t n_tensors, const int64_t *rows, const int64_t *cols, int world_size,
+                        int32_t *owner_out);
+
 /* ---- engine (replaces the process-global wgpu context, src/gpu/mod.rs:30-47) ----- */
 
 int vb_engine_create(int device, vb_engine **out);

@@ -1,0 +1,110 @@
+"""Sharded optimizers on 2 GPUs (skipped with fewer): one child process per GPU, the library's
+own NCCL communicator, results compared with the unsharded CPU oracle.
+
+Adam/SGD: ZeRO-1 slices of the arena + in-place all-gather.  Muon: whole matrices per owner +
+grouped broadcast.  Every rank must end with the full, bit-identical parameter set."""
+import os
+import sys
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _gpu_count():
+    import torch
+    return torch.cuda.device_count()
+
+
+def _worker(rank, world, shared, kind):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import time
+
+    import workloads
+    from volta_b200 import SGD, VB_NS_BF16, VB_NS_F32, Adam, Engine, Muon, Tensor
+    eng = Engine(rank)
+    if rank == 0:
+        shared["id"] = Engine.unique_id()
+    while "id" not in shared:
+        time.sleep(0.01)
+    eng.init_comm(shared["id"], rank, world)
+    assert (eng.rank, eng.world_size) == (rank, world)
+    if kind == "adam":
+        wl = workloads.c5_ragged_adam(n_tensors=96, max_log2=16, seed=11)
+    elif kind == "sgd":
+        wl = workloads.c2_cnn_sgd()
+    else:
+        shapes = [(256, 128), (128, 384), (64, 36), (100,), (512, 256), (256, 256)]
+        wl = workloads.Workload("muon_small", "muon", shapes, [("normal", 0.02)] * len(shapes), 1e-3,
+                                dict(lr=0.1, momentum=0.9, nesterov=True, ns_steps=5), 3)
+    h = wl.hyper
+    tensors = [Tensor(p, p.shape) for p in wl.make_params()]
+    if kind == "adam":
+        opt = Adam(tensors, h["lr"], h["betas"], h["eps"], h["weight_decay"], engine=eng)
+    elif kind == "sgd":
+        opt = SGD(tensors, h["lr"], h["momentum"], h["weight_decay"], engine=eng)
+    else:
+        opt = Muon(tensors, h["lr"], h["momentum"], h["nesterov"], h["ns_steps"],
+                   ns_mode=VB_NS_F32 if kind == "muon_f32" else VB_NS_BF16, engine=eng)
+    owned = 0
+    for s in (1, 2, 3):
+        opt.zero_grad()
+        for t, g in zip(tensors, wl.make_grads(s)):
+            t.grad = g
+        opt.step()
+    for i in range(len(tensors)):
+        lo, hi = opt.state_owned_range(i, 0)
+        owned += hi - lo
+    shared[f"params{rank}"] = [t.data.copy() for t in tensors]
+    shared[f"owned{rank}"] = owned
+    opt.close()
+    eng.close()
+
+
+@pytest.mark.parametrize("kind", ["adam", "sgd", "muon_f32", "muon_bf16"])
+def test_two_gpu_sharded_step_matches_oracle(oracle, kind):
+    if _gpu_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+
+    import workloads
+    ctx = mp.get_context("spawn")
+    with ctx.Manager() as mgr:
+        shared = mgr.dict()
+        procs = [ctx.Process(target=_worker, args=(r, 2, shared, kind)) for r in range(2)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(300)
+            assert p.exitcode == 0
+        res = dict(shared)
+    if kind == "adam":
+        wl = workloads.c5_ragged_adam(n_tensors=96, max_log2=16, seed=11)
+    elif kind == "sgd":
+        wl = workloads.c2_cnn_sgd()
+    else:
+        shapes = [(256, 128), (128, 384), (64, 36), (100,), (512, 256), (256, 256)]
+        wl = workloads.Workload("muon_small", "muon", shapes, [("normal", 0.02)] * len(shapes), 1e-3,
+                                dict(lr=0.1, momentum=0.9, nesterov=True, ns_steps=5), 3)
+    h = wl.hyper
+    ref = wl.make_params()
+    if kind == "adam":
+        o = oracle.Adam(ref, h["lr"], h["betas"], h["eps"], h["weight_decay"])
+    elif kind == "sgd":
+        o = oracle.SGD(ref, h["lr"], h["momentum"], h["weight_decay"])
+    else:
+        o = oracle.Muon(ref, h["lr"], h["momentum"], h["nesterov"], h["ns_steps"])
+    for s in (1, 2, 3):
+        o.step(wl.make_grads(s))
+    for a, b, r in zip(res["params0"], res["params1"], ref):
+        assert np.array_equal(a.view(np.uint32), b.view(np.uint32))  # both ranks hold the same parameters
+        if kind == "muon_bf16":
+            assert np.max(np.abs(a - r)) <= 2e-2 * 0.1 * 0.1 * 3 * max(1.0, float(np.max(np.abs(r))))
+        else:
+            assert np.array_equal(a.view(np.uint32), r.view(np.uint32))
+    # state is partitioned: the ranks' owned element counts add up to the whole
+    assert res["owned0"] + res["owned1"] == wl.total and min(res["owned0"], res["owned1"]) > 0

@@ -1,0 +1,152 @@
+"""The multi-rank path on CPU: two gloo ranks, the library's own sharding plans, the oracle as
+the arithmetic.  Checks that ZeRO-1 slicing of the arena (Adam/SGD) and whole-matrix ownership
+(Muon) followed by the exchange step reproduce the unsharded result bit for bit, i.e. that
+the host-side plan is a partition and the exchange layout (in-place all-gather of equal
+slices; broadcast of each matrix from its owner) is consistent between ranks."""
+import ctypes as C
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _plan(sizes, world, rank):
+    from volta_b200 import _lib
+    n = len(sizes)
+    arr = (C.c_int64 * n)(*sizes)
+    offs = (C.c_int64 * n)()
+    arena, lo, hi, nch = C.c_int64(), C.c_int64(), C.c_int64(), C.c_int64()
+    _lib.call("vb_plan_layout", n, arr, world, rank, 148, offs, C.byref(arena), C.byref(lo), C.byref(hi),
+              C.byref(nch), 0, None, None, None)
+    return [offs[i] for i in range(n)], arena.value, lo.value, hi.value
+
+
+def _adam_worker(rank, world, port, ret):
+    sys.path.insert(0, ROOT)
+    import oracle
+    import workloads
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        wl = workloads.c5_ragged_adam(n_tensors=64, max_log2=14, seed=7)
+        h = wl.hyper
+        offsets, arena, lo, hi = _plan(wl.sizes, world, rank)
+        theta = np.zeros(arena, np.float32)
+        for o, p in zip(offsets, wl.make_params()):
+            theta[o:o + p.size] = p.reshape(-1)
+        # this rank's slice only: m, v exist for [lo, hi)
+        mine = theta[lo:hi]
+        opt = oracle.Adam([mine], h["lr"], h["betas"], h["eps"], h["weight_decay"])
+        for s in (1, 2, 3):
+            g = np.zeros(arena, np.float32)
+            for o, gi in zip(offsets, wl.make_grads(s)):
+                g[o:o + gi.size] = gi.reshape(-1)
+            opt.step([np.ascontiguousarray(g[lo:hi])])
+            # exchange: in-place all-gather of equal slices
+            t = torch.from_numpy(theta)
+            dist.all_gather_into_tensor(t, t[lo:hi].clone())
+        ret[rank] = theta.copy()
+    finally:
+        dist.destroy_process_group()
+
+
+def _free_port():
+    import socket
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _spawn(fn, world):
+    ctx = mp.get_context("spawn")
+    with ctx.Manager() as mgr:
+        ret = mgr.dict()
+        port = _free_port()
+        procs = [ctx.Process(target=fn, args=(r, world, port, ret)) for r in range(world)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(120)
+            assert p.exitcode == 0
+        return dict(ret)
+
+
+def test_zero1_adam_two_ranks_matches_unsharded():
+    import oracle
+    import workloads
+    res = _spawn(_adam_worker, 2)
+    wl = workloads.c5_ragged_adam(n_tensors=64, max_log2=14, seed=7)
+    h = wl.hyper
+    params = wl.make_params()
+    opt = oracle.Adam(params, h["lr"], h["betas"], h["eps"], h["weight_decay"])
+    for s in (1, 2, 3):
+        opt.step(wl.make_grads(s))
+    offsets, arena, _, _ = _plan(wl.sizes, 2, 0)
+    assert np.array_equal(res[0], res[1])
+    for o, p in zip(offsets, params):
+        assert np.array_equal(res[0][o:o + p.size].view(np.uint32), p.reshape(-1).view(np.uint32))
+
+
+def _muon_worker(rank, world, port, ret):
+    sys.path.insert(0, ROOT)
+    import oracle
+    from volta_b200 import _lib
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        shapes = [(48, 32), (32, 96), (64, 64), (40,), (16, 16)]
+        rows = (C.c_int64 * len(shapes))(*[oracle.muon_dims(s)[0] for s in shapes])
+        cols = (C.c_int64 * len(shapes))(*[oracle.muon_dims(s)[1] for s in shapes])
+        owners = (C.c_int32 * len(shapes))()
+        _lib.call("vb_plan_muon_owners", len(shapes), rows, cols, world, owners)
+        rng = np.random.default_rng(0)
+        params = [(rng.standard_normal(s) * 0.02).astype(np.float32) for s in shapes]
+        owned = [i for i in range(len(shapes)) if owners[i] == rank]
+        opt = oracle.Muon([params[i] for i in owned], 0.1, 0.9, True, 5)
+        for _ in range(2):
+            grads = [(rng.standard_normal(s) * 1e-3).astype(np.float32) for s in shapes]
+            opt.step([grads[i] for i in owned])
+            for i in range(len(shapes)):  # every matrix from its owner
+                t = torch.from_numpy(params[i])
+                dist.broadcast(t, src=int(owners[i]))
+        ret[rank] = ([p.copy() for p in params], list(owners))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_muon_ownership_two_ranks_matches_unsharded():
+    import oracle
+    res = _spawn(_muon_worker, 2)
+    shapes = [(48, 32), (32, 96), (64, 64), (40,), (16, 16)]
+    rng = np.random.default_rng(0)
+    params = [(rng.standard_normal(s) * 0.02).astype(np.float32) for s in shapes]
+    opt = oracle.Muon(params, 0.1, 0.9, True, 5)
+    for _ in range(2):
+        opt.step([(rng.standard_normal(s) * 1e-3).astype(np.float32) for s in shapes])
+    assert res[0][1] == res[1][1] and set(res[0][1]) == {0, 1}  # both ranks own something
+    for a, b, c in zip(res[0][0], res[1][0], params):
+        assert np.array_equal(a, b) and np.array_equal(a.view(np.uint32), c.view(np.uint32))
+
+
+def test_muon_owner_plan_balances_c4():
+    import workloads
+    from volta_b200 import _lib
+    wl = workloads.c4_muon()
+    n = len(wl.shapes)
+    rows = (C.c_int64 * n)(*[s[0] for s in wl.shapes])
+    cols = (C.c_int64 * n)(*[s[1] for s in wl.shapes])
+    for world in (2, 4, 8):
+        owners = (C.c_int32 * n)()
+        _lib.call("vb_plan_muon_owners", n, rows, cols, world, owners)
+        load = np.zeros(world)
+        for i, s in enumerate(wl.shapes):
+            load[owners[i]] += 4.0 * max(s) * min(s) ** 2
+        assert load.max() / load.mean() < 1.05

@@ -50,6 +50,7 @@ SIGNATURES = {
     "vb_device_count": [C.POINTER(C.c_int)],
     "vb_plan_layout": [_i64, _i64p, C.c_int, C.c_int, C.c_int, _i64p, _i64p, _i64p, _i64p, _i64p, _i64,
                        _i64p, _i64p, _i64p],
+    "vb_plan_muon_owners": [_i64, _i64p, _i64p, C.c_int, C.POINTER(C.c_int32)],
     "vb_engine_create": [C.c_int, _vpp],
     "vb_engine_destroy": [_vp],
     "vb_engine_synchronize": [_vp],

@@ -316,6 +316,19 @@ int vb_plan_layout(int64_t n_tensors, const int64_t *sizes, int world_size, int 
     VB_API_END
 }
 
+int vb_plan_muon_owners(int64_t n_tensors, const int64_t *rows, const int64_t *cols, int world_size,
+                        int32_t *owner_out)
+{
+    VB_API_BEGIN
+    if (n_tensors < 0 || world_size < 1) return fail(VB_ERR_INVALID_ARG, "n_tensors or world_size is not valid");
+    if (n_tensors > 0 && (!rows || !cols || !owner_out)) return fail(VB_ERR_INVALID_ARG, "null argument");
+    std::vector<int> owners((size_t)n_tensors);
+    plan_muon_owners(n_tensors, rows, cols, world_size, owners.data());
+    for (int64_t i = 0; i < n_tensors; ++i) owner_out[i] = owners[(size_t)i];
+    return VB_OK;
+    VB_API_END
+}
+
 int vb_engine_create(int device, vb_engine **out)
 {
     VB_API_BEGIN
