@@ -206,6 +206,20 @@ def run_ours(args):
         eng.synchronize()
 
     peaks = load_peaks()
+
+    def max_over_ranks(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    if args.only_muon:
+        muon = run_muon(args, eng, world, rank, dev, barrier, max_over_ranks, peaks)
+        if rank == 0:
+            print(json.dumps({"metric": "muon_ns_tflops", "muon": muon}), flush=True)
+        return 0
+
     wl = workloads.c3_transformer_adam()
     h = wl.hyper
     params = wl.make_params()
@@ -250,13 +264,6 @@ def run_ours(args):
     _, kernel_ms = timed_steps(args.steps, VB_STEP_NO_EXCHANGE, per_step=True)
     barrier()
     clocks = sampler.stop() if rank == 0 else None
-
-    def max_over_ranks(x):
-        if world == 1:
-            return x
-        t = torch.tensor([x], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
 
     total_ms = max_over_ranks(total_ms)
     kernel_avg_ms = max_over_ranks(sum(kernel_ms) / len(kernel_ms))
@@ -345,13 +352,13 @@ def run_muon(args, eng, world, rank, dev, barrier, max_over_ranks, peaks):
 
     from volta_b200 import VB_NS_BF16, VB_NS_F32, Muon, Tensor
 
-    wl = workloads.c4_muon()
+    wl = workloads.c4_muon(layers=args.muon_layers)
     h = wl.hyper
     params = wl.make_params()
     grads = wl.make_grads(1)
     out = {}
     for mode_name, mode, steps in (("bf16", VB_NS_BF16, max(3, min(args.steps, 20))), ("f32", VB_NS_F32, 2)):
-        if mode_name == "f32" and args.skip_muon_f32:
+        if mode_name == "f32" and (args.skip_muon_f32 or args.only_muon):
             continue
         tensors = [Tensor(p, p.shape) for p in params]
         opt = Muon(tensors, h["lr"], h["momentum"], h["nesterov"], h["ns_steps"], ns_mode=mode, engine=eng)
@@ -408,9 +415,10 @@ def run_muon(args, eng, world, rank, dev, barrier, max_over_ranks, peaks):
                 "frac_of_nominal_2250": tflops / (2250.0 * world), "traffic": None,
                 "kernel": "ns_gemm_tc_kernel (tcgen05 bf16, 10 launches per step)"}
         opt.close()
-    out["config"] = {"workload": "c4_muon: 96 matrices (24 x {3072x1024, 1024x1024, 4096x1024, 1024x4096}), "
-                                 "301989888 f32 params, lr=0.1 momentum=0.9 nesterov ns_steps=5"}
-    if world == 1 and not args.no_cpu_baseline:
+    out["config"] = {"workload": f"c4_muon: {len(wl.shapes)} matrices ({args.muon_layers} x {{3072x1024, 1024x1024, "
+                                 f"4096x1024, 1024x4096}}), {wl.total} f32 params, lr=0.1 momentum=0.9 nesterov "
+                                 "ns_steps=5"}
+    if world == 1 and not args.no_cpu_baseline and "bf16" in out:
         sec, fl = time_cpu_muon_sample(h["ns_steps"])
         ref_flops = out["bf16"]["reference_formulation_flops_per_step"]
         out["cpu_baseline"] = {"value": fl / sec / 1e12, "unit": "TFLOP/s", "cores": 1, "kind": "port",
@@ -441,6 +449,7 @@ def main():
     ap.add_argument("--skip-muon", action="store_true", help="Adam only")
     ap.add_argument("--skip-muon-f32", action="store_true", help="skip the (slow) f32 Newton-Schulz timing")
     ap.add_argument("--only-muon", action="store_true", help="profiling runs: Muon bf16 only")
+    ap.add_argument("--muon-layers", type=int, default=24, help="profiling runs: fewer layers of the Muon set")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
