@@ -635,27 +635,35 @@ int muon_init(vb_optimizer *opt)
             const int sh = std::min(r, c);
             __nv_bfloat16 *xb[2] = {s->d_xb[0] + s->local_off[(size_t)t], s->d_xb[1] + s->local_off[(size_t)t]};
             __nv_bfloat16 *cb = s->d_cb + cb_off[(size_t)t];
-            CUtensorMap map_x[2], map_c;
-            for (int par = 0; par < 2; ++par) VB_TRY(make_bf16_tensor_map(&map_x[par], xb[par], c, r));
-            VB_TRY(make_bf16_tensor_map(&map_c, cb, sh, sh));
+            // X is fetched K-major (rows = m or n) or MN-major (rows = k) depending on the product
+            const int mn_mode = tc_mn_major_mode(c);
+            CUtensorMap map_x_k[2], map_x_mn[2], map_c;
+            for (int par = 0; par < 2; ++par) {
+                VB_TRY(make_bf16_tensor_map(&map_x_k[par], xb[par], c, r, TC_OP_K_MAJOR));
+                VB_TRY(make_bf16_tensor_map(&map_x_mn[par], xb[par], c, r, mn_mode));
+            }
+            VB_TRY(make_bf16_tensor_map(&map_c, cb, sh, sh, TC_OP_K_MAJOR));
             const int pidx = (int)gram[0].size();
             for (int par = 0; par < 2; ++par) {
                 // C = 3I - X^T X (tall: both operands are X read with k = row index, "MN-major")
                 // C = 3I - X X^T (wide: both operands are X, K-major)
                 TcGemmProblem g{};
-                g.map_a = map_x[par]; g.map_b = map_x[par];
+                g.map_a = tall ? map_x_mn[par] : map_x_k[par];
+                g.map_b = g.map_a;
                 g.M = sh; g.N = sh; g.K = tall ? r : c;
-                g.a_mn_major = tall ? 1 : 0; g.b_mn_major = tall ? 1 : 0;
+                g.a_mode = tall ? mn_mode : TC_OP_K_MAJOR;
+                g.b_mode = g.a_mode;
                 g.epilogue = TC_EPI_THREE_I_MINUS; g.ld_out = sh; g.tensor = t;
                 g.out_bf16 = cb; g.out_f32 = nullptr;
                 gram[par].push_back(g);
                 // X' = 0.5 X C (tall: A = X K-major, B = C which is symmetric)
                 // X' = 0.5 C X (wide: A = C, B = X read with k = row index)
                 TcGemmProblem u{};
-                u.map_a = tall ? map_x[par] : map_c;
-                u.map_b = tall ? map_c : map_x[par];
+                u.map_a = tall ? map_x_k[par] : map_c;
+                u.map_b = tall ? map_c : map_x_mn[par];
                 u.M = r; u.N = c; u.K = sh;
-                u.a_mn_major = 0; u.b_mn_major = tall ? 0 : 1;
+                u.a_mode = TC_OP_K_MAJOR;
+                u.b_mode = tall ? TC_OP_K_MAJOR : mn_mode;
                 u.epilogue = TC_EPI_HALF; u.ld_out = c; u.tensor = t;
                 u.out_bf16 = xb[par ^ 1]; u.out_f32 = nullptr;
                 upd[par].push_back(u);

@@ -35,14 +35,20 @@ struct F32GemmProblem {
 
 enum TcEpilogue { TC_EPI_THREE_I_MINUS = 0, TC_EPI_HALF = 1 };
 
+// How an operand of the tensor-core GEMM is laid out in memory and fetched by TMA.
+enum TcOperandMode {
+    TC_OP_K_MAJOR = 0,   // row-major [rows][k]: rows indexed by m (or n)
+    TC_OP_MN_BOXES = 1,  // row-major [k][rows]: rows indexed by k ("MN-major"), fetched as 64 x 64 boxes
+    TC_OP_MN_3D = 2      // the same, fetched through a 3-D view (row length a multiple of 64)
+};
+
 // D[M,N] = epilogue( sum_k A[m,k] * B[n,k] ) on the tensor cores, bf16 operands.
-// Each operand is a row-major bf16 matrix described by a TMA tensor map; it is "K-major"
-// when its rows are indexed by m (or n) and "MN-major" when its rows are indexed by k.
+// Each operand is a row-major bf16 matrix described by a TMA tensor map built for its mode.
 struct alignas(128) TcGemmProblem {
     CUtensorMap map_a;
     CUtensorMap map_b;
     int32_t M, N, K;
-    int32_t a_mn_major, b_mn_major;
+    int32_t a_mode, b_mode;  // TcOperandMode
     int32_t epilogue;
     int32_t ld_out;
     int32_t tensor;          // index into the optimizer's gradient-presence bytes
@@ -53,7 +59,8 @@ struct alignas(128) TcGemmProblem {
 int launch_ns_gemm_tc(const TcGemmProblem *d_problems, const GemmTile *d_tiles, int n_tiles,
                       const uint8_t *d_present, int *d_error_flag, int sm_count, cudaStream_t stream);
 void tc_gemm_tile_shape(int *bm, int *bn);
-int make_bf16_tensor_map(void *map_out, const void *base, int64_t inner, int64_t outer);
+int make_bf16_tensor_map(void *map_out, const void *base, int64_t inner, int64_t outer, int mode);
+int tc_mn_major_mode(int64_t inner);
 
 int launch_ns_gemm_f32(const F32GemmProblem *d_problems, const GemmTile *d_tiles, int n_tiles,
                        const uint8_t *d_present, int sm_count, cudaStream_t stream);

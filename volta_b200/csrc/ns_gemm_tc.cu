@@ -12,16 +12,31 @@
 // operand, f32 copy of the final update) are fused into the epilogues.
 //
 // One persistent launch handles one contraction of every matrix: a tile list
-// (problem, m0, n0) is walked by 148 CTAs.  Each CTA is warp specialised:
-//   warp 0     TMA producer  (kStages-deep ring of {A 128x64, B 256x64} bf16 tiles)
-//   warp 1     MMA issuer    (one thread; 4 x tcgen05.mma 128x256x16 per ring slot)
-//   warps 2-5  epilogue      (TMEM -> registers -> global), overlapped with the next tile's
-//                             main loop through two TMEM accumulator buffers
+// (problem, m0, n0) is walked by the whole GPU.  The kernel is warp specialised:
+//   warp 0     TMA producer  (ring of {A 128 x 64, B rows x 64} bf16 slots)
+//   warp 1     MMA issuer    (one thread; 4 x tcgen05.mma ...x16 per ring slot)
+//   warps 2-9  epilogue      (TMEM -> registers -> global), overlapped with the next tile's
+//                             main loop through two TMEM accumulator buffers.  Warp w reads
+//                             lane quarter w % 4 and half of the 256 columns, one 32-column
+//                             tcgen05.ld ahead of the stores, 256-bit global stores
+//
+// Two shapes of the same kernel (template parameter kCtas):
+//   kCtas = 2 (default)  a cluster of two CTAs -- the two SMs of a TPC -- computes a 256 x 256
+//       tile with tcgen05.mma.cta_group::2.  Each CTA stages its own 128 rows of A and its own
+//       128 rows of B (32 KiB per slot, 6 slots) and keeps its 128 x 256 half of the
+//       accumulator in its own TMEM.  The leader CTA issues the MMAs; both producers credit
+//       their bytes to the leader's `full` barrier (loads carry .cta_group::2; every CTA
+//       fetches its own rows, no load is shared between CTAs); tcgen05.commit with
+//       .multicast::cluster frees ring slots and publishes accumulators in both CTAs; the
+//       peer's epilogue warps arrive remotely on the leader's `tmem_empty`.
+//   kCtas = 1            one CTA per 128 x 256 tile (48 KiB per slot, 4 slots).  It needs 1.5x
+//       the shared-memory fill traffic per FLOP and is limited by it (measured 0.85 vs 1.0+
+//       PFLOP/s); kept selectable (VB_TC_ONE_CTA=1) for comparison.
+//
 // Every mbarrier wait is bounded: on expiry the CTA raises an abort flag that all roles
 // poll, records an error code for the host, releases its TMEM and returns.
 #include <cuda.h>
 #include <cuda_bf16.h>
-
 #include <stdlib.h>
 
 #include "ns_gemm.h"
@@ -30,31 +45,41 @@ namespace vb {
 
 namespace {
 
-constexpr int BM = 128;
-constexpr int BN = 256;
+constexpr int BM = 128;           // rows of A per CTA
+constexpr int BN = 256;           // tile columns
 constexpr int BK = 64;            // bf16 elements = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
-constexpr int kStages = 4;
-constexpr int kBoxRows = 64;      // every TMA box is 64 x 64 bf16 = 8 KiB
-constexpr int kBoxBytes = kBoxRows * BK * 2;
-constexpr int kABytes = BM * BK * 2;                    // 16 KiB
-constexpr int kBBytes = BN * BK * 2;                    // 32 KiB
-constexpr int kStageBytes = kABytes + kBBytes;          // 48 KiB
-constexpr int kAccCols = BN;                            // f32 columns per accumulator
-constexpr int kTmemCols = 2 * kAccCols;                 // 512: two accumulators
-constexpr int kThreads = 192;
-constexpr int kEpiWarps = 4;
-constexpr uint32_t kWaitLimit = 1u << 22;               // mbarrier polls before giving up
+constexpr int kBoxRows = 64;
+constexpr int kBoxBytes = kBoxRows * BK * 2;             // 8 KiB: a 64 x 64 bf16 box
+constexpr int kRows128Bytes = 128 * BK * 2;              // 16 KiB: 128 operand rows of one slot
+constexpr int kAccCols = BN;                             // f32 columns per accumulator
+constexpr int kTmemCols = 2 * kAccCols;                  // 512: two accumulators
+constexpr int kEpiWarps = 8;                             // two per TMEM lane quarter, 128 columns each
+constexpr int kThreads = 64 + kEpiWarps * 32;            // producer warp + MMA warp + epilogue warps
+constexpr uint32_t kWaitLimit = 1u << 22;                // mbarrier polls before giving up
 
+template <int kCtas>
+struct Cfg {
+    static constexpr int kStages = kCtas == 2 ? 6 : 4;
+    static constexpr int kBRows = BN / kCtas;                         // rows of B staged by one CTA
+    static constexpr int kStageBytes = kRows128Bytes + kBRows * BK * 2;
+    static constexpr int kTileM = BM * kCtas;
+};
+
+template <int kCtas>
 struct alignas(8) Barriers {
-    uint64_t full[kStages];
-    uint64_t empty[kStages];
+    uint64_t full[Cfg<kCtas>::kStages];
+    uint64_t empty[Cfg<kCtas>::kStages];
     uint64_t tmem_full[2];
     uint64_t tmem_empty[2];
     uint32_t tmem_base;
     uint32_t abort;
 };
-constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + (size_t)kStages * kStageBytes + sizeof(Barriers);
+template <int kCtas>
+constexpr size_t smem_bytes()
+{
+    return 1024 /*alignment slack*/ + (size_t)Cfg<kCtas>::kStages * Cfg<kCtas>::kStageBytes + sizeof(Barriers<kCtas>);
+}
 
 // ---- PTX wrappers -------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -71,6 +96,10 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes)
 __device__ __forceinline__ void mbar_arrive(uint64_t *bar)
 {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_remote_arrive(uint32_t cluster_addr)
+{
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
 {
@@ -93,29 +122,129 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
     }
     return false;
 }
-__device__ __forceinline__ void tma_load_2d(void *smem_dst, const CUtensorMap *map, int c0, int c1, uint64_t *bar)
+
+// Compile-time diagnostic (-DVB_TC_TIMING): cycles the first CTA pair spends in each kind of
+// wait, accumulated in g_wait_cycles[site + 4 * (blockIdx.x & 1)]; not built by default.
+#ifdef VB_TC_TIMING
+__device__ unsigned long long g_wait_cycles[16];
+__device__ __forceinline__ bool mbar_wait_timed(int site, uint64_t *bar, uint32_t parity, volatile uint32_t *abort_flag)
 {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(smem_u32(bar))
-        : "memory");
+    const long long t0 = clock64();
+    const bool ok = mbar_wait(bar, parity, abort_flag);
+    if (blockIdx.x < 2) atomicAdd(&g_wait_cycles[site + 4 * (blockIdx.x & 1)], (unsigned long long)(clock64() - t0));
+    return ok;
 }
+#define MBAR_WAIT(site, bar, parity) mbar_wait_timed(site, bar, parity, abort_flag)
+#else
+#define MBAR_WAIT(site, bar, parity) mbar_wait(bar, parity, abort_flag)
+#endif
+
+__device__ __forceinline__ uint32_t cluster_ctarank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of `local` (an address in this CTA's shared memory) in CTA `rank`
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local, uint32_t rank)
+{
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
+    return r;
+}
+
+// TMA loads into this CTA's shared memory.  `bar` is a shared::cluster address: this CTA's own
+// barrier, or (kCtas == 2, .cta_group::2) the leader's.  Every CTA fetches its own rows.
+template <int kCtas>
+__device__ __forceinline__ void tma_load_2d(void *smem_dst, const CUtensorMap *map, int c0, int c1, uint32_t bar)
+{
+    if (kCtas == 2)
+        asm volatile(
+            "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+            "[%0], [%1, {%2, %3}], [%4];"
+            ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(bar)
+            : "memory");
+    else
+        asm volatile(
+            "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+            ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(bar)
+            : "memory");
+}
+template <int kCtas>
+__device__ __forceinline__ void tma_load_3d(void *smem_dst, const CUtensorMap *map, int c0, int c1, int c2,
+                                            uint32_t bar)
+{
+    if (kCtas == 2)
+        asm volatile(
+            "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+            "[%0], [%1, {%2, %3, %4}], [%5];"
+            ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
+            : "memory");
+    else
+        asm volatile(
+            "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes "
+            "[%0], [%1, {%2, %3, %4}], [%5];"
+            ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
+            : "memory");
+}
+// Stages 128 operand rows x 64 k (16 KiB) with as few TMA instructions as the layout allows:
+// the issuing thread is the scarce resource (every instruction costs it a few hundred cycles).
+//   TC_OP_K_MAJOR   one 64 x 128 box of a [rows][k] matrix
+//   TC_OP_MN_BOXES  two 64 x 64 boxes of a [k][rows] matrix (any row count)
+//   TC_OP_MN_3D     one 64 x 64 x 2 box of the same matrix viewed as [rows/64][k][64]
+// All three leave the same image in shared memory.
+template <int kCtas>
+__device__ __forceinline__ void load_rows128(uint8_t *dst, const CUtensorMap *map, int mode, int row0, int k0,
+                                             uint32_t bar)
+{
+    if (mode == TC_OP_K_MAJOR) {
+        tma_load_2d<kCtas>(dst, map, k0, row0, bar);
+    } else if (mode == TC_OP_MN_3D) {
+        tma_load_3d<kCtas>(dst, map, 0, k0, row0 >> 6, bar);
+    } else {
+        tma_load_2d<kCtas>(dst, map, row0, k0, bar);
+        tma_load_2d<kCtas>(dst + kBoxBytes, map, row0 + kBoxRows, k0, bar);
+    }
+}
+
 __device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// Arrive on `bar` (same offset in every CTA of the group) once all MMAs issued so far are done.
+template <int kCtas>
 __device__ __forceinline__ void tcgen05_commit(uint64_t *bar)
 {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-                 : "memory");
+    if (kCtas == 2)
+        asm volatile(
+            "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+            ::"r"(smem_u32(bar)), "h"((uint16_t)3)
+            : "memory");
+    else
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                     : "memory");
 }
+template <int kCtas>
 __device__ __forceinline__ void tcgen05_mma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
                                                  uint32_t accumulate)
 {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-        : "memory");
+    if (kCtas == 2)
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+            : "memory");
+    else
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+            : "memory");
 }
 __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&v)[32])
 {
@@ -143,19 +272,36 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_
     d |= (uint64_t)2 << 61;  // SWIZZLE_128B
     return d;
 }
+// Descriptor of the 16-wide k slice `kk` of a staged operand.
+//   K-major : rows of 128 bytes, 8-row groups 1 KiB apart; 16 bf16 = 32 bytes along the row.
+//   MN-major: [k][64 rows] blocks of 8 KiB; 8-k groups 1 KiB apart (SBO), 64-row blocks 8 KiB
+//             apart (LBO); 16 k = 2 KiB further down the block.
+__device__ __forceinline__ uint64_t operand_desc(uint32_t base, int mode, int kk)
+{
+    return mode == TC_OP_K_MAJOR ? make_smem_desc(base + kk * 32, 16, 1024)
+                                 : make_smem_desc(base + kk * 2048, kBoxBytes, 1024);
+}
 
 // Instruction descriptor for kind::f16 with bf16 operands and f32 accumulation.
-__device__ __forceinline__ uint32_t make_idesc(int a_mn_major, int b_mn_major)
+__device__ __forceinline__ uint32_t make_idesc(int a_mode, int b_mode, int m)
 {
     uint32_t d = 0;
     d |= 1u << 4;                    // D format: f32
     d |= 1u << 7;                    // A format: bf16
     d |= 1u << 10;                   // B format: bf16
-    d |= (uint32_t)(a_mn_major & 1) << 15;
-    d |= (uint32_t)(b_mn_major & 1) << 16;
+    d |= (uint32_t)(a_mode != TC_OP_K_MAJOR) << 15;  // A is MN-major
+    d |= (uint32_t)(b_mode != TC_OP_K_MAJOR) << 16;  // B is MN-major
     d |= (uint32_t)(BN >> 3) << 17;  // N
-    d |= (uint32_t)(BM >> 4) << 24;  // M
+    d |= (uint32_t)(m >> 4) << 24;   // M (across the CTA group)
     return d;
+}
+
+// One 32-byte (sector-sized) global store.  The address must be 32-byte aligned.
+__device__ __forceinline__ void st_global_256(void *p, const uint32_t (&q)[8])
+{
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(q[0]), "r"(q[1]), "r"(q[2]),
+                 "r"(q[3]), "r"(q[4]), "r"(q[5]), "r"(q[6]), "r"(q[7])
+                 : "memory");
 }
 
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b)
@@ -164,76 +310,118 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b)
     return *reinterpret_cast<uint32_t *>(&h);
 }
 
+// What a role needs to know about a tile, fetched one tile ahead so that the dependent global
+// loads (tile -> problem -> fields) never sit between two tiles' main loops.
+struct TileInfo {
+    const TcGemmProblem *p;
+    int m0, n0, k_blocks, a_mode, b_mode;
+    bool skipped;  // gradient absent: nothing to do
+};
+__device__ __forceinline__ TileInfo fetch_tile(const TcGemmProblem *problems, const GemmTile *tiles, int n_tiles,
+                                               const uint8_t *present, int t)
+{
+    TileInfo ti;
+    ti.p = problems;
+    ti.m0 = ti.n0 = ti.k_blocks = ti.a_mode = ti.b_mode = 0;
+    ti.skipped = true;
+    if (t < n_tiles) {
+        const GemmTile tile = tiles[t];
+        const TcGemmProblem *p = problems + tile.problem;
+        ti.p = p;
+        ti.m0 = tile.m0;
+        ti.n0 = tile.n0;
+        ti.k_blocks = (p->K + BK - 1) / BK;
+        ti.a_mode = p->a_mode;
+        ti.b_mode = p->b_mode;
+        ti.skipped = present[p->tensor] == 0;
+    }
+    return ti;
+}
+
+template <int kCtas>
 __global__ void __launch_bounds__(kThreads, 1)
 ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__restrict__ tiles, int n_tiles,
                   const uint8_t *__restrict__ present, int *__restrict__ error_flag)
 {
+    using C = Cfg<kCtas>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    Barriers *bars = reinterpret_cast<Barriers *>(smem + (size_t)kStages * kStageBytes);
+    Barriers<kCtas> *bars = reinterpret_cast<Barriers<kCtas> *>(smem + (size_t)C::kStages * C::kStageBytes);
     volatile uint32_t *abort_flag = &bars->abort;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    const uint32_t cta_rank = kCtas == 2 ? cluster_ctarank() : 0u;  // 0 = leader
+    const int group_id = blockIdx.x / kCtas;                        // CTA pair (or CTA) index
+    const int n_groups = gridDim.x / kCtas;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) {
-            mbar_init(&bars->full[s], 1);
-            mbar_init(&bars->empty[s], 1);
+        for (int s = 0; s < C::kStages; ++s) {
+            mbar_init(&bars->full[s], 1);   // the (leader's) producer arrives; bytes come from every CTA
+            mbar_init(&bars->empty[s], 1);  // one commit from the MMA thread
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(&bars->tmem_full[a], 1);
-            mbar_init(&bars->tmem_empty[a], kEpiWarps);
+            mbar_init(&bars->tmem_empty[a], kCtas * kEpiWarps);  // epilogue warps of every CTA of the group
         }
         bars->abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) {  // TMEM allocation is warp-wide
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
-                         smem_u32(&bars->tmem_base)),
-                     "r"((uint32_t)kTmemCols)
-                     : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (warp == 1) {  // TMEM allocation is warp-wide; with two CTAs the same warp of both allocates
+        if (kCtas == 2) {
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                             smem_u32(&bars->tmem_base)),
+                         "r"((uint32_t)kTmemCols)
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                             smem_u32(&bars->tmem_base)),
+                         "r"((uint32_t)kTmemCols)
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     tcgen05_fence_before();
     __syncthreads();
+    if (kCtas == 2) cluster_sync_all();  // the peer's barriers exist before anything signals them
     tcgen05_fence_after();
     const uint32_t tmem_base = bars->tmem_base;
 
     if (warp == 0) {
-        // ---------------- TMA producer ----------------
+        // ---------------- TMA producer (every CTA) ----------------
         if (lane == 0) {
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
-                const GemmTile tile = tiles[t];
-                const TcGemmProblem *p = problems + tile.problem;
-                if (present[p->tensor] == 0) continue;
-                const int k_blocks = (p->K + BK - 1) / BK;
-                const int a_mn = p->a_mn_major, b_mn = p->b_mn_major;
-                for (int kb = 0; kb < k_blocks; ++kb) {
-                    if (!mbar_wait(&bars->empty[stage], phase ^ 1u, abort_flag)) {
+            TileInfo next = fetch_tile(problems, tiles, n_tiles, present, group_id);
+            for (int t = group_id; t < n_tiles && ok; t += n_groups) {
+                const TileInfo ti = next;
+                next = fetch_tile(problems, tiles, n_tiles, present, t + n_groups);
+                if (ti.skipped) continue;
+                const int a_row0 = ti.m0 + (int)cta_rank * BM;         // this CTA's rows of A
+                const int b_row0 = ti.n0 + (int)cta_rank * C::kBRows;  // this CTA's rows of B
+                for (int kb = 0; kb < ti.k_blocks; ++kb) {
+                    if (!MBAR_WAIT(0, &bars->empty[stage], phase ^ 1u)) {
                         ok = false;
                         break;
                     }
-                    uint8_t *sa = smem + (size_t)stage * kStageBytes;
-                    uint8_t *sb = sa + kABytes;
-                    mbar_expect_tx(&bars->full[stage], kStageBytes);
+                    uint8_t *sa = smem + (size_t)stage * C::kStageBytes;
+                    uint8_t *sb = sa + kRows128Bytes;
+                    // Only the leader posts the expected byte count (for all CTAs' loads): a remote
+                    // arrive from the peer would put a cluster round trip into every ring slot.
+                    // The peer's bytes may land before the leader's expect_tx; the phase cannot
+                    // complete until the leader has arrived.
+                    const uint32_t full_bar =
+                        kCtas == 2 ? map_to_cta(smem_u32(&bars->full[stage]), 0) : smem_u32(&bars->full[stage]);
+                    if (cta_rank == 0) mbar_expect_tx(&bars->full[stage], kCtas * C::kStageBytes);
                     const int k0 = kb * BK;
+                    load_rows128<kCtas>(sa, &ti.p->map_a, ti.a_mode, a_row0, k0, full_bar);
 #pragma unroll
-                    for (int j = 0; j < BM / kBoxRows; ++j) {
-                        const int r0 = tile.m0 + j * kBoxRows;
-                        if (a_mn) tma_load_2d(sa + j * kBoxBytes, &p->map_a, r0, k0, &bars->full[stage]);
-                        else      tma_load_2d(sa + j * kBoxBytes, &p->map_a, k0, r0, &bars->full[stage]);
-                    }
-#pragma unroll
-                    for (int j = 0; j < BN / kBoxRows; ++j) {
-                        const int r0 = tile.n0 + j * kBoxRows;
-                        if (b_mn) tma_load_2d(sb + j * kBoxBytes, &p->map_b, r0, k0, &bars->full[stage]);
-                        else      tma_load_2d(sb + j * kBoxBytes, &p->map_b, k0, r0, &bars->full[stage]);
-                    }
-                    if (++stage == kStages) {
+                    for (int j = 0; j < C::kBRows / 128; ++j)
+                        load_rows128<kCtas>(sb + j * kRows128Bytes, &ti.p->map_b, ti.b_mode, b_row0 + j * 128, k0,
+                                            full_bar);
+                    if (++stage == C::kStages) {
                         stage = 0;
                         phase ^= 1u;
                     }
@@ -246,53 +434,46 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
         }
         __syncwarp();
     } else if (warp == 1) {
-        // ---------------- MMA issuer ----------------
-        if (lane == 0) {
+        // ---------------- MMA issuer (leader CTA only) ----------------
+        if (lane == 0 && cta_rank == 0) {
             int stage = 0;
             uint32_t phase = 0;
             int acc = 0;
             uint32_t acc_phase = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
-                const GemmTile tile = tiles[t];
-                const TcGemmProblem *p = problems + tile.problem;
-                if (present[p->tensor] == 0) continue;
-                const int k_blocks = (p->K + BK - 1) / BK;
-                const int a_mn = p->a_mn_major, b_mn = p->b_mn_major;
-                const uint32_t idesc = make_idesc(a_mn, b_mn);
-                // the epilogue must have drained this accumulator
-                if (!mbar_wait(&bars->tmem_empty[acc], acc_phase ^ 1u, abort_flag)) {
+            TileInfo next = fetch_tile(problems, tiles, n_tiles, present, group_id);
+            for (int t = group_id; t < n_tiles && ok; t += n_groups) {
+                const TileInfo ti = next;
+                next = fetch_tile(problems, tiles, n_tiles, present, t + n_groups);
+                if (ti.skipped) continue;
+                const uint32_t idesc = make_idesc(ti.a_mode, ti.b_mode, C::kTileM);
+                // the epilogue(s) must have drained this accumulator
+                if (!MBAR_WAIT(1, &bars->tmem_empty[acc], acc_phase ^ 1u)) {
                     ok = false;
                     break;
                 }
                 tcgen05_fence_after();
                 const uint32_t tmem_d = tmem_base + (uint32_t)(acc * kAccCols);
-                for (int kb = 0; kb < k_blocks; ++kb) {
-                    if (!mbar_wait(&bars->full[stage], phase, abort_flag)) {
+                for (int kb = 0; kb < ti.k_blocks; ++kb) {
+                    if (!MBAR_WAIT(2, &bars->full[stage], phase)) {
                         ok = false;
                         break;
                     }
                     tcgen05_fence_after();
-                    const uint32_t sa = smem_u32(smem + (size_t)stage * kStageBytes);
-                    const uint32_t sb = sa + kABytes;
+                    const uint32_t sa = smem_u32(smem + (size_t)stage * C::kStageBytes);
+                    const uint32_t sb = sa + kRows128Bytes;
 #pragma unroll
-                    for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-                        // K-major: 16 bf16 = 32 bytes further along the swizzled 128-byte row.
-                        // MN-major: 16 k-rows = two 8-row groups of 1 KiB further down the box.
-                        const uint64_t da = a_mn ? make_smem_desc(sa + kk * 2048, kBoxBytes, 1024)
-                                                 : make_smem_desc(sa + kk * 32, 16, 1024);
-                        const uint64_t db = b_mn ? make_smem_desc(sb + kk * 2048, kBoxBytes, 1024)
-                                                 : make_smem_desc(sb + kk * 32, 16, 1024);
-                        tcgen05_mma_bf16(tmem_d, da, db, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
-                    }
-                    tcgen05_commit(&bars->empty[stage]);  // slot reusable once these MMAs have read it
-                    if (++stage == kStages) {
+                    for (int kk = 0; kk < BK / UMMA_K; ++kk)
+                        tcgen05_mma_bf16<kCtas>(tmem_d, operand_desc(sa, ti.a_mode, kk), operand_desc(sb, ti.b_mode, kk),
+                                                idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+                    tcgen05_commit<kCtas>(&bars->empty[stage]);  // slot reusable once these MMAs have read it
+                    if (++stage == C::kStages) {
                         stage = 0;
                         phase ^= 1u;
                     }
                 }
                 if (!ok) break;
-                tcgen05_commit(&bars->tmem_full[acc]);  // accumulator complete
+                tcgen05_commit<kCtas>(&bars->tmem_full[acc]);  // accumulator complete (in every CTA)
                 if (++acc == 2) {
                     acc = 0;
                     acc_phase ^= 1u;
@@ -305,65 +486,93 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
         }
         __syncwarp();
     } else {
-        // ---------------- epilogue (warps 2..5) ----------------
-        const int quarter = warp & 3;  // the TMEM lane quarter this warp may read
+        // ---------------- epilogue (warps 2..9 of every CTA) ----------------
+        const int quarter = warp & 3;          // the TMEM lane quarter this warp may read
+        const int col_half = (warp - 2) >> 2;  // which 128 of the 256 accumulator columns
+        constexpr int kChunks = (BN / 2) / 32;
         int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
-        for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
-            const GemmTile tile = tiles[t];
-            const TcGemmProblem *p = problems + tile.problem;
-            if (present[p->tensor] == 0) continue;
+        TileInfo next = fetch_tile(problems, tiles, n_tiles, present, group_id);
+        for (int t = group_id; t < n_tiles && ok; t += n_groups) {
+            const TileInfo ti = next;
+            next = fetch_tile(problems, tiles, n_tiles, present, t + n_groups);
+            if (ti.skipped) continue;
+            const TcGemmProblem *p = ti.p;
             const int M = p->M, N = p->N;
             const int epi = p->epilogue;
             __nv_bfloat16 *out_bf16 = p->out_bf16;
             float *out_f32 = p->out_f32;
             const int64_t ld = p->ld_out;
-            if (!mbar_wait(&bars->tmem_full[acc], acc_phase, abort_flag)) {
+            const bool bf16_rows_32b = (ld % 16) == 0;  // every bf16 output row starts on a 32-byte boundary
+            if (!MBAR_WAIT(3, &bars->tmem_full[acc], acc_phase)) {
                 ok = false;
                 break;
             }
             tcgen05_fence_after();
-            const int row = tile.m0 + quarter * 32 + lane;
-            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * kAccCols);
-#pragma unroll 1
-            for (int cc = 0; cc < BN / 32; ++cc) {
-                const int col0 = tile.n0 + cc * 32;
+            const int row = ti.m0 + (int)cta_rank * BM + quarter * 32 + lane;
+            const int tile_col0 = ti.n0 + col_half * (BN / 2);
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) +
+                                   (uint32_t)(acc * kAccCols + col_half * (BN / 2));
+            uint32_t v[2][32];
+            if (tile_col0 < N) tmem_ld_32x32(taddr, v[0]);
+#pragma unroll
+            for (int cc = 0; cc < kChunks; ++cc) {
+                const int col0 = tile_col0 + cc * 32;
                 if (col0 >= N) break;  // uniform across the warp
-                uint32_t v[32];
-                tmem_ld_32x32(taddr + (uint32_t)(cc * 32), v);
                 tmem_ld_wait();
+                if (cc + 1 < kChunks && col0 + 32 < N) tmem_ld_32x32(taddr + (uint32_t)((cc + 1) * 32), v[(cc + 1) & 1]);
                 if (row < M) {
                     float f[32];
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
-                        const float a = __uint_as_float(v[j]);
+                        const float a = __uint_as_float(v[cc & 1][j]);
                         if (epi == TC_EPI_THREE_I_MINUS) f[j] = (row == col0 + j) ? 3.0f - a : -a;  // muon.rs:76-89
                         else f[j] = 0.5f * a;                                                       // muon.rs:95-99
                     }
+                    if (out_bf16) {
+                        __nv_bfloat16 *dst = out_bf16 + (int64_t)row * ld + col0;
 #pragma unroll
-                    for (int g8 = 0; g8 < 4; ++g8) {  // groups of 8 columns: N is a multiple of 8
-                        const int col = col0 + g8 * 8;
-                        if (col >= N) break;
-                        if (out_bf16) {
-                            uint4 q;
-                            q.x = pack_bf16(f[g8 * 8 + 0], f[g8 * 8 + 1]);
-                            q.y = pack_bf16(f[g8 * 8 + 2], f[g8 * 8 + 3]);
-                            q.z = pack_bf16(f[g8 * 8 + 4], f[g8 * 8 + 5]);
-                            q.w = pack_bf16(f[g8 * 8 + 6], f[g8 * 8 + 7]);
-                            *reinterpret_cast<uint4 *>(out_bf16 + (int64_t)row * ld + col) = q;
+                        for (int g16 = 0; g16 < 2; ++g16) {  // 16 columns = one 32-byte sector per store
+                            const int col = col0 + g16 * 16;
+                            if (col + 16 <= N && bf16_rows_32b) {
+                                uint32_t q[8];
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) q[j] = pack_bf16(f[g16 * 16 + 2 * j], f[g16 * 16 + 2 * j + 1]);
+                                st_global_256(dst + g16 * 16, q);
+                            } else {  // 16-byte pieces (N and ld are multiples of 8)
+#pragma unroll
+                                for (int h = 0; h < 2; ++h) {
+                                    if (col + h * 8 >= N) break;
+                                    uint4 q;
+                                    q.x = pack_bf16(f[g16 * 16 + h * 8 + 0], f[g16 * 16 + h * 8 + 1]);
+                                    q.y = pack_bf16(f[g16 * 16 + h * 8 + 2], f[g16 * 16 + h * 8 + 3]);
+                                    q.z = pack_bf16(f[g16 * 16 + h * 8 + 4], f[g16 * 16 + h * 8 + 5]);
+                                    q.w = pack_bf16(f[g16 * 16 + h * 8 + 6], f[g16 * 16 + h * 8 + 7]);
+                                    *reinterpret_cast<uint4 *>(dst + g16 * 16 + h * 8) = q;
+                                }
+                            }
                         }
-                        if (out_f32) {
-                            float4 *dst = reinterpret_cast<float4 *>(out_f32 + (int64_t)row * ld + col);
-                            dst[0] = make_float4(f[g8 * 8 + 0], f[g8 * 8 + 1], f[g8 * 8 + 2], f[g8 * 8 + 3]);
-                            dst[1] = make_float4(f[g8 * 8 + 4], f[g8 * 8 + 5], f[g8 * 8 + 6], f[g8 * 8 + 7]);
+                    }
+                    if (out_f32) {
+                        float *dst = out_f32 + (int64_t)row * ld + col0;
+#pragma unroll
+                        for (int g8 = 0; g8 < 4; ++g8) {  // 8 columns = one 32-byte sector per store
+                            if (col0 + g8 * 8 >= N) break;
+                            uint32_t q[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) q[j] = __float_as_uint(f[g8 * 8 + j]);
+                            st_global_256(dst + g8 * 8, q);
                         }
                     }
                 }
             }
             tcgen05_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&bars->tmem_empty[acc]);
+            if (lane == 0) {
+                if (kCtas == 2) mbar_remote_arrive(map_to_cta(smem_u32(&bars->tmem_empty[acc]), 0));
+                else mbar_arrive(&bars->tmem_empty[acc]);
+            }
             if (++acc == 2) {
                 acc = 0;
                 acc_phase ^= 1u;
@@ -381,341 +590,22 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
     __syncthreads();
     if (bars->abort != 0 && threadIdx.x == 0) {
         // give copies that may still be in flight a bounded time to land before smem is released
-        for (int s = 0; s < kStages; ++s)
+        for (int s = 0; s < C::kStages; ++s)
             for (uint32_t i = 0; i < 4096u; ++i)
                 if (mbar_try_wait(&bars->full[s], 0) || mbar_try_wait(&bars->full[s], 1)) break;
     }
     __syncthreads();
+    if (kCtas == 2) cluster_sync_all();  // neither CTA leaves while its peer may still signal it or read its operands
     if (warp == 1) {
         tcgen05_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)kTmemCols)
-                     : "memory");
-    }
-}
-
-// =============================================================================================
-// Two-CTA variant: a cluster of two CTAs (the two SMs of a TPC) computes one 256 x 256 tile with
-// tcgen05.mma.cta_group::2.  Each CTA stages its own 128 rows of A and its own 128 rows of B
-// (32 KiB per ring slot instead of 48 KiB for half as many FLOPs again), which cuts the
-// L2 -> shared-memory traffic per FLOP by a third -- the limiter of the one-CTA kernel -- and
-// holds its own 128 x 256 half of the accumulator in its TMEM.
-//   * the MMA is issued by the leader CTA (cluster rank 0) only;
-//   * both producers credit their bytes to the leader's `full` barrier (loads carry
-//     .cta_group::2; every CTA fetches its own rows, no load is shared between CTAs);
-//   * tcgen05.commit with .multicast::cluster releases ring slots / publishes accumulators to
-//     both CTAs; the peer's epilogue warps arrive remotely on the leader's `tmem_empty`.
-// =============================================================================================
-constexpr int BM2 = 256;               // cluster tile rows (128 per CTA)
-constexpr int kStages2 = 6;
-constexpr int kBHalfBytes = (BN / 2) * BK * 2;           // 16 KiB: this CTA's half of B
-constexpr int kStageBytes2 = kABytes + kBHalfBytes;      // 32 KiB
-struct alignas(8) Barriers2 {
-    uint64_t full[kStages2];
-    uint64_t empty[kStages2];
-    uint64_t tmem_full[2];
-    uint64_t tmem_empty[2];
-    uint32_t tmem_base;
-    uint32_t abort;
-};
-constexpr size_t kSmemBytes2 = 1024 + (size_t)kStages2 * kStageBytes2 + sizeof(Barriers2);
-
-__device__ __forceinline__ uint32_t cluster_ctarank()
-{
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-__device__ __forceinline__ void cluster_sync_all()
-{
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// shared::cluster address of `local` (an address in this CTA's shared memory) in CTA `rank`
-__device__ __forceinline__ uint32_t map_to_cta(uint32_t local, uint32_t rank)
-{
-    uint32_t r;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
-    return r;
-}
-__device__ __forceinline__ void mbar_remote_expect_tx(uint32_t cluster_addr, uint32_t bytes)
-{
-    asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_addr),
-                 "r"(bytes)
-                 : "memory");
-}
-__device__ __forceinline__ void mbar_remote_arrive(uint32_t cluster_addr)
-{
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-// TMA load into this CTA's shared memory, completion bytes credited to a barrier that may live
-// in the peer CTA.  Every CTA fetches its own rows.
-__device__ __forceinline__ void tma_load_2d_pair(void *smem_dst, const CUtensorMap *map, int c0, int c1,
-                                                 uint32_t bar_cluster_addr)
-{
-    asm volatile(
-        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
-        "[%0], [%1, {%2, %3}], [%4];"
-        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(bar_cluster_addr)
-        : "memory");
-}
-__device__ __forceinline__ void tcgen05_commit_pair(uint64_t *bar)
-{
-    asm volatile(
-        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
-        ::"r"(smem_u32(bar)), "h"((uint16_t)3)
-        : "memory");
-}
-__device__ __forceinline__ void tcgen05_mma_bf16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
-                                                      uint32_t idesc, uint32_t accumulate)
-{
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-__device__ __forceinline__ uint32_t make_idesc_pair(int a_mn_major, int b_mn_major)
-{
-    uint32_t d = 0;
-    d |= 1u << 4;
-    d |= 1u << 7;
-    d |= 1u << 10;
-    d |= (uint32_t)(a_mn_major & 1) << 15;
-    d |= (uint32_t)(b_mn_major & 1) << 16;
-    d |= (uint32_t)(BN >> 3) << 17;   // N = 256
-    d |= (uint32_t)(BM2 >> 4) << 24;  // M = 256 across the pair
-    return d;
-}
-
-__global__ void __launch_bounds__(kThreads, 1)
-ns_gemm_tc2_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__restrict__ tiles, int n_tiles,
-                   const uint8_t *__restrict__ present, int *__restrict__ error_flag)
-{
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    Barriers2 *bars = reinterpret_cast<Barriers2 *>(smem + (size_t)kStages2 * kStageBytes2);
-    volatile uint32_t *abort_flag = &bars->abort;
-
-    const int warp = threadIdx.x >> 5;
-    const int lane = threadIdx.x & 31;
-    const uint32_t cta_rank = cluster_ctarank();       // 0 = leader
-    const int cluster_id = blockIdx.x >> 1;
-    const int n_clusters = gridDim.x >> 1;
-
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages2; ++s) {
-            mbar_init(&bars->full[s], 2);              // one arrive.expect_tx from each CTA's producer
-            mbar_init(&bars->empty[s], 1);             // one multicast commit from the leader's MMA thread
-        }
-        for (int a = 0; a < 2; ++a) {
-            mbar_init(&bars->tmem_full[a], 1);
-            mbar_init(&bars->tmem_empty[a], 2 * kEpiWarps);  // epilogue warps of both CTAs
-        }
-        bars->abort = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    if (warp == 1) {  // the same warp of both CTAs allocates the pair's tensor memory
-        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
-                         smem_u32(&bars->tmem_base)),
-                     "r"((uint32_t)kTmemCols)
-                     : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-    }
-    tcgen05_fence_before();
-    __syncthreads();
-    cluster_sync_all();  // the peer's barriers exist before anything signals them
-    tcgen05_fence_after();
-    const uint32_t tmem_base = bars->tmem_base;
-
-    if (warp == 0) {
-        // ---------------- TMA producer (both CTAs) ----------------
-        if (lane == 0) {
-            int stage = 0;
-            uint32_t phase = 0;
-            bool ok = true;
-            for (int t = cluster_id; t < n_tiles && ok; t += n_clusters) {
-                const GemmTile tile = tiles[t];
-                const TcGemmProblem *p = problems + tile.problem;
-                if (present[p->tensor] == 0) continue;
-                const int k_blocks = (p->K + BK - 1) / BK;
-                const int a_mn = p->a_mn_major, b_mn = p->b_mn_major;
-                const int a_row0 = tile.m0 + (int)cta_rank * BM;        // this CTA's rows of A
-                const int b_row0 = tile.n0 + (int)cta_rank * (BN / 2);  // this CTA's rows of B
-                for (int kb = 0; kb < k_blocks; ++kb) {
-                    if (!mbar_wait(&bars->empty[stage], phase ^ 1u, abort_flag)) {
-                        ok = false;
-                        break;
-                    }
-                    uint8_t *sa = smem + (size_t)stage * kStageBytes2;
-                    uint8_t *sb = sa + kABytes;
-                    const uint32_t full_leader = map_to_cta(smem_u32(&bars->full[stage]), 0);
-                    mbar_remote_expect_tx(full_leader, kStageBytes2);
-                    const int k0 = kb * BK;
-#pragma unroll
-                    for (int j = 0; j < BM / kBoxRows; ++j) {
-                        const int r0 = a_row0 + j * kBoxRows;
-                        if (a_mn) tma_load_2d_pair(sa + j * kBoxBytes, &p->map_a, r0, k0, full_leader);
-                        else      tma_load_2d_pair(sa + j * kBoxBytes, &p->map_a, k0, r0, full_leader);
-                    }
-#pragma unroll
-                    for (int j = 0; j < (BN / 2) / kBoxRows; ++j) {
-                        const int r0 = b_row0 + j * kBoxRows;
-                        if (b_mn) tma_load_2d_pair(sb + j * kBoxBytes, &p->map_b, r0, k0, full_leader);
-                        else      tma_load_2d_pair(sb + j * kBoxBytes, &p->map_b, k0, r0, full_leader);
-                    }
-                    if (++stage == kStages2) {
-                        stage = 0;
-                        phase ^= 1u;
-                    }
-                }
-            }
-            if (!ok) {
-                bars->abort = 1;
-                atomicExch(error_flag, 11);
-            }
-        }
-        __syncwarp();
-    } else if (warp == 1) {
-        // ---------------- MMA issuer (leader CTA only) ----------------
-        if (lane == 0 && cta_rank == 0) {
-            int stage = 0;
-            uint32_t phase = 0;
-            int acc = 0;
-            uint32_t acc_phase = 0;
-            bool ok = true;
-            for (int t = cluster_id; t < n_tiles && ok; t += n_clusters) {
-                const GemmTile tile = tiles[t];
-                const TcGemmProblem *p = problems + tile.problem;
-                if (present[p->tensor] == 0) continue;
-                const int k_blocks = (p->K + BK - 1) / BK;
-                const int a_mn = p->a_mn_major, b_mn = p->b_mn_major;
-                const uint32_t idesc = make_idesc_pair(a_mn, b_mn);
-                if (!mbar_wait(&bars->tmem_empty[acc], acc_phase ^ 1u, abort_flag)) {
-                    ok = false;
-                    break;
-                }
-                tcgen05_fence_after();
-                const uint32_t tmem_d = tmem_base + (uint32_t)(acc * kAccCols);
-                for (int kb = 0; kb < k_blocks; ++kb) {
-                    if (!mbar_wait(&bars->full[stage], phase, abort_flag)) {
-                        ok = false;
-                        break;
-                    }
-                    tcgen05_fence_after();
-                    const uint32_t sa = smem_u32(smem + (size_t)stage * kStageBytes2);
-                    const uint32_t sb = sa + kABytes;
-#pragma unroll
-                    for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-                        const uint64_t da = a_mn ? make_smem_desc(sa + kk * 2048, kBoxBytes, 1024)
-                                                 : make_smem_desc(sa + kk * 32, 16, 1024);
-                        const uint64_t db = b_mn ? make_smem_desc(sb + kk * 2048, kBoxBytes, 1024)
-                                                 : make_smem_desc(sb + kk * 32, 16, 1024);
-                        tcgen05_mma_bf16_pair(tmem_d, da, db, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
-                    }
-                    tcgen05_commit_pair(&bars->empty[stage]);  // frees the slot in both CTAs
-                    if (++stage == kStages2) {
-                        stage = 0;
-                        phase ^= 1u;
-                    }
-                }
-                if (!ok) break;
-                tcgen05_commit_pair(&bars->tmem_full[acc]);  // both CTAs' epilogues may read their halves
-                if (++acc == 2) {
-                    acc = 0;
-                    acc_phase ^= 1u;
-                }
-            }
-            if (!ok) {
-                bars->abort = 1;
-                atomicExch(error_flag, 12);
-            }
-        }
-        __syncwarp();
-    } else {
-        // ---------------- epilogue (warps 2..5 of both CTAs) ----------------
-        const int quarter = warp & 3;
-        int acc = 0;
-        uint32_t acc_phase = 0;
-        bool ok = true;
-        for (int t = cluster_id; t < n_tiles && ok; t += n_clusters) {
-            const GemmTile tile = tiles[t];
-            const TcGemmProblem *p = problems + tile.problem;
-            if (present[p->tensor] == 0) continue;
-            const int M = p->M, N = p->N;
-            const int epi = p->epilogue;
-            __nv_bfloat16 *out_bf16 = p->out_bf16;
-            float *out_f32 = p->out_f32;
-            const int64_t ld = p->ld_out;
-            if (!mbar_wait(&bars->tmem_full[acc], acc_phase, abort_flag)) {
-                ok = false;
-                break;
-            }
-            tcgen05_fence_after();
-            const int row = tile.m0 + (int)cta_rank * BM + quarter * 32 + lane;
-            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * kAccCols);
-#pragma unroll 1
-            for (int cc = 0; cc < BN / 32; ++cc) {
-                const int col0 = tile.n0 + cc * 32;
-                if (col0 >= N) break;
-                uint32_t v[32];
-                tmem_ld_32x32(taddr + (uint32_t)(cc * 32), v);
-                tmem_ld_wait();
-                if (row < M) {
-                    float f[32];
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const float a = __uint_as_float(v[j]);
-                        if (epi == TC_EPI_THREE_I_MINUS) f[j] = (row == col0 + j) ? 3.0f - a : -a;
-                        else f[j] = 0.5f * a;
-                    }
-#pragma unroll
-                    for (int g8 = 0; g8 < 4; ++g8) {
-                        const int col = col0 + g8 * 8;
-                        if (col >= N) break;
-                        if (out_bf16) {
-                            uint4 q;
-                            q.x = pack_bf16(f[g8 * 8 + 0], f[g8 * 8 + 1]);
-                            q.y = pack_bf16(f[g8 * 8 + 2], f[g8 * 8 + 3]);
-                            q.z = pack_bf16(f[g8 * 8 + 4], f[g8 * 8 + 5]);
-                            q.w = pack_bf16(f[g8 * 8 + 6], f[g8 * 8 + 7]);
-                            *reinterpret_cast<uint4 *>(out_bf16 + (int64_t)row * ld + col) = q;
-                        }
-                        if (out_f32) {
-                            float4 *dst = reinterpret_cast<float4 *>(out_f32 + (int64_t)row * ld + col);
-                            dst[0] = make_float4(f[g8 * 8 + 0], f[g8 * 8 + 1], f[g8 * 8 + 2], f[g8 * 8 + 3]);
-                            dst[1] = make_float4(f[g8 * 8 + 4], f[g8 * 8 + 5], f[g8 * 8 + 6], f[g8 * 8 + 7]);
-                        }
-                    }
-                }
-            }
-            tcgen05_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_remote_arrive(map_to_cta(smem_u32(&bars->tmem_empty[acc]), 0));
-            if (++acc == 2) {
-                acc = 0;
-                acc_phase ^= 1u;
-            }
-        }
-        if (!ok && lane == 0) {
-            bars->abort = 1;
-            atomicExch(error_flag, 13);
-        }
-        __syncwarp();
-    }
-
-    // ---------------- teardown ----------------
-    tcgen05_fence_before();
-    __syncthreads();
-    if (bars->abort != 0 && threadIdx.x == 0) {
-        for (int s = 0; s < kStages2; ++s)
-            for (uint32_t i = 0; i < 4096u; ++i)
-                if (mbar_try_wait(&bars->full[s], 0) || mbar_try_wait(&bars->full[s], 1)) break;
-    }
-    cluster_sync_all();  // neither CTA leaves while its peer may still signal it or read its operands
-    if (warp == 1) {
-        tcgen05_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)kTmemCols)
-                     : "memory");
+        if (kCtas == 2)
+            asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                         "r"((uint32_t)kTmemCols)
+                         : "memory");
+        else
+            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                         "r"((uint32_t)kTmemCols)
+                         : "memory");
     }
 }
 
@@ -736,8 +626,6 @@ EncodeTiledFn get_encode_fn()
     return fn;
 }
 
-}  // namespace
-
 // The two-CTA kernel is the default; VB_TC_ONE_CTA=1 selects the one-CTA kernel (128 x 256 tiles).
 bool tc_use_pair()
 {
@@ -749,28 +637,44 @@ bool tc_use_pair()
     return v == 1;
 }
 
+}  // namespace
+
 void tc_gemm_tile_shape(int *bm, int *bn)
 {
-    *bm = tc_use_pair() ? BM2 : BM;
+    *bm = tc_use_pair() ? Cfg<2>::kTileM : Cfg<1>::kTileM;
     *bn = BN;
 }
 
-// Tensor map over a row-major bf16 matrix [outer][inner] with 64 x 64 boxes and 128-byte
-// swizzle; out-of-range elements read as zero.
-int make_bf16_tensor_map(void *map_out, const void *base, int64_t inner, int64_t outer)
+// How an operand whose rows are indexed by k (an "MN-major" operand) is best staged: through
+// the 3-D view when its row length is a multiple of 64 elements, else as 64 x 64 boxes.
+int tc_mn_major_mode(int64_t inner) { return (inner % 64) == 0 ? TC_OP_MN_3D : TC_OP_MN_BOXES; }
+
+// Tensor map over a row-major bf16 matrix [outer][inner], 128-byte swizzle, out-of-range
+// elements read as zero.  `mode` selects the box the kernel will ask for (see load_rows128).
+int make_bf16_tensor_map(void *map_out, const void *base, int64_t inner, int64_t outer, int mode)
 {
     EncodeTiledFn fn = get_encode_fn();
     if (!fn) return fail(VB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
     if ((inner % 8) != 0 || (reinterpret_cast<uintptr_t>(base) & 15u) != 0)
         return fail(VB_ERR_UNSUPPORTED, "TMA needs 16-byte aligned rows (inner extent %lld)", (long long)inner);
-    cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
-    cuuint64_t strides[1] = {(cuuint64_t)inner * 2};
-    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)kBoxRows};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(reinterpret_cast<CUtensorMap *>(map_out), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
-                    const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    CUresult r;
+    cuuint32_t estr[3] = {1, 1, 1};
+    if (mode == TC_OP_MN_3D) {
+        if ((inner % 64) != 0) return fail(VB_ERR_INVALID_ARG, "the 3-D operand view needs rows of a multiple of 64");
+        cuuint64_t dims[3] = {64, (cuuint64_t)outer, (cuuint64_t)(inner / 64)};
+        cuuint64_t strides[2] = {(cuuint64_t)inner * 2, 128};
+        cuuint32_t box[3] = {64, 64, 2};
+        r = fn(reinterpret_cast<CUtensorMap *>(map_out), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(base),
+               dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    } else {
+        cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+        cuuint64_t strides[1] = {(cuuint64_t)inner * 2};
+        cuuint32_t box[2] = {(cuuint32_t)BK, mode == TC_OP_K_MAJOR ? 128u : (cuuint32_t)kBoxRows};
+        r = fn(reinterpret_cast<CUtensorMap *>(map_out), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base),
+               dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    }
     if (r != CUDA_SUCCESS) return fail(VB_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
     return VB_OK;
 }
@@ -779,25 +683,16 @@ int launch_ns_gemm_tc(const TcGemmProblem *d_problems, const GemmTile *d_tiles, 
                       const uint8_t *d_present, int *d_error_flag, int sm_count, cudaStream_t stream)
 {
     if (n_tiles <= 0) return VB_OK;
-    static bool attr_set = false;
-    if (!attr_set) {
-        VB_CUDA(cudaFuncSetAttribute(ns_gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     (int)kSmemBytes));
-        attr_set = true;
-    }
     if (tc_use_pair()) {
-        static bool attr2_set = false;
-        if (!attr2_set) {
-            VB_CUDA(cudaFuncSetAttribute(ns_gemm_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)kSmemBytes2));
-            attr2_set = true;
+        static bool attr_set = false;
+        if (!attr_set) {
+            VB_CUDA(cudaFuncSetAttribute(ns_gemm_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem_bytes<2>()));
+            attr_set = true;
         }
-        int clusters = sm_count / 2;  // one CTA pair per TPC
-        if (clusters > n_tiles) clusters = n_tiles;
         cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3((unsigned)(clusters * 2));
         cfg.blockDim = dim3(kThreads);
-        cfg.dynamicSmemBytes = kSmemBytes2;
+        cfg.dynamicSmemBytes = smem_bytes<2>();
         cfg.stream = stream;
         cudaLaunchAttribute attr[1];
         attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -806,13 +701,31 @@ int launch_ns_gemm_tc(const TcGemmProblem *d_problems, const GemmTile *d_tiles, 
         attr[0].val.clusterDim.z = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        VB_CUDA(cudaLaunchKernelEx(&cfg, ns_gemm_tc2_kernel, d_problems, d_tiles, n_tiles, d_present, d_error_flag));
+        // A persistent grid must be fully resident: ask how many CTA pairs the device holds at once.
+        static int max_clusters = 0;
+        if (max_clusters == 0) {
+            cfg.gridDim = dim3((unsigned)(sm_count / 2 * 2));
+            int n = 0;
+            VB_CUDA(cudaOccupancyMaxActiveClusters(&n, ns_gemm_tc_kernel<2>, &cfg));
+            if (n < 1) return fail(VB_ERR_CUDA, "the device cannot hold a 2-CTA cluster of the GEMM kernel");
+            max_clusters = n;
+        }
+        int clusters = max_clusters;
+        if (clusters > n_tiles) clusters = n_tiles;
+        cfg.gridDim = dim3((unsigned)(clusters * 2));
+        VB_CUDA(cudaLaunchKernelEx(&cfg, ns_gemm_tc_kernel<2>, d_problems, d_tiles, n_tiles, d_present, d_error_flag));
         return VB_OK;
+    }
+    static bool attr_set1 = false;
+    if (!attr_set1) {
+        VB_CUDA(cudaFuncSetAttribute(ns_gemm_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)smem_bytes<1>()));
+        attr_set1 = true;
     }
     int grid = sm_count;  // one persistent CTA per SM (it owns all 512 TMEM columns)
     if (grid > n_tiles) grid = n_tiles;
-    ns_gemm_tc_kernel<<<grid, kThreads, kSmemBytes, stream>>>(d_problems, d_tiles, n_tiles, d_present,
-                                                              d_error_flag);
+    ns_gemm_tc_kernel<1><<<grid, kThreads, smem_bytes<1>(), stream>>>(d_problems, d_tiles, n_tiles, d_present,
+                                                                     d_error_flag);
     VB_CUDA(cudaGetLastError());
     return VB_OK;
 }
