@@ -390,7 +390,9 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
 
     if (warp == 0) {
         // ---------------- TMA producer (every CTA) ----------------
-        if (lane == 0) {
+        // Two lanes share the issue work: lane 0 fetches A (and posts the byte count), lane 1
+        // fetches B.  Both wait on the same `empty` barrier.
+        if (lane < 2) {
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
@@ -414,13 +416,16 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
                     // complete until the leader has arrived.
                     const uint32_t full_bar =
                         kCtas == 2 ? map_to_cta(smem_u32(&bars->full[stage]), 0) : smem_u32(&bars->full[stage]);
-                    if (cta_rank == 0) mbar_expect_tx(&bars->full[stage], kCtas * C::kStageBytes);
                     const int k0 = kb * BK;
-                    load_rows128<kCtas>(sa, &ti.p->map_a, ti.a_mode, a_row0, k0, full_bar);
+                    if (lane == 0) {
+                        if (cta_rank == 0) mbar_expect_tx(&bars->full[stage], kCtas * C::kStageBytes);
+                        load_rows128<kCtas>(sa, &ti.p->map_a, ti.a_mode, a_row0, k0, full_bar);
+                    } else {
 #pragma unroll
-                    for (int j = 0; j < C::kBRows / 128; ++j)
-                        load_rows128<kCtas>(sb + j * kRows128Bytes, &ti.p->map_b, ti.b_mode, b_row0 + j * 128, k0,
-                                            full_bar);
+                        for (int j = 0; j < C::kBRows / 128; ++j)
+                            load_rows128<kCtas>(sb + j * kRows128Bytes, &ti.p->map_b, ti.b_mode, b_row0 + j * 128, k0,
+                                                full_bar);
+                    }
                     if (++stage == C::kStages) {
                         stage = 0;
                         phase ^= 1u;
