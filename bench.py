@@ -289,6 +289,8 @@ def run_ours(args):
     # ---- Muon (second headline: Newton-Schulz tensor TFLOP/s), on every rank ----
     muon = None if args.skip_muon else run_muon(args, eng, world, rank, dev, barrier, max_over_ranks, peaks)
 
+    c5 = None if args.skip_c5 else run_c5(args, eng, world, rank, dev, barrier, max_over_ranks, peaks)
+
     if rank != 0:
         return 0
 
@@ -328,8 +330,51 @@ def run_ours(args):
                                 "ms_per_step": sec * 1e3}
     if muon is not None:
         line["muon"] = muon
+    if c5 is not None:
+        line["c5_ragged_adam"] = c5
     print(json.dumps(line), flush=True)
     return 0
+
+
+def run_c5(args, eng, world, rank, dev, barrier, max_over_ranks, peaks):
+    """Ragged multi-tensor Adam (4096 tensors, sizes log-uniform in [1, 2^22], ~1.13e9 params):
+    the same kernel must hold its HBM fraction when the tensor list is ragged."""
+    import torch
+
+    from volta_b200 import VB_STEP_NO_EXCHANGE, Adam, Tensor
+    from volta_b200.interop import device_array
+
+    wl = workloads.c5_ragged_adam()
+    h = wl.hyper
+    tensors = [Tensor(np.zeros(n, np.float32)) for n in wl.sizes]
+    opt = Adam(tensors, h["lr"], h["betas"], h["eps"], h["weight_decay"], engine=eng)
+    p_ptr, g_ptr, arena, offsets = opt.arena_layout()
+    theta = torch.as_tensor(device_array(p_ptr, arena, opt), device=dev)
+    grad = torch.as_tensor(device_array(g_ptr, arena, opt), device=dev)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(1234)
+    theta.normal_(0.0, 1.0, generator=gen)
+    grad.normal_(0.0, 1e-3, generator=gen)
+    opt.mark_all_grads_present()
+    torch.cuda.synchronize()
+    steps = max(3, min(args.steps, 10))
+    for _ in range(3):
+        opt.step(VB_STEP_NO_EXCHANGE)
+    barrier()
+    eng.set_profiling(True)
+    eng.profile("update")
+    for _ in range(steps):
+        opt.step(VB_STEP_NO_EXCHANGE)
+    ms = max_over_ranks(eng.profile("update")[0] / steps)
+    eng.set_profiling(False)
+    barrier()
+    del theta, grad
+    opt.close()
+    gbs = ADAM_BYTES_PER_PARAM * (wl.total / world) / (ms * 1e-3) / 1e9
+    return {"workload": f"c5_ragged_adam: {len(wl.sizes)} tensors, {wl.total} f32 params, sizes in "
+                        f"[{min(wl.sizes)}, {max(wl.sizes)}], lr=3e-4 wd=0.1", "steps": steps,
+            "update_ms_per_step": ms, "params_per_s": wl.total / (ms * 1e-3), "achieved_gbs_per_gpu": gbs,
+            "frac_of_measured_hbm_peak": gbs / peaks["hbm_gbs"], "note": "update kernel only (no exchange)"}
 
 
 def time_cpu_muon_sample(ns_steps=5):
@@ -449,6 +494,7 @@ def main():
     ap.add_argument("--skip-muon", action="store_true", help="Adam only")
     ap.add_argument("--skip-muon-f32", action="store_true", help="skip the (slow) f32 Newton-Schulz timing")
     ap.add_argument("--only-muon", action="store_true", help="profiling runs: Muon bf16 only")
+    ap.add_argument("--skip-c5", action="store_true", help="skip the ragged 4096-tensor Adam section")
     ap.add_argument("--muon-layers", type=int, default=24, help="profiling runs: fewer layers of the Muon set")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":

@@ -301,3 +301,54 @@ def test_errors_are_reported_not_fatal(engine):
     with pytest.raises(VoltaB200Error):
         multi_tensor_step(engine, 2, [8], [0], [0], [0], [0], lr=1e-3, t=1)
     opt.close()
+
+
+def test_c5_full_size_ragged_properties(oracle, engine):
+    """The ragged stress configuration at full size (4096 tensors, sizes log-uniform in
+    [1, 2^22], 1.13e9 parameters, lr 3e-4, wd 0.1), two steps.  The arenas are filled on the
+    device; a sample of tensors (largest, smallest, random) is checked bit for bit against the
+    oracle, and size-independent properties are checked on everything: padding between tensors
+    stays zero, every parameter moves, m and v are finite and v >= 0."""
+    import torch
+    import workloads
+    from volta_b200 import Adam, Tensor
+    from volta_b200.interop import device_array
+    wl = workloads.c5_ragged_adam()
+    assert len(wl.sizes) == 4096 and wl.total == 1_129_164_500 and min(wl.sizes) >= 1 and max(wl.sizes) <= 2 ** 22
+    h = wl.hyper
+    tensors = [Tensor(np.zeros(n, np.float32)) for n in wl.sizes]
+    opt = Adam(tensors, h["lr"], h["betas"], h["eps"], h["weight_decay"], engine=engine)
+    p_ptr, g_ptr, arena, offsets = opt.arena_layout()
+    theta = torch.as_tensor(device_array(p_ptr, arena, opt), device="cuda:0")
+    grad = torch.as_tensor(device_array(g_ptr, arena, opt), device="cuda:0")
+    gen = torch.Generator(device="cuda:0")
+    gen.manual_seed(1234)
+    mask = torch.zeros(arena, dtype=torch.bool, device="cuda:0")
+    for o, n in zip(offsets, wl.sizes):
+        mask[o:o + n] = True
+    theta.normal_(0.0, 1.0, generator=gen)
+    theta.mul_(mask)  # padding must start (and stay) zero
+    order = np.argsort(wl.sizes)
+    rng = np.random.default_rng(0)
+    sample = sorted(set(order[:8].tolist() + order[-4:].tolist() + rng.choice(4096, 24, replace=False).tolist()))
+    ref_p = {i: theta[offsets[i]:offsets[i] + wl.sizes[i]].cpu().numpy().copy() for i in sample}
+    ref = oracle.Adam([ref_p[i] for i in sample], h["lr"], h["betas"], h["eps"], h["weight_decay"])
+    before = theta.clone()
+    opt.mark_all_grads_present()
+    for s in (1, 2):
+        grad.normal_(0.0, 1e-3, generator=gen)
+        grad.mul_(mask)
+        torch.cuda.synchronize()
+        gs = [grad[offsets[i]:offsets[i] + wl.sizes[i]].cpu().numpy().copy() for i in sample]
+        opt.step()
+        engine.synchronize()
+        ref.step(gs)
+    for k, i in enumerate(sample):
+        got = theta[offsets[i]:offsets[i] + wl.sizes[i]].cpu().numpy()
+        assert bits_equal(got, ref_p[i]), i
+        assert bits_equal(opt.state(i, 0), ref.m[k]) and bits_equal(opt.state(i, 1), ref.v[k])
+    assert not bool(theta[~mask].any())                      # padding untouched
+    assert bool(((theta != before) | ~mask).all())           # every parameter moved (wd 0.1, N(0,1) data)
+    assert bool(torch.isfinite(theta).all())
+    del theta, grad, before, mask
+    opt.close()
