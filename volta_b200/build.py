@@ -78,5 +78,29 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+CPP_TEST_SRC = os.path.join(HERE, "..", "tests", "cpp", "test_optimizers.cpp")
+CPP_TEST_BIN = os.path.join(HERE, "..", "tests", "cpp", "test_optimizers.bin")
+
+
+def build_cpp_tests(force: bool = False) -> str:
+    """Compiles the C++ replay of the reference's optimizer tests against the C++ host mirror
+    (include/volta_b200.hpp) and links it to the library."""
+    src, out = os.path.abspath(CPP_TEST_SRC), os.path.abspath(CPP_TEST_BIN)
+    hdr = os.path.join(HERE, "..", "include", "volta_b200.hpp")
+    newest = max(os.path.getmtime(src), os.path.getmtime(hdr), os.path.getmtime(LIB))
+    if not force and os.path.exists(out) and os.path.getmtime(out) >= newest:
+        return out
+    cuda_lib = os.path.join(os.path.dirname(os.path.dirname(os.path.realpath(_nvcc()))), "lib64") \
+        if os.path.sep in _nvcc() else "/usr/local/cuda/lib64"
+    cmd = ["g++", "-std=c++17", "-O2", "-I", os.path.join(HERE, "..", "include"), src, "-o", out,
+           "-L", HERE, "-lvolta_b200", "-Wl,-rpath,$ORIGIN/../../volta_b200", "-L", cuda_lib,
+           f"-Wl,-rpath,{cuda_lib}"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"g++ failed on the C++ tests:\n{r.stdout}\n{r.stderr}")
+    return out
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build_cpp_tests(force="--force" in sys.argv))
