@@ -225,6 +225,12 @@ def run_ours(args):
     params = wl.make_params()
     tensors = [Tensor(p, p.shape) for p in params]
     opt = Adam(tensors, h["lr"], h["betas"], h["eps"], h["weight_decay"], engine=eng)
+    if world > 1 and args.exchange == "peer":
+        mine = torch.frombuffer(bytearray(opt.ipc_handle()), dtype=torch.uint8).to(dev)
+        allh = torch.zeros(world * 64, dtype=torch.uint8, device=dev)
+        dist.all_gather_into_tensor(allh, mine)
+        blob = allh.cpu().numpy().tobytes()
+        opt.open_peers([blob[r * 64:(r + 1) * 64] for r in range(world)])
     _, _, arena, offsets = opt.arena_layout()
     grads_pinned = PinnedBuffer(arena)
     grads_pinned.array[:] = fill_arena(wl, offsets, arena, wl.make_grads(1))
@@ -304,7 +310,10 @@ def run_ours(args):
                                "157 tensors, 109602816 f32 params",
                    "l2": "inputs larger than L2 (1.75 GB of theta/g/m/v per step vs 126 MB)",
                    "parallelism": f"zero1x{world}" if world > 1 else "single",
-                   "exchange": "nccl all-gather of updated params inside step()" if world > 1 else "none"},
+                   "exchange": ("none" if world == 1 else
+                                "peer stores over NVLink fused into the update kernel, fenced by two one-float "
+                                "NCCL all-reduces" if args.exchange == "peer" else
+                                "nccl all-gather of updated params after the update kernel")},
         "update_only": {"value": wl.total / (kernel_avg_ms * 1e-3), "unit": "params/s",
                         "ms_per_step": kernel_avg_ms,
                         "note": "fused update kernel alone, max over ranks"},
@@ -495,6 +504,9 @@ def main():
     ap.add_argument("--skip-muon-f32", action="store_true", help="skip the (slow) f32 Newton-Schulz timing")
     ap.add_argument("--only-muon", action="store_true", help="profiling runs: Muon bf16 only")
     ap.add_argument("--skip-c5", action="store_true", help="skip the ragged 4096-tensor Adam section")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: updated parameters reach the other ranks by NVLink peer stores fused into the "
+                         "update kernel (default) or by an NCCL all-gather after it")
     ap.add_argument("--muon-layers", type=int, default=24, help="profiling runs: fewer layers of the Muon set")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":

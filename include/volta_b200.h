@@ -225,6 +225,17 @@ int vb_optimizer_zero_grad(vb_optimizer *opt);
 /* Hyper-parameters can change between steps (learning-rate schedules). */
 int vb_optimizer_set_lr(vb_optimizer *opt, float lr);
 
+/* Fused exchange over NVLink peer memory (Adam and SGD on a sharded engine; no counterpart in
+ * the reference).  Every rank exports a CUDA IPC handle of its parameter arena, the host
+ * gathers the world_size handles in rank order (any transport) and hands them to every
+ * rank.  From then on step() no longer runs an all-gather after the update: the update
+ * kernel itself stores each new parameter into the local arena and into the same position of
+ * every peer's arena, bracketed by two stream-ordered barriers (one-float NCCL all-reduces).
+ * All ranks must be processes on one node whose GPUs can reach each other (NVLink/NVSwitch). */
+#define VB_IPC_HANDLE_BYTES 64
+int vb_optimizer_ipc_handle(vb_optimizer *opt, void *handle64);
+int vb_optimizer_open_peers(vb_optimizer *opt, const void *handles, int n_handles);
+
 /* ---- optimizer state (private in the reference, src/nn/optim/adam.rs:5-14) -------- */
 
 /* which: 0 = first state (Adam m, SGD velocity, Muon velocity), 1 = Adam v.

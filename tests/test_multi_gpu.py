@@ -33,6 +33,8 @@ def _worker(rank, world, shared, kind):
         time.sleep(0.01)
     eng.init_comm(shared["id"], rank, world)
     assert (eng.rank, eng.world_size) == (rank, world)
+    peer = kind.endswith("_peer")  # exchange fused into the update kernel (NVLink peer stores)
+    kind = kind.replace("_peer", "")
     if kind == "adam":
         wl = workloads.c5_ragged_adam(n_tensors=96, max_log2=16, seed=11)
     elif kind == "sgd":
@@ -50,6 +52,11 @@ def _worker(rank, world, shared, kind):
     else:
         opt = Muon(tensors, h["lr"], h["momentum"], h["nesterov"], h["ns_steps"],
                    ns_mode=VB_NS_F32 if kind == "muon_f32" else VB_NS_BF16, engine=eng)
+    if peer:
+        shared[f"ipc{rank}"] = opt.ipc_handle()
+        while any(f"ipc{r}" not in shared for r in range(world)):
+            time.sleep(0.01)
+        opt.open_peers([shared[f"ipc{r}"] for r in range(world)])
     owned = 0
     for s in (1, 2, 3):
         opt.zero_grad()
@@ -65,7 +72,7 @@ def _worker(rank, world, shared, kind):
     eng.close()
 
 
-@pytest.mark.parametrize("kind", ["adam", "sgd", "muon_f32", "muon_bf16"])
+@pytest.mark.parametrize("kind", ["adam", "sgd", "adam_peer", "sgd_peer", "muon_f32", "muon_bf16"])
 def test_two_gpu_sharded_step_matches_oracle(oracle, kind):
     if _gpu_count() < 2:
         pytest.skip("needs 2 GPUs")
@@ -82,6 +89,7 @@ def test_two_gpu_sharded_step_matches_oracle(oracle, kind):
             p.join(300)
             assert p.exitcode == 0
         res = dict(shared)
+    kind = kind.replace("_peer", "")
     if kind == "adam":
         wl = workloads.c5_ragged_adam(n_tensors=96, max_log2=16, seed=11)
     elif kind == "sgd":

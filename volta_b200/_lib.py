@@ -86,6 +86,8 @@ SIGNATURES = {
     "vb_optimizer_set_lr": [_vp, C.c_float],
     "vb_optimizer_export_state": [_vp, _i64, C.c_int, _vp, _i64, _i64p, _i64p],
     "vb_optimizer_import_state": [_vp, _i64, C.c_int, _vp, _i64],
+    "vb_optimizer_ipc_handle": [_vp, _vp],
+    "vb_optimizer_open_peers": [_vp, _vp, C.c_int],
     "vb_optimizer_get_t": [_vp, _i64p],
     "vb_optimizer_set_t": [_vp, _i64],
     "vb_muon_download_update": [_vp, _i64, _vp, _i64],

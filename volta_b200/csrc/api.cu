@@ -230,6 +230,7 @@ static void free_optimizer(vb_optimizer *opt)
     if (!opt) return;
     if (opt->eng) cudaSetDevice(opt->eng->device);
     if (opt->muon) destroy_muon_state(opt->muon);
+    for (void *m : opt->peer_mappings) cudaIpcCloseMemHandle(m);
     cudaFree(opt->d_param);
     cudaFree(opt->d_grad);
     cudaFree(opt->d_s1);
@@ -738,11 +739,28 @@ int vb_optimizer_step_ex(vb_optimizer *opt, uint32_t flags)
     if (opt->n_chunks > 0) {
         bool all_present = true;
         for (int64_t i = 0; i < opt->n_tensors && all_present; ++i) all_present = opt->present[(size_t)i] != 0;
+        // With peer arenas mapped, the exchange is fused into the update: the kernel stores
+        // every new parameter locally and into each peer's arena.  Two stream-ordered barriers
+        // fence it: no rank is written to before it has reached its step (its earlier readers
+        // of the parameters are done), and no rank continues before all writes have landed.
+        const bool exchange = e->world > 1 && !(flags & VB_STEP_NO_EXCHANGE);
+        const bool fused = exchange && opt->peers.n > 0;
+        if (fused) {
+            prof_begin(e, VB_PHASE_EXCHANGE);
+            VB_TRY(comm_barrier(e));
+            prof_end(e, VB_PHASE_EXCHANGE);
+        }
         prof_begin(e, VB_PHASE_UPDATE);
         VB_TRY(launch_multi_tensor(op, opt->d_chunks, opt->n_chunks, opt->d_present, all_present, s,
-                                   e->sm_count, e->stream));
+                                   e->sm_count, e->stream, fused ? &opt->peers : nullptr));
         prof_end(e, VB_PHASE_UPDATE);
         e->launches += 1;
+        if (fused) {
+            prof_begin(e, VB_PHASE_EXCHANGE);
+            VB_TRY(comm_barrier(e));
+            prof_end(e, VB_PHASE_EXCHANGE);
+            return VB_OK;
+        }
     }
     if (e->world > 1 && !(flags & VB_STEP_NO_EXCHANGE)) {
         prof_begin(e, VB_PHASE_EXCHANGE);
@@ -817,6 +835,48 @@ int vb_optimizer_import_state(vb_optimizer *opt, int64_t tensor, int which, cons
                                 opt->eng->stream));
         VB_CUDA(cudaStreamSynchronize(opt->eng->stream));
     }
+    return VB_OK;
+    VB_API_END
+}
+
+int vb_optimizer_ipc_handle(vb_optimizer *opt, void *handle64)
+{
+    VB_API_BEGIN
+    VB_TRY(check_opt(opt));
+    if (!handle64) return fail(VB_ERR_INVALID_ARG, "handle64 is null");
+    static_assert(sizeof(cudaIpcMemHandle_t) == VB_IPC_HANDLE_BYTES, "CUDA IPC handles are 64 bytes");
+    VB_TRY(set_device(opt->eng));
+    cudaIpcMemHandle_t h;
+    VB_CUDA(cudaIpcGetMemHandle(&h, opt->d_param));
+    memcpy(handle64, &h, sizeof(h));
+    return VB_OK;
+    VB_API_END
+}
+
+int vb_optimizer_open_peers(vb_optimizer *opt, const void *handles, int n_handles)
+{
+    VB_API_BEGIN
+    VB_TRY(check_opt(opt));
+    vb_engine *e = opt->eng;
+    if (!handles) return fail(VB_ERR_INVALID_ARG, "handles is null");
+    if (n_handles != e->world)
+        return fail(VB_ERR_INVALID_ARG, "expected %d handles (one per rank), got %d", e->world, n_handles);
+    if (e->world - 1 > kMaxPeers) return fail(VB_ERR_UNSUPPORTED, "at most %d peers", kMaxPeers);
+    if (opt->kind == KIND_MUON) return fail(VB_ERR_UNSUPPORTED, "peer exchange is implemented for Adam and SGD");
+    if (opt->peers.n > 0) return fail(VB_ERR_STATE, "peers are already open");
+    VB_TRY(set_device(e));
+    PeerTable pt{};
+    pt.local_base = opt->d_param;
+    for (int r = 0; r < e->world; ++r) {
+        if (r == e->rank) continue;
+        cudaIpcMemHandle_t h;
+        memcpy(&h, (const char *)handles + (size_t)r * VB_IPC_HANDLE_BYTES, sizeof(h));
+        void *mapped = nullptr;
+        VB_CUDA(cudaIpcOpenMemHandle(&mapped, h, cudaIpcMemLazyEnablePeerAccess));
+        opt->peer_mappings.push_back(mapped);
+        pt.base[pt.n++] = (float *)mapped;
+    }
+    opt->peers = pt;
     return VB_OK;
     VB_API_END
 }

@@ -26,6 +26,7 @@ struct NcclApi {
     ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int) = nullptr;
     ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
     ncclResult_t (*AllGather)(const void *, void *, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*AllReduce)(const void *, void *, size_t, ncclDataType_t, int /*ncclRedOp_t*/, ncclComm_t, cudaStream_t) = nullptr;
     ncclResult_t (*Broadcast)(const void *, void *, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
     ncclResult_t (*GroupStart)() = nullptr;
     ncclResult_t (*GroupEnd)() = nullptr;
@@ -61,6 +62,7 @@ int load_api()
     VB_SYM(CommDestroy, "ncclCommDestroy")
     VB_SYM(AllGather, "ncclAllGather")
     VB_SYM(Broadcast, "ncclBroadcast")
+    VB_SYM(AllReduce, "ncclAllReduce")
     VB_SYM(GroupStart, "ncclGroupStart")
     VB_SYM(GroupEnd, "ncclGroupEnd")
     VB_SYM(GetErrorString, "ncclGetErrorString")
@@ -80,6 +82,7 @@ int load_api()
 
 struct Comm {
     ncclComm_t comm = nullptr;
+    float *d_token = nullptr;  // one float: the payload of the barrier all-reduce
 };
 
 int comm_unique_id(void *id128)
@@ -112,6 +115,7 @@ void comm_destroy(vb_engine *eng)
 {
     if (eng->comm) {
         if (eng->comm->comm && g_api.CommDestroy) g_api.CommDestroy(eng->comm->comm);
+        if (eng->comm->d_token) cudaFree(eng->comm->d_token);
         delete eng->comm;
         eng->comm = nullptr;
     }
@@ -123,6 +127,21 @@ int comm_all_gather_inplace(vb_engine *eng, float *base, int64_t count)
     if (!eng->comm) return fail(VB_ERR_STATE, "engine has no communicator");
     VB_NCCL(g_api.AllGather(base + (int64_t)eng->rank * count, base, (size_t)count, kNcclFloat,
                             eng->comm->comm, eng->stream));
+    return VB_OK;
+}
+
+// A one-float all-reduce used as a stream-ordered barrier across the ranks: it completes on
+// a rank only after every rank's stream has reached it, i.e. after all work the other ranks
+// enqueued before it (their update kernels and the peer stores in them) has finished.
+int comm_barrier(vb_engine *eng)
+{
+    if (!eng->comm) return fail(VB_ERR_STATE, "engine has no communicator");
+    if (!eng->comm->d_token) {
+        VB_CUDA(cudaMalloc(&eng->comm->d_token, sizeof(float)));
+        VB_CUDA(cudaMemsetAsync(eng->comm->d_token, 0, sizeof(float), eng->stream));
+    }
+    VB_NCCL(g_api.AllReduce(eng->comm->d_token, eng->comm->d_token, 1, kNcclFloat, 0 /*ncclSum*/, eng->comm->comm,
+                            eng->stream));
     return VB_OK;
 }
 

@@ -66,6 +66,10 @@ struct vb_optimizer {
     std::vector<uint8_t> present_on_dev; // last copy sent to d_present
 
     vb::MuonState *muon = nullptr;
+
+    // peer GPUs' parameter arenas opened through CUDA IPC (vb_optimizer_open_peers)
+    vb::PeerTable peers{};
+    std::vector<void *> peer_mappings;  // what cudaIpcOpenMemHandle returned, to close on destroy
 };
 
 namespace vb {
@@ -89,6 +93,7 @@ int comm_unique_id(void *id128);
 int comm_init(vb_engine *eng, const void *id128, int rank, int world);
 void comm_destroy(vb_engine *eng);
 int comm_all_gather_inplace(vb_engine *eng, float *base, int64_t elems_per_rank);
+int comm_barrier(vb_engine *eng);  // stream-ordered: completes once every rank's stream has reached it
 struct BcastItem {
     float *ptr;
     int64_t count;

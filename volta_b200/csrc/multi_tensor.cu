@@ -97,8 +97,11 @@ __device__ __forceinline__ FatChunk load_chunk(const FatChunk *c)
     return u.f;
 }
 
-template <int OP>
-__device__ __forceinline__ void update_chunk(const FatChunk &ch, const StepScalars &s)
+// PEERS: besides the local arena, every updated parameter is stored into the same arena
+// position on every peer GPU (plain st.global to peer-mapped memory over NVLink), so the
+// all-gather of updated parameters rides along with the update, piece by piece.
+template <int OP, bool PEERS>
+__device__ __forceinline__ void update_chunk(const FatChunk &ch, const StepScalars &s, const PeerTable &pt)
 {
     constexpr bool kHasS1 = (OP != OP_SGD);
     constexpr bool kHasS2 = (OP == OP_ADAM);
@@ -107,6 +110,8 @@ __device__ __forceinline__ void update_chunk(const FatChunk &ch, const StepScala
     float *__restrict__ s1 = kHasS1 ? ch.s1 : nullptr;
     float *__restrict__ s2 = kHasS2 ? ch.s2 : nullptr;
     const uint32_t n = ch.len;
+
+    const ptrdiff_t arena_pos = PEERS ? (p - pt.local_base) : 0;  // element offset inside the arena
 
     uintptr_t align_bits = reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g);
     if (kHasS1) align_bits |= reinterpret_cast<uintptr_t>(s1);
@@ -127,6 +132,11 @@ __device__ __forceinline__ void update_chunk(const FatChunk &ch, const StepScala
             update_vec<OP>(vp.lo, vg.lo, va.lo, vb.lo, s);
             update_vec<OP>(vp.hi, vg.hi, va.hi, vb.hi, s);
             st_vec8(p8 + i, vp);
+            if (PEERS) {
+#pragma unroll
+                for (int r = 0; r < kMaxPeers; ++r)  // unrolled: the table stays in the constant bank
+                    if (r < pt.n) st_vec8(reinterpret_cast<Vec8 *>(pt.base[r] + arena_pos) + i, vp);
+            }
             if (kHasS1) st_vec8(a8 + i, va);
             if (kHasS2) st_vec8(b8 + i, vb);
         }
@@ -144,6 +154,11 @@ __device__ __forceinline__ void update_chunk(const FatChunk &ch, const StepScala
             if (kHasS2) vb = __ldcs(b4 + i);
             update_vec<OP>(vp, vg, va, vb, s);
             __stcs(p4 + i, vp);
+            if (PEERS) {
+#pragma unroll
+                for (int r = 0; r < kMaxPeers; ++r)
+                    if (r < pt.n) reinterpret_cast<float4 *>(pt.base[r] + arena_pos)[i] = vp;
+            }
             if (kHasS1) __stcs(a4 + i, va);
             if (kHasS2) __stcs(b4 + i, vb);
         }
@@ -157,6 +172,11 @@ __device__ __forceinline__ void update_chunk(const FatChunk &ch, const StepScala
         if (kHasS2) vb = s2[i];
         update_one<OP>(vp, vg, va, vb, s);
         p[i] = vp;
+        if (PEERS) {
+#pragma unroll
+            for (int r = 0; r < kMaxPeers; ++r)
+                if (r < pt.n) pt.base[r][arena_pos + i] = vp;
+        }
         if (kHasS1) s1[i] = va;
         if (kHasS2) s2[i] = vb;
     }
@@ -165,10 +185,10 @@ __device__ __forceinline__ void update_chunk(const FatChunk &ch, const StepScala
 // CHECK_PRESENT = false is the common case (every tensor has a gradient): the descriptor of
 // the next chunk is fetched while the current one streams, so no dependent-load latency
 // sits between chunks.  With CHECK_PRESENT the per-tensor flag is looked up as well.
-template <int OP, bool CHECK_PRESENT>
+template <int OP, bool CHECK_PRESENT, bool PEERS>
 __global__ void __launch_bounds__(kThreads, kCtasPerSm)
 multi_tensor_update_kernel(const FatChunk *__restrict__ chunks, int64_t n_chunks,
-                           const uint8_t *__restrict__ present, const StepScalars s)
+                           const uint8_t *__restrict__ present, const StepScalars s, const PeerTable pt)
 {
     int64_t c = blockIdx.x;
     if (c >= n_chunks) return;
@@ -179,7 +199,7 @@ multi_tensor_update_kernel(const FatChunk *__restrict__ chunks, int64_t n_chunks
         FatChunk nxt = cur;
         if (has_next) nxt = load_chunk(chunks + cn);  // in flight while `cur` is processed
         // `grad == None` -> skip: adam.rs:81-84, sgd.rs:75-78
-        if (!CHECK_PRESENT || present[cur.tensor] != 0) update_chunk<OP>(cur, s);
+        if (!CHECK_PRESENT || present[cur.tensor] != 0) update_chunk<OP, PEERS>(cur, s, pt);
         if (!has_next) break;
         cur = nxt;
         c = cn;
@@ -239,16 +259,29 @@ int64_t pick_chunk_len(int64_t total_elements, int sm_count)
 
 template <int OP>
 static void launch_op(unsigned grid, const FatChunk *d_chunks, int64_t n_chunks, const uint8_t *d_present,
-                      bool all_present, const StepScalars &s, cudaStream_t stream)
+                      bool all_present, const StepScalars &s, const PeerTable *peers, cudaStream_t stream)
 {
+    if (peers && peers->n > 0) {
+        if (all_present)
+            multi_tensor_update_kernel<OP, false, true><<<grid, kThreads, 0, stream>>>(d_chunks, n_chunks, d_present, s,
+                                                                                     *peers);
+        else
+            multi_tensor_update_kernel<OP, true, true><<<grid, kThreads, 0, stream>>>(d_chunks, n_chunks, d_present, s,
+                                                                                    *peers);
+        return;
+    }
+    const PeerTable none{};
     if (all_present)
-        multi_tensor_update_kernel<OP, false><<<grid, kThreads, 0, stream>>>(d_chunks, n_chunks, d_present, s);
+        multi_tensor_update_kernel<OP, false, false><<<grid, kThreads, 0, stream>>>(d_chunks, n_chunks, d_present, s,
+                                                                                  none);
     else
-        multi_tensor_update_kernel<OP, true><<<grid, kThreads, 0, stream>>>(d_chunks, n_chunks, d_present, s);
+        multi_tensor_update_kernel<OP, true, false><<<grid, kThreads, 0, stream>>>(d_chunks, n_chunks, d_present, s,
+                                                                                 none);
 }
 
 int launch_multi_tensor(int op, const FatChunk *d_chunks, int64_t n_chunks, const uint8_t *d_present,
-                        bool all_present, const StepScalars &s, int sm_count, cudaStream_t stream)
+                        bool all_present, const StepScalars &s, int sm_count, cudaStream_t stream,
+                        const PeerTable *peers)
 {
     if (n_chunks <= 0) return VB_OK;
     if (op != OP_ADAM && op != OP_SGD_MOMENTUM && op != OP_SGD)
@@ -256,11 +289,13 @@ int launch_multi_tensor(int op, const FatChunk *d_chunks, int64_t n_chunks, cons
     int64_t grid = (int64_t)sm_count * kCtasPerSm;  // whole waves: a multiple of the SM count
     if (grid > n_chunks) grid = n_chunks;
     switch (op) {
-        case OP_ADAM: launch_op<OP_ADAM>((unsigned)grid, d_chunks, n_chunks, d_present, all_present, s, stream); break;
-        case OP_SGD_MOMENTUM:
-            launch_op<OP_SGD_MOMENTUM>((unsigned)grid, d_chunks, n_chunks, d_present, all_present, s, stream);
+        case OP_ADAM:
+            launch_op<OP_ADAM>((unsigned)grid, d_chunks, n_chunks, d_present, all_present, s, peers, stream);
             break;
-        default: launch_op<OP_SGD>((unsigned)grid, d_chunks, n_chunks, d_present, all_present, s, stream); break;
+        case OP_SGD_MOMENTUM:
+            launch_op<OP_SGD_MOMENTUM>((unsigned)grid, d_chunks, n_chunks, d_present, all_present, s, peers, stream);
+            break;
+        default: launch_op<OP_SGD>((unsigned)grid, d_chunks, n_chunks, d_present, all_present, s, peers, stream); break;
     }
     VB_CUDA(cudaGetLastError());
     return VB_OK;

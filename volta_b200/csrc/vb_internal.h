@@ -61,6 +61,14 @@ struct alignas(16) FatChunk {
 };
 static_assert(sizeof(FatChunk) == 48, "FatChunk is fetched as three 16-byte words");
 
+// Peer GPUs' parameter arenas (same layout as the local one), mapped into this process.
+constexpr int kMaxPeers = 7;
+struct PeerTable {
+    float *base[kMaxPeers];
+    const float *local_base;
+    int n;
+};
+
 // Scalars of one step, computed on the host in f32 exactly as the reference does.
 struct StepScalars {
     float lr;
@@ -84,7 +92,8 @@ StepScalars make_scalars(int op, float lr, float beta1, float beta2, float eps, 
 // Launches the fused multi-tensor update over `n_chunks` chunks.  `present` holds one
 // byte per tensor (0 = gradient absent, skip).
 int launch_multi_tensor(int op, const FatChunk *d_chunks, int64_t n_chunks, const uint8_t *d_present,
-                        bool all_present, const StepScalars &s, int sm_count, cudaStream_t stream);
+                        bool all_present, const StepScalars &s, int sm_count, cudaStream_t stream,
+                        const PeerTable *peers = nullptr);
 
 // Device, SM count and stream of an engine / launch bookkeeping, for translation units that
 // do not see the engine's definition (api.cu).

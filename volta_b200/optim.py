@@ -277,6 +277,21 @@ class _Optimizer:
     def t(self, value: int) -> None:
         call("vb_optimizer_set_t", self._h, int(value))
 
+    # -- fused exchange over NVLink peer memory (sharded Adam / SGD) -------------------------
+    def ipc_handle(self) -> bytes:
+        """CUDA IPC handle (64 bytes) of this rank's parameter arena."""
+        buf = C.create_string_buffer(64)
+        call("vb_optimizer_ipc_handle", self._h, buf)
+        return buf.raw
+
+    def open_peers(self, handles: Sequence[bytes]) -> None:
+        """``handles[r]`` = rank r's ``ipc_handle()``.  Afterwards ``step()`` stores updated
+        parameters straight into the peers' arenas instead of running an all-gather."""
+        blob = b"".join(handles)
+        if len(blob) != 64 * len(handles):
+            raise ValueError("every handle must be 64 bytes")
+        call("vb_optimizer_open_peers", self._h, C.c_char_p(blob), len(handles))
+
     # -- whole-arena access (one transfer for all tensors) ---------------------------------
     def arena_layout(self):
         """(param_ptr, grad_ptr, arena_elements, offsets[n_tensors])."""
