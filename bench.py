@@ -416,6 +416,12 @@ def run_muon(args, eng, world, rank, dev, barrier, max_over_ranks, peaks):
             continue
         tensors = [Tensor(p, p.shape) for p in params]
         opt = Muon(tensors, h["lr"], h["momentum"], h["nesterov"], h["ns_steps"], ns_mode=mode, engine=eng)
+        if world > 1 and args.exchange == "peer":
+            mine = torch.frombuffer(bytearray(opt.ipc_handle()), dtype=torch.uint8).to(dev)
+            allh = torch.zeros(world * 64, dtype=torch.uint8, device=dev)
+            torch.distributed.all_gather_into_tensor(allh, mine)
+            blob = allh.cpu().numpy().tobytes()
+            opt.open_peers([blob[r * 64:(r + 1) * 64] for r in range(world)])
         _, _, arena, offsets = opt.arena_layout()
         host = fill_arena(wl, offsets, arena, grads)
         opt.upload_arena(1, host)

@@ -225,12 +225,12 @@ int vb_optimizer_zero_grad(vb_optimizer *opt);
 /* Hyper-parameters can change between steps (learning-rate schedules). */
 int vb_optimizer_set_lr(vb_optimizer *opt, float lr);
 
-/* Fused exchange over NVLink peer memory (Adam and SGD on a sharded engine; no counterpart in
- * the reference).  Every rank exports a CUDA IPC handle of its parameter arena, the host
+/* Fused exchange over NVLink peer memory (sharded engines; no counterpart in the reference).  Every rank exports a CUDA IPC handle of its parameter arena, the host
  * gathers the world_size handles in rank order (any transport) and hands them to every
- * rank.  From then on step() no longer runs an all-gather after the update: the update
- * kernel itself stores each new parameter into the local arena and into the same position of
- * every peer's arena, bracketed by two stream-ordered barriers (one-float NCCL all-reduces).
+ * rank.  From then on step() no longer runs an all-gather / broadcast after the update: the
+ * update kernel (Adam, SGD) or the apply kernel (Muon, for the matrices a rank owns) stores
+ * each new parameter into the local arena and into the same position of every peer's arena,
+ * bracketed by two stream-ordered barriers (one-float NCCL all-reduces).
  * All ranks must be processes on one node whose GPUs can reach each other (NVLink/NVSwitch). */
 #define VB_IPC_HANDLE_BYTES 64
 int vb_optimizer_ipc_handle(vb_optimizer *opt, void *handle64);

@@ -72,7 +72,7 @@ def _worker(rank, world, shared, kind):
     eng.close()
 
 
-@pytest.mark.parametrize("kind", ["adam", "sgd", "adam_peer", "sgd_peer", "muon_f32", "muon_bf16"])
+@pytest.mark.parametrize("kind", ["adam", "sgd", "adam_peer", "sgd_peer", "muon_f32", "muon_bf16", "muon_f32_peer", "muon_bf16_peer"])
 def test_two_gpu_sharded_step_matches_oracle(oracle, kind):
     if _gpu_count() < 2:
         pytest.skip("needs 2 GPUs")

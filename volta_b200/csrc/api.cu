@@ -862,7 +862,6 @@ int vb_optimizer_open_peers(vb_optimizer *opt, const void *handles, int n_handle
     if (n_handles != e->world)
         return fail(VB_ERR_INVALID_ARG, "expected %d handles (one per rank), got %d", e->world, n_handles);
     if (e->world - 1 > kMaxPeers) return fail(VB_ERR_UNSUPPORTED, "at most %d peers", kMaxPeers);
-    if (opt->kind == KIND_MUON) return fail(VB_ERR_UNSUPPORTED, "peer exchange is implemented for Adam and SGD");
     if (opt->peers.n > 0) return fail(VB_ERR_STATE, "peers are already open");
     VB_TRY(set_device(e));
     PeerTable pt{};

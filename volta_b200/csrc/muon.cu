@@ -318,15 +318,17 @@ normalise_kernel(const TensorDesc *__restrict__ tensors, const ChunkDesc *__rest
 // ---- K6: apply -----------------------------------------------------------------------------------
 // w -= lr * u * 0.1 (muon.rs:158-160; Rust evaluates (lr * u) * 0.1).  TensorDesc.g here points
 // at the buffer that holds the final update of the tensor.
+template <bool PEERS>
 __global__ void __launch_bounds__(kEwThreads)
 apply_kernel(const TensorDesc *__restrict__ tensors, const ChunkDesc *__restrict__ chunks, int64_t n_chunks,
-             const uint8_t *__restrict__ present, float lr)
+             const uint8_t *__restrict__ present, float lr, const PeerTable pt)
 {
     for (int64_t c = blockIdx.x; c < n_chunks; c += gridDim.x) {
         const ChunkDesc ch = chunks[c];
         if (present[ch.tensor] == 0) continue;
         float *__restrict__ w = tensors[ch.tensor].p + ch.offset;
         const float *__restrict__ u = tensors[ch.tensor].g + ch.offset;
+        const ptrdiff_t arena_pos = PEERS ? (w - pt.local_base) : 0;
         const uint32_t n = ch.len;
         const uint32_t n4 = n >> 2;
         for (uint32_t i = threadIdx.x; i < n4; i += kEwThreads) {
@@ -337,9 +339,21 @@ apply_kernel(const TensorDesc *__restrict__ tensors, const ChunkDesc *__restrict
             wv.z = __fsub_rn(wv.z, __fmul_rn(__fmul_rn(lr, uv.z), 0.1f));
             wv.w = __fsub_rn(wv.w, __fmul_rn(__fmul_rn(lr, uv.w), 0.1f));
             __stcs(reinterpret_cast<float4 *>(w) + i, wv);
+            if (PEERS) {  // the owner's new weights go straight into every peer's arena (NVLink stores)
+#pragma unroll
+                for (int r = 0; r < kMaxPeers; ++r)
+                    if (r < pt.n) reinterpret_cast<float4 *>(pt.base[r] + arena_pos)[i] = wv;
+            }
         }
-        for (uint32_t i = (n4 << 2) + threadIdx.x; i < n; i += kEwThreads)
-            w[i] = __fsub_rn(w[i], __fmul_rn(__fmul_rn(lr, u[i]), 0.1f));
+        for (uint32_t i = (n4 << 2) + threadIdx.x; i < n; i += kEwThreads) {
+            const float wv = __fsub_rn(w[i], __fmul_rn(__fmul_rn(lr, u[i]), 0.1f));
+            w[i] = wv;
+            if (PEERS) {
+#pragma unroll
+                for (int r = 0; r < kMaxPeers; ++r)
+                    if (r < pt.n) pt.base[r][arena_pos + i] = wv;
+            }
+        }
     }
 }
 
@@ -752,15 +766,32 @@ int muon_step(vb_optimizer *opt, uint32_t flags)
             VB_CUDA(cudaMemcpyAsync(s->h_error, s->d_error, sizeof(int), cudaMemcpyDeviceToHost, e->stream));
     }
     prof_end(e, VB_PHASE_MUON_PRE);  // no-op if already closed (no Newton-Schulz matrices)
+    const bool exchange = e->world > 1 && !(flags & VB_STEP_NO_EXCHANGE);
+    const bool fused = exchange && opt->peers.n > 0;
+    if (fused) {  // see vb_optimizer_step_ex: nobody is written to before it has reached its step
+        prof_begin(e, VB_PHASE_EXCHANGE);
+        VB_TRY(comm_barrier(e));
+        prof_end(e, VB_PHASE_EXCHANGE);
+    }
     if (s->n_chunks > 0) {
         prof_begin(e, VB_PHASE_MUON_APPLY);
-        apply_kernel<<<ew_grid, kEwThreads, 0, e->stream>>>(s->d_desc_apply, s->d_chunks, s->n_chunks,
-                                                           opt->d_present, opt->lr);
+        if (fused)
+            apply_kernel<true><<<ew_grid, kEwThreads, 0, e->stream>>>(s->d_desc_apply, s->d_chunks, s->n_chunks,
+                                                                     opt->d_present, opt->lr, opt->peers);
+        else
+            apply_kernel<false><<<ew_grid, kEwThreads, 0, e->stream>>>(s->d_desc_apply, s->d_chunks, s->n_chunks,
+                                                                      opt->d_present, opt->lr, PeerTable{});
         VB_CUDA(cudaGetLastError());
         prof_end(e, VB_PHASE_MUON_APPLY);
         e->launches += 1;
     }
-    if (e->world > 1 && !(flags & VB_STEP_NO_EXCHANGE)) {
+    if (fused) {
+        prof_begin(e, VB_PHASE_EXCHANGE);
+        VB_TRY(comm_barrier(e));
+        prof_end(e, VB_PHASE_EXCHANGE);
+        return VB_OK;
+    }
+    if (exchange) {
         // every matrix from its owner; all ranks must hold the same gradient-presence flags
         std::vector<BcastItem> items;
         for (int64_t i = 0; i < opt->n_tensors; ++i)
