@@ -280,10 +280,11 @@ def run_ours(args):
     e2e_steps = 0 if args.skip_e2e else max(3, min(args.steps, 10))
     barrier()
     t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        opt.upload_arena(1, grads_pinned.array)      # host -> device: this step's gradients
+    lo, hi = opt.owned_range()  # N > 1: a rank moves only its own slice over PCIe (what a reduce-scatter
+    for _ in range(e2e_steps):  # would hand it, and the parameters it updated)
+        opt.upload_arena_range(1, grads_pinned.array[lo:hi], lo)     # host -> device: this step's gradients
         opt.step()
-        opt.download_arena(0, params_pinned.array)   # device -> host: updated parameters (blocks)
+        opt.download_arena_range(0, params_pinned.array[lo:hi], lo)  # device -> host: updated parameters (blocks)
     barrier()
     e2e_s = max_over_ranks((time.perf_counter() - t0) / max(e2e_steps, 1))
 
@@ -324,7 +325,8 @@ def run_ours(args):
                      "algorithmic_bytes_per_launch": ADAM_BYTES_PER_PARAM * (wl.total // world),
                      "launch_ms": kernel_avg_ms},
         "e2e": {"value": wl.total / e2e_s, "unit": "params/s", "h2d_bytes_per_step": arena * 4,
-                "d2h_bytes_per_step": arena * 4, "ms_per_step": e2e_s * 1e3, "steps": e2e_steps},
+                "d2h_bytes_per_step": arena * 4, "ms_per_step": e2e_s * 1e3, "steps": e2e_steps,
+                "note": "bytes are totals over all ranks; each rank moves its own 1/N slice of the arena"},
         "gpu_launches": int(launches),
         "clocks": clocks,
     }

@@ -203,6 +203,14 @@ int vb_optimizer_arena(vb_optimizer *opt, void **param_arena, void **grad_arena,
 int vb_optimizer_upload_arena(vb_optimizer *opt, int which, const float *host, int64_t n);
 int vb_optimizer_download_arena(vb_optimizer *opt, int which, float *host, int64_t n);
 
+/* The same for a slice [begin, begin + n) of the arena: a rank of a sharded engine needs only
+ * the gradients of its own slice (what a reduce-scatter would deliver) and publishes only the
+ * parameters it updated.  Uploading a gradient slice marks every tensor's gradient present. */
+int vb_optimizer_upload_arena_range(vb_optimizer *opt, int which, const float *host, int64_t begin, int64_t n);
+int vb_optimizer_download_arena_range(vb_optimizer *opt, int which, float *host, int64_t begin, int64_t n);
+/* The slice of the arena whose state this rank owns (Adam/SGD; the whole arena for Muon). */
+int vb_optimizer_owned_range(vb_optimizer *opt, int64_t *begin, int64_t *end);
+
 /* Presence of a gradient: step() skips tensors whose gradient is absent
  * (src/nn/optim/adam.rs:81-84, sgd.rs:75-78, muon.rs:110). */
 int vb_optimizer_set_grad_present(vb_optimizer *opt, int64_t tensor, int present);

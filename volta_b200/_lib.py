@@ -79,6 +79,9 @@ SIGNATURES = {
     "vb_optimizer_arena": [_vp, _vpp, _vpp, _i64p, _i64p],
     "vb_optimizer_upload_arena": [_vp, C.c_int, _vp, _i64],
     "vb_optimizer_download_arena": [_vp, C.c_int, _vp, _i64],
+    "vb_optimizer_upload_arena_range": [_vp, C.c_int, _vp, _i64, _i64],
+    "vb_optimizer_download_arena_range": [_vp, C.c_int, _vp, _i64, _i64],
+    "vb_optimizer_owned_range": [_vp, _i64p, _i64p],
     "vb_optimizer_set_grad_present": [_vp, _i64, C.c_int],
     "vb_optimizer_step": [_vp],
     "vb_optimizer_step_ex": [_vp, C.c_uint32],

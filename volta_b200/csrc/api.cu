@@ -696,6 +696,45 @@ int vb_optimizer_download_arena(vb_optimizer *opt, int which, float *host, int64
     return VB_OK;
 }
 
+static int arena_range_copy(vb_optimizer *opt, int which, void *host, int64_t begin, int64_t n, bool to_device)
+{
+    VB_TRY(check_opt(opt));
+    if (which != 0 && which != 1) return fail(VB_ERR_INVALID_ARG, "which must be 0 (params) or 1 (grads)");
+    if (begin < 0 || n < 0 || begin + n > opt->arena)
+        return fail(VB_ERR_INVALID_ARG, "range [%lld, %lld) is outside the arena of %lld elements", (long long)begin,
+                    (long long)(begin + n), (long long)opt->arena);
+    if (n == 0) return VB_OK;
+    if (!host) return fail(VB_ERR_INVALID_ARG, "host pointer is null");
+    VB_TRY(set_device(opt->eng));
+    float *dev = (which == 0 ? opt->d_param : opt->d_grad) + begin;
+    if (to_device) {
+        VB_CUDA(cudaMemcpyAsync(dev, host, (size_t)n * sizeof(float), cudaMemcpyHostToDevice, opt->eng->stream));
+        if (which == 1) std::fill(opt->present.begin(), opt->present.end(), (uint8_t)1);
+    } else {
+        VB_CUDA(cudaMemcpyAsync(host, dev, (size_t)n * sizeof(float), cudaMemcpyDeviceToHost, opt->eng->stream));
+        VB_CUDA(cudaStreamSynchronize(opt->eng->stream));
+    }
+    return VB_OK;
+}
+
+int vb_optimizer_upload_arena_range(vb_optimizer *opt, int which, const float *host, int64_t begin, int64_t n)
+{
+    return arena_range_copy(opt, which, (void *)host, begin, n, true);
+}
+
+int vb_optimizer_download_arena_range(vb_optimizer *opt, int which, float *host, int64_t begin, int64_t n)
+{
+    return arena_range_copy(opt, which, host, begin, n, false);
+}
+
+int vb_optimizer_owned_range(vb_optimizer *opt, int64_t *begin, int64_t *end)
+{
+    VB_TRY(check_opt(opt));
+    if (begin) *begin = opt->shard_begin;
+    if (end) *end = opt->shard_end;
+    return VB_OK;
+}
+
 int vb_optimizer_set_grad_present(vb_optimizer *opt, int64_t tensor, int present)
 {
     VB_TRY(check_tensor(opt, tensor, 0, false));

@@ -311,6 +311,23 @@ class _Optimizer:
         assert host.dtype == np.float32 and host.flags.c_contiguous
         call("vb_optimizer_download_arena", self._h, which, host.ctypes.data_as(C.c_void_p), host.size)
 
+    def owned_range(self):
+        """[begin, end) of the arena whose state this rank owns."""
+        lo, hi = C.c_int64(), C.c_int64()
+        call("vb_optimizer_owned_range", self._h, C.byref(lo), C.byref(hi))
+        return int(lo.value), int(hi.value)
+
+    def upload_arena_range(self, which: int, host: np.ndarray, begin: int) -> None:
+        assert host.dtype == np.float32 and host.flags.c_contiguous
+        call("vb_optimizer_upload_arena_range", self._h, which, host.ctypes.data_as(C.c_void_p), int(begin), host.size)
+        if which == 1:
+            self._present = [True] * len(self.params)
+
+    def download_arena_range(self, which: int, host: np.ndarray, begin: int) -> None:
+        assert host.dtype == np.float32 and host.flags.c_contiguous
+        call("vb_optimizer_download_arena_range", self._h, which, host.ctypes.data_as(C.c_void_p), int(begin),
+             host.size)
+
     def mark_all_grads_present(self) -> None:
         for i in range(len(self.params)):
             if not self._present[i]:
