@@ -493,7 +493,7 @@ def run_muon(args, eng, world, rank, dev, barrier, max_over_ranks, peaks):
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of multi_tensor_update_kernel<ADAM>
 # on this workload, from the ncu capture summarised in profiles/adam_c3_multi_tensor_update.md
-NCU_ADAM_C3_DRAM_BYTES_PER_LAUNCH = 3.0138e9
+NCU_ADAM_C3_DRAM_BYTES_PER_LAUNCH = 3.0164e9
 
 
 def traffic_from_profile():

@@ -129,6 +129,14 @@ int vb_engine_launch_count(vb_engine *engine, uint64_t *count);
 int vb_engine_set_profiling(vb_engine *engine, int enabled);
 int vb_engine_profile(vb_engine *engine, int phase, double *total_ms, int64_t *count);
 
+/* Failure-detection self-test (the reference's counterpart is sync_checked()'s timeout path,
+ * src/gpu/context.rs:448-505).  Runs the tensor-core GEMM kernel on a small problem whose
+ * loads are withheld, so that every bounded wait inside the kernel expires after
+ * `wait_limit` polls (0 = default).  The kernel must then record which role gave up, free
+ * its tensor memory and return; this call reports VB_ERR_TIMEOUT with that role in
+ * *role_code, and the engine stays usable.  Nothing faults or hangs. */
+int vb_debug_gemm_wait_expiry(vb_engine *engine, uint32_t wait_limit, int *role_code);
+
 /* Page-locked host memory for upload/download buffers (pinned buffers make the copies
  * asynchronous and full speed; a pinned upload buffer must stay unchanged until the next
  * vb_engine_synchronize or download).  Counterpart: the staging buffer pool,

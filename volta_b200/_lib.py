@@ -58,6 +58,7 @@ SIGNATURES = {
     "vb_engine_launch_count": [_vp, C.POINTER(C.c_uint64)],
     "vb_engine_set_profiling": [_vp, C.c_int],
     "vb_engine_profile": [_vp, C.c_int, C.POINTER(C.c_double), _i64p],
+    "vb_debug_gemm_wait_expiry": [_vp, C.c_uint32, C.POINTER(C.c_int)],
     "vb_host_alloc_pinned": [_vpp, C.c_size_t],
     "vb_host_free_pinned": [_vp],
     "vb_comm_unique_id": [_vp],

@@ -432,6 +432,16 @@ int vb_engine_profile(vb_engine *e, int phase, double *total_ms, int64_t *count)
     VB_API_END
 }
 
+int vb_debug_gemm_wait_expiry(vb_engine *e, uint32_t wait_limit, int *role_code)
+{
+    VB_API_BEGIN
+    if (!e) return fail(VB_ERR_INVALID_ARG, "engine is null");
+    if (role_code) *role_code = 0;
+    VB_TRY(set_device(e));
+    return debug_gemm_wait_expiry(e, wait_limit, role_code);
+    VB_API_END
+}
+
 int vb_comm_unique_id(void *id128)
 {
     VB_API_BEGIN

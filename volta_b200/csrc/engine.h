@@ -84,6 +84,7 @@ int muon_step(vb_optimizer *opt, uint32_t flags);
 int muon_download_update(vb_optimizer *opt, int64_t tensor, float *host, int64_t n);
 int muon_last_flops(vb_optimizer *opt, double *flops);
 int muon_owner(vb_optimizer *opt, int64_t tensor);
+int debug_gemm_wait_expiry(vb_engine *e, uint32_t wait_limit, int *role_code);
 int muon_check_error(vb_optimizer *opt);  // VB_ERR_TIMEOUT if a GEMM kernel reported a bounded wait expiring
 float *muon_velocity_ptr(vb_optimizer *opt, int64_t tensor);  // nullptr if not owned
 void plan_muon_owners(int64_t n, const int64_t *rows, const int64_t *cols, int world, int *owner_out);

@@ -818,6 +818,68 @@ int muon_download_update(vb_optimizer *opt, int64_t tensor, float *host, int64_t
     return muon_check_error(opt);
 }
 
+// Launches the tensor-core GEMM on a small synthetic problem whose producer withholds its
+// loads, so every role's bounded wait expires, and reports what the kernel recorded.
+int debug_gemm_wait_expiry(vb_engine *e, uint32_t wait_limit, int *role_code)
+{
+    const int n = 256;
+    __nv_bfloat16 *x = nullptr, *c = nullptr;
+    TcGemmProblem *d_prob = nullptr;
+    GemmTile *d_tile = nullptr;
+    uint8_t *d_present = nullptr;
+    int *d_err = nullptr;
+    int status = VB_OK, code = 0;
+    auto cleanup = [&]() {
+        cudaFree(x); cudaFree(c); cudaFree(d_prob); cudaFree(d_tile); cudaFree(d_present); cudaFree(d_err);
+    };
+#define VB_DBG_CUDA(expr)                                                                        \
+    do {                                                                                         \
+        cudaError_t _e = (expr);                                                                 \
+        if (_e != cudaSuccess) {                                                                 \
+            cleanup();                                                                           \
+            return fail(VB_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(_e));            \
+        }                                                                                        \
+    } while (0)
+    VB_DBG_CUDA(cudaMalloc(&x, (size_t)n * n * 2));
+    VB_DBG_CUDA(cudaMalloc(&c, (size_t)n * n * 2));
+    VB_DBG_CUDA(cudaMemsetAsync(x, 0, (size_t)n * n * 2, e->stream));
+    VB_DBG_CUDA(cudaMalloc(&d_prob, sizeof(TcGemmProblem)));
+    VB_DBG_CUDA(cudaMalloc(&d_tile, sizeof(GemmTile)));
+    VB_DBG_CUDA(cudaMalloc(&d_present, 1));
+    VB_DBG_CUDA(cudaMalloc(&d_err, sizeof(int)));
+    VB_DBG_CUDA(cudaMemsetAsync(d_present, 1, 1, e->stream));
+    VB_DBG_CUDA(cudaMemsetAsync(d_err, 0, sizeof(int), e->stream));
+    TcGemmProblem p{};
+    status = make_bf16_tensor_map(&p.map_a, x, n, n, TC_OP_K_MAJOR);
+    if (status == VB_OK) status = make_bf16_tensor_map(&p.map_b, x, n, n, TC_OP_K_MAJOR);
+    if (status != VB_OK) {
+        cleanup();
+        return status;
+    }
+    p.M = p.N = p.K = n;
+    p.a_mode = p.b_mode = TC_OP_K_MAJOR;
+    p.epilogue = TC_EPI_HALF;
+    p.ld_out = n;
+    p.tensor = 0;
+    p.withhold_loads = 1;
+    p.out_bf16 = c;
+    const GemmTile t{0, 0, 0, 0};
+    VB_DBG_CUDA(cudaMemcpyAsync(d_prob, &p, sizeof(p), cudaMemcpyHostToDevice, e->stream));
+    VB_DBG_CUDA(cudaMemcpyAsync(d_tile, &t, sizeof(t), cudaMemcpyHostToDevice, e->stream));
+    status = launch_ns_gemm_tc(d_prob, d_tile, 1, d_present, d_err, e->sm_count, e->stream, wait_limit);
+    if (status == VB_OK) {
+        VB_DBG_CUDA(cudaMemcpyAsync(&code, d_err, sizeof(int), cudaMemcpyDeviceToHost, e->stream));
+        VB_DBG_CUDA(cudaStreamSynchronize(e->stream));
+    }
+#undef VB_DBG_CUDA
+    cleanup();
+    if (status != VB_OK) return status;
+    if (role_code) *role_code = code;
+    if (code != 0)
+        return fail(VB_ERR_TIMEOUT, "a Newton-Schulz GEMM kernel gave up waiting on a pipeline barrier (role %d)", code);
+    return VB_OK;
+}
+
 int muon_last_flops(vb_optimizer *opt, double *flops)
 {
     *flops = opt->muon->last_flops;

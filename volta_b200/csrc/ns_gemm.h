@@ -52,12 +52,15 @@ struct alignas(128) TcGemmProblem {
     int32_t epilogue;
     int32_t ld_out;
     int32_t tensor;          // index into the optimizer's gradient-presence bytes
+    int32_t withhold_loads;  // test hook: the producer stages nothing, so the consumers' bounded waits expire
     __nv_bfloat16 *out_bf16; // may be null
     float *out_f32;          // may be null
 };
 
+// wait_limit: mbarrier polls before a role gives up (0 = the default, about a second).
 int launch_ns_gemm_tc(const TcGemmProblem *d_problems, const GemmTile *d_tiles, int n_tiles,
-                      const uint8_t *d_present, int *d_error_flag, int sm_count, cudaStream_t stream);
+                      const uint8_t *d_present, int *d_error_flag, int sm_count, cudaStream_t stream,
+                      uint32_t wait_limit = 0);
 void tc_gemm_tile_shape(int *bm, int *bn);
 int make_bf16_tensor_map(void *map_out, const void *base, int64_t inner, int64_t outer, int mode);
 int tc_mn_major_mode(int64_t inner);

@@ -56,7 +56,7 @@ constexpr int kAccCols = BN;                             // f32 columns per accu
 constexpr int kTmemCols = 2 * kAccCols;                  // 512: two accumulators
 constexpr int kEpiWarps = 8;                             // two per TMEM lane quarter, 128 columns each
 constexpr int kThreads = 64 + kEpiWarps * 32;            // producer warp + MMA warp + epilogue warps
-constexpr uint32_t kWaitLimit = 1u << 22;                // mbarrier polls before giving up
+constexpr uint32_t kDefaultWaitLimit = 1u << 22;         // mbarrier polls before giving up
 
 template <int kCtas>
 struct Cfg {
@@ -114,9 +114,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
     return ok != 0;
 }
 // Bounded wait.  Returns false if the barrier did not flip in time or another role aborted.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile uint32_t *abort_flag)
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile uint32_t *abort_flag,
+                                          uint32_t wait_limit)
 {
-    for (uint32_t i = 0; i < kWaitLimit; ++i) {
+    for (uint32_t i = 0; i < wait_limit; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 63u) == 63u && *abort_flag != 0u) return false;
     }
@@ -130,13 +131,13 @@ __device__ unsigned long long g_wait_cycles[16];
 __device__ __forceinline__ bool mbar_wait_timed(int site, uint64_t *bar, uint32_t parity, volatile uint32_t *abort_flag)
 {
     const long long t0 = clock64();
-    const bool ok = mbar_wait(bar, parity, abort_flag);
+    const bool ok = mbar_wait(bar, parity, abort_flag, kDefaultWaitLimit);
     if (blockIdx.x < 2) atomicAdd(&g_wait_cycles[site + 4 * (blockIdx.x & 1)], (unsigned long long)(clock64() - t0));
     return ok;
 }
 #define MBAR_WAIT(site, bar, parity) mbar_wait_timed(site, bar, parity, abort_flag)
 #else
-#define MBAR_WAIT(site, bar, parity) mbar_wait(bar, parity, abort_flag)
+#define MBAR_WAIT(site, bar, parity) mbar_wait(bar, parity, abort_flag, wait_limit)
 #endif
 
 __device__ __forceinline__ uint32_t cluster_ctarank()
@@ -315,7 +316,8 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b)
 struct TileInfo {
     const TcGemmProblem *p;
     int m0, n0, k_blocks, a_mode, b_mode;
-    bool skipped;  // gradient absent: nothing to do
+    bool skipped;   // gradient absent: nothing to do
+    bool withhold;  // test hook (TcGemmProblem::withhold_loads): the producer stages nothing
 };
 __device__ __forceinline__ TileInfo fetch_tile(const TcGemmProblem *problems, const GemmTile *tiles, int n_tiles,
                                                const uint8_t *present, int t)
@@ -324,6 +326,7 @@ __device__ __forceinline__ TileInfo fetch_tile(const TcGemmProblem *problems, co
     ti.p = problems;
     ti.m0 = ti.n0 = ti.k_blocks = ti.a_mode = ti.b_mode = 0;
     ti.skipped = true;
+    ti.withhold = false;
     if (t < n_tiles) {
         const GemmTile tile = tiles[t];
         const TcGemmProblem *p = problems + tile.problem;
@@ -334,6 +337,7 @@ __device__ __forceinline__ TileInfo fetch_tile(const TcGemmProblem *problems, co
         ti.a_mode = p->a_mode;
         ti.b_mode = p->b_mode;
         ti.skipped = present[p->tensor] == 0;
+        ti.withhold = p->withhold_loads != 0;
     }
     return ti;
 }
@@ -341,7 +345,7 @@ __device__ __forceinline__ TileInfo fetch_tile(const TcGemmProblem *problems, co
 template <int kCtas>
 __global__ void __launch_bounds__(kThreads, 1)
 ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__restrict__ tiles, int n_tiles,
-                  const uint8_t *__restrict__ present, int *__restrict__ error_flag)
+                  const uint8_t *__restrict__ present, int *__restrict__ error_flag, uint32_t wait_limit)
 {
     using C = Cfg<kCtas>;
     extern __shared__ uint8_t smem_raw[];
@@ -417,7 +421,10 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
                     const uint32_t full_bar =
                         kCtas == 2 ? map_to_cta(smem_u32(&bars->full[stage]), 0) : smem_u32(&bars->full[stage]);
                     const int k0 = kb * BK;
-                    if (lane == 0) {
+                    if (ti.withhold) {
+                        // Nothing is staged and no bytes are announced: the consumers' bounded waits
+                        // (and, a ring later, this thread's own) run out.  Used by the expiry test.
+                    } else if (lane == 0) {
                         if (cta_rank == 0) mbar_expect_tx(&bars->full[stage], kCtas * C::kStageBytes);
                         load_rows128<kCtas>(sa, &ti.p->map_a, ti.a_mode, a_row0, k0, full_bar);
                     } else {
@@ -685,9 +692,11 @@ int make_bf16_tensor_map(void *map_out, const void *base, int64_t inner, int64_t
 }
 
 int launch_ns_gemm_tc(const TcGemmProblem *d_problems, const GemmTile *d_tiles, int n_tiles,
-                      const uint8_t *d_present, int *d_error_flag, int sm_count, cudaStream_t stream)
+                      const uint8_t *d_present, int *d_error_flag, int sm_count, cudaStream_t stream,
+                      uint32_t wait_limit)
 {
     if (n_tiles <= 0) return VB_OK;
+    if (wait_limit == 0) wait_limit = kDefaultWaitLimit;
     if (tc_use_pair()) {
         static bool attr_set = false;
         if (!attr_set) {
@@ -718,7 +727,8 @@ int launch_ns_gemm_tc(const TcGemmProblem *d_problems, const GemmTile *d_tiles, 
         int clusters = max_clusters;
         if (clusters > n_tiles) clusters = n_tiles;
         cfg.gridDim = dim3((unsigned)(clusters * 2));
-        VB_CUDA(cudaLaunchKernelEx(&cfg, ns_gemm_tc_kernel<2>, d_problems, d_tiles, n_tiles, d_present, d_error_flag));
+        VB_CUDA(cudaLaunchKernelEx(&cfg, ns_gemm_tc_kernel<2>, d_problems, d_tiles, n_tiles, d_present, d_error_flag,
+                                   wait_limit));
         return VB_OK;
     }
     static bool attr_set1 = false;
@@ -730,7 +740,7 @@ int launch_ns_gemm_tc(const TcGemmProblem *d_problems, const GemmTile *d_tiles, 
     int grid = sm_count;  // one persistent CTA per SM (it owns all 512 TMEM columns)
     if (grid > n_tiles) grid = n_tiles;
     ns_gemm_tc_kernel<1><<<grid, kThreads, smem_bytes<1>(), stream>>>(d_problems, d_tiles, n_tiles, d_present,
-                                                                     d_error_flag);
+                                                                     d_error_flag, wait_limit);
     VB_CUDA(cudaGetLastError());
     return VB_OK;
 }
