@@ -406,15 +406,18 @@ def run_muon(args, eng, world, rank, dev, barrier, max_over_ranks, peaks):
     """Muon on the 96 matrices of the 24-layer d=1024 configuration: NS TFLOP/s."""
     import torch
 
-    from volta_b200 import VB_NS_BF16, VB_NS_F32, Muon, Tensor
+    from volta_b200 import VB_NS_BF16, VB_NS_F32, VB_NS_F32_TC, Muon, Tensor
 
     wl = workloads.c4_muon(layers=args.muon_layers)
     h = wl.hyper
     params = wl.make_params()
     grads = wl.make_grads(1)
     out = {}
-    for mode_name, mode, steps in (("bf16", VB_NS_BF16, max(3, min(args.steps, 20))), ("f32", VB_NS_F32, 2)):
+    for mode_name, mode, steps in (("bf16", VB_NS_BF16, max(3, min(args.steps, 20))),
+                                   ("f32_tc", VB_NS_F32_TC, max(3, min(args.steps, 5))), ("f32", VB_NS_F32, 2)):
         if mode_name == "f32" and (args.skip_muon_f32 or args.only_muon):
+            continue
+        if mode_name == "f32_tc" and args.only_muon and not args.muon_f32_tc:
             continue
         tensors = [Tensor(p, p.shape) for p in params]
         opt = Muon(tensors, h["lr"], h["momentum"], h["nesterov"], h["ns_steps"], ns_mode=mode, engine=eng)
@@ -429,7 +432,7 @@ def run_muon(args, eng, world, rank, dev, barrier, max_over_ranks, peaks):
         opt.upload_arena(1, host)
         del host
         eng.synchronize()
-        warm = 3 if mode_name == "bf16" else 1
+        warm = 1 if mode_name == "f32" else 3
         for _ in range(warm):
             opt.step()
         barrier()
@@ -466,6 +469,9 @@ def run_muon(args, eng, world, rank, dev, barrier, max_over_ranks, peaks):
             "pre_ms": pre_ms, "apply_ms": apply_ms, "exchange_ms": exch_ms,
             "params_per_s": wl.total / (step_ms * 1e-3), "steps": steps,
             "executed_flops_per_step": flops_total,
+            "note": {"bf16": "tcgen05 bf16, short-side Gram", "f32": "CUDA-core FFMA, bit-identical to the CPU arithmetic",
+                     "f32_tc": "tcgen05, operands split into three bf16 planes (six products per product); "
+                               "ns_tflops counts executed bf16 tensor FLOPs"}[mode_name],
             "reference_formulation_flops_per_step": sum(4.0 * r * c * c * h["ns_steps"] for r, c in wl.shapes),
             "gpu_launches": int(eng.launch_count - launches0),
         }
@@ -515,6 +521,7 @@ def main():
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="N > 1: updated parameters reach the other ranks by NVLink peer stores fused into the "
                          "update kernel (default) or by an NCCL all-gather after it")
+    ap.add_argument("--muon-f32-tc", action="store_true", help="with --only-muon: also time the f32-accurate TC path")
     ap.add_argument("--muon-layers", type=int, default=24, help="profiling runs: fewer layers of the Muon set")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":

@@ -67,7 +67,12 @@ typedef enum vb_ns_mode {
     VB_NS_F32 = 0,
     /* bf16 operands on the tcgen05 tensor cores, f32 accumulation in TMEM.
      * Target: relative Frobenius error <= 2e-2 per matrix. */
-    VB_NS_BF16 = 1
+    VB_NS_BF16 = 1,
+    /* f32-accurate on the tensor cores: every operand is split into three bf16 pieces
+     * (24 significand bits) and each product is six tcgen05 bf16 products accumulated in f32;
+     * the sum of squares keeps the reference's sequential order.  Same target as VB_NS_F32
+     * (<= 1e-5) at tensor-core speed, but not bit-identical to the CPU arithmetic. */
+    VB_NS_F32_TC = 2
 } vb_ns_mode;
 
 /* Flags of vb_optimizer_step_ex. */

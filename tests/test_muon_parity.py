@@ -221,3 +221,38 @@ def test_bf16_path_c4_layer_shapes(oracle, engine):
         err = rel_frobenius(opt.last_update(i), ref)
         assert err <= TOL_BF16, (s, err)
     opt.close()
+
+
+# ---- f32-accurate tensor-core path (three-way bf16 split) ---------------------------------------
+
+@pytest.mark.parametrize("shapes", [[(256, 128)], [(128, 384), (512, 512)], [(200, 72), (64, 36), (50,)], [(1032, 264)]])
+def test_f32_tc_path_meets_f32_tolerance(oracle, engine, shapes):
+    """VB_NS_F32_TC: operands split into three bf16 planes, six tensor-core products per product,
+    ordered sum of squares.  Same 1e-5 bound as the bit-faithful path (shapes whose rows are
+    not 16-byte aligned in bf16 run the bit-faithful kernels inside the same optimizer)."""
+    from volta_b200 import VB_NS_F32_TC
+    res = _run(oracle, engine, shapes, 3, VB_NS_F32_TC)
+    for r in res:
+        assert r["update"] <= TOL_F32, res
+        assert r["velocity_exact"]
+
+
+def test_f32_tc_path_c4_layer_shapes(oracle, engine):
+    """One layer of the benchmark configuration at full size on the f32-accurate tensor-core
+    path, against the f32 oracle and its f64-accumulating variant."""
+    from volta_b200 import VB_NS_F32_TC, Muon, Tensor
+    oracle.set_threads(oracle.max_threads())
+    shapes = [(3072, 1024), (1024, 1024), (4096, 1024)]
+    rng = np.random.default_rng(12)
+    grads = [(rng.standard_normal(s) * 1e-3).astype(np.float32) for s in shapes]
+    tensors = [Tensor((rng.standard_normal(s) * 0.02).astype(np.float32)) for s in shapes]
+    opt = Muon(tensors, 0.1, 0.9, True, 5, ns_mode=VB_NS_F32_TC, engine=engine)
+    for t, g in zip(tensors, grads):
+        t.grad = g
+    opt.step()
+    for i, g in enumerate(grads):
+        u = np.float32(0.9) * g + g
+        got = opt.last_update(i)
+        assert rel_frobenius(got, oracle.newton_schulz(u, 5)) <= TOL_F32
+        assert rel_frobenius(got, oracle.newton_schulz(u, 5, gemm_mode=1)) <= TOL_F32
+    opt.close()

@@ -18,6 +18,7 @@ STATUS_NAMES = {
 
 VB_NS_F32 = 0
 VB_NS_BF16 = 1
+VB_NS_F32_TC = 2
 VB_STEP_DEFAULT = 0
 VB_STEP_NO_EXCHANGE = 1
 

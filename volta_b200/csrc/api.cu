@@ -533,7 +533,7 @@ int vb_muon_create(vb_engine *engine, int64_t n_tensors, const int64_t *rows, co
     if (n_tensors < 0 || (n_tensors > 0 && (!rows || !cols)))
         return fail(VB_ERR_INVALID_ARG, "rows/cols is null or n_tensors negative");
     if (ns_steps < 0) return fail(VB_ERR_INVALID_ARG, "ns_steps is negative");
-    if (ns_mode != VB_NS_F32 && ns_mode != VB_NS_BF16)
+    if (ns_mode != VB_NS_F32 && ns_mode != VB_NS_BF16 && ns_mode != VB_NS_F32_TC)
         return fail(VB_ERR_INVALID_ARG, "unknown ns_mode %d", ns_mode);
     std::vector<int64_t> sizes((size_t)n_tensors);
     for (int64_t i = 0; i < n_tensors; ++i) {

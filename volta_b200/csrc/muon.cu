@@ -271,11 +271,13 @@ sumsq_ordered_kernel(const TensorDesc *__restrict__ tensors, const int32_t *__re
 // ---- K3b: normalise ----------------------------------------------------------------------------
 // x = u / sqrt(sumsq + 1e-8) where the norm exceeds 1e-8 (muon.rs:59-64).  Per tensor
 // (ns_kind): 1 = rewrite the f32 update buffer in place (operand of the f32 GEMMs, and the
-// final update when ns_steps == 0), 2 = write the bf16 operand of the first tensor-core GEMM.
+// final update when ns_steps == 0), 2 = write the bf16 operand of the first tensor-core GEMM,
+// 3 = write that operand split into three bf16 planes x = x0 + x1 + x2 (f32-accurate path).
 __global__ void __launch_bounds__(kEwThreads)
 normalise_kernel(const TensorDesc *__restrict__ tensors, const ChunkDesc *__restrict__ chunks, int64_t n_chunks,
                  const uint8_t *__restrict__ present, const uint8_t *__restrict__ ns_kind,
-                 const float *__restrict__ sumsq, const float *upd_base, __nv_bfloat16 *__restrict__ xb_base)
+                 const float *__restrict__ sumsq, const float *upd_base, __nv_bfloat16 *__restrict__ xb_base,
+                 int64_t plane_stride)
 {
     for (int64_t c = blockIdx.x; c < n_chunks; c += gridDim.x) {
         const ChunkDesc ch = chunks[c];
@@ -286,7 +288,18 @@ normalise_kernel(const TensorDesc *__restrict__ tensors, const ChunkDesc *__rest
         const bool scale = norm > 1e-8f;
         const uint32_t n = ch.len;
         const uint32_t n4 = n >> 2;
-        if (kind == 2) {
+        if (kind == 3) {
+            __nv_bfloat16 *xb = xb_base + (u - upd_base);
+            for (uint32_t i = threadIdx.x; i < n; i += kEwThreads) {
+                float x = scale ? __fdiv_rn(u[i], norm) : u[i];
+#pragma unroll
+                for (int pl = 0; pl < 3; ++pl) {
+                    const __nv_bfloat16 b = __float2bfloat16_rn(x);
+                    xb[pl * plane_stride + i] = b;
+                    x -= __bfloat162float(b);  // exact: the residual fits in f32
+                }
+            }
+        } else if (kind == 2) {
             __nv_bfloat16 *xb = xb_base + (u - upd_base);
             for (uint32_t i = threadIdx.x; i < n4; i += kEwThreads) {
                 float4 v = reinterpret_cast<const float4 *>(u)[i];
@@ -372,7 +385,10 @@ int upload(T **d, const std::vector<T> &h, cudaStream_t stream)
 struct MuonState {
     std::vector<int> owner;           // per tensor
     std::vector<int64_t> local_off;   // per tensor: offset into this rank's buffers, -1 if not owned
-    std::vector<uint8_t> ns_kind;     // per tensor: 0 no Newton-Schulz, 1 f32 CUDA-core path, 2 bf16 tensor-core path
+    std::vector<uint8_t> ns_kind;     // per tensor: 0 no Newton-Schulz, 1 f32 CUDA-core path, 2 bf16 tensor-core
+                                      // path, 3 split-bf16 (f32-accurate) tensor-core path
+    int planes = 1;                   // bf16 planes per tensor-core operand (3 on the split path)
+    int64_t cb_elems = 0;             // elements of one plane of the C buffer
     int64_t owned_elems = 0;
     float *d_upd = nullptr;           // update buffer u / X (f32), owned tensors
     float *d_xnext = nullptr;         // f32 path: the other Newton-Schulz buffer
@@ -502,8 +518,8 @@ int muon_init(vb_optimizer *opt)
         if (ns) {
             // The tensor-core path needs 16-byte aligned bf16 rows for TMA; other shapes of a
             // bf16-mode optimizer run the (more accurate) f32 path.
-            const bool tc = opt->ns_mode == VB_NS_BF16 && opt->ns_steps > 0 && (r % 8) == 0 && (c % 8) == 0;
-            s->ns_kind[(size_t)i] = tc ? 2 : 1;
+            const bool tc = opt->ns_mode != VB_NS_F32 && opt->ns_steps > 0 && (r % 8) == 0 && (c % 8) == 0;
+            s->ns_kind[(size_t)i] = !tc ? 1 : (opt->ns_mode == VB_NS_F32_TC ? 3 : 2);
         }
         if (s->owner[(size_t)i] != e->rank) continue;
         s->local_off[(size_t)i] = off;
@@ -511,7 +527,7 @@ int muon_init(vb_optimizer *opt)
         if (ns && opt->sizes[i] > 0) {
             if (r > 0x7fffffff || c > 0x7fffffff) return fail(VB_ERR_UNSUPPORTED, "matrix %lld is too large", (long long)i);
             ns_tensors.push_back((int32_t)i);
-            if (s->ns_kind[(size_t)i] == 2) {
+            if (s->ns_kind[(size_t)i] >= 2) {
                 tc_tensors.push_back((int32_t)i);
                 const int64_t sh = std::min(r, c);
                 cb_off[(size_t)i] = cb_elems;
@@ -575,13 +591,16 @@ int muon_init(vb_optimizer *opt)
         VB_CUDA(cudaMalloc(&s->d_xnext, owned_bytes));
         VB_CUDA(cudaMalloc(&s->d_gram, (size_t)std::max<int64_t>(gram_elems, 1) * sizeof(float)));
     }
+    s->planes = opt->ns_mode == VB_NS_F32_TC ? 3 : 1;
+    s->cb_elems = cb_elems;
     if (!tc_tensors.empty()) {
-        const size_t xb_bytes = (size_t)std::max<int64_t>(off, 1) * sizeof(__nv_bfloat16);
+        const size_t xb_bytes = (size_t)s->planes * (size_t)std::max<int64_t>(off, 1) * sizeof(__nv_bfloat16);
         for (int i = 0; i < 2; ++i) {
             VB_CUDA(cudaMalloc(&s->d_xb[i], xb_bytes));
             VB_CUDA(cudaMemsetAsync(s->d_xb[i], 0, xb_bytes, e->stream));
         }
-        VB_CUDA(cudaMalloc(&s->d_cb, (size_t)std::max<int64_t>(cb_elems, 1) * sizeof(__nv_bfloat16)));
+        VB_CUDA(cudaMalloc(&s->d_cb, (size_t)s->planes * (size_t)std::max<int64_t>(cb_elems, 1) *
+                                         sizeof(__nv_bfloat16)));
     }
     // where the final update of each tensor lives after a step
     std::vector<TensorDesc> desc_apply = desc;
@@ -652,11 +671,13 @@ int muon_init(vb_optimizer *opt)
             // X is fetched K-major (rows = m or n) or MN-major (rows = k) depending on the product
             const int mn_mode = tc_mn_major_mode(c);
             CUtensorMap map_x_k[2], map_x_mn[2], map_c;
+            const int planes = s->planes;
+            const int n_terms = planes == 3 ? 6 : 1;
             for (int par = 0; par < 2; ++par) {
-                VB_TRY(make_bf16_tensor_map(&map_x_k[par], xb[par], c, r, TC_OP_K_MAJOR));
-                VB_TRY(make_bf16_tensor_map(&map_x_mn[par], xb[par], c, r, mn_mode));
+                VB_TRY(make_bf16_tensor_map(&map_x_k[par], xb[par], c, r, TC_OP_K_MAJOR, planes, s->owned_elems));
+                VB_TRY(make_bf16_tensor_map(&map_x_mn[par], xb[par], c, r, mn_mode, planes, s->owned_elems));
             }
-            VB_TRY(make_bf16_tensor_map(&map_c, cb, sh, sh, TC_OP_K_MAJOR));
+            VB_TRY(make_bf16_tensor_map(&map_c, cb, sh, sh, TC_OP_K_MAJOR, planes, s->cb_elems));
             const int pidx = (int)gram[0].size();
             for (int par = 0; par < 2; ++par) {
                 // C = 3I - X^T X (tall: both operands are X read with k = row index, "MN-major")
@@ -668,6 +689,7 @@ int muon_init(vb_optimizer *opt)
                 g.a_mode = tall ? mn_mode : TC_OP_K_MAJOR;
                 g.b_mode = g.a_mode;
                 g.epilogue = TC_EPI_THREE_I_MINUS; g.ld_out = sh; g.tensor = t;
+                g.n_terms = n_terms; g.n_out_planes = planes; g.out_plane_stride = s->cb_elems;
                 g.out_bf16 = cb; g.out_f32 = nullptr;
                 gram[par].push_back(g);
                 // X' = 0.5 X C (tall: A = X K-major, B = C which is symmetric)
@@ -679,6 +701,7 @@ int muon_init(vb_optimizer *opt)
                 u.a_mode = TC_OP_K_MAJOR;
                 u.b_mode = tall ? TC_OP_K_MAJOR : mn_mode;
                 u.epilogue = TC_EPI_HALF; u.ld_out = c; u.tensor = t;
+                u.n_terms = n_terms; u.n_out_planes = planes; u.out_plane_stride = s->owned_elems;
                 u.out_bf16 = xb[par ^ 1]; u.out_f32 = nullptr;
                 upd[par].push_back(u);
                 if (par == final_par) {
@@ -691,7 +714,9 @@ int muon_init(vb_optimizer *opt)
                 for (int n0 = 0; n0 < sh; n0 += bn) gram_tiles.push_back(GemmTile{pidx, m0, n0, 0});
             for (int m0 = 0; m0 < r; m0 += bm)
                 for (int n0 = 0; n0 < c; n0 += bn) upd_tiles.push_back(GemmTile{pidx, m0, n0, 0});
-            s->flops_per_step += 4.0 * (double)std::max(r, c) * (double)sh * (double)sh * (double)opt->ns_steps;
+            // executed tensor-core FLOPs: six plane products per product on the split path
+            s->flops_per_step += (double)n_terms * 4.0 * (double)std::max(r, c) * (double)sh * (double)sh *
+                                 (double)opt->ns_steps;
         }
         for (int par = 0; par < 2; ++par) {
             VB_TRY(upload(&s->d_tc_gram[par], gram[par], e->stream));
@@ -714,7 +739,7 @@ int muon_step(vb_optimizer *opt, uint32_t flags)
     VB_TRY(muon_check_error(opt));
     VB_TRY(sync_present(opt));
     const int ew_grid = (int)std::min<int64_t>(std::max<int64_t>(s->n_chunks, 1), (int64_t)e->sm_count * 8);
-    const bool fast_norm = opt->ns_mode == VB_NS_BF16;
+    const bool fast_norm = opt->ns_mode == VB_NS_BF16;  // both f32 modes need the reference's ordered sum
     prof_begin(e, VB_PHASE_MUON_PRE);
     if (s->n_chunks > 0) {
         if (fast_norm)
@@ -737,7 +762,8 @@ int muon_step(vb_optimizer *opt, uint32_t flags)
                                                                         opt->d_present, s->d_sumsq);
         VB_CUDA(cudaGetLastError());
         normalise_kernel<<<ew_grid, kEwThreads, 0, e->stream>>>(s->d_desc, s->d_chunks, s->n_chunks, opt->d_present,
-                                                               s->d_ns_kind, s->d_sumsq, s->d_upd, s->d_xb[0]);
+                                                               s->d_ns_kind, s->d_sumsq, s->d_upd, s->d_xb[0],
+                                                               s->owned_elems);
         VB_CUDA(cudaGetLastError());
         e->launches += 2;
         prof_end(e, VB_PHASE_MUON_PRE);
@@ -861,6 +887,8 @@ int debug_gemm_wait_expiry(vb_engine *e, uint32_t wait_limit, int *role_code)
     p.epilogue = TC_EPI_HALF;
     p.ld_out = n;
     p.tensor = 0;
+    p.n_terms = 1;
+    p.n_out_planes = 1;
     p.withhold_loads = 1;
     p.out_bf16 = c;
     const GemmTile t{0, 0, 0, 0};

@@ -53,6 +53,9 @@ struct alignas(128) TcGemmProblem {
     int32_t ld_out;
     int32_t tensor;          // index into the optimizer's gradient-presence bytes
     int32_t withhold_loads;  // test hook: the producer stages nothing, so the consumers' bounded waits expire
+    int32_t n_terms;         // 1: plain bf16 operands; 6: operands split into three bf16 planes (f32-accurate)
+    int32_t n_out_planes;    // planes written to out_bf16: 1 (bf16 rounding) or 3 (split)
+    int64_t out_plane_stride;  // elements between output planes
     __nv_bfloat16 *out_bf16; // may be null
     float *out_f32;          // may be null
 };
@@ -62,7 +65,8 @@ int launch_ns_gemm_tc(const TcGemmProblem *d_problems, const GemmTile *d_tiles, 
                       const uint8_t *d_present, int *d_error_flag, int sm_count, cudaStream_t stream,
                       uint32_t wait_limit = 0);
 void tc_gemm_tile_shape(int *bm, int *bn);
-int make_bf16_tensor_map(void *map_out, const void *base, int64_t inner, int64_t outer, int mode);
+int make_bf16_tensor_map(void *map_out, const void *base, int64_t inner, int64_t outer, int mode, int planes = 1,
+                         int64_t plane_stride = 0);
 int tc_mn_major_mode(int64_t inner);
 
 int launch_ns_gemm_f32(const F32GemmProblem *d_problems, const GemmTile *d_tiles, int n_tiles,

@@ -161,21 +161,6 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t local, uint32_t rank)
 // TMA loads into this CTA's shared memory.  `bar` is a shared::cluster address: this CTA's own
 // barrier, or (kCtas == 2, .cta_group::2) the leader's.  Every CTA fetches its own rows.
 template <int kCtas>
-__device__ __forceinline__ void tma_load_2d(void *smem_dst, const CUtensorMap *map, int c0, int c1, uint32_t bar)
-{
-    if (kCtas == 2)
-        asm volatile(
-            "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
-            "[%0], [%1, {%2, %3}], [%4];"
-            ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(bar)
-            : "memory");
-    else
-        asm volatile(
-            "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-            ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(bar)
-            : "memory");
-}
-template <int kCtas>
 __device__ __forceinline__ void tma_load_3d(void *smem_dst, const CUtensorMap *map, int c0, int c1, int c2,
                                             uint32_t bar)
 {
@@ -192,23 +177,44 @@ __device__ __forceinline__ void tma_load_3d(void *smem_dst, const CUtensorMap *m
             ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
             : "memory");
 }
-// Stages 128 operand rows x 64 k (16 KiB) with as few TMA instructions as the layout allows:
-// the issuing thread is the scarce resource (every instruction costs it a few hundred cycles).
+template <int kCtas>
+__device__ __forceinline__ void tma_load_4d(void *smem_dst, const CUtensorMap *map, int c0, int c1, int c2, int c3,
+                                            uint32_t bar)
+{
+    if (kCtas == 2)
+        asm volatile(
+            "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+            "[%0], [%1, {%2, %3, %4, %5}], [%6];"
+            ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(c3),
+            "r"(bar)
+            : "memory");
+    else
+        asm volatile(
+            "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes "
+            "[%0], [%1, {%2, %3, %4, %5}], [%6];"
+            ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(c3),
+            "r"(bar)
+            : "memory");
+}
+// Stages 128 operand rows x 64 k (16 KiB) of plane `plane` with as few TMA instructions as the
+// layout allows: the issuing thread is the scarce resource (every instruction costs it a few
+// hundred cycles).  The outermost tensor-map dimension selects the plane (one plane for plain
+// bf16 operands, three for operands split into bf16 pieces).
 //   TC_OP_K_MAJOR   one 64 x 128 box of a [rows][k] matrix
 //   TC_OP_MN_BOXES  two 64 x 64 boxes of a [k][rows] matrix (any row count)
 //   TC_OP_MN_3D     one 64 x 64 x 2 box of the same matrix viewed as [rows/64][k][64]
 // All three leave the same image in shared memory.
 template <int kCtas>
 __device__ __forceinline__ void load_rows128(uint8_t *dst, const CUtensorMap *map, int mode, int row0, int k0,
-                                             uint32_t bar)
+                                             int plane, uint32_t bar)
 {
     if (mode == TC_OP_K_MAJOR) {
-        tma_load_2d<kCtas>(dst, map, k0, row0, bar);
+        tma_load_3d<kCtas>(dst, map, k0, row0, plane, bar);
     } else if (mode == TC_OP_MN_3D) {
-        tma_load_3d<kCtas>(dst, map, 0, k0, row0 >> 6, bar);
+        tma_load_4d<kCtas>(dst, map, 0, k0, row0 >> 6, plane, bar);
     } else {
-        tma_load_2d<kCtas>(dst, map, row0, k0, bar);
-        tma_load_2d<kCtas>(dst + kBoxBytes, map, row0 + kBoxRows, k0, bar);
+        tma_load_3d<kCtas>(dst, map, row0, k0, plane, bar);
+        tma_load_3d<kCtas>(dst + kBoxBytes, map, row0 + kBoxRows, k0, plane, bar);
     }
 }
 
@@ -311,11 +317,20 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b)
     return *reinterpret_cast<uint32_t *>(&h);
 }
 
+// Operands split into three bf16 planes x = x0 + x1 + x2 (each the bf16 rounding of what the
+// previous ones left over, 24 significand bits in all) give an f32-accurate product on the bf16
+// tensor cores: the six plane products below are accumulated (smallest first) into the same f32
+// accumulator; the dropped products x1*y2, x2*y1, x2*y2 are below 2^-24 relative.
+// Terms in issue order, (plane of A, plane of B): (0,2) (2,0) (1,1) (0,1) (1,0) (0,0); one
+// nibble per term, term 0 in the lowest nibble.
+__device__ __forceinline__ int term_plane_a(int n_terms, int term) { return n_terms == 1 ? 0 : ((0x010120 >> (4 * term)) & 15); }
+__device__ __forceinline__ int term_plane_b(int n_terms, int term) { return n_terms == 1 ? 0 : ((0x001102 >> (4 * term)) & 15); }
+
 // What a role needs to know about a tile, fetched one tile ahead so that the dependent global
 // loads (tile -> problem -> fields) never sit between two tiles' main loops.
 struct TileInfo {
     const TcGemmProblem *p;
-    int m0, n0, k_blocks, a_mode, b_mode;
+    int m0, n0, k_blocks, a_mode, b_mode, n_terms;
     bool skipped;   // gradient absent: nothing to do
     bool withhold;  // test hook (TcGemmProblem::withhold_loads): the producer stages nothing
 };
@@ -325,6 +340,7 @@ __device__ __forceinline__ TileInfo fetch_tile(const TcGemmProblem *problems, co
     TileInfo ti;
     ti.p = problems;
     ti.m0 = ti.n0 = ti.k_blocks = ti.a_mode = ti.b_mode = 0;
+    ti.n_terms = 1;
     ti.skipped = true;
     ti.withhold = false;
     if (t < n_tiles) {
@@ -336,6 +352,7 @@ __device__ __forceinline__ TileInfo fetch_tile(const TcGemmProblem *problems, co
         ti.k_blocks = (p->K + BK - 1) / BK;
         ti.a_mode = p->a_mode;
         ti.b_mode = p->b_mode;
+        ti.n_terms = p->n_terms;
         ti.skipped = present[p->tensor] == 0;
         ti.withhold = p->withhold_loads != 0;
     }
@@ -407,7 +424,9 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
                 if (ti.skipped) continue;
                 const int a_row0 = ti.m0 + (int)cta_rank * BM;         // this CTA's rows of A
                 const int b_row0 = ti.n0 + (int)cta_rank * C::kBRows;  // this CTA's rows of B
-                for (int kb = 0; kb < ti.k_blocks; ++kb) {
+                const int n_slots = ti.k_blocks * ti.n_terms;  // every (k block, plane pair) fills one ring slot
+                int kb = 0, term = 0;
+                for (int slot = 0; slot < n_slots; ++slot) {
                     if (!MBAR_WAIT(0, &bars->empty[stage], phase ^ 1u)) {
                         ok = false;
                         break;
@@ -426,16 +445,21 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
                         // (and, a ring later, this thread's own) run out.  Used by the expiry test.
                     } else if (lane == 0) {
                         if (cta_rank == 0) mbar_expect_tx(&bars->full[stage], kCtas * C::kStageBytes);
-                        load_rows128<kCtas>(sa, &ti.p->map_a, ti.a_mode, a_row0, k0, full_bar);
+                        load_rows128<kCtas>(sa, &ti.p->map_a, ti.a_mode, a_row0, k0, term_plane_a(ti.n_terms, term),
+                                            full_bar);
                     } else {
 #pragma unroll
                         for (int j = 0; j < C::kBRows / 128; ++j)
                             load_rows128<kCtas>(sb + j * kRows128Bytes, &ti.p->map_b, ti.b_mode, b_row0 + j * 128, k0,
-                                                full_bar);
+                                                term_plane_b(ti.n_terms, term), full_bar);
                     }
                     if (++stage == C::kStages) {
                         stage = 0;
                         phase ^= 1u;
+                    }
+                    if (++term == ti.n_terms) {
+                        term = 0;
+                        ++kb;
                     }
                 }
             }
@@ -466,7 +490,8 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
                 }
                 tcgen05_fence_after();
                 const uint32_t tmem_d = tmem_base + (uint32_t)(acc * kAccCols);
-                for (int kb = 0; kb < ti.k_blocks; ++kb) {
+                const int n_slots = ti.k_blocks * ti.n_terms;
+                for (int slot = 0; slot < n_slots; ++slot) {
                     if (!MBAR_WAIT(2, &bars->full[stage], phase)) {
                         ok = false;
                         break;
@@ -477,7 +502,7 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
 #pragma unroll
                     for (int kk = 0; kk < BK / UMMA_K; ++kk)
                         tcgen05_mma_bf16<kCtas>(tmem_d, operand_desc(sa, ti.a_mode, kk), operand_desc(sb, ti.b_mode, kk),
-                                                idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+                                                idesc, (slot > 0 || kk > 0) ? 1u : 0u);
                     tcgen05_commit<kCtas>(&bars->empty[stage]);  // slot reusable once these MMAs have read it
                     if (++stage == C::kStages) {
                         stage = 0;
@@ -516,6 +541,8 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
             __nv_bfloat16 *out_bf16 = p->out_bf16;
             float *out_f32 = p->out_f32;
             const int64_t ld = p->ld_out;
+            const int out_planes = p->n_out_planes;          // 1: bf16 rounding; 3: split into three bf16 pieces
+            const int64_t plane_stride = p->out_plane_stride;
             const bool bf16_rows_32b = (ld % 16) == 0;  // every bf16 output row starts on a 32-byte boundary
             if (!MBAR_WAIT(3, &bars->tmem_full[acc], acc_phase)) {
                 ok = false;
@@ -542,30 +569,6 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
                         if (epi == TC_EPI_THREE_I_MINUS) f[j] = (row == col0 + j) ? 3.0f - a : -a;  // muon.rs:76-89
                         else f[j] = 0.5f * a;                                                       // muon.rs:95-99
                     }
-                    if (out_bf16) {
-                        __nv_bfloat16 *dst = out_bf16 + (int64_t)row * ld + col0;
-#pragma unroll
-                        for (int g16 = 0; g16 < 2; ++g16) {  // 16 columns = one 32-byte sector per store
-                            const int col = col0 + g16 * 16;
-                            if (col + 16 <= N && bf16_rows_32b) {
-                                uint32_t q[8];
-#pragma unroll
-                                for (int j = 0; j < 8; ++j) q[j] = pack_bf16(f[g16 * 16 + 2 * j], f[g16 * 16 + 2 * j + 1]);
-                                st_global_256(dst + g16 * 16, q);
-                            } else {  // 16-byte pieces (N and ld are multiples of 8)
-#pragma unroll
-                                for (int h = 0; h < 2; ++h) {
-                                    if (col + h * 8 >= N) break;
-                                    uint4 q;
-                                    q.x = pack_bf16(f[g16 * 16 + h * 8 + 0], f[g16 * 16 + h * 8 + 1]);
-                                    q.y = pack_bf16(f[g16 * 16 + h * 8 + 2], f[g16 * 16 + h * 8 + 3]);
-                                    q.z = pack_bf16(f[g16 * 16 + h * 8 + 4], f[g16 * 16 + h * 8 + 5]);
-                                    q.w = pack_bf16(f[g16 * 16 + h * 8 + 6], f[g16 * 16 + h * 8 + 7]);
-                                    *reinterpret_cast<uint4 *>(dst + g16 * 16 + h * 8) = q;
-                                }
-                            }
-                        }
-                    }
                     if (out_f32) {
                         float *dst = out_f32 + (int64_t)row * ld + col0;
 #pragma unroll
@@ -575,6 +578,37 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
 #pragma unroll
                             for (int j = 0; j < 8; ++j) q[j] = __float_as_uint(f[g8 * 8 + j]);
                             st_global_256(dst + g8 * 8, q);
+                        }
+                    }
+                    if (out_bf16) {
+                        for (int pl = 0; pl < out_planes; ++pl) {
+                            __nv_bfloat16 *dst = out_bf16 + pl * plane_stride + (int64_t)row * ld + col0;
+#pragma unroll
+                            for (int g16 = 0; g16 < 2; ++g16) {  // 16 columns = one 32-byte sector per store
+                                const int col = col0 + g16 * 16;
+                                if (col + 16 <= N && bf16_rows_32b) {
+                                    uint32_t q[8];
+#pragma unroll
+                                    for (int j = 0; j < 8; ++j)
+                                        q[j] = pack_bf16(f[g16 * 16 + 2 * j], f[g16 * 16 + 2 * j + 1]);
+                                    st_global_256(dst + g16 * 16, q);
+                                } else {  // 16-byte pieces (N and ld are multiples of 8)
+#pragma unroll
+                                    for (int h = 0; h < 2; ++h) {
+                                        if (col + h * 8 >= N) break;
+                                        uint4 q;
+                                        q.x = pack_bf16(f[g16 * 16 + h * 8 + 0], f[g16 * 16 + h * 8 + 1]);
+                                        q.y = pack_bf16(f[g16 * 16 + h * 8 + 2], f[g16 * 16 + h * 8 + 3]);
+                                        q.z = pack_bf16(f[g16 * 16 + h * 8 + 4], f[g16 * 16 + h * 8 + 5]);
+                                        q.w = pack_bf16(f[g16 * 16 + h * 8 + 6], f[g16 * 16 + h * 8 + 7]);
+                                        *reinterpret_cast<uint4 *>(dst + g16 * 16 + h * 8) = q;
+                                    }
+                                }
+                            }
+                            if (pl + 1 < out_planes) {  // what this plane's rounding left over goes to the next
+#pragma unroll
+                                for (int j = 0; j < 32; ++j) f[j] -= __bfloat162float(__float2bfloat16_rn(f[j]));
+                            }
                         }
                     }
                 }
@@ -661,29 +695,34 @@ void tc_gemm_tile_shape(int *bm, int *bn)
 // the 3-D view when its row length is a multiple of 64 elements, else as 64 x 64 boxes.
 int tc_mn_major_mode(int64_t inner) { return (inner % 64) == 0 ? TC_OP_MN_3D : TC_OP_MN_BOXES; }
 
-// Tensor map over a row-major bf16 matrix [outer][inner], 128-byte swizzle, out-of-range
-// elements read as zero.  `mode` selects the box the kernel will ask for (see load_rows128).
-int make_bf16_tensor_map(void *map_out, const void *base, int64_t inner, int64_t outer, int mode)
+// Tensor map over `planes` row-major bf16 matrices [outer][inner] that lie `plane_stride`
+// elements apart (planes = 1 for plain operands, 3 for split ones), 128-byte swizzle,
+// out-of-range elements read as zero.  `mode` selects the box the kernel will ask for (see
+// load_rows128); the plane is the outermost coordinate.
+int make_bf16_tensor_map(void *map_out, const void *base, int64_t inner, int64_t outer, int mode, int planes,
+                         int64_t plane_stride)
 {
     EncodeTiledFn fn = get_encode_fn();
     if (!fn) return fail(VB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
-    if ((inner % 8) != 0 || (reinterpret_cast<uintptr_t>(base) & 15u) != 0)
+    if ((inner % 8) != 0 || (reinterpret_cast<uintptr_t>(base) & 15u) != 0 || (plane_stride % 8) != 0)
         return fail(VB_ERR_UNSUPPORTED, "TMA needs 16-byte aligned rows (inner extent %lld)", (long long)inner);
+    if (planes < 1) planes = 1;
+    const cuuint64_t pstride = (cuuint64_t)(planes > 1 ? plane_stride : inner * outer) * 2;
     CUresult r;
-    cuuint32_t estr[3] = {1, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
     if (mode == TC_OP_MN_3D) {
         if ((inner % 64) != 0) return fail(VB_ERR_INVALID_ARG, "the 3-D operand view needs rows of a multiple of 64");
-        cuuint64_t dims[3] = {64, (cuuint64_t)outer, (cuuint64_t)(inner / 64)};
-        cuuint64_t strides[2] = {(cuuint64_t)inner * 2, 128};
-        cuuint32_t box[3] = {64, 64, 2};
-        r = fn(reinterpret_cast<CUtensorMap *>(map_out), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(base),
+        cuuint64_t dims[4] = {64, (cuuint64_t)outer, (cuuint64_t)(inner / 64), (cuuint64_t)planes};
+        cuuint64_t strides[3] = {(cuuint64_t)inner * 2, 128, pstride};
+        cuuint32_t box[4] = {64, 64, 2, 1};
+        r = fn(reinterpret_cast<CUtensorMap *>(map_out), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void *>(base),
                dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     } else {
-        cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
-        cuuint64_t strides[1] = {(cuuint64_t)inner * 2};
-        cuuint32_t box[2] = {(cuuint32_t)BK, mode == TC_OP_K_MAJOR ? 128u : (cuuint32_t)kBoxRows};
-        r = fn(reinterpret_cast<CUtensorMap *>(map_out), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base),
+        cuuint64_t dims[3] = {(cuuint64_t)inner, (cuuint64_t)outer, (cuuint64_t)planes};
+        cuuint64_t strides[2] = {(cuuint64_t)inner * 2, pstride};
+        cuuint32_t box[3] = {(cuuint32_t)BK, mode == TC_OP_K_MAJOR ? 128u : (cuuint32_t)kBoxRows, 1};
+        r = fn(reinterpret_cast<CUtensorMap *>(map_out), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(base),
                dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     }

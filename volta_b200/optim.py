@@ -20,10 +20,10 @@ from typing import Iterable, List, Optional, Sequence
 import numpy as np
 
 from . import _lib
-from ._lib import VB_NS_BF16, VB_NS_F32, VB_STEP_DEFAULT, VB_STEP_NO_EXCHANGE, VoltaB200Error, call
+from ._lib import VB_NS_BF16, VB_NS_F32, VB_NS_F32_TC, VB_STEP_DEFAULT, VB_STEP_NO_EXCHANGE, VoltaB200Error, call
 
 __all__ = ["Engine", "Tensor", "Adam", "SGD", "Muon", "default_engine", "multi_tensor_step",
-           "VoltaB200Error", "VB_NS_F32", "VB_NS_BF16", "VB_STEP_NO_EXCHANGE"]
+           "VoltaB200Error", "VB_NS_F32", "VB_NS_BF16", "VB_NS_F32_TC", "VB_STEP_NO_EXCHANGE"]
 
 
 def _f32(a) -> np.ndarray:
@@ -371,8 +371,9 @@ def muon_dims(shape):
 
 class Muon(_Optimizer):
     """``Muon::new(params, lr, momentum, nesterov, ns_steps)`` (src/nn/optim/muon.rs:19-38).
-    ``ns_mode`` picks the Newton-Schulz arithmetic: ``VB_NS_F32`` (f32-faithful) or
-    ``VB_NS_BF16`` (tcgen05 bf16 tensor cores)."""
+    ``ns_mode`` picks the Newton-Schulz arithmetic: ``VB_NS_F32`` (bit-faithful, CUDA cores),
+    ``VB_NS_BF16`` (tcgen05 bf16 tensor cores) or ``VB_NS_F32_TC`` (f32-accurate on the tensor
+    cores through three-way bf16 splitting)."""
 
     def __init__(self, params, lr: float, momentum: float, nesterov: bool, ns_steps: int,
                  ns_mode: int = VB_NS_F32, engine: Optional[Engine] = None):
