@@ -688,7 +688,8 @@ int muon_init(vb_optimizer *opt)
                 g.M = sh; g.N = sh; g.K = tall ? r : c;
                 g.a_mode = tall ? mn_mode : TC_OP_K_MAJOR;
                 g.b_mode = g.a_mode;
-                g.epilogue = TC_EPI_THREE_I_MINUS; g.ld_out = sh; g.tensor = t;
+                // split path: keep the Gram itself and form 1.5 X - 0.5 X G in the update's epilogue
+                g.epilogue = planes == 3 ? TC_EPI_IDENTITY : TC_EPI_THREE_I_MINUS; g.ld_out = sh; g.tensor = t;
                 g.n_terms = n_terms; g.n_out_planes = planes; g.out_plane_stride = s->cb_elems;
                 g.out_bf16 = cb; g.out_f32 = nullptr;
                 gram[par].push_back(g);
@@ -700,7 +701,8 @@ int muon_init(vb_optimizer *opt)
                 u.M = r; u.N = c; u.K = sh;
                 u.a_mode = TC_OP_K_MAJOR;
                 u.b_mode = tall ? TC_OP_K_MAJOR : mn_mode;
-                u.epilogue = TC_EPI_HALF; u.ld_out = c; u.tensor = t;
+                u.epilogue = planes == 3 ? TC_EPI_NS_COMBINE : TC_EPI_HALF; u.ld_out = c; u.tensor = t;
+                u.in_bf16 = xb[par];
                 u.n_terms = n_terms; u.n_out_planes = planes; u.out_plane_stride = s->owned_elems;
                 u.out_bf16 = xb[par ^ 1]; u.out_f32 = nullptr;
                 upd[par].push_back(u);
@@ -772,10 +774,12 @@ int muon_step(vb_optimizer *opt, uint32_t flags)
             const int par = it & 1;
             const bool last = it == opt->ns_steps - 1;
             if (s->n_tc_gram_tiles > 0) {
+                const bool split = s->planes == 3;
                 VB_TRY(launch_ns_gemm_tc(s->d_tc_gram[par], s->d_tc_gram_tiles, s->n_tc_gram_tiles, opt->d_present,
-                                         s->d_error, e->sm_count, e->stream));
+                                         s->d_error, e->sm_count, e->stream, 0, split));
                 VB_TRY(launch_ns_gemm_tc(last ? s->d_tc_upd_final : s->d_tc_upd[par], s->d_tc_upd_tiles,
-                                         s->n_tc_upd_tiles, opt->d_present, s->d_error, e->sm_count, e->stream));
+                                         s->n_tc_upd_tiles, opt->d_present, s->d_error, e->sm_count, e->stream, 0,
+                                         split));
                 e->launches += 2;
             }
             if (s->n_gram_tiles > 0) {

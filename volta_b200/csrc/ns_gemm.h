@@ -33,7 +33,12 @@ struct F32GemmProblem {
     int32_t pad;
 };
 
-enum TcEpilogue { TC_EPI_THREE_I_MINUS = 0, TC_EPI_HALF = 1 };
+enum TcEpilogue {
+    TC_EPI_THREE_I_MINUS = 0,  // D = 3I - acc
+    TC_EPI_HALF = 1,           // D = 0.5 acc
+    TC_EPI_IDENTITY = 2,       // D = acc
+    TC_EPI_NS_COMBINE = 3      // D = 1.5 X - 0.5 acc, X read from in_bf16 at the output position
+};
 
 // How an operand of the tensor-core GEMM is laid out in memory and fetched by TMA.
 enum TcOperandMode {
@@ -56,6 +61,7 @@ struct alignas(128) TcGemmProblem {
     int32_t n_terms;         // 1: plain bf16 operands; 6: operands split into three bf16 planes (f32-accurate)
     int32_t n_out_planes;    // planes written to out_bf16: 1 (bf16 rounding) or 3 (split)
     int64_t out_plane_stride;  // elements between output planes
+    const __nv_bfloat16 *in_bf16;  // TC_EPI_NS_COMBINE only: planes of X (same ld and plane stride as the output)
     __nv_bfloat16 *out_bf16; // may be null
     float *out_f32;          // may be null
 };
@@ -63,7 +69,7 @@ struct alignas(128) TcGemmProblem {
 // wait_limit: mbarrier polls before a role gives up (0 = the default, about a second).
 int launch_ns_gemm_tc(const TcGemmProblem *d_problems, const GemmTile *d_tiles, int n_tiles,
                       const uint8_t *d_present, int *d_error_flag, int sm_count, cudaStream_t stream,
-                      uint32_t wait_limit = 0);
+                      uint32_t wait_limit = 0, bool split = false);
 void tc_gemm_tile_shape(int *bm, int *bn);
 int make_bf16_tensor_map(void *map_out, const void *base, int64_t inner, int64_t outer, int mode, int planes = 1,
                          int64_t plane_stride = 0);

@@ -161,6 +161,21 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t local, uint32_t rank)
 // TMA loads into this CTA's shared memory.  `bar` is a shared::cluster address: this CTA's own
 // barrier, or (kCtas == 2, .cta_group::2) the leader's.  Every CTA fetches its own rows.
 template <int kCtas>
+__device__ __forceinline__ void tma_load_2d(void *smem_dst, const CUtensorMap *map, int c0, int c1, uint32_t bar)
+{
+    if (kCtas == 2)
+        asm volatile(
+            "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+            "[%0], [%1, {%2, %3}], [%4];"
+            ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(bar)
+            : "memory");
+    else
+        asm volatile(
+            "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+            ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(bar)
+            : "memory");
+}
+template <int kCtas>
 __device__ __forceinline__ void tma_load_3d(void *smem_dst, const CUtensorMap *map, int c0, int c1, int c2,
                                             uint32_t bar)
 {
@@ -204,17 +219,28 @@ __device__ __forceinline__ void tma_load_4d(void *smem_dst, const CUtensorMap *m
 //   TC_OP_MN_BOXES  two 64 x 64 boxes of a [k][rows] matrix (any row count)
 //   TC_OP_MN_3D     one 64 x 64 x 2 box of the same matrix viewed as [rows/64][k][64]
 // All three leave the same image in shared memory.
-template <int kCtas>
+template <int kCtas, bool kSplit>
 __device__ __forceinline__ void load_rows128(uint8_t *dst, const CUtensorMap *map, int mode, int row0, int k0,
                                              int plane, uint32_t bar)
 {
-    if (mode == TC_OP_K_MAJOR) {
-        tma_load_3d<kCtas>(dst, map, k0, row0, plane, bar);
-    } else if (mode == TC_OP_MN_3D) {
-        tma_load_4d<kCtas>(dst, map, 0, k0, row0 >> 6, plane, bar);
+    if (kSplit) {  // tensor maps with a plane dimension
+        if (mode == TC_OP_K_MAJOR) {
+            tma_load_3d<kCtas>(dst, map, k0, row0, plane, bar);
+        } else if (mode == TC_OP_MN_3D) {
+            tma_load_4d<kCtas>(dst, map, 0, k0, row0 >> 6, plane, bar);
+        } else {
+            tma_load_3d<kCtas>(dst, map, row0, k0, plane, bar);
+            tma_load_3d<kCtas>(dst + kBoxBytes, map, row0 + kBoxRows, k0, plane, bar);
+        }
     } else {
-        tma_load_3d<kCtas>(dst, map, row0, k0, plane, bar);
-        tma_load_3d<kCtas>(dst + kBoxBytes, map, row0 + kBoxRows, k0, plane, bar);
+        if (mode == TC_OP_K_MAJOR) {
+            tma_load_2d<kCtas>(dst, map, k0, row0, bar);
+        } else if (mode == TC_OP_MN_3D) {
+            tma_load_3d<kCtas>(dst, map, 0, k0, row0 >> 6, bar);
+        } else {
+            tma_load_2d<kCtas>(dst, map, row0, k0, bar);
+            tma_load_2d<kCtas>(dst + kBoxBytes, map, row0 + kBoxRows, k0, bar);
+        }
     }
 }
 
@@ -359,7 +385,9 @@ __device__ __forceinline__ TileInfo fetch_tile(const TcGemmProblem *problems, co
     return ti;
 }
 
-template <int kCtas>
+// kSplit: the operands are three bf16 planes (f32-accurate path); the plain bf16 instantiation
+// carries none of that code.
+template <int kCtas, bool kSplit>
 __global__ void __launch_bounds__(kThreads, 1)
 ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__restrict__ tiles, int n_tiles,
                   const uint8_t *__restrict__ present, int *__restrict__ error_flag, uint32_t wait_limit)
@@ -424,7 +452,8 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
                 if (ti.skipped) continue;
                 const int a_row0 = ti.m0 + (int)cta_rank * BM;         // this CTA's rows of A
                 const int b_row0 = ti.n0 + (int)cta_rank * C::kBRows;  // this CTA's rows of B
-                const int n_slots = ti.k_blocks * ti.n_terms;  // every (k block, plane pair) fills one ring slot
+                const int n_terms = kSplit ? ti.n_terms : 1;
+                const int n_slots = ti.k_blocks * n_terms;  // every (k block, plane pair) fills one ring slot
                 int kb = 0, term = 0;
                 for (int slot = 0; slot < n_slots; ++slot) {
                     if (!MBAR_WAIT(0, &bars->empty[stage], phase ^ 1u)) {
@@ -445,19 +474,19 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
                         // (and, a ring later, this thread's own) run out.  Used by the expiry test.
                     } else if (lane == 0) {
                         if (cta_rank == 0) mbar_expect_tx(&bars->full[stage], kCtas * C::kStageBytes);
-                        load_rows128<kCtas>(sa, &ti.p->map_a, ti.a_mode, a_row0, k0, term_plane_a(ti.n_terms, term),
+                        load_rows128<kCtas, kSplit>(sa, &ti.p->map_a, ti.a_mode, a_row0, k0, term_plane_a(n_terms, term),
                                             full_bar);
                     } else {
 #pragma unroll
                         for (int j = 0; j < C::kBRows / 128; ++j)
-                            load_rows128<kCtas>(sb + j * kRows128Bytes, &ti.p->map_b, ti.b_mode, b_row0 + j * 128, k0,
-                                                term_plane_b(ti.n_terms, term), full_bar);
+                            load_rows128<kCtas, kSplit>(sb + j * kRows128Bytes, &ti.p->map_b, ti.b_mode, b_row0 + j * 128, k0,
+                                                term_plane_b(n_terms, term), full_bar);
                     }
                     if (++stage == C::kStages) {
                         stage = 0;
                         phase ^= 1u;
                     }
-                    if (++term == ti.n_terms) {
+                    if (++term == n_terms) {
                         term = 0;
                         ++kb;
                     }
@@ -490,7 +519,7 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
                 }
                 tcgen05_fence_after();
                 const uint32_t tmem_d = tmem_base + (uint32_t)(acc * kAccCols);
-                const int n_slots = ti.k_blocks * ti.n_terms;
+                const int n_slots = ti.k_blocks * (kSplit ? ti.n_terms : 1);
                 for (int slot = 0; slot < n_slots; ++slot) {
                     if (!MBAR_WAIT(2, &bars->full[stage], phase)) {
                         ok = false;
@@ -540,8 +569,10 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
             const int epi = p->epilogue;
             __nv_bfloat16 *out_bf16 = p->out_bf16;
             float *out_f32 = p->out_f32;
+            const __nv_bfloat16 *in_bf16 = p->in_bf16;  // TC_EPI_NS_COMBINE: the planes of X at the output position
             const int64_t ld = p->ld_out;
-            const int out_planes = p->n_out_planes;          // 1: bf16 rounding; 3: split into three bf16 pieces
+            const int out_planes = kSplit ? p->n_out_planes : 1;  // 1: bf16 rounding; 3: split into three pieces
+            const int out_planes_in = kSplit ? 3 : 1;             // planes of the operands (and of in_bf16)
             const int64_t plane_stride = p->out_plane_stride;
             const bool bf16_rows_32b = (ld % 16) == 0;  // every bf16 output row starts on a 32-byte boundary
             if (!MBAR_WAIT(3, &bars->tmem_full[acc], acc_phase)) {
@@ -567,7 +598,33 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
                     for (int j = 0; j < 32; ++j) {
                         const float a = __uint_as_float(v[cc & 1][j]);
                         if (epi == TC_EPI_THREE_I_MINUS) f[j] = (row == col0 + j) ? 3.0f - a : -a;  // muon.rs:76-89
-                        else f[j] = 0.5f * a;                                                       // muon.rs:95-99
+                        else if (epi == TC_EPI_HALF) f[j] = 0.5f * a;                               // muon.rs:95-99
+                        else f[j] = a;  // TC_EPI_IDENTITY, or TC_EPI_NS_COMBINE (finished below)
+                    }
+                    if (kSplit && epi == TC_EPI_NS_COMBINE) {
+                        // X' = 0.5 X (3I - G) evaluated as 1.5 X - 0.5 (X G): the accumulator holds only
+                        // the small product X G, so the tensor core's truncating f32 accumulation acts on
+                        // a term that is a few percent of the result instead of on the result itself.
+                        const __nv_bfloat16 *src = in_bf16 + (int64_t)row * ld + col0;
+                        float x[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) x[j] = 0.0f;
+                        for (int pl = out_planes_in - 1; pl >= 0; --pl) {  // smallest piece first: the sum is exact
+#pragma unroll
+                            for (int g8 = 0; g8 < 4; ++g8) {               // 8 columns = one 16-byte load
+                                if (col0 + g8 * 8 < N) {
+                                    const uint4 q = *reinterpret_cast<const uint4 *>(src + pl * plane_stride + g8 * 8);
+                                    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                                    for (int h = 0; h < 4; ++h) {  // bf16 -> f32 is a 16-bit shift
+                                        x[g8 * 8 + 2 * h] += __uint_as_float(w[h] << 16);
+                                        x[g8 * 8 + 2 * h + 1] += __uint_as_float(w[h] & 0xffff0000u);
+                                    }
+                                }
+                            }
+                        }
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) f[j] = fmaf(1.5f, x[j], -0.5f * f[j]);
                     }
                     if (out_f32) {
                         float *dst = out_f32 + (int64_t)row * ld + col0;
@@ -706,8 +763,10 @@ int make_bf16_tensor_map(void *map_out, const void *base, int64_t inner, int64_t
     if (!fn) return fail(VB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
     if ((inner % 8) != 0 || (reinterpret_cast<uintptr_t>(base) & 15u) != 0 || (plane_stride % 8) != 0)
         return fail(VB_ERR_UNSUPPORTED, "TMA needs 16-byte aligned rows (inner extent %lld)", (long long)inner);
-    if (planes < 1) planes = 1;
-    const cuuint64_t pstride = (cuuint64_t)(planes > 1 ? plane_stride : inner * outer) * 2;
+    // plain operands (planes <= 1) get maps without a plane dimension; split operands get one
+    // more, outermost, dimension
+    const bool with_planes = planes > 1;
+    const cuuint64_t pstride = (cuuint64_t)plane_stride * 2;
     CUresult r;
     cuuint32_t estr[4] = {1, 1, 1, 1};
     if (mode == TC_OP_MN_3D) {
@@ -715,73 +774,84 @@ int make_bf16_tensor_map(void *map_out, const void *base, int64_t inner, int64_t
         cuuint64_t dims[4] = {64, (cuuint64_t)outer, (cuuint64_t)(inner / 64), (cuuint64_t)planes};
         cuuint64_t strides[3] = {(cuuint64_t)inner * 2, 128, pstride};
         cuuint32_t box[4] = {64, 64, 2, 1};
-        r = fn(reinterpret_cast<CUtensorMap *>(map_out), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void *>(base),
-               dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        r = fn(reinterpret_cast<CUtensorMap *>(map_out), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, with_planes ? 4 : 3,
+               const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     } else {
         cuuint64_t dims[3] = {(cuuint64_t)inner, (cuuint64_t)outer, (cuuint64_t)planes};
         cuuint64_t strides[2] = {(cuuint64_t)inner * 2, pstride};
         cuuint32_t box[3] = {(cuuint32_t)BK, mode == TC_OP_K_MAJOR ? 128u : (cuuint32_t)kBoxRows, 1};
-        r = fn(reinterpret_cast<CUtensorMap *>(map_out), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(base),
-               dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        r = fn(reinterpret_cast<CUtensorMap *>(map_out), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, with_planes ? 3 : 2,
+               const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     }
     if (r != CUDA_SUCCESS) return fail(VB_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
     return VB_OK;
 }
 
+template <int kCtas, bool kSplit>
+static int launch_variant(const TcGemmProblem *d_problems, const GemmTile *d_tiles, int n_tiles,
+                          const uint8_t *d_present, int *d_error_flag, int sm_count, cudaStream_t stream,
+                          uint32_t wait_limit)
+{
+    static bool attr_set = false;
+    if (!attr_set) {
+        VB_CUDA(cudaFuncSetAttribute(ns_gemm_tc_kernel<kCtas, kSplit>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)smem_bytes<kCtas>()));
+        attr_set = true;
+    }
+    if (kCtas == 1) {
+        int grid = sm_count;  // one persistent CTA per SM (it owns all 512 TMEM columns)
+        if (grid > n_tiles) grid = n_tiles;
+        ns_gemm_tc_kernel<kCtas, kSplit><<<grid, kThreads, smem_bytes<kCtas>(), stream>>>(
+            d_problems, d_tiles, n_tiles, d_present, d_error_flag, wait_limit);
+        VB_CUDA(cudaGetLastError());
+        return VB_OK;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem_bytes<kCtas>();
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    // A persistent grid must be fully resident: ask how many CTA pairs the device holds at once.
+    static int max_clusters = 0;
+    if (max_clusters == 0) {
+        cfg.gridDim = dim3((unsigned)(sm_count / 2 * 2));
+        int n = 0;
+        VB_CUDA(cudaOccupancyMaxActiveClusters(&n, ns_gemm_tc_kernel<kCtas, kSplit>, &cfg));
+        if (n < 1) return fail(VB_ERR_CUDA, "the device cannot hold a 2-CTA cluster of the GEMM kernel");
+        max_clusters = n;
+    }
+    int clusters = max_clusters;
+    if (clusters > n_tiles) clusters = n_tiles;
+    cfg.gridDim = dim3((unsigned)(clusters * 2));
+    VB_CUDA(cudaLaunchKernelEx(&cfg, ns_gemm_tc_kernel<kCtas, kSplit>, d_problems, d_tiles, n_tiles, d_present,
+                               d_error_flag, wait_limit));
+    return VB_OK;
+}
+
+// split: the problems' operands are three bf16 planes (all problems of a launch are alike).
 int launch_ns_gemm_tc(const TcGemmProblem *d_problems, const GemmTile *d_tiles, int n_tiles,
                       const uint8_t *d_present, int *d_error_flag, int sm_count, cudaStream_t stream,
-                      uint32_t wait_limit)
+                      uint32_t wait_limit, bool split)
 {
     if (n_tiles <= 0) return VB_OK;
     if (wait_limit == 0) wait_limit = kDefaultWaitLimit;
-    if (tc_use_pair()) {
-        static bool attr_set = false;
-        if (!attr_set) {
-            VB_CUDA(cudaFuncSetAttribute(ns_gemm_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)smem_bytes<2>()));
-            attr_set = true;
-        }
-        cudaLaunchConfig_t cfg = {};
-        cfg.blockDim = dim3(kThreads);
-        cfg.dynamicSmemBytes = smem_bytes<2>();
-        cfg.stream = stream;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = 2;
-        attr[0].val.clusterDim.y = 1;
-        attr[0].val.clusterDim.z = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
-        // A persistent grid must be fully resident: ask how many CTA pairs the device holds at once.
-        static int max_clusters = 0;
-        if (max_clusters == 0) {
-            cfg.gridDim = dim3((unsigned)(sm_count / 2 * 2));
-            int n = 0;
-            VB_CUDA(cudaOccupancyMaxActiveClusters(&n, ns_gemm_tc_kernel<2>, &cfg));
-            if (n < 1) return fail(VB_ERR_CUDA, "the device cannot hold a 2-CTA cluster of the GEMM kernel");
-            max_clusters = n;
-        }
-        int clusters = max_clusters;
-        if (clusters > n_tiles) clusters = n_tiles;
-        cfg.gridDim = dim3((unsigned)(clusters * 2));
-        VB_CUDA(cudaLaunchKernelEx(&cfg, ns_gemm_tc_kernel<2>, d_problems, d_tiles, n_tiles, d_present, d_error_flag,
-                                   wait_limit));
-        return VB_OK;
-    }
-    static bool attr_set1 = false;
-    if (!attr_set1) {
-        VB_CUDA(cudaFuncSetAttribute(ns_gemm_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     (int)smem_bytes<1>()));
-        attr_set1 = true;
-    }
-    int grid = sm_count;  // one persistent CTA per SM (it owns all 512 TMEM columns)
-    if (grid > n_tiles) grid = n_tiles;
-    ns_gemm_tc_kernel<1><<<grid, kThreads, smem_bytes<1>(), stream>>>(d_problems, d_tiles, n_tiles, d_present,
-                                                                     d_error_flag, wait_limit);
-    VB_CUDA(cudaGetLastError());
-    return VB_OK;
+    if (tc_use_pair())
+        return split ? launch_variant<2, true>(d_problems, d_tiles, n_tiles, d_present, d_error_flag, sm_count, stream,
+                                               wait_limit)
+                     : launch_variant<2, false>(d_problems, d_tiles, n_tiles, d_present, d_error_flag, sm_count, stream,
+                                                wait_limit);
+    return split ? launch_variant<1, true>(d_problems, d_tiles, n_tiles, d_present, d_error_flag, sm_count, stream,
+                                           wait_limit)
+                 : launch_variant<1, false>(d_problems, d_tiles, n_tiles, d_present, d_error_flag, sm_count, stream,
+                                            wait_limit);
 }
 
 }  // namespace vb
