@@ -201,6 +201,14 @@ int vb_optimizer_download_params(vb_optimizer *opt, int64_t tensor, float *host,
 int vb_optimizer_upload_grad(vb_optimizer *opt, int64_t tensor, const float *host, int64_t n);
 int vb_optimizer_download_grad(vb_optimizer *opt, int64_t tensor, float *host, int64_t n);
 
+/* Adds one gradient contribution on the device, as backward() does for a parameter that is
+ * reached along several paths or over several micro-batches (RawTensor::accumulate_grad,
+ * src/autograd.rs:140-148,158-184): the first contribution after zero_grad() becomes the
+ * gradient, later ones are added element by element (one rounded f32 add each).  The source
+ * is host memory or a device buffer on the engine's device. */
+int vb_optimizer_accumulate_grad(vb_optimizer *opt, int64_t tensor, const float *host, int64_t n);
+int vb_optimizer_accumulate_grad_device(vb_optimizer *opt, int64_t tensor, const void *device_src, int64_t n);
+
 /* Device addresses (f32, 128-byte aligned) so producers can write gradients / read
  * parameters in place without staging.  Valid until the optimizer is destroyed. */
 int vb_optimizer_param_ptr(vb_optimizer *opt, int64_t tensor, void **device_ptr);

@@ -352,3 +352,33 @@ def test_c5_full_size_ragged_properties(oracle, engine):
     assert bool(torch.isfinite(theta).all())
     del theta, grad, before, mask
     opt.close()
+
+
+def test_gradient_accumulation_on_device(oracle, engine):
+    """RawTensor::accumulate_grad (src/autograd.rs:158-184): contributions are summed in arrival
+    order with one rounded add each; after zero_grad the next contribution replaces."""
+    import torch
+    from volta_b200 import Adam, Tensor, _lib
+    from volta_b200.optim import accumulate_grad
+    rng = np.random.default_rng(9)
+    n = 10007
+    p = Tensor(rng.standard_normal(n).astype(np.float32))
+    opt = Adam([p], 1e-3, (0.9, 0.999), 1e-8, 0.0, engine=engine)
+    parts = [(rng.standard_normal(n) * 0.01).astype(np.float32) for _ in range(3)]
+    accumulate_grad(p, parts[0])
+    accumulate_grad(p, parts[1])
+    dev = torch.from_numpy(parts[2]).to("cuda:0")
+    torch.cuda.synchronize()
+    _lib.call("vb_optimizer_accumulate_grad_device", opt._h, 0, dev.data_ptr(), n)
+    opt._present[0] = True
+    expect = ((parts[0] + parts[1]).astype(np.float32) + parts[2]).astype(np.float32)
+    assert bits_equal(p.grad, expect)
+    ref_p = p.data.copy()
+    ref = oracle.Adam([ref_p], 1e-3, (0.9, 0.999), 1e-8, 0.0)
+    opt.step()
+    ref.step([expect])
+    assert bits_equal(p.data, ref_p)
+    opt.zero_grad()
+    accumulate_grad(p, parts[1])          # first contribution after zero_grad replaces the old gradient
+    assert bits_equal(p.grad, parts[1])
+    opt.close()

@@ -76,6 +76,8 @@ SIGNATURES = {
     "vb_optimizer_download_params": [_vp, _i64, _vp, _i64],
     "vb_optimizer_upload_grad": [_vp, _i64, _vp, _i64],
     "vb_optimizer_download_grad": [_vp, _i64, _vp, _i64],
+    "vb_optimizer_accumulate_grad": [_vp, _i64, _vp, _i64],
+    "vb_optimizer_accumulate_grad_device": [_vp, _i64, _vp, _i64],
     "vb_optimizer_param_ptr": [_vp, _i64, _vpp],
     "vb_optimizer_grad_ptr": [_vp, _i64, _vpp],
     "vb_optimizer_arena": [_vp, _vpp, _vpp, _i64p, _i64p],

@@ -372,6 +372,7 @@ int vb_engine_destroy(vb_engine *e)
         if (e->prof_open[ph]) cudaEventDestroy(e->prof_open[ph]);
     }
     for (cudaEvent_t ev : e->prof_free) cudaEventDestroy(ev);
+    if (e->d_accum_scratch) cudaFree(e->d_accum_scratch);
     for (int i = 0; i < 2; ++i) {
         if (e->h_stage[i]) cudaFreeHost(e->h_stage[i]);
         if (e->d_stage[i]) cudaFree(e->d_stage[i]);
@@ -640,6 +641,57 @@ int vb_optimizer_upload_grad(vb_optimizer *opt, int64_t tensor, const float *hos
     VB_TRY(copy_tensor(opt, tensor, opt->d_grad, (void *)host, n, true));
     opt->present[(size_t)tensor] = 1;
     return VB_OK;
+}
+
+// `p.grad = match p.grad { None => Some(g), Some(e) => Some(e + g) }` (src/autograd.rs:140-148,158-184)
+static int accumulate(vb_optimizer *opt, int64_t tensor, const float *dev_src, int64_t n)
+{
+    float *grad = opt->d_grad + opt->offsets[tensor];
+    const bool add = opt->present[(size_t)tensor] != 0;
+    VB_TRY(launch_accumulate_grad(grad, dev_src, n, add, opt->eng->sm_count, opt->eng->stream));
+    opt->eng->launches += 1;
+    opt->present[(size_t)tensor] = 1;
+    return VB_OK;
+}
+
+int vb_optimizer_accumulate_grad_device(vb_optimizer *opt, int64_t tensor, const void *device_src, int64_t n)
+{
+    VB_API_BEGIN
+    VB_TRY(check_tensor(opt, tensor, n, true));
+    if (n > 0 && !device_src) return fail(VB_ERR_INVALID_ARG, "device_src is null");
+    if (((uintptr_t)device_src & 3u) != 0) return fail(VB_ERR_INVALID_ARG, "device_src is not 4-byte aligned");
+    VB_TRY(set_device(opt->eng));
+    return accumulate(opt, tensor, (const float *)device_src, n);
+    VB_API_END
+}
+
+int vb_optimizer_accumulate_grad(vb_optimizer *opt, int64_t tensor, const float *host, int64_t n)
+{
+    VB_API_BEGIN
+    VB_TRY(check_tensor(opt, tensor, n, true));
+    if (n > 0 && !host) return fail(VB_ERR_INVALID_ARG, "host pointer is null");
+    vb_engine *e = opt->eng;
+    VB_TRY(set_device(e));
+    if (n == 0) {
+        opt->present[(size_t)tensor] = 1;
+        return VB_OK;
+    }
+    if (!opt->present[(size_t)tensor]) {  // first contribution: it simply becomes the gradient
+        VB_CUDA(cudaMemcpyAsync(opt->d_grad + opt->offsets[tensor], host, (size_t)n * sizeof(float),
+                                cudaMemcpyHostToDevice, e->stream));
+        opt->present[(size_t)tensor] = 1;
+        return VB_OK;
+    }
+    if (e->accum_scratch_elems < (size_t)n) {
+        if (e->d_accum_scratch) VB_CUDA(cudaFree(e->d_accum_scratch));  // waits for earlier users
+        e->d_accum_scratch = nullptr;
+        e->accum_scratch_elems = 0;
+        VB_CUDA(cudaMalloc(&e->d_accum_scratch, (size_t)n * sizeof(float)));
+        e->accum_scratch_elems = (size_t)n;
+    }
+    VB_CUDA(cudaMemcpyAsync(e->d_accum_scratch, host, (size_t)n * sizeof(float), cudaMemcpyHostToDevice, e->stream));
+    return accumulate(opt, tensor, e->d_accum_scratch, n);
+    VB_API_END
 }
 
 int vb_optimizer_download_grad(vb_optimizer *opt, int64_t tensor, float *host, int64_t n)

@@ -26,6 +26,8 @@ struct vb_engine {
     size_t stage_bytes[2] = {0, 0};
     cudaEvent_t stage_done[2] = {nullptr, nullptr};
     int stage_next = 0;
+    float *d_accum_scratch = nullptr;  // staging for host contributions to vb_optimizer_accumulate_grad
+    size_t accum_scratch_elems = 0;
     // optional phase timing (vb_engine_set_profiling): event pairs per phase, summed on query
     bool profiling = false;
     std::vector<std::pair<cudaEvent_t, cudaEvent_t>> prof_pairs[VB_PHASE_COUNT];

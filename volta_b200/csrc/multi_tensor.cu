@@ -319,6 +319,43 @@ int launch_multi_tensor(int op, const FatChunk *d_chunks, int64_t n_chunks, cons
     return VB_OK;
 }
 
+// ---- gradient accumulation (src/autograd.rs:140-148,158-184) -------------------------------------
+// grad = present ? grad + contribution : contribution, element by element (one rounded add).
+__global__ void __launch_bounds__(256)
+accumulate_grad_kernel(float *__restrict__ grad, const float *__restrict__ src, int64_t n, int add)
+{
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (((reinterpret_cast<uintptr_t>(grad) | reinterpret_cast<uintptr_t>(src)) & 15u) == 0) {
+        const int64_t n4 = n >> 2;
+        for (int64_t i = tid; i < n4; i += stride) {
+            float4 s4 = __ldcs(reinterpret_cast<const float4 *>(src) + i);
+            if (add) {
+                const float4 g4 = reinterpret_cast<const float4 *>(grad)[i];
+                s4.x = __fadd_rn(g4.x, s4.x);
+                s4.y = __fadd_rn(g4.y, s4.y);
+                s4.z = __fadd_rn(g4.z, s4.z);
+                s4.w = __fadd_rn(g4.w, s4.w);
+            }
+            reinterpret_cast<float4 *>(grad)[i] = s4;
+        }
+        for (int64_t i = (n4 << 2) + tid; i < n; i += stride) grad[i] = add ? __fadd_rn(grad[i], src[i]) : src[i];
+    } else {
+        for (int64_t i = tid; i < n; i += stride) grad[i] = add ? __fadd_rn(grad[i], src[i]) : src[i];
+    }
+}
+
+int launch_accumulate_grad(float *grad, const float *src, int64_t n, bool add, int sm_count, cudaStream_t stream)
+{
+    if (n <= 0) return VB_OK;
+    int64_t blocks = (n / 4 + 255) / 256;
+    if (blocks < 1) blocks = 1;
+    if (blocks > (int64_t)sm_count * 8) blocks = (int64_t)sm_count * 8;
+    accumulate_grad_kernel<<<(unsigned)blocks, 256, 0, stream>>>(grad, src, n, add ? 1 : 0);
+    VB_CUDA(cudaGetLastError());
+    return VB_OK;
+}
+
 // ---------------------------------------------------------------------------------------------
 // vb_multi_tensor_step_static: the fused step for callers that must not allocate.
 //

@@ -100,6 +100,8 @@ int launch_multi_tensor(int op, const FatChunk *d_chunks, int64_t n_chunks, cons
 int engine_launch_info(vb_engine *e, int *device, int *sm_count, cudaStream_t *stream);
 void engine_count_launch(vb_engine *e);
 
+int launch_accumulate_grad(float *grad, const float *src, int64_t n, bool add, int sm_count, cudaStream_t stream);
+
 // Splits [begin, end) of each tensor into chunks.
 int64_t pick_chunk_len(int64_t total_elements, int sm_count);
 

@@ -22,7 +22,7 @@ import numpy as np
 from . import _lib
 from ._lib import VB_NS_BF16, VB_NS_F32, VB_NS_F32_TC, VB_STEP_DEFAULT, VB_STEP_NO_EXCHANGE, VoltaB200Error, call
 
-__all__ = ["Engine", "Tensor", "Adam", "SGD", "Muon", "default_engine", "multi_tensor_step",
+__all__ = ["Engine", "Tensor", "Adam", "SGD", "Muon", "default_engine", "multi_tensor_step", "accumulate_grad",
            "VoltaB200Error", "VB_NS_F32", "VB_NS_BF16", "VB_NS_F32_TC", "VB_STEP_NO_EXCHANGE"]
 
 
@@ -177,6 +177,19 @@ class Tensor:
             self._opt._upload_grad(self._index, arr)
         else:
             self._host_grad = arr.copy()
+
+
+def accumulate_grad(tensor: "Tensor", contribution) -> None:
+    """``RawTensor::accumulate_grad`` (src/autograd.rs:140-148,158-184) for a tensor held by an
+    optimizer: the first contribution becomes the gradient, later ones are added on the device."""
+    arr = _f32(contribution).reshape(-1)
+    if tensor._opt is None:
+        tensor._host_grad = arr.copy() if tensor._host_grad is None else (tensor._host_grad + arr).astype(np.float32)
+        return
+    if arr.size != tensor.size:
+        raise ValueError("gradient size mismatch")
+    call("vb_optimizer_accumulate_grad", tensor._opt._h, tensor._index, arr.ctypes.data_as(C.c_void_p), arr.size)
+    tensor._opt._present[tensor._index] = True
 
 
 class _Optimizer:
