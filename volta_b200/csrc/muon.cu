@@ -712,13 +712,23 @@ int muon_init(vb_optimizer *opt)
                     upd_final.push_back(u);
                 }
             }
+            // The Gram is symmetric: with square tiles only those on or above the diagonal are
+            // computed; off-diagonal ones are also stored transposed by the epilogue.
+            int gram_all = 0, gram_used = 0;
             for (int m0 = 0; m0 < sh; m0 += bm)
-                for (int n0 = 0; n0 < sh; n0 += bn) gram_tiles.push_back(GemmTile{pidx, m0, n0, 0});
+                for (int n0 = 0; n0 < sh; n0 += bn) {
+                    ++gram_all;
+                    if (bm == bn && n0 < m0) continue;
+                    ++gram_used;
+                    gram_tiles.push_back(GemmTile{pidx, m0, n0, (bm == bn && n0 > m0) ? GEMM_TILE_MIRROR : 0});
+                }
             for (int m0 = 0; m0 < r; m0 += bm)
                 for (int n0 = 0; n0 < c; n0 += bn) upd_tiles.push_back(GemmTile{pidx, m0, n0, 0});
-            // executed tensor-core FLOPs: six plane products per product on the split path
-            s->flops_per_step += (double)n_terms * 4.0 * (double)std::max(r, c) * (double)sh * (double)sh *
-                                 (double)opt->ns_steps;
+            // executed tensor-core FLOPs: six plane products per product on the split path; the
+            // Gram counts only the tiles that are computed
+            const double prod = 2.0 * (double)std::max(r, c) * (double)sh * (double)sh;
+            s->flops_per_step += (double)n_terms * (double)opt->ns_steps *
+                                 (prod * (double)gram_used / (double)gram_all + prod);
         }
         for (int par = 0; par < 2; ++par) {
             VB_TRY(upload(&s->d_tc_gram[par], gram[par], e->stream));

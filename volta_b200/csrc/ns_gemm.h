@@ -10,11 +10,13 @@
 
 namespace vb {
 
+enum GemmTileFlags { GEMM_TILE_MIRROR = 1 };  // symmetric output: also store this tile transposed
+
 struct GemmTile {
     int32_t problem;
     int32_t m0;
     int32_t n0;
-    int32_t pad;
+    int32_t flags;
 };
 
 enum F32Epilogue { F32_EPI_NONE = 0, F32_EPI_THREE_I_MINUS = 1, F32_EPI_HALF = 2 };

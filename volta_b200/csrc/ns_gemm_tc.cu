@@ -357,6 +357,7 @@ __device__ __forceinline__ int term_plane_b(int n_terms, int term) { return n_te
 struct TileInfo {
     const TcGemmProblem *p;
     int m0, n0, k_blocks, a_mode, b_mode, n_terms;
+    bool mirror;    // symmetric product: this off-diagonal tile is also stored transposed
     bool skipped;   // gradient absent: nothing to do
     bool withhold;  // test hook (TcGemmProblem::withhold_loads): the producer stages nothing
 };
@@ -369,12 +370,14 @@ __device__ __forceinline__ TileInfo fetch_tile(const TcGemmProblem *problems, co
     ti.n_terms = 1;
     ti.skipped = true;
     ti.withhold = false;
+    ti.mirror = false;
     if (t < n_tiles) {
         const GemmTile tile = tiles[t];
         const TcGemmProblem *p = problems + tile.problem;
         ti.p = p;
         ti.m0 = tile.m0;
         ti.n0 = tile.n0;
+        ti.mirror = (tile.flags & GEMM_TILE_MIRROR) != 0;
         ti.k_blocks = (p->K + BK - 1) / BK;
         ti.a_mode = p->a_mode;
         ti.b_mode = p->b_mode;
@@ -661,6 +664,15 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
                                         *reinterpret_cast<uint4 *>(dst + g16 * 16 + h * 8) = q;
                                     }
                                 }
+                            }
+                            if (ti.mirror) {
+                                // D is symmetric and only its upper tiles are computed: element (row, col)
+                                // also goes to (col, row).  For a fixed column the 32 lanes of the warp
+                                // hold 32 consecutive rows, i.e. one contiguous 64-byte run of the mirror.
+                                __nv_bfloat16 *mdst = out_bf16 + pl * plane_stride + (int64_t)col0 * ld + row;
+#pragma unroll
+                                for (int j = 0; j < 32; ++j)
+                                    if (col0 + j < N) mdst[(int64_t)j * ld] = __float2bfloat16_rn(f[j]);
                             }
                             if (pl + 1 < out_planes) {  // what this plane's rounding left over goes to the next
 #pragma unroll
