@@ -280,11 +280,11 @@ def run_ours(args):
     e2e_steps = 0 if args.skip_e2e else max(3, min(args.steps, 10))
     barrier()
     t0 = time.perf_counter()
-    lo, hi = opt.owned_range()  # N > 1: a rank moves only its own slice over PCIe (what a reduce-scatter
-    for _ in range(e2e_steps):  # would hand it, and the parameters it updated)
-        opt.upload_arena_range(1, grads_pinned.array[lo:hi], lo)     # host -> device: this step's gradients
-        opt.step()
-        opt.download_arena_range(0, params_pinned.array[lo:hi], lo)  # device -> host: updated parameters (blocks)
+    # One public call per step: gradients up from pinned host memory, update, parameters back down
+    # (blocks until they are in host memory).  N > 1: a rank moves only its own slice over PCIe
+    # (what a reduce-scatter would hand it, and the parameters it updated).
+    for _ in range(e2e_steps):
+        opt.step_host(grads_pinned.array, params_pinned.array, pieces=32)
     barrier()
     e2e_s = max_over_ranks((time.perf_counter() - t0) / max(e2e_steps, 1))
 

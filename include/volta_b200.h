@@ -247,6 +247,17 @@ int vb_optimizer_set_grad_present(vb_optimizer *opt, int64_t tensor, int present
 int vb_optimizer_step(vb_optimizer *opt);
 int vb_optimizer_step_ex(vb_optimizer *opt, uint32_t flags);
 
+/* The whole step for a host-resident model in one call (Adam, SGD): `grads_host` and
+ * `params_host` are host images of the arena (vb_optimizer_arena gives its length and the
+ * tensor offsets).  The owned part of the arena is cut into `pieces` (1..64); for each piece
+ * the gradients are copied to the device, updated, and the new parameters copied back, on
+ * three streams so that the upload of piece j+1, the update of piece j and the download of
+ * piece j-1 overlap (PCIe is full duplex).  Every gradient counts as present.  Returns when
+ * the parameters are in `params_host`.  Use pinned host memory (vb_host_alloc_pinned):
+ * pageable buffers work but serialise the copies.  This is what Volta's step() costs a
+ * CPU-resident model (src/nn/optim/adam.rs:70-95), minus the two gradient clones. */
+int vb_optimizer_step_host(vb_optimizer *opt, const float *grads_host, float *params_host, int pieces);
+
 /* zero_grad(): marks every gradient absent (`grad = None`, src/nn/optim/adam.rs:62-66,
  * sgd.rs:58-62, muon.rs:40-44).  The gradient arena itself is left as is. */
 int vb_optimizer_zero_grad(vb_optimizer *opt);

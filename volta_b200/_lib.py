@@ -89,6 +89,7 @@ SIGNATURES = {
     "vb_optimizer_set_grad_present": [_vp, _i64, C.c_int],
     "vb_optimizer_step": [_vp],
     "vb_optimizer_step_ex": [_vp, C.c_uint32],
+    "vb_optimizer_step_host": [_vp, _vp, _vp, C.c_int],
     "vb_optimizer_zero_grad": [_vp],
     "vb_optimizer_set_lr": [_vp, C.c_float],
     "vb_optimizer_export_state": [_vp, _i64, C.c_int, _vp, _i64, _i64p, _i64p],

@@ -202,6 +202,8 @@ static int build_chunk_table(vb_optimizer *opt, const Layout &L)
         f.pad = 0;
     }
     opt->n_chunks = (int64_t)fat.size();
+    opt->chunk_pos.resize(L.chunks.size());
+    for (size_t c = 0; c < L.chunks.size(); ++c) opt->chunk_pos[c] = opt->offsets[L.chunks[c].tensor] + L.chunks[c].offset;
     if (!fat.empty()) {
         VB_CUDA(cudaMalloc(&opt->d_chunks, fat.size() * sizeof(FatChunk)));
         VB_CUDA(cudaMemcpyAsync(opt->d_chunks, fat.data(), fat.size() * sizeof(FatChunk),
@@ -373,6 +375,9 @@ int vb_engine_destroy(vb_engine *e)
     }
     for (cudaEvent_t ev : e->prof_free) cudaEventDestroy(ev);
     if (e->d_accum_scratch) cudaFree(e->d_accum_scratch);
+    for (cudaEvent_t ev : e->pipe_events) cudaEventDestroy(ev);
+    if (e->h2d_stream) cudaStreamDestroy(e->h2d_stream);
+    if (e->d2h_stream) cudaStreamDestroy(e->d2h_stream);
     for (int i = 0; i < 2; ++i) {
         if (e->h_stage[i]) cudaFreeHost(e->h_stage[i]);
         if (e->d_stage[i]) cudaFree(e->d_stage[i]);
@@ -873,6 +878,71 @@ int vb_optimizer_step_ex(vb_optimizer *opt, uint32_t flags)
 }
 
 int vb_optimizer_step(vb_optimizer *opt) { return vb_optimizer_step_ex(opt, VB_STEP_DEFAULT); }
+
+int vb_optimizer_step_host(vb_optimizer *opt, const float *grads_host, float *params_host, int pieces)
+{
+    VB_API_BEGIN
+    VB_TRY(check_opt(opt));
+    vb_engine *e = opt->eng;
+    if (opt->kind == KIND_MUON) return fail(VB_ERR_UNSUPPORTED, "the pipelined host step is implemented for Adam and SGD");
+    if (!grads_host || !params_host) return fail(VB_ERR_INVALID_ARG, "host arena pointer is null");
+    if (pieces < 1) pieces = 1;
+    if (pieces > 64) pieces = 64;
+    VB_TRY(set_device(e));
+    if (!e->h2d_stream) VB_CUDA(cudaStreamCreateWithFlags(&e->h2d_stream, cudaStreamNonBlocking));
+    if (!e->d2h_stream) VB_CUDA(cudaStreamCreateWithFlags(&e->d2h_stream, cudaStreamNonBlocking));
+    while ((int)e->pipe_events.size() < 2 * pieces + 2) {
+        cudaEvent_t ev;
+        VB_CUDA(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+        e->pipe_events.push_back(ev);
+    }
+    int op;
+    StepScalars s;
+    if (opt->kind == KIND_ADAM) {
+        opt->t += 1;
+        op = OP_ADAM;
+        s = make_scalars(op, opt->lr, opt->beta1, opt->beta2, opt->eps, opt->weight_decay, opt->t);
+    } else {
+        op = opt->momentum > 0.0f ? OP_SGD_MOMENTUM : OP_SGD;
+        s = make_scalars(op, opt->lr, opt->momentum, 0.0f, 0.0f, opt->weight_decay, 0);
+    }
+    std::fill(opt->present.begin(), opt->present.end(), (uint8_t)1);  // a whole gradient arena arrives
+    opt->present_on_dev = opt->present;
+    VB_CUDA(cudaMemsetAsync(opt->d_present, 1, opt->present.size(), e->stream));
+    const bool fused = e->world > 1 && opt->peers.n > 0;
+    if (fused) VB_TRY(comm_barrier(e));
+    // everything enqueued so far (earlier steps, uploads) precedes the first copy of this step
+    cudaEvent_t ev_start = e->pipe_events[2 * pieces];
+    VB_CUDA(cudaEventRecord(ev_start, e->stream));
+    VB_CUDA(cudaStreamWaitEvent(e->h2d_stream, ev_start, 0));
+    VB_CUDA(cudaStreamWaitEvent(e->d2h_stream, ev_start, 0));
+    const int64_t nc = opt->n_chunks;
+    for (int j = 0; j < pieces; ++j) {
+        const int64_t c_lo = nc * j / pieces, c_hi = nc * (j + 1) / pieces;
+        if (c_hi <= c_lo) continue;
+        // the arena range the chunks [c_lo, c_hi) cover (gaps between tensors travel along)
+        const int64_t a_lo = j == 0 ? opt->shard_begin : opt->chunk_pos[(size_t)c_lo];
+        const int64_t a_hi = c_hi == nc ? opt->shard_end : opt->chunk_pos[(size_t)c_hi];
+        const size_t bytes = (size_t)(a_hi - a_lo) * sizeof(float);
+        VB_CUDA(cudaMemcpyAsync(opt->d_grad + a_lo, grads_host + a_lo, bytes, cudaMemcpyHostToDevice, e->h2d_stream));
+        VB_CUDA(cudaEventRecord(e->pipe_events[2 * j], e->h2d_stream));
+        VB_CUDA(cudaStreamWaitEvent(e->stream, e->pipe_events[2 * j], 0));
+        VB_TRY(launch_multi_tensor(op, opt->d_chunks + c_lo, c_hi - c_lo, opt->d_present, /*all_present=*/true, s,
+                                   e->sm_count, e->stream, fused ? &opt->peers : nullptr));
+        e->launches += 1;
+        VB_CUDA(cudaEventRecord(e->pipe_events[2 * j + 1], e->stream));
+        VB_CUDA(cudaStreamWaitEvent(e->d2h_stream, e->pipe_events[2 * j + 1], 0));
+        VB_CUDA(cudaMemcpyAsync(params_host + a_lo, opt->d_param + a_lo, bytes, cudaMemcpyDeviceToHost, e->d2h_stream));
+    }
+    if (e->world > 1) {
+        if (fused) VB_TRY(comm_barrier(e));
+        else VB_TRY(comm_all_gather_inplace(e, opt->d_param, opt->arena / e->world));
+    }
+    VB_CUDA(cudaStreamSynchronize(e->d2h_stream));
+    VB_CUDA(cudaStreamSynchronize(e->stream));
+    return VB_OK;
+    VB_API_END
+}
 
 int vb_optimizer_export_state(vb_optimizer *opt, int64_t tensor, int which, float *host, int64_t n,
                               int64_t *owned_begin, int64_t *owned_end)

@@ -26,6 +26,9 @@ struct vb_engine {
     size_t stage_bytes[2] = {0, 0};
     cudaEvent_t stage_done[2] = {nullptr, nullptr};
     int stage_next = 0;
+    // copy streams and events of the pipelined host step (vb_optimizer_step_host)
+    cudaStream_t h2d_stream = nullptr, d2h_stream = nullptr;
+    std::vector<cudaEvent_t> pipe_events;
     float *d_accum_scratch = nullptr;  // staging for host contributions to vb_optimizer_accumulate_grad
     size_t accum_scratch_elems = 0;
     // optional phase timing (vb_engine_set_profiling): event pairs per phase, summed on query
@@ -62,6 +65,7 @@ struct vb_optimizer {
 
     // descriptors
     vb::FatChunk *d_chunks = nullptr;
+    std::vector<int64_t> chunk_pos;  // arena position of each chunk's first element (ascending)
     int64_t n_chunks = 0;
     uint8_t *d_present = nullptr;
     std::vector<uint8_t> present;        // host truth

@@ -253,6 +253,16 @@ class _Optimizer:
         """``step()``: one fused update of every parameter that has a gradient."""
         call("vb_optimizer_step_ex", self._h, int(flags))
 
+    def step_host(self, grads_arena: np.ndarray, params_arena: np.ndarray, pieces: int = 8) -> None:
+        """One step of a host-resident model: gradients in, parameters out, both as host images of
+        the arena (``arena_layout()``); upload, update and download are pipelined piece by piece."""
+        assert grads_arena.dtype == np.float32 and params_arena.dtype == np.float32
+        assert grads_arena.flags.c_contiguous and params_arena.flags.c_contiguous
+        assert grads_arena.size == params_arena.size
+        call("vb_optimizer_step_host", self._h, grads_arena.ctypes.data_as(C.c_void_p),
+             params_arena.ctypes.data_as(C.c_void_p), int(pieces))
+        self._present = [True] * len(self.params)
+
     def zero_grad(self) -> None:
         """``zero_grad()``: every ``grad`` becomes ``None`` (adam.rs:62-66)."""
         call("vb_optimizer_zero_grad", self._h)
