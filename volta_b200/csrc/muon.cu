@@ -118,7 +118,8 @@ __global__ void reduce_partials_kernel(const float *__restrict__ partials, const
 // maps of thousands of consecutive elements with an ordered tree and applies the result to
 // k in one go.  If the result would leave the binade (k + inc >= 2^24), or s is not a normal
 // number yet, one thread walks the elements with real f32 additions until the exponent of s
-// changes and the block resumes from there; this happens about once per doubling of s.
+// changes and the block resumes from there; this happens about once per doubling of s.  The
+// per-warp maps localise the crossing to one warp's span (512 elements), so a walk is short.
 struct IncMap {
     uint32_t even;  // increment (in ulps) when k is even
     uint32_t odd;   // increment when k is odd
@@ -135,19 +136,29 @@ __device__ __forceinline__ IncMap compose(IncMap a, IncMap b)  // a first, then 
     return c;
 }
 
-__device__ __forceinline__ IncMap element_map(float a, int scale_exp)  // scale_exp = 23 - e
+__device__ __forceinline__ IncMap element_map(float a, float inv_ulp)  // inv_ulp = 2^(23 - e), a normal float
 {
+    // x = a / ulp = q + f, exact (power-of-two scaling).  q and the comparison of f with 1/2 are
+    // read off the bits of x with integer operations (no float->int conversions, which run at a
+    // quarter of the ALU rate): x = M * 2^(E - 150) with M the 24-bit significand.
     IncMap m;
-    const float x = scalbnf(a, scale_exp);  // a / ulp, exact (or 0 / inf on under/overflow)
-    if (!(x < 16777216.0f)) {               // also catches NaN
+    const uint32_t xb = __float_as_uint(__fmul_rn(a, inv_ulp));
+    const uint32_t E = xb >> 23;  // a >= 0: no sign bit (NaN/inf give E = 255)
+    if (E >= 151u) {              // x >= 2^24 (or inf/NaN): leaves the binade for certain
         m.even = m.odd = kIncSat;
         return m;
     }
-    const float q = floorf(x);
-    const float f = x - q;  // exact
-    const uint32_t qi = (uint32_t)q;
-    const uint32_t up = f > 0.5f ? 1u : 0u;
-    const uint32_t tie = f == 0.5f ? 1u : 0u;
+    if (E <= 125u) {              // x < 1/2 (including 0 and subnormal results): no change
+        m.even = m.odd = 0u;
+        return m;
+    }
+    const uint32_t M = (xb & 0x7fffffu) | 0x800000u;
+    const uint32_t sh = 150u - E;                 // 0 .. 24 fractional bits
+    const uint32_t qi = sh >= 24u ? 0u : (M >> sh);
+    const uint32_t rem = M & ((1u << sh) - 1u);   // sh <= 24 < 32
+    const uint32_t half = sh ? (1u << (sh - 1u)) : 0u;
+    const uint32_t up = (sh && rem > half) ? 1u : 0u;
+    const uint32_t tie = (sh && rem == half) ? 1u : 0u;
     m.even = qi + up + (tie & (qi & 1u));          // k even: k+q odd iff q odd -> round up to even
     m.odd = qi + up + (tie & ((qi & 1u) ^ 1u));    // k odd:  k+q odd iff q even
     return m;
@@ -155,13 +166,21 @@ __device__ __forceinline__ IncMap element_map(float a, int scale_exp)  // scale_
 
 __device__ __forceinline__ bool binade_ok(float s)
 {
+    // positive, finite, and large enough (>= 2^-100) that 1/ulp = 2^(23-e) is a normal float;
+    // smaller running sums are simply added one element at a time
     const uint32_t e = (__float_as_uint(s) >> 23) & 0xffu;
-    return s > 0.0f && e != 0u && e != 0xffu;  // positive, normal, finite
+    return s > 0.0f && e >= 27u && e != 0xffu;
 }
 
 constexpr int kSeqThreads = 512;
-constexpr int kSeqPerThread = 8;
-constexpr int kSeqChunk = kSeqThreads * kSeqPerThread;
+constexpr int kSeqPerThread = 16;
+constexpr int kSeqChunk = kSeqThreads * kSeqPerThread;       // 8192 elements per pass
+constexpr int kSeqWarpSpan = 32 * kSeqPerThread;             // elements one warp covers
+
+__device__ __forceinline__ float float_from_k(uint32_t bits_of_s, uint32_t k)
+{
+    return __uint_as_float((bits_of_s & 0x7f800000u) | (k & 0x7fffffu));
+}
 
 __global__ void __launch_bounds__(kSeqThreads)
 sumsq_ordered_kernel(const TensorDesc *__restrict__ tensors, const int32_t *__restrict__ ns_tensors,
@@ -185,10 +204,11 @@ sumsq_ordered_kernel(const TensorDesc *__restrict__ tensors, const int32_t *__re
     auto load = [&](int64_t base, float *dst) {
         const int64_t i0 = base + (int64_t)tid * kSeqPerThread;
         if (i0 + kSeqPerThread <= n) {  // tensors start 128-byte aligned: vector loads are aligned
-            const float4 a = *reinterpret_cast<const float4 *>(x + i0);
-            const float4 b = *reinterpret_cast<const float4 *>(x + i0 + 4);
-            dst[0] = a.x; dst[1] = a.y; dst[2] = a.z; dst[3] = a.w;
-            dst[4] = b.x; dst[5] = b.y; dst[6] = b.z; dst[7] = b.w;
+#pragma unroll
+            for (int q = 0; q < kSeqPerThread / 4; ++q) {
+                const float4 v = *reinterpret_cast<const float4 *>(x + i0 + 4 * q);
+                dst[4 * q + 0] = v.x; dst[4 * q + 1] = v.y; dst[4 * q + 2] = v.z; dst[4 * q + 3] = v.w;
+            }
         } else {
 #pragma unroll
             for (int i = 0; i < kSeqPerThread; ++i) dst[i] = (i0 + i < n) ? x[i0 + i] : 0.0f;
@@ -202,7 +222,7 @@ sumsq_ordered_kernel(const TensorDesc *__restrict__ tensors, const int32_t *__re
 #pragma unroll
         for (int i = 0; i < kSeqPerThread; ++i) {
             a[i] = __fmul_rn(cur[i], cur[i]);  // `x * x`, muon.rs:58 (padding squares to 0)
-            sq[tid * kSeqPerThread + i] = a[i];
+            sq[i * kSeqThreads + tid] = a[i];  // element tid*16+i, stored bank-conflict free
         }
         if (tid == 0) sh_start = 0;
         __syncthreads();
@@ -211,13 +231,15 @@ sumsq_ordered_kernel(const TensorDesc *__restrict__ tensors, const int32_t *__re
             const float s = sh_s;
             if (start >= cnt) break;
             const bool ok = binade_ok(s);
-            if (ok) {
-                const int scale_exp = 23 - ((int)((__float_as_uint(s) >> 23) & 0xffu) - 127);
+            if (ok && (warp + 1) * kSeqWarpSpan > start) {  // warps wholly before `start` have nothing to add
+                // 1/ulp(s) = 2^(23 - e) with e the unbiased exponent of s: biased exponent 150 - e - 127 + 127
+                const uint32_t biased = (__float_as_uint(s) >> 23) & 0xffu;
+                const float inv_ulp = __uint_as_float((277u - biased) << 23);
                 IncMap m = {0u, 0u};
 #pragma unroll
                 for (int i = 0; i < kSeqPerThread; ++i) {
                     const int idx = tid * kSeqPerThread + i;
-                    if (idx >= start && idx < cnt) m = compose(m, element_map(a[i], scale_exp));
+                    if (idx >= start && idx < cnt) m = compose(m, element_map(a[i], inv_ulp));
                 }
 #pragma unroll
                 for (int d = 1; d < 32; d <<= 1) {
@@ -231,24 +253,33 @@ sumsq_ordered_kernel(const TensorDesc *__restrict__ tensors, const int32_t *__re
             __syncthreads();
             if (tid == 0) {
                 float s_new = s;
-                bool advanced = false;
+                int walk_from = start;
+                bool done = false;
                 if (ok) {
-                    IncMap total = warp_maps[0];
-                    for (int w = 1; w < kSeqThreads / 32; ++w) total = compose(total, warp_maps[w]);
+                    // apply the warps' maps in order; stop at the first that would leave the binade
                     const uint32_t bits = __float_as_uint(s);
-                    const uint32_t k = (bits & 0x7fffffu) | 0x800000u;
-                    const uint32_t inc = (k & 1u) ? total.odd : total.even;
-                    if (k + inc < (1u << 24)) {
-                        s_new = __uint_as_float((bits & 0x7f800000u) | ((k + inc) & 0x7fffffu));
+                    uint32_t k = (bits & 0x7fffffu) | 0x800000u;
+                    int w = start / kSeqWarpSpan;
+                    const int w_end = (cnt + kSeqWarpSpan - 1) / kSeqWarpSpan;
+                    for (; w < w_end; ++w) {
+                        const IncMap wm = warp_maps[w];
+                        const uint32_t inc = (k & 1u) ? wm.odd : wm.even;
+                        if (k + inc >= (1u << 24)) break;
+                        k += inc;
+                    }
+                    s_new = float_from_k(bits, k);
+                    if (w == w_end) {
                         sh_start = cnt;
-                        advanced = true;
+                        done = true;
+                    } else {
+                        walk_from = max(start, w * kSeqWarpSpan);  // the crossing is inside warp w's span
                     }
                 }
-                if (!advanced) {
+                if (!done) {
                     // walk with real additions until s enters a new binade (or the chunk ends)
-                    int j = start;
+                    int j = walk_from;
                     while (j < cnt) {
-                        const float nx = __fadd_rn(s_new, sq[j]);
+                        const float nx = __fadd_rn(s_new, sq[(j % kSeqPerThread) * kSeqThreads + j / kSeqPerThread]);
                         const bool changed = ((__float_as_uint(nx) ^ __float_as_uint(s_new)) >> 23) != 0u;
                         s_new = nx;
                         ++j;
@@ -290,14 +321,38 @@ normalise_kernel(const TensorDesc *__restrict__ tensors, const ChunkDesc *__rest
         const uint32_t n4 = n >> 2;
         if (kind == 3) {
             __nv_bfloat16 *xb = xb_base + (u - upd_base);
-            for (uint32_t i = threadIdx.x; i < n; i += kEwThreads) {
-                float x = scale ? __fdiv_rn(u[i], norm) : u[i];
+            auto split3 = [&](float x, __nv_bfloat16 &b0, __nv_bfloat16 &b1, __nv_bfloat16 &b2) {
+                b0 = __float2bfloat16_rn(x);
+                x -= __bfloat162float(b0);  // exact: the residual fits in f32
+                b1 = __float2bfloat16_rn(x);
+                x -= __bfloat162float(b1);
+                b2 = __float2bfloat16_rn(x);
+            };
+            for (uint32_t i = threadIdx.x; i < n4; i += kEwThreads) {
+                float4 v = reinterpret_cast<const float4 *>(u)[i];
+                if (scale) {
+                    v.x = __fdiv_rn(v.x, norm); v.y = __fdiv_rn(v.y, norm);
+                    v.z = __fdiv_rn(v.z, norm); v.w = __fdiv_rn(v.w, norm);
+                }
+                __nv_bfloat16 p[3][4];
+                split3(v.x, p[0][0], p[1][0], p[2][0]);
+                split3(v.y, p[0][1], p[1][1], p[2][1]);
+                split3(v.z, p[0][2], p[1][2], p[2][2]);
+                split3(v.w, p[0][3], p[1][3], p[2][3]);
 #pragma unroll
                 for (int pl = 0; pl < 3; ++pl) {
-                    const __nv_bfloat16 b = __float2bfloat16_rn(x);
-                    xb[pl * plane_stride + i] = b;
-                    x -= __bfloat162float(b);  // exact: the residual fits in f32
+                    uint2 packed;
+                    packed.x = (uint32_t)__bfloat16_as_ushort(p[pl][0]) | ((uint32_t)__bfloat16_as_ushort(p[pl][1]) << 16);
+                    packed.y = (uint32_t)__bfloat16_as_ushort(p[pl][2]) | ((uint32_t)__bfloat16_as_ushort(p[pl][3]) << 16);
+                    reinterpret_cast<uint2 *>(xb + pl * plane_stride)[i] = packed;
                 }
+            }
+            for (uint32_t i = (n4 << 2) + threadIdx.x; i < n; i += kEwThreads) {
+                __nv_bfloat16 b0, b1, b2;
+                split3(scale ? __fdiv_rn(u[i], norm) : u[i], b0, b1, b2);
+                xb[i] = b0;
+                xb[plane_stride + i] = b1;
+                xb[2 * plane_stride + i] = b2;
             }
         } else if (kind == 2) {
             __nv_bfloat16 *xb = xb_base + (u - upd_base);
