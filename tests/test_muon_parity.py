@@ -142,18 +142,22 @@ def _bf16_round(x):
     return u.astype(np.uint32).view(np.float32)
 
 
-def _ns_bf16_model(x0, steps):
-    """numpy model of the bf16 path: operands rounded to bf16, f32-or-better accumulation,
-    short-side Gram; used to tell a wrong descriptor (O(1) error) from rounding (1e-3)."""
-    r, c = x0.shape
-    x = _bf16_round(x0).astype(np.float64)
+def _ns_bf16_model(u, steps):
+    """numpy model of the bf16 path: the unnormalised update rounded to bf16 is the first operand
+    and the first iteration's epilogues apply 1/norm (squared for the Gram); operands rounded to
+    bf16, f32-or-better accumulation, short-side Gram.  Used to tell a wrong descriptor (O(1)
+    error) from rounding (1e-3)."""
+    r, c = u.shape
+    inv = 1.0 / np.sqrt(np.sum(u.astype(np.float64) ** 2) + 1e-8)
+    x = _bf16_round(u).astype(np.float64)
     for it in range(steps):
+        s2, s1 = (inv * inv, inv) if it == 0 else (1.0, 1.0)
         if r >= c:
-            cm = _bf16_round((3.0 * np.eye(c) - x.T @ x).astype(np.float32)).astype(np.float64)
-            nx = 0.5 * (x @ cm)
+            cm = _bf16_round((3.0 * np.eye(c) - s2 * (x.T @ x)).astype(np.float32)).astype(np.float64)
+            nx = 0.5 * s1 * (x @ cm)
         else:
-            cm = _bf16_round((3.0 * np.eye(r) - x @ x.T).astype(np.float32)).astype(np.float64)
-            nx = 0.5 * (cm @ x)
+            cm = _bf16_round((3.0 * np.eye(r) - s2 * (x @ x.T)).astype(np.float32)).astype(np.float64)
+            nx = 0.5 * s1 * (cm @ x)
         x = nx if it == steps - 1 else _bf16_round(nx.astype(np.float32)).astype(np.float64)
     return x.astype(np.float32)
 
@@ -172,8 +176,7 @@ def test_bf16_path_single_matrix(oracle, engine, shape):
     opt.step()
     got = opt.last_update(0)
     ref = oracle.newton_schulz(g, 5)
-    x0 = g / np.sqrt(np.float32(np.sum(g.astype(np.float64) ** 2) + 1e-8)).astype(np.float32)
-    model = _ns_bf16_model(x0, 5)
+    model = _ns_bf16_model(g, 5)
     assert rel_frobenius(got, model) < 2e-3, (rel_frobenius(got, model), rel_frobenius(got, ref))
     assert rel_frobenius(got, ref) <= TOL_BF16
     assert np.allclose(w.data, -(np.float32(0.1) * got) * np.float32(0.1), rtol=0, atol=1e-9)

@@ -27,10 +27,14 @@ constexpr int kEwThreads = 256;
 
 // ---- K3a: momentum (+ Nesterov), optional per-chunk sum of squares ------------------------
 // TensorDesc fields here: p = weights, g = gradient, s1 = velocity, s2 = update buffer.
+// `direct_bf16` (may be null): tensors flagged there feed the tensor-core chain with the
+// *unnormalised* update (the 1/norm factors are applied by the first iteration's epilogues), so
+// this kernel writes the bf16 operand itself and the separate normalise pass is skipped.
 template <bool PARTIALS>
 __global__ void __launch_bounds__(kEwThreads)
 momentum_kernel(const TensorDesc *__restrict__ tensors, const ChunkDesc *__restrict__ chunks, int64_t n_chunks,
-                const uint8_t *__restrict__ present, float momentum, int nesterov, float *__restrict__ partials)
+                const uint8_t *__restrict__ present, float momentum, int nesterov, float *__restrict__ partials,
+                const uint8_t *__restrict__ direct_bf16, const float *upd_base, __nv_bfloat16 *__restrict__ xb_base)
 {
     __shared__ float warp_sums[kEwThreads / 32];
     for (int64_t c = blockIdx.x; c < n_chunks; c += gridDim.x) {
@@ -40,6 +44,8 @@ momentum_kernel(const TensorDesc *__restrict__ tensors, const ChunkDesc *__restr
         const float *__restrict__ g = td.g + ch.offset;
         float *__restrict__ v = td.s1 + ch.offset;
         float *__restrict__ u = td.s2 + ch.offset;
+        const bool to_bf16 = direct_bf16 != nullptr && direct_bf16[ch.tensor] != 0;
+        __nv_bfloat16 *__restrict__ xb = to_bf16 ? xb_base + (u - upd_base) : nullptr;
         const uint32_t n = ch.len;
         float local = 0.0f;
         const uint32_t n4 = n >> 2;  // chunk starts are 16-byte aligned by construction
@@ -60,7 +66,15 @@ momentum_kernel(const TensorDesc *__restrict__ tensors, const ChunkDesc *__restr
                 u4 = v4;
             }
             __stcs(reinterpret_cast<float4 *>(v) + i, v4);
-            reinterpret_cast<float4 *>(u)[i] = u4;  // read again soon: keep it in L2
+            if (to_bf16) {
+                __nv_bfloat162 lo = __floats2bfloat162_rn(u4.x, u4.y), hi = __floats2bfloat162_rn(u4.z, u4.w);
+                uint2 packed;
+                packed.x = *reinterpret_cast<uint32_t *>(&lo);
+                packed.y = *reinterpret_cast<uint32_t *>(&hi);
+                reinterpret_cast<uint2 *>(xb)[i] = packed;
+            } else {
+                reinterpret_cast<float4 *>(u)[i] = u4;  // read again soon: keep it in L2
+            }
             if (PARTIALS) local += u4.x * u4.x + u4.y * u4.y + u4.z * u4.z + u4.w * u4.w;
         }
         for (uint32_t i = (n4 << 2) + threadIdx.x; i < n; i += kEwThreads) {
@@ -68,7 +82,8 @@ momentum_kernel(const TensorDesc *__restrict__ tensors, const ChunkDesc *__restr
             const float vv = __fmaf_rn(momentum, v[i], gv);
             const float uv = nesterov ? __fadd_rn(__fmul_rn(momentum, vv), gv) : vv;
             v[i] = vv;
-            u[i] = uv;
+            if (to_bf16) xb[i] = __float2bfloat16_rn(uv);
+            else u[i] = uv;
             if (PARTIALS) local += uv * uv;
         }
         if (PARTIALS) {
@@ -308,12 +323,13 @@ __global__ void __launch_bounds__(kEwThreads)
 normalise_kernel(const TensorDesc *__restrict__ tensors, const ChunkDesc *__restrict__ chunks, int64_t n_chunks,
                  const uint8_t *__restrict__ present, const uint8_t *__restrict__ ns_kind,
                  const float *__restrict__ sumsq, const float *upd_base, __nv_bfloat16 *__restrict__ xb_base,
-                 int64_t plane_stride)
+                 int64_t plane_stride, const uint8_t *__restrict__ skip)
 {
     for (int64_t c = blockIdx.x; c < n_chunks; c += gridDim.x) {
         const ChunkDesc ch = chunks[c];
         const int kind = ns_kind[ch.tensor];
         if (present[ch.tensor] == 0 || kind == 0) continue;
+        if (skip != nullptr && skip[ch.tensor] != 0) continue;  // normalisation folded into the GEMM epilogues
         float *u = tensors[ch.tensor].s2 + ch.offset;
         const float norm = __fsqrt_rn(__fadd_rn(sumsq[ch.tensor], 1e-8f));
         const bool scale = norm > 1e-8f;
@@ -468,9 +484,11 @@ struct MuonState {
     GemmTile *d_gram_tiles = nullptr, *d_upd_tiles = nullptr;
     int n_gram_tiles = 0, n_upd_tiles = 0;
     // tensor-core GEMM schedules: [parity]; the last iteration's update writes the f32 result
-    TcGemmProblem *d_tc_gram[2] = {nullptr, nullptr};
-    TcGemmProblem *d_tc_upd[2] = {nullptr, nullptr};
-    TcGemmProblem *d_tc_upd_final = nullptr;
+    // tensor-core GEMM schedules, one problem array per Newton-Schulz iteration (the first may
+    // fold the normalisation in, the last writes the f32 result)
+    std::vector<TcGemmProblem *> d_tc_gram, d_tc_upd;
+    uint8_t *d_fold_norm = nullptr;    // per tensor: normalisation folded into the first iteration
+    bool fold_norm = false;
     GemmTile *d_tc_gram_tiles = nullptr, *d_tc_upd_tiles = nullptr;
     int n_tc_gram_tiles = 0, n_tc_upd_tiles = 0;
     int *d_error = nullptr;
@@ -500,10 +518,10 @@ void destroy_muon_state(MuonState *s)
     for (int i = 0; i < 2; ++i) {
         cudaFree(s->d_gram_prob[i]);
         cudaFree(s->d_upd_prob[i]);
-        cudaFree(s->d_tc_gram[i]);
-        cudaFree(s->d_tc_upd[i]);
     }
-    cudaFree(s->d_tc_upd_final);
+    for (TcGemmProblem *p : s->d_tc_gram) cudaFree(p);
+    for (TcGemmProblem *p : s->d_tc_upd) cudaFree(p);
+    cudaFree(s->d_fold_norm);
     cudaFree(s->d_gram_tiles);
     cudaFree(s->d_upd_tiles);
     cudaFree(s->d_tc_gram_tiles);
@@ -713,10 +731,16 @@ int muon_init(vb_optimizer *opt)
     if (!tc_tensors.empty()) {
         int bm, bn;
         tc_gemm_tile_shape(&bm, &bn);
-        std::vector<TcGemmProblem> gram[2], upd[2], upd_final;
+        const int iters = opt->ns_steps;
+        std::vector<std::vector<TcGemmProblem>> gram((size_t)iters), upd((size_t)iters);
         std::vector<GemmTile> gram_tiles, upd_tiles;
         std::stable_sort(tc_tensors.begin(), tc_tensors.end(), by_size);
-        const int final_par = (opt->ns_steps - 1) & 1;
+        // plain bf16 path: the momentum kernel writes the unnormalised bf16 operand and the first
+        // iteration's epilogues apply 1/norm; the split path keeps the reference's true division
+        s->fold_norm = s->planes == 1;
+        std::vector<uint8_t> fold((size_t)std::max<int64_t>(nt, 1), 0);
+        for (int32_t t : tc_tensors) fold[(size_t)t] = s->fold_norm ? 1 : 0;
+        VB_TRY(upload(&s->d_fold_norm, fold, e->stream));
         for (int32_t t : tc_tensors) {
             const int r = (int)opt->rows[t], c = (int)opt->cols[t];
             const bool tall = r >= c;
@@ -734,7 +758,9 @@ int muon_init(vb_optimizer *opt)
             }
             VB_TRY(make_bf16_tensor_map(&map_c, cb, sh, sh, TC_OP_K_MAJOR, planes, s->cb_elems));
             const int pidx = (int)gram[0].size();
-            for (int par = 0; par < 2; ++par) {
+            for (int it = 0; it < iters; ++it) {
+                const int par = it & 1;
+                const bool first = it == 0, last = it == iters - 1;
                 // C = 3I - X^T X (tall: both operands are X read with k = row index, "MN-major")
                 // C = 3I - X X^T (wide: both operands are X, K-major)
                 TcGemmProblem g{};
@@ -747,7 +773,11 @@ int muon_init(vb_optimizer *opt)
                 g.epilogue = planes == 3 ? TC_EPI_IDENTITY : TC_EPI_THREE_I_MINUS; g.ld_out = sh; g.tensor = t;
                 g.n_terms = n_terms; g.n_out_planes = planes; g.out_plane_stride = s->cb_elems;
                 g.out_bf16 = cb; g.out_f32 = nullptr;
-                gram[par].push_back(g);
+                if (first && s->fold_norm) {  // operands are u, not u/norm: G = (u^T u) / norm^2
+                    g.scale_sumsq = s->d_sumsq + t;
+                    g.scale_power = 2;
+                }
+                gram[(size_t)it].push_back(g);
                 // X' = 0.5 X C (tall: A = X K-major, B = C which is symmetric)
                 // X' = 0.5 C X (wide: A = C, B = X read with k = row index)
                 TcGemmProblem u{};
@@ -760,12 +790,15 @@ int muon_init(vb_optimizer *opt)
                 u.in_bf16 = xb[par];
                 u.n_terms = n_terms; u.n_out_planes = planes; u.out_plane_stride = s->owned_elems;
                 u.out_bf16 = xb[par ^ 1]; u.out_f32 = nullptr;
-                upd[par].push_back(u);
-                if (par == final_par) {
+                if (first && s->fold_norm) {  // X1 = 0.5 (u C) / norm
+                    u.scale_sumsq = s->d_sumsq + t;
+                    u.scale_power = 1;
+                }
+                if (last) {
                     u.out_bf16 = nullptr;  // last iteration: the f32 update is the result
                     u.out_f32 = s->d_upd + s->local_off[(size_t)t];
-                    upd_final.push_back(u);
                 }
+                upd[(size_t)it].push_back(u);
             }
             // The Gram is symmetric: with square tiles only those on or above the diagonal are
             // computed; off-diagonal ones are also stored transposed by the epilogue.
@@ -785,11 +818,12 @@ int muon_init(vb_optimizer *opt)
             s->flops_per_step += (double)n_terms * (double)opt->ns_steps *
                                  (prod * (double)gram_used / (double)gram_all + prod);
         }
-        for (int par = 0; par < 2; ++par) {
-            VB_TRY(upload(&s->d_tc_gram[par], gram[par], e->stream));
-            VB_TRY(upload(&s->d_tc_upd[par], upd[par], e->stream));
+        s->d_tc_gram.assign((size_t)iters, nullptr);
+        s->d_tc_upd.assign((size_t)iters, nullptr);
+        for (int it = 0; it < iters; ++it) {
+            VB_TRY(upload(&s->d_tc_gram[(size_t)it], gram[(size_t)it], e->stream));
+            VB_TRY(upload(&s->d_tc_upd[(size_t)it], upd[(size_t)it], e->stream));
         }
-        VB_TRY(upload(&s->d_tc_upd_final, upd_final, e->stream));
         VB_TRY(upload(&s->d_tc_gram_tiles, gram_tiles, e->stream));
         VB_TRY(upload(&s->d_tc_upd_tiles, upd_tiles, e->stream));
         s->n_tc_gram_tiles = (int)gram_tiles.size();
@@ -809,14 +843,17 @@ int muon_step(vb_optimizer *opt, uint32_t flags)
     const bool fast_norm = opt->ns_mode == VB_NS_BF16;  // both f32 modes need the reference's ordered sum
     prof_begin(e, VB_PHASE_MUON_PRE);
     if (s->n_chunks > 0) {
+        const uint8_t *direct = s->fold_norm ? s->d_fold_norm : nullptr;
         if (fast_norm)
             momentum_kernel<true><<<ew_grid, kEwThreads, 0, e->stream>>>(s->d_desc, s->d_chunks, s->n_chunks,
                                                                           opt->d_present, opt->momentum,
-                                                                          opt->nesterov, s->d_partials);
+                                                                          opt->nesterov, s->d_partials, direct,
+                                                                          s->d_upd, s->d_xb[0]);
         else
             momentum_kernel<false><<<ew_grid, kEwThreads, 0, e->stream>>>(s->d_desc, s->d_chunks, s->n_chunks,
                                                                            opt->d_present, opt->momentum,
-                                                                           opt->nesterov, s->d_partials);
+                                                                           opt->nesterov, s->d_partials, direct,
+                                                                           s->d_upd, s->d_xb[0]);
         VB_CUDA(cudaGetLastError());
         e->launches += 1;
     }
@@ -830,21 +867,19 @@ int muon_step(vb_optimizer *opt, uint32_t flags)
         VB_CUDA(cudaGetLastError());
         normalise_kernel<<<ew_grid, kEwThreads, 0, e->stream>>>(s->d_desc, s->d_chunks, s->n_chunks, opt->d_present,
                                                                s->d_ns_kind, s->d_sumsq, s->d_upd, s->d_xb[0],
-                                                               s->owned_elems);
+                                                               s->owned_elems, s->fold_norm ? s->d_fold_norm : nullptr);
         VB_CUDA(cudaGetLastError());
         e->launches += 2;
         prof_end(e, VB_PHASE_MUON_PRE);
         prof_begin(e, VB_PHASE_MUON_NS);
         for (int it = 0; it < opt->ns_steps; ++it) {
             const int par = it & 1;
-            const bool last = it == opt->ns_steps - 1;
             if (s->n_tc_gram_tiles > 0) {
                 const bool split = s->planes == 3;
-                VB_TRY(launch_ns_gemm_tc(s->d_tc_gram[par], s->d_tc_gram_tiles, s->n_tc_gram_tiles, opt->d_present,
-                                         s->d_error, e->sm_count, e->stream, 0, split));
-                VB_TRY(launch_ns_gemm_tc(last ? s->d_tc_upd_final : s->d_tc_upd[par], s->d_tc_upd_tiles,
-                                         s->n_tc_upd_tiles, opt->d_present, s->d_error, e->sm_count, e->stream, 0,
-                                         split));
+                VB_TRY(launch_ns_gemm_tc(s->d_tc_gram[(size_t)it], s->d_tc_gram_tiles, s->n_tc_gram_tiles,
+                                         opt->d_present, s->d_error, e->sm_count, e->stream, 0, split));
+                VB_TRY(launch_ns_gemm_tc(s->d_tc_upd[(size_t)it], s->d_tc_upd_tiles, s->n_tc_upd_tiles,
+                                         opt->d_present, s->d_error, e->sm_count, e->stream, 0, split));
                 e->launches += 2;
             }
             if (s->n_gram_tiles > 0) {

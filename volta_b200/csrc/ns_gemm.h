@@ -63,6 +63,10 @@ struct alignas(128) TcGemmProblem {
     int32_t n_terms;         // 1: plain bf16 operands; 6: operands split into three bf16 planes (f32-accurate)
     int32_t n_out_planes;    // planes written to out_bf16: 1 (bf16 rounding) or 3 (split)
     int64_t out_plane_stride;  // elements between output planes
+    const float *scale_sumsq;      // if set: the accumulator is scaled by s^scale_power, s = 1/sqrt(*scale_sumsq + 1e-8)
+                                   // (the Frobenius normalisation of muon.rs:59-64 folded into the first iteration)
+    int32_t scale_power;           // 1 or 2
+    int32_t pad0;
     const __nv_bfloat16 *in_bf16;  // TC_EPI_NS_COMBINE only: planes of X (same ld and plane stride as the output)
     __nv_bfloat16 *out_bf16; // may be null
     float *out_f32;          // may be null

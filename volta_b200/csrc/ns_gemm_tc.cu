@@ -573,6 +573,14 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
             __nv_bfloat16 *out_bf16 = p->out_bf16;
             float *out_f32 = p->out_f32;
             const __nv_bfloat16 *in_bf16 = p->in_bf16;  // TC_EPI_NS_COMBINE: the planes of X at the output position
+            // Frobenius normalisation folded into the first iteration (plain bf16 path): the operand is
+            // the unnormalised update u, the accumulator is scaled by 1/norm (or its square)
+            float acc_scale = 1.0f;
+            if (!kSplit && p->scale_sumsq) {
+                const float norm = sqrtf(*p->scale_sumsq + 1e-8f);  // muon.rs:59
+                const float inv = norm > 1e-8f ? 1.0f / norm : 1.0f;  // muon.rs:60
+                acc_scale = p->scale_power == 2 ? inv * inv : inv;
+            }
             const int64_t ld = p->ld_out;
             const int out_planes = kSplit ? p->n_out_planes : 1;  // 1: bf16 rounding; 3: split into three pieces
             const int out_planes_in = kSplit ? 3 : 1;             // planes of the operands (and of in_bf16)
@@ -599,7 +607,7 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
                     float f[32];
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
-                        const float a = __uint_as_float(v[cc & 1][j]);
+                        const float a = __uint_as_float(v[cc & 1][j]) * acc_scale;
                         if (epi == TC_EPI_THREE_I_MINUS) f[j] = (row == col0 + j) ? 3.0f - a : -a;  // muon.rs:76-89
                         else if (epi == TC_EPI_HALF) f[j] = 0.5f * a;                               // muon.rs:95-99
                         else f[j] = a;  // TC_EPI_IDENTITY, or TC_EPI_NS_COMBINE (finished below)
