@@ -480,7 +480,10 @@ def run_muon(args, eng, world, rank, dev, barrier, max_over_ranks, peaks):
                 "bound": "tensor", "achieved": tflops, "peak": peak, "unit": "TFLOP/s", "frac": tflops / peak,
                 "peak_source": peaks["source"] + " (cuBLAS bf16 sustained)",
                 "frac_of_burst_peak": tflops / (peaks["bf16_tflops"] * world),
-                "frac_of_nominal_2250": tflops / (2250.0 * world), "traffic": None,
+                "frac_of_nominal_2250": tflops / (2250.0 * world),
+                "traffic": NCU_MUON_4LAYER_DRAM_BYTES_PER_LAUNCH * args.muon_layers / 4.0 / world,
+                "traffic_note": "ncu capture of the 4-layer case (mean of a Gram and an update launch), scaled by "
+                                "layers / 4: per-launch traffic grows with the number of matrices",
                 "kernel": "ns_gemm_tc_kernel (tcgen05 bf16, 10 launches per step)"}
         opt.close()
     out["config"] = {"workload": f"c4_muon: {len(wl.shapes)} matrices ({args.muon_layers} x {{3072x1024, 1024x1024, "
@@ -500,6 +503,12 @@ def run_muon(args, eng, world, rank, dev, barrier, max_over_ranks, peaks):
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of multi_tensor_update_kernel<ADAM>
 # on this workload, from the ncu capture summarised in profiles/adam_c3_multi_tensor_update.md
 NCU_ADAM_C3_DRAM_BYTES_PER_LAUNCH = 3.0164e9
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of ns_gemm_tc_kernel<2, 0> on 4 layers of the Muon
+# workload (16 matrices): mean of a Gram launch (110.2 MB) and an update launch (205.3 MB), from the ncu
+# capture summarised in profiles/muon_c4_ns_gemm_tc.md
+NCU_MUON_4LAYER_DRAM_BYTES_PER_LAUNCH = 157.7e6
 
 
 def traffic_from_profile():
