@@ -33,8 +33,33 @@ def test_large_tensor_round_trip():
         assert back[k][1] == s and np.array_equal(back[k][0].view(np.uint32), d.view(np.uint32))
 
 
+def test_safetensors_layout_known_answer_and_library_reads_it(tmp_path):
+    """The published SafeTensors layout, byte for byte, and a cross-check with the safetensors
+    package (the Python binding of the crate Volta links, src/io.rs:6)."""
+    from volta_b200.checkpoint import decode_safetensors, encode_safetensors
+    state = {"b": (np.array([1.5, -2.0], np.float32), (2,)), "a": (np.array([0.25], np.float32), (1, 1))}
+    blob = encode_safetensors(state)
+    header = b'{"a":{"dtype":"F32","shape":[1,1],"data_offsets":[0,4]},"b":{"dtype":"F32","shape":[2],"data_offsets":[4,12]}}'
+    header += b" " * (-len(header) % 8)
+    assert blob == struct.pack("<Q", len(header)) + header + struct.pack("<fff", 0.25, 1.5, -2.0)
+    back = decode_safetensors(blob)
+    assert list(back) == ["a", "b"] and back["a"][1] == (1, 1) and np.array_equal(back["b"][0], [1.5, -2.0])
+    st = pytest.importorskip("safetensors.numpy")
+    path = os.path.join(tmp_path, "s.safetensors")
+    with open(path, "wb") as fh:
+        fh.write(blob)
+    lib = st.load_file(path)
+    assert lib["a"].shape == (1, 1) and np.array_equal(lib["b"], [1.5, -2.0])
+    theirs = st.save({"optimizer.t": np.array([7.0], np.float32), "optimizer.state0.0": np.arange(6, dtype=np.float32).reshape(2, 3)})
+    mine = decode_safetensors(theirs)
+    assert mine["optimizer.state0.0"][1] == (2, 3) and mine["optimizer.t"][0][0] == 7.0
+    with pytest.raises(ValueError):
+        decode_safetensors(blob[:20])
+
+
 @pytest.mark.gpu
-def test_resume_from_checkpoint_is_bit_identical(engine, tmp_path):
+@pytest.mark.parametrize("name", ["opt.bin", "opt.safetensors"])
+def test_resume_from_checkpoint_is_bit_identical(engine, tmp_path, name):
     from volta_b200 import Adam, Tensor
     from volta_b200.checkpoint import load_optimizer_state, save_optimizer_state
     rng = np.random.default_rng(3)
@@ -47,7 +72,7 @@ def test_resume_from_checkpoint_is_bit_identical(engine, tmp_path):
         for t, gi in zip(a, g):
             t.grad = gi
         opt_a.step()
-    path = os.path.join(tmp_path, "opt.bin")
+    path = os.path.join(tmp_path, name)
     save_optimizer_state(opt_a, path)
     b = [Tensor(t.data.copy()) for t in a]
     opt_b = Adam(b, 1e-3, (0.9, 0.999), 1e-8, 0.01, engine=engine)

@@ -11,12 +11,19 @@ writes the state of a ``volta_b200`` optimizer into that same container, so that
     optimizer.state0.<i>      parameter i's shape: Adam m / SGD velocity / Muon velocity
     optimizer.state1.<i>      parameter i's shape: Adam v
 
+The same dictionary can be written as a SafeTensors file, the other container Volta reads and
+writes (``save_safetensors`` / ``load_safetensors``, src/io.rs:280-345: every tensor F32).
+SafeTensors: u64 little-endian header length, a JSON header ``{name: {"dtype", "shape",
+"data_offsets": [begin, end]}}`` padded with spaces to a multiple of 8 bytes, then the tensors'
+bytes back to back in header order.
+
 bincode ``standard()``: little endian; unsigned integers as varints (< 251: one byte; 251 +
 u16; 252 + u32; 253 + u64); f32 as four bytes; ``Vec``/``String``/map = varint length + items;
 ``BTreeMap`` iterates in key order (byte-wise string order).
 """
 from __future__ import annotations
 
+import json
 import struct
 from typing import Dict, Tuple
 
@@ -94,6 +101,47 @@ def decode_state_dict(blob: bytes) -> StateDict:
     return state
 
 
+def encode_safetensors(state: StateDict) -> bytes:
+    """SafeTensors image of a state dict: all tensors F32, in key order (src/io.rs:321-345)."""
+    header = {}
+    offset = 0
+    blobs = []
+    for key in sorted(state, key=lambda k: k.encode("utf-8")):
+        data, shape = state[key]
+        flat = np.ascontiguousarray(data, dtype="<f4").reshape(-1)
+        if int(np.prod(shape, dtype=np.int64)) != flat.size:
+            raise ValueError(f"{key}: shape {shape} does not hold {flat.size} elements")
+        header[key] = {"dtype": "F32", "shape": [int(d) for d in shape],
+                       "data_offsets": [offset, offset + flat.size * 4]}
+        offset += flat.size * 4
+        blobs.append(flat.tobytes())
+    text = json.dumps(header, separators=(",", ":")).encode("utf-8")
+    text += b" " * (-len(text) % 8)
+    return struct.pack("<Q", len(text)) + text + b"".join(blobs)
+
+
+def decode_safetensors(blob: bytes) -> StateDict:
+    """Inverse of :func:`encode_safetensors`; accepts any SafeTensors file whose tensors are F32."""
+    if len(blob) < 8:
+        raise ValueError("SafeTensors file shorter than its length field")
+    (n,) = struct.unpack_from("<Q", blob, 0)
+    if 8 + n > len(blob):
+        raise ValueError("SafeTensors header runs past the end of the file")
+    header = json.loads(bytes(blob[8:8 + n]).decode("utf-8"))
+    base = 8 + n
+    out: StateDict = {}
+    for key in sorted((k for k in header if k != "__metadata__"), key=lambda k: k.encode("utf-8")):
+        info = header[key]
+        if info["dtype"] != "F32":
+            raise ValueError(f"{key}: dtype {info['dtype']} (optimizer state is F32)")
+        begin, end = info["data_offsets"]
+        shape = tuple(int(d) for d in info["shape"])
+        if end - begin != 4 * int(np.prod(shape, dtype=np.int64)) or base + end > len(blob):
+            raise ValueError(f"{key}: data_offsets do not match the shape or the file")
+        out[key] = (np.frombuffer(blob, dtype="<f4", count=(end - begin) // 4, offset=base + begin).copy(), shape)
+    return out
+
+
 _KINDS = {"Adam": 0, "SGD": 1, "Muon": 2}
 
 
@@ -117,14 +165,23 @@ def optimizer_state_dict(opt) -> StateDict:
     return state
 
 
-def save_optimizer_state(opt, path: str) -> None:
+def _is_safetensors(path: str, fmt: str) -> bool:
+    if fmt not in ("auto", "bincode", "safetensors"):
+        raise ValueError("format is 'auto', 'bincode' or 'safetensors'")
+    return fmt == "safetensors" or (fmt == "auto" and path.endswith(".safetensors"))
+
+
+def save_optimizer_state(opt, path: str, format: str = "auto") -> None:
+    """``format='auto'`` writes SafeTensors for ``*.safetensors`` and bincode otherwise."""
+    state = optimizer_state_dict(opt)
     with open(path, "wb") as fh:
-        fh.write(encode_state_dict(optimizer_state_dict(opt)))
+        fh.write(encode_safetensors(state) if _is_safetensors(path, format) else encode_state_dict(state))
 
 
-def load_optimizer_state(opt, path: str) -> None:
+def load_optimizer_state(opt, path: str, format: str = "auto") -> None:
     with open(path, "rb") as fh:
-        state = decode_state_dict(fh.read())
+        blob = fh.read()
+    state = decode_safetensors(blob) if _is_safetensors(path, format) else decode_state_dict(blob)
     kind = type(opt).__name__
     if int(state["optimizer.kind"][0][0]) != _KINDS[kind]:
         raise ValueError("checkpoint was written by a different optimizer kind")
