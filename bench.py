@@ -175,6 +175,16 @@ def run_reference(args):
 # GPU arm
 # ---------------------------------------------------------------------------------------------
 
+def gather_handles(mine: bytes, world: int, dev):
+    """Every rank's 64-byte CUDA IPC handle, in rank order (torch.distributed is the transport)."""
+    import torch
+    t = torch.frombuffer(bytearray(mine), dtype=torch.uint8).to(dev)
+    allh = torch.zeros(world * 64, dtype=torch.uint8, device=dev)
+    torch.distributed.all_gather_into_tensor(allh, t)
+    blob = allh.cpu().numpy().tobytes()
+    return [blob[r * 64:(r + 1) * 64] for r in range(world)]
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -226,11 +236,7 @@ def run_ours(args):
     tensors = [Tensor(p, p.shape) for p in params]
     opt = Adam(tensors, h["lr"], h["betas"], h["eps"], h["weight_decay"], engine=eng)
     if world > 1 and args.exchange == "peer":
-        mine = torch.frombuffer(bytearray(opt.ipc_handle()), dtype=torch.uint8).to(dev)
-        allh = torch.zeros(world * 64, dtype=torch.uint8, device=dev)
-        dist.all_gather_into_tensor(allh, mine)
-        blob = allh.cpu().numpy().tobytes()
-        opt.open_peers([blob[r * 64:(r + 1) * 64] for r in range(world)])
+        opt.open_peers(gather_handles(opt.ipc_handle(), world, dev))
     _, _, arena, offsets = opt.arena_layout()
     grads_pinned = PinnedBuffer(arena)
     grads_pinned.array[:] = fill_arena(wl, offsets, arena, wl.make_grads(1))
@@ -288,6 +294,24 @@ def run_ours(args):
     barrier()
     e2e_s = max_over_ranks((time.perf_counter() - t0) / max(e2e_steps, 1))
 
+    # ---- N > 1: the same step exchanging bf16 copies of the parameters instead of f32 ----
+    bf16_exchange = None
+    if world > 1:
+        from volta_b200 import VB_STEP_EXCHANGE_BF16
+        opt.enable_bf16_params()
+        if args.exchange == "peer":
+            opt.open_peers_bf16(gather_handles(opt.ipc_handle_bf16(), world, dev))
+        for _ in range(3):
+            opt.step(VB_STEP_EXCHANGE_BF16)
+        barrier()
+        half_ms, _ = timed_steps(args.steps, VB_STEP_EXCHANGE_BF16)
+        barrier()
+        half_ms = max_over_ranks(half_ms) / args.steps
+        bf16_exchange = {"value": wl.total / (half_ms * 1e-3), "unit": "params/s", "ms_per_step": half_ms,
+                         "note": "step(VB_STEP_EXCHANGE_BF16): the update kernel also writes bf16 copies of the new "
+                                 "parameters and only those cross NVLink (2 B/param instead of 4); f32 masters stay "
+                                 "exact on their owners"}
+
     opt.close()
     grads_pinned.free()
     params_pinned.free()
@@ -339,6 +363,8 @@ def run_ours(args):
                                 "sample": f"{len(times)} full steps of the same workload, 1 thread of "
                                           f"{os.cpu_count()} host cores (Volta's optimizer is single threaded)",
                                 "ms_per_step": sec * 1e3}
+    if bf16_exchange is not None:
+        line["bf16_exchange"] = bf16_exchange
     if muon is not None:
         line["muon"] = muon
     if c5 is not None:
@@ -422,11 +448,7 @@ def run_muon(args, eng, world, rank, dev, barrier, max_over_ranks, peaks):
         tensors = [Tensor(p, p.shape) for p in params]
         opt = Muon(tensors, h["lr"], h["momentum"], h["nesterov"], h["ns_steps"], ns_mode=mode, engine=eng)
         if world > 1 and args.exchange == "peer":
-            mine = torch.frombuffer(bytearray(opt.ipc_handle()), dtype=torch.uint8).to(dev)
-            allh = torch.zeros(world * 64, dtype=torch.uint8, device=dev)
-            torch.distributed.all_gather_into_tensor(allh, mine)
-            blob = allh.cpu().numpy().tobytes()
-            opt.open_peers([blob[r * 64:(r + 1) * 64] for r in range(world)])
+            opt.open_peers(gather_handles(opt.ipc_handle(), world, dev))
         _, _, arena, offsets = opt.arena_layout()
         host = fill_arena(wl, offsets, arena, grads)
         opt.upload_arena(1, host)
@@ -475,6 +497,23 @@ def run_muon(args, eng, world, rank, dev, barrier, max_over_ranks, peaks):
             "reference_formulation_flops_per_step": sum(4.0 * r * c * c * h["ns_steps"] for r, c in wl.shapes),
             "gpu_launches": int(eng.launch_count - launches0),
         }
+        if mode_name == "bf16" and world > 1:
+            from volta_b200 import VB_STEP_EXCHANGE_BF16
+            opt.enable_bf16_params()
+            if args.exchange == "peer":
+                opt.open_peers_bf16(gather_handles(opt.ipc_handle_bf16(), world, dev))
+            for _ in range(2):
+                opt.step(VB_STEP_EXCHANGE_BF16)
+            barrier()
+            e0.record(stream)
+            for _ in range(steps):
+                opt.step(VB_STEP_EXCHANGE_BF16)
+            e1.record(stream)
+            eng.synchronize()
+            barrier()
+            half_ms = max_over_ranks(e0.elapsed_time(e1) / steps)
+            out[mode_name]["bf16_exchange"] = {"ms_per_step": half_ms, "params_per_s": wl.total / (half_ms * 1e-3),
+                                               "note": "step(VB_STEP_EXCHANGE_BF16): owners send bf16 copies only"}
         if mode_name == "bf16":
             out[mode_name]["roofline"] = {
                 "bound": "tensor", "achieved": tflops, "peak": peak, "unit": "TFLOP/s", "frac": tflops / peak,

@@ -78,6 +78,8 @@ typedef enum vb_ns_mode {
 /* Flags of vb_optimizer_step_ex. */
 #define VB_STEP_DEFAULT 0u
 #define VB_STEP_NO_EXCHANGE 1u /* sharded engines: update the owned part only, skip the all-gather / broadcast */
+#define VB_STEP_EXCHANGE_BF16 2u /* sharded engines with the bf16 copy enabled: exchange only the bf16 copies (half the
+                                    bytes); f32 parameters other ranks own are left as they were */
 
 /* ---- library ---------------------------------------------------------------------- */
 
@@ -275,6 +277,29 @@ int vb_optimizer_set_lr(vb_optimizer *opt, float lr);
 #define VB_IPC_HANDLE_BYTES 64
 int vb_optimizer_ipc_handle(vb_optimizer *opt, void *handle64);
 int vb_optimizer_open_peers(vb_optimizer *opt, const void *handles, int n_handles);
+
+/* bf16 copies of the parameters, written by the update kernel next to the f32 master (no
+ * counterpart in the reference's optimizers; the rounding is the one its bf16 storage type
+ * uses, round to nearest even, src/storage.rs:499-505).  After enabling, the library keeps a
+ * second arena of one 16-bit word per parameter with bf16[i] == rne(param[i]): it is filled
+ * from the current parameters, refreshed by every upload of parameters through this API and
+ * written by every step for the parameters the step updates (call
+ * vb_optimizer_refresh_bf16_params after writing parameters through vb_optimizer_param_ptr).
+ * On a sharded engine the default step() exchanges both the f32 parameters and the copies;
+ * VB_STEP_EXCHANGE_BF16 exchanges only the copies: 2 instead of 4 bytes per parameter cross
+ * NVLink, every rank ends the step with the complete bf16 arena and with exact f32 values
+ * for the part it owns only.  The copies travel by NCCL, or by peer stores fused into the
+ * update / apply kernel once vb_optimizer_open_peers_bf16 was given every rank's
+ * vb_optimizer_ipc_handle_bf16 (same protocol as vb_optimizer_open_peers).
+ * Gradient-less parameters keep their value and their copy. */
+int vb_optimizer_enable_bf16_params(vb_optimizer *opt);
+int vb_optimizer_refresh_bf16_params(vb_optimizer *opt);
+/* Device address of tensor i's copy (valid until destroy). */
+int vb_optimizer_param_bf16_ptr(vb_optimizer *opt, int64_t tensor, void **out);
+/* Copies tensor i's bf16 words to the host (blocking). */
+int vb_optimizer_download_params_bf16(vb_optimizer *opt, int64_t tensor, uint16_t *host, int64_t n);
+int vb_optimizer_ipc_handle_bf16(vb_optimizer *opt, void *handle64);
+int vb_optimizer_open_peers_bf16(vb_optimizer *opt, const void *handles, int n_handles);
 
 /* ---- optimizer state (private in the reference, src/nn/optim/adam.rs:5-14) -------- */
 

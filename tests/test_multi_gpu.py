@@ -116,3 +116,117 @@ def test_two_gpu_sharded_step_matches_oracle(oracle, kind):
             assert np.array_equal(a.view(np.uint32), r.view(np.uint32))
     # state is partitioned: the ranks' owned element counts add up to the whole
     assert res["owned0"] + res["owned1"] == wl.total and min(res["owned0"], res["owned1"]) > 0
+
+
+def _bf16_rne(x):
+    u = np.ascontiguousarray(x, np.float32).view(np.uint32).astype(np.uint64)
+    return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+
+
+def _small_workload(kind):
+    import workloads
+    if kind == "adam":
+        return workloads.c5_ragged_adam(n_tensors=96, max_log2=16, seed=11)
+    if kind == "sgd":
+        return workloads.c2_cnn_sgd()
+    shapes = [(256, 128), (128, 384), (64, 36), (100,), (512, 256), (256, 256), (3, 3)]
+    return workloads.Workload("muon_small", "muon", shapes, [("normal", 0.02)] * len(shapes), 1e-3,
+                              dict(lr=0.1, momentum=0.9, nesterov=True, ns_steps=5), 3)
+
+
+def _worker_bf16(rank, world, shared, kind, transport, what):
+    """`what` = "half": step(VB_STEP_EXCHANGE_BF16), only the bf16 copies cross; "both": default step with
+    the copies enabled.  `transport` = "nccl" or "peer" (stores fused into the kernel)."""
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import time
+
+    from volta_b200 import SGD, VB_NS_F32, VB_STEP_EXCHANGE_BF16, Adam, Engine, Muon, Tensor
+    eng = Engine(rank)
+    if rank == 0:
+        shared["id"] = Engine.unique_id()
+    while "id" not in shared:
+        time.sleep(0.01)
+    eng.init_comm(shared["id"], rank, world)
+    wl = _small_workload(kind)
+    h = wl.hyper
+    tensors = [Tensor(p, p.shape) for p in wl.make_params()]
+    if kind == "adam":
+        opt = Adam(tensors, h["lr"], h["betas"], h["eps"], h["weight_decay"], engine=eng)
+    elif kind == "sgd":
+        opt = SGD(tensors, h["lr"], h["momentum"], h["weight_decay"], engine=eng)
+    else:
+        opt = Muon(tensors, h["lr"], h["momentum"], h["nesterov"], h["ns_steps"], ns_mode=VB_NS_F32, engine=eng)
+    opt.enable_bf16_params()
+
+    def gather(key, value):
+        shared[f"{key}{rank}"] = value
+        while any(f"{key}{r}" not in shared for r in range(world)):
+            time.sleep(0.01)
+        return [shared[f"{key}{r}"] for r in range(world)]
+
+    if transport == "peer":
+        opt.open_peers_bf16(gather("ipch", opt.ipc_handle_bf16()))
+        if what == "both":
+            opt.open_peers(gather("ipc", opt.ipc_handle()))
+    for s in (1, 2, 3):
+        opt.zero_grad()
+        for t, g in zip(tensors, wl.make_grads(s)):
+            t.grad = g
+        opt.step(VB_STEP_EXCHANGE_BF16 if what == "half" else 0)
+    shared[f"params{rank}"] = [t.data.copy() for t in tensors]
+    shared[f"half{rank}"] = [opt.bf16_params(i) for i in range(len(tensors))]
+    shared[f"owned{rank}"] = [opt.state_owned_range(i, 0) for i in range(len(tensors))]
+    opt.close()
+    eng.close()
+
+
+@pytest.mark.parametrize("kind,transport,what", [
+    ("adam", "nccl", "half"), ("adam", "peer", "half"), ("adam", "peer", "both"), ("adam", "nccl", "both"),
+    ("sgd", "peer", "half"), ("muon_f32", "nccl", "half"), ("muon_f32", "peer", "half"), ("muon_f32", "peer", "both")])
+def test_two_gpu_bf16_copies_exchange(oracle, kind, transport, what):
+    """bf16 copies of the parameters written by the update / apply kernel: every rank ends with
+    rne(theta) for ALL parameters; with the bf16-only exchange the f32 values are exact on the
+    part a rank owns (the rest keeps its old value), with the default step everywhere."""
+    if _gpu_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    with ctx.Manager() as mgr:
+        shared = mgr.dict()
+        procs = [ctx.Process(target=_worker_bf16, args=(r, 2, shared, kind, transport, what)) for r in range(2)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(300)
+            assert p.exitcode == 0
+        res = dict(shared)
+    wl = _small_workload(kind)
+    h = wl.hyper
+    ref = wl.make_params()
+    start = [p.copy() for p in ref]
+    if kind == "adam":
+        o = oracle.Adam(ref, h["lr"], h["betas"], h["eps"], h["weight_decay"])
+    elif kind == "sgd":
+        o = oracle.SGD(ref, h["lr"], h["momentum"], h["weight_decay"])
+    else:
+        o = oracle.Muon(ref, h["lr"], h["momentum"], h["nesterov"], h["ns_steps"])
+    for s in (1, 2, 3):
+        o.step(wl.make_grads(s))
+    owned_total = 0
+    for rank in (0, 1):
+        for i, r in enumerate(ref):
+            want = _bf16_rne(r).reshape(r.shape)
+            assert np.array_equal(res[f"half{rank}"][i], want), (rank, i)
+            got = res[f"params{rank}"][i].reshape(-1).view(np.uint32)
+            exact = r.reshape(-1).view(np.uint32)
+            if what == "both":
+                assert np.array_equal(got, exact)
+            else:
+                lo, hi = res[f"owned{rank}"][i]
+                owned_total += hi - lo
+                assert np.array_equal(got[lo:hi], exact[lo:hi])
+                stale = start[i].reshape(-1).view(np.uint32)
+                assert np.array_equal(got[:lo], stale[:lo]) and np.array_equal(got[hi:], stale[hi:])
+    if what == "half":
+        assert owned_total == wl.total

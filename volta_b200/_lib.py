@@ -21,6 +21,7 @@ VB_NS_BF16 = 1
 VB_NS_F32_TC = 2
 VB_STEP_DEFAULT = 0
 VB_STEP_NO_EXCHANGE = 1
+VB_STEP_EXCHANGE_BF16 = 2
 
 
 class VoltaB200Error(RuntimeError):
@@ -96,6 +97,12 @@ SIGNATURES = {
     "vb_optimizer_import_state": [_vp, _i64, C.c_int, _vp, _i64],
     "vb_optimizer_ipc_handle": [_vp, _vp],
     "vb_optimizer_open_peers": [_vp, _vp, C.c_int],
+    "vb_optimizer_enable_bf16_params": [_vp],
+    "vb_optimizer_refresh_bf16_params": [_vp],
+    "vb_optimizer_param_bf16_ptr": [_vp, C.c_int64, C.POINTER(C.c_void_p)],
+    "vb_optimizer_download_params_bf16": [_vp, C.c_int64, _vp, C.c_int64],
+    "vb_optimizer_ipc_handle_bf16": [_vp, _vp],
+    "vb_optimizer_open_peers_bf16": [_vp, _vp, C.c_int],
     "vb_optimizer_get_t": [_vp, _i64p],
     "vb_optimizer_set_t": [_vp, _i64],
     "vb_muon_download_update": [_vp, _i64, _vp, _i64],

@@ -234,6 +234,7 @@ static void free_optimizer(vb_optimizer *opt)
     if (opt->muon) destroy_muon_state(opt->muon);
     for (void *m : opt->peer_mappings) cudaIpcCloseMemHandle(m);
     cudaFree(opt->d_param);
+    cudaFree(opt->d_param_bf16);
     cudaFree(opt->d_grad);
     cudaFree(opt->d_s1);
     cudaFree(opt->d_s2);
@@ -272,6 +273,45 @@ using namespace vb;
     catch (const std::bad_alloc &) { return fail(VB_ERR_STATE, "out of host memory"); } \
     catch (const std::exception &ex) { return fail(VB_ERR_STATE, "exception: %s", ex.what()); } \
     catch (...) { return fail(VB_ERR_STATE, "unknown exception"); }
+
+namespace vb {
+
+int plan_exchange(vb_optimizer *opt, uint32_t flags, ExchangePlan *plan)
+{
+    vb_engine *e = opt->eng;
+    if (flags & ~(VB_STEP_NO_EXCHANGE | VB_STEP_EXCHANGE_BF16)) return fail(VB_ERR_INVALID_ARG, "unknown step flags 0x%x", flags);
+    const bool half = opt->d_param_bf16 != nullptr;
+    const bool half_only = (flags & VB_STEP_EXCHANGE_BF16) != 0;
+    if (half_only && !half)
+        return fail(VB_ERR_STATE, "VB_STEP_EXCHANGE_BF16 needs vb_optimizer_enable_bf16_params first");
+    ExchangePlan xp;
+    xp.pt.local_base = opt->d_param;
+    xp.pt.half_local = opt->d_param_bf16;
+    const bool exchange = e->world > 1 && !(flags & VB_STEP_NO_EXCHANGE);
+    if (exchange) {
+        if (!half_only) {
+            if (opt->peers.n > 0) {
+                xp.pt.n = opt->peers.n;
+                for (int r = 0; r < opt->peers.n; ++r) xp.pt.base[r] = opt->peers.base[r];
+            } else {
+                xp.nccl_f32 = true;
+            }
+        }
+        if (half) {
+            if (opt->peers.n_half > 0) {
+                xp.pt.n_half = opt->peers.n_half;
+                for (int r = 0; r < opt->peers.n_half; ++r) xp.pt.half_base[r] = opt->peers.half_base[r];
+            } else {
+                xp.nccl_half = true;
+            }
+        }
+        xp.fused = xp.pt.n > 0 || xp.pt.n_half > 0;
+    }
+    *plan = xp;
+    return VB_OK;
+}
+
+}  // namespace vb
 
 extern "C" {
 
@@ -608,6 +648,15 @@ int vb_optimizer_total_size(vb_optimizer *opt, int64_t *n)
     return VB_OK;
 }
 
+// Keeps the bf16 copy (if enabled) equal to the rounded f32 parameters after they were
+// written by an upload: arena elements [begin, begin + n).
+static int refresh_bf16(vb_optimizer *opt, int64_t begin, int64_t n)
+{
+    if (!opt->d_param_bf16 || n <= 0) return VB_OK;
+    return launch_f32_to_bf16(opt->d_param_bf16 + begin, opt->d_param + begin, n, opt->eng->sm_count,
+                              opt->eng->stream);
+}
+
 static int copy_tensor(vb_optimizer *opt, int64_t tensor, float *dev_base, void *host, int64_t n,
                        bool to_device)
 {
@@ -619,6 +668,7 @@ static int copy_tensor(vb_optimizer *opt, int64_t tensor, float *dev_base, void 
     if (to_device) {
         VB_CUDA(cudaMemcpyAsync(dev, host, (size_t)n * sizeof(float), cudaMemcpyHostToDevice,
                                 opt->eng->stream));
+        if (dev_base == opt->d_param) VB_TRY(refresh_bf16(opt, opt->offsets[tensor], n));
     } else {
         VB_CUDA(cudaMemcpyAsync(host, dev, (size_t)n * sizeof(float), cudaMemcpyDeviceToHost,
                                 opt->eng->stream));
@@ -745,6 +795,7 @@ int vb_optimizer_upload_arena(vb_optimizer *opt, int which, const float *host, i
     VB_CUDA(cudaMemcpyAsync(which == 0 ? opt->d_param : opt->d_grad, host, (size_t)n * sizeof(float),
                             cudaMemcpyHostToDevice, opt->eng->stream));
     if (which == 1) std::fill(opt->present.begin(), opt->present.end(), (uint8_t)1);
+    else VB_TRY(refresh_bf16(opt, 0, n));
     return VB_OK;
 }
 
@@ -777,6 +828,7 @@ static int arena_range_copy(vb_optimizer *opt, int which, void *host, int64_t be
     if (to_device) {
         VB_CUDA(cudaMemcpyAsync(dev, host, (size_t)n * sizeof(float), cudaMemcpyHostToDevice, opt->eng->stream));
         if (which == 1) std::fill(opt->present.begin(), opt->present.end(), (uint8_t)1);
+        else VB_TRY(refresh_bf16(opt, begin, n));
     } else {
         VB_CUDA(cudaMemcpyAsync(host, dev, (size_t)n * sizeof(float), cudaMemcpyDeviceToHost, opt->eng->stream));
         VB_CUDA(cudaStreamSynchronize(opt->eng->stream));
@@ -842,35 +894,37 @@ int vb_optimizer_step_ex(vb_optimizer *opt, uint32_t flags)
         s = make_scalars(op, opt->lr, opt->momentum, 0.0f, 0.0f, opt->weight_decay, 0);
     }
     VB_TRY(sync_present(opt));
+    ExchangePlan xp;
+    VB_TRY(plan_exchange(opt, flags, &xp));
+    // With peer arenas mapped, the exchange is fused into the update: the kernel stores
+    // every new parameter locally and into each peer's arena.  Two stream-ordered barriers
+    // fence it: no rank is written to before it has reached its step (its earlier readers
+    // of the parameters are done), and no rank continues before all writes have landed.
+    // Every rank takes part in them, also one whose slice holds no tensor element.
+    if (xp.fused) {
+        prof_begin(e, VB_PHASE_EXCHANGE);
+        VB_TRY(comm_barrier(e));
+        prof_end(e, VB_PHASE_EXCHANGE);
+    }
     if (opt->n_chunks > 0) {
         bool all_present = true;
         for (int64_t i = 0; i < opt->n_tensors && all_present; ++i) all_present = opt->present[(size_t)i] != 0;
-        // With peer arenas mapped, the exchange is fused into the update: the kernel stores
-        // every new parameter locally and into each peer's arena.  Two stream-ordered barriers
-        // fence it: no rank is written to before it has reached its step (its earlier readers
-        // of the parameters are done), and no rank continues before all writes have landed.
-        const bool exchange = e->world > 1 && !(flags & VB_STEP_NO_EXCHANGE);
-        const bool fused = exchange && opt->peers.n > 0;
-        if (fused) {
-            prof_begin(e, VB_PHASE_EXCHANGE);
-            VB_TRY(comm_barrier(e));
-            prof_end(e, VB_PHASE_EXCHANGE);
-        }
         prof_begin(e, VB_PHASE_UPDATE);
         VB_TRY(launch_multi_tensor(op, opt->d_chunks, opt->n_chunks, opt->d_present, all_present, s,
-                                   e->sm_count, e->stream, fused ? &opt->peers : nullptr));
+                                   e->sm_count, e->stream, &xp.pt));
         prof_end(e, VB_PHASE_UPDATE);
         e->launches += 1;
-        if (fused) {
-            prof_begin(e, VB_PHASE_EXCHANGE);
-            VB_TRY(comm_barrier(e));
-            prof_end(e, VB_PHASE_EXCHANGE);
-            return VB_OK;
-        }
     }
-    if (e->world > 1 && !(flags & VB_STEP_NO_EXCHANGE)) {
+    if (xp.fused) {
         prof_begin(e, VB_PHASE_EXCHANGE);
-        VB_TRY(comm_all_gather_inplace(e, opt->d_param, opt->arena / e->world));
+        VB_TRY(comm_barrier(e));
+        prof_end(e, VB_PHASE_EXCHANGE);
+    }
+    if (xp.nccl_f32 || xp.nccl_half) {
+        prof_begin(e, VB_PHASE_EXCHANGE);
+        if (xp.nccl_f32) VB_TRY(comm_all_gather_inplace(e, opt->d_param, opt->arena / e->world));
+        if (xp.nccl_half)
+            VB_TRY(comm_all_gather_inplace_bytes(e, opt->d_param_bf16, opt->arena / e->world * (int64_t)sizeof(uint16_t)));
         prof_end(e, VB_PHASE_EXCHANGE);
     }
     return VB_OK;
@@ -909,8 +963,9 @@ int vb_optimizer_step_host(vb_optimizer *opt, const float *grads_host, float *pa
     std::fill(opt->present.begin(), opt->present.end(), (uint8_t)1);  // a whole gradient arena arrives
     opt->present_on_dev = opt->present;
     VB_CUDA(cudaMemsetAsync(opt->d_present, 1, opt->present.size(), e->stream));
-    const bool fused = e->world > 1 && opt->peers.n > 0;
-    if (fused) VB_TRY(comm_barrier(e));
+    ExchangePlan xp;
+    VB_TRY(plan_exchange(opt, VB_STEP_DEFAULT, &xp));
+    if (xp.fused) VB_TRY(comm_barrier(e));
     // everything enqueued so far (earlier steps, uploads) precedes the first copy of this step
     cudaEvent_t ev_start = e->pipe_events[2 * pieces];
     VB_CUDA(cudaEventRecord(ev_start, e->stream));
@@ -928,16 +983,16 @@ int vb_optimizer_step_host(vb_optimizer *opt, const float *grads_host, float *pa
         VB_CUDA(cudaEventRecord(e->pipe_events[2 * j], e->h2d_stream));
         VB_CUDA(cudaStreamWaitEvent(e->stream, e->pipe_events[2 * j], 0));
         VB_TRY(launch_multi_tensor(op, opt->d_chunks + c_lo, c_hi - c_lo, opt->d_present, /*all_present=*/true, s,
-                                   e->sm_count, e->stream, fused ? &opt->peers : nullptr));
+                                   e->sm_count, e->stream, &xp.pt));
         e->launches += 1;
         VB_CUDA(cudaEventRecord(e->pipe_events[2 * j + 1], e->stream));
         VB_CUDA(cudaStreamWaitEvent(e->d2h_stream, e->pipe_events[2 * j + 1], 0));
         VB_CUDA(cudaMemcpyAsync(params_host + a_lo, opt->d_param + a_lo, bytes, cudaMemcpyDeviceToHost, e->d2h_stream));
     }
-    if (e->world > 1) {
-        if (fused) VB_TRY(comm_barrier(e));
-        else VB_TRY(comm_all_gather_inplace(e, opt->d_param, opt->arena / e->world));
-    }
+    if (xp.fused) VB_TRY(comm_barrier(e));
+    if (xp.nccl_f32) VB_TRY(comm_all_gather_inplace(e, opt->d_param, opt->arena / e->world));
+    if (xp.nccl_half)
+        VB_TRY(comm_all_gather_inplace_bytes(e, opt->d_param_bf16, opt->arena / e->world * (int64_t)sizeof(uint16_t)));
     VB_CUDA(cudaStreamSynchronize(e->d2h_stream));
     VB_CUDA(cudaStreamSynchronize(e->stream));
     return VB_OK;
@@ -1024,19 +1079,15 @@ int vb_optimizer_ipc_handle(vb_optimizer *opt, void *handle64)
     VB_API_END
 }
 
-int vb_optimizer_open_peers(vb_optimizer *opt, const void *handles, int n_handles)
+static int open_peer_handles(vb_optimizer *opt, const void *handles, int n_handles, void **mapped_out)
 {
-    VB_API_BEGIN
-    VB_TRY(check_opt(opt));
     vb_engine *e = opt->eng;
     if (!handles) return fail(VB_ERR_INVALID_ARG, "handles is null");
     if (n_handles != e->world)
         return fail(VB_ERR_INVALID_ARG, "expected %d handles (one per rank), got %d", e->world, n_handles);
     if (e->world - 1 > kMaxPeers) return fail(VB_ERR_UNSUPPORTED, "at most %d peers", kMaxPeers);
-    if (opt->peers.n > 0) return fail(VB_ERR_STATE, "peers are already open");
     VB_TRY(set_device(e));
-    PeerTable pt{};
-    pt.local_base = opt->d_param;
+    int n = 0;
     for (int r = 0; r < e->world; ++r) {
         if (r == e->rank) continue;
         cudaIpcMemHandle_t h;
@@ -1044,9 +1095,97 @@ int vb_optimizer_open_peers(vb_optimizer *opt, const void *handles, int n_handle
         void *mapped = nullptr;
         VB_CUDA(cudaIpcOpenMemHandle(&mapped, h, cudaIpcMemLazyEnablePeerAccess));
         opt->peer_mappings.push_back(mapped);
-        pt.base[pt.n++] = (float *)mapped;
+        mapped_out[n++] = mapped;
     }
-    opt->peers = pt;
+    return VB_OK;
+}
+
+int vb_optimizer_enable_bf16_params(vb_optimizer *opt)
+{
+    VB_API_BEGIN
+    VB_TRY(check_opt(opt));
+    if (opt->d_param_bf16) return VB_OK;
+    VB_TRY(set_device(opt->eng));
+    uint16_t *buf = nullptr;
+    VB_CUDA(cudaMalloc((void **)&buf, (size_t)std::max<int64_t>(opt->arena, 1) * sizeof(uint16_t)));
+    opt->d_param_bf16 = buf;
+    return refresh_bf16(opt, 0, opt->arena);
+    VB_API_END
+}
+
+int vb_optimizer_refresh_bf16_params(vb_optimizer *opt)
+{
+    VB_API_BEGIN
+    VB_TRY(check_opt(opt));
+    if (!opt->d_param_bf16) return fail(VB_ERR_STATE, "the bf16 copy is not enabled");
+    VB_TRY(set_device(opt->eng));
+    return refresh_bf16(opt, 0, opt->arena);
+    VB_API_END
+}
+
+int vb_optimizer_param_bf16_ptr(vb_optimizer *opt, int64_t tensor, void **out)
+{
+    VB_TRY(check_tensor(opt, tensor, 0, false));
+    if (!out) return fail(VB_ERR_INVALID_ARG, "out is null");
+    if (!opt->d_param_bf16) return fail(VB_ERR_STATE, "the bf16 copy is not enabled");
+    *out = opt->d_param_bf16 + opt->offsets[tensor];
+    return VB_OK;
+}
+
+int vb_optimizer_download_params_bf16(vb_optimizer *opt, int64_t tensor, uint16_t *host, int64_t n)
+{
+    VB_API_BEGIN
+    VB_TRY(check_tensor(opt, tensor, n, true));
+    if (!opt->d_param_bf16) return fail(VB_ERR_STATE, "the bf16 copy is not enabled");
+    if (n == 0) return VB_OK;
+    if (!host) return fail(VB_ERR_INVALID_ARG, "host pointer is null");
+    VB_TRY(set_device(opt->eng));
+    VB_CUDA(cudaMemcpyAsync(host, opt->d_param_bf16 + opt->offsets[tensor], (size_t)n * sizeof(uint16_t),
+                            cudaMemcpyDeviceToHost, opt->eng->stream));
+    VB_CUDA(cudaStreamSynchronize(opt->eng->stream));
+    if (opt->kind == KIND_MUON) return muon_check_error(opt);
+    return VB_OK;
+    VB_API_END
+}
+
+int vb_optimizer_ipc_handle_bf16(vb_optimizer *opt, void *handle64)
+{
+    VB_API_BEGIN
+    VB_TRY(check_opt(opt));
+    if (!handle64) return fail(VB_ERR_INVALID_ARG, "handle64 is null");
+    if (!opt->d_param_bf16) return fail(VB_ERR_STATE, "the bf16 copy is not enabled");
+    VB_TRY(set_device(opt->eng));
+    cudaIpcMemHandle_t h;
+    VB_CUDA(cudaIpcGetMemHandle(&h, opt->d_param_bf16));
+    memcpy(handle64, &h, sizeof(h));
+    return VB_OK;
+    VB_API_END
+}
+
+int vb_optimizer_open_peers_bf16(vb_optimizer *opt, const void *handles, int n_handles)
+{
+    VB_API_BEGIN
+    VB_TRY(check_opt(opt));
+    if (!opt->d_param_bf16) return fail(VB_ERR_STATE, "the bf16 copy is not enabled");
+    if (opt->peers.n_half > 0) return fail(VB_ERR_STATE, "bf16 peers are already open");
+    void *mapped[kMaxPeers] = {};
+    VB_TRY(open_peer_handles(opt, handles, n_handles, mapped));
+    for (int r = 0; r < opt->eng->world - 1; ++r) opt->peers.half_base[r] = (uint16_t *)mapped[r];
+    opt->peers.n_half = opt->eng->world - 1;
+    return VB_OK;
+    VB_API_END
+}
+
+int vb_optimizer_open_peers(vb_optimizer *opt, const void *handles, int n_handles)
+{
+    VB_API_BEGIN
+    VB_TRY(check_opt(opt));
+    if (opt->peers.n > 0) return fail(VB_ERR_STATE, "peers are already open");
+    void *mapped[kMaxPeers] = {};
+    VB_TRY(open_peer_handles(opt, handles, n_handles, mapped));
+    for (int r = 0; r < opt->eng->world - 1; ++r) opt->peers.base[r] = (float *)mapped[r];
+    opt->peers.local_base = opt->d_param;
+    opt->peers.n = opt->eng->world - 1;
     return VB_OK;
     VB_API_END
 }

@@ -19,6 +19,7 @@ typedef struct {
 typedef int ncclResult_t;   // ncclSuccess == 0
 typedef int ncclDataType_t; // ncclFloat32 == 7
 constexpr ncclDataType_t kNcclFloat = 7;
+constexpr ncclDataType_t kNcclUint8 = 1;
 
 struct NcclApi {
     void *handle = nullptr;
@@ -130,6 +131,15 @@ int comm_all_gather_inplace(vb_engine *eng, float *base, int64_t count)
     return VB_OK;
 }
 
+// The same for a buffer addressed in bytes (the bf16 copies of the parameters).
+int comm_all_gather_inplace_bytes(vb_engine *eng, void *base, int64_t bytes)
+{
+    if (!eng->comm) return fail(VB_ERR_STATE, "engine has no communicator");
+    VB_NCCL(g_api.AllGather((char *)base + (int64_t)eng->rank * bytes, base, (size_t)bytes, kNcclUint8,
+                            eng->comm->comm, eng->stream));
+    return VB_OK;
+}
+
 // A one-float all-reduce used as a stream-ordered barrier across the ranks: it completes on
 // a rank only after every rank's stream has reached it, i.e. after all work the other ranks
 // enqueued before it (their update kernels and the peer stores in them) has finished.
@@ -152,8 +162,9 @@ int comm_group_broadcast(vb_engine *eng, const BcastItem *items, int64_t n_items
     if (n_items == 0) return VB_OK;
     VB_NCCL(g_api.GroupStart());
     for (int64_t i = 0; i < n_items; ++i) {
-        ncclResult_t r = g_api.Broadcast(items[i].ptr, items[i].ptr, (size_t)items[i].count, kNcclFloat,
-                                         items[i].root, eng->comm->comm, eng->stream);
+        ncclResult_t r = g_api.Broadcast(items[i].ptr, items[i].ptr, (size_t)items[i].count,
+                                         items[i].elem_bytes == 4 ? kNcclFloat : kNcclUint8, items[i].root,
+                                         eng->comm->comm, eng->stream);
         if (r != 0) {
             g_api.GroupEnd();
             return fail(VB_ERR_NCCL, "ncclBroadcast failed: %s (%d)", g_api.GetErrorString(r), r);

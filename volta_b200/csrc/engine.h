@@ -73,7 +73,11 @@ struct vb_optimizer {
 
     vb::MuonState *muon = nullptr;
 
-    // peer GPUs' parameter arenas opened through CUDA IPC (vb_optimizer_open_peers)
+    // bf16 copy of the parameter arena (vb_optimizer_enable_bf16_params), one word per element
+    uint16_t *d_param_bf16 = nullptr;
+
+    // peer GPUs' parameter arenas (f32, and bf16 copies) opened through CUDA IPC
+    // (vb_optimizer_open_peers / vb_optimizer_open_peers_bf16)
     vb::PeerTable peers{};
     std::vector<void *> peer_mappings;  // what cudaIpcOpenMemHandle returned, to close on destroy
 };
@@ -100,13 +104,26 @@ int comm_unique_id(void *id128);
 int comm_init(vb_engine *eng, const void *id128, int rank, int world);
 void comm_destroy(vb_engine *eng);
 int comm_all_gather_inplace(vb_engine *eng, float *base, int64_t elems_per_rank);
+int comm_all_gather_inplace_bytes(vb_engine *eng, void *base, int64_t bytes_per_rank);
 int comm_barrier(vb_engine *eng);  // stream-ordered: completes once every rank's stream has reached it
 struct BcastItem {
-    float *ptr;
-    int64_t count;
+    void *ptr;
+    int64_t count;  // elements of `elem_bytes` bytes (4: f32, 1: raw bytes)
     int root;
+    int elem_bytes;
 };
 int comm_group_broadcast(vb_engine *eng, const BcastItem *items, int64_t n_items);
+
+// What one step writes besides the local f32 parameters, from the step flags, the bf16 copy
+// and the peers that are open: the table handed to the update / apply kernel, whether the
+// two stream-ordered barriers are needed around it, and which copies NCCL still has to move.
+struct ExchangePlan {
+    PeerTable pt{};
+    bool fused = false;      // the kernel stores into peers: fence it with barriers
+    bool nccl_f32 = false;   // f32 parameters go by all-gather / broadcast after the kernel
+    bool nccl_half = false;  // bf16 copies go by all-gather / broadcast after the kernel
+};
+int plan_exchange(vb_optimizer *opt, uint32_t flags, ExchangePlan *plan);
 
 inline int sync_present(vb_optimizer *opt)
 {

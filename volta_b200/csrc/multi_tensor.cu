@@ -11,6 +11,7 @@
 // a*b+c, so every operation below is an explicitly rounded intrinsic (__fmul_rn,
 // __fadd_rn, ... are never fused by nvcc) and __fmaf_rn appears only where the
 // reference writes mul_add.  Division and square root are the IEEE-rounded forms.
+#include <cuda_bf16.h>
 #include <stdlib.h>
 
 #include "vb_internal.h"
@@ -102,10 +103,27 @@ __device__ __forceinline__ FatChunk load_chunk(const FatChunk *c)
     return u.f;
 }
 
+// f32 -> bf16, round to nearest even (the conversion Volta's storage uses for its bf16
+// dtype, src/storage.rs:499-505), two per 32-bit word, low element in the low half.
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi)
+{
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t *>(&v);
+}
+
+__device__ __forceinline__ uint16_t bf16_bits(float x)
+{
+    const __nv_bfloat16 v = __float2bfloat16_rn(x);
+    return *reinterpret_cast<const uint16_t *>(&v);
+}
+
 // PEERS: besides the local arena, every updated parameter is stored into the same arena
 // position on every peer GPU (plain st.global to peer-mapped memory over NVLink), so the
 // all-gather of updated parameters rides along with the update, piece by piece.
-template <int OP, bool PEERS>
+// HALF: 1 = the new parameter is also written, rounded to bf16, into the local bf16 copy of the
+// arena; 2 = and into every peer's bf16 copy (2 bytes per parameter over NVLink instead of 4
+// when PEERS is off).
+template <int OP, bool PEERS, int HALF>
 __device__ __forceinline__ void update_chunk(const FatChunk &ch, const StepScalars &s, const PeerTable &pt)
 {
     constexpr bool kHasS1 = (OP != OP_SGD);
@@ -116,7 +134,7 @@ __device__ __forceinline__ void update_chunk(const FatChunk &ch, const StepScala
     float *__restrict__ s2 = kHasS2 ? ch.s2 : nullptr;
     const uint32_t n = ch.len;
 
-    const ptrdiff_t arena_pos = PEERS ? (p - pt.local_base) : 0;  // element offset inside the arena
+    const ptrdiff_t arena_pos = (PEERS || HALF) ? (p - pt.local_base) : 0;  // element offset inside the arena
 
     uintptr_t align_bits = reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g);
     if (kHasS1) align_bits |= reinterpret_cast<uintptr_t>(s1);
@@ -142,6 +160,16 @@ __device__ __forceinline__ void update_chunk(const FatChunk &ch, const StepScala
                 for (int r = 0; r < kMaxPeers; ++r)  // unrolled: the table stays in the constant bank
                     if (r < pt.n) st_vec8(reinterpret_cast<Vec8 *>(pt.base[r] + arena_pos) + i, vp);
             }
+            if (HALF) {  // arena_pos is a multiple of 8 here: 16-byte aligned bf16 octets
+                const uint4 h = make_uint4(pack_bf16x2(vp.lo.x, vp.lo.y), pack_bf16x2(vp.lo.z, vp.lo.w),
+                                           pack_bf16x2(vp.hi.x, vp.hi.y), pack_bf16x2(vp.hi.z, vp.hi.w));
+                reinterpret_cast<uint4 *>(pt.half_local + arena_pos)[i] = h;
+                if (HALF == 2) {
+#pragma unroll
+                    for (int r = 0; r < kMaxPeers; ++r)
+                        if (r < pt.n_half) reinterpret_cast<uint4 *>(pt.half_base[r] + arena_pos)[i] = h;
+                }
+            }
             if (kHasS1) st_vec8(a8 + i, va);
             if (kHasS2) st_vec8(b8 + i, vb);
         }
@@ -164,6 +192,15 @@ __device__ __forceinline__ void update_chunk(const FatChunk &ch, const StepScala
                 for (int r = 0; r < kMaxPeers; ++r)
                     if (r < pt.n) reinterpret_cast<float4 *>(pt.base[r] + arena_pos)[i] = vp;
             }
+            if (HALF) {
+                const uint2 h = make_uint2(pack_bf16x2(vp.x, vp.y), pack_bf16x2(vp.z, vp.w));
+                reinterpret_cast<uint2 *>(pt.half_local + arena_pos)[i] = h;
+                if (HALF == 2) {
+#pragma unroll
+                    for (int r = 0; r < kMaxPeers; ++r)
+                        if (r < pt.n_half) reinterpret_cast<uint2 *>(pt.half_base[r] + arena_pos)[i] = h;
+                }
+            }
             if (kHasS1) __stcs(a4 + i, va);
             if (kHasS2) __stcs(b4 + i, vb);
         }
@@ -182,6 +219,15 @@ __device__ __forceinline__ void update_chunk(const FatChunk &ch, const StepScala
             for (int r = 0; r < kMaxPeers; ++r)
                 if (r < pt.n) pt.base[r][arena_pos + i] = vp;
         }
+        if (HALF) {
+            const uint16_t h = bf16_bits(vp);
+            pt.half_local[arena_pos + i] = h;
+            if (HALF == 2) {
+#pragma unroll
+                for (int r = 0; r < kMaxPeers; ++r)
+                    if (r < pt.n_half) pt.half_base[r][arena_pos + i] = h;
+            }
+        }
         if (kHasS1) s1[i] = va;
         if (kHasS2) s2[i] = vb;
     }
@@ -190,7 +236,7 @@ __device__ __forceinline__ void update_chunk(const FatChunk &ch, const StepScala
 // CHECK_PRESENT = false is the common case (every tensor has a gradient): the descriptor of
 // the next chunk is fetched while the current one streams, so no dependent-load latency
 // sits between chunks.  With CHECK_PRESENT the per-tensor flag is looked up as well.
-template <int OP, bool CHECK_PRESENT, bool PEERS>
+template <int OP, bool CHECK_PRESENT, bool PEERS, int HALF>
 __global__ void __launch_bounds__(kThreads, kCtasPerSmMax)
 multi_tensor_update_kernel(const FatChunk *__restrict__ chunks, int64_t n_chunks,
                            const uint8_t *__restrict__ present, const StepScalars s, const PeerTable pt)
@@ -204,7 +250,7 @@ multi_tensor_update_kernel(const FatChunk *__restrict__ chunks, int64_t n_chunks
         FatChunk nxt = cur;
         if (has_next) nxt = load_chunk(chunks + cn);  // in flight while `cur` is processed
         // `grad == None` -> skip: adam.rs:81-84, sgd.rs:75-78
-        if (!CHECK_PRESENT || present[cur.tensor] != 0) update_chunk<OP, PEERS>(cur, s, pt);
+        if (!CHECK_PRESENT || present[cur.tensor] != 0) update_chunk<OP, PEERS, HALF>(cur, s, pt);
         if (!has_next) break;
         cur = nxt;
         c = cn;
@@ -275,26 +321,35 @@ static int ctas_per_sm(int op)
     return op == OP_ADAM ? 2 : op == OP_SGD_MOMENTUM ? kSgdMomentumCtasPerSm : kSgdCtasPerSm;
 }
 
+template <int OP, bool PEERS, int HALF>
+static void launch_variant(unsigned grid, const FatChunk *d_chunks, int64_t n_chunks, const uint8_t *d_present,
+                           bool all_present, const StepScalars &s, const PeerTable &pt, cudaStream_t stream)
+{
+    if (all_present)
+        multi_tensor_update_kernel<OP, false, PEERS, HALF><<<grid, kThreads, 0, stream>>>(d_chunks, n_chunks,
+                                                                                         d_present, s, pt);
+    else
+        multi_tensor_update_kernel<OP, true, PEERS, HALF><<<grid, kThreads, 0, stream>>>(d_chunks, n_chunks,
+                                                                                        d_present, s, pt);
+}
+
 template <int OP>
 static void launch_op(unsigned grid, const FatChunk *d_chunks, int64_t n_chunks, const uint8_t *d_present,
                       bool all_present, const StepScalars &s, const PeerTable *peers, cudaStream_t stream)
 {
-    if (peers && peers->n > 0) {
-        if (all_present)
-            multi_tensor_update_kernel<OP, false, true><<<grid, kThreads, 0, stream>>>(d_chunks, n_chunks, d_present, s,
-                                                                                     *peers);
-        else
-            multi_tensor_update_kernel<OP, true, true><<<grid, kThreads, 0, stream>>>(d_chunks, n_chunks, d_present, s,
-                                                                                    *peers);
-        return;
+    const PeerTable pt = peers ? *peers : PeerTable{};
+    const bool f32_peers = pt.n > 0;
+    const int half = pt.half_local == nullptr ? 0 : pt.n_half > 0 ? 2 : 1;
+    if (half == 0) {
+        if (f32_peers) launch_variant<OP, true, 0>(grid, d_chunks, n_chunks, d_present, all_present, s, pt, stream);
+        else launch_variant<OP, false, 0>(grid, d_chunks, n_chunks, d_present, all_present, s, pt, stream);
+    } else if (half == 1) {
+        if (f32_peers) launch_variant<OP, true, 1>(grid, d_chunks, n_chunks, d_present, all_present, s, pt, stream);
+        else launch_variant<OP, false, 1>(grid, d_chunks, n_chunks, d_present, all_present, s, pt, stream);
+    } else {
+        if (f32_peers) launch_variant<OP, true, 2>(grid, d_chunks, n_chunks, d_present, all_present, s, pt, stream);
+        else launch_variant<OP, false, 2>(grid, d_chunks, n_chunks, d_present, all_present, s, pt, stream);
     }
-    const PeerTable none{};
-    if (all_present)
-        multi_tensor_update_kernel<OP, false, false><<<grid, kThreads, 0, stream>>>(d_chunks, n_chunks, d_present, s,
-                                                                                  none);
-    else
-        multi_tensor_update_kernel<OP, true, false><<<grid, kThreads, 0, stream>>>(d_chunks, n_chunks, d_present, s,
-                                                                                 none);
 }
 
 int launch_multi_tensor(int op, const FatChunk *d_chunks, int64_t n_chunks, const uint8_t *d_present,
@@ -315,6 +370,35 @@ int launch_multi_tensor(int op, const FatChunk *d_chunks, int64_t n_chunks, cons
             break;
         default: launch_op<OP_SGD>((unsigned)grid, d_chunks, n_chunks, d_present, all_present, s, peers, stream); break;
     }
+    VB_CUDA(cudaGetLastError());
+    return VB_OK;
+}
+
+// ---- bf16 copy of a run of parameters (after an upload) ---------------------------------------------
+__global__ void __launch_bounds__(256)
+f32_to_bf16_kernel(uint16_t *__restrict__ dst, const float *__restrict__ src, int64_t n)
+{
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    int64_t done = 0;
+    if ((reinterpret_cast<uintptr_t>(src) & 15u) == 0 && (reinterpret_cast<uintptr_t>(dst) & 7u) == 0) {
+        const int64_t n4 = n >> 2;
+        for (int64_t i = tid; i < n4; i += stride) {
+            const float4 v = __ldcs(reinterpret_cast<const float4 *>(src) + i);
+            reinterpret_cast<uint2 *>(dst)[i] = make_uint2(pack_bf16x2(v.x, v.y), pack_bf16x2(v.z, v.w));
+        }
+        done = n4 << 2;
+    }
+    for (int64_t i = done + tid; i < n; i += stride) dst[i] = bf16_bits(src[i]);
+}
+
+int launch_f32_to_bf16(uint16_t *dst, const float *src, int64_t n, int sm_count, cudaStream_t stream)
+{
+    if (n <= 0) return VB_OK;
+    int64_t grid = (n / 4 + 255) / 256;
+    if (grid > (int64_t)sm_count * 8) grid = (int64_t)sm_count * 8;
+    if (grid < 1) grid = 1;
+    f32_to_bf16_kernel<<<(unsigned)grid, 256, 0, stream>>>(dst, src, n);
     VB_CUDA(cudaGetLastError());
     return VB_OK;
 }

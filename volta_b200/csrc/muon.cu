@@ -402,7 +402,7 @@ normalise_kernel(const TensorDesc *__restrict__ tensors, const ChunkDesc *__rest
 // ---- K6: apply -----------------------------------------------------------------------------------
 // w -= lr * u * 0.1 (muon.rs:158-160; Rust evaluates (lr * u) * 0.1).  TensorDesc.g here points
 // at the buffer that holds the final update of the tensor.
-template <bool PEERS>
+template <bool PEERS, int HALF>
 __global__ void __launch_bounds__(kEwThreads)
 apply_kernel(const TensorDesc *__restrict__ tensors, const ChunkDesc *__restrict__ chunks, int64_t n_chunks,
              const uint8_t *__restrict__ present, float lr, const PeerTable pt)
@@ -412,7 +412,7 @@ apply_kernel(const TensorDesc *__restrict__ tensors, const ChunkDesc *__restrict
         if (present[ch.tensor] == 0) continue;
         float *__restrict__ w = tensors[ch.tensor].p + ch.offset;
         const float *__restrict__ u = tensors[ch.tensor].g + ch.offset;
-        const ptrdiff_t arena_pos = PEERS ? (w - pt.local_base) : 0;
+        const ptrdiff_t arena_pos = (PEERS || HALF) ? (w - pt.local_base) : 0;
         const uint32_t n = ch.len;
         const uint32_t n4 = n >> 2;
         for (uint32_t i = threadIdx.x; i < n4; i += kEwThreads) {
@@ -428,6 +428,17 @@ apply_kernel(const TensorDesc *__restrict__ tensors, const ChunkDesc *__restrict
                 for (int r = 0; r < kMaxPeers; ++r)
                     if (r < pt.n) reinterpret_cast<float4 *>(pt.base[r] + arena_pos)[i] = wv;
             }
+            if (HALF) {  // bf16 copy of the new weights: local, and (HALF == 2) on every peer
+                const __nv_bfloat162 lo = __floats2bfloat162_rn(wv.x, wv.y), hi = __floats2bfloat162_rn(wv.z, wv.w);
+                const uint2 h = make_uint2(*reinterpret_cast<const uint32_t *>(&lo),
+                                           *reinterpret_cast<const uint32_t *>(&hi));
+                reinterpret_cast<uint2 *>(pt.half_local + arena_pos)[i] = h;
+                if (HALF == 2) {
+#pragma unroll
+                    for (int r = 0; r < kMaxPeers; ++r)
+                        if (r < pt.n_half) reinterpret_cast<uint2 *>(pt.half_base[r] + arena_pos)[i] = h;
+                }
+            }
         }
         for (uint32_t i = (n4 << 2) + threadIdx.x; i < n; i += kEwThreads) {
             const float wv = __fsub_rn(w[i], __fmul_rn(__fmul_rn(lr, u[i]), 0.1f));
@@ -436,6 +447,16 @@ apply_kernel(const TensorDesc *__restrict__ tensors, const ChunkDesc *__restrict
 #pragma unroll
                 for (int r = 0; r < kMaxPeers; ++r)
                     if (r < pt.n) pt.base[r][arena_pos + i] = wv;
+            }
+            if (HALF) {
+                const __nv_bfloat16 hb = __float2bfloat16_rn(wv);
+                const uint16_t h = *reinterpret_cast<const uint16_t *>(&hb);
+                pt.half_local[arena_pos + i] = h;
+                if (HALF == 2) {
+#pragma unroll
+                    for (int r = 0; r < kMaxPeers; ++r)
+                        if (r < pt.n_half) pt.half_base[r][arena_pos + i] = h;
+                }
             }
         }
     }
@@ -896,38 +917,49 @@ int muon_step(vb_optimizer *opt, uint32_t flags)
             VB_CUDA(cudaMemcpyAsync(s->h_error, s->d_error, sizeof(int), cudaMemcpyDeviceToHost, e->stream));
     }
     prof_end(e, VB_PHASE_MUON_PRE);  // no-op if already closed (no Newton-Schulz matrices)
-    const bool exchange = e->world > 1 && !(flags & VB_STEP_NO_EXCHANGE);
-    const bool fused = exchange && opt->peers.n > 0;
-    if (fused) {  // see vb_optimizer_step_ex: nobody is written to before it has reached its step
+    ExchangePlan xp;
+    VB_TRY(plan_exchange(opt, flags, &xp));
+    if (xp.fused) {  // see vb_optimizer_step_ex: nobody is written to before it has reached its step
         prof_begin(e, VB_PHASE_EXCHANGE);
         VB_TRY(comm_barrier(e));
         prof_end(e, VB_PHASE_EXCHANGE);
     }
     if (s->n_chunks > 0) {
         prof_begin(e, VB_PHASE_MUON_APPLY);
-        if (fused)
-            apply_kernel<true><<<ew_grid, kEwThreads, 0, e->stream>>>(s->d_desc_apply, s->d_chunks, s->n_chunks,
-                                                                     opt->d_present, opt->lr, opt->peers);
-        else
-            apply_kernel<false><<<ew_grid, kEwThreads, 0, e->stream>>>(s->d_desc_apply, s->d_chunks, s->n_chunks,
-                                                                      opt->d_present, opt->lr, PeerTable{});
+        const bool f32_peers = xp.pt.n > 0;
+        const int half = xp.pt.half_local == nullptr ? 0 : xp.pt.n_half > 0 ? 2 : 1;
+#define VB_APPLY(P, H)                                                                                      \
+    apply_kernel<P, H><<<ew_grid, kEwThreads, 0, e->stream>>>(s->d_desc_apply, s->d_chunks, s->n_chunks, \
+                                                             opt->d_present, opt->lr, xp.pt)
+        if (half == 0) {
+            if (f32_peers) VB_APPLY(true, 0); else VB_APPLY(false, 0);
+        } else if (half == 1) {
+            if (f32_peers) VB_APPLY(true, 1); else VB_APPLY(false, 1);
+        } else {
+            if (f32_peers) VB_APPLY(true, 2); else VB_APPLY(false, 2);
+        }
+#undef VB_APPLY
         VB_CUDA(cudaGetLastError());
         prof_end(e, VB_PHASE_MUON_APPLY);
         e->launches += 1;
     }
-    if (fused) {
+    if (xp.fused) {
         prof_begin(e, VB_PHASE_EXCHANGE);
         VB_TRY(comm_barrier(e));
         prof_end(e, VB_PHASE_EXCHANGE);
-        return VB_OK;
     }
-    if (exchange) {
+    if (xp.nccl_f32 || xp.nccl_half) {
         // every matrix from its owner; all ranks must hold the same gradient-presence flags
         std::vector<BcastItem> items;
-        for (int64_t i = 0; i < opt->n_tensors; ++i)
-            if (opt->present[(size_t)i] && opt->sizes[(size_t)i] > 0)
+        for (int64_t i = 0; i < opt->n_tensors; ++i) {
+            if (!opt->present[(size_t)i] || opt->sizes[(size_t)i] == 0) continue;
+            if (xp.nccl_f32)
                 items.push_back(BcastItem{opt->d_param + opt->offsets[(size_t)i], opt->sizes[(size_t)i],
-                                          s->owner[(size_t)i]});
+                                          s->owner[(size_t)i], 4});
+            if (xp.nccl_half)
+                items.push_back(BcastItem{opt->d_param_bf16 + opt->offsets[(size_t)i], opt->sizes[(size_t)i] * 2,
+                                          s->owner[(size_t)i], 1});
+        }
         prof_begin(e, VB_PHASE_EXCHANGE);
         VB_TRY(comm_group_broadcast(e, items.data(), (int64_t)items.size()));
         prof_end(e, VB_PHASE_EXCHANGE);

@@ -61,12 +61,18 @@ struct alignas(16) FatChunk {
 };
 static_assert(sizeof(FatChunk) == 48, "FatChunk is fetched as three 16-byte words");
 
-// Peer GPUs' parameter arenas (same layout as the local one), mapped into this process.
+// Peer GPUs' parameter arenas (same layout as the local one), mapped into this process, and
+// the optional bf16 copies of the parameters (one 16-bit word per arena element, local and
+// on the peers).  A launch stores f32 to `n` peers, bf16 locally when `half_local` is set and
+// bf16 to `n_half` peers.
 constexpr int kMaxPeers = 7;
 struct PeerTable {
     float *base[kMaxPeers];
+    uint16_t *half_base[kMaxPeers];
     const float *local_base;
+    uint16_t *half_local;
     int n;
+    int n_half;
 };
 
 // Scalars of one step, computed on the host in f32 exactly as the reference does.
@@ -99,6 +105,9 @@ int launch_multi_tensor(int op, const FatChunk *d_chunks, int64_t n_chunks, cons
 // do not see the engine's definition (api.cu).
 int engine_launch_info(vb_engine *e, int *device, int *sm_count, cudaStream_t *stream);
 void engine_count_launch(vb_engine *e);
+
+// bf16[i] = round-to-nearest-even(src[i]) for i in [0, n)
+int launch_f32_to_bf16(uint16_t *dst, const float *src, int64_t n, int sm_count, cudaStream_t stream);
 
 int launch_accumulate_grad(float *grad, const float *src, int64_t n, bool add, int sm_count, cudaStream_t stream);
 

@@ -20,10 +20,11 @@ from typing import Iterable, List, Optional, Sequence
 import numpy as np
 
 from . import _lib
-from ._lib import VB_NS_BF16, VB_NS_F32, VB_NS_F32_TC, VB_STEP_DEFAULT, VB_STEP_NO_EXCHANGE, VoltaB200Error, call
+from ._lib import (VB_NS_BF16, VB_NS_F32, VB_NS_F32_TC, VB_STEP_DEFAULT, VB_STEP_EXCHANGE_BF16, VB_STEP_NO_EXCHANGE,
+                   VoltaB200Error, call)
 
 __all__ = ["Engine", "Tensor", "Adam", "SGD", "Muon", "default_engine", "multi_tensor_step", "accumulate_grad",
-           "VoltaB200Error", "VB_NS_F32", "VB_NS_BF16", "VB_NS_F32_TC", "VB_STEP_NO_EXCHANGE"]
+           "VoltaB200Error", "VB_NS_F32", "VB_NS_BF16", "VB_NS_F32_TC", "VB_STEP_NO_EXCHANGE", "VB_STEP_EXCHANGE_BF16"]
 
 
 def _f32(a) -> np.ndarray:
@@ -314,6 +315,41 @@ class _Optimizer:
         if len(blob) != 64 * len(handles):
             raise ValueError("every handle must be 64 bytes")
         call("vb_optimizer_open_peers", self._h, C.c_char_p(blob), len(handles))
+
+    # -- bf16 copies of the parameters, written next to the f32 master ----------------------
+    def enable_bf16_params(self) -> None:
+        """Keeps ``bf16[i] == round_to_nearest_even(param[i])`` in a second arena from now on;
+        ``step(VB_STEP_EXCHANGE_BF16)`` then exchanges only these copies between ranks."""
+        call("vb_optimizer_enable_bf16_params", self._h)
+
+    def refresh_bf16_params(self) -> None:
+        call("vb_optimizer_refresh_bf16_params", self._h)
+
+    def bf16_params(self, i: int) -> np.ndarray:
+        """Parameter ``i``'s bf16 copy as raw 16-bit words (``uint16``) in the tensor's shape."""
+        shape = self.params[i].shape
+        n = int(np.prod(shape, dtype=np.int64))
+        out = np.empty(n, np.uint16)
+        call("vb_optimizer_download_params_bf16", self._h, i, out.ctypes.data_as(C.c_void_p), n)
+        return out.reshape(shape)
+
+    def bf16_param_ptr(self, i: int) -> int:
+        p = C.c_void_p()
+        call("vb_optimizer_param_bf16_ptr", self._h, i, C.byref(p))
+        return int(p.value or 0)
+
+    def ipc_handle_bf16(self) -> bytes:
+        buf = C.create_string_buffer(64)
+        call("vb_optimizer_ipc_handle_bf16", self._h, buf)
+        return buf.raw
+
+    def open_peers_bf16(self, handles: Sequence[bytes]) -> None:
+        """``handles[r]`` = rank r's ``ipc_handle_bf16()``: the copies then reach the peers by
+        stores fused into the update / apply kernel instead of an NCCL call."""
+        blob = b"".join(handles)
+        if len(blob) != 64 * len(handles):
+            raise ValueError("every handle must be 64 bytes")
+        call("vb_optimizer_open_peers_bf16", self._h, C.c_char_p(blob), len(handles))
 
     # -- whole-arena access (one transfer for all tensors) ---------------------------------
     def arena_layout(self):
