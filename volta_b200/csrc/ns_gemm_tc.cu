@@ -292,6 +292,21 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&v)[32])
         : "r"(taddr));
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// Load and wait in one statement: the values are final when the statement ends.
+__device__ __forceinline__ void tmem_ld_32x32_sync(uint32_t taddr, uint32_t (&v)[32])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n\t"
+        "tcgen05.wait::ld.sync.aligned;"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+}
 
 // Shared-memory matrix descriptor (sm_100 format): start address, leading/stride byte offsets
 // (all >> 4), version 1, 128-byte swizzle.
@@ -354,6 +369,192 @@ __device__ __forceinline__ int term_plane_b(int n_terms, int term) { return n_te
 
 // What a role needs to know about a tile, fetched one tile ahead so that the dependent global
 // loads (tile -> problem -> fields) never sit between two tiles' main loops.
+// One 32-column piece of an accumulator row on the common path of the plain bf16 kernel
+// (interior tile, output rows 32-byte aligned): one multiply per element, the 3I of the
+// Gram epilogue added only by the one warp piece that holds the diagonal, bf16 rounding, two
+// 256-bit stores.  The epilogue warps share their scheduler with the producer and the MMA
+// thread, so the instruction count here decides how much the drain disturbs the main loop.
+template <int EPI>
+__device__ __forceinline__ void drain_chunk_fast(const uint32_t (&v)[32], float mult, bool diagonal_piece, int lane,
+                                                 __nv_bfloat16 *__restrict__ dst_bf16, float *__restrict__ dst_f32,
+                                                 __nv_bfloat16 *__restrict__ mirror_dst, int64_t ld)
+{
+    float f[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]) * mult;
+    if (EPI == TC_EPI_THREE_I_MINUS && diagonal_piece) {  // warp-uniform: row - col0 == lane
+#pragma unroll
+        for (int j = 0; j < 32; ++j) f[j] = (j == lane) ? 3.0f + f[j] : f[j];
+    }
+    if (dst_f32) {
+#pragma unroll
+        for (int g8 = 0; g8 < 4; ++g8) {
+            uint32_t q[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) q[j] = __float_as_uint(f[g8 * 8 + j]);
+            st_global_256(dst_f32 + g8 * 8, q);
+        }
+    }
+    if (dst_bf16) {
+#pragma unroll
+        for (int g16 = 0; g16 < 2; ++g16) {
+            uint32_t q[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) q[j] = pack_bf16(f[g16 * 16 + 2 * j], f[g16 * 16 + 2 * j + 1]);
+            st_global_256(dst_bf16 + g16 * 16, q);
+        }
+        if (mirror_dst) {  // symmetric product: element (row, col) also goes to (col, row)
+#pragma unroll
+            for (int j = 0; j < 32; ++j) mirror_dst[(int64_t)j * ld] = __float2bfloat16_rn(f[j]);
+        }
+    }
+}
+
+template <int EPI>
+__device__ __forceinline__ void drain_fast(uint32_t taddr, int row, int tile_col0, bool row_ok, float mult, int lane,
+                                           __nv_bfloat16 *out_bf16, float *out_f32, bool mirror, int64_t ld)
+{
+    constexpr int kPieces = (BN / 2) / 32;
+    uint32_t v[2][32];
+    tmem_ld_32x32(taddr, v[0]);
+#pragma unroll
+    for (int cc = 0; cc < kPieces; ++cc) {
+        const int col0 = tile_col0 + cc * 32;
+        tmem_ld_wait();
+        if (cc + 1 < kPieces) tmem_ld_32x32(taddr + (uint32_t)((cc + 1) * 32), v[(cc + 1) & 1]);
+        if (row_ok) {
+            const int64_t at = (int64_t)row * ld + col0;
+            drain_chunk_fast<EPI>(v[cc & 1], mult, row - col0 == lane, lane, out_bf16 ? out_bf16 + at : nullptr,
+                                  out_f32 ? out_f32 + at : nullptr,
+                                  (mirror && out_bf16) ? out_bf16 + (int64_t)col0 * ld + row : nullptr, ld);
+        }
+    }
+}
+
+// Every other case: ragged edges (columns beyond N, unaligned output rows), and all of the
+// split (f32-accurate) kernel's epilogues.  Element-wise code with the bounds checks inside.
+struct DrainArgs {
+    uint32_t taddr;
+    int row, tile_col0, M, N, epi, lane;
+    float acc_scale;
+    int64_t ld, plane_stride;
+    int out_planes, out_planes_in;
+    bool bf16_rows_32b, mirror;
+    __nv_bfloat16 *out_bf16;
+    float *out_f32;
+    const __nv_bfloat16 *in_bf16;
+};
+template <bool kSplit>
+__device__ __forceinline__ void drain_generic(const DrainArgs &a)
+{
+    constexpr int kChunks = (BN / 2) / 32;
+    const uint32_t taddr = a.taddr;
+    const int row = a.row, tile_col0 = a.tile_col0, M = a.M, N = a.N, epi = a.epi;
+    const float acc_scale = a.acc_scale;
+    const int64_t ld = a.ld, plane_stride = a.plane_stride;
+    const int out_planes = a.out_planes, out_planes_in = a.out_planes_in;
+    const bool bf16_rows_32b = a.bf16_rows_32b, mirror = a.mirror;
+    __nv_bfloat16 *out_bf16 = a.out_bf16;
+    float *out_f32 = a.out_f32;
+    const __nv_bfloat16 *in_bf16 = a.in_bf16;
+    // One load in flight at a time, waited for in the same statement: the registers a
+    // tcgen05.ld targets are written asynchronously, so nothing may touch or move them before
+    // the wait; this path is off the critical path (ragged edges; the split kernel's main loop is
+    // six times longer), so it does not pipeline its loads.
+    uint32_t v[32];
+    for (int cc = 0; cc < kChunks; ++cc) {
+        const int col0 = tile_col0 + cc * 32;
+        if (col0 >= N) break;  // uniform across the warp
+        tmem_ld_32x32_sync(taddr + (uint32_t)(cc * 32), v);
+        if (row < M) {
+            float f[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const float a = __uint_as_float(v[j]) * acc_scale;
+                if (epi == TC_EPI_THREE_I_MINUS) f[j] = (row == col0 + j) ? 3.0f - a : -a;  // muon.rs:76-89
+                else if (epi == TC_EPI_HALF) f[j] = 0.5f * a;                               // muon.rs:95-99
+                else f[j] = a;  // TC_EPI_IDENTITY, or TC_EPI_NS_COMBINE (finished below)
+            }
+            if (kSplit && epi == TC_EPI_NS_COMBINE) {
+                // X' = 0.5 X (3I - G) evaluated as 1.5 X - 0.5 (X G): the accumulator holds only
+                // the small product X G, so the tensor core's truncating f32 accumulation acts on
+                // a term that is a few percent of the result instead of on the result itself.
+                const __nv_bfloat16 *src = in_bf16 + (int64_t)row * ld + col0;
+                float x[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) x[j] = 0.0f;
+                for (int pl = out_planes_in - 1; pl >= 0; --pl) {  // smallest piece first: the sum is exact
+#pragma unroll
+                    for (int g8 = 0; g8 < 4; ++g8) {               // 8 columns = one 16-byte load
+                        if (col0 + g8 * 8 < N) {
+                            const uint4 q = *reinterpret_cast<const uint4 *>(src + pl * plane_stride + g8 * 8);
+                            const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                            for (int h = 0; h < 4; ++h) {  // bf16 -> f32 is a 16-bit shift
+                                x[g8 * 8 + 2 * h] += __uint_as_float(w[h] << 16);
+                                x[g8 * 8 + 2 * h + 1] += __uint_as_float(w[h] & 0xffff0000u);
+                            }
+                        }
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < 32; ++j) f[j] = fmaf(1.5f, x[j], -0.5f * f[j]);
+            }
+            if (out_f32) {
+                float *dst = out_f32 + (int64_t)row * ld + col0;
+#pragma unroll
+                for (int g8 = 0; g8 < 4; ++g8) {  // 8 columns = one 32-byte sector per store
+                    if (col0 + g8 * 8 >= N) break;
+                    uint32_t q[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) q[j] = __float_as_uint(f[g8 * 8 + j]);
+                    st_global_256(dst + g8 * 8, q);
+                }
+            }
+            if (out_bf16) {
+                for (int pl = 0; pl < out_planes; ++pl) {
+                    __nv_bfloat16 *dst = out_bf16 + pl * plane_stride + (int64_t)row * ld + col0;
+#pragma unroll
+                    for (int g16 = 0; g16 < 2; ++g16) {  // 16 columns = one 32-byte sector per store
+                        const int col = col0 + g16 * 16;
+                        if (col + 16 <= N && bf16_rows_32b) {
+                            uint32_t q[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                q[j] = pack_bf16(f[g16 * 16 + 2 * j], f[g16 * 16 + 2 * j + 1]);
+                            st_global_256(dst + g16 * 16, q);
+                        } else {  // 16-byte pieces (N and ld are multiples of 8)
+#pragma unroll
+                            for (int h = 0; h < 2; ++h) {
+                                if (col + h * 8 >= N) break;
+                                uint4 q;
+                                q.x = pack_bf16(f[g16 * 16 + h * 8 + 0], f[g16 * 16 + h * 8 + 1]);
+                                q.y = pack_bf16(f[g16 * 16 + h * 8 + 2], f[g16 * 16 + h * 8 + 3]);
+                                q.z = pack_bf16(f[g16 * 16 + h * 8 + 4], f[g16 * 16 + h * 8 + 5]);
+                                q.w = pack_bf16(f[g16 * 16 + h * 8 + 6], f[g16 * 16 + h * 8 + 7]);
+                                *reinterpret_cast<uint4 *>(dst + g16 * 16 + h * 8) = q;
+                            }
+                        }
+                    }
+                    if (mirror) {
+                        // D is symmetric and only its upper tiles are computed: element (row, col)
+                        // also goes to (col, row).  For a fixed column the 32 lanes of the warp
+                        // hold 32 consecutive rows, i.e. one contiguous 64-byte run of the mirror.
+                        __nv_bfloat16 *mdst = out_bf16 + pl * plane_stride + (int64_t)col0 * ld + row;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (col0 + j < N) mdst[(int64_t)j * ld] = __float2bfloat16_rn(f[j]);
+                    }
+                    if (pl + 1 < out_planes) {  // what this plane's rounding left over goes to the next
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) f[j] -= __bfloat162float(__float2bfloat16_rn(f[j]));
+                    }
+                }
+            }
+        }
+    }
+}
+
 struct TileInfo {
     const TcGemmProblem *p;
     int m0, n0, k_blocks, a_mode, b_mode, n_terms;
@@ -558,7 +759,6 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
         // ---------------- epilogue (warps 2..9 of every CTA) ----------------
         const int quarter = warp & 3;          // the TMEM lane quarter this warp may read
         const int col_half = (warp - 2) >> 2;  // which 128 of the 256 accumulator columns
-        constexpr int kChunks = (BN / 2) / 32;
         int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
@@ -590,108 +790,46 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
                 ok = false;
                 break;
             }
+#ifdef VB_TC_TIMING
+            const long long t_body0 = clock64();
+#endif
             tcgen05_fence_after();
             const int row = ti.m0 + (int)cta_rank * BM + quarter * 32 + lane;
             const int tile_col0 = ti.n0 + col_half * (BN / 2);
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) +
                                    (uint32_t)(acc * kAccCols + col_half * (BN / 2));
-            uint32_t v[2][32];
-            if (tile_col0 < N) tmem_ld_32x32(taddr, v[0]);
-#pragma unroll
-            for (int cc = 0; cc < kChunks; ++cc) {
-                const int col0 = tile_col0 + cc * 32;
-                if (col0 >= N) break;  // uniform across the warp
-                tmem_ld_wait();
-                if (cc + 1 < kChunks && col0 + 32 < N) tmem_ld_32x32(taddr + (uint32_t)((cc + 1) * 32), v[(cc + 1) & 1]);
-                if (row < M) {
-                    float f[32];
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const float a = __uint_as_float(v[cc & 1][j]) * acc_scale;
-                        if (epi == TC_EPI_THREE_I_MINUS) f[j] = (row == col0 + j) ? 3.0f - a : -a;  // muon.rs:76-89
-                        else if (epi == TC_EPI_HALF) f[j] = 0.5f * a;                               // muon.rs:95-99
-                        else f[j] = a;  // TC_EPI_IDENTITY, or TC_EPI_NS_COMBINE (finished below)
-                    }
-                    if (kSplit && epi == TC_EPI_NS_COMBINE) {
-                        // X' = 0.5 X (3I - G) evaluated as 1.5 X - 0.5 (X G): the accumulator holds only
-                        // the small product X G, so the tensor core's truncating f32 accumulation acts on
-                        // a term that is a few percent of the result instead of on the result itself.
-                        const __nv_bfloat16 *src = in_bf16 + (int64_t)row * ld + col0;
-                        float x[32];
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) x[j] = 0.0f;
-                        for (int pl = out_planes_in - 1; pl >= 0; --pl) {  // smallest piece first: the sum is exact
-#pragma unroll
-                            for (int g8 = 0; g8 < 4; ++g8) {               // 8 columns = one 16-byte load
-                                if (col0 + g8 * 8 < N) {
-                                    const uint4 q = *reinterpret_cast<const uint4 *>(src + pl * plane_stride + g8 * 8);
-                                    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-                                    for (int h = 0; h < 4; ++h) {  // bf16 -> f32 is a 16-bit shift
-                                        x[g8 * 8 + 2 * h] += __uint_as_float(w[h] << 16);
-                                        x[g8 * 8 + 2 * h + 1] += __uint_as_float(w[h] & 0xffff0000u);
-                                    }
-                                }
-                            }
-                        }
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) f[j] = fmaf(1.5f, x[j], -0.5f * f[j]);
-                    }
-                    if (out_f32) {
-                        float *dst = out_f32 + (int64_t)row * ld + col0;
-#pragma unroll
-                        for (int g8 = 0; g8 < 4; ++g8) {  // 8 columns = one 32-byte sector per store
-                            if (col0 + g8 * 8 >= N) break;
-                            uint32_t q[8];
-#pragma unroll
-                            for (int j = 0; j < 8; ++j) q[j] = __float_as_uint(f[g8 * 8 + j]);
-                            st_global_256(dst + g8 * 8, q);
-                        }
-                    }
-                    if (out_bf16) {
-                        for (int pl = 0; pl < out_planes; ++pl) {
-                            __nv_bfloat16 *dst = out_bf16 + pl * plane_stride + (int64_t)row * ld + col0;
-#pragma unroll
-                            for (int g16 = 0; g16 < 2; ++g16) {  // 16 columns = one 32-byte sector per store
-                                const int col = col0 + g16 * 16;
-                                if (col + 16 <= N && bf16_rows_32b) {
-                                    uint32_t q[8];
-#pragma unroll
-                                    for (int j = 0; j < 8; ++j)
-                                        q[j] = pack_bf16(f[g16 * 16 + 2 * j], f[g16 * 16 + 2 * j + 1]);
-                                    st_global_256(dst + g16 * 16, q);
-                                } else {  // 16-byte pieces (N and ld are multiples of 8)
-#pragma unroll
-                                    for (int h = 0; h < 2; ++h) {
-                                        if (col + h * 8 >= N) break;
-                                        uint4 q;
-                                        q.x = pack_bf16(f[g16 * 16 + h * 8 + 0], f[g16 * 16 + h * 8 + 1]);
-                                        q.y = pack_bf16(f[g16 * 16 + h * 8 + 2], f[g16 * 16 + h * 8 + 3]);
-                                        q.z = pack_bf16(f[g16 * 16 + h * 8 + 4], f[g16 * 16 + h * 8 + 5]);
-                                        q.w = pack_bf16(f[g16 * 16 + h * 8 + 6], f[g16 * 16 + h * 8 + 7]);
-                                        *reinterpret_cast<uint4 *>(dst + g16 * 16 + h * 8) = q;
-                                    }
-                                }
-                            }
-                            if (ti.mirror) {
-                                // D is symmetric and only its upper tiles are computed: element (row, col)
-                                // also goes to (col, row).  For a fixed column the 32 lanes of the warp
-                                // hold 32 consecutive rows, i.e. one contiguous 64-byte run of the mirror.
-                                __nv_bfloat16 *mdst = out_bf16 + pl * plane_stride + (int64_t)col0 * ld + row;
-#pragma unroll
-                                for (int j = 0; j < 32; ++j)
-                                    if (col0 + j < N) mdst[(int64_t)j * ld] = __float2bfloat16_rn(f[j]);
-                            }
-                            if (pl + 1 < out_planes) {  // what this plane's rounding left over goes to the next
-#pragma unroll
-                                for (int j = 0; j < 32; ++j) f[j] -= __bfloat162float(__float2bfloat16_rn(f[j]));
-                            }
-                        }
-                    }
-                }
+            // Common case of the plain bf16 kernel: the warp's 128 columns lie inside the matrix and
+            // output rows start on 32-byte boundaries.
+            const bool fast = !kSplit && tile_col0 + BN / 2 <= N && bf16_rows_32b &&
+                              (epi == TC_EPI_HALF || epi == TC_EPI_THREE_I_MINUS || epi == TC_EPI_IDENTITY);
+            if (fast) {
+                // (a * s) * 0.5 == a * (s * 0.5) and -(a * s) == a * (-s) exactly
+                if (epi == TC_EPI_HALF)
+                    drain_fast<TC_EPI_HALF>(taddr, row, tile_col0, row < M, 0.5f * acc_scale, lane, out_bf16, out_f32,
+                                            ti.mirror, ld);
+                else if (epi == TC_EPI_THREE_I_MINUS)
+                    drain_fast<TC_EPI_THREE_I_MINUS>(taddr, row, tile_col0, row < M, -acc_scale, lane, out_bf16,
+                                                     out_f32, ti.mirror, ld);
+                else
+                    drain_fast<TC_EPI_IDENTITY>(taddr, row, tile_col0, row < M, acc_scale, lane, out_bf16, out_f32,
+                                                ti.mirror, ld);
+            }
+            if (!fast) {
+                DrainArgs da;
+                da.taddr = taddr; da.row = row; da.tile_col0 = tile_col0; da.M = M; da.N = N; da.epi = epi;
+                da.lane = lane; da.acc_scale = acc_scale; da.ld = ld; da.plane_stride = plane_stride;
+                da.out_planes = out_planes; da.out_planes_in = out_planes_in; da.bf16_rows_32b = bf16_rows_32b;
+                da.mirror = ti.mirror; da.out_bf16 = out_bf16; da.out_f32 = out_f32; da.in_bf16 = in_bf16;
+                drain_generic<kSplit>(da);
             }
             tcgen05_fence_before();
             __syncwarp();
+#ifdef VB_TC_TIMING
+            if (blockIdx.x == 0 && warp == 2 && lane == 0) {
+                atomicAdd(&g_wait_cycles[8], (unsigned long long)(clock64() - t_body0));
+                atomicAdd(&g_wait_cycles[10], 1ull);
+            }
+#endif
             if (lane == 0) {
                 if (kCtas == 2) mbar_remote_arrive(map_to_cta(smem_u32(&bars->tmem_empty[acc]), 0));
                 else mbar_arrive(&bars->tmem_empty[acc]);
