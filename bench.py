@@ -363,6 +363,18 @@ def run_ours(args):
                                 "sample": f"{len(times)} full steps of the same workload, 1 thread of "
                                           f"{os.cpu_count()} host cores (Volta's optimizer is single threaded)",
                                 "ms_per_step": sec * 1e3}
+    if world > 1:
+        # Every rank must receive the (N-1)/N of the updated parameters it does not own: NVLink
+        # ingress bounds the whole step whatever the update costs.  770 GB/s is the peer-copy rate
+        # measured per direction per GPU on this pool (900 nominal).
+        ingress = 4.0 * wl.total * (world - 1) / world
+        floor_ms = ingress / 770e9 * 1e3
+        line["exchange_roofline"] = {"bound": "nvlink ingress per GPU", "bytes_in_per_gpu": ingress, "peak": 770.0,
+                                     "unit": "GB/s", "floor_ms": floor_ms,
+                                     "achieved": ingress / (ms_per_step * 1e-3) / 1e9,
+                                     "frac": floor_ms / ms_per_step,
+                                     "note": "strong scaling of the whole step is capped by this floor; the update "
+                                             "kernel itself scales with 1/N (update_only)"}
     if bf16_exchange is not None:
         line["bf16_exchange"] = bf16_exchange
     if muon is not None:
