@@ -294,6 +294,23 @@ def run_ours(args):
     barrier()
     e2e_s = max_over_ranks((time.perf_counter() - t0) / max(e2e_steps, 1))
 
+    # ---- N > 1: data-parallel step, the reduce-scatter of gradients fused into the kernel's loads ----
+    dp_step = None
+    if world > 1 and args.exchange == "peer":
+        from volta_b200 import VB_STEP_MEAN_GRADS
+        opt.open_peers_grads(gather_handles(opt.ipc_handle_grads(), world, dev))
+        for _ in range(3):
+            opt.step(VB_STEP_MEAN_GRADS)
+        barrier()
+        dp_ms, _ = timed_steps(args.steps, VB_STEP_MEAN_GRADS)
+        barrier()
+        dp_ms = max_over_ranks(dp_ms) / args.steps
+        dp_step = {"value": wl.total / (dp_ms * 1e-3), "unit": "params/s", "ms_per_step": dp_ms,
+                   "note": "step(VB_STEP_MEAN_GRADS): every rank holds its own gradient of the whole model; the "
+                           "owner's update kernel reads all ranks' gradients over NVLink, adds them in rank order, "
+                           "updates and stores the new parameters to every rank (reduce-scatter + Adam + all-gather "
+                           "in one kernel)"}
+
     # ---- N > 1: the same step exchanging bf16 copies of the parameters instead of f32 ----
     bf16_exchange = None
     if world > 1:
@@ -375,6 +392,8 @@ def run_ours(args):
                                      "frac": floor_ms / ms_per_step,
                                      "note": "strong scaling of the whole step is capped by this floor; the update "
                                              "kernel itself scales with 1/N (update_only)"}
+    if dp_step is not None:
+        line["data_parallel_step"] = dp_step
     if bf16_exchange is not None:
         line["bf16_exchange"] = bf16_exchange
     if muon is not None:

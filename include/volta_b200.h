@@ -78,6 +78,10 @@ typedef enum vb_ns_mode {
 /* Flags of vb_optimizer_step_ex. */
 #define VB_STEP_DEFAULT 0u
 #define VB_STEP_NO_EXCHANGE 1u /* sharded engines: update the owned part only, skip the all-gather / broadcast */
+#define VB_STEP_REDUCE_GRADS 4u /* sharded engines, after vb_optimizer_open_peers_grads: the gradient of every element a
+                                   rank updates is the sum of all ranks' gradients (a reduce-scatter fused into the
+                                   update kernel's loads) */
+#define VB_STEP_MEAN_GRADS 8u   /* as VB_STEP_REDUCE_GRADS, the sum multiplied by 1 / world_size */
 #define VB_STEP_EXCHANGE_BF16 2u /* sharded engines with the bf16 copy enabled: exchange only the bf16 copies (half the
                                     bytes); f32 parameters other ranks own are left as they were */
 
@@ -277,6 +281,21 @@ int vb_optimizer_set_lr(vb_optimizer *opt, float lr);
 #define VB_IPC_HANDLE_BYTES 64
 int vb_optimizer_ipc_handle(vb_optimizer *opt, void *handle64);
 int vb_optimizer_open_peers(vb_optimizer *opt, const void *handles, int n_handles);
+
+/* Data-parallel gradients (no counterpart in the reference, which has one process and one
+ * device).  Every rank holds its own gradient of the whole model in its gradient arena; after
+ * vb_optimizer_open_peers_grads was given every rank's vb_optimizer_ipc_handle_grads,
+ * step_ex(VB_STEP_REDUCE_GRADS) makes the update kernel (Adam, SGD) or the momentum kernel
+ * (Muon) of the owning rank read the element's gradient from every rank over NVLink and add
+ * the values in rank order, one rounded f32 addition per rank (VB_STEP_MEAN_GRADS: then multiply
+ * by 1 / world_size): the reduce-scatter rides in the kernel's loads, gradients are read once,
+ * and no reduced gradient is ever written.  The step is fenced by the same two stream-ordered
+ * barriers as the fused parameter exchange, so work enqueued on the engine's stream after
+ * step() (uploads through this API included) cannot overtake the peers' reads; a producer that
+ * writes gradients from another stream must first wait for the engine's stream.  All ranks must
+ * hold the same presence flags. */
+int vb_optimizer_ipc_handle_grads(vb_optimizer *opt, void *handle64);
+int vb_optimizer_open_peers_grads(vb_optimizer *opt, const void *handles, int n_handles);
 
 /* bf16 copies of the parameters, written by the update kernel next to the f32 master (no
  * counterpart in the reference's optimizers; the rounding is the one its bf16 storage type

@@ -230,3 +230,89 @@ def test_two_gpu_bf16_copies_exchange(oracle, kind, transport, what):
                 assert np.array_equal(got[:lo], stale[:lo]) and np.array_equal(got[hi:], stale[hi:])
     if what == "half":
         assert owned_total == wl.total
+
+
+def _rank_grads(wl, step, rank):
+    """Rank-specific gradients of the whole model (what data parallelism gives each rank)."""
+    return [(g * np.float32(1.0 + 0.25 * rank) + np.float32(1e-4 * rank)).astype(np.float32)
+            for g in wl.make_grads(step * 7 + rank)]
+
+
+def _worker_reduce(rank, world, shared, kind, transport, mean):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import time
+
+    from volta_b200 import (SGD, VB_NS_F32, VB_STEP_MEAN_GRADS, VB_STEP_REDUCE_GRADS, Adam, Engine, Muon, Tensor)
+    eng = Engine(rank)
+    if rank == 0:
+        shared["id"] = Engine.unique_id()
+    while "id" not in shared:
+        time.sleep(0.01)
+    eng.init_comm(shared["id"], rank, world)
+    wl = _small_workload(kind)
+    h = wl.hyper
+    tensors = [Tensor(p, p.shape) for p in wl.make_params()]
+    if kind == "adam":
+        opt = Adam(tensors, h["lr"], h["betas"], h["eps"], h["weight_decay"], engine=eng)
+    elif kind == "sgd":
+        opt = SGD(tensors, h["lr"], h["momentum"], h["weight_decay"], engine=eng)
+    else:
+        opt = Muon(tensors, h["lr"], h["momentum"], h["nesterov"], h["ns_steps"], ns_mode=VB_NS_F32, engine=eng)
+
+    def gather(key, value):
+        shared[f"{key}{rank}"] = value
+        while any(f"{key}{r}" not in shared for r in range(world)):
+            time.sleep(0.01)
+        return [shared[f"{key}{r}"] for r in range(world)]
+
+    opt.open_peers_grads(gather("ipcg", opt.ipc_handle_grads()))
+    if transport == "peer":
+        opt.open_peers(gather("ipc", opt.ipc_handle()))
+    for s in (1, 2, 3):
+        for t, g in zip(tensors, _rank_grads(wl, s, rank)):
+            t.grad = g
+        opt.step(VB_STEP_MEAN_GRADS if mean else VB_STEP_REDUCE_GRADS)
+        eng.synchronize()   # the next upload overwrites gradients the peers read during this step
+    shared[f"params{rank}"] = [t.data.copy() for t in tensors]
+    opt.close()
+    eng.close()
+
+
+@pytest.mark.parametrize("kind,transport,mean", [("adam", "peer", False), ("adam", "nccl", True), ("sgd", "peer", True),
+                                                 ("muon_f32", "peer", False), ("muon_f32", "nccl", True)])
+def test_two_gpu_gradient_reduction_fused_into_the_update(oracle, kind, transport, mean):
+    """Data-parallel step: each rank holds its own gradient of the whole model; the owning rank's
+    kernel adds the ranks' values in rank order while it loads them.  Bit-identical to the oracle
+    stepping with the gradients summed the same way on the host."""
+    if _gpu_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    with ctx.Manager() as mgr:
+        shared = mgr.dict()
+        procs = [ctx.Process(target=_worker_reduce, args=(r, 2, shared, kind, transport, mean)) for r in range(2)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(300)
+            assert p.exitcode == 0
+        res = dict(shared)
+    wl = _small_workload(kind)
+    h = wl.hyper
+    ref = wl.make_params()
+    if kind == "adam":
+        o = oracle.Adam(ref, h["lr"], h["betas"], h["eps"], h["weight_decay"])
+    elif kind == "sgd":
+        o = oracle.SGD(ref, h["lr"], h["momentum"], h["weight_decay"])
+    else:
+        o = oracle.Muon(ref, h["lr"], h["momentum"], h["nesterov"], h["ns_steps"])
+    for s in (1, 2, 3):
+        g0, g1 = _rank_grads(wl, s, 0), _rank_grads(wl, s, 1)
+        summed = [(a + b).astype(np.float32) for a, b in zip(g0, g1)]          # one rounded add, rank order
+        if mean:
+            summed = [(x * np.float32(0.5)).astype(np.float32) for x in summed]
+        o.step(summed)
+    for a, b, r in zip(res["params0"], res["params1"], ref):
+        assert np.array_equal(a.view(np.uint32), r.view(np.uint32))
+        assert np.array_equal(b.view(np.uint32), r.view(np.uint32))

@@ -5,10 +5,11 @@
 Importing this package needs the built library; there is no CPU or PyTorch fallback.
 """
 from . import _lib
-from .optim import (VB_NS_BF16, VB_NS_F32, VB_NS_F32_TC, VB_STEP_EXCHANGE_BF16, VB_STEP_NO_EXCHANGE, Adam, Engine, Muon, PinnedBuffer,
+from .optim import (VB_NS_BF16, VB_NS_F32, VB_NS_F32_TC, VB_STEP_EXCHANGE_BF16, VB_STEP_MEAN_GRADS, VB_STEP_NO_EXCHANGE,
+                    VB_STEP_REDUCE_GRADS, Adam, Engine, Muon, PinnedBuffer,
                     SGD, Tensor, VoltaB200Error, default_engine, multi_tensor_step)
 
 _lib.load()  # fail loudly at import time if the CUDA library has not been built
 
 __all__ = ["Adam", "SGD", "Muon", "Tensor", "Engine", "PinnedBuffer", "default_engine",
-           "multi_tensor_step", "VoltaB200Error", "VB_NS_F32", "VB_NS_BF16", "VB_NS_F32_TC", "VB_STEP_NO_EXCHANGE", "VB_STEP_EXCHANGE_BF16"]
+           "multi_tensor_step", "VoltaB200Error", "VB_NS_F32", "VB_NS_BF16", "VB_NS_F32_TC", "VB_STEP_NO_EXCHANGE", "VB_STEP_EXCHANGE_BF16", "VB_STEP_REDUCE_GRADS", "VB_STEP_MEAN_GRADS"]

@@ -22,6 +22,8 @@ VB_NS_F32_TC = 2
 VB_STEP_DEFAULT = 0
 VB_STEP_NO_EXCHANGE = 1
 VB_STEP_EXCHANGE_BF16 = 2
+VB_STEP_REDUCE_GRADS = 4
+VB_STEP_MEAN_GRADS = 8
 
 
 class VoltaB200Error(RuntimeError):
@@ -97,6 +99,8 @@ SIGNATURES = {
     "vb_optimizer_import_state": [_vp, _i64, C.c_int, _vp, _i64],
     "vb_optimizer_ipc_handle": [_vp, _vp],
     "vb_optimizer_open_peers": [_vp, _vp, C.c_int],
+    "vb_optimizer_ipc_handle_grads": [_vp, _vp],
+    "vb_optimizer_open_peers_grads": [_vp, _vp, C.c_int],
     "vb_optimizer_enable_bf16_params": [_vp],
     "vb_optimizer_refresh_bf16_params": [_vp],
     "vb_optimizer_param_bf16_ptr": [_vp, C.c_int64, C.POINTER(C.c_void_p)],

@@ -279,7 +279,8 @@ namespace vb {
 int plan_exchange(vb_optimizer *opt, uint32_t flags, ExchangePlan *plan)
 {
     vb_engine *e = opt->eng;
-    if (flags & ~(VB_STEP_NO_EXCHANGE | VB_STEP_EXCHANGE_BF16)) return fail(VB_ERR_INVALID_ARG, "unknown step flags 0x%x", flags);
+    if (flags & ~(VB_STEP_NO_EXCHANGE | VB_STEP_EXCHANGE_BF16 | VB_STEP_REDUCE_GRADS | VB_STEP_MEAN_GRADS))
+        return fail(VB_ERR_INVALID_ARG, "unknown step flags 0x%x", flags);
     const bool half = opt->d_param_bf16 != nullptr;
     const bool half_only = (flags & VB_STEP_EXCHANGE_BF16) != 0;
     if (half_only && !half)
@@ -307,6 +308,17 @@ int plan_exchange(vb_optimizer *opt, uint32_t flags, ExchangePlan *plan)
         }
         xp.fused = xp.pt.n > 0 || xp.pt.n_half > 0;
     }
+    if (flags & (VB_STEP_REDUCE_GRADS | VB_STEP_MEAN_GRADS)) {
+        if (e->world > 1) {
+            if (opt->peers.n_grad != e->world - 1)
+                return fail(VB_ERR_STATE, "VB_STEP_REDUCE_GRADS needs vb_optimizer_open_peers_grads first");
+            xp.pt.n_grad = opt->peers.n_grad;
+            for (int r = 0; r < opt->peers.n_grad; ++r) xp.pt.grad_base[r] = opt->peers.grad_base[r];
+            xp.fused = true;  // peers' gradients are read: fence the step on both sides
+        }
+        xp.pt.rank = e->rank;
+    }
+    xp.pt.grad_scale = (flags & VB_STEP_MEAN_GRADS) ? 1.0f / (float)e->world : 1.0f;
     *plan = xp;
     return VB_OK;
 }
@@ -1186,6 +1198,32 @@ int vb_optimizer_open_peers(vb_optimizer *opt, const void *handles, int n_handle
     for (int r = 0; r < opt->eng->world - 1; ++r) opt->peers.base[r] = (float *)mapped[r];
     opt->peers.local_base = opt->d_param;
     opt->peers.n = opt->eng->world - 1;
+    return VB_OK;
+    VB_API_END
+}
+
+int vb_optimizer_ipc_handle_grads(vb_optimizer *opt, void *handle64)
+{
+    VB_API_BEGIN
+    VB_TRY(check_opt(opt));
+    if (!handle64) return fail(VB_ERR_INVALID_ARG, "handle64 is null");
+    VB_TRY(set_device(opt->eng));
+    cudaIpcMemHandle_t h;
+    VB_CUDA(cudaIpcGetMemHandle(&h, opt->d_grad));
+    memcpy(handle64, &h, sizeof(h));
+    return VB_OK;
+    VB_API_END
+}
+
+int vb_optimizer_open_peers_grads(vb_optimizer *opt, const void *handles, int n_handles)
+{
+    VB_API_BEGIN
+    VB_TRY(check_opt(opt));
+    if (opt->peers.n_grad > 0) return fail(VB_ERR_STATE, "gradient peers are already open");
+    void *mapped[kMaxPeers] = {};
+    VB_TRY(open_peer_handles(opt, handles, n_handles, mapped));
+    for (int r = 0; r < opt->eng->world - 1; ++r) opt->peers.grad_base[r] = (const float *)mapped[r];
+    opt->peers.n_grad = opt->eng->world - 1;
     return VB_OK;
     VB_API_END
 }

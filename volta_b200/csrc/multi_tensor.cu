@@ -117,13 +117,61 @@ __device__ __forceinline__ uint16_t bf16_bits(float x)
     return *reinterpret_cast<const uint16_t *>(&v);
 }
 
+// Gradient of one element under data parallelism: the sum of every rank's gradient at the
+// same arena position, added in rank order (one rounded f32 add per rank, so the result does
+// not depend on which rank computes it), then scaled.  The peers' values come over NVLink as
+// plain loads; the loop is unrolled so that the table stays in the constant bank.
+__device__ __forceinline__ const float *grad_source(const PeerTable &pt, const float *local, ptrdiff_t arena_pos, int k)
+{
+    // rank k's gradient arena at this position: peers are stored in rank order without this rank
+    const float *arena = k == pt.rank ? local : (k < pt.rank ? pt.grad_base[k < kMaxPeers ? k : 0] : pt.grad_base[k > 0 ? k - 1 : 0]);
+    return arena + arena_pos;
+}
+
+__device__ __forceinline__ Vec8 sum_grads8(const PeerTable &pt, const float *local, ptrdiff_t arena_pos, uint32_t i)
+{
+    Vec8 term[kMaxPeers + 1];
+#pragma unroll
+    for (int k = 0; k <= kMaxPeers; ++k)  // all loads first: NVLink latency overlaps
+        if (k <= pt.n_grad) term[k] = ld_vec8(reinterpret_cast<const Vec8 *>(grad_source(pt, local, arena_pos, k)) + i);
+    Vec8 acc = term[0];
+#pragma unroll
+    for (int k = 1; k <= kMaxPeers; ++k) {
+        if (k <= pt.n_grad) {
+            acc.lo.x = __fadd_rn(acc.lo.x, term[k].lo.x); acc.lo.y = __fadd_rn(acc.lo.y, term[k].lo.y);
+            acc.lo.z = __fadd_rn(acc.lo.z, term[k].lo.z); acc.lo.w = __fadd_rn(acc.lo.w, term[k].lo.w);
+            acc.hi.x = __fadd_rn(acc.hi.x, term[k].hi.x); acc.hi.y = __fadd_rn(acc.hi.y, term[k].hi.y);
+            acc.hi.z = __fadd_rn(acc.hi.z, term[k].hi.z); acc.hi.w = __fadd_rn(acc.hi.w, term[k].hi.w);
+        }
+    }
+    const float sc = pt.grad_scale;
+    acc.lo.x = __fmul_rn(acc.lo.x, sc); acc.lo.y = __fmul_rn(acc.lo.y, sc); acc.lo.z = __fmul_rn(acc.lo.z, sc);
+    acc.lo.w = __fmul_rn(acc.lo.w, sc); acc.hi.x = __fmul_rn(acc.hi.x, sc); acc.hi.y = __fmul_rn(acc.hi.y, sc);
+    acc.hi.z = __fmul_rn(acc.hi.z, sc); acc.hi.w = __fmul_rn(acc.hi.w, sc);
+    return acc;
+}
+
+__device__ __forceinline__ float sum_grads1(const PeerTable &pt, const float *local, ptrdiff_t arena_pos, uint32_t i)
+{
+    float acc = 0.0f;
+#pragma unroll
+    for (int k = 0; k <= kMaxPeers; ++k) {
+        if (k <= pt.n_grad) {
+            const float t = grad_source(pt, local, arena_pos, k)[i];
+            acc = k == 0 ? t : __fadd_rn(acc, t);
+        }
+    }
+    return __fmul_rn(acc, pt.grad_scale);
+}
+
 // PEERS: besides the local arena, every updated parameter is stored into the same arena
 // position on every peer GPU (plain st.global to peer-mapped memory over NVLink), so the
 // all-gather of updated parameters rides along with the update, piece by piece.
 // HALF: 1 = the new parameter is also written, rounded to bf16, into the local bf16 copy of the
 // arena; 2 = and into every peer's bf16 copy (2 bytes per parameter over NVLink instead of 4
 // when PEERS is off).
-template <int OP, bool PEERS, int HALF>
+// GSUM: the gradient is summed over the ranks' gradient arenas (see sum_grads8).
+template <int OP, bool PEERS, int HALF, bool GSUM>
 __device__ __forceinline__ void update_chunk(const FatChunk &ch, const StepScalars &s, const PeerTable &pt)
 {
     constexpr bool kHasS1 = (OP != OP_SGD);
@@ -134,7 +182,8 @@ __device__ __forceinline__ void update_chunk(const FatChunk &ch, const StepScala
     float *__restrict__ s2 = kHasS2 ? ch.s2 : nullptr;
     const uint32_t n = ch.len;
 
-    const ptrdiff_t arena_pos = (PEERS || HALF) ? (p - pt.local_base) : 0;  // element offset inside the arena
+    const ptrdiff_t arena_pos = (PEERS || HALF || GSUM) ? (p - pt.local_base) : 0;  // element offset inside the arena
+    const float *g_arena = g - arena_pos;  // this rank's gradient arena (same layout as the parameters)
 
     uintptr_t align_bits = reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g);
     if (kHasS1) align_bits |= reinterpret_cast<uintptr_t>(s1);
@@ -149,7 +198,7 @@ __device__ __forceinline__ void update_chunk(const FatChunk &ch, const StepScala
         Vec8 *__restrict__ b8 = reinterpret_cast<Vec8 *>(s2);
         for (uint32_t i = threadIdx.x; i < n8; i += kThreads) {
             Vec8 vp = ld_vec8(p8 + i), va, vb;
-            const Vec8 vg = ld_vec8(g8 + i);
+            const Vec8 vg = GSUM ? sum_grads8(pt, g_arena, arena_pos, i) : ld_vec8(g8 + i);
             if (kHasS1) va = ld_vec8(a8 + i);
             if (kHasS2) vb = ld_vec8(b8 + i);
             update_vec<OP>(vp.lo, vg.lo, va.lo, vb.lo, s);
@@ -182,7 +231,15 @@ __device__ __forceinline__ void update_chunk(const FatChunk &ch, const StepScala
         float4 *__restrict__ b4 = reinterpret_cast<float4 *>(s2);
         for (uint32_t i = threadIdx.x; i < n4; i += kThreads) {
             float4 vp = __ldcs(p4 + i), va, vb;
-            const float4 vg = __ldcs(g4 + i);
+            float4 vg;
+            if (GSUM) {
+                vg.x = sum_grads1(pt, g_arena, arena_pos, 4 * i);
+                vg.y = sum_grads1(pt, g_arena, arena_pos, 4 * i + 1);
+                vg.z = sum_grads1(pt, g_arena, arena_pos, 4 * i + 2);
+                vg.w = sum_grads1(pt, g_arena, arena_pos, 4 * i + 3);
+            } else {
+                vg = __ldcs(g4 + i);
+            }
             if (kHasS1) va = __ldcs(a4 + i);
             if (kHasS2) vb = __ldcs(b4 + i);
             update_vec<OP>(vp, vg, va, vb, s);
@@ -209,7 +266,7 @@ __device__ __forceinline__ void update_chunk(const FatChunk &ch, const StepScala
     // ragged tail (n mod 8 / n mod 4) or a chunk whose pointers are not 16-byte aligned
     for (uint32_t i = done + threadIdx.x; i < n; i += kThreads) {
         float vp = p[i], va = 0.0f, vb = 0.0f;
-        const float vg = g[i];
+        const float vg = GSUM ? sum_grads1(pt, g_arena, arena_pos, i) : g[i];
         if (kHasS1) va = s1[i];
         if (kHasS2) vb = s2[i];
         update_one<OP>(vp, vg, va, vb, s);
@@ -236,8 +293,8 @@ __device__ __forceinline__ void update_chunk(const FatChunk &ch, const StepScala
 // CHECK_PRESENT = false is the common case (every tensor has a gradient): the descriptor of
 // the next chunk is fetched while the current one streams, so no dependent-load latency
 // sits between chunks.  With CHECK_PRESENT the per-tensor flag is looked up as well.
-template <int OP, bool CHECK_PRESENT, bool PEERS, int HALF>
-__global__ void __launch_bounds__(kThreads, kCtasPerSmMax)
+template <int OP, bool CHECK_PRESENT, bool PEERS, int HALF, bool GSUM>
+__global__ void __launch_bounds__(kThreads, GSUM ? 2 : kCtasPerSmMax)  // GSUM holds up to 8 vectors of gradients
 multi_tensor_update_kernel(const FatChunk *__restrict__ chunks, int64_t n_chunks,
                            const uint8_t *__restrict__ present, const StepScalars s, const PeerTable pt)
 {
@@ -250,7 +307,7 @@ multi_tensor_update_kernel(const FatChunk *__restrict__ chunks, int64_t n_chunks
         FatChunk nxt = cur;
         if (has_next) nxt = load_chunk(chunks + cn);  // in flight while `cur` is processed
         // `grad == None` -> skip: adam.rs:81-84, sgd.rs:75-78
-        if (!CHECK_PRESENT || present[cur.tensor] != 0) update_chunk<OP, PEERS, HALF>(cur, s, pt);
+        if (!CHECK_PRESENT || present[cur.tensor] != 0) update_chunk<OP, PEERS, HALF, GSUM>(cur, s, pt);
         if (!has_next) break;
         cur = nxt;
         c = cn;
@@ -321,16 +378,16 @@ static int ctas_per_sm(int op)
     return op == OP_ADAM ? 2 : op == OP_SGD_MOMENTUM ? kSgdMomentumCtasPerSm : kSgdCtasPerSm;
 }
 
-template <int OP, bool PEERS, int HALF>
+template <int OP, bool PEERS, int HALF, bool GSUM>
 static void launch_variant(unsigned grid, const FatChunk *d_chunks, int64_t n_chunks, const uint8_t *d_present,
                            bool all_present, const StepScalars &s, const PeerTable &pt, cudaStream_t stream)
 {
     if (all_present)
-        multi_tensor_update_kernel<OP, false, PEERS, HALF><<<grid, kThreads, 0, stream>>>(d_chunks, n_chunks,
-                                                                                         d_present, s, pt);
+        multi_tensor_update_kernel<OP, false, PEERS, HALF, GSUM><<<grid, kThreads, 0, stream>>>(d_chunks, n_chunks,
+                                                                                               d_present, s, pt);
     else
-        multi_tensor_update_kernel<OP, true, PEERS, HALF><<<grid, kThreads, 0, stream>>>(d_chunks, n_chunks,
-                                                                                        d_present, s, pt);
+        multi_tensor_update_kernel<OP, true, PEERS, HALF, GSUM><<<grid, kThreads, 0, stream>>>(d_chunks, n_chunks,
+                                                                                              d_present, s, pt);
 }
 
 template <int OP>
@@ -340,16 +397,26 @@ static void launch_op(unsigned grid, const FatChunk *d_chunks, int64_t n_chunks,
     const PeerTable pt = peers ? *peers : PeerTable{};
     const bool f32_peers = pt.n > 0;
     const int half = pt.half_local == nullptr ? 0 : pt.n_half > 0 ? 2 : 1;
-    if (half == 0) {
-        if (f32_peers) launch_variant<OP, true, 0>(grid, d_chunks, n_chunks, d_present, all_present, s, pt, stream);
-        else launch_variant<OP, false, 0>(grid, d_chunks, n_chunks, d_present, all_present, s, pt, stream);
+#define VB_LAUNCH(P, H, G) launch_variant<OP, P, H, G>(grid, d_chunks, n_chunks, d_present, all_present, s, pt, stream)
+    if (pt.n_grad > 0) {
+        // gradients summed over the ranks: built for the exchanges a data-parallel step uses
+        if (half == 2 && !f32_peers) VB_LAUNCH(false, 2, true);
+        else if (half == 2) VB_LAUNCH(true, 2, true);
+        else if (half == 1 && f32_peers) VB_LAUNCH(true, 1, true);
+        else if (half == 1) VB_LAUNCH(false, 1, true);
+        else if (f32_peers) VB_LAUNCH(true, 0, true);
+        else VB_LAUNCH(false, 0, true);
+    } else if (half == 0) {
+        if (f32_peers) VB_LAUNCH(true, 0, false);
+        else VB_LAUNCH(false, 0, false);
     } else if (half == 1) {
-        if (f32_peers) launch_variant<OP, true, 1>(grid, d_chunks, n_chunks, d_present, all_present, s, pt, stream);
-        else launch_variant<OP, false, 1>(grid, d_chunks, n_chunks, d_present, all_present, s, pt, stream);
+        if (f32_peers) VB_LAUNCH(true, 1, false);
+        else VB_LAUNCH(false, 1, false);
     } else {
-        if (f32_peers) launch_variant<OP, true, 2>(grid, d_chunks, n_chunks, d_present, all_present, s, pt, stream);
-        else launch_variant<OP, false, 2>(grid, d_chunks, n_chunks, d_present, all_present, s, pt, stream);
+        if (f32_peers) VB_LAUNCH(true, 2, false);
+        else VB_LAUNCH(false, 2, false);
     }
+#undef VB_LAUNCH
 }
 
 int launch_multi_tensor(int op, const FatChunk *d_chunks, int64_t n_chunks, const uint8_t *d_present,

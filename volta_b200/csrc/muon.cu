@@ -30,11 +30,56 @@ constexpr int kEwThreads = 256;
 // `direct_bf16` (may be null): tensors flagged there feed the tensor-core chain with the
 // *unnormalised* update (the 1/norm factors are applied by the first iteration's epilogues), so
 // this kernel writes the bf16 operand itself and the separate normalise pass is skipped.
-template <bool PARTIALS>
+// Data-parallel gradients (GSUM): the gradient of an element is the sum of every rank's value at
+// the same position of its gradient arena, added in rank order, then scaled (see PeerTable).
+struct GradPeers {
+    const float *base[kMaxPeers];  // peers' gradient arenas in rank order, without this rank
+    const float *local_base;       // this rank's gradient arena
+    int n, rank;
+    float scale;
+};
+__device__ __forceinline__ const float *grad_source(const GradPeers &gp, const float *local, ptrdiff_t pos, int k)
+{
+    const float *arena = k == gp.rank ? local : (k < gp.rank ? gp.base[k < kMaxPeers ? k : 0] : gp.base[k > 0 ? k - 1 : 0]);
+    return arena + pos;
+}
+__device__ __forceinline__ float4 sum_grads4(const GradPeers &gp, const float *local, ptrdiff_t pos, uint32_t i)
+{
+    float4 term[kMaxPeers + 1];
+#pragma unroll
+    for (int k = 0; k <= kMaxPeers; ++k)
+        if (k <= gp.n) term[k] = __ldcs(reinterpret_cast<const float4 *>(grad_source(gp, local, pos, k)) + i);
+    float4 acc = term[0];
+#pragma unroll
+    for (int k = 1; k <= kMaxPeers; ++k) {
+        if (k <= gp.n) {
+            acc.x = __fadd_rn(acc.x, term[k].x); acc.y = __fadd_rn(acc.y, term[k].y);
+            acc.z = __fadd_rn(acc.z, term[k].z); acc.w = __fadd_rn(acc.w, term[k].w);
+        }
+    }
+    acc.x = __fmul_rn(acc.x, gp.scale); acc.y = __fmul_rn(acc.y, gp.scale);
+    acc.z = __fmul_rn(acc.z, gp.scale); acc.w = __fmul_rn(acc.w, gp.scale);
+    return acc;
+}
+__device__ __forceinline__ float sum_grads1(const GradPeers &gp, const float *local, ptrdiff_t pos, uint32_t i)
+{
+    float acc = 0.0f;
+#pragma unroll
+    for (int k = 0; k <= kMaxPeers; ++k) {
+        if (k <= gp.n) {
+            const float t = grad_source(gp, local, pos, k)[i];
+            acc = k == 0 ? t : __fadd_rn(acc, t);
+        }
+    }
+    return __fmul_rn(acc, gp.scale);
+}
+
+template <bool PARTIALS, bool GSUM>
 __global__ void __launch_bounds__(kEwThreads)
 momentum_kernel(const TensorDesc *__restrict__ tensors, const ChunkDesc *__restrict__ chunks, int64_t n_chunks,
                 const uint8_t *__restrict__ present, float momentum, int nesterov, float *__restrict__ partials,
-                const uint8_t *__restrict__ direct_bf16, const float *upd_base, __nv_bfloat16 *__restrict__ xb_base)
+                const uint8_t *__restrict__ direct_bf16, const float *upd_base, __nv_bfloat16 *__restrict__ xb_base,
+                const GradPeers gp)
 {
     __shared__ float warp_sums[kEwThreads / 32];
     for (int64_t c = blockIdx.x; c < n_chunks; c += gridDim.x) {
@@ -47,10 +92,12 @@ momentum_kernel(const TensorDesc *__restrict__ tensors, const ChunkDesc *__restr
         const bool to_bf16 = direct_bf16 != nullptr && direct_bf16[ch.tensor] != 0;
         __nv_bfloat16 *__restrict__ xb = to_bf16 ? xb_base + (u - upd_base) : nullptr;
         const uint32_t n = ch.len;
+        const ptrdiff_t gpos = GSUM ? (g - gp.local_base) : 0;  // position inside the gradient arena
+        const float *g_arena = g - gpos;
         float local = 0.0f;
         const uint32_t n4 = n >> 2;  // chunk starts are 16-byte aligned by construction
         for (uint32_t i = threadIdx.x; i < n4; i += kEwThreads) {
-            const float4 g4 = __ldcs(reinterpret_cast<const float4 *>(g) + i);
+            const float4 g4 = GSUM ? sum_grads4(gp, g_arena, gpos, i) : __ldcs(reinterpret_cast<const float4 *>(g) + i);
             float4 v4 = __ldcs(reinterpret_cast<const float4 *>(v) + i);
             float4 u4;
             v4.x = __fmaf_rn(momentum, v4.x, g4.x);
@@ -78,7 +125,7 @@ momentum_kernel(const TensorDesc *__restrict__ tensors, const ChunkDesc *__restr
             if (PARTIALS) local += u4.x * u4.x + u4.y * u4.y + u4.z * u4.z + u4.w * u4.w;
         }
         for (uint32_t i = (n4 << 2) + threadIdx.x; i < n; i += kEwThreads) {
-            const float gv = g[i];
+            const float gv = GSUM ? sum_grads1(gp, g_arena, gpos, i) : g[i];
             const float vv = __fmaf_rn(momentum, v[i], gv);
             const float uv = nesterov ? __fadd_rn(__fmul_rn(momentum, vv), gv) : vv;
             v[i] = vv;
@@ -862,19 +909,34 @@ int muon_step(vb_optimizer *opt, uint32_t flags)
     VB_TRY(sync_present(opt));
     const int ew_grid = (int)std::min<int64_t>(std::max<int64_t>(s->n_chunks, 1), (int64_t)e->sm_count * 8);
     const bool fast_norm = opt->ns_mode == VB_NS_BF16;  // both f32 modes need the reference's ordered sum
+    ExchangePlan xp;
+    VB_TRY(plan_exchange(opt, flags, &xp));
+    const bool gsum = xp.pt.n_grad > 0;
+    if (gsum) {  // peers' gradients are read by the first kernel: every rank must have reached its step
+        prof_begin(e, VB_PHASE_EXCHANGE);
+        VB_TRY(comm_barrier(e));
+        prof_end(e, VB_PHASE_EXCHANGE);
+    }
     prof_begin(e, VB_PHASE_MUON_PRE);
     if (s->n_chunks > 0) {
         const uint8_t *direct = s->fold_norm ? s->d_fold_norm : nullptr;
-        if (fast_norm)
-            momentum_kernel<true><<<ew_grid, kEwThreads, 0, e->stream>>>(s->d_desc, s->d_chunks, s->n_chunks,
-                                                                          opt->d_present, opt->momentum,
-                                                                          opt->nesterov, s->d_partials, direct,
-                                                                          s->d_upd, s->d_xb[0]);
-        else
-            momentum_kernel<false><<<ew_grid, kEwThreads, 0, e->stream>>>(s->d_desc, s->d_chunks, s->n_chunks,
-                                                                           opt->d_present, opt->momentum,
-                                                                           opt->nesterov, s->d_partials, direct,
-                                                                           s->d_upd, s->d_xb[0]);
+        GradPeers gp{};
+        gp.local_base = opt->d_grad;
+        gp.n = xp.pt.n_grad;
+        gp.rank = xp.pt.rank;
+        gp.scale = xp.pt.grad_scale;
+        for (int r = 0; r < gp.n; ++r) gp.base[r] = xp.pt.grad_base[r];
+        // a one-rank engine asked for the mean or the sum of gradients: scale 1, nothing to add
+#define VB_MOMENTUM(P, G)                                                                                      \
+    momentum_kernel<P, G><<<ew_grid, kEwThreads, 0, e->stream>>>(s->d_desc, s->d_chunks, s->n_chunks,      \
+                                                                opt->d_present, opt->momentum, opt->nesterov, \
+                                                                s->d_partials, direct, s->d_upd, s->d_xb[0], gp)
+        if (fast_norm) {
+            if (gsum) VB_MOMENTUM(true, true); else VB_MOMENTUM(true, false);
+        } else {
+            if (gsum) VB_MOMENTUM(false, true); else VB_MOMENTUM(false, false);
+        }
+#undef VB_MOMENTUM
         VB_CUDA(cudaGetLastError());
         e->launches += 1;
     }
@@ -917,9 +979,7 @@ int muon_step(vb_optimizer *opt, uint32_t flags)
             VB_CUDA(cudaMemcpyAsync(s->h_error, s->d_error, sizeof(int), cudaMemcpyDeviceToHost, e->stream));
     }
     prof_end(e, VB_PHASE_MUON_PRE);  // no-op if already closed (no Newton-Schulz matrices)
-    ExchangePlan xp;
-    VB_TRY(plan_exchange(opt, flags, &xp));
-    if (xp.fused) {  // see vb_optimizer_step_ex: nobody is written to before it has reached its step
+    if (xp.fused && !gsum) {  // see vb_optimizer_step_ex: nobody is written to before it has reached its step
         prof_begin(e, VB_PHASE_EXCHANGE);
         VB_TRY(comm_barrier(e));
         prof_end(e, VB_PHASE_EXCHANGE);

@@ -69,10 +69,14 @@ constexpr int kMaxPeers = 7;
 struct PeerTable {
     float *base[kMaxPeers];
     uint16_t *half_base[kMaxPeers];
+    const float *grad_base[kMaxPeers];  // peers' gradient arenas, in rank order without this rank
     const float *local_base;
     uint16_t *half_local;
     int n;
     int n_half;
+    int n_grad;        // > 0: the gradient of an element is the sum over all ranks, in rank order
+    int rank;          // this rank's place in that order
+    float grad_scale;  // the sum is multiplied by this (1, or 1 / world for the mean)
 };
 
 // Scalars of one step, computed on the host in f32 exactly as the reference does.

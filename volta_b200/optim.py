@@ -20,11 +20,12 @@ from typing import Iterable, List, Optional, Sequence
 import numpy as np
 
 from . import _lib
-from ._lib import (VB_NS_BF16, VB_NS_F32, VB_NS_F32_TC, VB_STEP_DEFAULT, VB_STEP_EXCHANGE_BF16, VB_STEP_NO_EXCHANGE,
+from ._lib import (VB_NS_BF16, VB_NS_F32, VB_NS_F32_TC, VB_STEP_DEFAULT, VB_STEP_EXCHANGE_BF16, VB_STEP_MEAN_GRADS,
+                   VB_STEP_NO_EXCHANGE, VB_STEP_REDUCE_GRADS,
                    VoltaB200Error, call)
 
 __all__ = ["Engine", "Tensor", "Adam", "SGD", "Muon", "default_engine", "multi_tensor_step", "accumulate_grad",
-           "VoltaB200Error", "VB_NS_F32", "VB_NS_BF16", "VB_NS_F32_TC", "VB_STEP_NO_EXCHANGE", "VB_STEP_EXCHANGE_BF16"]
+           "VoltaB200Error", "VB_NS_F32", "VB_NS_BF16", "VB_NS_F32_TC", "VB_STEP_NO_EXCHANGE", "VB_STEP_EXCHANGE_BF16", "VB_STEP_REDUCE_GRADS", "VB_STEP_MEAN_GRADS"]
 
 
 def _f32(a) -> np.ndarray:
@@ -315,6 +316,20 @@ class _Optimizer:
         if len(blob) != 64 * len(handles):
             raise ValueError("every handle must be 64 bytes")
         call("vb_optimizer_open_peers", self._h, C.c_char_p(blob), len(handles))
+
+    # -- data-parallel gradients: reduce-scatter fused into the update kernel's loads -------
+    def ipc_handle_grads(self) -> bytes:
+        buf = C.create_string_buffer(64)
+        call("vb_optimizer_ipc_handle_grads", self._h, buf)
+        return buf.raw
+
+    def open_peers_grads(self, handles: Sequence[bytes]) -> None:
+        """``handles[r]`` = rank r's ``ipc_handle_grads()``; afterwards ``step(VB_STEP_REDUCE_GRADS)``
+        (or ``VB_STEP_MEAN_GRADS``) updates with the sum (mean) of all ranks' gradients."""
+        blob = b"".join(handles)
+        if len(blob) != 64 * len(handles):
+            raise ValueError("every handle must be 64 bytes")
+        call("vb_optimizer_open_peers_grads", self._h, C.c_char_p(blob), len(handles))
 
     # -- bf16 copies of the parameters, written next to the f32 master ----------------------
     def enable_bf16_params(self) -> None:
