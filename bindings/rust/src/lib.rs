@@ -46,6 +46,13 @@ pub mod ffi {
     pub const VB_NS_F32: c_int = 0;
     pub const VB_NS_BF16: c_int = 1;
     pub const VB_NS_F32_TC: c_int = 2;
+    /// Flags of `vb_optimizer_step_ex`.
+    pub const VB_STEP_DEFAULT: u32 = 0;
+    pub const VB_STEP_NO_EXCHANGE: u32 = 1;
+    pub const VB_STEP_EXCHANGE_BF16: u32 = 2;
+    pub const VB_STEP_REDUCE_GRADS: u32 = 4;
+    pub const VB_STEP_MEAN_GRADS: u32 = 8;
+    pub const VB_IPC_HANDLE_BYTES: usize = 64;
 
     unsafe extern "C" {
         pub fn vb_last_error() -> *const c_char;
@@ -71,6 +78,19 @@ pub mod ffi {
         pub fn vb_optimizer_set_grad_present(opt: *mut vb_optimizer, tensor: i64, present: c_int) -> c_int;
         pub fn vb_optimizer_step(opt: *mut vb_optimizer) -> c_int;
         pub fn vb_optimizer_zero_grad(opt: *mut vb_optimizer) -> c_int;
+        // one process per GPU: communicator, sharded step, fused exchanges (no counterpart in Volta)
+        pub fn vb_comm_unique_id(id128: *mut c_void) -> c_int;
+        pub fn vb_engine_comm_init(engine: *mut vb_engine, id128: *const c_void, rank: c_int, world: c_int) -> c_int;
+        pub fn vb_optimizer_step_ex(opt: *mut vb_optimizer, flags: u32) -> c_int;
+        pub fn vb_optimizer_ipc_handle(opt: *mut vb_optimizer, handle64: *mut c_void) -> c_int;
+        pub fn vb_optimizer_open_peers(opt: *mut vb_optimizer, handles: *const c_void, n_handles: c_int) -> c_int;
+        pub fn vb_optimizer_ipc_handle_grads(opt: *mut vb_optimizer, handle64: *mut c_void) -> c_int;
+        pub fn vb_optimizer_open_peers_grads(opt: *mut vb_optimizer, handles: *const c_void, n_handles: c_int) -> c_int;
+        pub fn vb_optimizer_enable_bf16_params(opt: *mut vb_optimizer) -> c_int;
+        pub fn vb_optimizer_param_bf16_ptr(opt: *mut vb_optimizer, tensor: i64, out: *mut *mut c_void) -> c_int;
+        pub fn vb_optimizer_download_params_bf16(opt: *mut vb_optimizer, tensor: i64, host: *mut u16, n: i64) -> c_int;
+        pub fn vb_optimizer_ipc_handle_bf16(opt: *mut vb_optimizer, handle64: *mut c_void) -> c_int;
+        pub fn vb_optimizer_open_peers_bf16(opt: *mut vb_optimizer, handles: *const c_void, n_handles: c_int) -> c_int;
         pub fn vb_multi_tensor_step(
             engine: *mut vb_engine, hp: *const vb_optimizer_step_params, n_tensors: i64, sizes: *const i64,
             params: *const *mut c_void, grads: *const *const c_void, state1: *const *mut c_void,
