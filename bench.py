@@ -159,7 +159,7 @@ def run_reference(args):
         "n_gpus": args.gpus, "steps": len(times), "warmup": min(args.warmup, 1), "ms_per_step": sec * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
-        "config": {"workload": "c3_transformer_adam: Adam wd=0.01, 157 tensors, 109602816 f32 params",
+        "config": {"workload": C3_WORKLOAD,
                    "host_cores_available": os.cpu_count()},
         "cpu_baseline": {"value": value, "unit": "params/s", "cores": cores, "kind": "port",
                          "sample": f"{len(times)} full steps of the whole workload, 1 thread "
@@ -174,6 +174,10 @@ def run_reference(args):
 # ---------------------------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------------------------
+
+C3_WORKLOAD = ("c3_transformer_adam: Adam lr=1e-3 betas=(0.9,0.999) eps=1e-8 wd=0.01, 157 tensors, "
+               "109602816 f32 params")
+
 
 def gather_handles(mine: bytes, world: int, dev):
     """Every rank's 64-byte CUDA IPC handle, in rank order (torch.distributed is the transport)."""
@@ -348,8 +352,7 @@ def run_ours(args):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
-        "config": {"workload": "c3_transformer_adam: Adam lr=1e-3 betas=(0.9,0.999) eps=1e-8 wd=0.01, "
-                               "157 tensors, 109602816 f32 params",
+        "config": {"workload": C3_WORKLOAD,
                    "l2": "inputs larger than L2 (1.75 GB of theta/g/m/v per step vs 126 MB)",
                    "parallelism": f"zero1x{world}" if world > 1 else "single",
                    "exchange": ("none" if world == 1 else
