@@ -876,7 +876,10 @@ int muon_init(vb_optimizer *opt)
                     ++gram_all;
                     if (bm == bn && n0 < m0) continue;
                     ++gram_used;
-                    gram_tiles.push_back(GemmTile{pidx, m0, n0, (bm == bn && n0 > m0) ? GEMM_TILE_MIRROR : 0});
+                    int flags = 0;
+                    if (bm == bn && n0 > m0) flags |= GEMM_TILE_MIRROR;
+                    if (bm == bn && n0 == m0 && planes == 1) flags |= GEMM_TILE_B_IS_A;
+                    gram_tiles.push_back(GemmTile{pidx, m0, n0, flags});
                 }
             for (int m0 = 0; m0 < r; m0 += bm)
                 for (int n0 = 0; n0 < c; n0 += bn) upd_tiles.push_back(GemmTile{pidx, m0, n0, 0});

@@ -10,7 +10,10 @@
 
 namespace vb {
 
-enum GemmTileFlags { GEMM_TILE_MIRROR = 1 };  // symmetric output: also store this tile transposed
+enum GemmTileFlags {
+    GEMM_TILE_MIRROR = 1,  // symmetric output: also store this tile transposed
+    GEMM_TILE_B_IS_A = 2   // diagonal tile of X^T X (or X X^T): the rows of B are the rows of A, staged once
+};
 
 struct GemmTile {
     int32_t problem;

@@ -559,6 +559,7 @@ struct TileInfo {
     const TcGemmProblem *p;
     int m0, n0, k_blocks, a_mode, b_mode, n_terms;
     bool mirror;    // symmetric product: this off-diagonal tile is also stored transposed
+    bool b_is_a;    // diagonal tile of a symmetric product: B's rows are A's rows, staged once
     bool skipped;   // gradient absent: nothing to do
     bool withhold;  // test hook (TcGemmProblem::withhold_loads): the producer stages nothing
 };
@@ -572,6 +573,7 @@ __device__ __forceinline__ TileInfo fetch_tile(const TcGemmProblem *problems, co
     ti.skipped = true;
     ti.withhold = false;
     ti.mirror = false;
+    ti.b_is_a = false;
     if (t < n_tiles) {
         const GemmTile tile = tiles[t];
         const TcGemmProblem *p = problems + tile.problem;
@@ -579,6 +581,7 @@ __device__ __forceinline__ TileInfo fetch_tile(const TcGemmProblem *problems, co
         ti.m0 = tile.m0;
         ti.n0 = tile.n0;
         ti.mirror = (tile.flags & GEMM_TILE_MIRROR) != 0;
+        ti.b_is_a = (tile.flags & GEMM_TILE_B_IS_A) != 0;
         ti.k_blocks = (p->K + BK - 1) / BK;
         ti.a_mode = p->a_mode;
         ti.b_mode = p->b_mode;
@@ -656,6 +659,9 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
                 if (ti.skipped) continue;
                 const int a_row0 = ti.m0 + (int)cta_rank * BM;         // this CTA's rows of A
                 const int b_row0 = ti.n0 + (int)cta_rank * C::kBRows;  // this CTA's rows of B
+                // diagonal tile of a symmetric product (pair kernel, plain bf16): each CTA's 128 rows of
+                // B are its 128 rows of A, so they are fetched once and the MMA reads A's slot twice
+                const bool alias_b = kCtas == 2 && !kSplit && ti.b_is_a;
                 const int n_terms = kSplit ? ti.n_terms : 1;
                 const int n_slots = ti.k_blocks * n_terms;  // every (k block, plane pair) fills one ring slot
                 int kb = 0, term = 0;
@@ -677,10 +683,11 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
                         // Nothing is staged and no bytes are announced: the consumers' bounded waits
                         // (and, a ring later, this thread's own) run out.  Used by the expiry test.
                     } else if (lane == 0) {
-                        if (cta_rank == 0) mbar_expect_tx(&bars->full[stage], kCtas * C::kStageBytes);
+                        if (cta_rank == 0)
+                            mbar_expect_tx(&bars->full[stage], alias_b ? kCtas * kRows128Bytes : kCtas * C::kStageBytes);
                         load_rows128<kCtas, kSplit>(sa, &ti.p->map_a, ti.a_mode, a_row0, k0, term_plane_a(n_terms, term),
                                             full_bar);
-                    } else {
+                    } else if (!alias_b) {
 #pragma unroll
                         for (int j = 0; j < C::kBRows / 128; ++j)
                             load_rows128<kCtas, kSplit>(sb + j * kRows128Bytes, &ti.p->map_b, ti.b_mode, b_row0 + j * 128, k0,
@@ -731,7 +738,7 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
                     }
                     tcgen05_fence_after();
                     const uint32_t sa = smem_u32(smem + (size_t)stage * C::kStageBytes);
-                    const uint32_t sb = sa + kRows128Bytes;
+                    const uint32_t sb = (kCtas == 2 && !kSplit && ti.b_is_a) ? sa : sa + kRows128Bytes;
 #pragma unroll
                     for (int kk = 0; kk < BK / UMMA_K; ++kk)
                         tcgen05_mma_bf16<kCtas>(tmem_d, operand_desc(sa, ti.a_mode, kk), operand_desc(sb, ti.b_mode, kk),
