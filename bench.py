@@ -579,9 +579,9 @@ NCU_ADAM_C3_DRAM_BYTES_PER_LAUNCH = 3.0164e9
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of ns_gemm_tc_kernel<2, 0> on 4 layers of the Muon
-# workload (16 matrices): mean of a Gram launch (110.2 MB) and an update launch (205.3 MB), from the ncu
+# workload (16 matrices): mean of a Gram launch (110.4 MB) and an update launch (206.8 MB), from the ncu
 # capture summarised in profiles/muon_c4_ns_gemm_tc.md
-NCU_MUON_4LAYER_DRAM_BYTES_PER_LAUNCH = 157.7e6
+NCU_MUON_4LAYER_DRAM_BYTES_PER_LAUNCH = 158.6e6
 
 
 def traffic_from_profile():
