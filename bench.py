@@ -6,7 +6,7 @@
 One "step" is one optimizer step() over the whole parameter set of the workload with
 the gradients already resident in HBM.  Headline workload: Adam (weight decay 0.01) on
 the 12-layer d=768 transformer parameter set, 109 602 816 f32 parameters (28 B/param of
-HBM traffic).  Rank 0 prints ONE JSON line; see README/DESIGN for the meaning of keys.
+HBM traffic).  Rank 0 prints ONE JSON line.
 
 N > 1 is launched by torch.distributed.run, one rank per GPU: the arena is sharded
 ZeRO-1 style (each rank updates arena/N elements) and step() ends with the NCCL

@@ -1,6 +1,6 @@
 """GPU parity of the fused multi-tensor Adam / SGD path against the CPU oracle.
 
-Tolerances (BASELINE north star): max relative error on params, m and v <= 1e-6 after one
+Tolerances: max relative error on params, m and v <= 1e-6 after one
 step and <= 1e-5 after 100 steps.  The kernels are written to be bit-identical to the
 reference's CPU arithmetic, so most cases assert exact equality, which implies both.
 Everything goes through the C ABI (the ctypes mirror in volta_b200.optim).

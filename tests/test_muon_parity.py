@@ -1,6 +1,6 @@
 """GPU parity of Muon (momentum, normalisation, Newton-Schulz, apply) against the oracle.
 
-Tolerances (BASELINE north star), per matrix, on the Newton-Schulz output ("update"):
+Tolerances, per matrix, on the Newton-Schulz output ("update"):
 relative Frobenius error <= 1e-5 on the f32 path and <= 2e-2 on the bf16 tensor-core path.
 The oracle's contraction restates matrixmultiply's blocking; the reference itself holds no
 numeric test for Muon, so these compare against the restatement (and, for context, against
