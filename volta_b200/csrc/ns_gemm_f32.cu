@@ -42,6 +42,52 @@ __device__ __forceinline__ float load_b(const F32GemmProblem &p, int k, int n)
     return p.B[(int64_t)k * p.ldb + n];
 }
 
+// Register-staged copy of the next k tile on the aligned interior path: the global loads are
+// issued before the multiply-add block of the current tile and written to shared memory
+// after it, so their latency overlaps the arithmetic.
+struct Staged {
+    float4 a[2], b[2];
+};
+
+__device__ __forceinline__ void fetch_tiles(const F32GemmProblem &p, int m0, int n0, int k0, Staged &r)
+{
+    const int tid = threadIdx.x;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int idx = tid + i * kThreads;  // 0..511
+        if (p.trans_a) {
+            const int k = idx >> 5, m4 = (idx & 31) << 2;
+            r.a[i] = __ldg(reinterpret_cast<const float4 *>(p.A + (int64_t)(k0 + k) * p.lda + m0 + m4));
+        } else {
+            const int m = idx >> 2, k4 = (idx & 3) << 2;
+            r.a[i] = __ldg(reinterpret_cast<const float4 *>(p.A + (int64_t)(m0 + m) * p.lda + k0 + k4));
+        }
+        const int k = idx >> 5, n4 = (idx & 31) << 2;
+        r.b[i] = __ldg(reinterpret_cast<const float4 *>(p.B + (int64_t)(k0 + k) * p.ldb + n0 + n4));
+    }
+}
+
+__device__ __forceinline__ void commit_tiles(const F32GemmProblem &p, const Staged &r, Smem &s, int buf)
+{
+    const int tid = threadIdx.x;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int idx = tid + i * kThreads;
+        if (p.trans_a) {
+            const int k = idx >> 5, m4 = (idx & 31) << 2;
+            *reinterpret_cast<float4 *>(&s.a[buf][k][m4]) = r.a[i];
+        } else {
+            const int m = idx >> 2, k4 = (idx & 3) << 2;
+            s.a[buf][k4 + 0][m] = r.a[i].x;
+            s.a[buf][k4 + 1][m] = r.a[i].y;
+            s.a[buf][k4 + 2][m] = r.a[i].z;
+            s.a[buf][k4 + 3][m] = r.a[i].w;
+        }
+        const int k = idx >> 5, n4 = (idx & 31) << 2;
+        *reinterpret_cast<float4 *>(&s.b[buf][k][n4]) = r.b[i];
+    }
+}
+
 __device__ __forceinline__ void load_tiles(const F32GemmProblem &p, int m0, int n0, int k0, Smem &s, int buf,
                                            bool fast)
 {
@@ -87,11 +133,18 @@ __device__ __forceinline__ void load_tiles(const F32GemmProblem &p, int m0, int 
     }
 }
 
-__global__ void __launch_bounds__(kThreads)
+// Dynamic shared memory: the staging buffers, then one running total per accumulator and
+// thread ([i][j][thread]: conflict free).  The totals live there because they are touched
+// once per 256 values of k, while keeping them in registers would halve the occupancy.
+constexpr size_t kSmemBytes = sizeof(Smem) + (size_t)TM * TN * kThreads * sizeof(float);
+
+__global__ void __launch_bounds__(kThreads, 2)
 ns_gemm_f32_kernel(const F32GemmProblem *__restrict__ problems, const GemmTile *__restrict__ tiles, int n_tiles,
                    const uint8_t *__restrict__ present)
 {
-    __shared__ Smem s;
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    Smem &s = *reinterpret_cast<Smem *>(smem_raw);
+    float *total = reinterpret_cast<float *>(smem_raw + sizeof(Smem)) + threadIdx.x;  // [(i * TN + j) * kThreads]
     const int tid = threadIdx.x;
     const int tx = tid & 15, ty = tid >> 4;  // 16 x 16 threads, each an 8 x 8 block of C
 
@@ -105,12 +158,11 @@ ns_gemm_f32_kernel(const F32GemmProblem *__restrict__ problems, const GemmTile *
                              ((reinterpret_cast<uintptr_t>(p.B) & 15) == 0);
         const bool full_mn = aligned && (m0 + BM <= p.M) && (n0 + BN <= p.N);
 
-        float total[TM][TN];
         float acc[TM][TN];
 #pragma unroll
         for (int i = 0; i < TM; ++i)
 #pragma unroll
-            for (int j = 0; j < TN; ++j) total[i][j] = acc[i][j] = 0.0f;
+            for (int j = 0; j < TN; ++j) acc[i][j] = 0.0f;
 
         const int k_tiles = (p.K + BK - 1) / BK;
         __syncthreads();  // previous tile's readers are done with smem
@@ -118,8 +170,11 @@ ns_gemm_f32_kernel(const F32GemmProblem *__restrict__ problems, const GemmTile *
         __syncthreads();
         for (int kt = 0; kt < k_tiles; ++kt) {
             const int buf = kt & 1;
-            if (kt + 1 < k_tiles)
-                load_tiles(p, m0, n0, (kt + 1) * BK, s, buf ^ 1, full_mn && (kt + 2) * BK <= p.K);
+            const bool has_next = kt + 1 < k_tiles;
+            const bool next_fast = has_next && full_mn && (kt + 2) * BK <= p.K;
+            Staged staged;
+            if (next_fast) fetch_tiles(p, m0, n0, (kt + 1) * BK, staged);  // lands while this tile is multiplied
+            else if (has_next) load_tiles(p, m0, n0, (kt + 1) * BK, s, buf ^ 1, false);
             const int k0 = kt * BK;
             // a new 256-block starts: fold the finished chain into the running result
             if (k0 > 0 && (k0 % kKBlock) == 0) {
@@ -128,7 +183,8 @@ ns_gemm_f32_kernel(const F32GemmProblem *__restrict__ problems, const GemmTile *
                 for (int i = 0; i < TM; ++i)
 #pragma unroll
                     for (int j = 0; j < TN; ++j) {
-                        total[i][j] = first ? acc[i][j] : __fadd_rn(total[i][j], acc[i][j]);
+                        float *slot = total + (i * TN + j) * kThreads;
+                        *slot = first ? acc[i][j] : __fadd_rn(*slot, acc[i][j]);
                         acc[i][j] = 0.0f;
                     }
             }
@@ -148,6 +204,7 @@ ns_gemm_f32_kernel(const F32GemmProblem *__restrict__ problems, const GemmTile *
 #pragma unroll
                     for (int j = 0; j < TN; ++j) acc[i][j] = __fmaf_rn(av[i], bv[j], acc[i][j]);
             }
+            if (next_fast) commit_tiles(p, staged, s, buf ^ 1);
             __syncthreads();
         }
         const bool single_block = (p.K <= kKBlock);
@@ -162,7 +219,7 @@ ns_gemm_f32_kernel(const F32GemmProblem *__restrict__ problems, const GemmTile *
                 const int n = n0 + (j < 4 ? tx * 4 + j : 64 + tx * 4 + (j - 4));
                 if (n >= p.N) continue;
                 // zero-padded k beyond K adds fma(0, 0, acc) = acc: no effect on the chain
-                float r = single_block ? acc[i][j] : __fadd_rn(total[i][j], acc[i][j]);
+                float r = single_block ? acc[i][j] : __fadd_rn(total[(i * TN + j) * kThreads], acc[i][j]);
                 if (p.K == 0) r = 0.0f;
                 if (p.epilogue == F32_EPI_THREE_I_MINUS)
                     r = (m == n) ? __fsub_rn(3.0f, r) : -r;  // muon.rs:76-89
@@ -182,7 +239,9 @@ int launch_ns_gemm_f32(const F32GemmProblem *d_problems, const GemmTile *d_tiles
     if (n_tiles <= 0) return VB_OK;
     int grid = sm_count * 2;
     if (grid > n_tiles) grid = n_tiles;
-    ns_gemm_f32_kernel<<<grid, kThreads, 0, stream>>>(d_problems, d_tiles, n_tiles, d_present);
+    // the attribute is per device; setting it again is cheap next to a launch of this size
+    VB_CUDA(cudaFuncSetAttribute(ns_gemm_f32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+    ns_gemm_f32_kernel<<<grid, kThreads, kSmemBytes, stream>>>(d_problems, d_tiles, n_tiles, d_present);
     VB_CUDA(cudaGetLastError());
     return VB_OK;
 }
