@@ -475,7 +475,7 @@ def run_muon(args, eng, world, rank, dev, barrier, max_over_ranks, peaks):
     out = {}
     for mode_name, mode, steps in (("bf16", VB_NS_BF16, max(3, min(args.steps, 20))),
                                    ("f32_tc", VB_NS_F32_TC, max(3, min(args.steps, 5))), ("f32", VB_NS_F32, 2)):
-        if mode_name == "f32" and (args.skip_muon_f32 or args.only_muon):
+        if mode_name == "f32" and (args.skip_muon_f32 or (args.only_muon and not args.muon_f32)):
             continue
         if mode_name == "f32_tc" and args.only_muon and not args.muon_f32_tc:
             continue
@@ -604,6 +604,7 @@ def main():
                     help="N > 1: updated parameters reach the other ranks by NVLink peer stores fused into the "
                          "update kernel (default) or by an NCCL all-gather after it")
     ap.add_argument("--muon-f32-tc", action="store_true", help="with --only-muon: also time the f32-accurate TC path")
+    ap.add_argument("--muon-f32", action="store_true", help="with --only-muon: also time the bit-faithful f32 path")
     ap.add_argument("--muon-layers", type=int, default=24, help="profiling runs: fewer layers of the Muon set")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
