@@ -506,6 +506,9 @@ def run_muon(args, eng, world, rank, dev, barrier, max_over_ranks, peaks):
         stream = torch.cuda.ExternalStream(eng.stream, device=dev)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         launches0 = eng.launch_count
+        sampler = ClockSampler(dev.index) if rank == 0 and mode_name == "bf16" else None
+        if sampler is not None:
+            sampler.start()
         barrier()
         e0.record(stream)
         for _ in range(steps):
@@ -513,6 +516,7 @@ def run_muon(args, eng, world, rank, dev, barrier, max_over_ranks, peaks):
         e1.record(stream)
         eng.synchronize()
         barrier()
+        muon_clocks = sampler.stop() if sampler is not None else None
         step_ms = max_over_ranks(e0.elapsed_time(e1) / steps)
         ns_ms = max_over_ranks(eng.profile("muon_ns")[0] / steps)
         pre_ms = eng.profile("muon_pre")[0] / steps
@@ -539,6 +543,8 @@ def run_muon(args, eng, world, rank, dev, barrier, max_over_ranks, peaks):
             "reference_formulation_flops_per_step": sum(4.0 * r * c * c * h["ns_steps"] for r, c in wl.shapes),
             "gpu_launches": int(eng.launch_count - launches0),
         }
+        if muon_clocks is not None:
+            out[mode_name]["clocks"] = muon_clocks
         if mode_name == "bf16" and world > 1:
             from volta_b200 import VB_STEP_EXCHANGE_BF16
             opt.enable_bf16_params()
