@@ -60,7 +60,7 @@ constexpr uint32_t kDefaultWaitLimit = 1u << 22;         // mbarrier polls befor
 
 template <int kCtas>
 struct Cfg {
-    static constexpr int kStages = kCtas == 2 ? 6 : 4;
+    static constexpr int kStages = kCtas == 2 ? 6 : 4;  // 4..7 slots measure the same: operand bandwidth, not latency, is the limit
     static constexpr int kBRows = BN / kCtas;                         // rows of B staged by one CTA
     static constexpr int kStageBytes = kRows128Bytes + kBRows * BK * 2;
     static constexpr int kTileM = BM * kCtas;
