@@ -538,8 +538,8 @@ def run_muon(args, eng, world, rank, dev, barrier, max_over_ranks, peaks):
             "params_per_s": wl.total / (step_ms * 1e-3), "steps": steps,
             "executed_flops_per_step": flops_total,
             "note": {"bf16": "tcgen05 bf16, short-side Gram, symmetric Gram computed on and above the diagonal only", "f32": "CUDA-core FFMA, bit-identical to the CPU arithmetic",
-                     "f32_tc": "tcgen05, operands split into three bf16 planes (six products per product); "
-                               "ns_tflops counts executed bf16 tensor FLOPs"}[mode_name],
+                     "f32_tc": "tcgen05, operands held as two f16 planes (three products per product); "
+                               "ns_tflops counts executed f16 tensor FLOPs"}[mode_name],
             "reference_formulation_flops_per_step": sum(4.0 * r * c * c * h["ns_steps"] for r, c in wl.shapes),
             "gpu_launches": int(eng.launch_count - launches0),
         }

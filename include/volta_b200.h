@@ -68,10 +68,13 @@ typedef enum vb_ns_mode {
     /* bf16 operands on the tcgen05 tensor cores, f32 accumulation in TMEM.
      * Target: relative Frobenius error <= 2e-2 per matrix. */
     VB_NS_BF16 = 1,
-    /* f32-accurate on the tensor cores: every operand is split into three bf16 pieces
-     * (24 significand bits) and each product is six tcgen05 bf16 products accumulated in f32;
+    /* f32-accurate on the tensor cores: every operand is held as two f16 pieces of the value
+     * scaled by 2^15 (22 significand bits; Newton-Schulz operands are bounded by 1 once the
+     * update is normalised) and each product is three tcgen05 f16 products accumulated in f32;
      * the sum of squares keeps the reference's sequential order.  Same target as VB_NS_F32
-     * (<= 1e-5) at tensor-core speed, but not bit-identical to the CPU arithmetic. */
+     * (<= 1e-5) at tensor-core speed, but not bit-identical to the CPU arithmetic.  An update
+     * whose norm is at most 1e-8 is not normalised by the reference (src/nn/optim/muon.rs:60);
+     * such an update is below the range of the f16 pieces and comes out as zero here. */
     VB_NS_F32_TC = 2
 } vb_ns_mode;
 

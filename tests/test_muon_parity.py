@@ -228,11 +228,11 @@ def test_bf16_path_c4_layer_shapes(oracle, engine):
     opt.close()
 
 
-# ---- f32-accurate tensor-core path (three-way bf16 split) ---------------------------------------
+# ---- f32-accurate tensor-core path (two f16 planes per operand) ----------------------------------
 
 @pytest.mark.parametrize("shapes", [[(256, 128)], [(128, 384), (512, 512)], [(200, 72), (64, 36), (50,)], [(1032, 264)]])
 def test_f32_tc_path_meets_f32_tolerance(oracle, engine, shapes):
-    """VB_NS_F32_TC: operands split into three bf16 planes, six tensor-core products per product,
+    """VB_NS_F32_TC: operands held as two f16 planes, three tensor-core products per product,
     ordered sum of squares.  Same 1e-5 bound as the bit-faithful path (shapes whose rows are
     not 16-byte aligned in bf16 run the bit-faithful kernels inside the same optimizer)."""
     from volta_b200 import VB_NS_F32_TC

@@ -365,7 +365,7 @@ sumsq_ordered_kernel(const TensorDesc *__restrict__ tensors, const int32_t *__re
 // x = u / sqrt(sumsq + 1e-8) where the norm exceeds 1e-8 (muon.rs:59-64).  Per tensor
 // (ns_kind): 1 = rewrite the f32 update buffer in place (operand of the f32 GEMMs, and the
 // final update when ns_steps == 0), 2 = write the bf16 operand of the first tensor-core GEMM,
-// 3 = write that operand split into three bf16 planes x = x0 + x1 + x2 (f32-accurate path).
+// 3 = write that operand as two f16 planes of x * 2^15 (f32-accurate tensor-core path).
 __global__ void __launch_bounds__(kEwThreads)
 normalise_kernel(const TensorDesc *__restrict__ tensors, const ChunkDesc *__restrict__ chunks, int64_t n_chunks,
                  const uint8_t *__restrict__ present, const uint8_t *__restrict__ ns_kind,
@@ -384,38 +384,31 @@ normalise_kernel(const TensorDesc *__restrict__ tensors, const ChunkDesc *__rest
         const uint32_t n4 = n >> 2;
         if (kind == 3) {
             __nv_bfloat16 *xb = xb_base + (u - upd_base);
-            auto split3 = [&](float x, __nv_bfloat16 &b0, __nv_bfloat16 &b1, __nv_bfloat16 &b2) {
-                b0 = __float2bfloat16_rn(x);
-                x -= __bfloat162float(b0);  // exact: the residual fits in f32
-                b1 = __float2bfloat16_rn(x);
-                x -= __bfloat162float(b1);
-                b2 = __float2bfloat16_rn(x);
-            };
+            unsigned short *xh = reinterpret_cast<unsigned short *>(xb);
             for (uint32_t i = threadIdx.x; i < n4; i += kEwThreads) {
                 float4 v = reinterpret_cast<const float4 *>(u)[i];
                 if (scale) {
                     v.x = __fdiv_rn(v.x, norm); v.y = __fdiv_rn(v.y, norm);
                     v.z = __fdiv_rn(v.z, norm); v.w = __fdiv_rn(v.w, norm);
                 }
-                __nv_bfloat16 p[3][4];
-                split3(v.x, p[0][0], p[1][0], p[2][0]);
-                split3(v.y, p[0][1], p[1][1], p[2][1]);
-                split3(v.z, p[0][2], p[1][2], p[2][2]);
-                split3(v.w, p[0][3], p[1][3], p[2][3]);
+                unsigned short p[2][4];
+                split_f16(v.x * kSplitScale, p[0][0], p[1][0]);
+                split_f16(v.y * kSplitScale, p[0][1], p[1][1]);
+                split_f16(v.z * kSplitScale, p[0][2], p[1][2]);
+                split_f16(v.w * kSplitScale, p[0][3], p[1][3]);
 #pragma unroll
-                for (int pl = 0; pl < 3; ++pl) {
+                for (int pl = 0; pl < kSplitPlanes; ++pl) {
                     uint2 packed;
-                    packed.x = (uint32_t)__bfloat16_as_ushort(p[pl][0]) | ((uint32_t)__bfloat16_as_ushort(p[pl][1]) << 16);
-                    packed.y = (uint32_t)__bfloat16_as_ushort(p[pl][2]) | ((uint32_t)__bfloat16_as_ushort(p[pl][3]) << 16);
-                    reinterpret_cast<uint2 *>(xb + pl * plane_stride)[i] = packed;
+                    packed.x = (uint32_t)p[pl][0] | ((uint32_t)p[pl][1] << 16);
+                    packed.y = (uint32_t)p[pl][2] | ((uint32_t)p[pl][3] << 16);
+                    reinterpret_cast<uint2 *>(xh + pl * plane_stride)[i] = packed;
                 }
             }
             for (uint32_t i = (n4 << 2) + threadIdx.x; i < n; i += kEwThreads) {
-                __nv_bfloat16 b0, b1, b2;
-                split3(scale ? __fdiv_rn(u[i], norm) : u[i], b0, b1, b2);
-                xb[i] = b0;
-                xb[plane_stride + i] = b1;
-                xb[2 * plane_stride + i] = b2;
+                unsigned short h0, h1;
+                split_f16((scale ? __fdiv_rn(u[i], norm) : u[i]) * kSplitScale, h0, h1);
+                xh[i] = h0;
+                xh[plane_stride + i] = h1;
             }
         } else if (kind == 2) {
             __nv_bfloat16 *xb = xb_base + (u - upd_base);
@@ -526,7 +519,7 @@ struct MuonState {
     std::vector<int64_t> local_off;   // per tensor: offset into this rank's buffers, -1 if not owned
     std::vector<uint8_t> ns_kind;     // per tensor: 0 no Newton-Schulz, 1 f32 CUDA-core path, 2 bf16 tensor-core
                                       // path, 3 split-bf16 (f32-accurate) tensor-core path
-    int planes = 1;                   // bf16 planes per tensor-core operand (3 on the split path)
+    int planes = 1;                   // 16-bit planes per tensor-core operand (2 on the split path)
     int64_t cb_elems = 0;             // elements of one plane of the C buffer
     int64_t owned_elems = 0;
     float *d_upd = nullptr;           // update buffer u / X (f32), owned tensors
@@ -732,7 +725,7 @@ int muon_init(vb_optimizer *opt)
         VB_CUDA(cudaMalloc(&s->d_xnext, owned_bytes));
         VB_CUDA(cudaMalloc(&s->d_gram, (size_t)std::max<int64_t>(gram_elems, 1) * sizeof(float)));
     }
-    s->planes = opt->ns_mode == VB_NS_F32_TC ? 3 : 1;
+    s->planes = opt->ns_mode == VB_NS_F32_TC ? kSplitPlanes : 1;
     s->cb_elems = cb_elems;
     if (!tc_tensors.empty()) {
         const size_t xb_bytes = (size_t)s->planes * (size_t)std::max<int64_t>(off, 1) * sizeof(__nv_bfloat16);
@@ -819,7 +812,7 @@ int muon_init(vb_optimizer *opt)
             const int mn_mode = tc_mn_major_mode(c);
             CUtensorMap map_x_k[2], map_x_mn[2], map_c;
             const int planes = s->planes;
-            const int n_terms = planes == 3 ? 6 : 1;
+            const int n_terms = planes > 1 ? kSplitTerms : 1;
             for (int par = 0; par < 2; ++par) {
                 VB_TRY(make_bf16_tensor_map(&map_x_k[par], xb[par], c, r, TC_OP_K_MAJOR, planes, s->owned_elems));
                 VB_TRY(make_bf16_tensor_map(&map_x_mn[par], xb[par], c, r, mn_mode, planes, s->owned_elems));
@@ -838,7 +831,7 @@ int muon_init(vb_optimizer *opt)
                 g.a_mode = tall ? mn_mode : TC_OP_K_MAJOR;
                 g.b_mode = g.a_mode;
                 // split path: keep the Gram itself and form 1.5 X - 0.5 X G in the update's epilogue
-                g.epilogue = planes == 3 ? TC_EPI_IDENTITY : TC_EPI_THREE_I_MINUS; g.ld_out = sh; g.tensor = t;
+                g.epilogue = planes > 1 ? TC_EPI_IDENTITY : TC_EPI_THREE_I_MINUS; g.ld_out = sh; g.tensor = t;
                 g.n_terms = n_terms; g.n_out_planes = planes; g.out_plane_stride = s->cb_elems;
                 g.out_bf16 = cb; g.out_f32 = nullptr;
                 if (first && s->fold_norm) {  // operands are u, not u/norm: G = (u^T u) / norm^2
@@ -854,7 +847,7 @@ int muon_init(vb_optimizer *opt)
                 u.M = r; u.N = c; u.K = sh;
                 u.a_mode = TC_OP_K_MAJOR;
                 u.b_mode = tall ? TC_OP_K_MAJOR : mn_mode;
-                u.epilogue = planes == 3 ? TC_EPI_NS_COMBINE : TC_EPI_HALF; u.ld_out = c; u.tensor = t;
+                u.epilogue = planes > 1 ? TC_EPI_NS_COMBINE : TC_EPI_HALF; u.ld_out = c; u.tensor = t;
                 u.in_bf16 = xb[par];
                 u.n_terms = n_terms; u.n_out_planes = planes; u.out_plane_stride = s->owned_elems;
                 u.out_bf16 = xb[par ^ 1]; u.out_f32 = nullptr;
@@ -883,7 +876,7 @@ int muon_init(vb_optimizer *opt)
                 }
             for (int m0 = 0; m0 < r; m0 += bm)
                 for (int n0 = 0; n0 < c; n0 += bn) upd_tiles.push_back(GemmTile{pidx, m0, n0, 0});
-            // executed tensor-core FLOPs: six plane products per product on the split path; the
+            // executed tensor-core FLOPs: three plane products per product on the split path; the
             // Gram counts only the tiles that are computed
             const double prod = 2.0 * (double)std::max(r, c) * (double)sh * (double)sh;
             s->flops_per_step += (double)n_terms * (double)opt->ns_steps *
@@ -961,7 +954,7 @@ int muon_step(vb_optimizer *opt, uint32_t flags)
         for (int it = 0; it < opt->ns_steps; ++it) {
             const int par = it & 1;
             if (s->n_tc_gram_tiles > 0) {
-                const bool split = s->planes == 3;
+                const bool split = s->planes > 1;
                 VB_TRY(launch_ns_gemm_tc(s->d_tc_gram[(size_t)it], s->d_tc_gram_tiles, s->n_tc_gram_tiles,
                                          opt->d_present, s->d_error, e->sm_count, e->stream, 0, split));
                 VB_TRY(launch_ns_gemm_tc(s->d_tc_upd[(size_t)it], s->d_tc_upd_tiles, s->n_tc_upd_tiles,

@@ -5,10 +5,34 @@
 
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 #include "vb_internal.h"
 
 namespace vb {
+
+// The f32-accurate tensor-core path holds every operand as two f16 planes of the value
+// scaled by 2^15 (see ns_gemm_tc.cu); the 16-bit words travel in the same buffers and tensor
+// maps as the bf16 operands of the plain path.
+constexpr float kSplitScale = 32768.0f;            // 2^15
+constexpr float kSplitInvScale = 1.0f / 32768.0f;  // 2^-15
+constexpr int kSplitPlanes = 2;
+constexpr int kSplitTerms = 3;  // plane products per product
+
+#ifdef __CUDACC__
+__device__ __forceinline__ float f16_bits_to_float(uint32_t bits16)
+{
+    return __half2float(__ushort_as_half((unsigned short)bits16));
+}
+// scaled value -> its two f16 planes: h0 = f16(xs), h1 = f16(xs - h0) (the difference is exact)
+__device__ __forceinline__ void split_f16(float xs, unsigned short &h0, unsigned short &h1)
+{
+    const __half a = __float2half_rn(xs);
+    const __half b = __float2half_rn(xs - __half2float(a));
+    h0 = __half_as_ushort(a);
+    h1 = __half_as_ushort(b);
+}
+#endif
 
 enum GemmTileFlags {
     GEMM_TILE_MIRROR = 1,  // symmetric output: also store this tile transposed
@@ -63,7 +87,7 @@ struct alignas(128) TcGemmProblem {
     int32_t ld_out;
     int32_t tensor;          // index into the optimizer's gradient-presence bytes
     int32_t withhold_loads;  // test hook: the producer stages nothing, so the consumers' bounded waits expire
-    int32_t n_terms;         // 1: plain bf16 operands; 6: operands split into three bf16 planes (f32-accurate)
+    int32_t n_terms;         // 1: plain bf16 operands; 3: operands held as two f16 planes (f32-accurate)
     int32_t n_out_planes;    // planes written to out_bf16: 1 (bf16 rounding) or 3 (split)
     int64_t out_plane_stride;  // elements between output planes
     const float *scale_sumsq;      // if set: the accumulator is scaled by s^scale_power, s = 1/sqrt(*scale_sumsq + 1e-8)

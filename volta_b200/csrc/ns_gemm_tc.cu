@@ -37,6 +37,7 @@
 // poll, records an error code for the host, releases its TMEM and returns.
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <stdlib.h>
 
 #include "ns_gemm.h"
@@ -331,12 +332,12 @@ __device__ __forceinline__ uint64_t operand_desc(uint32_t base, int mode, int kk
 }
 
 // Instruction descriptor for kind::f16 with bf16 operands and f32 accumulation.
-__device__ __forceinline__ uint32_t make_idesc(int a_mode, int b_mode, int m)
+__device__ __forceinline__ uint32_t make_idesc(int a_mode, int b_mode, int m, bool fp16)
 {
     uint32_t d = 0;
     d |= 1u << 4;                    // D format: f32
-    d |= 1u << 7;                    // A format: bf16
-    d |= 1u << 10;                   // B format: bf16
+    d |= (fp16 ? 0u : 1u) << 7;      // A format: f16 (0) or bf16 (1)
+    d |= (fp16 ? 0u : 1u) << 10;     // B format
     d |= (uint32_t)(a_mode != TC_OP_K_MAJOR) << 15;  // A is MN-major
     d |= (uint32_t)(b_mode != TC_OP_K_MAJOR) << 16;  // B is MN-major
     d |= (uint32_t)(BN >> 3) << 17;  // N
@@ -358,14 +359,16 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b)
     return *reinterpret_cast<uint32_t *>(&h);
 }
 
-// Operands split into three bf16 planes x = x0 + x1 + x2 (each the bf16 rounding of what the
-// previous ones left over, 24 significand bits in all) give an f32-accurate product on the bf16
-// tensor cores: the six plane products below are accumulated (smallest first) into the same f32
-// accumulator; the dropped products x1*y2, x2*y1, x2*y2 are below 2^-24 relative.
-// Terms in issue order, (plane of A, plane of B): (0,2) (2,0) (1,1) (0,1) (1,0) (0,0); one
-// nibble per term, term 0 in the lowest nibble.
-__device__ __forceinline__ int term_plane_a(int n_terms, int term) { return n_terms == 1 ? 0 : ((0x010120 >> (4 * term)) & 15); }
-__device__ __forceinline__ int term_plane_b(int n_terms, int term) { return n_terms == 1 ? 0 : ((0x001102 >> (4 * term)) & 15); }
+// The f32-accurate path: every operand is held as two f16 planes of the value scaled by 2^15,
+//     x * 2^15 = h0 + h1,   h0 = f16(x * 2^15),   h1 = f16(x * 2^15 - h0),
+// 22 significand bits in all (Newton-Schulz operands are bounded by 1 in magnitude once the
+// update is normalised, so the scaled values stay below the f16 maximum and the small plane
+// stays out of the f16 subnormals for every element that matters to the Frobenius norm).
+// Three plane products, smallest first, are accumulated into the same f32 accumulator:
+// (plane of A, plane of B) = (0,1) (1,0) (0,0); the dropped h1*h1 is below 2^-22 relative.
+// The accumulator then holds 2^30 times the product.  One nibble per term, term 0 lowest.
+__device__ __forceinline__ int term_plane_a(int n_terms, int term) { return n_terms == 1 ? 0 : ((0x010 >> (4 * term)) & 15); }
+__device__ __forceinline__ int term_plane_b(int n_terms, int term) { return n_terms == 1 ? 0 : ((0x001 >> (4 * term)) & 15); }
 
 // What a role needs to know about a tile, fetched one tile ahead so that the dependent global
 // loads (tile -> problem -> fields) never sit between two tiles' main loops.
@@ -444,6 +447,29 @@ struct DrainArgs {
     float *out_f32;
     const __nv_bfloat16 *in_bf16;
 };
+// 16-bit output formats: bf16 on the plain path, f16 planes on the split path.
+template <bool kHalf>
+__device__ __forceinline__ uint32_t pack16(float a, float b)
+{
+    if (kHalf) {
+        const __half2 h = __floats2half2_rn(a, b);
+        return *reinterpret_cast<const uint32_t *>(&h);
+    }
+    return pack_bf16(a, b);
+}
+template <bool kHalf>
+__device__ __forceinline__ unsigned short round16(float a)
+{
+    if (kHalf) return __half_as_ushort(__float2half_rn(a));
+    return __bfloat16_as_ushort(__float2bfloat16_rn(a));
+}
+template <bool kHalf>
+__device__ __forceinline__ float rounded16(float a)
+{
+    if (kHalf) return __half2float(__float2half_rn(a));
+    return __bfloat162float(__float2bfloat16_rn(a));
+}
+
 template <bool kSplit>
 __device__ __forceinline__ void drain_generic(const DrainArgs &a)
 {
@@ -460,7 +486,7 @@ __device__ __forceinline__ void drain_generic(const DrainArgs &a)
     // One load in flight at a time, waited for in the same statement: the registers a
     // tcgen05.ld targets are written asynchronously, so nothing may touch or move them before
     // the wait; this path is off the critical path (ragged edges; the split kernel's main loop is
-    // six times longer), so it does not pipeline its loads.
+    // three times longer), so it does not pipeline its loads.
     uint32_t v[32];
     for (int cc = 0; cc < kChunks; ++cc) {
         const int col0 = tile_col0 + cc * 32;
@@ -490,15 +516,15 @@ __device__ __forceinline__ void drain_generic(const DrainArgs &a)
                             const uint4 q = *reinterpret_cast<const uint4 *>(src + pl * plane_stride + g8 * 8);
                             const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
-                            for (int h = 0; h < 4; ++h) {  // bf16 -> f32 is a 16-bit shift
-                                x[g8 * 8 + 2 * h] += __uint_as_float(w[h] << 16);
-                                x[g8 * 8 + 2 * h + 1] += __uint_as_float(w[h] & 0xffff0000u);
+                            for (int h = 0; h < 4; ++h) {
+                                x[g8 * 8 + 2 * h] += f16_bits_to_float(w[h] & 0xffffu);
+                                x[g8 * 8 + 2 * h + 1] += f16_bits_to_float(w[h] >> 16);
                             }
                         }
                     }
                 }
 #pragma unroll
-                for (int j = 0; j < 32; ++j) f[j] = fmaf(1.5f, x[j], -0.5f * f[j]);
+                for (int j = 0; j < 32; ++j) f[j] = fmaf(1.5f, x[j] * kSplitInvScale, -0.5f * f[j]);
             }
             if (out_f32) {
                 float *dst = out_f32 + (int64_t)row * ld + col0;
@@ -512,6 +538,10 @@ __device__ __forceinline__ void drain_generic(const DrainArgs &a)
                 }
             }
             if (out_bf16) {
+                if (kSplit) {  // the planes hold the value times 2^15
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) f[j] *= kSplitScale;
+                }
                 for (int pl = 0; pl < out_planes; ++pl) {
                     __nv_bfloat16 *dst = out_bf16 + pl * plane_stride + (int64_t)row * ld + col0;
 #pragma unroll
@@ -521,17 +551,17 @@ __device__ __forceinline__ void drain_generic(const DrainArgs &a)
                             uint32_t q[8];
 #pragma unroll
                             for (int j = 0; j < 8; ++j)
-                                q[j] = pack_bf16(f[g16 * 16 + 2 * j], f[g16 * 16 + 2 * j + 1]);
+                                q[j] = pack16<kSplit>(f[g16 * 16 + 2 * j], f[g16 * 16 + 2 * j + 1]);
                             st_global_256(dst + g16 * 16, q);
                         } else {  // 16-byte pieces (N and ld are multiples of 8)
 #pragma unroll
                             for (int h = 0; h < 2; ++h) {
                                 if (col + h * 8 >= N) break;
                                 uint4 q;
-                                q.x = pack_bf16(f[g16 * 16 + h * 8 + 0], f[g16 * 16 + h * 8 + 1]);
-                                q.y = pack_bf16(f[g16 * 16 + h * 8 + 2], f[g16 * 16 + h * 8 + 3]);
-                                q.z = pack_bf16(f[g16 * 16 + h * 8 + 4], f[g16 * 16 + h * 8 + 5]);
-                                q.w = pack_bf16(f[g16 * 16 + h * 8 + 6], f[g16 * 16 + h * 8 + 7]);
+                                q.x = pack16<kSplit>(f[g16 * 16 + h * 8 + 0], f[g16 * 16 + h * 8 + 1]);
+                                q.y = pack16<kSplit>(f[g16 * 16 + h * 8 + 2], f[g16 * 16 + h * 8 + 3]);
+                                q.z = pack16<kSplit>(f[g16 * 16 + h * 8 + 4], f[g16 * 16 + h * 8 + 5]);
+                                q.w = pack16<kSplit>(f[g16 * 16 + h * 8 + 6], f[g16 * 16 + h * 8 + 7]);
                                 *reinterpret_cast<uint4 *>(dst + g16 * 16 + h * 8) = q;
                             }
                         }
@@ -543,11 +573,12 @@ __device__ __forceinline__ void drain_generic(const DrainArgs &a)
                         __nv_bfloat16 *mdst = out_bf16 + pl * plane_stride + (int64_t)col0 * ld + row;
 #pragma unroll
                         for (int j = 0; j < 32; ++j)
-                            if (col0 + j < N) mdst[(int64_t)j * ld] = __float2bfloat16_rn(f[j]);
+                            if (col0 + j < N)
+                                reinterpret_cast<unsigned short *>(mdst)[(int64_t)j * ld] = round16<kSplit>(f[j]);
                     }
                     if (pl + 1 < out_planes) {  // what this plane's rounding left over goes to the next
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) f[j] -= __bfloat162float(__float2bfloat16_rn(f[j]));
+                        for (int j = 0; j < 32; ++j) f[j] -= rounded16<kSplit>(f[j]);
                     }
                 }
             }
@@ -592,7 +623,7 @@ __device__ __forceinline__ TileInfo fetch_tile(const TcGemmProblem *problems, co
     return ti;
 }
 
-// kSplit: the operands are three bf16 planes (f32-accurate path); the plain bf16 instantiation
+// kSplit: the operands are two f16 planes (f32-accurate path); the plain bf16 instantiation
 // carries none of that code.
 template <int kCtas, bool kSplit>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -722,7 +753,7 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
                 const TileInfo ti = next;
                 next = fetch_tile(problems, tiles, n_tiles, present, t + n_groups);
                 if (ti.skipped) continue;
-                const uint32_t idesc = make_idesc(ti.a_mode, ti.b_mode, C::kTileM);
+                const uint32_t idesc = make_idesc(ti.a_mode, ti.b_mode, C::kTileM, kSplit);
                 // the epilogue(s) must have drained this accumulator
                 if (!MBAR_WAIT(1, &bars->tmem_empty[acc], acc_phase ^ 1u)) {
                     ok = false;
@@ -782,15 +813,15 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
             const __nv_bfloat16 *in_bf16 = p->in_bf16;  // TC_EPI_NS_COMBINE: the planes of X at the output position
             // Frobenius normalisation folded into the first iteration (plain bf16 path): the operand is
             // the unnormalised update u, the accumulator is scaled by 1/norm (or its square)
-            float acc_scale = 1.0f;
+            float acc_scale = kSplit ? kSplitInvScale * kSplitInvScale : 1.0f;  // split operands carry 2^15 each
             if (!kSplit && p->scale_sumsq) {
                 const float norm = sqrtf(*p->scale_sumsq + 1e-8f);  // muon.rs:59
                 const float inv = norm > 1e-8f ? 1.0f / norm : 1.0f;  // muon.rs:60
                 acc_scale = p->scale_power == 2 ? inv * inv : inv;
             }
             const int64_t ld = p->ld_out;
-            const int out_planes = kSplit ? p->n_out_planes : 1;  // 1: bf16 rounding; 3: split into three pieces
-            const int out_planes_in = kSplit ? 3 : 1;             // planes of the operands (and of in_bf16)
+            const int out_planes = kSplit ? p->n_out_planes : 1;  // 1: bf16 rounding; 2: the two f16 planes
+            const int out_planes_in = kSplit ? kSplitPlanes : 1;  // planes of the operands (and of in_bf16)
             const int64_t plane_stride = p->out_plane_stride;
             const bool bf16_rows_32b = (ld % 16) == 0;  // every bf16 output row starts on a 32-byte boundary
             if (!MBAR_WAIT(3, &bars->tmem_full[acc], acc_phase)) {
@@ -1001,7 +1032,7 @@ static int launch_variant(const TcGemmProblem *d_problems, const GemmTile *d_til
     return VB_OK;
 }
 
-// split: the problems' operands are three bf16 planes (all problems of a launch are alike).
+// split: the problems' operands are two f16 planes (all problems of a launch are alike).
 int launch_ns_gemm_tc(const TcGemmProblem *d_problems, const GemmTile *d_tiles, int n_tiles,
                       const uint8_t *d_present, int *d_error_flag, int sm_count, cudaStream_t stream,
                       uint32_t wait_limit, bool split)
