@@ -244,120 +244,271 @@ __device__ __forceinline__ float float_from_k(uint32_t bits_of_s, uint32_t k)
     return __uint_as_float((bits_of_s & 0x7f800000u) | (k & 0x7fffffu));
 }
 
+// The chain above is sequential per matrix, but almost all of its work can be done ahead of it
+// in parallel.  A block of 8192 consecutive elements is one composed map once the binade of the
+// running sum at the block's start is known, and that binade can be guessed from an ordinary
+// (tree) prefix sum, which differs from the sequential sum by parts in 10^3 only:
+//   1. block_sumsq_kernel       tree sum of squares of every block            (parallel)
+//   2. block_guess_kernel       prefix over a matrix's blocks -> guessed exponent per block
+//   3. block_map_kernel         composed map of every block under its guess   (parallel)
+//   4. sumsq_ordered_kernel     walks the blocks: a guessed map is used when the running sum
+//                               really is in the guessed binade and stays there (one integer
+//                               add per block); any other block (the first ones, the ~25 binade
+//                               crossings, a wrong guess) is redone exactly by the whole CTA.
+// The result is the same sequence of roundings either way.
+struct SeqBlock {
+    int32_t tensor;  // index into the optimizer's tensors
+    int32_t index;   // block number inside the tensor
+};
+
+__device__ __forceinline__ void load_block16(const float *__restrict__ x, int64_t n, int64_t base, int tid, float *dst)
+{
+    const int64_t i0 = base + (int64_t)tid * 16;
+    if (i0 + 16 <= n) {  // tensors start 128-byte aligned: vector loads are aligned
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const float4 v = *reinterpret_cast<const float4 *>(x + i0 + 4 * q);
+            dst[4 * q + 0] = v.x; dst[4 * q + 1] = v.y; dst[4 * q + 2] = v.z; dst[4 * q + 3] = v.w;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) dst[i] = (i0 + i < n) ? x[i0 + i] : 0.0f;
+    }
+}
+
+__global__ void __launch_bounds__(512)
+block_sumsq_kernel(const TensorDesc *__restrict__ tensors, const SeqBlock *__restrict__ blocks, int n_blocks,
+                   const int64_t *__restrict__ sizes, const uint8_t *__restrict__ present,
+                   float *__restrict__ block_sum)
+{
+    __shared__ float warp_sums[16];
+    for (int b = blockIdx.x; b < n_blocks; b += gridDim.x) {
+        const SeqBlock sb = blocks[b];
+        if (present[sb.tensor] == 0) continue;
+        float v[16];
+        load_block16(tensors[sb.tensor].s2, sizes[sb.tensor], (int64_t)sb.index * 8192, threadIdx.x, v);
+        float acc = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) acc += v[i] * v[i];
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, d);
+        if ((threadIdx.x & 31) == 0) warp_sums[threadIdx.x >> 5] = acc;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float t = 0.0f;
+#pragma unroll
+            for (int w = 0; w < 16; ++w) t += warp_sums[w];
+            block_sum[b] = t;
+        }
+        __syncthreads();
+    }
+}
+
+// One warp per matrix: biased exponent of the (approximate) sum of everything before each block.
+__global__ void block_guess_kernel(const float *__restrict__ block_sum, const int64_t *__restrict__ first_block,
+                                   const int32_t *__restrict__ ns_tensors, int n_ns,
+                                   const uint8_t *__restrict__ present, int32_t *__restrict__ guess)
+{
+    const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (w >= n_ns) return;
+    if (present[ns_tensors[w]] == 0) return;
+    const int lane = threadIdx.x & 31;
+    const int64_t lo = first_block[w], hi = first_block[w + 1];
+    double carry = 0.0;
+    for (int64_t base = lo; base < hi; base += 32) {
+        const int64_t i = base + lane;
+        const double mine = i < hi ? (double)block_sum[i] : 0.0;
+        double incl = mine;  // inclusive prefix over the 32 lanes
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const double o = __shfl_up_sync(0xffffffffu, incl, d);
+            if (lane >= d) incl += o;
+        }
+        if (i < hi) guess[i] = (int32_t)((__float_as_uint((float)(carry + incl - mine)) >> 23) & 0xffu);
+        carry += __shfl_sync(0xffffffffu, incl, 31);
+    }
+}
+
+__global__ void __launch_bounds__(512)
+block_map_kernel(const TensorDesc *__restrict__ tensors, const SeqBlock *__restrict__ blocks, int n_blocks,
+                 const int64_t *__restrict__ sizes, const uint8_t *__restrict__ present,
+                 const int32_t *__restrict__ guess, IncMap *__restrict__ block_map)
+{
+    __shared__ IncMap warp_maps[16];
+    for (int b = blockIdx.x; b < n_blocks; b += gridDim.x) {
+        const SeqBlock sb = blocks[b];
+        if (present[sb.tensor] == 0) continue;
+        const uint32_t biased = (uint32_t)guess[b];
+        if (biased < 27u || biased == 0xffu) {  // no usable guess (empty prefix, tiny sums): the chain redoes it
+            if (threadIdx.x == 0) block_map[b] = IncMap{kIncSat, kIncSat};
+            continue;
+        }
+        float v[16];
+        load_block16(tensors[sb.tensor].s2, sizes[sb.tensor], (int64_t)sb.index * 8192, threadIdx.x, v);
+        const float inv_ulp = __uint_as_float((277u - biased) << 23);
+        IncMap m = {0u, 0u};
+#pragma unroll
+        for (int i = 0; i < 16; ++i) m = compose(m, element_map(__fmul_rn(v[i], v[i]), inv_ulp));
+        const int lane = threadIdx.x & 31;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            IncMap o;
+            o.even = __shfl_down_sync(0xffffffffu, m.even, d);
+            o.odd = __shfl_down_sync(0xffffffffu, m.odd, d);
+            if ((lane & (2 * d - 1)) == 0) m = compose(m, o);
+        }
+        if (lane == 0) warp_maps[threadIdx.x >> 5] = m;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            IncMap t = warp_maps[0];
+#pragma unroll
+            for (int w = 1; w < 16; ++w) t = compose(t, warp_maps[w]);
+            block_map[b] = t;
+        }
+        __syncthreads();
+    }
+}
+
 __global__ void __launch_bounds__(kSeqThreads)
 sumsq_ordered_kernel(const TensorDesc *__restrict__ tensors, const int32_t *__restrict__ ns_tensors,
                      const int64_t *__restrict__ sizes, const uint8_t *__restrict__ present,
-                     float *__restrict__ sumsq)
+                     float *__restrict__ sumsq, const int64_t *__restrict__ first_block,
+                     const IncMap *__restrict__ block_map, const int32_t *__restrict__ guess)
 {
+    constexpr int kWindow = 512;  // blocks whose guessed maps are staged in shared memory at a time
     __shared__ float sq[kSeqChunk];
     __shared__ IncMap warp_maps[kSeqThreads / 32];
+    __shared__ IncMap win_map[kWindow];
+    __shared__ int32_t win_guess[kWindow];
     __shared__ float sh_s;
     __shared__ int sh_start;
+    __shared__ int sh_next;
 
     const int t = ns_tensors[blockIdx.x];
     if (present[t] == 0) return;
     const float *__restrict__ x = tensors[t].s2;  // the update buffer
     const int64_t n = sizes[t];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int64_t n_blocks = (n + kSeqChunk - 1) / kSeqChunk;
+    const int64_t fb = block_map ? first_block[blockIdx.x] : 0;
 
     if (tid == 0) sh_s = 0.0f;
-
-    float cur[kSeqPerThread], nxt[kSeqPerThread];
-    auto load = [&](int64_t base, float *dst) {
-        const int64_t i0 = base + (int64_t)tid * kSeqPerThread;
-        if (i0 + kSeqPerThread <= n) {  // tensors start 128-byte aligned: vector loads are aligned
-#pragma unroll
-            for (int q = 0; q < kSeqPerThread / 4; ++q) {
-                const float4 v = *reinterpret_cast<const float4 *>(x + i0 + 4 * q);
-                dst[4 * q + 0] = v.x; dst[4 * q + 1] = v.y; dst[4 * q + 2] = v.z; dst[4 * q + 3] = v.w;
-            }
-        } else {
-#pragma unroll
-            for (int i = 0; i < kSeqPerThread; ++i) dst[i] = (i0 + i < n) ? x[i0 + i] : 0.0f;
-        }
-    };
-    load(0, cur);
-    for (int64_t base = 0; base < n; base += kSeqChunk) {
-        if (base + kSeqChunk < n) load(base + kSeqChunk, nxt);  // prefetch the next chunk
-        const int cnt = (int)min((int64_t)kSeqChunk, n - base);
-        float a[kSeqPerThread];
-#pragma unroll
-        for (int i = 0; i < kSeqPerThread; ++i) {
-            a[i] = __fmul_rn(cur[i], cur[i]);  // `x * x`, muon.rs:58 (padding squares to 0)
-            sq[i * kSeqThreads + tid] = a[i];  // element tid*16+i, stored bank-conflict free
-        }
-        if (tid == 0) sh_start = 0;
-        __syncthreads();
-        for (;;) {
-            const int start = sh_start;
-            const float s = sh_s;
-            if (start >= cnt) break;
-            const bool ok = binade_ok(s);
-            if (ok && (warp + 1) * kSeqWarpSpan > start) {  // warps wholly before `start` have nothing to add
-                // 1/ulp(s) = 2^(23 - e) with e the unbiased exponent of s: biased exponent 150 - e - 127 + 127
-                const uint32_t biased = (__float_as_uint(s) >> 23) & 0xffu;
-                const float inv_ulp = __uint_as_float((277u - biased) << 23);
-                IncMap m = {0u, 0u};
-#pragma unroll
-                for (int i = 0; i < kSeqPerThread; ++i) {
-                    const int idx = tid * kSeqPerThread + i;
-                    if (idx >= start && idx < cnt) m = compose(m, element_map(a[i], inv_ulp));
-                }
-#pragma unroll
-                for (int d = 1; d < 32; d <<= 1) {
-                    IncMap o;
-                    o.even = __shfl_down_sync(0xffffffffu, m.even, d);
-                    o.odd = __shfl_down_sync(0xffffffffu, m.odd, d);
-                    if ((lane & (2 * d - 1)) == 0) m = compose(m, o);
-                }
-                if (lane == 0) warp_maps[warp] = m;
-            }
-            __syncthreads();
-            if (tid == 0) {
-                float s_new = s;
-                int walk_from = start;
-                bool done = false;
-                if (ok) {
-                    // apply the warps' maps in order; stop at the first that would leave the binade
-                    const uint32_t bits = __float_as_uint(s);
-                    uint32_t k = (bits & 0x7fffffu) | 0x800000u;
-                    int w = start / kSeqWarpSpan;
-                    const int w_end = (cnt + kSeqWarpSpan - 1) / kSeqWarpSpan;
-                    for (; w < w_end; ++w) {
-                        const IncMap wm = warp_maps[w];
-                        const uint32_t inc = (k & 1u) ? wm.odd : wm.even;
-                        if (k + inc >= (1u << 24)) break;
-                        k += inc;
-                    }
-                    s_new = float_from_k(bits, k);
-                    if (w == w_end) {
-                        sh_start = cnt;
-                        done = true;
-                    } else {
-                        walk_from = max(start, w * kSeqWarpSpan);  // the crossing is inside warp w's span
-                    }
-                }
-                if (!done) {
-                    // walk with real additions until s enters a new binade (or the chunk ends)
-                    int j = walk_from;
-                    while (j < cnt) {
-                        const float nx = __fadd_rn(s_new, sq[(j % kSeqPerThread) * kSeqThreads + j / kSeqPerThread]);
-                        const bool changed = ((__float_as_uint(nx) ^ __float_as_uint(s_new)) >> 23) != 0u;
-                        s_new = nx;
-                        ++j;
-                        if (changed && binade_ok(s_new)) break;
-                    }
-                    sh_start = j;
-                }
-                sh_s = s_new;
-            }
-            __syncthreads();
-        }
-        __syncthreads();  // everyone has left the loop before sq / sh_start are rewritten
-#pragma unroll
-        for (int i = 0; i < kSeqPerThread; ++i) cur[i] = nxt[i];
-    }
     __syncthreads();
+
+    for (int64_t win = 0; win < n_blocks; win += kWindow) {
+        const int wn = (int)min((int64_t)kWindow, n_blocks - win);
+        if (block_map != nullptr && tid < wn) {
+            win_map[tid] = block_map[fb + win + tid];
+            win_guess[tid] = guess[fb + win + tid];
+        }
+        __syncthreads();
+        int b = 0;
+        for (;;) {
+            if (tid == 0) {
+                // take the guessed maps while the running sum is in the guessed binade and stays there
+                float s = sh_s;
+                int bb = b;
+                if (block_map != nullptr) {
+                    while (bb < wn) {
+                        const uint32_t bits = __float_as_uint(s);
+                        if (!binade_ok(s) || (int32_t)((bits >> 23) & 0xffu) != win_guess[bb]) break;
+                        const IncMap m = win_map[bb];
+                        const uint32_t k = (bits & 0x7fffffu) | 0x800000u;
+                        const uint32_t inc = (k & 1u) ? m.odd : m.even;
+                        if (k + inc >= (1u << 24)) break;  // would leave the binade (or the map is saturated)
+                        s = float_from_k(bits, k + inc);
+                        ++bb;
+                    }
+                }
+                sh_s = s;
+                sh_next = bb;
+            }
+            __syncthreads();
+            b = sh_next;
+            if (b >= wn) break;
+
+            // ---- block win + b exactly, by the whole CTA --------------------------------------
+            const int64_t base = (win + b) * kSeqChunk;
+            const int cnt = (int)min((int64_t)kSeqChunk, n - base);
+            float a[kSeqPerThread];
+            load_block16(x, n, base, tid, a);
+#pragma unroll
+            for (int i = 0; i < kSeqPerThread; ++i) {
+                a[i] = __fmul_rn(a[i], a[i]);      // `x * x`, muon.rs:58 (padding squares to 0)
+                sq[i * kSeqThreads + tid] = a[i];  // element tid*16+i, stored bank-conflict free
+            }
+            if (tid == 0) sh_start = 0;
+            __syncthreads();
+            for (;;) {
+                const int start = sh_start;
+                const float s = sh_s;
+                if (start >= cnt) break;
+                const bool ok = binade_ok(s);
+                if (ok && (warp + 1) * kSeqWarpSpan > start) {  // warps wholly before `start` have nothing to add
+                    // 1/ulp(s) = 2^(23 - e) with e the unbiased exponent of s: biased exponent 150 - e - 127 + 127
+                    const uint32_t biased = (__float_as_uint(s) >> 23) & 0xffu;
+                    const float inv_ulp = __uint_as_float((277u - biased) << 23);
+                    IncMap m = {0u, 0u};
+#pragma unroll
+                    for (int i = 0; i < kSeqPerThread; ++i) {
+                        const int idx = tid * kSeqPerThread + i;
+                        if (idx >= start && idx < cnt) m = compose(m, element_map(a[i], inv_ulp));
+                    }
+#pragma unroll
+                    for (int d = 1; d < 32; d <<= 1) {
+                        IncMap o;
+                        o.even = __shfl_down_sync(0xffffffffu, m.even, d);
+                        o.odd = __shfl_down_sync(0xffffffffu, m.odd, d);
+                        if ((lane & (2 * d - 1)) == 0) m = compose(m, o);
+                    }
+                    if (lane == 0) warp_maps[warp] = m;
+                }
+                __syncthreads();
+                if (tid == 0) {
+                    float s_new = s;
+                    int walk_from = start;
+                    bool done = false;
+                    if (ok) {
+                        // apply the warps' maps in order; stop at the first that would leave the binade
+                        const uint32_t bits = __float_as_uint(s);
+                        uint32_t k = (bits & 0x7fffffu) | 0x800000u;
+                        int w = start / kSeqWarpSpan;
+                        const int w_end = (cnt + kSeqWarpSpan - 1) / kSeqWarpSpan;
+                        for (; w < w_end; ++w) {
+                            const IncMap wm = warp_maps[w];
+                            const uint32_t inc = (k & 1u) ? wm.odd : wm.even;
+                            if (k + inc >= (1u << 24)) break;
+                            k += inc;
+                        }
+                        s_new = float_from_k(bits, k);
+                        if (w == w_end) {
+                            sh_start = cnt;
+                            done = true;
+                        } else {
+                            walk_from = max(start, w * kSeqWarpSpan);  // the crossing is inside warp w's span
+                        }
+                    }
+                    if (!done) {
+                        // walk with real additions until s enters a new binade (or the block ends)
+                        int j = walk_from;
+                        while (j < cnt) {
+                            const float nx = __fadd_rn(s_new, sq[(j % kSeqPerThread) * kSeqThreads + j / kSeqPerThread]);
+                            const bool changed = ((__float_as_uint(nx) ^ __float_as_uint(s_new)) >> 23) != 0u;
+                            s_new = nx;
+                            ++j;
+                            if (changed && binade_ok(s_new)) break;
+                        }
+                        sh_start = j;
+                    }
+                    sh_s = s_new;
+                }
+                __syncthreads();
+            }
+            __syncthreads();  // everyone has left the loop before sq / sh_start / sh_s are touched again
+            b += 1;
+        }
+        __syncthreads();  // the staged window is rewritten next
+    }
     if (tid == 0) sumsq[t] = sh_s;
 }
 
@@ -534,6 +685,14 @@ struct MuonState {
     int32_t *d_ns_tensors = nullptr;  // owned tensors that run Newton-Schulz
     int n_ns = 0;
     int64_t *d_first_chunk = nullptr;
+    // ordered sum of squares (f32 modes): 8192-element blocks of the Newton-Schulz tensors, their
+    // tree sums, guessed exponents and guessed maps (see block_map_kernel)
+    SeqBlock *d_seq_blocks = nullptr;
+    int64_t *d_first_block = nullptr;  // per Newton-Schulz tensor (n_ns + 1)
+    float *d_block_sum = nullptr;
+    int32_t *d_block_guess = nullptr;
+    IncMap *d_block_map = nullptr;
+    int n_seq_blocks = 0;
     TensorDesc *d_desc = nullptr;        // p = w, g = grad, s1 = velocity, s2 = update buffer
     TensorDesc *d_desc_apply = nullptr;  // p = w, g = final update
     ChunkDesc *d_chunks = nullptr;
@@ -573,6 +732,11 @@ void destroy_muon_state(MuonState *s)
     cudaFree(s->d_sizes);
     cudaFree(s->d_ns_tensors);
     cudaFree(s->d_first_chunk);
+    cudaFree(s->d_seq_blocks);
+    cudaFree(s->d_first_block);
+    cudaFree(s->d_block_sum);
+    cudaFree(s->d_block_guess);
+    cudaFree(s->d_block_map);
     cudaFree(s->d_desc);
     cudaFree(s->d_desc_apply);
     cudaFree(s->d_chunks);
@@ -719,6 +883,30 @@ int muon_init(vb_optimizer *opt)
     VB_TRY(upload(&s->d_sizes, opt->sizes, e->stream));
     VB_TRY(upload(&s->d_ns_tensors, ns_tensors, e->stream));
     VB_CUDA(cudaMalloc(&s->d_partials, (size_t)std::max<int64_t>(s->n_chunks, 1) * sizeof(float)));
+    if (opt->ns_mode != VB_NS_BF16 && !ns_tensors.empty()) {
+        // block tables of the ordered sum of squares; VB_SUMSQ_SERIAL=1 keeps the one-CTA-per-matrix
+        // chain without the parallel pre-pass (for comparison)
+        const char *serial = getenv("VB_SUMSQ_SERIAL");
+        if (!(serial && *serial == '1')) {
+            std::vector<SeqBlock> blocks;
+            std::vector<int64_t> first_block(ns_tensors.size() + 1, 0);
+            for (size_t j = 0; j < ns_tensors.size(); ++j) {
+                first_block[j] = (int64_t)blocks.size();
+                const int64_t nb = (opt->sizes[(size_t)ns_tensors[j]] + kSeqChunk - 1) / kSeqChunk;
+                for (int64_t b = 0; b < nb; ++b) blocks.push_back(SeqBlock{ns_tensors[j], (int32_t)b});
+            }
+            first_block[ns_tensors.size()] = (int64_t)blocks.size();
+            if (blocks.size() < (size_t)0x7fffffff) {
+                s->n_seq_blocks = (int)blocks.size();
+                VB_TRY(upload(&s->d_seq_blocks, blocks, e->stream));
+                VB_TRY(upload(&s->d_first_block, first_block, e->stream));
+                const size_t nb = std::max<size_t>(blocks.size(), 1);
+                VB_CUDA(cudaMalloc(&s->d_block_sum, nb * sizeof(float)));
+                VB_CUDA(cudaMalloc(&s->d_block_guess, nb * sizeof(int32_t)));
+                VB_CUDA(cudaMalloc(&s->d_block_map, nb * sizeof(IncMap)));
+            }
+        }
+    }
 
     const bool odd = (opt->ns_steps & 1) != 0;
     if (!f32_tensors.empty()) {
@@ -940,9 +1128,22 @@ int muon_step(vb_optimizer *opt, uint32_t flags)
         if (fast_norm)
             reduce_partials_kernel<<<(s->n_ns + 3) / 4, 128, 0, e->stream>>>(s->d_partials, s->d_first_chunk,
                                                                             s->d_ns_tensors, s->n_ns, s->d_sumsq);
-        else
-            sumsq_ordered_kernel<<<s->n_ns, kSeqThreads, 0, e->stream>>>(s->d_desc, s->d_ns_tensors, s->d_sizes,
-                                                                        opt->d_present, s->d_sumsq);
+        else {
+            if (s->n_seq_blocks > 0) {
+                const int grid = std::min(s->n_seq_blocks, e->sm_count * 4);
+                block_sumsq_kernel<<<grid, 512, 0, e->stream>>>(s->d_desc, s->d_seq_blocks, s->n_seq_blocks, s->d_sizes,
+                                                                opt->d_present, s->d_block_sum);
+                block_guess_kernel<<<(s->n_ns + 3) / 4, 128, 0, e->stream>>>(s->d_block_sum, s->d_first_block,
+                                                                            s->d_ns_tensors, s->n_ns, opt->d_present,
+                                                                            s->d_block_guess);
+                block_map_kernel<<<grid, 512, 0, e->stream>>>(s->d_desc, s->d_seq_blocks, s->n_seq_blocks, s->d_sizes,
+                                                              opt->d_present, s->d_block_guess, s->d_block_map);
+                e->launches += 3;
+            }
+            sumsq_ordered_kernel<<<s->n_ns, kSeqThreads, 0, e->stream>>>(
+                s->d_desc, s->d_ns_tensors, s->d_sizes, opt->d_present, s->d_sumsq, s->d_first_block,
+                s->n_seq_blocks > 0 ? s->d_block_map : nullptr, s->d_block_guess);
+        }
         VB_CUDA(cudaGetLastError());
         normalise_kernel<<<ew_grid, kEwThreads, 0, e->stream>>>(s->d_desc, s->d_chunks, s->n_chunks, opt->d_present,
                                                                s->d_ns_kind, s->d_sumsq, s->d_upd, s->d_xb[0],
