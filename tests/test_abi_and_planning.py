@@ -30,6 +30,22 @@ def test_library_exports_every_declared_symbol():
     assert lib.vb_abi_version() == 1000
 
 
+def test_python_constants_match_the_header():
+    """Flags, modes and sizes are written twice (header and ctypes module): they must agree."""
+    from volta_b200 import _lib
+    text = open(HEADER).read()
+    defines = {k: int(v.rstrip("u"), 0) for k, v in re.findall(r"#define\s+(VB_[A-Z0-9_]+)\s+(\d+u?)\b", text)}
+    for name in ("VB_STEP_DEFAULT", "VB_STEP_NO_EXCHANGE", "VB_STEP_EXCHANGE_BF16", "VB_STEP_REDUCE_GRADS",
+                 "VB_STEP_MEAN_GRADS"):
+        assert defines[name] == getattr(_lib, name), name
+    assert defines["VB_IPC_HANDLE_BYTES"] == 64
+    enums = dict(re.findall(r"\b(VB_NS_[A-Z0-9_]+)\s*=\s*(\d+)", text))
+    for name in ("VB_NS_F32", "VB_NS_BF16", "VB_NS_F32_TC"):
+        assert int(enums[name]) == getattr(_lib, name), name
+    flags = [defines[n] for n in defines if n.startswith("VB_STEP_") and defines[n]]
+    assert len(set(flags)) == len(flags) and all(f & (f - 1) == 0 for f in flags)   # distinct single bits
+
+
 def test_step_params_mirror_layout():
     """32-byte, same field order as Volta's OptimizerStepParams (src/gpu/kernels.rs:42-54)."""
     from volta_b200._lib import StepParams
