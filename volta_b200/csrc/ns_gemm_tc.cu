@@ -65,6 +65,11 @@ struct Cfg {
     static constexpr int kBRows = BN / kCtas;                         // rows of B staged by one CTA
     static constexpr int kStageBytes = kRows128Bytes + kBRows * BK * 2;
     static constexpr int kTileM = BM * kCtas;
+    // Split kernel: one ring slot holds both planes of A and of B for one k block (two images of
+    // the plain slot, plane 0 then plane 1), so that each plane crosses from L2 once per k block
+    // although it enters two of the three plane products.
+    static constexpr int kSplitStages = kStages / 2;
+    static constexpr int kSplitStageBytes = 2 * kStageBytes;
 };
 
 template <int kCtas>
@@ -693,15 +698,15 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
                 // diagonal tile of a symmetric product (pair kernel, plain bf16): each CTA's 128 rows of
                 // B are its 128 rows of A, so they are fetched once and the MMA reads A's slot twice
                 const bool alias_b = kCtas == 2 && !kSplit && ti.b_is_a;
-                const int n_terms = kSplit ? ti.n_terms : 1;
-                const int n_slots = ti.k_blocks * n_terms;  // every (k block, plane pair) fills one ring slot
-                int kb = 0, term = 0;
+                constexpr int kRing = kSplit ? C::kSplitStages : C::kStages;
+                constexpr int kSlotBytes = kSplit ? C::kSplitStageBytes : C::kStageBytes;
+                const int n_slots = ti.k_blocks;  // one ring slot per k block
                 for (int slot = 0; slot < n_slots; ++slot) {
                     if (!MBAR_WAIT(0, &bars->empty[stage], phase ^ 1u)) {
                         ok = false;
                         break;
                     }
-                    uint8_t *sa = smem + (size_t)stage * C::kStageBytes;
+                    uint8_t *sa = smem + (size_t)stage * kSlotBytes;
                     uint8_t *sb = sa + kRows128Bytes;
                     // Only the leader posts the expected byte count (for all CTAs' loads): a remote
                     // arrive from the peer would put a cluster round trip into every ring slot.
@@ -709,28 +714,28 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
                     // complete until the leader has arrived.
                     const uint32_t full_bar =
                         kCtas == 2 ? map_to_cta(smem_u32(&bars->full[stage]), 0) : smem_u32(&bars->full[stage]);
-                    const int k0 = kb * BK;
+                    const int k0 = slot * BK;
                     if (ti.withhold) {
                         // Nothing is staged and no bytes are announced: the consumers' bounded waits
                         // (and, a ring later, this thread's own) run out.  Used by the expiry test.
                     } else if (lane == 0) {
                         if (cta_rank == 0)
-                            mbar_expect_tx(&bars->full[stage], alias_b ? kCtas * kRows128Bytes : kCtas * C::kStageBytes);
-                        load_rows128<kCtas, kSplit>(sa, &ti.p->map_a, ti.a_mode, a_row0, k0, term_plane_a(n_terms, term),
-                                            full_bar);
+                            mbar_expect_tx(&bars->full[stage], alias_b ? kCtas * kRows128Bytes : kCtas * kSlotBytes);
+#pragma unroll
+                        for (int pl = 0; pl < (kSplit ? kSplitPlanes : 1); ++pl)
+                            load_rows128<kCtas, kSplit>(sa + pl * C::kStageBytes, &ti.p->map_a, ti.a_mode, a_row0, k0, pl,
+                                                        full_bar);
                     } else if (!alias_b) {
 #pragma unroll
-                        for (int j = 0; j < C::kBRows / 128; ++j)
-                            load_rows128<kCtas, kSplit>(sb + j * kRows128Bytes, &ti.p->map_b, ti.b_mode, b_row0 + j * 128, k0,
-                                                term_plane_b(n_terms, term), full_bar);
+                        for (int pl = 0; pl < (kSplit ? kSplitPlanes : 1); ++pl)
+#pragma unroll
+                            for (int j = 0; j < C::kBRows / 128; ++j)
+                                load_rows128<kCtas, kSplit>(sb + pl * C::kStageBytes + j * kRows128Bytes, &ti.p->map_b,
+                                                            ti.b_mode, b_row0 + j * 128, k0, pl, full_bar);
                     }
-                    if (++stage == C::kStages) {
+                    if (++stage == kRing) {
                         stage = 0;
                         phase ^= 1u;
-                    }
-                    if (++term == n_terms) {
-                        term = 0;
-                        ++kb;
                     }
                 }
             }
@@ -761,21 +766,39 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
                 }
                 tcgen05_fence_after();
                 const uint32_t tmem_d = tmem_base + (uint32_t)(acc * kAccCols);
-                const int n_slots = ti.k_blocks * (kSplit ? ti.n_terms : 1);
+                constexpr int kRing = kSplit ? C::kSplitStages : C::kStages;
+                constexpr int kSlotBytes = kSplit ? C::kSplitStageBytes : C::kStageBytes;
+                const int n_slots = ti.k_blocks;
                 for (int slot = 0; slot < n_slots; ++slot) {
                     if (!MBAR_WAIT(2, &bars->full[stage], phase)) {
                         ok = false;
                         break;
                     }
                     tcgen05_fence_after();
-                    const uint32_t sa = smem_u32(smem + (size_t)stage * C::kStageBytes);
-                    const uint32_t sb = (kCtas == 2 && !kSplit && ti.b_is_a) ? sa : sa + kRows128Bytes;
+                    const uint32_t base = smem_u32(smem + (size_t)stage * kSlotBytes);
+                    if (kSplit) {
+                        // three plane products per k block, smallest first, from the two staged planes
 #pragma unroll
-                    for (int kk = 0; kk < BK / UMMA_K; ++kk)
-                        tcgen05_mma_bf16<kCtas>(tmem_d, operand_desc(sa, ti.a_mode, kk), operand_desc(sb, ti.b_mode, kk),
-                                                idesc, (slot > 0 || kk > 0) ? 1u : 0u);
+                        for (int term = 0; term < kSplitTerms; ++term) {
+                            const uint32_t sa = base + (uint32_t)(term_plane_a(kSplitTerms, term) * C::kStageBytes);
+                            const uint32_t sb = base + (uint32_t)(term_plane_b(kSplitTerms, term) * C::kStageBytes) +
+                                                kRows128Bytes;
+#pragma unroll
+                            for (int kk = 0; kk < BK / UMMA_K; ++kk)
+                                tcgen05_mma_bf16<kCtas>(tmem_d, operand_desc(sa, ti.a_mode, kk),
+                                                        operand_desc(sb, ti.b_mode, kk), idesc,
+                                                        (slot > 0 || term > 0 || kk > 0) ? 1u : 0u);
+                        }
+                    } else {
+                        const uint32_t sa = base;
+                        const uint32_t sb = (kCtas == 2 && ti.b_is_a) ? sa : sa + kRows128Bytes;
+#pragma unroll
+                        for (int kk = 0; kk < BK / UMMA_K; ++kk)
+                            tcgen05_mma_bf16<kCtas>(tmem_d, operand_desc(sa, ti.a_mode, kk),
+                                                    operand_desc(sb, ti.b_mode, kk), idesc, (slot > 0 || kk > 0) ? 1u : 0u);
+                    }
                     tcgen05_commit<kCtas>(&bars->empty[stage]);  // slot reusable once these MMAs have read it
-                    if (++stage == C::kStages) {
+                    if (++stage == kRing) {
                         stage = 0;
                         phase ^= 1u;
                     }
