@@ -665,6 +665,13 @@ int upload(T **d, const std::vector<T> &h, cudaStream_t stream)
 
 }  // namespace
 
+// VB_TC_NO_TRANSPOSE=1 keeps the direct form X' = X C for tall matrices (for comparison).
+static bool use_transposed_update()
+{
+    const char *e = getenv("VB_TC_NO_TRANSPOSE");
+    return !(e && *e == '1');
+}
+
 struct MuonState {
     std::vector<int> owner;           // per tensor
     std::vector<int64_t> local_off;   // per tensor: offset into this rank's buffers, -1 if not owned
@@ -710,7 +717,8 @@ struct MuonState {
     uint8_t *d_fold_norm = nullptr;    // per tensor: normalisation folded into the first iteration
     bool fold_norm = false;
     GemmTile *d_tc_gram_tiles = nullptr, *d_tc_upd_tiles = nullptr;
-    int n_tc_gram_tiles = 0, n_tc_upd_tiles = 0;
+    GemmTile *d_tc_upd_tiles_last = nullptr;  // the last iteration's update is always in the direct form
+    int n_tc_gram_tiles = 0, n_tc_upd_tiles = 0, n_tc_upd_tiles_last = 0;
     int *d_error = nullptr;
     int *h_error = nullptr;              // pinned mirror of d_error, refreshed after every step
     double flops_per_step = 0.0;
@@ -751,6 +759,7 @@ void destroy_muon_state(MuonState *s)
     cudaFree(s->d_upd_tiles);
     cudaFree(s->d_tc_gram_tiles);
     cudaFree(s->d_tc_upd_tiles);
+    cudaFree(s->d_tc_upd_tiles_last);
     cudaFree(s->d_error);
     if (s->h_error) cudaFreeHost(s->h_error);
     delete s;
@@ -982,7 +991,7 @@ int muon_init(vb_optimizer *opt)
         tc_gemm_tile_shape(&bm, &bn);
         const int iters = opt->ns_steps;
         std::vector<std::vector<TcGemmProblem>> gram((size_t)iters), upd((size_t)iters);
-        std::vector<GemmTile> gram_tiles, upd_tiles;
+        std::vector<GemmTile> gram_tiles, upd_tiles, upd_tiles_last;
         std::stable_sort(tc_tensors.begin(), tc_tensors.end(), by_size);
         // plain bf16 path: the momentum kernel writes the unnormalised bf16 operand and the first
         // iteration's epilogues apply 1/norm; the split path keeps the reference's true division
@@ -1034,12 +1043,19 @@ int muon_init(vb_optimizer *opt)
                 // C is symmetric, so it can be staged either way round; the tensor core reads an
                 // MN-major A operand measurably faster than a K-major one (wide update: +7.6 %), so
                 // as the A operand C is staged MN-major.
+                // Tall matrices on the plain bf16 path go one step further and compute the transposed
+                // product (X C)^T = C X^T: A = C (MN-major), B = X with its rows as the n index
+                // (K-major), and the epilogue stores each element at the transposed position, which is
+                // X' in its ordinary row-major layout (+5 % on the tall update GEMMs).
+                // (not in the last iteration, whose f32 result would go out in 4-byte pieces)
+                const bool upd_t = tall && planes == 1 && !last && use_transposed_update();
                 TcGemmProblem u{};
-                u.map_a = tall ? map_x_k[par] : map_c_mn;
-                u.map_b = tall ? map_c : map_x_mn[par];
-                u.M = r; u.N = c; u.K = sh;
-                u.a_mode = tall ? TC_OP_K_MAJOR : c_mn_mode;
+                u.map_a = upd_t ? map_c_mn : (tall ? map_x_k[par] : map_c_mn);
+                u.map_b = upd_t ? map_x_k[par] : (tall ? map_c : map_x_mn[par]);
+                u.M = upd_t ? sh : r; u.N = upd_t ? r : c; u.K = sh;
+                u.a_mode = (upd_t || !tall) ? c_mn_mode : TC_OP_K_MAJOR;
                 u.b_mode = tall ? TC_OP_K_MAJOR : mn_mode;
+                u.transpose_out = upd_t ? 1 : 0;
                 u.epilogue = planes > 1 ? TC_EPI_NS_COMBINE : TC_EPI_HALF; u.ld_out = c; u.tensor = t;
                 u.in_bf16 = xb[par];
                 u.n_terms = n_terms; u.n_out_planes = planes; u.out_plane_stride = s->owned_elems;
@@ -1067,8 +1083,11 @@ int muon_init(vb_optimizer *opt)
                     if (bm == bn && n0 == m0 && planes == 1) flags |= GEMM_TILE_B_IS_A;
                     gram_tiles.push_back(GemmTile{pidx, m0, n0, flags});
                 }
+            const bool upd_t = tall && planes == 1 && use_transposed_update();  // as above: the update computes (X C)^T
+            for (int m0 = 0; m0 < (upd_t ? sh : r); m0 += bm)
+                for (int n0 = 0; n0 < (upd_t ? r : c); n0 += bn) upd_tiles.push_back(GemmTile{pidx, m0, n0, 0});
             for (int m0 = 0; m0 < r; m0 += bm)
-                for (int n0 = 0; n0 < c; n0 += bn) upd_tiles.push_back(GemmTile{pidx, m0, n0, 0});
+                for (int n0 = 0; n0 < c; n0 += bn) upd_tiles_last.push_back(GemmTile{pidx, m0, n0, 0});
             // executed tensor-core FLOPs: three plane products per product on the split path; the
             // Gram counts only the tiles that are computed
             const double prod = 2.0 * (double)std::max(r, c) * (double)sh * (double)sh;
@@ -1083,6 +1102,8 @@ int muon_init(vb_optimizer *opt)
         }
         VB_TRY(upload(&s->d_tc_gram_tiles, gram_tiles, e->stream));
         VB_TRY(upload(&s->d_tc_upd_tiles, upd_tiles, e->stream));
+        VB_TRY(upload(&s->d_tc_upd_tiles_last, upd_tiles_last, e->stream));
+        s->n_tc_upd_tiles_last = (int)upd_tiles_last.size();
         s->n_tc_gram_tiles = (int)gram_tiles.size();
         s->n_tc_upd_tiles = (int)upd_tiles.size();
     }
@@ -1163,7 +1184,9 @@ int muon_step(vb_optimizer *opt, uint32_t flags)
                 const bool split = s->planes > 1;
                 VB_TRY(launch_ns_gemm_tc(s->d_tc_gram[(size_t)it], s->d_tc_gram_tiles, s->n_tc_gram_tiles,
                                          opt->d_present, s->d_error, e->sm_count, e->stream, 0, split));
-                VB_TRY(launch_ns_gemm_tc(s->d_tc_upd[(size_t)it], s->d_tc_upd_tiles, s->n_tc_upd_tiles,
+                const bool last_it = it == opt->ns_steps - 1;
+                VB_TRY(launch_ns_gemm_tc(s->d_tc_upd[(size_t)it], last_it ? s->d_tc_upd_tiles_last : s->d_tc_upd_tiles,
+                                         last_it ? s->n_tc_upd_tiles_last : s->n_tc_upd_tiles,
                                          opt->d_present, s->d_error, e->sm_count, e->stream, 0, split));
                 e->launches += 2;
             }

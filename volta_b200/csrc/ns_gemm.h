@@ -87,6 +87,7 @@ struct alignas(128) TcGemmProblem {
     int32_t ld_out;
     int32_t tensor;          // index into the optimizer's gradient-presence bytes
     int32_t withhold_loads;  // test hook: the producer stages nothing, so the consumers' bounded waits expire
+    int32_t transpose_out;   // plain kernel: D[m][n] is stored at out[n * ld_out + m] (the output matrix is D^T)
     int32_t n_terms;         // 1: plain bf16 operands; 3: operands held as two f16 planes (f32-accurate)
     int32_t n_out_planes;    // planes written to out_bf16: 1 (bf16 rounding) or 3 (split)
     int64_t out_plane_stride;  // elements between output planes

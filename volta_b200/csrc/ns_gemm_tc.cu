@@ -385,7 +385,7 @@ __device__ __forceinline__ int term_plane_b(int n_terms, int term) { return n_te
 template <int EPI>
 __device__ __forceinline__ void drain_chunk_fast(const uint32_t (&v)[32], float mult, bool diagonal_piece, int lane,
                                                  __nv_bfloat16 *__restrict__ dst_bf16, float *__restrict__ dst_f32,
-                                                 __nv_bfloat16 *__restrict__ mirror_dst, int64_t ld)
+                                                 __nv_bfloat16 *__restrict__ mirror_dst, float *__restrict__ t_f32, int64_t ld)
 {
     float f[32];
 #pragma unroll
@@ -403,6 +403,10 @@ __device__ __forceinline__ void drain_chunk_fast(const uint32_t (&v)[32], float 
             st_global_256(dst_f32 + g8 * 8, q);
         }
     }
+    if (t_f32) {  // transposed output: for a fixed column the warp's 32 rows are 128 contiguous bytes
+#pragma unroll
+        for (int j = 0; j < 32; ++j) t_f32[(int64_t)j * ld] = f[j];
+    }
     if (dst_bf16) {
 #pragma unroll
         for (int g16 = 0; g16 < 2; ++g16) {
@@ -411,16 +415,17 @@ __device__ __forceinline__ void drain_chunk_fast(const uint32_t (&v)[32], float 
             for (int j = 0; j < 8; ++j) q[j] = pack_bf16(f[g16 * 16 + 2 * j], f[g16 * 16 + 2 * j + 1]);
             st_global_256(dst_bf16 + g16 * 16, q);
         }
-        if (mirror_dst) {  // symmetric product: element (row, col) also goes to (col, row)
+    }
+    if (mirror_dst) {  // symmetric product (element (row, col) also goes to (col, row)) or transposed output
 #pragma unroll
-            for (int j = 0; j < 32; ++j) mirror_dst[(int64_t)j * ld] = __float2bfloat16_rn(f[j]);
-        }
+        for (int j = 0; j < 32; ++j) mirror_dst[(int64_t)j * ld] = __float2bfloat16_rn(f[j]);
     }
 }
 
 template <int EPI>
 __device__ __forceinline__ void drain_fast(uint32_t taddr, int row, int tile_col0, bool row_ok, float mult, int lane,
-                                           __nv_bfloat16 *out_bf16, float *out_f32, bool mirror, int64_t ld)
+                                           __nv_bfloat16 *out_bf16, float *out_f32, bool mirror, bool transpose,
+                                           int64_t ld)
 {
     constexpr int kPieces = (BN / 2) / 32;
     uint32_t v[2][32];
@@ -431,10 +436,13 @@ __device__ __forceinline__ void drain_fast(uint32_t taddr, int row, int tile_col
         tmem_ld_wait();
         if (cc + 1 < kPieces) tmem_ld_32x32(taddr + (uint32_t)((cc + 1) * 32), v[(cc + 1) & 1]);
         if (row_ok) {
-            const int64_t at = (int64_t)row * ld + col0;
-            drain_chunk_fast<EPI>(v[cc & 1], mult, row - col0 == lane, lane, out_bf16 ? out_bf16 + at : nullptr,
-                                  out_f32 ? out_f32 + at : nullptr,
-                                  (mirror && out_bf16) ? out_bf16 + (int64_t)col0 * ld + row : nullptr, ld);
+            const int64_t at = (int64_t)row * ld + col0;        // D[row][col0]
+            const int64_t at_t = (int64_t)col0 * ld + row;      // the same element of the transposed matrix
+            drain_chunk_fast<EPI>(v[cc & 1], mult, row - col0 == lane, lane,
+                                  (out_bf16 && !transpose) ? out_bf16 + at : nullptr,
+                                  (out_f32 && !transpose) ? out_f32 + at : nullptr,
+                                  (out_bf16 && (mirror || transpose)) ? out_bf16 + at_t : nullptr,
+                                  (out_f32 && transpose) ? out_f32 + at_t : nullptr, ld);
         }
     }
 }
@@ -447,7 +455,7 @@ struct DrainArgs {
     float acc_scale;
     int64_t ld, plane_stride;
     int out_planes, out_planes_in;
-    bool bf16_rows_32b, mirror;
+    bool bf16_rows_32b, mirror, transpose;
     __nv_bfloat16 *out_bf16;
     float *out_f32;
     const __nv_bfloat16 *in_bf16;
@@ -484,7 +492,8 @@ __device__ __forceinline__ void drain_generic(const DrainArgs &a)
     const float acc_scale = a.acc_scale;
     const int64_t ld = a.ld, plane_stride = a.plane_stride;
     const int out_planes = a.out_planes, out_planes_in = a.out_planes_in;
-    const bool bf16_rows_32b = a.bf16_rows_32b, mirror = a.mirror;
+    const bool bf16_rows_32b = a.bf16_rows_32b, transpose = a.transpose;
+    const bool mirror = a.mirror || transpose;  // the transposed position is written in both cases
     __nv_bfloat16 *out_bf16 = a.out_bf16;
     float *out_f32 = a.out_f32;
     const __nv_bfloat16 *in_bf16 = a.in_bf16;
@@ -531,7 +540,13 @@ __device__ __forceinline__ void drain_generic(const DrainArgs &a)
 #pragma unroll
                 for (int j = 0; j < 32; ++j) f[j] = fmaf(1.5f, x[j] * kSplitInvScale, -0.5f * f[j]);
             }
-            if (out_f32) {
+            if (out_f32 && transpose) {
+                float *tdst = out_f32 + (int64_t)col0 * ld + row;
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (col0 + j < N) tdst[(int64_t)j * ld] = f[j];
+            }
+            if (out_f32 && !transpose) {
                 float *dst = out_f32 + (int64_t)row * ld + col0;
 #pragma unroll
                 for (int g8 = 0; g8 < 4; ++g8) {  // 8 columns = one 32-byte sector per store
@@ -551,6 +566,7 @@ __device__ __forceinline__ void drain_generic(const DrainArgs &a)
                     __nv_bfloat16 *dst = out_bf16 + pl * plane_stride + (int64_t)row * ld + col0;
 #pragma unroll
                     for (int g16 = 0; g16 < 2; ++g16) {  // 16 columns = one 32-byte sector per store
+                        if (transpose) break;            // only the transposed position is written
                         const int col = col0 + g16 * 16;
                         if (col + 16 <= N && bf16_rows_32b) {
                             uint32_t q[8];
@@ -847,6 +863,7 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
             const int out_planes_in = kSplit ? kSplitPlanes : 1;  // planes of the operands (and of in_bf16)
             const int64_t plane_stride = p->out_plane_stride;
             const bool bf16_rows_32b = (ld % 16) == 0;  // every bf16 output row starts on a 32-byte boundary
+            const bool transpose = !kSplit && p->transpose_out != 0;
             if (!MBAR_WAIT(3, &bars->tmem_full[acc], acc_phase)) {
                 ok = false;
                 break;
@@ -867,20 +884,20 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
                 // (a * s) * 0.5 == a * (s * 0.5) and -(a * s) == a * (-s) exactly
                 if (epi == TC_EPI_HALF)
                     drain_fast<TC_EPI_HALF>(taddr, row, tile_col0, row < M, 0.5f * acc_scale, lane, out_bf16, out_f32,
-                                            ti.mirror, ld);
+                                            ti.mirror, transpose, ld);
                 else if (epi == TC_EPI_THREE_I_MINUS)
                     drain_fast<TC_EPI_THREE_I_MINUS>(taddr, row, tile_col0, row < M, -acc_scale, lane, out_bf16,
-                                                     out_f32, ti.mirror, ld);
+                                                     out_f32, ti.mirror, transpose, ld);
                 else
                     drain_fast<TC_EPI_IDENTITY>(taddr, row, tile_col0, row < M, acc_scale, lane, out_bf16, out_f32,
-                                                ti.mirror, ld);
+                                                ti.mirror, transpose, ld);
             }
             if (!fast) {
                 DrainArgs da;
                 da.taddr = taddr; da.row = row; da.tile_col0 = tile_col0; da.M = M; da.N = N; da.epi = epi;
                 da.lane = lane; da.acc_scale = acc_scale; da.ld = ld; da.plane_stride = plane_stride;
                 da.out_planes = out_planes; da.out_planes_in = out_planes_in; da.bf16_rows_32b = bf16_rows_32b;
-                da.mirror = ti.mirror; da.out_bf16 = out_bf16; da.out_f32 = out_f32; da.in_bf16 = in_bf16;
+                da.mirror = ti.mirror; da.transpose = transpose; da.out_bf16 = out_bf16; da.out_f32 = out_f32; da.in_bf16 = in_bf16;
                 drain_generic<kSplit>(da);
             }
             tcgen05_fence_before();
