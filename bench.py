@@ -294,7 +294,7 @@ def run_ours(args):
     # (blocks until they are in host memory).  N > 1: a rank moves only its own slice over PCIe
     # (what a reduce-scatter would hand it, and the parameters it updated).
     for _ in range(e2e_steps):
-        opt.step_host(grads_pinned.array, params_pinned.array, pieces=32)
+        opt.step_host(grads_pinned.array, params_pinned.array, pieces=max(4, 32 // world))  # ~14 MB per piece
     barrier()
     e2e_s = max_over_ranks((time.perf_counter() - t0) / max(e2e_steps, 1))
 
