@@ -179,6 +179,30 @@ C3_WORKLOAD = ("c3_transformer_adam: Adam lr=1e-3 betas=(0.9,0.999) eps=1e-8 wd=
                "109602816 f32 params")
 
 
+def bind_near_gpu(local_rank: int):
+    """Runs this rank on the CPUs of its GPU's NUMA node, so that the pinned host buffers it allocates
+    afterwards (first touch) and its copy threads sit next to the GPU's PCIe root.  Best effort: returns
+    the node, or None where the topology is not exposed."""
+    try:
+        import torch
+        pr = torch.cuda.get_device_properties(local_rank)
+        bdf = f"{pr.pci_domain_id:04x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
+        node = int(open(f"/sys/bus/pci/devices/{bdf.lower()}/numa_node").read().strip())
+        if node < 0:
+            return None
+        cpus = set()
+        for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        cpus &= os.sched_getaffinity(0)
+        if not cpus:
+            return None
+        os.sched_setaffinity(0, cpus)
+        return node
+    except (OSError, ValueError, AttributeError, TypeError):
+        return None
+
+
 def gather_handles(mine: bytes, world: int, dev):
     """Every rank's 64-byte CUDA IPC handle, in rank order (torch.distributed is the transport)."""
     import torch
@@ -204,6 +228,7 @@ def run_ours(args):
             raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run (one rank per GPU)")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    numa_node = bind_near_gpu(local_rank) if world > 1 else None
     eng = Engine(local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
@@ -378,7 +403,8 @@ def run_ours(args):
                      "launch_ms": kernel_avg_ms},
         "e2e": {"value": wl.total / e2e_s, "unit": "params/s", "h2d_bytes_per_step": arena * 4,
                 "d2h_bytes_per_step": arena * 4, "ms_per_step": e2e_s * 1e3, "steps": e2e_steps,
-                "note": "bytes are totals over all ranks; each rank moves its own 1/N slice of the arena"},
+                "note": "bytes are totals over all ranks; each rank moves its own 1/N slice of the arena",
+                "rank0_numa_node": numa_node},
         "gpu_launches": int(launches),
         "clocks": clocks,
     }
