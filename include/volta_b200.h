@@ -72,9 +72,9 @@ typedef enum vb_ns_mode {
      * scaled by 2^15 (22 significand bits; Newton-Schulz operands are bounded by 1 once the
      * update is normalised) and each product is three tcgen05 f16 products accumulated in f32;
      * the sum of squares keeps the reference's sequential order.  Same target as VB_NS_F32
-     * (<= 1e-5) at tensor-core speed, but not bit-identical to the CPU arithmetic.  An update
-     * whose norm is at most 1e-8 is not normalised by the reference (src/nn/optim/muon.rs:60);
-     * such an update is below the range of the f16 pieces and comes out as zero here. */
+     * (<= 1e-5) at tensor-core speed, but not bit-identical to the CPU arithmetic.  Updates far
+     * smaller than sqrt(1e-8), whose normalised form is tiny (src/nn/optim/muon.rs:59), are held
+     * with a larger power of two so that the bound covers them as well. */
     VB_NS_F32_TC = 2
 } vb_ns_mode;
 

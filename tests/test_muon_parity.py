@@ -261,3 +261,27 @@ def test_f32_tc_path_c4_layer_shapes(oracle, engine):
         assert rel_frobenius(got, oracle.newton_schulz(u, 5)) <= TOL_F32
         assert rel_frobenius(got, oracle.newton_schulz(u, 5, gemm_mode=1)) <= TOL_F32
     opt.close()
+
+
+def test_f32_tc_tiny_updates(oracle, engine):
+    """Updates far smaller than sqrt(1e-8): the 1e-8 under the root dominates the norm
+    (muon.rs:59), the normalised update is tiny and the f16 pieces are held with a larger power of
+    two so that they stay in the normal f16 range.  Same 1e-5 bound; zero gradients give zero."""
+    from volta_b200 import VB_NS_F32_TC, Muon, Tensor
+    rng = np.random.default_rng(21)
+    for scale in (1e-15, 1e-13, 1e-11, 1e-9, 1e-7, 1e-5):
+        g = (rng.standard_normal((128, 64)) * scale).astype(np.float32)
+        w = Tensor(np.ones((128, 64), np.float32))
+        opt = Muon([w], 0.1, 0.0, False, 5, ns_mode=VB_NS_F32_TC, engine=engine)
+        w.grad = g
+        opt.step()
+        got = opt.last_update(0)
+        assert np.all(np.isfinite(got))
+        assert rel_frobenius(got, oracle.newton_schulz(g, 5)) <= TOL_F32, scale
+        opt.close()
+    w = Tensor(np.ones((128, 64), np.float32))
+    opt = Muon([w], 0.1, 0.0, False, 5, ns_mode=VB_NS_F32_TC, engine=engine)
+    w.grad = np.zeros((128, 64), np.float32)
+    opt.step()
+    assert not np.any(opt.last_update(0)) and np.array_equal(w.data, np.ones((128, 64), np.float32))
+    opt.close()

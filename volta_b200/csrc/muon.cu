@@ -536,6 +536,7 @@ normalise_kernel(const TensorDesc *__restrict__ tensors, const ChunkDesc *__rest
         if (kind == 3) {
             __nv_bfloat16 *xb = xb_base + (u - upd_base);
             unsigned short *xh = reinterpret_cast<unsigned short *>(xb);
+            const float kScale = ldexpf(1.0f, 15 - split_exponent(sumsq[ch.tensor]));  // 2^15 unless the update is tiny
             for (uint32_t i = threadIdx.x; i < n4; i += kEwThreads) {
                 float4 v = reinterpret_cast<const float4 *>(u)[i];
                 if (scale) {
@@ -543,10 +544,10 @@ normalise_kernel(const TensorDesc *__restrict__ tensors, const ChunkDesc *__rest
                     v.z = __fdiv_rn(v.z, norm); v.w = __fdiv_rn(v.w, norm);
                 }
                 unsigned short p[2][4];
-                split_f16(v.x * kSplitScale, p[0][0], p[1][0]);
-                split_f16(v.y * kSplitScale, p[0][1], p[1][1]);
-                split_f16(v.z * kSplitScale, p[0][2], p[1][2]);
-                split_f16(v.w * kSplitScale, p[0][3], p[1][3]);
+                split_f16(v.x * kScale, p[0][0], p[1][0]);
+                split_f16(v.y * kScale, p[0][1], p[1][1]);
+                split_f16(v.z * kScale, p[0][2], p[1][2]);
+                split_f16(v.w * kScale, p[0][3], p[1][3]);
 #pragma unroll
                 for (int pl = 0; pl < kSplitPlanes; ++pl) {
                     uint2 packed;
@@ -557,7 +558,7 @@ normalise_kernel(const TensorDesc *__restrict__ tensors, const ChunkDesc *__rest
             }
             for (uint32_t i = (n4 << 2) + threadIdx.x; i < n; i += kEwThreads) {
                 unsigned short h0, h1;
-                split_f16((scale ? __fdiv_rn(u[i], norm) : u[i]) * kSplitScale, h0, h1);
+                split_f16((scale ? __fdiv_rn(u[i], norm) : u[i]) * kScale, h0, h1);
                 xh[i] = h0;
                 xh[plane_stride + i] = h1;
             }
@@ -1058,6 +1059,7 @@ int muon_init(vb_optimizer *opt)
                 u.transpose_out = upd_t ? 1 : 0;
                 u.epilogue = planes > 1 ? TC_EPI_NS_COMBINE : TC_EPI_HALF; u.ld_out = c; u.tensor = t;
                 u.in_bf16 = xb[par];
+                if (planes > 1) u.split_sumsq = s->d_sumsq + t;
                 u.n_terms = n_terms; u.n_out_planes = planes; u.out_plane_stride = s->owned_elems;
                 u.out_bf16 = xb[par ^ 1]; u.out_f32 = nullptr;
                 if (first && s->fold_norm) {  // X1 = 0.5 (u C) / norm

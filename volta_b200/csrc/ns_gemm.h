@@ -24,6 +24,24 @@ __device__ __forceinline__ float f16_bits_to_float(uint32_t bits16)
 {
     return __half2float(__ushort_as_half((unsigned short)bits16));
 }
+// Exponent e <= 0 of the power of two that bounds every Newton-Schulz iterate of a matrix whose
+// update has the sequential sum of squares `sumsq`: the normalised update x = u / sqrt(sumsq + 1e-8)
+// has Frobenius norm phi <= 1, every singular value of an iterate is at most min(1, 1.5^it phi)
+// (sigma' = 1.5 sigma - 0.5 sigma^3), and 8 phi covers five iterations.  X is then held scaled by
+// 2^(15 - e) and the Gram by 2^(15 - 2e), which keeps both planes in the normal f16 range also for
+// updates far smaller than sqrt(1e-8).  e = 0 whenever phi >= 1/16, i.e. for every update whose
+// norm is not dwarfed by the 1e-8 under the root.  Same inputs, same result, wherever it is called.
+__device__ __forceinline__ int split_exponent(float sumsq)
+{
+    const float root = __fsqrt_rn(sumsq);
+    const float norm = __fsqrt_rn(__fadd_rn(sumsq, 1e-8f));
+    const float phi = norm > 1e-8f ? __fdiv_rn(root, norm) : root;
+    const float b = fminf(1.0f, 8.0f * phi);
+    if (!(b > 0.0f)) return -40;
+    int ex;
+    (void)frexpf(b, &ex);  // b = m * 2^ex with m in [0.5, 1): b < 2^ex
+    return ex > 0 ? 0 : (ex < -40 ? -40 : ex);
+}
 // scaled value -> its two f16 planes: h0 = f16(xs), h1 = f16(xs - h0) (the difference is exact)
 __device__ __forceinline__ void split_f16(float xs, unsigned short &h0, unsigned short &h1)
 {
@@ -91,6 +109,7 @@ struct alignas(128) TcGemmProblem {
     int32_t n_terms;         // 1: plain bf16 operands; 3: operands held as two f16 planes (f32-accurate)
     int32_t n_out_planes;    // planes written to out_bf16: 1 (bf16 rounding) or 3 (split)
     int64_t out_plane_stride;  // elements between output planes
+    const float *split_sumsq;      // split kernel, update problems: the matrix's sum of squares (see split_exponent)
     const float *scale_sumsq;      // if set: the accumulator is scaled by s^scale_power, s = 1/sqrt(*scale_sumsq + 1e-8)
                                    // (the Frobenius normalisation of muon.rs:59-64 folded into the first iteration)
     int32_t scale_power;           // 1 or 2

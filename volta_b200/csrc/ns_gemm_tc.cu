@@ -451,7 +451,7 @@ __device__ __forceinline__ void drain_fast(uint32_t taddr, int row, int tile_col
 // split (f32-accurate) kernel's epilogues.  Element-wise code with the bounds checks inside.
 struct DrainArgs {
     uint32_t taddr;
-    int row, tile_col0, M, N, epi, lane;
+    int row, tile_col0, M, N, epi, lane, split_e;
     float acc_scale;
     int64_t ld, plane_stride;
     int out_planes, out_planes_in;
@@ -538,7 +538,14 @@ __device__ __forceinline__ void drain_generic(const DrainArgs &a)
                     }
                 }
 #pragma unroll
-                for (int j = 0; j < 32; ++j) f[j] = fmaf(1.5f, x[j] * kSplitInvScale, -0.5f * f[j]);
+                for (int j = 0; j < 32; ++j) f[j] = fmaf(1.5f, x[j], -0.5f * f[j]);  // X' scaled by 2^(15 - e)
+            }
+            // the update of the split kernel is in the scaled domain: what goes out in f32 is scaled back
+            const bool scaled = kSplit && epi == TC_EPI_NS_COMBINE;
+            if (scaled && out_f32) {
+                const float back = ldexpf(1.0f, a.split_e - 15);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) f[j] *= back;
             }
             if (out_f32 && transpose) {
                 float *tdst = out_f32 + (int64_t)col0 * ld + row;
@@ -558,7 +565,7 @@ __device__ __forceinline__ void drain_generic(const DrainArgs &a)
                 }
             }
             if (out_bf16) {
-                if (kSplit) {  // the planes hold the value times 2^15
+                if (kSplit && !scaled) {  // the planes hold the value times 2^15 (the update is scaled already)
 #pragma unroll
                     for (int j = 0; j < 32; ++j) f[j] *= kSplitScale;
                 }
@@ -852,7 +859,14 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
             const __nv_bfloat16 *in_bf16 = p->in_bf16;  // TC_EPI_NS_COMBINE: the planes of X at the output position
             // Frobenius normalisation folded into the first iteration (plain bf16 path): the operand is
             // the unnormalised update u, the accumulator is scaled by 1/norm (or its square)
-            float acc_scale = kSplit ? kSplitInvScale * kSplitInvScale : 1.0f;  // split operands carry 2^15 each
+            // split operands carry 2^15 each (Gram: acc = 2^30 G, the exponent of tiny updates cancels
+            // in what is stored); the update works in the scaled domain, see drain_generic
+            float acc_scale = kSplit ? kSplitInvScale * kSplitInvScale : 1.0f;
+            int split_e = 0;
+            if (kSplit && epi == TC_EPI_NS_COMBINE) {
+                if (p->split_sumsq) split_e = split_exponent(*p->split_sumsq);
+                acc_scale = ldexpf(1.0f, 2 * split_e - 15);  // acc = 2^(30 - 3e) (X G)  ->  2^(15 - e) (X G)
+            }
             if (!kSplit && p->scale_sumsq) {
                 const float norm = sqrtf(*p->scale_sumsq + 1e-8f);  // muon.rs:59
                 const float inv = norm > 1e-8f ? 1.0f / norm : 1.0f;  // muon.rs:60
@@ -895,7 +909,7 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
             if (!fast) {
                 DrainArgs da;
                 da.taddr = taddr; da.row = row; da.tile_col0 = tile_col0; da.M = M; da.N = N; da.epi = epi;
-                da.lane = lane; da.acc_scale = acc_scale; da.ld = ld; da.plane_stride = plane_stride;
+                da.lane = lane; da.acc_scale = acc_scale; da.split_e = split_e; da.ld = ld; da.plane_stride = plane_stride;
                 da.out_planes = out_planes; da.out_planes_in = out_planes_in; da.bf16_rows_32b = bf16_rows_32b;
                 da.mirror = ti.mirror; da.transpose = transpose; da.out_bf16 = out_bf16; da.out_f32 = out_f32; da.in_bf16 = in_bf16;
                 drain_generic<kSplit>(da);
