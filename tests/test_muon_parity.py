@@ -285,3 +285,22 @@ def test_f32_tc_tiny_updates(oracle, engine):
     opt.step()
     assert not np.any(opt.last_update(0)) and np.array_equal(w.data, np.ones((128, 64), np.float32))
     opt.close()
+
+
+@pytest.mark.parametrize("mode_name", ["bf16", "f32_tc"])
+def test_tensor_core_paths_across_gradient_scales(oracle, engine, mode_name):
+    """Gradient magnitudes from 1e-15 to 1e15: the tensor-core paths stay finite and inside their
+    bounds (bf16 operands have f32's range; the f16 pieces carry a per-matrix power of two)."""
+    from volta_b200 import VB_NS_BF16, VB_NS_F32_TC, Muon, Tensor
+    mode, tol = (VB_NS_BF16, TOL_BF16) if mode_name == "bf16" else (VB_NS_F32_TC, TOL_F32)
+    rng = np.random.default_rng(5)
+    for scale in (1e-15, 1e-10, 1e-6, 1.0, 1e4, 1e8, 1e15):
+        g = (rng.standard_normal((256, 128)) * scale).astype(np.float32)
+        w = Tensor(np.ones((256, 128), np.float32))
+        opt = Muon([w], 0.1, 0.0, False, 5, ns_mode=mode, engine=engine)
+        w.grad = g
+        opt.step()
+        got = opt.last_update(0)
+        assert np.all(np.isfinite(got)), scale
+        assert rel_frobenius(got, oracle.newton_schulz(g, 5)) <= tol, scale
+        opt.close()
