@@ -414,3 +414,39 @@ def test_pipelined_host_step_matches_oracle(oracle, engine, pieces):
     opt.close()
     gbuf.free()
     pbuf.free()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("kind", ["adam", "sgd_momentum"])
+def test_special_values_follow_ieee_like_the_cpu(oracle, engine, kind):
+    """Zeros of both signs, subnormals, the largest finite numbers, infinities and NaN in parameters
+    and gradients: the kernels use IEEE division / square root / fused multiply-add without flushing
+    subnormals, so every finite or infinite result has the CPU's bits and NaN appears exactly where
+    the CPU produces one (NaN payloads are not compared)."""
+    from volta_b200 import SGD, Adam, Tensor
+    specials = np.array([0.0, -0.0, 1e-45, -1e-45, 1e-39, 1.1754944e-38, 3.4028235e38, -3.4028235e38,
+                         np.inf, -np.inf, np.nan, 1.0, -1.0, 1e-20, 1e20, 65504.0], np.float32)
+    p0 = np.repeat(specials, specials.size)           # every parameter value ...
+    g0 = np.tile(specials, specials.size)             # ... against every gradient value
+    t = Tensor(p0.copy())
+    ref = [p0.copy()]
+    if kind == "adam":
+        opt, o = Adam([t], 1e-3, (0.9, 0.999), 1e-8, 0.01, engine=engine), oracle.Adam(ref, 1e-3, (0.9, 0.999), 1e-8, 0.01)
+    else:
+        opt, o = SGD([t], 0.01, 0.9, 5e-4, engine=engine), oracle.SGD(ref, 0.01, 0.9, 5e-4)
+    with np.errstate(all="ignore"):
+        for step in range(3):
+            t.grad = g0
+            opt.step()
+            o.step([g0])
+            got, want = t.data.reshape(-1), ref[0].reshape(-1)
+            nan_g, nan_w = np.isnan(got), np.isnan(want)
+            assert np.array_equal(nan_g, nan_w), step
+            assert np.array_equal(got[~nan_g].view(np.uint32), want[~nan_w].view(np.uint32)), step
+            for which in range(2 if kind == "adam" else 1):
+                cpu_state = ([o.m, o.v] if kind == "adam" else [o.velocity])[which][0]
+                sg, sw = opt.state(0, which).reshape(-1), cpu_state.reshape(-1)
+                assert np.array_equal(np.isnan(sg), np.isnan(sw))
+                m = ~np.isnan(sg)
+                assert np.array_equal(sg[m].view(np.uint32), sw[m].view(np.uint32)), (step, which)
+    opt.close()
