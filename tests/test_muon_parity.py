@@ -304,3 +304,28 @@ def test_tensor_core_paths_across_gradient_scales(oracle, engine, mode_name):
         assert np.all(np.isfinite(got)), scale
         assert rel_frobenius(got, oracle.newton_schulz(g, 5)) <= tol, scale
         opt.close()
+
+
+@pytest.mark.parametrize("ns_steps", [0, 1, 2, 3, 6])
+@pytest.mark.parametrize("mode_name", ["bf16", "f32_tc", "f32"])
+def test_iteration_counts(oracle, engine, mode_name, ns_steps):
+    """First == last iteration, odd and even counts, none at all: tall, wide and square matrices
+    (the tall update changes form between the last iteration and the others)."""
+    from volta_b200 import VB_NS_BF16, VB_NS_F32, VB_NS_F32_TC, Muon, Tensor
+    mode, tol = {"bf16": (VB_NS_BF16, TOL_BF16), "f32_tc": (VB_NS_F32_TC, TOL_F32), "f32": (VB_NS_F32, 0.0)}[mode_name]
+    rng = np.random.default_rng(100 + ns_steps)
+    shapes = [(512, 256), (256, 512), (256, 256), (264, 72)]
+    grads = [(rng.standard_normal(s) * 1e-3).astype(np.float32) for s in shapes]
+    tensors = [Tensor(np.zeros(s, np.float32)) for s in shapes]
+    opt = Muon(tensors, 0.1, 0.0, False, ns_steps, ns_mode=mode, engine=engine)
+    for t, g in zip(tensors, grads):
+        t.grad = g
+    opt.step()
+    for i, g in enumerate(grads):
+        got, ref = opt.last_update(i), oracle.newton_schulz(g, ns_steps)
+        if mode_name == "f32" or ns_steps == 0:
+            # no iteration: the result is the normalised update itself, exact on every path
+            assert bits_equal(got, ref) or rel_frobenius(got, ref) <= tol, (shapes[i], rel_frobenius(got, ref))
+        else:
+            assert rel_frobenius(got, ref) <= tol, (shapes[i], rel_frobenius(got, ref))
+    opt.close()
