@@ -75,3 +75,26 @@ def test_bf16_only_exchange_needs_the_copies(engine):
     with pytest.raises(VoltaB200Error):
         opt.bf16_params(0)
     opt.close()
+
+
+def test_copies_follow_the_pipelined_host_step(engine):
+    """vb_optimizer_step_host with the copies enabled: every piece's update kernel writes them too."""
+    import workloads
+    from volta_b200 import Adam, PinnedBuffer, Tensor
+    wl = workloads.c5_ragged_adam(n_tensors=120, max_log2=15, seed=31)
+    h = wl.hyper
+    tensors = [Tensor(p, p.shape) for p in wl.make_params()]
+    opt = Adam(tensors, h["lr"], h["betas"], h["eps"], h["weight_decay"], engine=engine)
+    opt.enable_bf16_params()
+    _, _, arena, offsets = opt.arena_layout()
+    gbuf, pbuf = PinnedBuffer(arena), PinnedBuffer(arena)
+    gbuf.array[:] = 0
+    for s in (1, 2):
+        for o, g in zip(offsets, wl.make_grads(s)):
+            gbuf.array[o:o + g.size] = g.reshape(-1)
+        opt.step_host(gbuf.array, pbuf.array, pieces=5)
+        for i, (o, t) in enumerate(zip(offsets, tensors)):
+            assert np.array_equal(opt.bf16_params(i).reshape(-1), bf16_rne(pbuf.array[o:o + t.size]))
+    opt.close()
+    gbuf.free()
+    pbuf.free()
