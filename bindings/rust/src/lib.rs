@@ -55,10 +55,13 @@ pub mod ffi {
     pub const VB_IPC_HANDLE_BYTES: usize = 64;
 
     unsafe extern "C" {
+        pub fn vb_abi_version() -> c_int;
         pub fn vb_last_error() -> *const c_char;
         pub fn vb_engine_create(device: c_int, out: *mut *mut vb_engine) -> c_int;
         pub fn vb_engine_destroy(engine: *mut vb_engine) -> c_int;
         pub fn vb_engine_synchronize(engine: *mut vb_engine) -> c_int;
+        pub fn vb_engine_synchronize_deadline(engine: *mut vb_engine, timeout_ms: f64) -> c_int;
+        pub fn vb_engine_set_wait_limit_ms(engine: *mut vb_engine, milliseconds: u32) -> c_int;
         pub fn vb_adam_create(
             engine: *mut vb_engine, n_tensors: i64, sizes: *const i64, lr: f32, beta1: f32, beta2: f32,
             eps: f32, weight_decay: f32, out: *mut *mut vb_optimizer,
@@ -82,6 +85,13 @@ pub mod ffi {
         pub fn vb_comm_unique_id(id128: *mut c_void) -> c_int;
         pub fn vb_engine_comm_init(engine: *mut vb_engine, id128: *const c_void, rank: c_int, world: c_int) -> c_int;
         pub fn vb_optimizer_step_ex(opt: *mut vb_optimizer, flags: u32) -> c_int;
+        pub fn vb_plan_muon_owners(
+            n_tensors: i64, rows: *const i64, cols: *const i64, world_size: c_int, ns_mode: c_int, ns_steps: c_int,
+            owner_out: *mut i32, rank_cost_out: *mut f64,
+        ) -> c_int;
+        // every rank gathers all fingerprints before the first sharded step; a mismatch is an error on all ranks
+        pub fn vb_optimizer_plan_fingerprint(opt: *mut vb_optimizer, fingerprint: *mut u64) -> c_int;
+        pub fn vb_plan_fingerprints_agree(fingerprints: *const u64, n_ranks: c_int, first_mismatch: *mut c_int) -> c_int;
         pub fn vb_optimizer_ipc_handle(opt: *mut vb_optimizer, handle64: *mut c_void) -> c_int;
         pub fn vb_optimizer_open_peers(opt: *mut vb_optimizer, handles: *const c_void, n_handles: c_int) -> c_int;
         pub fn vb_optimizer_ipc_handle_grads(opt: *mut vb_optimizer, handle64: *mut c_void) -> c_int;

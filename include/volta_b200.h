@@ -112,11 +112,34 @@ int vb_plan_layout(int64_t n_tensors, const int64_t *sizes, int world_size, int 
                    int64_t *chunk_tensor, int64_t *chunk_offset, int64_t *chunk_len);
 
 /* Pure host planning, no CUDA call: which rank owns each Muon tensor.  Whole tensors are
- * taken in order of decreasing Newton-Schulz cost (4 * long side * short side^2 FLOPs per
- * iteration) and given to the least-loaded rank; this is the assignment vb_muon_create
- * uses.  No counterpart in the reference (single process). */
+ * taken in order of decreasing estimated cost per step under the arithmetic `ns_mode` really
+ * executes and given to the least-loaded rank; this is the assignment vb_muon_create uses.
+ * Cost: VB_NS_F32 runs the reference's formulation, 4 * rows * cols^2 FLOPs per iteration
+ * whatever the orientation (src/nn/optim/muon.rs:73 forms cols x cols), on the CUDA cores; the
+ * tensor-core modes run the short-side form, 2 * long * short^2 for the update plus the tiles on
+ * and above the diagonal of the symmetric Gram (three plane products each in VB_NS_F32_TC);
+ * shapes that a tensor-core mode hands to the f32 kernels (a side not a multiple of 8) are
+ * charged as such; every tensor also pays its element-wise passes.  rank_cost_out (world_size
+ * entries, may be NULL) receives each rank's summed estimate in seconds.  No counterpart in the
+ * reference (single process). */
 int vb_plan_muon_owners(int64_t n_tensors, const int64_t *rows, const int64_t *cols, int world_size,
-                        int32_t *owner_out);
+                        int ns_mode, int ns_steps, int32_t *owner_out, double *rank_cost_out);
+
+/* Plan fingerprints: do all ranks describe the same optimizer?  A sharded step is a collective;
+ * ranks that disagree on the tensor list, the hyper-parameters, the mode or the world size would
+ * write into each other's arenas at wrong offsets or wait for each other for ever.  The
+ * fingerprint is a 64-bit hash of exactly those inputs (not of the rank).  The host gathers the
+ * ranks' fingerprints over its own transport before vb_optimizer_open_peers or the first step and
+ * hands them to vb_plan_fingerprints_agree, which returns VB_ERR_STATE (on every rank, since every
+ * rank sees the same list) naming the first rank that differs from rank 0.  vb_plan_fingerprint is
+ * the pure host form (no CUDA call, usable before any engine exists): kind 0 Adam, 1 SGD, 2 Muon;
+ * sizes_or_rows / cols as in the create calls (cols NULL for Adam and SGD); hyper and ints are
+ * the scalar arguments of the create call in order.  Counterpart in the reference: none (single
+ * process); its own pre-flight check is check_system_resources, src/gpu/monitor.rs:58-100. */
+int vb_plan_fingerprint(int kind, int64_t n_tensors, const int64_t *sizes_or_rows, const int64_t *cols,
+                        const float *hyper, int n_hyper, const int32_t *ints, int n_ints, int world_size,
+                        uint64_t *fingerprint);
+int vb_plan_fingerprints_agree(const uint64_t *fingerprints, int n_ranks, int *first_mismatch);
 
 /* ---- engine (replaces the process-global wgpu context, src/gpu/mod.rs:30-47) ----- */
 
@@ -124,6 +147,17 @@ int vb_engine_create(int device, vb_engine **out);
 int vb_engine_destroy(vb_engine *engine);
 /* Blocks until everything enqueued so far has run (GpuContext::sync, src/gpu/context.rs:342-382). */
 int vb_engine_synchronize(vb_engine *engine);
+/* The same with a deadline on the host: polls the stream for at most timeout_ms and returns
+ * VB_ERR_TIMEOUT if work is still queued (sync_checked()'s timeout path,
+ * src/gpu/context.rs:448-505).  Nothing is cancelled: the engine stays usable and a later
+ * synchronize can wait for the rest.  Both forms also report, as VB_ERR_TIMEOUT, a device-side
+ * wait of one of the engine's optimizers that ran out (see vb_engine_set_wait_limit_ms). */
+int vb_engine_synchronize_deadline(vb_engine *engine, double timeout_ms);
+/* Bound, in milliseconds of device wall time, of every wait of this engine's kernels on another
+ * rank (the flag barrier around sharded steps).  Default 5000.  A wait that runs out ends the
+ * step on every rank: each rank's next call on the optimizer (or synchronize) returns
+ * VB_ERR_TIMEOUT, the optimizer is fail-stop from then on, the CUDA context stays usable. */
+int vb_engine_set_wait_limit_ms(vb_engine *engine, uint32_t milliseconds);
 /* The engine's cudaStream_t, for callers that enqueue their own producers of gradients. */
 int vb_engine_stream(vb_engine *engine, void **cuda_stream);
 /* Kernels launched by this engine since creation (bookkeeping for benchmarks). */
@@ -150,6 +184,18 @@ int vb_engine_profile(vb_engine *engine, int phase, double *total_ms, int64_t *c
  * its tensor memory and return; this call reports VB_ERR_TIMEOUT with that role in
  * *role_code, and the engine stays usable.  Nothing faults or hangs. */
 int vb_debug_gemm_wait_expiry(vb_engine *engine, uint32_t wait_limit, int *role_code);
+/* The same inside a real optimizer: the next step of this Muon optimizer withholds the loads of
+ * its first tensor-core launch, with `wait_limit` polls per wait (0 = default).  That launch
+ * records the expiry; every later kernel of the step sees the record and stores nothing, so the
+ * weights keep their pre-step values (the velocity has advanced).  The step itself returns
+ * VB_OK (work is enqueued); the next call that waits for the stream returns VB_ERR_TIMEOUT and
+ * the optimizer is fail-stop from then on. */
+int vb_debug_muon_withhold_loads(vb_optimizer *opt, uint32_t wait_limit);
+/* Self-test of the flag barrier that fences sharded steps (a rank that never arrives, simulated
+ * on one GPU by a flag nobody sets): runs one fence kernel of the given phase (1 start, 2 end)
+ * against a peer block in this GPU's own memory with a bound of timeout_ms.  Reports
+ * VB_ERR_TIMEOUT with the phase in *code; the engine stays usable.  Nothing faults or hangs. */
+int vb_debug_fence_wait_expiry(vb_engine *engine, uint32_t timeout_ms, int phase, int *code);
 
 /* Page-locked host memory for upload/download buffers (pinned buffers make the copies
  * asynchronous and full speed; a pinned upload buffer must stay unchanged until the next
@@ -191,6 +237,8 @@ int vb_muon_create(vb_engine *engine, int64_t n_tensors, const int64_t *rows, co
                    vb_optimizer **out);
 
 int vb_optimizer_destroy(vb_optimizer *opt);
+/* The fingerprint of this optimizer's plan (see vb_plan_fingerprint). */
+int vb_optimizer_plan_fingerprint(vb_optimizer *opt, uint64_t *fingerprint);
 
 /* ---- tensors of an optimizer ------------------------------------------------------ */
 
@@ -279,7 +327,9 @@ int vb_optimizer_set_lr(vb_optimizer *opt, float lr);
  * rank.  From then on step() no longer runs an all-gather / broadcast after the update: the
  * update kernel (Adam, SGD) or the apply kernel (Muon, for the matrices a rank owns) stores
  * each new parameter into the local arena and into the same position of every peer's arena,
- * bracketed by two stream-ordered barriers (one-float NCCL all-reduces).
+ * fenced on both sides by a flag barrier in the same peer-mapped memory (one epoch word per rank,
+ * system-scope release stores and acquire polls by a one-warp kernel; every wait is bounded by
+ * vb_engine_set_wait_limit_ms).  All ranks must make the same sequence of step calls.
  * All ranks must be processes on one node whose GPUs can reach each other (NVLink/NVSwitch). */
 #define VB_IPC_HANDLE_BYTES 64
 int vb_optimizer_ipc_handle(vb_optimizer *opt, void *handle64);
@@ -350,7 +400,9 @@ int vb_muon_last_ns_flops(vb_optimizer *opt, double *flops);
  * state2 entries (and, for op 0, state1 entries) may be NULL where the op does not use
  * them.  hp->t is the step number the bias correction uses; it is computed on the host
  * with the reference's CPU arithmetic (powi, src/nn/optim/adam.rs:188-189), not the
- * shader's per-thread pow(). */
+ * shader's per-thread pow().  Before anything is launched every pointer the op touches is
+ * checked on the host: non-null, 4-byte aligned and, the first time a pointer set is seen,
+ * device memory of the engine's device; a violation returns VB_ERR_INVALID_ARG. */
 int vb_multi_tensor_step(vb_engine *engine, const vb_optimizer_step_params *hp, int64_t n_tensors,
                          const int64_t *sizes, void *const *params, const void *const *grads,
                          void *const *state1, void *const *state2);
@@ -374,6 +426,9 @@ int vb_multi_tensor_step(vb_engine *engine, const vb_optimizer_step_params *hp, 
  *    call uses is rewritten by that call (nothing in it must start at zero).  Calls issued on
  *    one engine are ordered by its stream; calls from different engines or streams that
  *    overlap on the GPU race on the table and must be serialised by the caller;
+ *  - the host array the table is staged through is one per process, shared by all devices and
+ *    host threads; the library holds a lock while it fills the array and hands it to the copy,
+ *    so concurrent callers on different devices are safe on the host side (they serialise);
  *  - the first call on a device also looks up the array's device address; make that first
  *    call before any stream capture begins. */
 int vb_multi_tensor_step_static(vb_engine *engine, const vb_optimizer_step_params *hp,

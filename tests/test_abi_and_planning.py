@@ -27,7 +27,7 @@ def test_library_exports_every_declared_symbol():
         assert hasattr(lib, name), f"{name} is declared in include/volta_b200.h but not exported"
     bound = set(_lib.SIGNATURES) | set(_lib.OTHER_SYMBOLS)
     assert set(names) == bound, set(names) ^ bound
-    assert lib.vb_abi_version() == 1000
+    assert lib.vb_abi_version() == 1001
 
 
 def test_python_constants_match_the_header():

@@ -1,4 +1,4 @@
-"""Sharded optimizers on 2 GPUs (skipped with fewer): one child process per GPU, the library's
+"""Sharded optimizers on 2 and 4 GPUs (skipped with fewer): one child process per GPU, the library's
 own NCCL communicator, results compared with the unsharded CPU oracle.
 
 Adam/SGD: ZeRO-1 slices of the arena + in-place all-gather.  Muon: whole matrices per owner +
@@ -72,17 +72,19 @@ def _worker(rank, world, shared, kind):
     eng.close()
 
 
-@pytest.mark.parametrize("kind", ["adam", "sgd", "adam_peer", "sgd_peer", "muon_f32", "muon_bf16", "muon_f32_peer", "muon_bf16_peer"])
-def test_two_gpu_sharded_step_matches_oracle(oracle, kind):
-    if _gpu_count() < 2:
-        pytest.skip("needs 2 GPUs")
+@pytest.mark.parametrize("world,kind", [(2, k) for k in ("adam", "sgd", "adam_peer", "sgd_peer", "muon_f32", "muon_bf16",
+                                                         "muon_f32_peer", "muon_bf16_peer")] +
+                         [(4, k) for k in ("adam", "adam_peer", "sgd_peer", "muon_f32_peer", "muon_bf16_peer")])
+def test_sharded_step_matches_oracle(oracle, world, kind):
+    if _gpu_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
 
     import workloads
     ctx = mp.get_context("spawn")
     with ctx.Manager() as mgr:
         shared = mgr.dict()
-        procs = [ctx.Process(target=_worker, args=(r, 2, shared, kind)) for r in range(2)]
+        procs = [ctx.Process(target=_worker, args=(r, world, shared, kind)) for r in range(world)]
         for p in procs:
             p.start()
         for p in procs:
@@ -108,14 +110,17 @@ def test_two_gpu_sharded_step_matches_oracle(oracle, kind):
         o = oracle.Muon(ref, h["lr"], h["momentum"], h["nesterov"], h["ns_steps"])
     for s in (1, 2, 3):
         o.step(wl.make_grads(s))
-    for a, b, r in zip(res["params0"], res["params1"], ref):
-        assert np.array_equal(a.view(np.uint32), b.view(np.uint32))  # both ranks hold the same parameters
+    for i, r in enumerate(ref):
+        a = res["params0"][i]
+        for rank in range(1, world):   # every rank holds the same parameters
+            assert np.array_equal(a.view(np.uint32), res[f"params{rank}"][i].view(np.uint32)), (rank, i)
         if kind == "muon_bf16":
             assert np.max(np.abs(a - r)) <= 2e-2 * 0.1 * 0.1 * 3 * max(1.0, float(np.max(np.abs(r))))
         else:
             assert np.array_equal(a.view(np.uint32), r.view(np.uint32))
     # state is partitioned: the ranks' owned element counts add up to the whole
-    assert res["owned0"] + res["owned1"] == wl.total and min(res["owned0"], res["owned1"]) > 0
+    owned = [res[f"owned{rank}"] for rank in range(world)]
+    assert sum(owned) == wl.total and min(owned) > 0
 
 
 def _bf16_rne(x):

@@ -65,12 +65,12 @@ def _free_port():
     return port
 
 
-def _spawn(fn, world):
+def _spawn(fn, world, *extra):
     ctx = mp.get_context("spawn")
     with ctx.Manager() as mgr:
         ret = mgr.dict()
         port = _free_port()
-        procs = [ctx.Process(target=fn, args=(r, world, port, ret)) for r in range(world)]
+        procs = [ctx.Process(target=fn, args=(r, world, port, ret, *extra)) for r in range(world)]
         for p in procs:
             p.start()
         for p in procs:
@@ -106,7 +106,7 @@ def _muon_worker(rank, world, port, ret):
         rows = (C.c_int64 * len(shapes))(*[oracle.muon_dims(s)[0] for s in shapes])
         cols = (C.c_int64 * len(shapes))(*[oracle.muon_dims(s)[1] for s in shapes])
         owners = (C.c_int32 * len(shapes))()
-        _lib.call("vb_plan_muon_owners", len(shapes), rows, cols, world, owners)
+        _lib.call("vb_plan_muon_owners", len(shapes), rows, cols, world, 0, 5, owners, None)
         rng = np.random.default_rng(0)
         params = [(rng.standard_normal(s) * 0.02).astype(np.float32) for s in shapes]
         owned = [i for i in range(len(shapes)) if owners[i] == rank]
@@ -136,17 +136,69 @@ def test_muon_ownership_two_ranks_matches_unsharded():
         assert np.array_equal(a, b) and np.array_equal(a.view(np.uint32), c.view(np.uint32))
 
 
-def test_muon_owner_plan_balances_c4():
+@pytest.mark.parametrize("mode", [0, 1, 2])
+def test_muon_owner_plan_balances_c4_under_the_executed_cost(mode):
+    """Ownership is planned with the cost the mode executes: the bit-faithful f32 kernels run
+    4 * rows * cols^2 FLOPs per iteration (4x more for 1024 x 4096 than for 4096 x 1024), the
+    tensor-core modes the short-side form.  The heaviest rank stays within 5 % of the mean."""
     import workloads
     from volta_b200 import _lib
     wl = workloads.c4_muon()
     n = len(wl.shapes)
     rows = (C.c_int64 * n)(*[s[0] for s in wl.shapes])
     cols = (C.c_int64 * n)(*[s[1] for s in wl.shapes])
+
+    def executed(shape):
+        r, c = shape
+        if mode == 0:
+            return 4.0 * r * c * c                      # src/nn/optim/muon.rs:73: always cols x cols
+        long_, short = max(r, c), min(r, c)
+        t = -(-short // 256)
+        upper = (t * (t + 1) / 2) / (t * t)
+        return 2.0 * long_ * short * short * (1.0 + upper)
+
     for world in (2, 4, 8):
         owners = (C.c_int32 * n)()
-        _lib.call("vb_plan_muon_owners", n, rows, cols, world, owners)
+        est = (C.c_double * world)()
+        _lib.call("vb_plan_muon_owners", n, rows, cols, world, mode, 5, owners, est)
         load = np.zeros(world)
         for i, s in enumerate(wl.shapes):
-            load[owners[i]] += 4.0 * max(s) * min(s) ** 2
-        assert load.max() / load.mean() < 1.05
+            load[owners[i]] += executed(s)
+        assert load.max() / load.mean() <= 1.05, (mode, world, load)
+        assert max(est) / (sum(est) / world) <= 1.05
+
+
+def _fingerprint_worker(rank, world, port, ret, odd_rank):
+    """Every rank hashes its own description of the optimizer, the ranks all-gather the hashes over
+    gloo (the host's transport) and each checks the list before anything would be launched."""
+    sys.path.insert(0, ROOT)
+    from volta_b200 import VoltaB200Error, plan_fingerprint, verify_plan
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        sizes = [4096, 12, 777]
+        if rank == odd_rank:
+            sizes = [4096, 12, 778]   # this rank built its model differently
+        fp = plan_fingerprint("adam", sizes, [1e-3, 0.9, 0.999, 1e-8, 0.01], world_size=world)
+        mine = torch.tensor([fp & 0x7fffffffffffffff, fp >> 63], dtype=torch.int64)
+        gathered = [torch.zeros(2, dtype=torch.int64) for _ in range(world)]
+        dist.all_gather(gathered, mine)
+        fps = [int(g[0]) | (int(g[1]) << 63) for g in gathered]
+        try:
+            verify_plan(fps)
+            ret[rank] = "ok"
+        except VoltaB200Error as exc:
+            ret[rank] = (exc.status, exc.message)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_ranks_with_different_tensor_lists_are_caught_before_the_first_step():
+    """Host-side failure detection between ranks (no GPU involved): a size mismatch is found by
+    comparing plan fingerprints, and every rank gets the same VB_ERR_STATE."""
+    res = _spawn(_fingerprint_worker, 2, -1)
+    assert res[0] == "ok" and res[1] == "ok"
+    res = _spawn(_fingerprint_worker, 2, 1)
+    for rank in (0, 1):
+        status, message = res[rank]
+        assert status == 5 and "rank 1" in message

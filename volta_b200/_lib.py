@@ -54,7 +54,16 @@ SIGNATURES = {
     "vb_device_count": [C.POINTER(C.c_int)],
     "vb_plan_layout": [_i64, _i64p, C.c_int, C.c_int, C.c_int, _i64p, _i64p, _i64p, _i64p, _i64p, _i64,
                        _i64p, _i64p, _i64p],
-    "vb_plan_muon_owners": [_i64, _i64p, _i64p, C.c_int, C.POINTER(C.c_int32)],
+    "vb_plan_muon_owners": [_i64, _i64p, _i64p, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int32),
+                            C.POINTER(C.c_double)],
+    "vb_plan_fingerprint": [C.c_int, _i64, _i64p, _i64p, _f32p, C.c_int, C.POINTER(C.c_int32), C.c_int, C.c_int,
+                            C.POINTER(C.c_uint64)],
+    "vb_plan_fingerprints_agree": [C.POINTER(C.c_uint64), C.c_int, C.POINTER(C.c_int)],
+    "vb_optimizer_plan_fingerprint": [_vp, C.POINTER(C.c_uint64)],
+    "vb_engine_synchronize_deadline": [_vp, C.c_double],
+    "vb_engine_set_wait_limit_ms": [_vp, C.c_uint32],
+    "vb_debug_muon_withhold_loads": [_vp, C.c_uint32],
+    "vb_debug_fence_wait_expiry": [_vp, C.c_uint32, C.c_int, C.POINTER(C.c_int)],
     "vb_engine_create": [C.c_int, _vpp],
     "vb_engine_destroy": [_vp],
     "vb_engine_synchronize": [_vp],

@@ -19,7 +19,7 @@ CSRC = os.path.join(HERE, "csrc")
 OBJ_DIR = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libvolta_b200.so")
 
-SOURCES = ["api.cu", "multi_tensor.cu", "muon.cu", "ns_gemm_f32.cu", "ns_gemm_tc.cu", "comm.cpp"]
+SOURCES = ["api.cu", "multi_tensor.cu", "muon.cu", "ns_gemm_f32.cu", "ns_gemm_tc.cu", "exchange_fence.cu", "comm.cpp"]
 
 # No --use_fast_math: the Adam/SGD kernels promise bit parity with IEEE f32 arithmetic,
 # which needs precise division/sqrt and no flush-to-zero (nvcc's defaults, spelled out).

@@ -2,10 +2,13 @@
 // access, step().  The arithmetic lives in multi_tensor.cu (Adam/SGD) and muon.cu.
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <algorithm>
+#include <chrono>
 #include <new>
+#include <thread>
 
 #include "engine.h"
 
@@ -162,11 +165,15 @@ static int build_arena(vb_optimizer *opt, int n_state_buffers, bool shard_states
     opt->arena = L->arena;
     opt->shard_begin = L->shard_begin;
     opt->shard_end = L->shard_end;
-    const size_t arena_bytes = (size_t)opt->arena * sizeof(float);
+    // each arena a peer can map ends with the flag block of the exchange fence (vb_internal.h)
+    const size_t arena_bytes = (size_t)opt->arena * sizeof(float) + kSyncWords * sizeof(uint32_t);
     VB_CUDA(cudaMalloc(&opt->d_param, arena_bytes));
     VB_CUDA(cudaMalloc(&opt->d_grad, arena_bytes));
     VB_CUDA(cudaMemsetAsync(opt->d_param, 0, arena_bytes, e->stream));
     VB_CUDA(cudaMemsetAsync(opt->d_grad, 0, arena_bytes, e->stream));
+    VB_CUDA(cudaHostAlloc((void **)&opt->h_fence_error, sizeof(uint32_t), cudaHostAllocMapped));
+    *opt->h_fence_error = 0;
+    VB_CUDA(cudaHostGetDevicePointer((void **)&opt->d_fence_error, opt->h_fence_error, 0));
     opt->state_elems = opt->shard_end - opt->shard_begin;
     const size_t state_bytes = (size_t)opt->state_elems * sizeof(float);
     if (n_state_buffers >= 1) {  // Storage::new_zeros, adam.rs:26-47 / sgd.rs:30-41
@@ -230,7 +237,11 @@ static int validate_sizes(int64_t n_tensors, const int64_t *sizes)
 static void free_optimizer(vb_optimizer *opt)
 {
     if (!opt) return;
-    if (opt->eng) cudaSetDevice(opt->eng->device);
+    if (opt->eng) {
+        cudaSetDevice(opt->eng->device);
+        auto &list = opt->eng->optimizers;
+        list.erase(std::remove(list.begin(), list.end(), opt), list.end());
+    }
     if (opt->muon) destroy_muon_state(opt->muon);
     for (void *m : opt->peer_mappings) cudaIpcCloseMemHandle(m);
     cudaFree(opt->d_param);
@@ -240,6 +251,7 @@ static void free_optimizer(vb_optimizer *opt)
     cudaFree(opt->d_s2);
     cudaFree(opt->d_chunks);
     cudaFree(opt->d_present);
+    if (opt->h_fence_error) cudaFreeHost(opt->h_fence_error);
     delete opt;
 }
 
@@ -263,6 +275,83 @@ static int create_elementwise(vb_engine *engine, int kind, int64_t n_tensors, co
     return VB_OK;
 }
 
+
+int check_caller_buffers(const vb_optimizer_step_params *hp, int64_t n_tensors, const int64_t *sizes,
+                         void *const *params, const void *const *grads, void *const *state1, void *const *state2,
+                         int64_t *total)
+{
+    *total = 0;
+    if (hp->op > 2u) return fail(VB_ERR_INVALID_ARG, "op %u is not 0 (SGD), 1 (SGD+momentum) or 2 (Adam)", hp->op);
+    VB_TRY(validate_sizes(n_tensors, sizes));
+    if (n_tensors == 0) return VB_OK;
+    if (!params || !grads) return fail(VB_ERR_INVALID_ARG, "params/grads is null");
+    if (hp->op >= 1 && !state1) return fail(VB_ERR_INVALID_ARG, "state1 is null for op %u", hp->op);
+    if (hp->op == 2 && !state2) return fail(VB_ERR_INVALID_ARG, "state2 is null for Adam");
+    if (hp->op == 2 && !(hp->t >= 1.0f && hp->t <= 2147483648.0f))
+        return fail(VB_ERR_INVALID_ARG, "Adam needs t >= 1");
+    for (int64_t i = 0; i < n_tensors; ++i) {
+        if (sizes[i] == 0) continue;
+        if (!params[i] || !grads[i])
+            return fail(VB_ERR_INVALID_ARG, "params[%lld] or grads[%lld] is null", (long long)i, (long long)i);
+        if (hp->op >= 1 && !state1[i]) return fail(VB_ERR_INVALID_ARG, "state1[%lld] is null", (long long)i);
+        if (hp->op == 2 && !state2[i]) return fail(VB_ERR_INVALID_ARG, "state2[%lld] is null", (long long)i);
+        // every array the kernel's scalar path touches must hold aligned f32 values
+        uintptr_t bits = (uintptr_t)params[i] | (uintptr_t)grads[i];
+        if (hp->op >= 1) bits |= (uintptr_t)state1[i];
+        if (hp->op == 2) bits |= (uintptr_t)state2[i];
+        if (bits & 3u)
+            return fail(VB_ERR_INVALID_ARG, "tensor %lld: params, grads and state pointers must be 4-byte aligned",
+                        (long long)i);
+        *total += sizes[i];
+    }
+    return VB_OK;
+}
+
+static uint64_t fnv1a(uint64_t h, const void *data, size_t n)
+{
+    const unsigned char *p = static_cast<const unsigned char *>(data);
+    for (size_t i = 0; i < n; ++i) h = (h ^ p[i]) * 0x100000001b3ull;
+    return h;
+}
+
+int check_caller_memory(vb_engine *e, const vb_optimizer_step_params *hp, int64_t n_tensors, const int64_t *sizes,
+                        void *const *params, const void *const *grads, void *const *state1, void *const *state2)
+{
+    uint64_t h = 0xcbf29ce484222325ull;
+    h = fnv1a(h, &hp->op, sizeof(hp->op));
+    h = fnv1a(h, sizes, (size_t)n_tensors * sizeof(int64_t));
+    h = fnv1a(h, params, (size_t)n_tensors * sizeof(void *));
+    h = fnv1a(h, grads, (size_t)n_tensors * sizeof(void *));
+    if (hp->op >= 1) h = fnv1a(h, state1, (size_t)n_tensors * sizeof(void *));
+    if (hp->op == 2) h = fnv1a(h, state2, (size_t)n_tensors * sizeof(void *));
+    if (h == 0) h = 1;
+    for (uint64_t seen : e->checked_sets)
+        if (seen == h) return VB_OK;
+    const void *const *arrays[4] = {(const void *const *)params, grads, hp->op >= 1 ? (const void *const *)state1 : nullptr,
+                                    hp->op == 2 ? (const void *const *)state2 : nullptr};
+    const char *names[4] = {"params", "grads", "state1", "state2"};
+    for (int a = 0; a < 4; ++a) {
+        if (!arrays[a]) continue;
+        for (int64_t i = 0; i < n_tensors; ++i) {
+            if (sizes[i] == 0) continue;
+            cudaPointerAttributes attr;
+            const cudaError_t err = cudaPointerGetAttributes(&attr, arrays[a][i]);
+            if (err != cudaSuccess) {
+                cudaGetLastError();
+                return fail(VB_ERR_INVALID_ARG, "%s[%lld] is not a pointer CUDA knows: %s", names[a], (long long)i,
+                            cudaGetErrorString(err));
+            }
+            if (attr.type != cudaMemoryTypeDevice && attr.type != cudaMemoryTypeManaged)
+                return fail(VB_ERR_INVALID_ARG, "%s[%lld] is not device memory", names[a], (long long)i);
+            if (attr.type == cudaMemoryTypeDevice && attr.device != e->device)
+                return fail(VB_ERR_INVALID_ARG, "%s[%lld] lives on device %d, the engine runs on device %d", names[a],
+                            (long long)i, attr.device, e->device);
+        }
+    }
+    e->checked_sets[e->checked_next] = h;
+    e->checked_next = (e->checked_next + 1) & 3;
+    return VB_OK;
+}
 }  // namespace vb
 
 using namespace vb;
@@ -319,7 +408,68 @@ int plan_exchange(vb_optimizer *opt, uint32_t flags, ExchangePlan *plan)
         xp.pt.rank = e->rank;
     }
     xp.pt.grad_scale = (flags & VB_STEP_MEAN_GRADS) ? 1.0f / (float)e->world : 1.0f;
+    if (xp.fused) {
+        // The flag blocks sit behind whichever arena every rank has opened on every other rank:
+        // parameters first, then the bf16 copies, then the gradients (all ranks open the same set).
+        FenceArgs &f = xp.fence;
+        const size_t arena = (size_t)opt->arena;
+        if (xp.pt.n > 0) {
+            f.local = reinterpret_cast<uint32_t *>(opt->d_param + arena);
+            f.n_peers = xp.pt.n;
+            for (int r = 0; r < f.n_peers; ++r) f.peer[r] = reinterpret_cast<uint32_t *>(xp.pt.base[r] + arena);
+        } else if (xp.pt.n_half > 0) {
+            f.local = reinterpret_cast<uint32_t *>(opt->d_param_bf16 + arena);
+            f.n_peers = xp.pt.n_half;
+            for (int r = 0; r < f.n_peers; ++r) f.peer[r] = reinterpret_cast<uint32_t *>(xp.pt.half_base[r] + arena);
+        } else {
+            f.local = reinterpret_cast<uint32_t *>(opt->d_grad + arena);
+            f.n_peers = xp.pt.n_grad;
+            for (int r = 0; r < f.n_peers; ++r)
+                f.peer[r] = reinterpret_cast<uint32_t *>(const_cast<float *>(xp.pt.grad_base[r]) + arena);
+        }
+        f.host_error = opt->d_fence_error;
+        f.rank = e->rank;
+        f.wait_ns = (uint64_t)e->wait_limit_ms * 1000000ull;
+        static const bool nccl_fence = [] {
+            const char *v = getenv("VB_EXCHANGE_FENCE");
+            return v && strcmp(v, "nccl") == 0;
+        }();
+        xp.nccl_fence = nccl_fence;
+    }
     *plan = xp;
+    return VB_OK;
+}
+
+int exchange_fence(vb_optimizer *opt, const ExchangePlan &plan, int phase)
+{
+    if (!plan.fused) return VB_OK;
+    vb_engine *e = opt->eng;
+    prof_begin(e, VB_PHASE_EXCHANGE);
+    int st;
+    if (plan.nccl_fence) {
+        st = comm_barrier(e);
+    } else {
+        FenceArgs f = plan.fence;
+        if (phase == 1) opt->fence_epoch += 1;  // both halves of a step carry the same epoch
+        f.epoch = opt->fence_epoch;
+        st = launch_exchange_fence(f, phase, e->stream);
+        e->launches += 1;
+    }
+    prof_end(e, VB_PHASE_EXCHANGE);
+    return st;
+}
+
+int fence_check_error(vb_optimizer *opt)
+{
+    if (opt->sticky_status != 0)
+        return fail(opt->sticky_status, "an earlier step of this optimizer timed out; it is fail-stop (destroy it)");
+    if (opt->h_fence_error && *reinterpret_cast<volatile uint32_t *>(opt->h_fence_error) != 0) {
+        const unsigned code = *reinterpret_cast<volatile uint32_t *>(opt->h_fence_error);
+        opt->sticky_status = VB_ERR_TIMEOUT;
+        return fail(VB_ERR_TIMEOUT,
+                    "a rank did not reach the %s of a sharded step within %u ms: the optimizer is fail-stop on every "
+                    "rank", code == 1 ? "start" : "end", opt->eng->wait_limit_ms);
+    }
     return VB_OK;
 }
 
@@ -327,7 +477,7 @@ int plan_exchange(vb_optimizer *opt, uint32_t flags, ExchangePlan *plan)
 
 extern "C" {
 
-int vb_abi_version(void) { return 1000; }
+int vb_abi_version(void) { return 1001; }
 
 const char *vb_last_error(void) { return g_err; }
 
@@ -371,17 +521,80 @@ int vb_plan_layout(int64_t n_tensors, const int64_t *sizes, int world_size, int 
     VB_API_END
 }
 
-int vb_plan_muon_owners(int64_t n_tensors, const int64_t *rows, const int64_t *cols, int world_size,
-                        int32_t *owner_out)
+int vb_plan_muon_owners(int64_t n_tensors, const int64_t *rows, const int64_t *cols, int world_size, int ns_mode,
+                        int ns_steps, int32_t *owner_out, double *rank_cost_out)
 {
     VB_API_BEGIN
     if (n_tensors < 0 || world_size < 1) return fail(VB_ERR_INVALID_ARG, "n_tensors or world_size is not valid");
     if (n_tensors > 0 && (!rows || !cols || !owner_out)) return fail(VB_ERR_INVALID_ARG, "null argument");
+    if (ns_mode != VB_NS_F32 && ns_mode != VB_NS_BF16 && ns_mode != VB_NS_F32_TC)
+        return fail(VB_ERR_INVALID_ARG, "unknown ns_mode %d", ns_mode);
     std::vector<int> owners((size_t)n_tensors);
-    plan_muon_owners(n_tensors, rows, cols, world_size, owners.data());
-    for (int64_t i = 0; i < n_tensors; ++i) owner_out[i] = owners[(size_t)i];
+    plan_muon_owners(n_tensors, rows, cols, world_size, ns_mode, ns_steps, owners.data());
+    if (rank_cost_out)
+        for (int r = 0; r < world_size; ++r) rank_cost_out[r] = 0.0;
+    for (int64_t i = 0; i < n_tensors; ++i) {
+        owner_out[i] = owners[(size_t)i];
+        if (rank_cost_out) rank_cost_out[owners[(size_t)i]] += muon_tensor_cost(rows[i], cols[i], ns_mode, ns_steps);
+    }
     return VB_OK;
     VB_API_END
+}
+
+// ---- plan fingerprints: do all ranks describe the same optimizer? -----------------------------
+
+static uint64_t plan_hash(int kind, int64_t n, const int64_t *a, const int64_t *b, const float *hyper, int n_hyper,
+                          const int32_t *ints, int n_ints, int world)
+{
+    uint64_t h = 0xcbf29ce484222325ull;
+    const int32_t head[3] = {vb_abi_version(), kind, world};
+    h = fnv1a(h, head, sizeof(head));
+    h = fnv1a(h, &n, sizeof(n));
+    if (a) h = fnv1a(h, a, (size_t)n * sizeof(int64_t));
+    if (b) h = fnv1a(h, b, (size_t)n * sizeof(int64_t));
+    if (hyper) h = fnv1a(h, hyper, (size_t)n_hyper * sizeof(float));
+    if (ints) h = fnv1a(h, ints, (size_t)n_ints * sizeof(int32_t));
+    return h;
+}
+
+int vb_plan_fingerprint(int kind, int64_t n_tensors, const int64_t *sizes_or_rows, const int64_t *cols,
+                        const float *hyper, int n_hyper, const int32_t *ints, int n_ints, int world_size,
+                        uint64_t *fingerprint)
+{
+    if (!fingerprint) return fail(VB_ERR_INVALID_ARG, "fingerprint is null");
+    if (n_tensors < 0 || (n_tensors > 0 && !sizes_or_rows) || n_hyper < 0 || n_ints < 0 || (n_hyper > 0 && !hyper) ||
+        (n_ints > 0 && !ints) || world_size < 1)
+        return fail(VB_ERR_INVALID_ARG, "invalid argument");
+    *fingerprint = plan_hash(kind, n_tensors, sizes_or_rows, cols, hyper, n_hyper, ints, n_ints, world_size);
+    return VB_OK;
+}
+
+int vb_optimizer_plan_fingerprint(vb_optimizer *opt, uint64_t *fingerprint)
+{
+    VB_TRY(check_opt(opt));
+    if (!fingerprint) return fail(VB_ERR_INVALID_ARG, "fingerprint is null");
+    const float hyper[6] = {opt->lr, opt->beta1, opt->beta2, opt->eps, opt->weight_decay, opt->momentum};
+    const int32_t ints[4] = {opt->nesterov, opt->ns_steps, opt->ns_mode, opt->d_param_bf16 ? 1 : 0};
+    const bool muon = opt->kind == KIND_MUON;
+    *fingerprint = plan_hash(opt->kind, opt->n_tensors, muon ? opt->rows.data() : opt->sizes.data(),
+                             muon ? opt->cols.data() : nullptr, hyper, 6, ints, 4, opt->eng->world);
+    return VB_OK;
+}
+
+int vb_plan_fingerprints_agree(const uint64_t *fingerprints, int n_ranks, int *first_mismatch)
+{
+    if (!fingerprints || n_ranks < 1) return fail(VB_ERR_INVALID_ARG, "invalid argument");
+    if (first_mismatch) *first_mismatch = -1;
+    for (int r = 1; r < n_ranks; ++r) {
+        if (fingerprints[r] != fingerprints[0]) {
+            if (first_mismatch) *first_mismatch = r;
+            return fail(VB_ERR_STATE,
+                        "rank %d describes a different optimizer than rank 0 (tensor list, hyper-parameters, mode or "
+                        "world size): fingerprint %016llx against %016llx; no sharded step may be launched",
+                        r, (unsigned long long)fingerprints[r], (unsigned long long)fingerprints[0]);
+        }
+    }
+    return VB_OK;
 }
 
 int vb_engine_create(int device, vb_engine **out)
@@ -426,6 +639,7 @@ int vb_engine_destroy(vb_engine *e)
         if (e->prof_open[ph]) cudaEventDestroy(e->prof_open[ph]);
     }
     for (cudaEvent_t ev : e->prof_free) cudaEventDestroy(ev);
+    if (e->deadline_event) cudaEventDestroy(e->deadline_event);
     if (e->d_accum_scratch) cudaFree(e->d_accum_scratch);
     for (cudaEvent_t ev : e->pipe_events) cudaEventDestroy(ev);
     if (e->h2d_stream) cudaStreamDestroy(e->h2d_stream);
@@ -440,10 +654,53 @@ int vb_engine_destroy(vb_engine *e)
     return VB_OK;
 }
 
+// After the stream has drained: the first error any optimizer of the engine recorded on the
+// device (a fence wait or a GEMM wait that ran out).
+static int engine_device_errors(vb_engine *e)
+{
+    for (vb_optimizer *opt : e->optimizers) {
+        VB_TRY(fence_check_error(opt));
+        if (opt->kind == KIND_MUON) VB_TRY(muon_check_error(opt));
+    }
+    return VB_OK;
+}
+
 int vb_engine_synchronize(vb_engine *e)
 {
     if (!e) return fail(VB_ERR_INVALID_ARG, "engine is null");
     VB_CUDA(cudaStreamSynchronize(e->stream));
+    return engine_device_errors(e);
+}
+
+int vb_engine_synchronize_deadline(vb_engine *e, double timeout_ms)
+{
+    VB_API_BEGIN
+    if (!e) return fail(VB_ERR_INVALID_ARG, "engine is null");
+    if (!(timeout_ms >= 0.0)) return fail(VB_ERR_INVALID_ARG, "timeout_ms must be >= 0");
+    VB_TRY(set_device(e));
+    if (!e->deadline_event) VB_CUDA(cudaEventCreateWithFlags(&e->deadline_event, cudaEventDisableTiming));
+    VB_CUDA(cudaEventRecord(e->deadline_event, e->stream));
+    const auto t0 = std::chrono::steady_clock::now();
+    for (;;) {
+        const cudaError_t q = cudaEventQuery(e->deadline_event);
+        if (q == cudaSuccess) break;
+        if (q != cudaErrorNotReady)
+            return fail(VB_ERR_CUDA, "cudaEventQuery failed: %s (%d)", cudaGetErrorString(q), (int)q);
+        const double ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+        if (ms > timeout_ms)
+            return fail(VB_ERR_TIMEOUT, "the engine's stream did not drain within %.3f ms (work is still queued; the "
+                                        "engine stays usable and a later synchronize can wait for it)", timeout_ms);
+        std::this_thread::sleep_for(std::chrono::microseconds(20));
+    }
+    return engine_device_errors(e);
+    VB_API_END
+}
+
+int vb_engine_set_wait_limit_ms(vb_engine *e, uint32_t ms)
+{
+    if (!e) return fail(VB_ERR_INVALID_ARG, "engine is null");
+    if (ms == 0) return fail(VB_ERR_INVALID_ARG, "the wait limit must be at least 1 ms");
+    e->wait_limit_ms = ms;
     return VB_OK;
 }
 
@@ -497,6 +754,55 @@ int vb_debug_gemm_wait_expiry(vb_engine *e, uint32_t wait_limit, int *role_code)
     if (role_code) *role_code = 0;
     VB_TRY(set_device(e));
     return debug_gemm_wait_expiry(e, wait_limit, role_code);
+    VB_API_END
+}
+
+int vb_debug_muon_withhold_loads(vb_optimizer *opt, uint32_t wait_limit)
+{
+    VB_TRY(check_opt(opt));
+    if (opt->kind != KIND_MUON) return fail(VB_ERR_INVALID_ARG, "not a Muon optimizer");
+    return muon_debug_withhold(opt, wait_limit);
+}
+
+int vb_debug_fence_wait_expiry(vb_engine *e, uint32_t timeout_ms, int phase, int *code)
+{
+    VB_API_BEGIN
+    if (!e) return fail(VB_ERR_INVALID_ARG, "engine is null");
+    if (phase != 1 && phase != 2) return fail(VB_ERR_INVALID_ARG, "phase must be 1 or 2");
+    if (code) *code = 0;
+    VB_TRY(set_device(e));
+    // two flag blocks in this GPU's own memory: "this rank" and a peer that never shows up
+    uint32_t *blocks = nullptr, *h_err = nullptr, *d_err = nullptr;
+    VB_CUDA(cudaMalloc((void **)&blocks, 2 * kSyncWords * sizeof(uint32_t)));
+    cudaError_t err = cudaMemsetAsync(blocks, 0, 2 * kSyncWords * sizeof(uint32_t), e->stream);
+    if (err == cudaSuccess) err = cudaHostAlloc((void **)&h_err, sizeof(uint32_t), cudaHostAllocMapped);
+    if (err == cudaSuccess) {
+        *h_err = 0;
+        err = cudaHostGetDevicePointer((void **)&d_err, h_err, 0);
+    }
+    int st = VB_OK;
+    if (err == cudaSuccess) {
+        FenceArgs f{};
+        f.local = blocks;
+        f.peer[0] = blocks + kSyncWords;
+        f.host_error = d_err;
+        f.n_peers = 1;
+        f.rank = 0;
+        f.epoch = 1;
+        f.wait_ns = (uint64_t)(timeout_ms ? timeout_ms : 1u) * 1000000ull;
+        st = launch_exchange_fence(f, phase, e->stream);
+        if (st == VB_OK) err = cudaStreamSynchronize(e->stream);
+    }
+    const uint32_t got = (err == cudaSuccess && h_err) ? *reinterpret_cast<volatile uint32_t *>(h_err) : 0u;
+    cudaFree(blocks);
+    if (h_err) cudaFreeHost(h_err);
+    if (err != cudaSuccess) return fail(VB_ERR_CUDA, "fence self-test: %s", cudaGetErrorString(err));
+    if (st != VB_OK) return st;
+    if (code) *code = (int)got;
+    if (got != 0)
+        return fail(VB_ERR_TIMEOUT, "the exchange fence gave up waiting for a peer in phase %u after %u ms", got,
+                    timeout_ms);
+    return VB_OK;
     VB_API_END
 }
 
@@ -557,6 +863,7 @@ int vb_adam_create(vb_engine *engine, int64_t n_tensors, const int64_t *sizes, f
     opt->beta2 = beta2;
     opt->eps = eps;
     opt->weight_decay = weight_decay;
+    engine->optimizers.push_back(opt);
     *out = opt;
     return VB_OK;
     VB_API_END
@@ -576,6 +883,7 @@ int vb_sgd_create(vb_engine *engine, int64_t n_tensors, const int64_t *sizes, fl
     opt->lr = lr;
     opt->momentum = momentum;
     opt->weight_decay = weight_decay;
+    engine->optimizers.push_back(opt);
     *out = opt;
     return VB_OK;
     VB_API_END
@@ -620,6 +928,7 @@ int vb_muon_create(vb_engine *engine, int64_t n_tensors, const int64_t *rows, co
         free_optimizer(opt);
         return st;
     }
+    engine->optimizers.push_back(opt);
     *out = opt;
     return VB_OK;
     VB_API_END
@@ -893,8 +1202,14 @@ int vb_optimizer_step_ex(vb_optimizer *opt, uint32_t flags)
     VB_TRY(check_opt(opt));
     vb_engine *e = opt->eng;
     VB_TRY(set_device(e));
+    VB_TRY(fence_check_error(opt));
     if (opt->kind == KIND_MUON) return muon_step(opt, flags);
 
+    // everything that can refuse the step comes before any state changes (a refused step must
+    // not advance Adam's t: the retry would no longer match the reference)
+    ExchangePlan xp;
+    VB_TRY(plan_exchange(opt, flags, &xp));
+    VB_TRY(sync_present(opt));
     int op;
     StepScalars s;
     if (opt->kind == KIND_ADAM) {
@@ -905,19 +1220,12 @@ int vb_optimizer_step_ex(vb_optimizer *opt, uint32_t flags)
         op = opt->momentum > 0.0f ? OP_SGD_MOMENTUM : OP_SGD;  // sgd.rs:207
         s = make_scalars(op, opt->lr, opt->momentum, 0.0f, 0.0f, opt->weight_decay, 0);
     }
-    VB_TRY(sync_present(opt));
-    ExchangePlan xp;
-    VB_TRY(plan_exchange(opt, flags, &xp));
     // With peer arenas mapped, the exchange is fused into the update: the kernel stores
-    // every new parameter locally and into each peer's arena.  Two stream-ordered barriers
-    // fence it: no rank is written to before it has reached its step (its earlier readers
-    // of the parameters are done), and no rank continues before all writes have landed.
-    // Every rank takes part in them, also one whose slice holds no tensor element.
-    if (xp.fused) {
-        prof_begin(e, VB_PHASE_EXCHANGE);
-        VB_TRY(comm_barrier(e));
-        prof_end(e, VB_PHASE_EXCHANGE);
-    }
+    // every new parameter locally and into each peer's arena.  A flag barrier in peer-mapped
+    // memory fences it on both sides: no rank is written to before it has reached its step (its
+    // earlier readers of the parameters are done), and no rank continues before all writes have
+    // landed.  Every rank takes part, also one whose slice holds no tensor element.
+    VB_TRY(exchange_fence(opt, xp, 1));
     if (opt->n_chunks > 0) {
         bool all_present = true;
         for (int64_t i = 0; i < opt->n_tensors && all_present; ++i) all_present = opt->present[(size_t)i] != 0;
@@ -927,11 +1235,7 @@ int vb_optimizer_step_ex(vb_optimizer *opt, uint32_t flags)
         prof_end(e, VB_PHASE_UPDATE);
         e->launches += 1;
     }
-    if (xp.fused) {
-        prof_begin(e, VB_PHASE_EXCHANGE);
-        VB_TRY(comm_barrier(e));
-        prof_end(e, VB_PHASE_EXCHANGE);
-    }
+    VB_TRY(exchange_fence(opt, xp, 2));
     if (xp.nccl_f32 || xp.nccl_half) {
         prof_begin(e, VB_PHASE_EXCHANGE);
         if (xp.nccl_f32) VB_TRY(comm_all_gather_inplace(e, opt->d_param, opt->arena / e->world));
@@ -962,6 +1266,9 @@ int vb_optimizer_step_host(vb_optimizer *opt, const float *grads_host, float *pa
         VB_CUDA(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
         e->pipe_events.push_back(ev);
     }
+    VB_TRY(fence_check_error(opt));
+    ExchangePlan xp;
+    VB_TRY(plan_exchange(opt, VB_STEP_DEFAULT, &xp));
     int op;
     StepScalars s;
     if (opt->kind == KIND_ADAM) {
@@ -975,9 +1282,7 @@ int vb_optimizer_step_host(vb_optimizer *opt, const float *grads_host, float *pa
     std::fill(opt->present.begin(), opt->present.end(), (uint8_t)1);  // a whole gradient arena arrives
     opt->present_on_dev = opt->present;
     VB_CUDA(cudaMemsetAsync(opt->d_present, 1, opt->present.size(), e->stream));
-    ExchangePlan xp;
-    VB_TRY(plan_exchange(opt, VB_STEP_DEFAULT, &xp));
-    if (xp.fused) VB_TRY(comm_barrier(e));
+    VB_TRY(exchange_fence(opt, xp, 1));
     // everything enqueued so far (earlier steps, uploads) precedes the first copy of this step
     cudaEvent_t ev_start = e->pipe_events[2 * pieces];
     VB_CUDA(cudaEventRecord(ev_start, e->stream));
@@ -1001,13 +1306,13 @@ int vb_optimizer_step_host(vb_optimizer *opt, const float *grads_host, float *pa
         VB_CUDA(cudaStreamWaitEvent(e->d2h_stream, e->pipe_events[2 * j + 1], 0));
         VB_CUDA(cudaMemcpyAsync(params_host + a_lo, opt->d_param + a_lo, bytes, cudaMemcpyDeviceToHost, e->d2h_stream));
     }
-    if (xp.fused) VB_TRY(comm_barrier(e));
+    VB_TRY(exchange_fence(opt, xp, 2));
     if (xp.nccl_f32) VB_TRY(comm_all_gather_inplace(e, opt->d_param, opt->arena / e->world));
     if (xp.nccl_half)
         VB_TRY(comm_all_gather_inplace_bytes(e, opt->d_param_bf16, opt->arena / e->world * (int64_t)sizeof(uint16_t)));
     VB_CUDA(cudaStreamSynchronize(e->d2h_stream));
     VB_CUDA(cudaStreamSynchronize(e->stream));
-    return VB_OK;
+    return fence_check_error(opt);
     VB_API_END
 }
 
@@ -1119,7 +1424,9 @@ int vb_optimizer_enable_bf16_params(vb_optimizer *opt)
     if (opt->d_param_bf16) return VB_OK;
     VB_TRY(set_device(opt->eng));
     uint16_t *buf = nullptr;
-    VB_CUDA(cudaMalloc((void **)&buf, (size_t)std::max<int64_t>(opt->arena, 1) * sizeof(uint16_t)));
+    const size_t bytes = (size_t)opt->arena * sizeof(uint16_t) + kSyncWords * sizeof(uint32_t);
+    VB_CUDA(cudaMalloc((void **)&buf, bytes));
+    VB_CUDA(cudaMemsetAsync(buf, 0, bytes, opt->eng->stream));
     opt->d_param_bf16 = buf;
     return refresh_bf16(opt, 0, opt->arena);
     VB_API_END
@@ -1285,27 +1592,13 @@ int vb_multi_tensor_step(vb_engine *e, const vb_optimizer_step_params *hp, int64
                          void *const *state1, void *const *state2)
 {
     VB_API_BEGIN
-    if (!e || !hp) return fail(VB_ERR_INVALID_ARG, "null argument");
-    if (hp->op > 2u) return fail(VB_ERR_INVALID_ARG, "op %u is not 0 (SGD), 1 (SGD+momentum) or 2 (Adam)", hp->op);
-    VB_TRY(validate_sizes(n_tensors, sizes));
-    if (n_tensors == 0) return VB_OK;
-    if (!params || !grads) return fail(VB_ERR_INVALID_ARG, "params/grads is null");
-    if (hp->op >= 1 && !state1) return fail(VB_ERR_INVALID_ARG, "state1 is null for op %u", hp->op);
-    if (hp->op == 2 && !state2) return fail(VB_ERR_INVALID_ARG, "state2 is null for Adam");
-    if (hp->op == 2 && !(hp->t >= 1.0f && hp->t <= 2147483648.0f))
-        return fail(VB_ERR_INVALID_ARG, "Adam needs t >= 1");
-    VB_TRY(set_device(e));
-
+    if (!hp) return fail(VB_ERR_INVALID_ARG, "null argument");
     int64_t total = 0;
-    for (int64_t i = 0; i < n_tensors; ++i) {
-        if (sizes[i] == 0) continue;
-        if (!params[i] || !grads[i]) return fail(VB_ERR_INVALID_ARG, "params[%lld] or grads[%lld] is null", (long long)i, (long long)i);
-        if (hp->op >= 1 && !state1[i]) return fail(VB_ERR_INVALID_ARG, "state1[%lld] is null", (long long)i);
-        if (hp->op == 2 && !state2[i]) return fail(VB_ERR_INVALID_ARG, "state2[%lld] is null", (long long)i);
-        if (((uintptr_t)params[i] | (uintptr_t)grads[i]) & 3u)
-            return fail(VB_ERR_INVALID_ARG, "tensor %lld is not 4-byte aligned", (long long)i);
-        total += sizes[i];
-    }
+    VB_TRY(check_caller_buffers(hp, n_tensors, sizes, params, grads, state1, state2, &total));
+    if (!e) return fail(VB_ERR_INVALID_ARG, "engine is null");
+    if (total == 0) return VB_OK;
+    VB_TRY(set_device(e));
+    VB_TRY(check_caller_memory(e, hp, n_tensors, sizes, params, grads, state1, state2));
     const int64_t chunk_len = pick_chunk_len(total, e->sm_count);
     int64_t n_chunks = 0;
     for (int64_t i = 0; i < n_tensors; ++i) n_chunks += (sizes[i] + chunk_len - 1) / chunk_len;

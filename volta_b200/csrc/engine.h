@@ -11,6 +11,8 @@ struct MuonState;  // muon.cu: matrices, work buffers and GEMM schedules of a Mu
 void destroy_muon_state(MuonState *);
 }  // namespace vb
 
+struct vb_optimizer;
+
 struct vb_engine {
     int device = 0;
     cudaStream_t stream = nullptr;
@@ -31,6 +33,13 @@ struct vb_engine {
     std::vector<cudaEvent_t> pipe_events;
     float *d_accum_scratch = nullptr;  // staging for host contributions to vb_optimizer_accumulate_grad
     size_t accum_scratch_elems = 0;
+    // caller-buffer entry points: hashes of the pointer sets whose memory type and device were
+    // already checked (cudaPointerGetAttributes costs about a microsecond per pointer)
+    uint64_t checked_sets[4] = {0, 0, 0, 0};
+    int checked_next = 0;
+    std::vector<vb_optimizer *> optimizers;  // alive optimizers of this engine (their error words are read on synchronize)
+    cudaEvent_t deadline_event = nullptr;  // vb_engine_synchronize_deadline
+    uint32_t wait_limit_ms = 5000;         // bound of every device-side wait on another rank
     // optional phase timing (vb_engine_set_profiling): event pairs per phase, summed on query
     bool profiling = false;
     std::vector<std::pair<cudaEvent_t, cudaEvent_t>> prof_pairs[VB_PHASE_COUNT];
@@ -80,6 +89,13 @@ struct vb_optimizer {
     // (vb_optimizer_open_peers / vb_optimizer_open_peers_bf16)
     vb::PeerTable peers{};
     std::vector<void *> peer_mappings;  // what cudaIpcOpenMemHandle returned, to close on destroy
+
+    // device-side fence around steps that touch peer memory (exchange_fence.cu): epoch of the
+    // last fenced step and a mapped pinned word a fence kernel writes when a wait runs out
+    uint32_t fence_epoch = 0;
+    uint32_t *h_fence_error = nullptr;
+    uint32_t *d_fence_error = nullptr;  // device alias of h_fence_error
+    int sticky_status = 0;              // fail-stop: set once a step reported VB_ERR_TIMEOUT
 };
 
 namespace vb {
@@ -95,9 +111,12 @@ int muon_download_update(vb_optimizer *opt, int64_t tensor, float *host, int64_t
 int muon_last_flops(vb_optimizer *opt, double *flops);
 int muon_owner(vb_optimizer *opt, int64_t tensor);
 int debug_gemm_wait_expiry(vb_engine *e, uint32_t wait_limit, int *role_code);
+int muon_debug_withhold(vb_optimizer *opt, uint32_t wait_limit);  // test hook, see vb_debug_muon_withhold_loads
 int muon_check_error(vb_optimizer *opt);  // VB_ERR_TIMEOUT if a GEMM kernel reported a bounded wait expiring
 float *muon_velocity_ptr(vb_optimizer *opt, int64_t tensor);  // nullptr if not owned
-void plan_muon_owners(int64_t n, const int64_t *rows, const int64_t *cols, int world, int *owner_out);
+void plan_muon_owners(int64_t n, const int64_t *rows, const int64_t *cols, int world, int ns_mode, int ns_steps,
+                      int *owner_out);
+double muon_tensor_cost(int64_t rows, int64_t cols, int ns_mode, int ns_steps);  // estimated seconds per step
 
 // comm.cpp
 int comm_unique_id(void *id128);
@@ -119,11 +138,17 @@ int comm_group_broadcast(vb_engine *eng, const BcastItem *items, int64_t n_items
 // two stream-ordered barriers are needed around it, and which copies NCCL still has to move.
 struct ExchangePlan {
     PeerTable pt{};
+    FenceArgs fence{};       // the flag barrier around a fused step (n_peers == 0: none needed)
+    bool nccl_fence = false; // VB_EXCHANGE_FENCE=nccl: one-float all-reduces instead (for comparison)
     bool fused = false;      // the kernel stores into peers: fence it with barriers
     bool nccl_f32 = false;   // f32 parameters go by all-gather / broadcast after the kernel
     bool nccl_half = false;  // bf16 copies go by all-gather / broadcast after the kernel
 };
 int plan_exchange(vb_optimizer *opt, uint32_t flags, ExchangePlan *plan);
+// The two halves of the barrier around a fused step; no-ops when the plan needs none.
+int exchange_fence(vb_optimizer *opt, const ExchangePlan &plan, int phase);
+// VB_ERR_TIMEOUT once a fence wait of this optimizer ran out on any rank (fail-stop).
+int fence_check_error(vb_optimizer *opt);
 
 inline int sync_present(vb_optimizer *opt)
 {

@@ -14,6 +14,8 @@
 #include <cuda_bf16.h>
 #include <stdlib.h>
 
+#include <mutex>
+
 #include "vb_internal.h"
 
 namespace vb {
@@ -525,6 +527,8 @@ int launch_accumulate_grad(float *grad, const float *src, int64_t n, bool add, i
 //  * every GPU that loads the library carries the array (384 KiB) until the process exits;
 //  * all calls on a device share it: two calls that overlap on the GPU (different engines
 //    or streams) race; calls on one engine are ordered by its stream and are safe;
+//  * the host staging array is shared by every device and host thread of the process; a lock
+//    around filling it and handing it to the copy keeps concurrent callers apart on the host;
 //  * the first call on a device looks the array's address up (cudaGetSymbolAddress), so
 //    make that first call before starting a stream capture.
 // ---------------------------------------------------------------------------------------------
@@ -539,7 +543,8 @@ static __device__ __align__(256) unsigned char g_static_chunk_table[VB_STATIC_MA
 
 namespace {
 
-FatChunk g_static_host_table[VB_STATIC_MAX_CHUNKS];       // staging on the host, equally fixed
+FatChunk g_static_host_table[VB_STATIC_MAX_CHUNKS];       // staging on the host, equally fixed, one per process
+std::mutex g_static_host_mutex;                           // serialises host threads filling it
 FatChunk *g_static_dev_ptr[VB_STATIC_MAX_DEVICES] = {};   // resolved device address, per device
 
 // Once per device, with that device current.
@@ -569,30 +574,14 @@ extern "C" int vb_multi_tensor_step_static(vb_engine *engine, const vb_optimizer
     using namespace vb;
     int device = 0, sm_count = 0;
     cudaStream_t stream = nullptr;
-    if (!engine || !hp) return fail(VB_ERR_INVALID_ARG, "null argument");
+    if (!hp) return fail(VB_ERR_INVALID_ARG, "null argument");
+    int64_t total = 0;
+    VB_TRY(check_caller_buffers(hp, n_tensors, sizes, params, grads, state1, state2, &total));
+    if (!engine) return fail(VB_ERR_INVALID_ARG, "engine is null");
     if (engine_launch_info(engine, &device, &sm_count, &stream) != VB_OK) return VB_ERR_INVALID_ARG;
-    if (hp->op > 2u) return fail(VB_ERR_INVALID_ARG, "op %u is not 0 (SGD), 1 (SGD+momentum) or 2 (Adam)", hp->op);
-    if (n_tensors < 0) return fail(VB_ERR_INVALID_ARG, "n_tensors is negative");
-    if (n_tensors == 0) return VB_OK;
-    if (!sizes || !params || !grads) return fail(VB_ERR_INVALID_ARG, "sizes/params/grads is null");
-    if (hp->op >= 1 && !state1) return fail(VB_ERR_INVALID_ARG, "state1 is null for op %u", hp->op);
-    if (hp->op == 2 && !state2) return fail(VB_ERR_INVALID_ARG, "state2 is null for Adam");
-    if (hp->op == 2 && !(hp->t >= 1.0f && hp->t <= 2147483648.0f)) return fail(VB_ERR_INVALID_ARG, "Adam needs t >= 1");
     if (n_tensors > VB_STATIC_MAX_CHUNKS)
         return fail(VB_ERR_UNSUPPORTED, "%lld tensors exceed the static table (%d chunks); use vb_multi_tensor_step",
                     (long long)n_tensors, VB_STATIC_MAX_CHUNKS);
-    int64_t total = 0;
-    for (int64_t i = 0; i < n_tensors; ++i) {
-        if (sizes[i] < 0) return fail(VB_ERR_INVALID_ARG, "sizes[%lld] is negative", (long long)i);
-        if (sizes[i] == 0) continue;
-        if (!params[i] || !grads[i])
-            return fail(VB_ERR_INVALID_ARG, "params[%lld] or grads[%lld] is null", (long long)i, (long long)i);
-        if (hp->op >= 1 && !state1[i]) return fail(VB_ERR_INVALID_ARG, "state1[%lld] is null", (long long)i);
-        if (hp->op == 2 && !state2[i]) return fail(VB_ERR_INVALID_ARG, "state2[%lld] is null", (long long)i);
-        if (((uintptr_t)params[i] | (uintptr_t)grads[i]) & 3u)
-            return fail(VB_ERR_INVALID_ARG, "tensor %lld is not 4-byte aligned", (long long)i);
-        total += sizes[i];
-    }
     if (total == 0) return VB_OK;
     // smallest chunk length (doubling from the usual one) whose table fits the fixed array
     int64_t chunk_len = pick_chunk_len(total, sm_count);
@@ -609,9 +598,15 @@ extern "C" int vb_multi_tensor_step_static(vb_engine *engine, const vb_optimizer
                         VB_STATIC_MAX_CHUNKS);
         chunk_len *= 2;
     }
+    VB_CUDA(cudaSetDevice(device));
+    VB_TRY(check_caller_memory(engine, hp, n_tensors, sizes, params, grads, state1, state2));
+    // The host staging array is one per process: the lock keeps two host threads (driving two
+    // engines, on the same or on different devices) from interleaving their tables in it.  It is
+    // held until cudaMemcpyAsync returns; the source is ordinary (pageable) host memory, so by
+    // then the runtime has taken its copy and the array can be refilled.
+    std::lock_guard<std::mutex> lock(g_static_host_mutex);
     FatChunk *d_table = nullptr;
     VB_TRY(static_table_address(device, &d_table));  // first call on this device: resolves the address
-    VB_CUDA(cudaSetDevice(device));
     int64_t c = 0;
     for (int64_t i = 0; i < n_tensors; ++i) {
         for (int64_t b = 0; b < sizes[i]; b += chunk_len) {
@@ -626,9 +621,7 @@ extern "C" int vb_multi_tensor_step_static(vb_engine *engine, const vb_optimizer
         }
     }
     // The used prefix of the device table is rewritten on every call; nothing in it has to
-    // start at zero and entries beyond n_chunks are never read.  The source is ordinary
-    // (pageable) host memory, so the runtime has taken its copy when this call returns and the
-    // host array can be refilled by the next call.
+    // start at zero and entries beyond n_chunks are never read.
     VB_CUDA(cudaMemcpyAsync(d_table, g_static_host_table, (size_t)n_chunks * sizeof(FatChunk), cudaMemcpyHostToDevice,
                             stream));
     const StepScalars s =

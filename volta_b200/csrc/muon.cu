@@ -13,6 +13,9 @@
 // is a fixed, small number of launches whatever the number of parameters.
 #include <cuda_bf16.h>
 
+#include <math.h>
+#include <stddef.h>
+
 #include <algorithm>
 #include <numeric>
 
@@ -597,8 +600,11 @@ normalise_kernel(const TensorDesc *__restrict__ tensors, const ChunkDesc *__rest
 template <bool PEERS, int HALF>
 __global__ void __launch_bounds__(kEwThreads)
 apply_kernel(const TensorDesc *__restrict__ tensors, const ChunkDesc *__restrict__ chunks, int64_t n_chunks,
-             const uint8_t *__restrict__ present, float lr, const PeerTable pt)
+             const uint8_t *__restrict__ present, float lr, const PeerTable pt, const int *__restrict__ error_flag)
 {
+    // A Newton-Schulz kernel of this step gave up a wait: its update buffers are half written.
+    // Nothing is applied, so the weights (here and on the peers) keep their pre-step values.
+    if (error_flag != nullptr && *reinterpret_cast<const volatile int *>(error_flag) != 0) return;
     for (int64_t c = blockIdx.x; c < n_chunks; c += gridDim.x) {
         const ChunkDesc ch = chunks[c];
         if (present[ch.tensor] == 0) continue;
@@ -722,6 +728,8 @@ struct MuonState {
     int n_tc_gram_tiles = 0, n_tc_upd_tiles = 0, n_tc_upd_tiles_last = 0;
     int *d_error = nullptr;
     int *h_error = nullptr;              // pinned mirror of d_error, refreshed after every step
+    bool debug_withhold = false;         // test hook: the next step's first Gram launch stages nothing
+    uint32_t debug_wait_limit = 0;
     double flops_per_step = 0.0;
     double last_flops = 0.0;
 };
@@ -766,17 +774,35 @@ void destroy_muon_state(MuonState *s)
     delete s;
 }
 
-// Whole matrices are owned by one rank: tensors are taken in order of decreasing
-// Newton-Schulz cost (4 * long side * short side^2 FLOPs per iteration; elements for 1-D
-// tensors) and each goes to the rank with the least work so far (ties: lowest rank).
-void plan_muon_owners(int64_t n, const int64_t *rows, const int64_t *cols, int world, int *owner_out)
+// Estimated device time of one tensor's share of a step, in seconds, under the arithmetic the
+// mode really executes: the bit-faithful f32 kernels run the reference's formulation,
+// 4 * rows * cols^2 FLOPs per iteration whatever the orientation (muon.rs:73: always cols x cols),
+// on the CUDA cores; the tensor-core modes run the short-side form with the symmetric Gram
+// computed on and above the diagonal (three plane products per product in the f32-accurate
+// mode); every tensor also pays its element-wise passes.  Only the ratios matter.
+double muon_tensor_cost(int64_t rows, int64_t cols, int ns_mode, int ns_steps)
+{
+    const double r = (double)rows, c = (double)cols;
+    const double elementwise = r * c * 40.0 / 6.5e12;  // momentum, normalise, apply: ~40 B per element from HBM
+    if (!(rows > 1 && cols > 1) || ns_steps <= 0) return elementwise;
+    const bool tc = ns_mode != VB_NS_F32 && (rows % 8) == 0 && (cols % 8) == 0;
+    if (!tc) return elementwise + 4.0 * r * c * c * (double)ns_steps / 45e12;
+    const double L = std::max(r, c), S = std::min(r, c);
+    const double t = std::ceil(S / 256.0);                  // 256 x 256 tiles per side of the Gram
+    const double upper = (t * (t + 1.0) / 2.0) / (t * t);   // share of the Gram that is computed
+    const double planes = ns_mode == VB_NS_F32_TC ? 3.0 : 1.0;
+    return elementwise + planes * (double)ns_steps * 2.0 * L * S * S * (1.0 + upper) / 1.15e15;
+}
+
+// Whole matrices are owned by one rank: tensors are taken in order of decreasing estimated
+// cost (muon_tensor_cost) and each goes to the rank with the least work so far (ties: lowest
+// rank).
+void plan_muon_owners(int64_t n, const int64_t *rows, const int64_t *cols, int world, int ns_mode, int ns_steps,
+                      int *owner_out)
 {
     std::vector<int64_t> order((size_t)n);
     std::iota(order.begin(), order.end(), 0);
-    auto cost = [&](int64_t i) -> double {
-        const double r = (double)rows[i], c = (double)cols[i];
-        return (r > 1 && c > 1) ? 4.0 * r * c * std::min(r, c) : r * c * 1e-3;
-    };
+    auto cost = [&](int64_t i) -> double { return muon_tensor_cost(rows[i], cols[i], ns_mode, ns_steps); };
     std::stable_sort(order.begin(), order.end(), [&](int64_t a, int64_t b) { return cost(a) > cost(b); });
     std::vector<double> load((size_t)world, 0.0);
     for (int64_t i : order) {
@@ -813,7 +839,7 @@ int muon_init(vb_optimizer *opt)
     opt->muon = s;
     const int64_t nt = opt->n_tensors;
     s->owner.assign((size_t)nt, 0);
-    plan_muon_owners(nt, opt->rows.data(), opt->cols.data(), e->world, s->owner.data());
+    plan_muon_owners(nt, opt->rows.data(), opt->cols.data(), e->world, opt->ns_mode, opt->ns_steps, s->owner.data());
     s->local_off.assign((size_t)nt, -1);
     s->ns_kind.assign((size_t)std::max<int64_t>(nt, 1), 0);
     s->final_update.assign((size_t)nt, nullptr);
@@ -1117,20 +1143,28 @@ int muon_step(vb_optimizer *opt, uint32_t flags)
 {
     vb_engine *e = opt->eng;
     MuonState *s = opt->muon;
-    VB_TRY(muon_check_error(opt));
+    ExchangePlan xp;
+    VB_TRY(plan_exchange(opt, flags, &xp));  // the same outcome on every rank: nothing is enqueued on a refusal
+    // A GEMM kernel of an earlier step gave up a wait on this rank: the optimizer is fail-stop,
+    // but this rank still takes every fence and collective of the step (its kernels skip their
+    // work), so that no other rank is left waiting for it; the fence tells the peers.
+    const int local_status = muon_check_error(opt);
+    const bool compute = local_status == VB_OK;
     VB_TRY(sync_present(opt));
+    xp.fence.local_error = s->d_error;
     const int ew_grid = (int)std::min<int64_t>(std::max<int64_t>(s->n_chunks, 1), (int64_t)e->sm_count * 8);
     const bool fast_norm = opt->ns_mode == VB_NS_BF16;  // both f32 modes need the reference's ordered sum
-    ExchangePlan xp;
-    VB_TRY(plan_exchange(opt, flags, &xp));
     const bool gsum = xp.pt.n_grad > 0;
-    if (gsum) {  // peers' gradients are read by the first kernel: every rank must have reached its step
-        prof_begin(e, VB_PHASE_EXCHANGE);
-        VB_TRY(comm_barrier(e));
-        prof_end(e, VB_PHASE_EXCHANGE);
+    // peers' gradients are read by the first kernel: every rank must have reached its step
+    if (gsum) VB_TRY(exchange_fence(opt, xp, 1));
+    const uint32_t gemm_wait_limit = s->debug_wait_limit;  // 0 = the default; set by the expiry test hook
+    if (s->debug_withhold && compute && !s->d_tc_gram.empty()) {
+        const int32_t one = 1;
+        VB_CUDA(cudaMemcpyAsync(reinterpret_cast<char *>(s->d_tc_gram[0]) + offsetof(TcGemmProblem, withhold_loads), &one,
+                                sizeof(one), cudaMemcpyHostToDevice, e->stream));
     }
     prof_begin(e, VB_PHASE_MUON_PRE);
-    if (s->n_chunks > 0) {
+    if (s->n_chunks > 0 && compute) {
         const uint8_t *direct = s->fold_norm ? s->d_fold_norm : nullptr;
         GradPeers gp{};
         gp.local_base = opt->d_grad;
@@ -1152,7 +1186,7 @@ int muon_step(vb_optimizer *opt, uint32_t flags)
         VB_CUDA(cudaGetLastError());
         e->launches += 1;
     }
-    if (s->n_ns > 0) {
+    if (s->n_ns > 0 && compute) {
         if (fast_norm)
             reduce_partials_kernel<<<(s->n_ns + 3) / 4, 128, 0, e->stream>>>(s->d_partials, s->d_first_chunk,
                                                                             s->d_ns_tensors, s->n_ns, s->d_sumsq);
@@ -1185,11 +1219,11 @@ int muon_step(vb_optimizer *opt, uint32_t flags)
             if (s->n_tc_gram_tiles > 0) {
                 const bool split = s->planes > 1;
                 VB_TRY(launch_ns_gemm_tc(s->d_tc_gram[(size_t)it], s->d_tc_gram_tiles, s->n_tc_gram_tiles,
-                                         opt->d_present, s->d_error, e->sm_count, e->stream, 0, split));
+                                         opt->d_present, s->d_error, e->sm_count, e->stream, gemm_wait_limit, split));
                 const bool last_it = it == opt->ns_steps - 1;
                 VB_TRY(launch_ns_gemm_tc(s->d_tc_upd[(size_t)it], last_it ? s->d_tc_upd_tiles_last : s->d_tc_upd_tiles,
                                          last_it ? s->n_tc_upd_tiles_last : s->n_tc_upd_tiles,
-                                         opt->d_present, s->d_error, e->sm_count, e->stream, 0, split));
+                                         opt->d_present, s->d_error, e->sm_count, e->stream, gemm_wait_limit, split));
                 e->launches += 2;
             }
             if (s->n_gram_tiles > 0) {
@@ -1206,18 +1240,22 @@ int muon_step(vb_optimizer *opt, uint32_t flags)
             VB_CUDA(cudaMemcpyAsync(s->h_error, s->d_error, sizeof(int), cudaMemcpyDeviceToHost, e->stream));
     }
     prof_end(e, VB_PHASE_MUON_PRE);  // no-op if already closed (no Newton-Schulz matrices)
-    if (xp.fused && !gsum) {  // see vb_optimizer_step_ex: nobody is written to before it has reached its step
-        prof_begin(e, VB_PHASE_EXCHANGE);
-        VB_TRY(comm_barrier(e));
-        prof_end(e, VB_PHASE_EXCHANGE);
+    if (s->debug_withhold && compute && !s->d_tc_gram.empty()) {
+        const int32_t zero = 0;
+        VB_CUDA(cudaMemcpyAsync(reinterpret_cast<char *>(s->d_tc_gram[0]) + offsetof(TcGemmProblem, withhold_loads), &zero,
+                                sizeof(zero), cudaMemcpyHostToDevice, e->stream));
+        s->debug_withhold = false;
+        s->debug_wait_limit = 0;
     }
-    if (s->n_chunks > 0) {
+    // see vb_optimizer_step_ex: nobody is written to before it has reached its step
+    if (!gsum) VB_TRY(exchange_fence(opt, xp, 1));
+    if (s->n_chunks > 0 && compute) {
         prof_begin(e, VB_PHASE_MUON_APPLY);
         const bool f32_peers = xp.pt.n > 0;
         const int half = xp.pt.half_local == nullptr ? 0 : xp.pt.n_half > 0 ? 2 : 1;
 #define VB_APPLY(P, H)                                                                                      \
     apply_kernel<P, H><<<ew_grid, kEwThreads, 0, e->stream>>>(s->d_desc_apply, s->d_chunks, s->n_chunks, \
-                                                             opt->d_present, opt->lr, xp.pt)
+                                                             opt->d_present, opt->lr, xp.pt, s->d_error)
         if (half == 0) {
             if (f32_peers) VB_APPLY(true, 0); else VB_APPLY(false, 0);
         } else if (half == 1) {
@@ -1230,11 +1268,7 @@ int muon_step(vb_optimizer *opt, uint32_t flags)
         prof_end(e, VB_PHASE_MUON_APPLY);
         e->launches += 1;
     }
-    if (xp.fused) {
-        prof_begin(e, VB_PHASE_EXCHANGE);
-        VB_TRY(comm_barrier(e));
-        prof_end(e, VB_PHASE_EXCHANGE);
-    }
+    VB_TRY(exchange_fence(opt, xp, 2));
     if (xp.nccl_f32 || xp.nccl_half) {
         // every matrix from its owner; all ranks must hold the same gradient-presence flags
         std::vector<BcastItem> items;
@@ -1251,6 +1285,17 @@ int muon_step(vb_optimizer *opt, uint32_t flags)
         VB_TRY(comm_group_broadcast(e, items.data(), (int64_t)items.size()));
         prof_end(e, VB_PHASE_EXCHANGE);
     }
+    if (!compute) return muon_check_error(opt);  // sets the message again
+    return VB_OK;
+}
+
+int muon_debug_withhold(vb_optimizer *opt, uint32_t wait_limit)
+{
+    MuonState *s = opt->muon;
+    if (!s || s->d_tc_gram.empty())
+        return fail(VB_ERR_STATE, "the optimizer runs no tensor-core Newton-Schulz kernel on this rank");
+    s->debug_withhold = true;
+    s->debug_wait_limit = wait_limit;
     return VB_OK;
 }
 

@@ -80,6 +80,7 @@ struct alignas(8) Barriers {
     uint64_t tmem_empty[2];
     uint32_t tmem_base;
     uint32_t abort;
+    uint32_t skip;  // the error flag was already set when this CTA started: do nothing
 };
 template <int kCtas>
 constexpr size_t smem_bytes()
@@ -680,6 +681,9 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
             mbar_init(&bars->tmem_empty[a], kCtas * kEpiWarps);  // epilogue warps of every CTA of the group
         }
         bars->abort = 0;
+        // An earlier kernel of the chain gave up a wait: its output is half written, so this
+        // launch computes and stores nothing (read once per CTA: every role sees the same value).
+        bars->skip = *reinterpret_cast<const volatile int *>(error_flag) != 0 ? 1u : 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {  // TMEM allocation is warp-wide; with two CTAs the same warp of both allocates
@@ -702,6 +706,7 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
     if (kCtas == 2) cluster_sync_all();  // the peer's barriers exist before anything signals them
     tcgen05_fence_after();
     const uint32_t tmem_base = bars->tmem_base;
+    if (bars->skip != 0u) n_tiles = 0;
 
     if (warp == 0) {
         // ---------------- TMA producer (every CTA) ----------------
@@ -725,7 +730,9 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
                 constexpr int kSlotBytes = kSplit ? C::kSplitStageBytes : C::kStageBytes;
                 const int n_slots = ti.k_blocks;  // one ring slot per k block
                 for (int slot = 0; slot < n_slots; ++slot) {
-                    if (!MBAR_WAIT(0, &bars->empty[stage], phase ^ 1u)) {
+                    // both producer lanes act on one decision: if either saw the wait run out (or
+                    // the abort flag), both stop here
+                    if (!__all_sync(0x3u, MBAR_WAIT(0, &bars->empty[stage], phase ^ 1u))) {
                         ok = false;
                         break;
                     }
@@ -878,7 +885,9 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
             const int64_t plane_stride = p->out_plane_stride;
             const bool bf16_rows_32b = (ld % 16) == 0;  // every bf16 output row starts on a 32-byte boundary
             const bool transpose = !kSplit && p->transpose_out != 0;
-            if (!MBAR_WAIT(3, &bars->tmem_full[acc], acc_phase)) {
+            // warp-uniform: near expiry some lanes could see the barrier flip and others give up;
+            // the whole warp must take the same branch before the aligned tcgen05.ld below
+            if (!__all_sync(0xffffffffu, MBAR_WAIT(3, &bars->tmem_full[acc], acc_phase))) {
                 ok = false;
                 break;
             }

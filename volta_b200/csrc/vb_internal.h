@@ -79,6 +79,31 @@ struct PeerTable {
     float grad_scale;  // the sum is multiplied by this (1, or 1 / world for the mean)
 };
 
+// Flag words that order the ranks around a step that touches peer memory.  Every arena that can
+// be opened by the peers (parameters, bf16 copies, gradients) carries one block of kSyncWords
+// 32-bit words behind its last element, so a peer that maps the arena maps the block as well.
+// Rank r writes word [r] of a group in every rank's block; a rank polls only its own block.
+constexpr int kSyncWords = 256;       // 1 KiB
+constexpr int kSyncArrive = 0;        // [r]: epoch of the last step rank r has reached
+constexpr int kSyncDone = 32;         // [r]: epoch of the last step whose peer accesses rank r has finished
+constexpr int kSyncError = 64;        // [r]: non-zero once rank r gave up a wait (sticky)
+struct FenceArgs {
+    uint32_t *local;                  // this rank's block
+    uint32_t *peer[kMaxPeers];        // the peers' blocks, in rank order without this rank
+    uint32_t *host_error;             // mapped pinned word the host reads without a copy (may be null)
+    const int *local_error;           // if set and non-zero: a kernel of this rank failed during the step; the
+                                      // fence reports it to every rank as if a wait had run out
+    int n_peers;
+    int rank;
+    uint32_t epoch;
+    uint64_t wait_ns;                 // bound of each wait
+};
+// phase 1: tell every peer "rank has reached step `epoch`" and wait until all peers have;
+// phase 2: tell every peer "rank's accesses of step `epoch` are complete" and wait for theirs.
+// A wait that runs out stores an error code for every rank and for the host and returns; later
+// waits on any rank then give up at once, so all ranks fail together.
+int launch_exchange_fence(const FenceArgs &args, int phase, cudaStream_t stream);
+
 // Scalars of one step, computed on the host in f32 exactly as the reference does.
 struct StepScalars {
     float lr;
@@ -104,6 +129,17 @@ StepScalars make_scalars(int op, float lr, float beta1, float beta2, float eps, 
 int launch_multi_tensor(int op, const FatChunk *d_chunks, int64_t n_chunks, const uint8_t *d_present,
                         bool all_present, const StepScalars &s, int sm_count, cudaStream_t stream,
                         const PeerTable *peers = nullptr);
+
+// Checks shared by the two caller-buffer entry points, all on the host and before any launch:
+// null pointers, 4-byte alignment of every array the op touches (a misaligned pointer would
+// fault the scalar path of the kernel), Adam's t, and -- once per distinct pointer set -- that
+// every pointer is device (or managed) memory of the engine's device.  Allocates nothing.
+// *total receives the number of elements.
+int check_caller_buffers(const vb_optimizer_step_params *hp, int64_t n_tensors, const int64_t *sizes,
+                         void *const *params, const void *const *grads, void *const *state1, void *const *state2,
+                         int64_t *total);
+int check_caller_memory(vb_engine *e, const vb_optimizer_step_params *hp, int64_t n_tensors, const int64_t *sizes,
+                        void *const *params, const void *const *grads, void *const *state1, void *const *state2);
 
 // Device, SM count and stream of an engine / launch bookkeeping, for translation units that
 // do not see the engine's definition (api.cu).

@@ -25,6 +25,7 @@ from ._lib import (VB_NS_BF16, VB_NS_F32, VB_NS_F32_TC, VB_STEP_DEFAULT, VB_STEP
                    VoltaB200Error, call)
 
 __all__ = ["Engine", "Tensor", "Adam", "SGD", "Muon", "default_engine", "multi_tensor_step", "accumulate_grad",
+           "verify_plan", "plan_fingerprint",
            "VoltaB200Error", "VB_NS_F32", "VB_NS_BF16", "VB_NS_F32_TC", "VB_STEP_NO_EXCHANGE", "VB_STEP_EXCHANGE_BF16", "VB_STEP_REDUCE_GRADS", "VB_STEP_MEAN_GRADS"]
 
 
@@ -46,8 +47,18 @@ class Engine:
             call("vb_engine_destroy", self._h)
             self._h = C.c_void_p()
 
-    def synchronize(self) -> None:
-        call("vb_engine_synchronize", self._h)
+    def synchronize(self, timeout_ms: Optional[float] = None) -> None:
+        """Waits for the engine's stream.  With ``timeout_ms`` the wait has a deadline on the host
+        (the counterpart of ``sync_checked()``, src/gpu/context.rs:448-505): ``VB_ERR_TIMEOUT`` is
+        raised if work is still queued when it passes; nothing is cancelled."""
+        if timeout_ms is None:
+            call("vb_engine_synchronize", self._h)
+        else:
+            call("vb_engine_synchronize_deadline", self._h, float(timeout_ms))
+
+    def set_wait_limit_ms(self, ms: int) -> None:
+        """Bound of every device-side wait on another rank (default 5000 ms)."""
+        call("vb_engine_set_wait_limit_ms", self._h, int(ms))
 
     @property
     def stream(self) -> int:
@@ -302,6 +313,14 @@ class _Optimizer:
     def t(self, value: int) -> None:
         call("vb_optimizer_set_t", self._h, int(value))
 
+    # -- do all ranks describe the same optimizer? -------------------------------------------
+    def plan_fingerprint(self) -> int:
+        """64-bit hash of the tensor list, hyper-parameters, mode and world size (not of the
+        rank).  Gather it from every rank and pass the list to ``verify_plan``."""
+        fp = C.c_uint64()
+        call("vb_optimizer_plan_fingerprint", self._h, C.byref(fp))
+        return int(fp.value)
+
     # -- fused exchange over NVLink peer memory (sharded Adam / SGD) -------------------------
     def ipc_handle(self) -> bytes:
         """CUDA IPC handle (64 bytes) of this rank's parameter arena."""
@@ -471,6 +490,36 @@ class Muon(_Optimizer):
         f = C.c_double()
         call("vb_muon_last_ns_flops", self._h, C.byref(f))
         return float(f.value)
+
+
+def verify_plan(fingerprints: Sequence[int]) -> None:
+    """Raises ``VoltaB200Error`` (``VB_ERR_STATE``) on every rank if the ranks' plan fingerprints
+    (gathered in rank order over the host's own transport) differ: a sharded step is a collective
+    and must not be launched by ranks that describe different optimizers."""
+    n = len(fingerprints)
+    arr = (C.c_uint64 * max(n, 1))(*[int(f) for f in fingerprints])
+    bad = C.c_int(-1)
+    call("vb_plan_fingerprints_agree", arr, n, C.byref(bad))
+
+
+def plan_fingerprint(kind: str, sizes_or_shapes, hyper: Sequence[float], ints: Sequence[int] = (),
+                     world_size: int = 1) -> int:
+    """The same fingerprint without a device (``vb_plan_fingerprint``): ``kind`` "adam" | "sgd" |
+    "muon"; element counts for Adam / SGD, shapes for Muon."""
+    k = {"adam": 0, "sgd": 1, "muon": 2}[kind]
+    if k == 2:
+        dims = [muon_dims(s) for s in sizes_or_shapes]
+        a, b = [d[0] for d in dims], [d[1] for d in dims]
+    else:
+        a, b = [int(x) for x in sizes_or_shapes], None
+    n = len(a)
+    arr_a = (C.c_int64 * max(n, 1))(*a)
+    arr_b = (C.c_int64 * max(n, 1))(*b) if b is not None else None
+    hy = (C.c_float * max(len(hyper), 1))(*[float(x) for x in hyper])
+    it = (C.c_int32 * max(len(ints), 1))(*[int(x) for x in ints])
+    fp = C.c_uint64()
+    call("vb_plan_fingerprint", k, n, arr_a, arr_b, hy, len(hyper), it, len(ints), int(world_size), C.byref(fp))
+    return int(fp.value)
 
 
 def multi_tensor_step(engine: Engine, op: int, sizes: Sequence[int], params: Sequence[int],
