@@ -20,6 +20,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -35,6 +36,9 @@ sys.path.insert(0, ROOT)
 import workloads  # noqa: E402
 
 ADAM_BYTES_PER_PARAM = 28  # read theta, g, m, v (16) + write theta, m, v (12)
+C3_WORKLOAD = ("c3_transformer_adam: Adam lr=1e-3 betas=(0.9,0.999) eps=1e-8 wd=0.01, 157 tensors, "
+               "109602816 f32 params")
+MIN_TIMED_SECONDS = 0.5   # every headline number is the median of K-step blocks that together run at least this long
 
 
 def load_peaks():
@@ -65,7 +69,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-i", str(self.gpu_index), "-lms", "20"],
+                 "-i", str(self.gpu_index), "-lms", "10"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -145,25 +149,32 @@ def time_cpu_adam(wl, steps, warmup, max_seconds=25.0):
     return times
 
 
+def bench_config(n_gpus: int):
+    """The workload description both arms print (identical for the same N)."""
+    return {"workload": C3_WORKLOAD,
+            "inputs_vs_l2": "inputs larger than L2 (1.75 GB of theta/g/m/v per step vs 126 MB): no flush needed",
+            "sharding": "single GPU" if n_gpus == 1 else f"parameter arena in {n_gpus} equal slices (ZeRO-1), one rank per GPU"}
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
     wl = workloads.c3_transformer_adam()
-    times = time_cpu_adam(wl, args.steps, min(args.warmup, 1), max_seconds=120.0)
+    times = time_cpu_adam(wl, args.steps, args.warmup, max_seconds=240.0)
     sec = sum(times) / len(times)
     value = wl.total / sec
     cores = 1
     line = {
         "impl": "reference", "metric": "adam_params_per_s", "value": value, "unit": "params/s",
-        "n_gpus": args.gpus, "steps": len(times), "warmup": min(args.warmup, 1), "ms_per_step": sec * 1e3,
+        "n_gpus": args.gpus, "steps": len(times), "warmup": args.warmup, "ms_per_step": sec * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
-        "config": {"workload": C3_WORKLOAD,
-                   "host_cores_available": os.cpu_count()},
+        "config": bench_config(args.gpus),
         "cpu_baseline": {"value": value, "unit": "params/s", "cores": cores, "kind": "port",
+                         "host_cores_available": os.cpu_count(),
                          "sample": f"{len(times)} full steps of the whole workload, 1 thread "
-                                   "(Volta's optimizer is single threaded)"},
+                                   "(Volta's optimizer is single threaded: Tensor = Rc<RefCell<_>>)"},
         "e2e": {"value": value, "unit": "params/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -174,10 +185,6 @@ def run_reference(args):
 # ---------------------------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------------------------
-
-C3_WORKLOAD = ("c3_transformer_adam: Adam lr=1e-3 betas=(0.9,0.999) eps=1e-8 wd=0.01, 157 tensors, "
-               "109602816 f32 params")
-
 
 def bind_near_gpu(local_rank: int):
     """Runs this rank on the CPUs of its GPU's NUMA node, so that the pinned host buffers it allocates
@@ -213,6 +220,141 @@ def gather_handles(mine: bytes, world: int, dev):
     return [blob[r * 64:(r + 1) * 64] for r in range(world)]
 
 
+def timed_blocks(run_block, barrier, max_over_ranks, min_seconds=MIN_TIMED_SECONDS, max_blocks=400):
+    """Runs `run_block()` (which enqueues one K-step block and returns its device milliseconds after
+    waiting for it) again and again, each block between a barrier + synchronize on both sides, until
+    the blocks together cover `min_seconds`.  Every rank runs the same number of blocks (decided from
+    the first block's max-over-ranks time).  Returns the per-block times, max over ranks."""
+    barrier()
+    first = max_over_ranks(run_block())
+    barrier()
+    n = int(min(max_blocks, max(3, math.ceil(min_seconds * 1e3 / max(first, 1e-3)))))
+    out = [first]
+    for _ in range(n - 1):
+        ms = run_block()
+        barrier()
+        out.append(max_over_ranks(ms))
+    return out
+
+
+def block_stats(blocks_ms, steps):
+    return {"count": len(blocks_ms), "steps_per_block": steps, "median_ms": statistics.median(blocks_ms),
+            "min_ms": min(blocks_ms), "max_ms": max(blocks_ms), "timed_seconds": sum(blocks_ms) * 1e-3}
+
+
+def run_parity(eng, world, rank, dev, exchange):
+    """Outside every timed region: small Adam, SGD and Muon workloads sharded over all ranks with the
+    benchmark's exchange, three steps each; rank 0 runs the CPU oracle and every rank compares its WHOLE
+    parameter set with it.  Returns the `parity` object; any mismatch makes the run exit non-zero."""
+    import torch
+    import torch.distributed as dist
+
+    import oracle
+    import volta_b200
+    from volta_b200 import SGD, VB_NS_BF16, VB_NS_F32, Adam, Muon, Tensor
+
+    muon_shapes = [(256, 128), (128, 384), (64, 36), (100,), (512, 256), (256, 256), (384, 384), (128, 512),
+                   (768, 256), (3, 3)]
+    muon_wl = workloads.Workload("muon_parity", "muon", muon_shapes, [("normal", 0.02)] * len(muon_shapes), 1e-3,
+                                 dict(lr=0.1, momentum=0.9, nesterov=True, ns_steps=5), 3)
+    cases = [("adam", workloads.c5_ragged_adam(n_tensors=96, max_log2=16, seed=11), None),
+             ("sgd", workloads.c2_cnn_sgd(), None),
+             ("muon_f32", muon_wl, VB_NS_F32), ("muon_bf16", muon_wl, VB_NS_BF16)]
+    out = {"n_ranks": world, "steps": 3, "exchange": exchange if world > 1 else "none"}
+    all_equal = True
+    for name, wl, mode in cases:
+        h = wl.hyper
+        tensors = [Tensor(p, p.shape) for p in wl.make_params()]
+        if name == "adam":
+            opt = Adam(tensors, h["lr"], h["betas"], h["eps"], h["weight_decay"], engine=eng)
+        elif name == "sgd":
+            opt = SGD(tensors, h["lr"], h["momentum"], h["weight_decay"], engine=eng)
+        else:
+            opt = Muon(tensors, h["lr"], h["momentum"], h["nesterov"], h["ns_steps"], ns_mode=mode, engine=eng)
+        if world > 1:
+            fps = torch.zeros(world, dtype=torch.int64, device=dev)
+            mine = torch.tensor([opt.plan_fingerprint() & 0x7fffffffffffffff], dtype=torch.int64, device=dev)
+            dist.all_gather_into_tensor(fps, mine)
+            volta_b200.verify_plan([int(x) for x in fps.cpu().tolist()])   # all ranks describe the same optimizer
+            if exchange == "peer":
+                opt.open_peers(gather_handles(opt.ipc_handle(), world, dev))
+        for s in (1, 2, 3):
+            opt.zero_grad()
+            for t, g in zip(tensors, wl.make_grads(s)):
+                t.grad = g
+            opt.step()
+        eng.synchronize()
+        got = np.concatenate([t.data.reshape(-1) for t in tensors])
+        opt.close()
+        # the oracle's result, computed once on rank 0 and handed to every rank
+        want = torch.zeros(got.size, dtype=torch.float32, device=dev)
+        if rank == 0:
+            oracle.build()
+            ref = wl.make_params()
+            if name == "adam":
+                o = oracle.Adam(ref, h["lr"], h["betas"], h["eps"], h["weight_decay"])
+            elif name == "sgd":
+                o = oracle.SGD(ref, h["lr"], h["momentum"], h["weight_decay"])
+            else:
+                o = oracle.Muon(ref, h["lr"], h["momentum"], h["nesterov"], h["ns_steps"])
+            for s in (1, 2, 3):
+                o.step(wl.make_grads(s))
+            want.copy_(torch.from_numpy(np.concatenate([r.reshape(-1) for r in ref])))
+        if world > 1:
+            dist.broadcast(want, 0)
+        want = want.cpu().numpy()
+        exact = bool(np.array_equal(got.view(np.uint32), want.view(np.uint32)))
+        # parameters moved by lr * 0.1 * update per step: relate the difference to the distance travelled
+        start = np.concatenate([p.reshape(-1) for p in wl.make_params()])
+        rel = float(np.linalg.norm(got.astype(np.float64) - want) / max(np.linalg.norm(want.astype(np.float64) - start), 1e-300))
+        digest = int(np.bitwise_xor.reduce(got.view(np.uint32).astype(np.uint64) * np.uint64(0x9E3779B97F4A7C15)
+                                           + np.arange(got.size, dtype=np.uint64)) & np.uint64(0x7fffffffffffffff))
+        stats = torch.tensor([1.0 if exact else 0.0, -rel], dtype=torch.float64, device=dev)
+        dig = torch.tensor([digest], dtype=torch.int64, device=dev)
+        if world > 1:
+            dist.all_reduce(stats, op=dist.ReduceOp.MIN)   # all ranks exact; the largest relative error
+            digs = torch.zeros(world, dtype=torch.int64, device=dev)
+            dist.all_gather_into_tensor(digs, dig)
+            all_equal = all_equal and len(set(digs.cpu().tolist())) == 1
+        if name == "muon_bf16":
+            out["muon_bf16_rel_fro_max"] = -float(stats[1].item())
+        else:
+            out[f"{name}_bit_identical"] = bool(stats[0].item() == 1.0)
+    out["all_ranks_equal"] = all_equal
+    out["ok"] = bool(out["adam_bit_identical"] and out["sgd_bit_identical"] and out["muon_f32_bit_identical"]
+                     and out["muon_bf16_rel_fro_max"] <= 2e-2 and all_equal)
+    return out
+
+
+def pcie_floor(opt, grads_pinned, params_pinned, dev, barrier, max_over_ranks, reps=5):
+    """Plain pinned copies of this rank's slice up (gradients) and down (parameters), issued together on two
+    streams by all ranks at once, no kernel: what the host side gives one end-to-end step."""
+    import torch
+
+    from volta_b200.interop import device_array
+    p_ptr, g_ptr, arena, _ = opt.arena_layout()
+    lo, hi = opt.owned_range()
+    theta = torch.as_tensor(device_array(p_ptr, arena, opt), device=dev)
+    grad = torch.as_tensor(device_array(g_ptr, arena, opt), device=dev)
+    host_g = torch.from_numpy(grads_pinned.array)
+    host_p = torch.from_numpy(params_pinned.array)
+    up, down = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+    times = []
+    for _ in range(reps):
+        barrier()
+        t0 = time.perf_counter()
+        with torch.cuda.stream(up):
+            grad[lo:hi].copy_(host_g[lo:hi], non_blocking=True)
+        with torch.cuda.stream(down):
+            host_p[lo:hi].copy_(theta[lo:hi], non_blocking=True)
+        up.synchronize()
+        down.synchronize()
+        times.append(time.perf_counter() - t0)
+    barrier()
+    del theta, grad
+    return max_over_ranks(statistics.median(times)) * 1e3, bool(host_g.is_pinned())
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -228,7 +370,8 @@ def run_ours(args):
             raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run (one rank per GPU)")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-    numa_node = bind_near_gpu(local_rank) if world > 1 else None
+    numa_node = bind_near_gpu(local_rank)
+    cpu_set = sorted(os.sched_getaffinity(0))
     eng = Engine(local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
@@ -259,6 +402,14 @@ def run_ours(args):
             print(json.dumps({"metric": "muon_ns_tflops", "muon": muon}), flush=True)
         return 0
 
+    # ---- parity first (outside every timed region): all ranks against the CPU oracle ----
+    parity = None if args.skip_parity else run_parity(eng, world, rank, dev, args.exchange)
+    if parity is not None and not parity["ok"]:
+        if rank == 0:
+            print(json.dumps({"metric": "adam_params_per_s", "value": None, "n_gpus": world, "parity": parity,
+                              "error": "parity against the CPU oracle failed; nothing was timed"}), flush=True)
+        return 3
+
     wl = workloads.c3_transformer_adam()
     h = wl.hyper
     params = wl.make_params()
@@ -275,19 +426,18 @@ def run_ours(args):
 
     stream = torch.cuda.ExternalStream(eng.stream, device=dev)
 
-    def timed_steps(n, flags=0, per_step=False):
-        evs = [torch.cuda.Event(enable_timing=True) for _ in range(n + 1)]
-        evs[0].record(stream)
-        for i in range(n):
-            opt.step(flags)
-            if per_step or i == n - 1:
-                evs[i + 1].record(stream)
-        eng.synchronize()
-        total = evs[0].elapsed_time(evs[n])
-        steps_ms = [evs[i].elapsed_time(evs[i + 1]) for i in range(n)] if per_step else None
-        return total, steps_ms
+    def make_block(flags=0):
+        def run_block():
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(args.steps):
+                opt.step(flags)
+            e1.record(stream)
+            eng.synchronize()
+            return e0.elapsed_time(e1)
+        return run_block
 
-    # ---- device-resident timing: W warm-up steps, then exactly K steps ----
+    # ---- device-resident timing: W warm-up steps, then blocks of exactly K steps ----
     for _ in range(args.warmup):
         opt.step()
     barrier()
@@ -295,33 +445,69 @@ def run_ours(args):
     if rank == 0:
         sampler.start()
     launches0 = eng.launch_count
-    barrier()
-    total_ms, _ = timed_steps(args.steps)
-    barrier()
+    blocks = timed_blocks(make_block(0), barrier, max_over_ranks)
     launches = eng.launch_count - launches0
-
-    # the update kernel alone (no exchange), per-launch durations, for the roofline
-    barrier()
-    _, kernel_ms = timed_steps(args.steps, VB_STEP_NO_EXCHANGE, per_step=True)
-    barrier()
+    # the update kernel alone (no exchange): at N = 1 that is the same launch sequence
+    if world > 1:
+        kernel_blocks = timed_blocks(make_block(VB_STEP_NO_EXCHANGE), barrier, max_over_ranks, min_seconds=0.3)
+    else:
+        kernel_blocks = blocks
     clocks = sampler.stop() if rank == 0 else None
 
-    total_ms = max_over_ranks(total_ms)
-    kernel_avg_ms = max_over_ranks(sum(kernel_ms) / len(kernel_ms))
-    ms_per_step = total_ms / args.steps
+    ms_per_step = statistics.median(blocks) / args.steps
+    kernel_avg_ms = statistics.median(kernel_blocks) / args.steps
     value = wl.total / (ms_per_step * 1e-3)
 
+    # ---- the fabric's own rate for the exchange, measured in this run (N > 1, peer exchange) ----
+    nvlink = None
+    if world > 1 and args.exchange == "peer":
+        opt.peer_copy_probe(2)
+        barrier()
+        probe_ms = max_over_ranks(opt.peer_copy_probe(6))
+        barrier()
+        ingress = 4.0 * arena * (world - 1) / world
+        nvlink = {"ms": probe_ms, "bytes_in_per_gpu": ingress, "gbs_in_per_gpu": ingress / (probe_ms * 1e-3) / 1e9,
+                  "how": "every rank copies its slice of the parameter arena into every peer's arena with the copy "
+                         "engines, all ranks at once, between the two halves of the exchange fence (6 repetitions)"}
+
     # ---- end to end through the public API with host buffers ----
-    e2e_steps = 0 if args.skip_e2e else max(3, min(args.steps, 10))
-    barrier()
-    t0 = time.perf_counter()
-    # One public call per step: gradients up from pinned host memory, update, parameters back down
-    # (blocks until they are in host memory).  N > 1: a rank moves only its own slice over PCIe
-    # (what a reduce-scatter would hand it, and the parameters it updated).
-    for _ in range(e2e_steps):
-        opt.step_host(grads_pinned.array, params_pinned.array, pieces=max(4, 32 // world))  # ~14 MB per piece
-    barrier()
-    e2e_s = max_over_ranks((time.perf_counter() - t0) / max(e2e_steps, 1))
+    e2e = None
+    if not args.skip_e2e:
+        e2e_steps = args.steps
+        pieces = max(4, 32 // world)   # ~14 MB per piece
+        for _ in range(2):
+            opt.step_host(grads_pinned.array, params_pinned.array, pieces=pieces)
+        barrier()
+        t0 = time.perf_counter()
+        # One public call per step: gradients up from pinned host memory, update, parameters back down
+        # (blocks until they are in host memory).  N > 1: a rank moves only its own slice over PCIe
+        # (what a reduce-scatter would hand it, and the parameters it updated).
+        for _ in range(e2e_steps):
+            opt.step_host(grads_pinned.array, params_pinned.array, pieces=pieces)
+        barrier()
+        e2e_s = max_over_ranks((time.perf_counter() - t0) / e2e_steps)
+        # phases of the same call (a separate short pass: the extra events are not in the number above)
+        eng.set_profiling(True)
+        for ph in ("host_h2d", "update", "host_d2h", "exchange"):
+            eng.profile(ph)
+        n_ph = 5
+        for _ in range(n_ph):
+            opt.step_host(grads_pinned.array, params_pinned.array, pieces=pieces)
+        phases = {ph: max_over_ranks(eng.profile(ph)[0] / n_ph) for ph in ("host_h2d", "update", "host_d2h", "exchange")}
+        eng.set_profiling(False)
+        floor_ms, pinned_seen = pcie_floor(opt, grads_pinned, params_pinned, dev, barrier, max_over_ranks)
+        e2e = {"value": wl.total / e2e_s, "unit": "params/s", "h2d_bytes_per_step": arena * 4,
+               "d2h_bytes_per_step": arena * 4, "ms_per_step": e2e_s * 1e3, "steps": e2e_steps, "pieces": pieces,
+               "phases_ms": {"h2d_span": phases["host_h2d"], "update_span": phases["update"],
+                             "d2h_span": phases["host_d2h"], "fences": phases["exchange"],
+                             "note": "device time from the first to the last operation of each of the three streams of "
+                                     "one call (they overlap), max over ranks, from a separate 5-call pass"},
+               "pcie_floor_ms": floor_ms,
+               "pcie_floor_note": "plain pinned copies of every rank's slice up and down, issued together by all ranks, no "
+                                  "kernel (median of 5, max over ranks); pinned memory recognised: " + str(pinned_seen),
+               "frac_of_pcie_floor": floor_ms / (e2e_s * 1e3),
+               "note": "bytes are totals over all ranks; each rank moves its own 1/N slice of the arena",
+               "rank0_numa_node": numa_node, "rank0_cpus": f"{len(cpu_set)} CPUs {cpu_set[0]}-{cpu_set[-1]}"}
 
     # ---- N > 1: data-parallel step, the reduce-scatter of gradients fused into the kernel's loads ----
     # (These extra sections must never cost the headline: a library error in one of them, which every
@@ -333,10 +519,8 @@ def run_ours(args):
             opt.open_peers_grads(gather_handles(opt.ipc_handle_grads(), world, dev))
             for _ in range(3):
                 opt.step(VB_STEP_MEAN_GRADS)
-            barrier()
-            dp_ms, _ = timed_steps(args.steps, VB_STEP_MEAN_GRADS)
-            barrier()
-            dp_ms = max_over_ranks(dp_ms) / args.steps
+            dp_blocks = timed_blocks(make_block(VB_STEP_MEAN_GRADS), barrier, max_over_ranks, min_seconds=0.2)
+            dp_ms = statistics.median(dp_blocks) / args.steps
             dp_step = {"value": wl.total / (dp_ms * 1e-3), "unit": "params/s", "ms_per_step": dp_ms,
                        "note": "step(VB_STEP_MEAN_GRADS): every rank holds its own gradient of the whole model; the "
                                "owner's update kernel reads all ranks' gradients over NVLink, adds them in rank "
@@ -355,10 +539,8 @@ def run_ours(args):
                 opt.open_peers_bf16(gather_handles(opt.ipc_handle_bf16(), world, dev))
             for _ in range(3):
                 opt.step(VB_STEP_EXCHANGE_BF16)
-            barrier()
-            half_ms, _ = timed_steps(args.steps, VB_STEP_EXCHANGE_BF16)
-            barrier()
-            half_ms = max_over_ranks(half_ms) / args.steps
+            half_blocks = timed_blocks(make_block(VB_STEP_EXCHANGE_BF16), barrier, max_over_ranks, min_seconds=0.2)
+            half_ms = statistics.median(half_blocks) / args.steps
             bf16_exchange = {"value": wl.total / (half_ms * 1e-3), "unit": "params/s", "ms_per_step": half_ms,
                              "note": "step(VB_STEP_EXCHANGE_BF16): the update kernel also writes bf16 copies of the "
                                      "new parameters and only those cross NVLink (2 B/param instead of 4); f32 "
@@ -380,55 +562,69 @@ def run_ours(args):
         return 0
 
     achieved_gbs = ADAM_BYTES_PER_PARAM * (wl.total / world) / (kernel_avg_ms * 1e-3) / 1e9
+    config = bench_config(world)
     line = {
         "metric": "adam_params_per_s", "value": value, "unit": "params/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
-        "config": {"workload": C3_WORKLOAD,
-                   "l2": "inputs larger than L2 (1.75 GB of theta/g/m/v per step vs 126 MB)",
-                   "parallelism": f"zero1x{world}" if world > 1 else "single",
-                   "exchange": ("none" if world == 1 else
-                                "peer stores over NVLink fused into the update kernel, fenced by two one-float "
-                                "NCCL all-reduces" if args.exchange == "peer" else
-                                "nccl all-gather of updated params after the update kernel")},
+        "config": config,
+        "arm_details": {"exchange": ("none" if world == 1 else
+                                     "peer stores over NVLink fused into the update kernel, fenced by a flag barrier in "
+                                     "peer-mapped memory" if args.exchange == "peer" else
+                                     "nccl all-gather of updated params after the update kernel")},
+        "blocks": block_stats(blocks, args.steps),
         "update_only": {"value": wl.total / (kernel_avg_ms * 1e-3), "unit": "params/s",
-                        "ms_per_step": kernel_avg_ms,
+                        "ms_per_step": kernel_avg_ms, "blocks": block_stats(kernel_blocks, args.steps),
                         "note": "fused update kernel alone, max over ranks"},
         "roofline": {"bound": "hbm", "achieved": achieved_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                     "frac": achieved_gbs / peaks["hbm_gbs"], "traffic": None,
+                     "frac": achieved_gbs / peaks["hbm_gbs"], "traffic": NCU_ADAM_C3_DRAM_BYTES_PER_LAUNCH / world,
+                     "traffic_note": "ncu capture of a whole-arena launch" + ("" if world == 1 else
+                                     f", divided by {world}: a launch covers this rank's slice and traffic is "
+                                     "proportional to the elements updated"),
                      "peak_source": peaks["source"], "frac_of_nominal_8tbs": achieved_gbs / 8000.0,
                      "kernel": "multi_tensor_update_kernel<ADAM>",
                      "algorithmic_bytes_per_launch": ADAM_BYTES_PER_PARAM * (wl.total // world),
                      "launch_ms": kernel_avg_ms},
-        "e2e": {"value": wl.total / e2e_s, "unit": "params/s", "h2d_bytes_per_step": arena * 4,
-                "d2h_bytes_per_step": arena * 4, "ms_per_step": e2e_s * 1e3, "steps": e2e_steps,
-                "note": "bytes are totals over all ranks; each rank moves its own 1/N slice of the arena",
-                "rank0_numa_node": numa_node},
         "gpu_launches": int(launches),
+        "gpu_launches_note": f"update and fence kernels launched inside the {len(blocks)} timed blocks",
         "clocks": clocks,
     }
-    line["roofline"]["traffic"] = traffic_from_profile()
+    if clocks and clocks.get("sm_mhz"):
+        line["ms_per_step_x_sm_mhz"] = ms_per_step * clocks["sm_mhz"]
+    if e2e is not None:
+        line["e2e"] = e2e
+    if parity is not None:
+        line["parity"] = parity
 
-    if world == 1 and not args.no_cpu_baseline:
-        times = time_cpu_adam(wl, 12, 1, max_seconds=20.0)
+    if not args.no_cpu_baseline:
+        n_cpu = 12 if world == 1 else 3
+        times = time_cpu_adam(wl, n_cpu, 1, max_seconds=20.0 if world == 1 else 4.0)
         sec = sum(times) / len(times)
         line["cpu_baseline"] = {"value": wl.total / sec, "unit": "params/s", "cores": 1, "kind": "port",
                                 "sample": f"{len(times)} full steps of the same workload, 1 thread of "
-                                          f"{os.cpu_count()} host cores (Volta's optimizer is single threaded)",
+                                          f"{os.cpu_count()} host cores (Volta's optimizer is single threaded)"
+                                          + ("" if world == 1 else "; a shorter sample than at N=1"),
                                 "ms_per_step": sec * 1e3}
     if world > 1:
         # Every rank must receive the (N-1)/N of the updated parameters it does not own: NVLink
-        # ingress bounds the whole step whatever the update costs.  770 GB/s is the peer-copy rate
-        # measured per direction per GPU on this pool (900 nominal).
-        ingress = 4.0 * wl.total * (world - 1) / world
-        floor_ms = ingress / 770e9 * 1e3
-        line["exchange_roofline"] = {"bound": "nvlink ingress per GPU", "bytes_in_per_gpu": ingress, "peak": 770.0,
-                                     "unit": "GB/s", "floor_ms": floor_ms,
+        # ingress bounds the whole step whatever the update costs.
+        ingress = 4.0 * arena * (world - 1) / world
+        if nvlink is not None:
+            peak, src = nvlink["gbs_in_per_gpu"], "measured in this run (copy engines, all ranks sending at once)"
+        else:
+            peak, src = 770.0, "peer-copy rate of an earlier measurement (900 GB/s nominal)"
+        floor_ms = ingress / (peak * 1e9) * 1e3
+        line["exchange_roofline"] = {"bound": "nvlink ingress per GPU", "bytes_in_per_gpu": ingress, "peak": peak,
+                                     "peak_source": src, "unit": "GB/s", "floor_ms": floor_ms,
                                      "achieved": ingress / (ms_per_step * 1e-3) / 1e9,
                                      "frac": floor_ms / ms_per_step,
+                                     "strong_scaling_efficiency_bound": (wl.total / (floor_ms * 1e-3)) / world,
                                      "note": "strong scaling of the whole step is capped by this floor; the update "
-                                             "kernel itself scales with 1/N (update_only)"}
+                                             "kernel itself scales with 1/N (update_only); "
+                                             "strong_scaling_efficiency_bound is params/s per GPU at the floor"}
+        if nvlink is not None:
+            line["exchange_roofline"]["probe"] = nvlink
     if dp_step is not None:
         line["data_parallel_step"] = dp_step
     if bf16_exchange is not None:
@@ -535,19 +731,27 @@ def run_muon(args, eng, world, rank, dev, barrier, max_over_ranks, peaks):
         sampler = ClockSampler(dev.index) if rank == 0 and mode_name == "bf16" else None
         if sampler is not None:
             sampler.start()
-        barrier()
-        e0.record(stream)
-        for _ in range(steps):
-            opt.step()
-        e1.record(stream)
-        eng.synchronize()
-        barrier()
+
+        def run_block():
+            e0.record(stream)
+            for _ in range(steps):
+                opt.step()
+            e1.record(stream)
+            eng.synchronize()
+            return e0.elapsed_time(e1)
+
+        # blocks of `steps` steps until the timed region is long enough for the clocks to settle
+        # (the bit-faithful f32 mode is slow enough as it is)
+        blocks = timed_blocks(run_block, barrier, max_over_ranks,
+                              min_seconds=MIN_TIMED_SECONDS if mode_name == "bf16" else 0.25 if mode_name == "f32_tc" else 0.0,
+                              max_blocks=40)
         muon_clocks = sampler.stop() if sampler is not None else None
-        step_ms = max_over_ranks(e0.elapsed_time(e1) / steps)
-        ns_ms = max_over_ranks(eng.profile("muon_ns")[0] / steps)
-        pre_ms = eng.profile("muon_pre")[0] / steps
-        apply_ms = eng.profile("muon_apply")[0] / steps
-        exch_ms = eng.profile("exchange")[0] / steps
+        n_steps_total = steps * len(blocks)
+        step_ms = statistics.median(blocks) / steps
+        ns_ms = max_over_ranks(eng.profile("muon_ns")[0] / n_steps_total)
+        pre_ms = eng.profile("muon_pre")[0] / n_steps_total
+        apply_ms = eng.profile("muon_apply")[0] / n_steps_total
+        exch_ms = eng.profile("exchange")[0] / n_steps_total
         eng.set_profiling(False)
         flops_rank = opt.last_ns_flops
         if world > 1:
@@ -561,7 +765,7 @@ def run_muon(args, eng, world, rank, dev, barrier, max_over_ranks, peaks):
         out[mode_name] = {
             "ns_tflops": tflops, "ns_ms_per_step": ns_ms, "ms_per_step": step_ms,
             "pre_ms": pre_ms, "apply_ms": apply_ms, "exchange_ms": exch_ms,
-            "params_per_s": wl.total / (step_ms * 1e-3), "steps": steps,
+            "params_per_s": wl.total / (step_ms * 1e-3), "steps": steps, "blocks": block_stats(blocks, steps),
             "executed_flops_per_step": flops_total,
             "note": {"bf16": "tcgen05 bf16, short-side Gram, symmetric Gram computed on and above the diagonal only", "f32": "CUDA-core FFMA, bit-identical to the CPU arithmetic",
                      "f32_tc": "tcgen05, operands held as two f16 planes (three products per product); "
@@ -624,10 +828,6 @@ NCU_ADAM_C3_DRAM_BYTES_PER_LAUNCH = 3.0164e9
 NCU_MUON_4LAYER_DRAM_BYTES_PER_LAUNCH = 158.6e6
 
 
-def traffic_from_profile():
-    return NCU_ADAM_C3_DRAM_BYTES_PER_LAUNCH
-
-
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -640,6 +840,7 @@ def main():
     ap.add_argument("--skip-muon-f32", action="store_true", help="skip the (slow) f32 Newton-Schulz timing")
     ap.add_argument("--only-muon", action="store_true", help="profiling runs: Muon bf16 only")
     ap.add_argument("--skip-c5", action="store_true", help="skip the ragged 4096-tensor Adam section")
+    ap.add_argument("--skip-parity", action="store_true", help="profiling runs: skip the parity block")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="N > 1: updated parameters reach the other ranks by NVLink peer stores fused into the "
                          "update kernel (default) or by an NCCL all-gather after it")

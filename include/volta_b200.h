@@ -172,8 +172,10 @@ int vb_engine_launch_count(vb_engine *engine, uint64_t *count);
 #define VB_PHASE_MUON_PRE 1  /* Muon momentum, sum of squares, normalise */
 #define VB_PHASE_MUON_NS 2   /* Muon Newton-Schulz GEMM chain */
 #define VB_PHASE_MUON_APPLY 3
-#define VB_PHASE_EXCHANGE 4  /* NCCL all-gather / broadcast */
-#define VB_PHASE_COUNT 5
+#define VB_PHASE_EXCHANGE 4  /* fences of a fused exchange; NCCL all-gather / broadcast */
+#define VB_PHASE_HOST_H2D 5  /* vb_optimizer_step_host: gradient uploads (first to last, on their own stream) */
+#define VB_PHASE_HOST_D2H 6  /* vb_optimizer_step_host: parameter downloads (first to last, on their own stream) */
+#define VB_PHASE_COUNT 7
 int vb_engine_set_profiling(vb_engine *engine, int enabled);
 int vb_engine_profile(vb_engine *engine, int phase, double *total_ms, int64_t *count);
 
@@ -334,6 +336,16 @@ int vb_optimizer_set_lr(vb_optimizer *opt, float lr);
 #define VB_IPC_HANDLE_BYTES 64
 int vb_optimizer_ipc_handle(vb_optimizer *opt, void *handle64);
 int vb_optimizer_open_peers(vb_optimizer *opt, const void *handles, int n_handles);
+/* Measures, in the running job, what the NVLink fabric gives the parameter exchange: every rank
+ * copies the slice of the parameter arena it owns to the same position of every peer's arena
+ * with the copy engines (one cudaMemcpyAsync per peer, all in flight together, `reps` times),
+ * between the two halves of the exchange fence, so all ranks send and receive at once and the
+ * time covers the arrival of everybody's data.  The copies rewrite values the peers already hold
+ * after a step, so the parameters are unchanged.  *ms_per_rep is this rank's device time per
+ * repetition; bytes in and out per repetition are (world - 1) slices each.  Needs
+ * vb_optimizer_open_peers; all ranks must call it together.  Benchmarks use the result as the
+ * measured ceiling of a sharded step's exchange. */
+int vb_optimizer_peer_copy_probe(vb_optimizer *opt, int reps, double *ms_per_rep);
 
 /* Data-parallel gradients (no counterpart in the reference, which has one process and one
  * device).  Every rank holds its own gradient of the whole model in its gradient arena; after
@@ -386,7 +398,13 @@ int vb_optimizer_get_t(vb_optimizer *opt, int64_t *t);
 int vb_optimizer_set_t(vb_optimizer *opt, int64_t t);
 
 /* Muon only: copies the orthogonalised update of the last step for one tensor (the
- * reference's local `update`, src/nn/optim/muon.rs:139-155) to the host. */
+ * reference's local `update`, src/nn/optim/muon.rs:139-155) to the host.  In the reference the
+ * update is a temporary of step(); here the last Newton-Schulz launch of a tensor-core mode
+ * applies it to the weights in its epilogue and does not store it unless
+ * vb_muon_set_keep_update(opt, 1) was called before the step (VB_ERR_STATE otherwise; matrices
+ * on the f32 kernels and vectors are always available).  Keeping it costs 4 bytes of HBM
+ * writes per parameter and step. */
+int vb_muon_set_keep_update(vb_optimizer *opt, int keep);
 int vb_muon_download_update(vb_optimizer *opt, int64_t tensor, float *host, int64_t n);
 /* Muon only: tensor-core FLOPs executed by the last step's Newton-Schulz chain. */
 int vb_muon_last_ns_flops(vb_optimizer *opt, double *flops);

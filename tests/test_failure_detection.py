@@ -26,7 +26,7 @@ def test_bounded_wait_expiry_is_reported_and_engine_survives(oracle, engine):
     rng = np.random.default_rng(0)
     g = (rng.standard_normal((256, 384)) * 1e-3).astype(np.float32)
     w = Tensor(np.zeros((256, 384), np.float32))
-    opt = Muon([w], 0.1, 0.0, False, 5, ns_mode=VB_NS_BF16, engine=engine)
+    opt = Muon([w], 0.1, 0.0, False, 5, ns_mode=VB_NS_BF16, engine=engine, keep_update=True)
     w.grad = g
     opt.step()
     assert rel_frobenius(opt.last_update(0), oracle.newton_schulz(g, 5)) <= 2e-2

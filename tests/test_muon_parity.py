@@ -24,7 +24,7 @@ def _run(oracle, engine, shapes, steps, ns_mode, lr=0.1, momentum=0.9, nesterov=
     params = [(rng.standard_normal(s) * param_std).astype(np.float32) for s in shapes]
     ref_params = [p.copy() for p in params]
     tensors = [Tensor(p, p.shape) for p in params]
-    opt = Muon(tensors, lr, momentum, nesterov, ns_steps, ns_mode=ns_mode, engine=engine)
+    opt = Muon(tensors, lr, momentum, nesterov, ns_steps, ns_mode=ns_mode, engine=engine, keep_update=True)
     ref = oracle.Muon(ref_params, lr, momentum, nesterov, ns_steps, gemm_mode=gemm_mode)
     out = []
     for s in range(1, steps + 1):
@@ -55,7 +55,7 @@ def test_reference_muon_test(engine):
     from volta_b200 import VB_NS_F32, Muon, Tensor
     x = Tensor([1.0, -1.0, 0.5, 0.5], (2, 2), True)
     x.grad = [0.1, 0.1, -0.1, -0.1]
-    opt = Muon([x], 0.1, 0.9, True, 5, ns_mode=VB_NS_F32, engine=engine)
+    opt = Muon([x], 0.1, 0.9, True, 5, ns_mode=VB_NS_F32, engine=engine, keep_update=True)
     before = x.data.copy()
     opt.step()
     after = x.data.copy()
@@ -123,7 +123,7 @@ def test_ordered_sum_adversarial_values(oracle, engine):
     cases.append(x)                                                                # big first, then tiny
     for g in cases:
         w = Tensor(np.zeros((n_r, n_c), np.float32))
-        opt = Muon([w], 0.1, 0.0, False, 0, ns_mode=VB_NS_F32, engine=engine)
+        opt = Muon([w], 0.1, 0.0, False, 0, ns_mode=VB_NS_F32, engine=engine, keep_update=True)
         w.grad = g
         opt.step()
         wr = np.zeros((n_r, n_c), np.float32)
@@ -171,7 +171,7 @@ def test_bf16_path_single_matrix(oracle, engine, shape):
     rng = np.random.default_rng(sum(shape))
     g = (rng.standard_normal(shape) * 1e-3).astype(np.float32)
     w = Tensor(np.zeros(shape, np.float32))
-    opt = Muon([w], 0.1, 0.0, False, 5, ns_mode=VB_NS_BF16, engine=engine)
+    opt = Muon([w], 0.1, 0.0, False, 5, ns_mode=VB_NS_BF16, engine=engine, keep_update=True)
     w.grad = g
     opt.step()
     got = opt.last_update(0)
@@ -211,7 +211,7 @@ def test_bf16_path_c4_layer_shapes(oracle, engine):
     rng = np.random.default_rng(11)
     grads = [(rng.standard_normal(s) * 1e-3).astype(np.float32) for s in shapes]
     tensors = [Tensor((rng.standard_normal(s) * 0.02).astype(np.float32)) for s in shapes]
-    opt = Muon(tensors, 0.1, 0.9, True, 5, ns_mode=VB_NS_BF16, engine=engine)
+    opt = Muon(tensors, 0.1, 0.9, True, 5, ns_mode=VB_NS_BF16, engine=engine, keep_update=True)
     for t, g in zip(tensors, grads):
         t.grad = g
     opt.step()
@@ -251,7 +251,7 @@ def test_f32_tc_path_c4_layer_shapes(oracle, engine):
     rng = np.random.default_rng(12)
     grads = [(rng.standard_normal(s) * 1e-3).astype(np.float32) for s in shapes]
     tensors = [Tensor((rng.standard_normal(s) * 0.02).astype(np.float32)) for s in shapes]
-    opt = Muon(tensors, 0.1, 0.9, True, 5, ns_mode=VB_NS_F32_TC, engine=engine)
+    opt = Muon(tensors, 0.1, 0.9, True, 5, ns_mode=VB_NS_F32_TC, engine=engine, keep_update=True)
     for t, g in zip(tensors, grads):
         t.grad = g
     opt.step()
@@ -272,7 +272,7 @@ def test_f32_tc_tiny_updates(oracle, engine):
     for scale in (1e-15, 1e-13, 1e-11, 1e-9, 1e-7, 1e-5):
         g = (rng.standard_normal((128, 64)) * scale).astype(np.float32)
         w = Tensor(np.ones((128, 64), np.float32))
-        opt = Muon([w], 0.1, 0.0, False, 5, ns_mode=VB_NS_F32_TC, engine=engine)
+        opt = Muon([w], 0.1, 0.0, False, 5, ns_mode=VB_NS_F32_TC, engine=engine, keep_update=True)
         w.grad = g
         opt.step()
         got = opt.last_update(0)
@@ -280,7 +280,7 @@ def test_f32_tc_tiny_updates(oracle, engine):
         assert rel_frobenius(got, oracle.newton_schulz(g, 5)) <= TOL_F32, scale
         opt.close()
     w = Tensor(np.ones((128, 64), np.float32))
-    opt = Muon([w], 0.1, 0.0, False, 5, ns_mode=VB_NS_F32_TC, engine=engine)
+    opt = Muon([w], 0.1, 0.0, False, 5, ns_mode=VB_NS_F32_TC, engine=engine, keep_update=True)
     w.grad = np.zeros((128, 64), np.float32)
     opt.step()
     assert not np.any(opt.last_update(0)) and np.array_equal(w.data, np.ones((128, 64), np.float32))
@@ -297,7 +297,7 @@ def test_tensor_core_paths_across_gradient_scales(oracle, engine, mode_name):
     for scale in (1e-15, 1e-10, 1e-6, 1.0, 1e4, 1e8, 1e15):
         g = (rng.standard_normal((256, 128)) * scale).astype(np.float32)
         w = Tensor(np.ones((256, 128), np.float32))
-        opt = Muon([w], 0.1, 0.0, False, 5, ns_mode=mode, engine=engine)
+        opt = Muon([w], 0.1, 0.0, False, 5, ns_mode=mode, engine=engine, keep_update=True)
         w.grad = g
         opt.step()
         got = opt.last_update(0)
@@ -317,7 +317,7 @@ def test_iteration_counts(oracle, engine, mode_name, ns_steps):
     shapes = [(512, 256), (256, 512), (256, 256), (264, 72)]
     grads = [(rng.standard_normal(s) * 1e-3).astype(np.float32) for s in shapes]
     tensors = [Tensor(np.zeros(s, np.float32)) for s in shapes]
-    opt = Muon(tensors, 0.1, 0.0, False, ns_steps, ns_mode=mode, engine=engine)
+    opt = Muon(tensors, 0.1, 0.0, False, ns_steps, ns_mode=mode, engine=engine, keep_update=True)
     for t, g in zip(tensors, grads):
         t.grad = g
     opt.step()
@@ -329,3 +329,110 @@ def test_iteration_counts(oracle, engine, mode_name, ns_steps):
         else:
             assert rel_frobenius(got, ref) <= tol, (shapes[i], rel_frobenius(got, ref))
     opt.close()
+
+
+# ---- one whole layer of the benchmark configuration, three consecutive steps, all three modes --------
+
+C4_LAYER = [(3072, 1024), (1024, 1024), (4096, 1024), (1024, 4096)]
+
+
+@pytest.fixture(scope="module")
+def c4_layer_reference(oracle):
+    """The CPU oracle on one full layer (3072x1024, 1024x1024, 4096x1024 and the wide 1024x4096, the
+    latter in the reference's own cols x cols formulation, src/nn/optim/muon.rs:73), momentum 0.9 with
+    Nesterov, five Newton-Schulz iterations, three consecutive steps: ~1.5 TFLOP of CPU work on all
+    host threads.  Computed once for the three modes."""
+    oracle.set_threads(oracle.max_threads())
+    rng = np.random.default_rng(2024)
+    start = [(rng.standard_normal(s) * 0.02).astype(np.float32) for s in C4_LAYER]
+    grads = [[(rng.standard_normal(s) * 1e-3).astype(np.float32) for s in C4_LAYER] for _ in range(3)]
+    params = [p.copy() for p in start]
+    ref = oracle.Muon(params, 0.1, 0.9, True, 5)
+    updates, weights, velocity = [], [], []
+    for gs in grads:
+        ref.step(gs)
+        updates.append([u.copy() for u in ref.last_update])
+        weights.append([p.copy() for p in params])
+        velocity.append([v.copy() for v in ref.velocity])
+    oracle.set_threads(1)
+    return dict(start=start, grads=grads, updates=updates, weights=weights, velocity=velocity)
+
+
+@pytest.mark.parametrize("mode_name", ["f32", "f32_tc", "bf16"])
+def test_c4_layer_three_steps_with_momentum(engine, c4_layer_reference, mode_name):
+    """Momentum carried through Newton-Schulz at full size: per step the update of every matrix
+    (the wide one included) against the oracle, the velocity bit for bit, and the weights, whose
+    distance travelled since the start must agree to the mode's bound (bit for bit on the f32 path)."""
+    from volta_b200 import VB_NS_BF16, VB_NS_F32, VB_NS_F32_TC, Muon, Tensor
+    mode, tol = {"f32": (VB_NS_F32, 0.0), "f32_tc": (VB_NS_F32_TC, TOL_F32), "bf16": (VB_NS_BF16, TOL_BF16)}[mode_name]
+    ref = c4_layer_reference
+    tensors = [Tensor(p.copy()) for p in ref["start"]]
+    opt = Muon(tensors, 0.1, 0.9, True, 5, ns_mode=mode, engine=engine, keep_update=True)
+    for step in range(3):
+        opt.zero_grad()
+        for t, g in zip(tensors, ref["grads"][step]):
+            t.grad = g
+        opt.step()
+        for i, shape in enumerate(C4_LAYER):
+            got = opt.last_update(i)
+            want = ref["updates"][step][i]
+            assert bits_equal(opt.state(i, 0), ref["velocity"][step][i]), (step, shape)
+            if mode_name == "f32":
+                assert bits_equal(got, want), (step, shape, rel_frobenius(got, want))
+                assert bits_equal(tensors[i].data, ref["weights"][step][i]), (step, shape)
+            else:
+                assert rel_frobenius(got, want) <= tol, (step, shape, rel_frobenius(got, want))
+                moved = tensors[i].data.astype(np.float64) - ref["start"][i]
+                moved_ref = ref["weights"][step][i].astype(np.float64) - ref["start"][i]
+                # f32 weights of size 0.02 carry ~1e-8 of rounding per step of size ~1e-5: allow for it
+                assert rel_frobenius(moved, moved_ref) <= tol + 2e-3 * (mode_name == "f32_tc"), (step, shape)
+    opt.close()
+
+
+def test_f32_path_tall_c4_matrix_five_iterations(oracle, engine):
+    """The bit-faithful kernels at the benchmark's tall shape with all five iterations."""
+    from volta_b200 import VB_NS_F32, Muon, Tensor
+    oracle.set_threads(oracle.max_threads())
+    rng = np.random.default_rng(8)
+    g = (rng.standard_normal((4096, 1024)) * 1e-3).astype(np.float32)
+    w = Tensor(np.zeros((4096, 1024), np.float32))
+    opt = Muon([w], 0.1, 0.0, False, 5, ns_mode=VB_NS_F32, engine=engine, keep_update=True)
+    w.grad = g
+    opt.step()
+    assert bits_equal(opt.last_update(0), oracle.newton_schulz(g, 5))
+    oracle.set_threads(1)
+    opt.close()
+
+
+@pytest.mark.parametrize("mode_name", ["bf16", "f32_tc"])
+def test_apply_fused_into_the_last_launch_gives_the_same_weights(oracle, engine, mode_name):
+    """By default the tensor-core modes apply the update inside their last launch and never store
+    it; with keep_update it is stored as well.  The weights must be the same bit for bit either way
+    (and they are compared with the oracle wherever the update is: every test above keeps it), over
+    full and ragged tiles, a matrix on the f32 kernels, a vector, missing gradients and momentum."""
+    from volta_b200 import VB_NS_BF16, VB_NS_F32_TC, Muon, Tensor, VoltaB200Error
+    mode = VB_NS_BF16 if mode_name == "bf16" else VB_NS_F32_TC
+    shapes = [(512, 256), (256, 768), (264, 72), (1032, 264), (64, 36), (50,), (256, 256)]
+    rng = np.random.default_rng(17)
+    start = [(rng.standard_normal(s) * 0.02).astype(np.float32) for s in shapes]
+    grads = [[(rng.standard_normal(s) * 1e-3).astype(np.float32) for s in shapes] for _ in range(3)]
+    results = []
+    for keep in (True, False):
+        tensors = [Tensor(p.copy()) for p in start]
+        opt = Muon(tensors, 0.1, 0.9, True, 5, ns_mode=mode, engine=engine, keep_update=keep)
+        for step, gs in enumerate(grads):
+            opt.zero_grad()
+            for i, (t, g) in enumerate(zip(tensors, gs)):
+                if (i + step) % 4 != 3:      # some gradients are missing in every step
+                    t.grad = g
+            opt.step()
+        if not keep:
+            with pytest.raises(VoltaB200Error) as ei:
+                opt.last_update(0)
+            assert ei.value.status == 5           # not stored: VB_ERR_STATE
+            assert opt.last_update(4).shape == (64, 36)   # the f32-kernel matrix always is
+        results.append([t.data.copy() for t in tensors])
+        opt.close()
+    for a, b, p0 in zip(results[0], results[1], start):
+        assert bits_equal(a, b)
+        assert not bits_equal(a, p0)

@@ -108,6 +108,7 @@ SIGNATURES = {
     "vb_optimizer_import_state": [_vp, _i64, C.c_int, _vp, _i64],
     "vb_optimizer_ipc_handle": [_vp, _vp],
     "vb_optimizer_open_peers": [_vp, _vp, C.c_int],
+    "vb_optimizer_peer_copy_probe": [_vp, C.c_int, C.POINTER(C.c_double)],
     "vb_optimizer_ipc_handle_grads": [_vp, _vp],
     "vb_optimizer_open_peers_grads": [_vp, _vp, C.c_int],
     "vb_optimizer_enable_bf16_params": [_vp],
@@ -118,6 +119,7 @@ SIGNATURES = {
     "vb_optimizer_open_peers_bf16": [_vp, _vp, C.c_int],
     "vb_optimizer_get_t": [_vp, _i64p],
     "vb_optimizer_set_t": [_vp, _i64],
+    "vb_muon_set_keep_update": [_vp, C.c_int],
     "vb_muon_download_update": [_vp, _i64, _vp, _i64],
     "vb_muon_last_ns_flops": [_vp, C.POINTER(C.c_double)],
     "vb_multi_tensor_step": [_vp, C.POINTER(StepParams), _i64, _i64p, _vpp, _vpp, _vpp, _vpp],

@@ -61,21 +61,21 @@ static cudaEvent_t prof_event(vb_engine *e)
     return ev;
 }
 
-void prof_begin(vb_engine *e, int phase)
+void prof_begin(vb_engine *e, int phase, cudaStream_t stream)
 {
     if (!e->profiling) return;
     cudaEvent_t ev = prof_event(e);
     if (!ev) return;
-    cudaEventRecord(ev, e->stream);
+    cudaEventRecord(ev, stream ? stream : e->stream);
     e->prof_open[phase] = ev;
 }
 
-void prof_end(vb_engine *e, int phase)
+void prof_end(vb_engine *e, int phase, cudaStream_t stream)
 {
     if (!e->profiling || !e->prof_open[phase]) return;
     cudaEvent_t ev = prof_event(e);
     if (!ev) return;
-    cudaEventRecord(ev, e->stream);
+    cudaEventRecord(ev, stream ? stream : e->stream);
     e->prof_pairs[phase].emplace_back(e->prof_open[phase], ev);
     e->prof_open[phase] = nullptr;
 }
@@ -640,6 +640,10 @@ int vb_engine_destroy(vb_engine *e)
     }
     for (cudaEvent_t ev : e->prof_free) cudaEventDestroy(ev);
     if (e->deadline_event) cudaEventDestroy(e->deadline_event);
+    for (cudaStream_t st : e->peer_streams)
+        if (st) cudaStreamDestroy(st);
+    for (cudaEvent_t ev : e->peer_events)
+        if (ev) cudaEventDestroy(ev);
     if (e->d_accum_scratch) cudaFree(e->d_accum_scratch);
     for (cudaEvent_t ev : e->pipe_events) cudaEventDestroy(ev);
     if (e->h2d_stream) cudaStreamDestroy(e->h2d_stream);
@@ -732,6 +736,8 @@ int vb_engine_profile(vb_engine *e, int phase, double *total_ms, int64_t *count)
     if (phase < 0 || phase >= VB_PHASE_COUNT) return fail(VB_ERR_INVALID_ARG, "unknown phase %d", phase);
     VB_CUDA(cudaSetDevice(e->device));
     VB_CUDA(cudaStreamSynchronize(e->stream));
+    if (e->h2d_stream) VB_CUDA(cudaStreamSynchronize(e->h2d_stream));
+    if (e->d2h_stream) VB_CUDA(cudaStreamSynchronize(e->d2h_stream));
     double total = 0.0;
     for (auto &pr : e->prof_pairs[phase]) {
         float ms = 0.0f;
@@ -1288,6 +1294,10 @@ int vb_optimizer_step_host(vb_optimizer *opt, const float *grads_host, float *pa
     VB_CUDA(cudaEventRecord(ev_start, e->stream));
     VB_CUDA(cudaStreamWaitEvent(e->h2d_stream, ev_start, 0));
     VB_CUDA(cudaStreamWaitEvent(e->d2h_stream, ev_start, 0));
+    // phase timing (when on): the span of each stream's part of the step; the three overlap
+    prof_begin(e, VB_PHASE_HOST_H2D, e->h2d_stream);
+    prof_begin(e, VB_PHASE_UPDATE);
+    prof_begin(e, VB_PHASE_HOST_D2H, e->d2h_stream);
     const int64_t nc = opt->n_chunks;
     for (int j = 0; j < pieces; ++j) {
         const int64_t c_lo = nc * j / pieces, c_hi = nc * (j + 1) / pieces;
@@ -1306,6 +1316,9 @@ int vb_optimizer_step_host(vb_optimizer *opt, const float *grads_host, float *pa
         VB_CUDA(cudaStreamWaitEvent(e->d2h_stream, e->pipe_events[2 * j + 1], 0));
         VB_CUDA(cudaMemcpyAsync(params_host + a_lo, opt->d_param + a_lo, bytes, cudaMemcpyDeviceToHost, e->d2h_stream));
     }
+    prof_end(e, VB_PHASE_HOST_H2D, e->h2d_stream);
+    prof_end(e, VB_PHASE_UPDATE);
+    prof_end(e, VB_PHASE_HOST_D2H, e->d2h_stream);
     VB_TRY(exchange_fence(opt, xp, 2));
     if (xp.nccl_f32) VB_TRY(comm_all_gather_inplace(e, opt->d_param, opt->arena / e->world));
     if (xp.nccl_half)
@@ -1509,6 +1522,47 @@ int vb_optimizer_open_peers(vb_optimizer *opt, const void *handles, int n_handle
     VB_API_END
 }
 
+int vb_optimizer_peer_copy_probe(vb_optimizer *opt, int reps, double *ms_per_rep)
+{
+    VB_API_BEGIN
+    VB_TRY(check_opt(opt));
+    if (!ms_per_rep || reps < 1) return fail(VB_ERR_INVALID_ARG, "reps must be >= 1 and ms_per_rep non-null");
+    vb_engine *e = opt->eng;
+    if (opt->peers.n <= 0) return fail(VB_ERR_STATE, "vb_optimizer_open_peers first");
+    if (opt->kind == KIND_MUON) return fail(VB_ERR_UNSUPPORTED, "the probe copies arena slices (Adam, SGD)");
+    VB_TRY(set_device(e));
+    VB_TRY(fence_check_error(opt));
+    const int np = opt->peers.n;
+    for (int k = 0; k < np; ++k)
+        if (!e->peer_streams[k]) VB_CUDA(cudaStreamCreateWithFlags(&e->peer_streams[k], cudaStreamNonBlocking));
+    for (int k = 0; k < np + 3; ++k)
+        if (!e->peer_events[k]) VB_CUDA(cudaEventCreateWithFlags(&e->peer_events[k], k < np + 1 ? cudaEventDisableTiming : cudaEventDefault));
+    cudaEvent_t ev_fork = e->peer_events[np], t0 = e->peer_events[np + 1], t1 = e->peer_events[np + 2];
+    ExchangePlan xp;
+    VB_TRY(plan_exchange(opt, VB_STEP_DEFAULT, &xp));
+    const size_t bytes = (size_t)(opt->shard_end - opt->shard_begin) * sizeof(float);
+    VB_TRY(exchange_fence(opt, xp, 1));  // every rank is here: all start sending together
+    VB_CUDA(cudaEventRecord(t0, e->stream));
+    for (int rep = 0; rep < reps; ++rep) {
+        VB_CUDA(cudaEventRecord(ev_fork, e->stream));
+        for (int k = 0; k < np; ++k) {
+            VB_CUDA(cudaStreamWaitEvent(e->peer_streams[k], ev_fork, 0));
+            VB_CUDA(cudaMemcpyAsync(opt->peers.base[k] + opt->shard_begin, opt->d_param + opt->shard_begin, bytes,
+                                    cudaMemcpyDeviceToDevice, e->peer_streams[k]));
+            VB_CUDA(cudaEventRecord(e->peer_events[k], e->peer_streams[k]));
+            VB_CUDA(cudaStreamWaitEvent(e->stream, e->peer_events[k], 0));
+        }
+    }
+    VB_TRY(exchange_fence(opt, xp, 2));  // ... and every rank's copies into this arena have landed
+    VB_CUDA(cudaEventRecord(t1, e->stream));
+    VB_CUDA(cudaStreamSynchronize(e->stream));
+    float ms = 0.0f;
+    VB_CUDA(cudaEventElapsedTime(&ms, t0, t1));
+    *ms_per_rep = (double)ms / (double)reps;
+    return fence_check_error(opt);
+    VB_API_END
+}
+
 int vb_optimizer_ipc_handle_grads(vb_optimizer *opt, void *handle64)
 {
     VB_API_BEGIN
@@ -1559,6 +1613,13 @@ int vb_muon_download_update(vb_optimizer *opt, int64_t tensor, float *host, int6
     VB_TRY(set_device(opt->eng));
     return muon_download_update(opt, tensor, host, n);
     VB_API_END
+}
+
+int vb_muon_set_keep_update(vb_optimizer *opt, int keep)
+{
+    VB_TRY(check_opt(opt));
+    if (opt->kind != KIND_MUON) return fail(VB_ERR_INVALID_ARG, "not a Muon optimizer");
+    return muon_set_keep_update(opt, keep);
 }
 
 int vb_muon_last_ns_flops(vb_optimizer *opt, double *flops)

@@ -31,6 +31,8 @@ struct vb_engine {
     // copy streams and events of the pipelined host step (vb_optimizer_step_host)
     cudaStream_t h2d_stream = nullptr, d2h_stream = nullptr;
     std::vector<cudaEvent_t> pipe_events;
+    cudaStream_t peer_streams[vb::kMaxPeers] = {};  // vb_optimizer_peer_copy_probe: one copy stream per peer
+    cudaEvent_t peer_events[vb::kMaxPeers + 3] = {};
     float *d_accum_scratch = nullptr;  // staging for host contributions to vb_optimizer_accumulate_grad
     size_t accum_scratch_elems = 0;
     // caller-buffer entry points: hashes of the pointer sets whose memory type and device were
@@ -101,8 +103,8 @@ struct vb_optimizer {
 namespace vb {
 
 // api.cu: phase timing; no-ops unless profiling is on
-void prof_begin(vb_engine *e, int phase);
-void prof_end(vb_engine *e, int phase);
+void prof_begin(vb_engine *e, int phase, cudaStream_t stream = nullptr);  // stream: default the engine's
+void prof_end(vb_engine *e, int phase, cudaStream_t stream = nullptr);
 
 // muon.cu
 int muon_init(vb_optimizer *opt);
@@ -111,6 +113,7 @@ int muon_download_update(vb_optimizer *opt, int64_t tensor, float *host, int64_t
 int muon_last_flops(vb_optimizer *opt, double *flops);
 int muon_owner(vb_optimizer *opt, int64_t tensor);
 int debug_gemm_wait_expiry(vb_engine *e, uint32_t wait_limit, int *role_code);
+int muon_set_keep_update(vb_optimizer *opt, int keep);
 int muon_debug_withhold(vb_optimizer *opt, uint32_t wait_limit);  // test hook, see vb_debug_muon_withhold_loads
 int muon_check_error(vb_optimizer *opt);  // VB_ERR_TIMEOUT if a GEMM kernel reported a bounded wait expiring
 float *muon_velocity_ptr(vb_optimizer *opt, int64_t tensor);  // nullptr if not owned

@@ -15,6 +15,7 @@
 
 #include <math.h>
 #include <stddef.h>
+#include <stdlib.h>
 
 #include <algorithm>
 #include <numeric>
@@ -728,6 +729,13 @@ struct MuonState {
     int n_tc_gram_tiles = 0, n_tc_upd_tiles = 0, n_tc_upd_tiles_last = 0;
     int *d_error = nullptr;
     int *h_error = nullptr;              // pinned mirror of d_error, refreshed after every step
+    // The last update launch applies its result to the weights itself (tensor-core matrices); the
+    // apply kernel then covers only the other tensors.  VB_MUON_UNFUSED_APPLY=1 keeps the separate
+    // pass for all (for comparison).  keep_update: the f32 update is stored as well.
+    bool fuse_apply = false;
+    bool keep_update = false;
+    ChunkDesc *d_chunks_apply = nullptr;
+    int64_t n_chunks_apply = 0;
     bool debug_withhold = false;         // test hook: the next step's first Gram launch stages nothing
     uint32_t debug_wait_limit = 0;
     double flops_per_step = 0.0;
@@ -757,6 +765,7 @@ void destroy_muon_state(MuonState *s)
     cudaFree(s->d_desc);
     cudaFree(s->d_desc_apply);
     cudaFree(s->d_chunks);
+    cudaFree(s->d_chunks_apply);
     for (int i = 0; i < 2; ++i) {
         cudaFree(s->d_gram_prob[i]);
         cudaFree(s->d_upd_prob[i]);
@@ -912,6 +921,15 @@ int muon_init(vb_optimizer *opt)
     }
     first_chunk[(size_t)nt] = (int64_t)chunks.size();
     s->n_chunks = (int64_t)chunks.size();
+    {
+        const char *unfused = getenv("VB_MUON_UNFUSED_APPLY");
+        s->fuse_apply = !(unfused && *unfused == '1');
+        std::vector<ChunkDesc> apply_chunks;
+        for (const ChunkDesc &c : chunks)
+            if (!(s->fuse_apply && s->ns_kind[c.tensor] >= 2)) apply_chunks.push_back(c);
+        s->n_chunks_apply = (int64_t)apply_chunks.size();
+        VB_TRY(upload(&s->d_chunks_apply, apply_chunks, e->stream));
+    }
     VB_TRY(upload(&s->d_desc, desc, e->stream));
     VB_TRY(upload(&s->d_chunks, chunks, e->stream));
     VB_TRY(upload(&s->d_first_chunk, first_chunk, e->stream));
@@ -1095,6 +1113,8 @@ int muon_init(vb_optimizer *opt)
                 if (last) {
                     u.out_bf16 = nullptr;  // last iteration: the f32 update is the result
                     u.out_f32 = s->d_upd + s->local_off[(size_t)t];
+                    u.apply_w = opt->d_param + opt->offsets[(size_t)t];  // used when the launch applies it
+                    u.apply_arena_pos = opt->offsets[(size_t)t];
                 }
                 upd[(size_t)it].push_back(u);
             }
@@ -1156,7 +1176,11 @@ int muon_step(vb_optimizer *opt, uint32_t flags)
     const bool fast_norm = opt->ns_mode == VB_NS_BF16;  // both f32 modes need the reference's ordered sum
     const bool gsum = xp.pt.n_grad > 0;
     // peers' gradients are read by the first kernel: every rank must have reached its step
-    if (gsum) VB_TRY(exchange_fence(opt, xp, 1));
+    bool fence1_done = false;
+    if (gsum) {
+        VB_TRY(exchange_fence(opt, xp, 1));
+        fence1_done = true;
+    }
     const uint32_t gemm_wait_limit = s->debug_wait_limit;  // 0 = the default; set by the expiry test hook
     if (s->debug_withhold && compute && !s->d_tc_gram.empty()) {
         const int32_t one = 1;
@@ -1221,9 +1245,25 @@ int muon_step(vb_optimizer *opt, uint32_t flags)
                 VB_TRY(launch_ns_gemm_tc(s->d_tc_gram[(size_t)it], s->d_tc_gram_tiles, s->n_tc_gram_tiles,
                                          opt->d_present, s->d_error, e->sm_count, e->stream, gemm_wait_limit, split));
                 const bool last_it = it == opt->ns_steps - 1;
+                TcApplyArgs ap{};
+                if (last_it && s->fuse_apply) {
+                    // this launch writes the new weights (also into the peers): nobody is written to
+                    // before it has reached its step
+                    if (!fence1_done) {
+                        prof_end(e, VB_PHASE_MUON_NS);
+                        VB_TRY(exchange_fence(opt, xp, 1));
+                        prof_begin(e, VB_PHASE_MUON_NS);
+                        fence1_done = true;
+                    }
+                    ap.enabled = 1;
+                    ap.keep_update = s->keep_update ? 1 : 0;
+                    ap.lr = opt->lr;
+                    ap.pt = xp.pt;
+                }
                 VB_TRY(launch_ns_gemm_tc(s->d_tc_upd[(size_t)it], last_it ? s->d_tc_upd_tiles_last : s->d_tc_upd_tiles,
                                          last_it ? s->n_tc_upd_tiles_last : s->n_tc_upd_tiles,
-                                         opt->d_present, s->d_error, e->sm_count, e->stream, gemm_wait_limit, split));
+                                         opt->d_present, s->d_error, e->sm_count, e->stream, gemm_wait_limit, split,
+                                         ap.enabled ? &ap : nullptr));
                 e->launches += 2;
             }
             if (s->n_gram_tiles > 0) {
@@ -1248,14 +1288,16 @@ int muon_step(vb_optimizer *opt, uint32_t flags)
         s->debug_wait_limit = 0;
     }
     // see vb_optimizer_step_ex: nobody is written to before it has reached its step
-    if (!gsum) VB_TRY(exchange_fence(opt, xp, 1));
-    if (s->n_chunks > 0 && compute) {
+    if (!fence1_done) VB_TRY(exchange_fence(opt, xp, 1));
+    if (s->n_chunks_apply > 0 && compute) {
         prof_begin(e, VB_PHASE_MUON_APPLY);
         const bool f32_peers = xp.pt.n > 0;
         const int half = xp.pt.half_local == nullptr ? 0 : xp.pt.n_half > 0 ? 2 : 1;
+        const int apply_grid = (int)std::min<int64_t>(s->n_chunks_apply, (int64_t)e->sm_count * 8);
 #define VB_APPLY(P, H)                                                                                      \
-    apply_kernel<P, H><<<ew_grid, kEwThreads, 0, e->stream>>>(s->d_desc_apply, s->d_chunks, s->n_chunks, \
-                                                             opt->d_present, opt->lr, xp.pt, s->d_error)
+    apply_kernel<P, H><<<apply_grid, kEwThreads, 0, e->stream>>>(s->d_desc_apply, s->d_chunks_apply,      \
+                                                                s->n_chunks_apply, opt->d_present, opt->lr, xp.pt, \
+                                                                s->d_error)
         if (half == 0) {
             if (f32_peers) VB_APPLY(true, 0); else VB_APPLY(false, 0);
         } else if (half == 1) {
@@ -1289,6 +1331,12 @@ int muon_step(vb_optimizer *opt, uint32_t flags)
     return VB_OK;
 }
 
+int muon_set_keep_update(vb_optimizer *opt, int keep)
+{
+    opt->muon->keep_update = keep != 0;
+    return VB_OK;
+}
+
 int muon_debug_withhold(vb_optimizer *opt, uint32_t wait_limit)
 {
     MuonState *s = opt->muon;
@@ -1306,6 +1354,9 @@ int muon_download_update(vb_optimizer *opt, int64_t tensor, float *host, int64_t
         return fail(VB_ERR_STATE, "tensor %lld is owned by rank %d", (long long)tensor, s->owner[(size_t)tensor]);
     if (n == 0) return VB_OK;
     if (!host) return fail(VB_ERR_INVALID_ARG, "host pointer is null");
+    if (s->fuse_apply && s->ns_kind[(size_t)tensor] >= 2 && opt->ns_steps > 0 && !s->keep_update)
+        return fail(VB_ERR_STATE, "the update of a tensor-core matrix is applied inside the last GEMM and not stored; "
+                                  "call vb_muon_set_keep_update(opt, 1) before the step");
     VB_CUDA(cudaMemcpyAsync(host, s->final_update[(size_t)tensor], (size_t)n * sizeof(float),
                             cudaMemcpyDeviceToHost, opt->eng->stream));
     VB_CUDA(cudaStreamSynchronize(opt->eng->stream));

@@ -117,12 +117,28 @@ struct alignas(128) TcGemmProblem {
     const __nv_bfloat16 *in_bf16;  // TC_EPI_NS_COMBINE only: planes of X (same ld and plane stride as the output)
     __nv_bfloat16 *out_bf16; // may be null
     float *out_f32;          // may be null
+    // Launches with TcApplyArgs::enabled: the weights of this matrix (row-major, ld_out) and the
+    // arena position of their first element; the epilogue applies the update to them in place.
+    float *apply_w;
+    int64_t apply_arena_pos;
+};
+
+// The last update launch of a step can apply its result instead of (or besides) storing it:
+//     w -= (lr * u) * 0.1                                            (src/nn/optim/muon.rs:158-160)
+// with u the f32 value the epilogue would have written, so the weights are those the separate
+// apply kernel computes, bit for bit.  With peer arenas in `pt` the new weights (and their bf16
+// copies) are also stored into every peer, as that kernel does.
+struct TcApplyArgs {
+    int enabled;      // 0: an ordinary launch
+    int keep_update;  // also store the f32 update (for vb_muon_download_update)
+    float lr;
+    PeerTable pt;
 };
 
 // wait_limit: mbarrier polls before a role gives up (0 = the default, about a second).
 int launch_ns_gemm_tc(const TcGemmProblem *d_problems, const GemmTile *d_tiles, int n_tiles,
                       const uint8_t *d_present, int *d_error_flag, int sm_count, cudaStream_t stream,
-                      uint32_t wait_limit = 0, bool split = false);
+                      uint32_t wait_limit = 0, bool split = false, const TcApplyArgs *apply = nullptr);
 void tc_gemm_tile_shape(int *bm, int *bn);
 int make_bf16_tensor_map(void *map_out, const void *base, int64_t inner, int64_t outer, int mode, int planes = 1,
                          int64_t plane_stride = 0);

@@ -359,10 +359,45 @@ __device__ __forceinline__ void st_global_256(void *p, const uint32_t (&q)[8])
                  : "memory");
 }
 
+__device__ __forceinline__ void ld_global_256(const void *p, uint32_t (&q)[8])
+{
+    asm volatile("ld.global.L1::no_allocate.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(q[0]), "=r"(q[1]), "=r"(q[2]), "=r"(q[3]), "=r"(q[4]), "=r"(q[5]), "=r"(q[6]), "=r"(q[7])
+                 : "l"(p));
+}
+
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b)
 {
     __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
     return *reinterpret_cast<uint32_t *>(&h);
+}
+
+// Muon's apply on 8 consecutive weights of one row (32-byte aligned): w -= (lr * u) * 0.1 with the
+// reference's order of operations (src/nn/optim/muon.rs:158-160, each product and the difference
+// rounded once), then the stores the apply kernel would do: the local arena, every peer's arena,
+// the bf16 copy and the peers' bf16 copies.  `wq` holds the old weights and receives the new ones.
+__device__ __forceinline__ void apply_octet(uint32_t (&wq)[8], const float *u, float lr, float *w_dst, int64_t arena_pos,
+                                            const PeerTable &pt)
+{
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+        wq[j] = __float_as_uint(__fsub_rn(__uint_as_float(wq[j]), __fmul_rn(__fmul_rn(lr, u[j]), 0.1f)));
+    st_global_256(w_dst, wq);
+    if (pt.n > 0) {
+#pragma unroll
+        for (int r = 0; r < kMaxPeers; ++r)
+            if (r < pt.n) st_global_256(pt.base[r] + arena_pos, wq);
+    }
+    if (pt.half_local != nullptr) {
+        const uint4 h = make_uint4(pack_bf16(__uint_as_float(wq[0]), __uint_as_float(wq[1])),
+                                   pack_bf16(__uint_as_float(wq[2]), __uint_as_float(wq[3])),
+                                   pack_bf16(__uint_as_float(wq[4]), __uint_as_float(wq[5])),
+                                   pack_bf16(__uint_as_float(wq[6]), __uint_as_float(wq[7])));
+        *reinterpret_cast<uint4 *>(pt.half_local + arena_pos) = h;
+#pragma unroll
+        for (int r = 0; r < kMaxPeers; ++r)
+            if (r < pt.n_half) *reinterpret_cast<uint4 *>(pt.half_base[r] + arena_pos) = h;
+    }
 }
 
 // The f32-accurate path: every operand is held as two f16 planes of the value scaled by 2^15,
@@ -386,11 +421,23 @@ __device__ __forceinline__ int term_plane_b(int n_terms, int term) { return n_te
 template <int EPI>
 __device__ __forceinline__ void drain_chunk_fast(const uint32_t (&v)[32], float mult, bool diagonal_piece, int lane,
                                                  __nv_bfloat16 *__restrict__ dst_bf16, float *__restrict__ dst_f32,
-                                                 __nv_bfloat16 *__restrict__ mirror_dst, float *__restrict__ t_f32, int64_t ld)
+                                                 __nv_bfloat16 *__restrict__ mirror_dst, float *__restrict__ t_f32, int64_t ld,
+                                                 float *__restrict__ w_dst, int64_t w_arena_pos, const TcApplyArgs &ap)
 {
+    // fused apply: fetch the old weights of this row piece first (4 x 32 bytes), the arithmetic on
+    // the accumulator hides their latency
+    uint32_t wq[4][8];
+    if (w_dst) {
+#pragma unroll
+        for (int g8 = 0; g8 < 4; ++g8) ld_global_256(w_dst + g8 * 8, wq[g8]);
+    }
     float f[32];
 #pragma unroll
     for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]) * mult;
+    if (w_dst) {
+#pragma unroll
+        for (int g8 = 0; g8 < 4; ++g8) apply_octet(wq[g8], f + g8 * 8, ap.lr, w_dst + g8 * 8, w_arena_pos + g8 * 8, ap.pt);
+    }
     if (EPI == TC_EPI_THREE_I_MINUS && diagonal_piece) {  // warp-uniform: row - col0 == lane
 #pragma unroll
         for (int j = 0; j < 32; ++j) f[j] = (j == lane) ? 3.0f + f[j] : f[j];
@@ -426,7 +473,7 @@ __device__ __forceinline__ void drain_chunk_fast(const uint32_t (&v)[32], float 
 template <int EPI>
 __device__ __forceinline__ void drain_fast(uint32_t taddr, int row, int tile_col0, bool row_ok, float mult, int lane,
                                            __nv_bfloat16 *out_bf16, float *out_f32, bool mirror, bool transpose,
-                                           int64_t ld)
+                                           int64_t ld, float *apply_w, int64_t apply_pos, const TcApplyArgs &ap)
 {
     constexpr int kPieces = (BN / 2) / 32;
     uint32_t v[2][32];
@@ -443,7 +490,8 @@ __device__ __forceinline__ void drain_fast(uint32_t taddr, int row, int tile_col
                                   (out_bf16 && !transpose) ? out_bf16 + at : nullptr,
                                   (out_f32 && !transpose) ? out_f32 + at : nullptr,
                                   (out_bf16 && (mirror || transpose)) ? out_bf16 + at_t : nullptr,
-                                  (out_f32 && transpose) ? out_f32 + at_t : nullptr, ld);
+                                  (out_f32 && transpose) ? out_f32 + at_t : nullptr, ld,
+                                  apply_w ? apply_w + at : nullptr, apply_pos + at, ap);
         }
     }
 }
@@ -460,6 +508,9 @@ struct DrainArgs {
     __nv_bfloat16 *out_bf16;
     float *out_f32;
     const __nv_bfloat16 *in_bf16;
+    float *apply_w;        // fused apply: the matrix's weights (null: none), see TcApplyArgs
+    int64_t apply_pos;     // arena position of the matrix's first element
+    const TcApplyArgs *ap;
 };
 // 16-bit output formats: bf16 on the plain path, f16 planes on the split path.
 template <bool kHalf>
@@ -543,10 +594,20 @@ __device__ __forceinline__ void drain_generic(const DrainArgs &a)
             }
             // the update of the split kernel is in the scaled domain: what goes out in f32 is scaled back
             const bool scaled = kSplit && epi == TC_EPI_NS_COMBINE;
-            if (scaled && out_f32) {
+            if (scaled && (out_f32 != nullptr || a.apply_w != nullptr)) {
                 const float back = ldexpf(1.0f, a.split_e - 15);
 #pragma unroll
                 for (int j = 0; j < 32; ++j) f[j] *= back;
+            }
+            if (a.apply_w != nullptr) {  // never combined with a transposed output
+                const int64_t at = (int64_t)row * ld + col0;
+#pragma unroll
+                for (int g8 = 0; g8 < 4; ++g8) {  // N and ld are multiples of 8: whole octets, 32-byte aligned
+                    if (col0 + g8 * 8 >= N) break;
+                    uint32_t wq[8];
+                    ld_global_256(a.apply_w + at + g8 * 8, wq);
+                    apply_octet(wq, f + g8 * 8, a.ap->lr, a.apply_w + at + g8 * 8, a.apply_pos + at + g8 * 8, a.ap->pt);
+                }
             }
             if (out_f32 && transpose) {
                 float *tdst = out_f32 + (int64_t)col0 * ld + row;
@@ -657,7 +718,8 @@ __device__ __forceinline__ TileInfo fetch_tile(const TcGemmProblem *problems, co
 template <int kCtas, bool kSplit>
 __global__ void __launch_bounds__(kThreads, 1)
 ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__restrict__ tiles, int n_tiles,
-                  const uint8_t *__restrict__ present, int *__restrict__ error_flag, uint32_t wait_limit)
+                  const uint8_t *__restrict__ present, int *__restrict__ error_flag, uint32_t wait_limit,
+                  const __grid_constant__ TcApplyArgs ap)
 {
     using C = Cfg<kCtas>;
     extern __shared__ uint8_t smem_raw[];
@@ -862,7 +924,10 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
             const int M = p->M, N = p->N;
             const int epi = p->epilogue;
             __nv_bfloat16 *out_bf16 = p->out_bf16;
-            float *out_f32 = p->out_f32;
+            // a launch that applies its result keeps the f32 update only on request
+            float *apply_w = ap.enabled ? p->apply_w : nullptr;
+            const int64_t apply_pos = p->apply_arena_pos;
+            float *out_f32 = (apply_w != nullptr && !ap.keep_update) ? nullptr : p->out_f32;
             const __nv_bfloat16 *in_bf16 = p->in_bf16;  // TC_EPI_NS_COMBINE: the planes of X at the output position
             // Frobenius normalisation folded into the first iteration (plain bf16 path): the operand is
             // the unnormalised update u, the accumulator is scaled by 1/norm (or its square)
@@ -907,13 +972,13 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
                 // (a * s) * 0.5 == a * (s * 0.5) and -(a * s) == a * (-s) exactly
                 if (epi == TC_EPI_HALF)
                     drain_fast<TC_EPI_HALF>(taddr, row, tile_col0, row < M, 0.5f * acc_scale, lane, out_bf16, out_f32,
-                                            ti.mirror, transpose, ld);
+                                            ti.mirror, transpose, ld, apply_w, apply_pos, ap);
                 else if (epi == TC_EPI_THREE_I_MINUS)
                     drain_fast<TC_EPI_THREE_I_MINUS>(taddr, row, tile_col0, row < M, -acc_scale, lane, out_bf16,
-                                                     out_f32, ti.mirror, transpose, ld);
+                                                     out_f32, ti.mirror, transpose, ld, nullptr, 0, ap);
                 else
                     drain_fast<TC_EPI_IDENTITY>(taddr, row, tile_col0, row < M, acc_scale, lane, out_bf16, out_f32,
-                                                ti.mirror, transpose, ld);
+                                                ti.mirror, transpose, ld, nullptr, 0, ap);
             }
             if (!fast) {
                 DrainArgs da;
@@ -921,6 +986,7 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
                 da.lane = lane; da.acc_scale = acc_scale; da.split_e = split_e; da.ld = ld; da.plane_stride = plane_stride;
                 da.out_planes = out_planes; da.out_planes_in = out_planes_in; da.bf16_rows_32b = bf16_rows_32b;
                 da.mirror = ti.mirror; da.transpose = transpose; da.out_bf16 = out_bf16; da.out_f32 = out_f32; da.in_bf16 = in_bf16;
+                da.apply_w = apply_w; da.apply_pos = apply_pos; da.ap = &ap;
                 drain_generic<kSplit>(da);
             }
             tcgen05_fence_before();
@@ -1051,7 +1117,7 @@ int make_bf16_tensor_map(void *map_out, const void *base, int64_t inner, int64_t
 template <int kCtas, bool kSplit>
 static int launch_variant(const TcGemmProblem *d_problems, const GemmTile *d_tiles, int n_tiles,
                           const uint8_t *d_present, int *d_error_flag, int sm_count, cudaStream_t stream,
-                          uint32_t wait_limit)
+                          uint32_t wait_limit, const TcApplyArgs &ap)
 {
     static bool attr_set = false;
     if (!attr_set) {
@@ -1063,7 +1129,7 @@ static int launch_variant(const TcGemmProblem *d_problems, const GemmTile *d_til
         int grid = sm_count;  // one persistent CTA per SM (it owns all 512 TMEM columns)
         if (grid > n_tiles) grid = n_tiles;
         ns_gemm_tc_kernel<kCtas, kSplit><<<grid, kThreads, smem_bytes<kCtas>(), stream>>>(
-            d_problems, d_tiles, n_tiles, d_present, d_error_flag, wait_limit);
+            d_problems, d_tiles, n_tiles, d_present, d_error_flag, wait_limit, ap);
         VB_CUDA(cudaGetLastError());
         return VB_OK;
     }
@@ -1091,26 +1157,27 @@ static int launch_variant(const TcGemmProblem *d_problems, const GemmTile *d_til
     if (clusters > n_tiles) clusters = n_tiles;
     cfg.gridDim = dim3((unsigned)(clusters * 2));
     VB_CUDA(cudaLaunchKernelEx(&cfg, ns_gemm_tc_kernel<kCtas, kSplit>, d_problems, d_tiles, n_tiles, d_present,
-                               d_error_flag, wait_limit));
+                               d_error_flag, wait_limit, ap));
     return VB_OK;
 }
 
 // split: the problems' operands are two f16 planes (all problems of a launch are alike).
 int launch_ns_gemm_tc(const TcGemmProblem *d_problems, const GemmTile *d_tiles, int n_tiles,
                       const uint8_t *d_present, int *d_error_flag, int sm_count, cudaStream_t stream,
-                      uint32_t wait_limit, bool split)
+                      uint32_t wait_limit, bool split, const TcApplyArgs *apply)
 {
     if (n_tiles <= 0) return VB_OK;
     if (wait_limit == 0) wait_limit = kDefaultWaitLimit;
+    const TcApplyArgs ap = apply ? *apply : TcApplyArgs{};
     if (tc_use_pair())
         return split ? launch_variant<2, true>(d_problems, d_tiles, n_tiles, d_present, d_error_flag, sm_count, stream,
-                                               wait_limit)
+                                               wait_limit, ap)
                      : launch_variant<2, false>(d_problems, d_tiles, n_tiles, d_present, d_error_flag, sm_count, stream,
-                                                wait_limit);
+                                                wait_limit, ap);
     return split ? launch_variant<1, true>(d_problems, d_tiles, n_tiles, d_present, d_error_flag, sm_count, stream,
-                                           wait_limit)
+                                           wait_limit, ap)
                  : launch_variant<1, false>(d_problems, d_tiles, n_tiles, d_present, d_error_flag, sm_count, stream,
-                                            wait_limit);
+                                            wait_limit, ap);
 }
 
 }  // namespace vb

@@ -73,7 +73,7 @@ class Engine:
         call("vb_engine_launch_count", self._h, C.byref(n))
         return int(n.value)
 
-    PHASES = {"update": 0, "muon_pre": 1, "muon_ns": 2, "muon_apply": 3, "exchange": 4}
+    PHASES = {"update": 0, "muon_pre": 1, "muon_ns": 2, "muon_apply": 3, "exchange": 4, "host_h2d": 5, "host_d2h": 6}
 
     def set_profiling(self, enabled: bool) -> None:
         call("vb_engine_set_profiling", self._h, int(bool(enabled)))
@@ -336,6 +336,14 @@ class _Optimizer:
             raise ValueError("every handle must be 64 bytes")
         call("vb_optimizer_open_peers", self._h, C.c_char_p(blob), len(handles))
 
+    def peer_copy_probe(self, reps: int = 4) -> float:
+        """Device milliseconds per repetition of "every rank copies its slice to every peer with
+        the copy engines, all at once" (``vb_optimizer_peer_copy_probe``): the fabric's own rate
+        for the parameter exchange, measured in the running job.  All ranks call it together."""
+        ms = C.c_double()
+        call("vb_optimizer_peer_copy_probe", self._h, int(reps), C.byref(ms))
+        return float(ms.value)
+
     # -- data-parallel gradients: reduce-scatter fused into the update kernel's loads -------
     def ipc_handle_grads(self) -> bytes:
         buf = C.create_string_buffer(64)
@@ -469,7 +477,10 @@ class Muon(_Optimizer):
     cores through three-way bf16 splitting)."""
 
     def __init__(self, params, lr: float, momentum: float, nesterov: bool, ns_steps: int,
-                 ns_mode: int = VB_NS_F32, engine: Optional[Engine] = None):
+                 ns_mode: int = VB_NS_F32, engine: Optional[Engine] = None, keep_update: bool = False):
+        """``keep_update``: also store the orthogonalised update of every step so that
+        ``last_update(i)`` can return it (the tensor-core modes otherwise apply it to the weights
+        inside their last launch and never write it; the reference's ``update`` is a temporary too)."""
         super().__init__(params, engine)
         n = len(self.params)
         dims = [muon_dims(p.shape) for p in self.params]
@@ -477,6 +488,8 @@ class Muon(_Optimizer):
         cols = (C.c_int64 * max(n, 1))(*[d[1] for d in dims])
         call("vb_muon_create", self.engine._h, n, rows, cols, lr, momentum, int(bool(nesterov)),
              int(ns_steps), int(ns_mode), C.byref(self._h))
+        if keep_update:
+            call("vb_muon_set_keep_update", self._h, 1)
         self._adopt()
 
     def last_update(self, i: int) -> np.ndarray:
