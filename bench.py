@@ -226,14 +226,17 @@ def timed_blocks(run_block, barrier, max_over_ranks, min_seconds=MIN_TIMED_SECON
     the blocks together cover `min_seconds`.  Every rank runs the same number of blocks (decided from
     the first block's max-over-ranks time).  Returns the per-block times, max over ranks."""
     barrier()
-    first = max_over_ranks(run_block())
+    mine = [run_block()]
+    first = max_over_ranks(mine[0])
     barrier()
     n = int(min(max_blocks, max(3, math.ceil(min_seconds * 1e3 / max(first, 1e-3)))))
     out = [first]
     for _ in range(n - 1):
         ms = run_block()
         barrier()
+        mine.append(ms)
         out.append(max_over_ranks(ms))
+    timed_blocks.last_local = mine   # this rank's own times of the same blocks
     return out
 
 
@@ -453,6 +456,11 @@ def run_ours(args):
     else:
         kernel_blocks = blocks
     clocks = sampler.stop() if rank == 0 else None
+    per_rank_update_ms = [statistics.median(timed_blocks.last_local) / args.steps]
+    if world > 1:
+        t = torch.zeros(world, dtype=torch.float64, device=dev)
+        dist.all_gather_into_tensor(t, torch.tensor(per_rank_update_ms, dtype=torch.float64, device=dev))
+        per_rank_update_ms = [float(x) for x in t.cpu().tolist()]
 
     ms_per_step = statistics.median(blocks) / args.steps
     kernel_avg_ms = statistics.median(kernel_blocks) / args.steps
@@ -576,6 +584,7 @@ def run_ours(args):
         "blocks": block_stats(blocks, args.steps),
         "update_only": {"value": wl.total / (kernel_avg_ms * 1e-3), "unit": "params/s",
                         "ms_per_step": kernel_avg_ms, "blocks": block_stats(kernel_blocks, args.steps),
+                        "per_rank_ms_per_step": per_rank_update_ms,
                         "note": "fused update kernel alone, max over ranks"},
         "roofline": {"bound": "hbm", "achieved": achieved_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": achieved_gbs / peaks["hbm_gbs"], "traffic": NCU_ADAM_C3_DRAM_BYTES_PER_LAUNCH / world,
