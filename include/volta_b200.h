@@ -394,6 +394,11 @@ int vb_optimizer_export_state(vb_optimizer *opt, int64_t tensor, int which, floa
                               int64_t *owned_begin, int64_t *owned_end);
 int vb_optimizer_import_state(vb_optimizer *opt, int64_t tensor, int which, const float *host,
                               int64_t n);
+/* Puts the optimizer's state back to what the constructor leaves (moments / velocity zero,
+ * src/nn/optim/adam.rs:26-47, sgd.rs:30-41, muon.rs:26-29; t = 0), on the device, without
+ * touching parameters or gradients.  Benchmarks use it to replay a configuration from its
+ * start; a training loop that restarts a schedule can too. */
+int vb_optimizer_reset_state(vb_optimizer *opt);
 int vb_optimizer_get_t(vb_optimizer *opt, int64_t *t);
 int vb_optimizer_set_t(vb_optimizer *opt, int64_t t);
 

@@ -117,6 +117,7 @@ SIGNATURES = {
     "vb_optimizer_download_params_bf16": [_vp, C.c_int64, _vp, C.c_int64],
     "vb_optimizer_ipc_handle_bf16": [_vp, _vp],
     "vb_optimizer_open_peers_bf16": [_vp, _vp, C.c_int],
+    "vb_optimizer_reset_state": [_vp],
     "vb_optimizer_get_t": [_vp, _i64p],
     "vb_optimizer_set_t": [_vp, _i64],
     "vb_muon_set_keep_update": [_vp, C.c_int],

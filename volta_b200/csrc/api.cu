@@ -1589,6 +1589,24 @@ int vb_optimizer_open_peers_grads(vb_optimizer *opt, const void *handles, int n_
     VB_API_END
 }
 
+int vb_optimizer_reset_state(vb_optimizer *opt)
+{
+    VB_API_BEGIN
+    VB_TRY(check_opt(opt));
+    vb_engine *e = opt->eng;
+    VB_TRY(set_device(e));
+    if (opt->kind == KIND_MUON) {
+        VB_TRY(muon_reset_velocity(opt));
+    } else {
+        const size_t bytes = (size_t)opt->state_elems * sizeof(float);
+        if (opt->d_s1) VB_CUDA(cudaMemsetAsync(opt->d_s1, 0, bytes, e->stream));
+        if (opt->d_s2) VB_CUDA(cudaMemsetAsync(opt->d_s2, 0, bytes, e->stream));
+    }
+    opt->t = 0;
+    return VB_OK;
+    VB_API_END
+}
+
 int vb_optimizer_get_t(vb_optimizer *opt, int64_t *t)
 {
     VB_TRY(check_opt(opt));

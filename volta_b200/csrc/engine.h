@@ -114,6 +114,7 @@ int muon_last_flops(vb_optimizer *opt, double *flops);
 int muon_owner(vb_optimizer *opt, int64_t tensor);
 int debug_gemm_wait_expiry(vb_engine *e, uint32_t wait_limit, int *role_code);
 int muon_set_keep_update(vb_optimizer *opt, int keep);
+int muon_reset_velocity(vb_optimizer *opt);
 int muon_debug_withhold(vb_optimizer *opt, uint32_t wait_limit);  // test hook, see vb_debug_muon_withhold_loads
 int muon_check_error(vb_optimizer *opt);  // VB_ERR_TIMEOUT if a GEMM kernel reported a bounded wait expiring
 float *muon_velocity_ptr(vb_optimizer *opt, int64_t tensor);  // nullptr if not owned

@@ -59,9 +59,20 @@ constexpr int kEpiWarps = 8;                             // two per TMEM lane qu
 constexpr int kThreads = 64 + kEpiWarps * 32;            // producer warp + MMA warp + epilogue warps
 constexpr uint32_t kDefaultWaitLimit = 1u << 22;         // mbarrier polls before giving up
 
-template <int kCtas>
+// Staging of the plain kernel's epilogue: each epilogue warp owns 32 rows of 128 payload bytes
+// (+ 16 of padding, which makes both the row-per-lane writes and the 4-lanes-per-row reads free
+// of bank conflicts).  A lane holds one accumulator row, so a direct global store would touch 32
+// different rows per instruction, one 32-byte sector each; through this buffer the warp writes
+// 8 whole 128-byte lines per instruction instead.
+constexpr int kStageRowBytes = 144;
+constexpr int kStageWarpBytes = 32 * kStageRowBytes;
+constexpr int kMaxStages = 6;
+
+template <int kCtas, bool kSplit>
 struct Cfg {
-    static constexpr int kStages = kCtas == 2 ? 6 : 4;  // 4..7 slots measure the same: operand bandwidth, not latency, is the limit
+    // ring slots: 4..7 measure the same on the plain kernel (operand bandwidth, not latency, is the
+    // limit), so it gives one up for the epilogue staging; the split kernel keeps three double slots
+    static constexpr int kStages = kSplit ? (kCtas == 2 ? 6 : 4) : (kCtas == 2 ? 5 : 3);
     static constexpr int kBRows = BN / kCtas;                         // rows of B staged by one CTA
     static constexpr int kStageBytes = kRows128Bytes + kBRows * BK * 2;
     static constexpr int kTileM = BM * kCtas;
@@ -70,22 +81,23 @@ struct Cfg {
     // although it enters two of the three plane products.
     static constexpr int kSplitStages = kStages / 2;
     static constexpr int kSplitStageBytes = 2 * kStageBytes;
+    static constexpr int kEpiStageBytes = kSplit ? 0 : kEpiWarps * kStageWarpBytes;
 };
 
-template <int kCtas>
 struct alignas(8) Barriers {
-    uint64_t full[Cfg<kCtas>::kStages];
-    uint64_t empty[Cfg<kCtas>::kStages];
+    uint64_t full[kMaxStages];
+    uint64_t empty[kMaxStages];
     uint64_t tmem_full[2];
     uint64_t tmem_empty[2];
     uint32_t tmem_base;
     uint32_t abort;
     uint32_t skip;  // the error flag was already set when this CTA started: do nothing
 };
-template <int kCtas>
+template <int kCtas, bool kSplit>
 constexpr size_t smem_bytes()
 {
-    return 1024 /*alignment slack*/ + (size_t)Cfg<kCtas>::kStages * Cfg<kCtas>::kStageBytes + sizeof(Barriers<kCtas>);
+    return 1024 /*alignment slack*/ + (size_t)Cfg<kCtas, kSplit>::kStages * Cfg<kCtas, kSplit>::kStageBytes +
+           Cfg<kCtas, kSplit>::kEpiStageBytes + sizeof(Barriers);
 }
 
 // ---- PTX wrappers -------------------------------------------------------------------------
@@ -376,12 +388,12 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b)
 // reference's order of operations (src/nn/optim/muon.rs:158-160, each product and the difference
 // rounded once), then the stores the apply kernel would do: the local arena, every peer's arena,
 // the bf16 copy and the peers' bf16 copies.  `wq` holds the old weights and receives the new ones.
-__device__ __forceinline__ void apply_octet(uint32_t (&wq)[8], const float *u, float lr, float *w_dst, int64_t arena_pos,
-                                            const PeerTable &pt)
+__device__ __forceinline__ void apply_octet(uint32_t (&wq)[8], const uint32_t (&u)[8], float lr, float *w_dst,
+                                            int64_t arena_pos, const PeerTable &pt)
 {
 #pragma unroll
     for (int j = 0; j < 8; ++j)
-        wq[j] = __float_as_uint(__fsub_rn(__uint_as_float(wq[j]), __fmul_rn(__fmul_rn(lr, u[j]), 0.1f)));
+        wq[j] = __float_as_uint(__fsub_rn(__uint_as_float(wq[j]), __fmul_rn(__fmul_rn(lr, __uint_as_float(u[j])), 0.1f)));
     st_global_256(w_dst, wq);
     if (pt.n > 0) {
 #pragma unroll
@@ -413,69 +425,44 @@ __device__ __forceinline__ int term_plane_b(int n_terms, int term) { return n_te
 
 // What a role needs to know about a tile, fetched one tile ahead so that the dependent global
 // loads (tile -> problem -> fields) never sit between two tiles' main loops.
-// One 32-column piece of an accumulator row on the common path of the plain bf16 kernel
-// (interior tile, output rows 32-byte aligned): one multiply per element, the 3I of the
-// Gram epilogue added only by the one warp piece that holds the diagonal, bf16 rounding, two
-// 256-bit stores.  The epilogue warps share their scheduler with the producer and the MMA
-// thread, so the instruction count here decides how much the drain disturbs the main loop.
-template <int EPI>
-__device__ __forceinline__ void drain_chunk_fast(const uint32_t (&v)[32], float mult, bool diagonal_piece, int lane,
-                                                 __nv_bfloat16 *__restrict__ dst_bf16, float *__restrict__ dst_f32,
-                                                 __nv_bfloat16 *__restrict__ mirror_dst, float *__restrict__ t_f32, int64_t ld,
-                                                 float *__restrict__ w_dst, int64_t w_arena_pos, const TcApplyArgs &ap)
+// The common path of the plain bf16 kernel (the warp's 128 columns lie inside the matrix, output
+// rows start on 32-byte boundaries): one multiply per element, the 3I of the Gram epilogue added
+// only by the one warp piece that holds the diagonal, bf16 rounding.  The epilogue warps share
+// their schedulers with the producer and the MMA thread, so the instruction count here decides
+// how much the drain disturbs the main loop.
+//
+// A lane owns one accumulator row (TMEM lane = row), so direct stores would hit 32 rows per
+// instruction with one 32-byte sector each.  Row-major outputs therefore go through the warp's
+// staging buffer in shared memory: every lane writes its row piece, then the warp reads the
+// buffer back with four lanes per row and stores 8 whole 128-byte lines per instruction (bf16:
+// two 32-column pieces make one line; f32: one piece is one line).  The fused apply reads and
+// writes the weights in the same line-per-four-lanes pattern.  Outputs at the transposed position
+// (the mirror of a symmetric tile, the transposed update) are contiguous along the rows the 32
+// lanes hold and are stored directly, 64 or 128 bytes per instruction.
+__device__ __forceinline__ void st_shared_128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d)
 {
-    // fused apply: fetch the old weights of this row piece first (4 x 32 bytes), the arithmetic on
-    // the accumulator hides their latency
-    uint32_t wq[4][8];
-    if (w_dst) {
-#pragma unroll
-        for (int g8 = 0; g8 < 4; ++g8) ld_global_256(w_dst + g8 * 8, wq[g8]);
-    }
-    float f[32];
-#pragma unroll
-    for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]) * mult;
-    if (w_dst) {
-#pragma unroll
-        for (int g8 = 0; g8 < 4; ++g8) apply_octet(wq[g8], f + g8 * 8, ap.lr, w_dst + g8 * 8, w_arena_pos + g8 * 8, ap.pt);
-    }
-    if (EPI == TC_EPI_THREE_I_MINUS && diagonal_piece) {  // warp-uniform: row - col0 == lane
-#pragma unroll
-        for (int j = 0; j < 32; ++j) f[j] = (j == lane) ? 3.0f + f[j] : f[j];
-    }
-    if (dst_f32) {
-#pragma unroll
-        for (int g8 = 0; g8 < 4; ++g8) {
-            uint32_t q[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) q[j] = __float_as_uint(f[g8 * 8 + j]);
-            st_global_256(dst_f32 + g8 * 8, q);
-        }
-    }
-    if (t_f32) {  // transposed output: for a fixed column the warp's 32 rows are 128 contiguous bytes
-#pragma unroll
-        for (int j = 0; j < 32; ++j) t_f32[(int64_t)j * ld] = f[j];
-    }
-    if (dst_bf16) {
-#pragma unroll
-        for (int g16 = 0; g16 < 2; ++g16) {
-            uint32_t q[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) q[j] = pack_bf16(f[g16 * 16 + 2 * j], f[g16 * 16 + 2 * j + 1]);
-            st_global_256(dst_bf16 + g16 * 16, q);
-        }
-    }
-    if (mirror_dst) {  // symmetric product (element (row, col) also goes to (col, row)) or transposed output
-#pragma unroll
-        for (int j = 0; j < 32; ++j) mirror_dst[(int64_t)j * ld] = __float2bfloat16_rn(f[j]);
-    }
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ void ld_shared_128(uint32_t addr, uint32_t &a, uint32_t &b, uint32_t &c, uint32_t &d)
+{
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "r"(addr) : "memory");
 }
 
 template <int EPI>
-__device__ __forceinline__ void drain_fast(uint32_t taddr, int row, int tile_col0, bool row_ok, float mult, int lane,
+__device__ __forceinline__ void drain_fast(uint32_t taddr, int row0, int tile_col0, int M, float mult, int lane,
                                            __nv_bfloat16 *out_bf16, float *out_f32, bool mirror, bool transpose,
-                                           int64_t ld, float *apply_w, int64_t apply_pos, const TcApplyArgs &ap)
+                                           int64_t ld, float *apply_w, int64_t apply_pos, const TcApplyArgs &ap,
+                                           uint32_t stage)
 {
     constexpr int kPieces = (BN / 2) / 32;
+    const int row = row0 + lane;  // the accumulator row this lane holds
+    const bool row_ok = row < M;
+    const bool direct_bf16 = out_bf16 != nullptr && !transpose;
+    const bool direct_f32 = (out_f32 != nullptr && !transpose) || apply_w != nullptr;
+    // read-back mapping: four lanes per row (32 bytes each), eight rows per pass, four passes
+    const int r_sub = lane >> 2, seg = lane & 3;
+    const uint32_t my_row = stage + (uint32_t)(lane * kStageRowBytes);
+    const uint32_t rd_base = stage + (uint32_t)(r_sub * kStageRowBytes + seg * 32);
     uint32_t v[2][32];
     tmem_ld_32x32(taddr, v[0]);
 #pragma unroll
@@ -483,15 +470,72 @@ __device__ __forceinline__ void drain_fast(uint32_t taddr, int row, int tile_col
         const int col0 = tile_col0 + cc * 32;
         tmem_ld_wait();
         if (cc + 1 < kPieces) tmem_ld_32x32(taddr + (uint32_t)((cc + 1) * 32), v[(cc + 1) & 1]);
+        float f[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[cc & 1][j]) * mult;
+        if (EPI == TC_EPI_THREE_I_MINUS && row - col0 == lane) {  // warp-uniform: the piece that holds the diagonal
+#pragma unroll
+            for (int j = 0; j < 32; ++j) f[j] = (j == lane) ? 3.0f + f[j] : f[j];
+        }
         if (row_ok) {
-            const int64_t at = (int64_t)row * ld + col0;        // D[row][col0]
-            const int64_t at_t = (int64_t)col0 * ld + row;      // the same element of the transposed matrix
-            drain_chunk_fast<EPI>(v[cc & 1], mult, row - col0 == lane, lane,
-                                  (out_bf16 && !transpose) ? out_bf16 + at : nullptr,
-                                  (out_f32 && !transpose) ? out_f32 + at : nullptr,
-                                  (out_bf16 && (mirror || transpose)) ? out_bf16 + at_t : nullptr,
-                                  (out_f32 && transpose) ? out_f32 + at_t : nullptr, ld,
-                                  apply_w ? apply_w + at : nullptr, apply_pos + at, ap);
+            const int64_t at_t = (int64_t)col0 * ld + row;  // element (row, col0) of the transposed matrix
+            if (out_f32 != nullptr && transpose) {
+                float *t = out_f32 + at_t;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) t[(int64_t)j * ld] = f[j];
+            }
+            if (out_bf16 != nullptr && (mirror || transpose)) {
+                __nv_bfloat16 *t = out_bf16 + at_t;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) t[(int64_t)j * ld] = __float2bfloat16_rn(f[j]);
+            }
+        }
+        if (direct_bf16) {
+            const uint32_t dst = my_row + (uint32_t)((cc & 1) * 64);
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+                st_shared_128(dst + q * 16, pack_bf16(f[8 * q], f[8 * q + 1]), pack_bf16(f[8 * q + 2], f[8 * q + 3]),
+                              pack_bf16(f[8 * q + 4], f[8 * q + 5]), pack_bf16(f[8 * q + 6], f[8 * q + 7]));
+            if (cc & 1) {  // two pieces = 64 columns = one 128-byte line per row
+                __syncwarp();
+                const int colp = col0 - 32;
+#pragma unroll
+                for (int pass = 0; pass < 4; ++pass) {
+                    uint32_t q[8];
+                    const uint32_t src = rd_base + (uint32_t)(pass * 8 * kStageRowBytes);
+                    ld_shared_128(src, q[0], q[1], q[2], q[3]);
+                    ld_shared_128(src + 16, q[4], q[5], q[6], q[7]);
+                    const int r = row0 + r_sub + 8 * pass;
+                    if (r < M) st_global_256(out_bf16 + (int64_t)r * ld + colp + seg * 16, q);
+                }
+                __syncwarp();
+            }
+        }
+        if (direct_f32) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+                st_shared_128(my_row + q * 16, __float_as_uint(f[4 * q]), __float_as_uint(f[4 * q + 1]),
+                              __float_as_uint(f[4 * q + 2]), __float_as_uint(f[4 * q + 3]));
+            __syncwarp();
+            uint32_t u[4][8], wq[4][8];
+#pragma unroll
+            for (int pass = 0; pass < 4; ++pass) {  // all loads of the old weights first: their latency overlaps
+                const int r = row0 + r_sub + 8 * pass;
+                if (apply_w != nullptr && r < M) ld_global_256(apply_w + (int64_t)r * ld + col0 + seg * 8, wq[pass]);
+                const uint32_t src = rd_base + (uint32_t)(pass * 8 * kStageRowBytes);
+                ld_shared_128(src, u[pass][0], u[pass][1], u[pass][2], u[pass][3]);
+                ld_shared_128(src + 16, u[pass][4], u[pass][5], u[pass][6], u[pass][7]);
+            }
+#pragma unroll
+            for (int pass = 0; pass < 4; ++pass) {
+                const int r = row0 + r_sub + 8 * pass;
+                if (r < M) {
+                    const int64_t at = (int64_t)r * ld + col0 + seg * 8;
+                    if (apply_w != nullptr) apply_octet(wq[pass], u[pass], ap.lr, apply_w + at, apply_pos + at, ap.pt);
+                    if (out_f32 != nullptr && !transpose) st_global_256(out_f32 + at, u[pass]);
+                }
+            }
+            __syncwarp();
         }
     }
 }
@@ -604,9 +648,11 @@ __device__ __forceinline__ void drain_generic(const DrainArgs &a)
 #pragma unroll
                 for (int g8 = 0; g8 < 4; ++g8) {  // N and ld are multiples of 8: whole octets, 32-byte aligned
                     if (col0 + g8 * 8 >= N) break;
-                    uint32_t wq[8];
+                    uint32_t wq[8], uq[8];
                     ld_global_256(a.apply_w + at + g8 * 8, wq);
-                    apply_octet(wq, f + g8 * 8, a.ap->lr, a.apply_w + at + g8 * 8, a.apply_pos + at + g8 * 8, a.ap->pt);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) uq[j] = __float_as_uint(f[g8 * 8 + j]);
+                    apply_octet(wq, uq, a.ap->lr, a.apply_w + at + g8 * 8, a.apply_pos + at + g8 * 8, a.ap->pt);
                 }
             }
             if (out_f32 && transpose) {
@@ -721,10 +767,11 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
                   const uint8_t *__restrict__ present, int *__restrict__ error_flag, uint32_t wait_limit,
                   const __grid_constant__ TcApplyArgs ap)
 {
-    using C = Cfg<kCtas>;
+    using C = Cfg<kCtas, kSplit>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    Barriers<kCtas> *bars = reinterpret_cast<Barriers<kCtas> *>(smem + (size_t)C::kStages * C::kStageBytes);
+    uint8_t *epi_stage = smem + (size_t)C::kStages * C::kStageBytes;
+    Barriers *bars = reinterpret_cast<Barriers *>(epi_stage + C::kEpiStageBytes);
     volatile uint32_t *abort_flag = &bars->abort;
 
     const int warp = threadIdx.x >> 5;
@@ -912,6 +959,7 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
         // ---------------- epilogue (warps 2..9 of every CTA) ----------------
         const int quarter = warp & 3;          // the TMEM lane quarter this warp may read
         const int col_half = (warp - 2) >> 2;  // which 128 of the 256 accumulator columns
+        const uint32_t my_stage = smem_u32(epi_stage) + (uint32_t)((warp - 2) * kStageWarpBytes);  // plain kernel only
         int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
@@ -966,19 +1014,21 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
                                    (uint32_t)(acc * kAccCols + col_half * (BN / 2));
             // Common case of the plain bf16 kernel: the warp's 128 columns lie inside the matrix and
             // output rows start on 32-byte boundaries.
+            // (one staging buffer per warp: a launch writes its result row-major either as bf16 or as f32)
             const bool fast = !kSplit && tile_col0 + BN / 2 <= N && bf16_rows_32b &&
+                              (out_bf16 == nullptr || transpose || (out_f32 == nullptr && apply_w == nullptr)) &&
                               (epi == TC_EPI_HALF || epi == TC_EPI_THREE_I_MINUS || epi == TC_EPI_IDENTITY);
             if (fast) {
                 // (a * s) * 0.5 == a * (s * 0.5) and -(a * s) == a * (-s) exactly
                 if (epi == TC_EPI_HALF)
-                    drain_fast<TC_EPI_HALF>(taddr, row, tile_col0, row < M, 0.5f * acc_scale, lane, out_bf16, out_f32,
-                                            ti.mirror, transpose, ld, apply_w, apply_pos, ap);
+                    drain_fast<TC_EPI_HALF>(taddr, row - lane, tile_col0, M, 0.5f * acc_scale, lane, out_bf16, out_f32,
+                                            ti.mirror, transpose, ld, apply_w, apply_pos, ap, my_stage);
                 else if (epi == TC_EPI_THREE_I_MINUS)
-                    drain_fast<TC_EPI_THREE_I_MINUS>(taddr, row, tile_col0, row < M, -acc_scale, lane, out_bf16,
-                                                     out_f32, ti.mirror, transpose, ld, nullptr, 0, ap);
+                    drain_fast<TC_EPI_THREE_I_MINUS>(taddr, row - lane, tile_col0, M, -acc_scale, lane, out_bf16,
+                                                     out_f32, ti.mirror, transpose, ld, nullptr, 0, ap, my_stage);
                 else
-                    drain_fast<TC_EPI_IDENTITY>(taddr, row, tile_col0, row < M, acc_scale, lane, out_bf16, out_f32,
-                                                ti.mirror, transpose, ld, nullptr, 0, ap);
+                    drain_fast<TC_EPI_IDENTITY>(taddr, row - lane, tile_col0, M, acc_scale, lane, out_bf16, out_f32,
+                                                ti.mirror, transpose, ld, nullptr, 0, ap, my_stage);
             }
             if (!fast) {
                 DrainArgs da;
@@ -1069,7 +1119,7 @@ bool tc_use_pair()
 
 void tc_gemm_tile_shape(int *bm, int *bn)
 {
-    *bm = tc_use_pair() ? Cfg<2>::kTileM : Cfg<1>::kTileM;
+    *bm = tc_use_pair() ? 2 * BM : BM;
     *bn = BN;
 }
 
@@ -1122,20 +1172,20 @@ static int launch_variant(const TcGemmProblem *d_problems, const GemmTile *d_til
     static bool attr_set = false;
     if (!attr_set) {
         VB_CUDA(cudaFuncSetAttribute(ns_gemm_tc_kernel<kCtas, kSplit>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     (int)smem_bytes<kCtas>()));
+                                     (int)smem_bytes<kCtas, kSplit>()));
         attr_set = true;
     }
     if (kCtas == 1) {
         int grid = sm_count;  // one persistent CTA per SM (it owns all 512 TMEM columns)
         if (grid > n_tiles) grid = n_tiles;
-        ns_gemm_tc_kernel<kCtas, kSplit><<<grid, kThreads, smem_bytes<kCtas>(), stream>>>(
+        ns_gemm_tc_kernel<kCtas, kSplit><<<grid, kThreads, smem_bytes<kCtas, kSplit>(), stream>>>(
             d_problems, d_tiles, n_tiles, d_present, d_error_flag, wait_limit, ap);
         VB_CUDA(cudaGetLastError());
         return VB_OK;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.blockDim = dim3(kThreads);
-    cfg.dynamicSmemBytes = smem_bytes<kCtas>();
+    cfg.dynamicSmemBytes = smem_bytes<kCtas, kSplit>();
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;

@@ -303,6 +303,10 @@ class _Optimizer:
         arr = _f32(values).reshape(-1)
         call("vb_optimizer_import_state", self._h, i, which, arr.ctypes.data_as(C.c_void_p), arr.size)
 
+    def reset_state(self) -> None:
+        """Moments / velocity back to zero and ``t`` to 0, as a newly constructed optimizer has them."""
+        call("vb_optimizer_reset_state", self._h)
+
     @property
     def t(self) -> int:
         t = C.c_int64()
