@@ -57,33 +57,14 @@ __device__ __forceinline__ void st_vec8(Vec8 *p, const Vec8 &r)
                  : "memory");
 }
 
-// IEEE division and square root whose speed does not collapse on subnormal operands.
-//
-// __fdiv_rn and __fsqrt_rn are correctly rounded, but the hardware's quick sequence only covers
-// operands well inside the normal range; a subnormal numerator or radicand sends the whole warp
-// through a long fallback, and the update kernel turns from HBM-bound into ALU-bound (measured:
-// 6.7 -> 4.5 TB/s).  That state is not exotic: a parameter whose gradient is zero (an embedding row
-// that no batch touches) decays under weight decay until parameter and moments are subnormal,
-// and any parameter trained to a fixed point g + wd * theta = 0 does the same.  Scaling by a power
-// of two is exact as long as nothing leaves the normal range, and correct rounding commutes with
-// it, so the subnormal cases are moved into the quick sequence's range and scaled back.  Results
-// are the bits of __fdiv_rn / __fsqrt_rn in every case (the rare quotient that is itself
-// subnormal still takes the fallback).
-__device__ __forceinline__ float sqrt_rn_robust(float x)
-{
-    if (x >= 1.17549435e-38f || !(x > 0.0f)) return __fsqrt_rn(x);  // normal, zero, negative, NaN, inf
-    return __fmul_rn(__fsqrt_rn(__fmul_rn(x, 0x1p+64f)), 0x1p-32f);  // subnormal: the root is normal
-}
-__device__ __forceinline__ float div_rn_robust(float a, float b)
-{
-    const float aa = fabsf(a), ab = fabsf(b);
-    if (!(aa < 0x1p-100f) || aa == 0.0f || !(ab >= 0x1p-60f && ab <= 0x1p+20f)) return __fdiv_rn(a, b);
-    // tiny numerator, ordinary denominator: a * 2^80 is exact and lies in [2^-69, 2^-20)
-    const float qs = __fdiv_rn(__fmul_rn(a, 0x1p+80f), b);  // |qs| in [2^-89, 2^40]
-    if (fabsf(qs) >= 0x1p-46f) return __fmul_rn(qs, 0x1p-80f);  // the quotient is normal: exact scaling back
-    return __fdiv_rn(a, b);                                    // subnormal quotient: one rounding, the long way
-}
-
+// Division and square root are the IEEE-rounded forms.  Their quick hardware sequence covers
+// operands inside the normal range; a subnormal numerator or quotient sends the warp through a
+// long fallback and the kernel turns from HBM-bound into ALU-bound (measured: 6.7 -> 4.5 TB/s when
+// most elements are affected, e.g. after thousands of steps on one constant gradient, which trains
+// every parameter to the fixed point g + wd * theta = 0 where the effective gradient and the first
+// moment underflow).  Routing those cases around the fallback by exact power-of-two scaling was
+// tried: the extra compares cost 5-8 % on ordinary values, because the kernel already sits at the
+// edge of the issue rate, and a subnormal quotient needs the fallback anyway.  Exactness wins.
 template <int OP>
 __device__ __forceinline__ void update_one(float &p, float g, float &s1, float &s2,
                                            const StepScalars &s)
@@ -97,7 +78,7 @@ __device__ __forceinline__ void update_one(float &p, float g, float &s1, float &
         // adam.rs:196-204: theta -= lr * m_hat / (sqrt(v_hat) + eps)
         const float m_hat = __fmul_rn(s1, s.m_hat_scale);
         const float v_hat = __fmul_rn(s2, s.v_hat_scale);
-        p = __fsub_rn(p, div_rn_robust(__fmul_rn(s.lr, m_hat), __fadd_rn(sqrt_rn_robust(v_hat), s.eps)));
+        p = __fsub_rn(p, __fdiv_rn(__fmul_rn(s.lr, m_hat), __fadd_rn(__fsqrt_rn(v_hat), s.eps)));
     } else if (OP == OP_SGD_MOMENTUM) {
         // sgd.rs:216-218, 225-227
         s1 = __fmaf_rn(s.beta1, s1, -__fmul_rn(s.lr, g));
