@@ -19,6 +19,7 @@ one core.
 from __future__ import annotations
 
 import argparse
+import datetime
 import json
 import math
 import os
@@ -225,6 +226,7 @@ def timed_blocks(run_block, barrier, max_over_ranks, min_seconds=MIN_TIMED_SECON
     waiting for it) again and again, each block between a barrier + synchronize on both sides, until
     the blocks together cover `min_seconds`.  Every rank runs the same number of blocks (decided from
     the first block's max-over-ranks time).  Returns the per-block times, max over ranks."""
+    min_seconds = min(min_seconds, timed_blocks.cap_seconds)
     barrier()
     mine = [run_block()]
     first = max_over_ranks(mine[0])
@@ -238,6 +240,9 @@ def timed_blocks(run_block, barrier, max_over_ranks, min_seconds=MIN_TIMED_SECON
         out.append(max_over_ranks(ms))
     timed_blocks.last_local = mine   # this rank's own times of the same blocks
     return out
+
+
+timed_blocks.cap_seconds = MIN_TIMED_SECONDS   # lowered by --min-seconds
 
 
 def block_stats(blocks_ms, steps):
@@ -377,7 +382,8 @@ def run_ours(args):
     cpu_set = sorted(os.sched_getaffinity(0))
     eng = Engine(local_rank)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        # a rank that fails must not leave the others waiting in a collective for the default ten minutes
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
         idt = torch.zeros(128, dtype=torch.uint8, device=dev)
         if rank == 0:
             idt.copy_(torch.frombuffer(bytearray(Engine.unique_id()), dtype=torch.uint8))
@@ -874,6 +880,9 @@ def main():
     ap.add_argument("--only-muon", action="store_true", help="profiling runs: Muon bf16 only")
     ap.add_argument("--skip-c5", action="store_true", help="skip the ragged 4096-tensor Adam section")
     ap.add_argument("--skip-parity", action="store_true", help="profiling runs: skip the parity block")
+    ap.add_argument("--min-seconds", type=float, default=MIN_TIMED_SECONDS,
+                    help="each headline number is the median of K-step blocks that together run at least this long "
+                         "(profiling runs: 0 = three blocks)")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="N > 1: updated parameters reach the other ranks by NVLink peer stores fused into the "
                          "update kernel (default) or by an NCCL all-gather after it")
@@ -883,6 +892,7 @@ def main():
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
+    timed_blocks.cap_seconds = args.min_seconds
     if args.impl == "reference":
         return run_reference(args)
     return run_ours(args)

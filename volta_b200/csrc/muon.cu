@@ -727,6 +727,10 @@ struct MuonState {
     GemmTile *d_tc_gram_tiles = nullptr, *d_tc_upd_tiles = nullptr;
     GemmTile *d_tc_upd_tiles_last = nullptr;  // the last iteration's update is always in the direct form
     int n_tc_gram_tiles = 0, n_tc_upd_tiles = 0, n_tc_upd_tiles_last = 0;
+    // update products whose output width is a multiple of 512 run on 256 x 512 tiles (a quarter
+    // less operand traffic from L2); the lists above then hold only the other matrices
+    GemmTile *d_tc_upd_tiles_wide = nullptr, *d_tc_upd_tiles_last_wide = nullptr;
+    int n_tc_upd_tiles_wide = 0, n_tc_upd_tiles_last_wide = 0;
     int *d_error = nullptr;
     int *h_error = nullptr;              // pinned mirror of d_error, refreshed after every step
     // The last update launch applies its result to the weights itself (tensor-core matrices); the
@@ -779,6 +783,8 @@ void destroy_muon_state(MuonState *s)
     cudaFree(s->d_tc_gram_tiles);
     cudaFree(s->d_tc_upd_tiles);
     cudaFree(s->d_tc_upd_tiles_last);
+    cudaFree(s->d_tc_upd_tiles_wide);
+    cudaFree(s->d_tc_upd_tiles_last_wide);
     cudaFree(s->d_error);
     if (s->h_error) cudaFreeHost(s->h_error);
     delete s;
@@ -1037,7 +1043,8 @@ int muon_init(vb_optimizer *opt)
         tc_gemm_tile_shape(&bm, &bn);
         const int iters = opt->ns_steps;
         std::vector<std::vector<TcGemmProblem>> gram((size_t)iters), upd((size_t)iters);
-        std::vector<GemmTile> gram_tiles, upd_tiles, upd_tiles_last;
+        std::vector<GemmTile> gram_tiles, upd_tiles, upd_tiles_last, upd_tiles_wide, upd_tiles_last_wide;
+        const int wide_cols = s->planes == 1 ? tc_gemm_wide_cols() : 0;
         std::stable_sort(tc_tensors.begin(), tc_tensors.end(), by_size);
         // plain bf16 path: the momentum kernel writes the unnormalised bf16 operand and the first
         // iteration's epilogues apply 1/norm; the split path keeps the reference's true division
@@ -1133,10 +1140,19 @@ int muon_init(vb_optimizer *opt)
                     gram_tiles.push_back(GemmTile{pidx, m0, n0, flags});
                 }
             const bool upd_t = tall && planes == 1 && use_transposed_update();  // as above: the update computes (X C)^T
-            for (int m0 = 0; m0 < (upd_t ? sh : r); m0 += bm)
-                for (int n0 = 0; n0 < (upd_t ? r : c); n0 += bn) upd_tiles.push_back(GemmTile{pidx, m0, n0, 0});
-            for (int m0 = 0; m0 < r; m0 += bm)
-                for (int n0 = 0; n0 < c; n0 += bn) upd_tiles_last.push_back(GemmTile{pidx, m0, n0, 0});
+            {
+                const int um = upd_t ? sh : r, un = upd_t ? r : c;
+                const bool wide = wide_cols > 0 && un % wide_cols == 0;
+                for (int m0 = 0; m0 < um; m0 += bm)
+                    for (int n0 = 0; n0 < un; n0 += wide ? wide_cols : bn)
+                        (wide ? upd_tiles_wide : upd_tiles).push_back(GemmTile{pidx, m0, n0, 0});
+            }
+            {
+                const bool wide = wide_cols > 0 && c % wide_cols == 0;
+                for (int m0 = 0; m0 < r; m0 += bm)
+                    for (int n0 = 0; n0 < c; n0 += wide ? wide_cols : bn)
+                        (wide ? upd_tiles_last_wide : upd_tiles_last).push_back(GemmTile{pidx, m0, n0, 0});
+            }
             // executed tensor-core FLOPs: three plane products per product on the split path; the
             // Gram counts only the tiles that are computed
             const double prod = 2.0 * (double)std::max(r, c) * (double)sh * (double)sh;
@@ -1152,6 +1168,10 @@ int muon_init(vb_optimizer *opt)
         VB_TRY(upload(&s->d_tc_gram_tiles, gram_tiles, e->stream));
         VB_TRY(upload(&s->d_tc_upd_tiles, upd_tiles, e->stream));
         VB_TRY(upload(&s->d_tc_upd_tiles_last, upd_tiles_last, e->stream));
+        VB_TRY(upload(&s->d_tc_upd_tiles_wide, upd_tiles_wide, e->stream));
+        VB_TRY(upload(&s->d_tc_upd_tiles_last_wide, upd_tiles_last_wide, e->stream));
+        s->n_tc_upd_tiles_wide = (int)upd_tiles_wide.size();
+        s->n_tc_upd_tiles_last_wide = (int)upd_tiles_last_wide.size();
         s->n_tc_upd_tiles_last = (int)upd_tiles_last.size();
         s->n_tc_gram_tiles = (int)gram_tiles.size();
         s->n_tc_upd_tiles = (int)upd_tiles.size();
@@ -1270,7 +1290,12 @@ int muon_step(vb_optimizer *opt, uint32_t flags)
                                          last_it ? s->n_tc_upd_tiles_last : s->n_tc_upd_tiles,
                                          opt->d_present, s->d_error, e->sm_count, e->stream, gemm_wait_limit, split,
                                          ap.enabled ? &ap : nullptr));
-                e->launches += 2;
+                const int n_wide = last_it ? s->n_tc_upd_tiles_last_wide : s->n_tc_upd_tiles_wide;
+                VB_TRY(launch_ns_gemm_tc(s->d_tc_upd[(size_t)it],
+                                         last_it ? s->d_tc_upd_tiles_last_wide : s->d_tc_upd_tiles_wide, n_wide,
+                                         opt->d_present, s->d_error, e->sm_count, e->stream, gemm_wait_limit, split,
+                                         ap.enabled ? &ap : nullptr, /*wide=*/true));
+                e->launches += 1 + ((last_it ? s->n_tc_upd_tiles_last : s->n_tc_upd_tiles) > 0) + (n_wide > 0);
             }
             if (s->n_gram_tiles > 0) {
                 VB_TRY(launch_ns_gemm_f32(s->d_gram_prob[par], s->d_gram_tiles, s->n_gram_tiles, opt->d_present,

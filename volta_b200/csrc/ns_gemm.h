@@ -138,8 +138,9 @@ struct TcApplyArgs {
 // wait_limit: mbarrier polls before a role gives up (0 = the default, about a second).
 int launch_ns_gemm_tc(const TcGemmProblem *d_problems, const GemmTile *d_tiles, int n_tiles,
                       const uint8_t *d_present, int *d_error_flag, int sm_count, cudaStream_t stream,
-                      uint32_t wait_limit = 0, bool split = false, const TcApplyArgs *apply = nullptr);
+                      uint32_t wait_limit = 0, bool split = false, const TcApplyArgs *apply = nullptr, bool wide = false);
 void tc_gemm_tile_shape(int *bm, int *bn);
+int tc_gemm_wide_cols();  // columns of the wide tile (512) of the update products, 0 if not in use
 int make_bf16_tensor_map(void *map_out, const void *base, int64_t inner, int64_t outer, int mode, int planes = 1,
                          int64_t plane_stride = 0);
 int tc_mn_major_mode(int64_t inner);

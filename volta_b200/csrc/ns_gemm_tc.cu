@@ -59,21 +59,31 @@ constexpr int kEpiWarps = 8;                             // two per TMEM lane qu
 constexpr int kThreads = 64 + kEpiWarps * 32;            // producer warp + MMA warp + epilogue warps
 constexpr uint32_t kDefaultWaitLimit = 1u << 22;         // mbarrier polls before giving up
 
-// Staging of the plain kernel's epilogue: each epilogue warp owns 32 rows of 128 payload bytes
-// (+ 16 of padding, which makes both the row-per-lane writes and the 4-lanes-per-row reads free
-// of bank conflicts).  A lane holds one accumulator row, so a direct global store would touch 32
-// different rows per instruction, one 32-byte sector each; through this buffer the warp writes
-// 8 whole 128-byte lines per instruction instead.
-constexpr int kStageRowBytes = 144;
+// Staging of the plain kernel's epilogue: each epilogue warp owns 32 rows of 128 bytes.  A lane
+// holds one accumulator row, so a direct global store would touch 32 different rows per
+// instruction, one 32-byte sector each; through this buffer the warp writes 8 whole 128-byte
+// lines per instruction instead.  The 16-byte pieces of row r sit at position (piece ^ (r & 7)),
+// which makes both the row-per-lane writes and the four-lanes-per-row reads free of bank
+// conflicts without padding.
+constexpr int kStageRowBytes = 128;
 constexpr int kStageWarpBytes = 32 * kStageRowBytes;
 constexpr int kMaxStages = 6;
 
-template <int kCtas, bool kSplit>
+// kWide (CTA pairs, plain bf16 operands only): the tile is 256 x 512.  The two 256-column halves of
+// the accumulator fill all 512 TMEM columns and share the staged rows of A, so a tile fetches
+// 256 + 512 operand rows per k block instead of 2 x (256 + 256) for the same work: a quarter less
+// traffic from L2, which is what bounds the k = 1024 update products.  There is no second
+// accumulator to drain into while the next tile runs; instead each half has its own full / empty
+// barriers, the ring keeps filling during the drain, and the MMA thread starts a half as soon as
+// that half has been drained.
+template <int kCtas, bool kSplit, bool kWide = false>
 struct Cfg {
-    // ring slots: 4..7 measure the same on the plain kernel (operand bandwidth, not latency, is the
-    // limit), so it gives one up for the epilogue staging; the split kernel keeps three double slots
-    static constexpr int kStages = kSplit ? (kCtas == 2 ? 6 : 4) : (kCtas == 2 ? 5 : 3);
-    static constexpr int kBRows = BN / kCtas;                         // rows of B staged by one CTA
+    static_assert(!kWide || (kCtas == 2 && !kSplit), "the wide tile exists for the plain pair kernel");
+    // ring slots: 4..7 measure the same on the plain pair kernel (operand bandwidth, not latency, is
+    // the limit); the one-CTA kernel gives one up for the epilogue staging
+    static constexpr int kStages = kWide ? 4 : (kCtas == 2 ? 6 : (kSplit ? 4 : 3));
+    static constexpr int kHalves = kWide ? 2 : 1;                     // 256-column accumulator halves per tile
+    static constexpr int kBRows = BN * kHalves / kCtas;               // rows of B staged by one CTA
     static constexpr int kStageBytes = kRows128Bytes + kBRows * BK * 2;
     static constexpr int kTileM = BM * kCtas;
     // Split kernel: one ring slot holds both planes of A and of B for one k block (two images of
@@ -93,12 +103,15 @@ struct alignas(8) Barriers {
     uint32_t abort;
     uint32_t skip;  // the error flag was already set when this CTA started: do nothing
 };
-template <int kCtas, bool kSplit>
+template <int kCtas, bool kSplit, bool kWide>
 constexpr size_t smem_bytes()
 {
-    return 1024 /*alignment slack*/ + (size_t)Cfg<kCtas, kSplit>::kStages * Cfg<kCtas, kSplit>::kStageBytes +
-           Cfg<kCtas, kSplit>::kEpiStageBytes + sizeof(Barriers);
+    using C = Cfg<kCtas, kSplit, kWide>;
+    return 1024 /*alignment slack*/ + (size_t)C::kStages * C::kStageBytes + C::kEpiStageBytes + sizeof(Barriers);
 }
+static_assert(smem_bytes<2, false, true>() <= 232448 && smem_bytes<2, false, false>() <= 232448 &&
+                  smem_bytes<2, true, false>() <= 232448,
+              "a CTA has 227 KiB of shared memory");
 
 // ---- PTX wrappers -------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -462,7 +475,9 @@ __device__ __forceinline__ void drain_fast(uint32_t taddr, int row0, int tile_co
     // read-back mapping: four lanes per row (32 bytes each), eight rows per pass, four passes
     const int r_sub = lane >> 2, seg = lane & 3;
     const uint32_t my_row = stage + (uint32_t)(lane * kStageRowBytes);
-    const uint32_t rd_base = stage + (uint32_t)(r_sub * kStageRowBytes + seg * 32);
+    const uint32_t my_sw = (uint32_t)(lane & 7);
+    const uint32_t rd_row = stage + (uint32_t)(r_sub * kStageRowBytes);  // row r_sub + 8 * pass: (row & 7) == r_sub
+    const uint32_t rd_c0 = (uint32_t)(((2 * seg) ^ r_sub) << 4), rd_c1 = (uint32_t)(((2 * seg + 1) ^ r_sub) << 4);
     uint32_t v[2][32];
     tmem_ld_32x32(taddr, v[0]);
 #pragma unroll
@@ -491,20 +506,20 @@ __device__ __forceinline__ void drain_fast(uint32_t taddr, int row0, int tile_co
             }
         }
         if (direct_bf16) {
-            const uint32_t dst = my_row + (uint32_t)((cc & 1) * 64);
 #pragma unroll
             for (int q = 0; q < 4; ++q)
-                st_shared_128(dst + q * 16, pack_bf16(f[8 * q], f[8 * q + 1]), pack_bf16(f[8 * q + 2], f[8 * q + 3]),
-                              pack_bf16(f[8 * q + 4], f[8 * q + 5]), pack_bf16(f[8 * q + 6], f[8 * q + 7]));
+                st_shared_128(my_row + ((((uint32_t)((cc & 1) * 4 + q)) ^ my_sw) << 4), pack_bf16(f[8 * q], f[8 * q + 1]),
+                              pack_bf16(f[8 * q + 2], f[8 * q + 3]), pack_bf16(f[8 * q + 4], f[8 * q + 5]),
+                              pack_bf16(f[8 * q + 6], f[8 * q + 7]));
             if (cc & 1) {  // two pieces = 64 columns = one 128-byte line per row
                 __syncwarp();
                 const int colp = col0 - 32;
 #pragma unroll
                 for (int pass = 0; pass < 4; ++pass) {
                     uint32_t q[8];
-                    const uint32_t src = rd_base + (uint32_t)(pass * 8 * kStageRowBytes);
-                    ld_shared_128(src, q[0], q[1], q[2], q[3]);
-                    ld_shared_128(src + 16, q[4], q[5], q[6], q[7]);
+                    const uint32_t src = rd_row + (uint32_t)(pass * 8 * kStageRowBytes);
+                    ld_shared_128(src + rd_c0, q[0], q[1], q[2], q[3]);
+                    ld_shared_128(src + rd_c1, q[4], q[5], q[6], q[7]);
                     const int r = row0 + r_sub + 8 * pass;
                     if (r < M) st_global_256(out_bf16 + (int64_t)r * ld + colp + seg * 16, q);
                 }
@@ -514,7 +529,7 @@ __device__ __forceinline__ void drain_fast(uint32_t taddr, int row0, int tile_co
         if (direct_f32) {
 #pragma unroll
             for (int q = 0; q < 8; ++q)
-                st_shared_128(my_row + q * 16, __float_as_uint(f[4 * q]), __float_as_uint(f[4 * q + 1]),
+                st_shared_128(my_row + ((((uint32_t)q) ^ my_sw) << 4), __float_as_uint(f[4 * q]), __float_as_uint(f[4 * q + 1]),
                               __float_as_uint(f[4 * q + 2]), __float_as_uint(f[4 * q + 3]));
             __syncwarp();
             uint32_t u[4][8], wq[4][8];
@@ -522,9 +537,9 @@ __device__ __forceinline__ void drain_fast(uint32_t taddr, int row0, int tile_co
             for (int pass = 0; pass < 4; ++pass) {  // all loads of the old weights first: their latency overlaps
                 const int r = row0 + r_sub + 8 * pass;
                 if (apply_w != nullptr && r < M) ld_global_256(apply_w + (int64_t)r * ld + col0 + seg * 8, wq[pass]);
-                const uint32_t src = rd_base + (uint32_t)(pass * 8 * kStageRowBytes);
-                ld_shared_128(src, u[pass][0], u[pass][1], u[pass][2], u[pass][3]);
-                ld_shared_128(src + 16, u[pass][4], u[pass][5], u[pass][6], u[pass][7]);
+                const uint32_t src = rd_row + (uint32_t)(pass * 8 * kStageRowBytes);
+                ld_shared_128(src + rd_c0, u[pass][0], u[pass][1], u[pass][2], u[pass][3]);
+                ld_shared_128(src + rd_c1, u[pass][4], u[pass][5], u[pass][6], u[pass][7]);
             }
 #pragma unroll
             for (int pass = 0; pass < 4; ++pass) {
@@ -761,13 +776,13 @@ __device__ __forceinline__ TileInfo fetch_tile(const TcGemmProblem *problems, co
 
 // kSplit: the operands are two f16 planes (f32-accurate path); the plain bf16 instantiation
 // carries none of that code.
-template <int kCtas, bool kSplit>
+template <int kCtas, bool kSplit, bool kWide>
 __global__ void __launch_bounds__(kThreads, 1)
 ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__restrict__ tiles, int n_tiles,
                   const uint8_t *__restrict__ present, int *__restrict__ error_flag, uint32_t wait_limit,
                   const __grid_constant__ TcApplyArgs ap)
 {
-    using C = Cfg<kCtas, kSplit>;
+    using C = Cfg<kCtas, kSplit, kWide>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t *epi_stage = smem + (size_t)C::kStages * C::kStageBytes;
@@ -868,9 +883,11 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
 #pragma unroll
                         for (int pl = 0; pl < (kSplit ? kSplitPlanes : 1); ++pl)
 #pragma unroll
-                            for (int j = 0; j < C::kBRows / 128; ++j)
+                            for (int j = 0; j < C::kBRows / 128; ++j)  // wide tile: this CTA's 128 rows of each half
                                 load_rows128<kCtas, kSplit>(sb + pl * C::kStageBytes + j * kRows128Bytes, &ti.p->map_b,
-                                                            ti.b_mode, b_row0 + j * 128, k0, pl, full_bar);
+                                                            ti.b_mode,
+                                                            kWide ? ti.n0 + j * BN + (int)cta_rank * 128 : b_row0 + j * 128,
+                                                            k0, pl, full_bar);
                     }
                     if (++stage == kRing) {
                         stage = 0;
@@ -898,12 +915,15 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
                 next = fetch_tile(problems, tiles, n_tiles, present, t + n_groups);
                 if (ti.skipped) continue;
                 const uint32_t idesc = make_idesc(ti.a_mode, ti.b_mode, C::kTileM, kSplit);
-                // the epilogue(s) must have drained this accumulator
-                if (!MBAR_WAIT(1, &bars->tmem_empty[acc], acc_phase ^ 1u)) {
-                    ok = false;
-                    break;
+                // the epilogue(s) must have drained this accumulator (wide tile: each half is waited
+                // for right before its first MMA, see below)
+                if (!kWide) {
+                    if (!MBAR_WAIT(1, &bars->tmem_empty[acc], acc_phase ^ 1u)) {
+                        ok = false;
+                        break;
+                    }
+                    tcgen05_fence_after();
                 }
-                tcgen05_fence_after();
                 const uint32_t tmem_d = tmem_base + (uint32_t)(acc * kAccCols);
                 constexpr int kRing = kSplit ? C::kSplitStages : C::kStages;
                 constexpr int kSlotBytes = kSplit ? C::kSplitStageBytes : C::kStageBytes;
@@ -928,6 +948,24 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
                                                         operand_desc(sb, ti.b_mode, kk), idesc,
                                                         (slot > 0 || term > 0 || kk > 0) ? 1u : 0u);
                         }
+                    } else if (kWide) {
+                        // both halves of the 512 accumulator columns read the same staged rows of A
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            if (slot == 0) {  // this half must have been drained by the previous tile's epilogue
+                                if (!MBAR_WAIT(1, &bars->tmem_empty[h], acc_phase ^ 1u)) {
+                                    ok = false;
+                                    break;
+                                }
+                                tcgen05_fence_after();
+                            }
+                            const uint32_t sb = base + kRows128Bytes + (uint32_t)(h * kRows128Bytes);
+#pragma unroll
+                            for (int kk = 0; kk < BK / UMMA_K; ++kk)
+                                tcgen05_mma_bf16<kCtas>(tmem_base + (uint32_t)(h * kAccCols), operand_desc(base, ti.a_mode, kk),
+                                                        operand_desc(sb, ti.b_mode, kk), idesc, (slot > 0 || kk > 0) ? 1u : 0u);
+                        }
+                        if (!ok) break;
                     } else {
                         const uint32_t sa = base;
                         const uint32_t sb = (kCtas == 2 && ti.b_is_a) ? sa : sa + kRows128Bytes;
@@ -943,10 +981,16 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
                     }
                 }
                 if (!ok) break;
-                tcgen05_commit<kCtas>(&bars->tmem_full[acc]);  // accumulator complete (in every CTA)
-                if (++acc == 2) {
-                    acc = 0;
+                if (kWide) {  // both halves complete (in every CTA); every tile uses both barriers
+                    tcgen05_commit<kCtas>(&bars->tmem_full[0]);
+                    tcgen05_commit<kCtas>(&bars->tmem_full[1]);
                     acc_phase ^= 1u;
+                } else {
+                    tcgen05_commit<kCtas>(&bars->tmem_full[acc]);  // accumulator complete (in every CTA)
+                    if (++acc == 2) {
+                        acc = 0;
+                        acc_phase ^= 1u;
+                    }
                 }
             }
             if (!ok) {
@@ -998,9 +1042,14 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
             const int64_t plane_stride = p->out_plane_stride;
             const bool bf16_rows_32b = (ld % 16) == 0;  // every bf16 output row starts on a 32-byte boundary
             const bool transpose = !kSplit && p->transpose_out != 0;
+            // One accumulator of 256 columns per tile, alternating between the two TMEM buffers; or
+            // (wide tile) both buffers in every tile, as the two halves of its 512 columns.
+#pragma unroll 1
+            for (int h = 0; h < C::kHalves && ok; ++h) {
+            const int buf = kWide ? h : acc;
             // warp-uniform: near expiry some lanes could see the barrier flip and others give up;
             // the whole warp must take the same branch before the aligned tcgen05.ld below
-            if (!__all_sync(0xffffffffu, MBAR_WAIT(3, &bars->tmem_full[acc], acc_phase))) {
+            if (!__all_sync(0xffffffffu, MBAR_WAIT(3, &bars->tmem_full[buf], acc_phase))) {
                 ok = false;
                 break;
             }
@@ -1009,9 +1058,9 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
 #endif
             tcgen05_fence_after();
             const int row = ti.m0 + (int)cta_rank * BM + quarter * 32 + lane;
-            const int tile_col0 = ti.n0 + col_half * (BN / 2);
+            const int tile_col0 = ti.n0 + h * BN + col_half * (BN / 2);
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) +
-                                   (uint32_t)(acc * kAccCols + col_half * (BN / 2));
+                                   (uint32_t)(buf * kAccCols + col_half * (BN / 2));
             // Common case of the plain bf16 kernel: the warp's 128 columns lie inside the matrix and
             // output rows start on 32-byte boundaries.
             // (one staging buffer per warp: a launch writes its result row-major either as bf16 or as f32)
@@ -1048,10 +1097,13 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
             }
 #endif
             if (lane == 0) {
-                if (kCtas == 2) mbar_remote_arrive(map_to_cta(smem_u32(&bars->tmem_empty[acc]), 0));
-                else mbar_arrive(&bars->tmem_empty[acc]);
+                if (kCtas == 2) mbar_remote_arrive(map_to_cta(smem_u32(&bars->tmem_empty[buf]), 0));
+                else mbar_arrive(&bars->tmem_empty[buf]);
             }
-            if (++acc == 2) {
+            }  // halves
+            if (kWide) {
+                acc_phase ^= 1u;
+            } else if (++acc == 2) {
                 acc = 0;
                 acc_phase ^= 1u;
             }
@@ -1164,28 +1216,28 @@ int make_bf16_tensor_map(void *map_out, const void *base, int64_t inner, int64_t
     return VB_OK;
 }
 
-template <int kCtas, bool kSplit>
+template <int kCtas, bool kSplit, bool kWide>
 static int launch_variant(const TcGemmProblem *d_problems, const GemmTile *d_tiles, int n_tiles,
                           const uint8_t *d_present, int *d_error_flag, int sm_count, cudaStream_t stream,
                           uint32_t wait_limit, const TcApplyArgs &ap)
 {
     static bool attr_set = false;
     if (!attr_set) {
-        VB_CUDA(cudaFuncSetAttribute(ns_gemm_tc_kernel<kCtas, kSplit>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     (int)smem_bytes<kCtas, kSplit>()));
+        VB_CUDA(cudaFuncSetAttribute(ns_gemm_tc_kernel<kCtas, kSplit, kWide>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)smem_bytes<kCtas, kSplit, kWide>()));
         attr_set = true;
     }
     if (kCtas == 1) {
         int grid = sm_count;  // one persistent CTA per SM (it owns all 512 TMEM columns)
         if (grid > n_tiles) grid = n_tiles;
-        ns_gemm_tc_kernel<kCtas, kSplit><<<grid, kThreads, smem_bytes<kCtas, kSplit>(), stream>>>(
+        ns_gemm_tc_kernel<kCtas, kSplit, kWide><<<grid, kThreads, smem_bytes<kCtas, kSplit, kWide>(), stream>>>(
             d_problems, d_tiles, n_tiles, d_present, d_error_flag, wait_limit, ap);
         VB_CUDA(cudaGetLastError());
         return VB_OK;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.blockDim = dim3(kThreads);
-    cfg.dynamicSmemBytes = smem_bytes<kCtas, kSplit>();
+    cfg.dynamicSmemBytes = smem_bytes<kCtas, kSplit, kWide>();
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -1199,14 +1251,14 @@ static int launch_variant(const TcGemmProblem *d_problems, const GemmTile *d_til
     if (max_clusters == 0) {
         cfg.gridDim = dim3((unsigned)(sm_count / 2 * 2));
         int n = 0;
-        VB_CUDA(cudaOccupancyMaxActiveClusters(&n, ns_gemm_tc_kernel<kCtas, kSplit>, &cfg));
+        VB_CUDA(cudaOccupancyMaxActiveClusters(&n, ns_gemm_tc_kernel<kCtas, kSplit, kWide>, &cfg));
         if (n < 1) return fail(VB_ERR_CUDA, "the device cannot hold a 2-CTA cluster of the GEMM kernel");
         max_clusters = n;
     }
     int clusters = max_clusters;
     if (clusters > n_tiles) clusters = n_tiles;
     cfg.gridDim = dim3((unsigned)(clusters * 2));
-    VB_CUDA(cudaLaunchKernelEx(&cfg, ns_gemm_tc_kernel<kCtas, kSplit>, d_problems, d_tiles, n_tiles, d_present,
+    VB_CUDA(cudaLaunchKernelEx(&cfg, ns_gemm_tc_kernel<kCtas, kSplit, kWide>, d_problems, d_tiles, n_tiles, d_present,
                                d_error_flag, wait_limit, ap));
     return VB_OK;
 }
@@ -1214,20 +1266,40 @@ static int launch_variant(const TcGemmProblem *d_problems, const GemmTile *d_til
 // split: the problems' operands are two f16 planes (all problems of a launch are alike).
 int launch_ns_gemm_tc(const TcGemmProblem *d_problems, const GemmTile *d_tiles, int n_tiles,
                       const uint8_t *d_present, int *d_error_flag, int sm_count, cudaStream_t stream,
-                      uint32_t wait_limit, bool split, const TcApplyArgs *apply)
+                      uint32_t wait_limit, bool split, const TcApplyArgs *apply, bool wide)
 {
     if (n_tiles <= 0) return VB_OK;
     if (wait_limit == 0) wait_limit = kDefaultWaitLimit;
     const TcApplyArgs ap = apply ? *apply : TcApplyArgs{};
+    if (wide) {
+        if (split || !tc_use_pair()) return fail(VB_ERR_INVALID_ARG, "the wide tile exists for the plain pair kernel");
+        return launch_variant<2, false, true>(d_problems, d_tiles, n_tiles, d_present, d_error_flag, sm_count, stream,
+                                              wait_limit, ap);
+    }
     if (tc_use_pair())
-        return split ? launch_variant<2, true>(d_problems, d_tiles, n_tiles, d_present, d_error_flag, sm_count, stream,
-                                               wait_limit, ap)
-                     : launch_variant<2, false>(d_problems, d_tiles, n_tiles, d_present, d_error_flag, sm_count, stream,
-                                                wait_limit, ap);
-    return split ? launch_variant<1, true>(d_problems, d_tiles, n_tiles, d_present, d_error_flag, sm_count, stream,
-                                           wait_limit, ap)
-                 : launch_variant<1, false>(d_problems, d_tiles, n_tiles, d_present, d_error_flag, sm_count, stream,
-                                            wait_limit, ap);
+        return split ? launch_variant<2, true, false>(d_problems, d_tiles, n_tiles, d_present, d_error_flag, sm_count,
+                                                      stream, wait_limit, ap)
+                     : launch_variant<2, false, false>(d_problems, d_tiles, n_tiles, d_present, d_error_flag, sm_count,
+                                                       stream, wait_limit, ap);
+    return split ? launch_variant<1, true, false>(d_problems, d_tiles, n_tiles, d_present, d_error_flag, sm_count, stream,
+                                                  wait_limit, ap)
+                 : launch_variant<1, false, false>(d_problems, d_tiles, n_tiles, d_present, d_error_flag, sm_count, stream,
+                                                   wait_limit, ap);
+}
+
+// Columns of a wide tile, or 0 where the wide kernel is not in use.  It is off unless
+// VB_TC_WIDE=1: measured on the 96-matrix configuration it fetches a quarter less from L2 but
+// cannot hide its drain (all 512 TMEM columns belong to one tile), and the update products end up
+// 10 % slower than with 256 x 256 tiles and two accumulators (Newton-Schulz chain 5.14 ms against
+// 4.87 ms per step).  Kept selectable, and covered by the parity tests when selected.
+int tc_gemm_wide_cols()
+{
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("VB_TC_WIDE");
+        v = (tc_use_pair() && e && *e == '1') ? 2 * BN : 0;
+    }
+    return v;
 }
 
 }  // namespace vb
