@@ -436,3 +436,54 @@ def test_apply_fused_into_the_last_launch_gives_the_same_weights(oracle, engine,
     for a, b, p0 in zip(results[0], results[1], start):
         assert bits_equal(a, b)
         assert not bits_equal(a, p0)
+
+
+WIDE_TILE_CHECK = r"""
+import sys
+import numpy as np
+sys.path.insert(0, {root!r})
+import oracle
+import volta_b200
+from volta_b200 import VB_NS_BF16, Engine, Muon, Tensor
+oracle.build()
+eng = Engine(0)
+rng = np.random.default_rng(31)
+shapes = [(1024, 512), (512, 1024), (1024, 1024), (1536, 512), (384, 256), (264, 72)]
+start = [(rng.standard_normal(s) * 0.02).astype(np.float32) for s in shapes]
+tensors = [Tensor(p.copy()) for p in start]
+opt = Muon(tensors, 0.1, 0.9, True, 5, ns_mode=VB_NS_BF16, engine=eng, keep_update=True)
+ref_p = [p.copy() for p in start]
+ref = oracle.Muon(ref_p, 0.1, 0.9, True, 5)
+worst = 0.0
+for step in range(2):
+    gs = [(rng.standard_normal(s) * 1e-3).astype(np.float32) for s in shapes]
+    for t, g in zip(tensors, gs):
+        t.grad = g
+    opt.step()
+    ref.step(gs)
+    for i in range(len(shapes)):
+        a, b = opt.last_update(i).astype(np.float64), ref.last_update[i].astype(np.float64)
+        worst = max(worst, float(np.linalg.norm(a - b) / np.linalg.norm(b)))
+moved = max(float(np.linalg.norm(t.data.astype(np.float64) - r) / np.linalg.norm(r.astype(np.float64) - p0))
+            for t, r, p0 in zip(tensors, ref_p, start))
+opt.close()
+eng.close()
+print("WORST", worst, moved)
+assert worst <= 2e-2 and moved <= 2e-2
+"""
+
+
+def test_wide_update_tile_when_selected():
+    """VB_TC_WIDE=1 runs the update products whose width is a multiple of 512 on 256 x 512 tiles (both
+    accumulator halves share the staged rows of A).  The variant is off by default because it
+    measured slower; selected, it must meet the same bound.  The switch is read once per process,
+    hence the child process."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, VB_TC_WIDE="1")
+    r = subprocess.run([sys.executable, "-c", WIDE_TILE_CHECK.format(root=root)], env=env, capture_output=True,
+                       text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert "WORST" in r.stdout
