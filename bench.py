@@ -806,6 +806,9 @@ def run_muon(args, eng, world, rank, dev, barrier, max_over_ranks, peaks):
             "pre_ms": pre_ms, "apply_ms": apply_ms, "exchange_ms": exch_ms,
             "params_per_s": wl.total / (step_ms * 1e-3), "steps": steps, "blocks": block_stats(blocks, steps),
             "executed_flops_per_step": flops_total,
+            "apply_note": "apply_ms is the last update launch, which applies its result to the weights in its epilogue "
+                          "(8 B/param of HBM traffic on top of the product); it is part of ns_ms_per_step as well"
+                          if mode_name != "f32" else "separate apply pass",
             "note": {"bf16": "tcgen05 bf16, short-side Gram, symmetric Gram computed on and above the diagonal only", "f32": "CUDA-core FFMA, bit-identical to the CPU arithmetic",
                      "f32_tc": "tcgen05, operands held as two f16 planes (three products per product); "
                                "ns_tflops counts executed f16 tensor FLOPs"}[mode_name],

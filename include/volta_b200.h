@@ -171,7 +171,8 @@ int vb_engine_launch_count(vb_engine *engine, uint64_t *count);
 #define VB_PHASE_UPDATE 0    /* fused Adam / SGD launch */
 #define VB_PHASE_MUON_PRE 1  /* Muon momentum, sum of squares, normalise */
 #define VB_PHASE_MUON_NS 2   /* Muon Newton-Schulz GEMM chain */
-#define VB_PHASE_MUON_APPLY 3
+#define VB_PHASE_MUON_APPLY 3 /* the separate apply pass, or the last update launch when it applies its result itself
+                                (that launch is then counted under VB_PHASE_MUON_NS as well) */
 #define VB_PHASE_EXCHANGE 4  /* fences of a fused exchange; NCCL all-gather / broadcast */
 #define VB_PHASE_HOST_H2D 5  /* vb_optimizer_step_host: gradient uploads (first to last, on their own stream) */
 #define VB_PHASE_HOST_D2H 6  /* vb_optimizer_step_host: parameter downloads (first to last, on their own stream) */

@@ -473,16 +473,17 @@ assert worst <= 2e-2 and moved <= 2e-2
 """
 
 
-def test_wide_update_tile_when_selected():
-    """VB_TC_WIDE=1 runs the update products whose width is a multiple of 512 on 256 x 512 tiles (both
-    accumulator halves share the staged rows of A).  The variant is off by default because it
-    measured slower; selected, it must meet the same bound.  The switch is read once per process,
-    hence the child process."""
+def test_wide_tiles_when_selected():
+    """VB_TC_WIDE=1 / VB_TC_WIDE_GRAM=1 run the update products whose width is a multiple of 512, and
+    the symmetric Gram products, on 256 x 512 tiles (both accumulator halves share the staged rows
+    of A; Gram tiles come with one or two halves and the half on the diagonal reads A's rows as
+    its B).  The variants are off by default because they measured slower; selected, they must
+    meet the same bound.  The switches are read once per process, hence the child process."""
     import os
     import subprocess
     import sys
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    env = dict(os.environ, VB_TC_WIDE="1")
+    env = dict(os.environ, VB_TC_WIDE="1", VB_TC_WIDE_GRAM="1")
     r = subprocess.run([sys.executable, "-c", WIDE_TILE_CHECK.format(root=root)], env=env, capture_output=True,
                        text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]

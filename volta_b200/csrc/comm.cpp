@@ -26,6 +26,7 @@ struct NcclApi {
     ncclResult_t (*GetUniqueId)(ncclUniqueId *) = nullptr;
     ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int) = nullptr;
     ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+    ncclResult_t (*CommAbort)(ncclComm_t) = nullptr;  // optional: teardown after a failed collective
     ncclResult_t (*AllGather)(const void *, void *, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
     ncclResult_t (*AllReduce)(const void *, void *, size_t, ncclDataType_t, int /*ncclRedOp_t*/, ncclComm_t, cudaStream_t) = nullptr;
     ncclResult_t (*Broadcast)(const void *, void *, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
@@ -69,6 +70,7 @@ int load_api()
     VB_SYM(GetErrorString, "ncclGetErrorString")
     VB_SYM(GetVersion, "ncclGetVersion")
 #undef VB_SYM
+    *(void **)(&g_api.CommAbort) = dlsym(h, "ncclCommAbort");
     return VB_OK;
 }
 
@@ -78,12 +80,22 @@ int load_api()
         if (_r != 0)                                                                      \
             return fail(VB_ERR_NCCL, "%s failed: %s (%d)", #expr, g_api.GetErrorString(_r), _r); \
     } while (0)
+// The same for collectives on an engine's communicator: remembers the failure for teardown.
+#define VB_NCCL_ON(eng, expr)                                                             \
+    do {                                                                                  \
+        ncclResult_t _r = (expr);                                                         \
+        if (_r != 0) {                                                                    \
+            (eng)->comm->failed = true;                                                   \
+            return fail(VB_ERR_NCCL, "%s failed: %s (%d)", #expr, g_api.GetErrorString(_r), _r); \
+        }                                                                                 \
+    } while (0)
 
 }  // namespace
 
 struct Comm {
     ncclComm_t comm = nullptr;
     float *d_token = nullptr;  // one float: the payload of the barrier all-reduce
+    bool failed = false;       // a collective returned an error: tear down with ncclCommAbort
 };
 
 int comm_unique_id(void *id128)
@@ -115,7 +127,10 @@ int comm_init(vb_engine *eng, const void *id128, int rank, int world)
 void comm_destroy(vb_engine *eng)
 {
     if (eng->comm) {
-        if (eng->comm->comm && g_api.CommDestroy) g_api.CommDestroy(eng->comm->comm);
+        // ncclCommDestroy waits for outstanding collectives; after a failed one they may never
+        // finish (a peer is gone), so the communicator is aborted instead
+        if (eng->comm->comm && eng->comm->failed && g_api.CommAbort) g_api.CommAbort(eng->comm->comm);
+        else if (eng->comm->comm && g_api.CommDestroy) g_api.CommDestroy(eng->comm->comm);
         if (eng->comm->d_token) cudaFree(eng->comm->d_token);
         delete eng->comm;
         eng->comm = nullptr;
@@ -126,8 +141,8 @@ void comm_destroy(vb_engine *eng)
 int comm_all_gather_inplace(vb_engine *eng, float *base, int64_t count)
 {
     if (!eng->comm) return fail(VB_ERR_STATE, "engine has no communicator");
-    VB_NCCL(g_api.AllGather(base + (int64_t)eng->rank * count, base, (size_t)count, kNcclFloat,
-                            eng->comm->comm, eng->stream));
+    VB_NCCL_ON(eng, g_api.AllGather(base + (int64_t)eng->rank * count, base, (size_t)count, kNcclFloat,
+                                    eng->comm->comm, eng->stream));
     return VB_OK;
 }
 
@@ -135,14 +150,16 @@ int comm_all_gather_inplace(vb_engine *eng, float *base, int64_t count)
 int comm_all_gather_inplace_bytes(vb_engine *eng, void *base, int64_t bytes)
 {
     if (!eng->comm) return fail(VB_ERR_STATE, "engine has no communicator");
-    VB_NCCL(g_api.AllGather((char *)base + (int64_t)eng->rank * bytes, base, (size_t)bytes, kNcclUint8,
-                            eng->comm->comm, eng->stream));
+    VB_NCCL_ON(eng, g_api.AllGather((char *)base + (int64_t)eng->rank * bytes, base, (size_t)bytes, kNcclUint8,
+                                    eng->comm->comm, eng->stream));
     return VB_OK;
 }
 
 // A one-float all-reduce used as a stream-ordered barrier across the ranks: it completes on
 // a rank only after every rank's stream has reached it, i.e. after all work the other ranks
-// enqueued before it (their update kernels and the peer stores in them) has finished.
+// enqueued before it (their update kernels and the peer stores in them) has finished.  The
+// default fence of a fused step is the flag barrier of exchange_fence.cu; this one is selected by
+// VB_EXCHANGE_FENCE=nccl for comparison (its wait has no bound).
 int comm_barrier(vb_engine *eng)
 {
     if (!eng->comm) return fail(VB_ERR_STATE, "engine has no communicator");
@@ -150,8 +167,8 @@ int comm_barrier(vb_engine *eng)
         VB_CUDA(cudaMalloc(&eng->comm->d_token, sizeof(float)));
         VB_CUDA(cudaMemsetAsync(eng->comm->d_token, 0, sizeof(float), eng->stream));
     }
-    VB_NCCL(g_api.AllReduce(eng->comm->d_token, eng->comm->d_token, 1, kNcclFloat, 0 /*ncclSum*/, eng->comm->comm,
-                            eng->stream));
+    VB_NCCL_ON(eng, g_api.AllReduce(eng->comm->d_token, eng->comm->d_token, 1, kNcclFloat, 0 /*ncclSum*/,
+                                    eng->comm->comm, eng->stream));
     return VB_OK;
 }
 
@@ -167,10 +184,11 @@ int comm_group_broadcast(vb_engine *eng, const BcastItem *items, int64_t n_items
                                          eng->comm->comm, eng->stream);
         if (r != 0) {
             g_api.GroupEnd();
+            eng->comm->failed = true;
             return fail(VB_ERR_NCCL, "ncclBroadcast failed: %s (%d)", g_api.GetErrorString(r), r);
         }
     }
-    VB_NCCL(g_api.GroupEnd());
+    VB_NCCL_ON(eng, g_api.GroupEnd());
     return VB_OK;
 }
 

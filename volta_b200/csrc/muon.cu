@@ -729,8 +729,8 @@ struct MuonState {
     int n_tc_gram_tiles = 0, n_tc_upd_tiles = 0, n_tc_upd_tiles_last = 0;
     // update products whose output width is a multiple of 512 run on 256 x 512 tiles (a quarter
     // less operand traffic from L2); the lists above then hold only the other matrices
-    GemmTile *d_tc_upd_tiles_wide = nullptr, *d_tc_upd_tiles_last_wide = nullptr;
-    int n_tc_upd_tiles_wide = 0, n_tc_upd_tiles_last_wide = 0;
+    GemmTile *d_tc_upd_tiles_wide = nullptr, *d_tc_upd_tiles_last_wide = nullptr, *d_tc_gram_tiles_wide = nullptr;
+    int n_tc_upd_tiles_wide = 0, n_tc_upd_tiles_last_wide = 0, n_tc_gram_tiles_wide = 0;
     int *d_error = nullptr;
     int *h_error = nullptr;              // pinned mirror of d_error, refreshed after every step
     // The last update launch applies its result to the weights itself (tensor-core matrices); the
@@ -784,6 +784,7 @@ void destroy_muon_state(MuonState *s)
     cudaFree(s->d_tc_upd_tiles);
     cudaFree(s->d_tc_upd_tiles_last);
     cudaFree(s->d_tc_upd_tiles_wide);
+    cudaFree(s->d_tc_gram_tiles_wide);
     cudaFree(s->d_tc_upd_tiles_last_wide);
     cudaFree(s->d_error);
     if (s->h_error) cudaFreeHost(s->h_error);
@@ -1043,8 +1044,9 @@ int muon_init(vb_optimizer *opt)
         tc_gemm_tile_shape(&bm, &bn);
         const int iters = opt->ns_steps;
         std::vector<std::vector<TcGemmProblem>> gram((size_t)iters), upd((size_t)iters);
-        std::vector<GemmTile> gram_tiles, upd_tiles, upd_tiles_last, upd_tiles_wide, upd_tiles_last_wide;
+        std::vector<GemmTile> gram_tiles, upd_tiles, upd_tiles_last, upd_tiles_wide, upd_tiles_last_wide, gram_tiles_wide;
         const int wide_cols = s->planes == 1 ? tc_gemm_wide_cols() : 0;
+        const int wide_gram_cols = s->planes == 1 ? tc_gemm_wide_gram_cols() : 0;
         std::stable_sort(tc_tensors.begin(), tc_tensors.end(), by_size);
         // plain bf16 path: the momentum kernel writes the unnormalised bf16 operand and the first
         // iteration's epilogues apply 1/norm; the split path keeps the reference's true division
@@ -1129,7 +1131,28 @@ int muon_init(vb_optimizer *opt)
             // The Gram is symmetric: with square tiles only those on or above the diagonal are
             // computed; off-diagonal ones are also stored transposed by the epilogue.
             int gram_all = 0, gram_used = 0;
-            for (int m0 = 0; m0 < sh; m0 += bm)
+            const bool gram_wide = wide_gram_cols == 2 * bn && bm == bn && sh % bn == 0;
+            if (gram_wide) {
+                // rows of tiles on and above the diagonal, two 256-column halves per tile where a
+                // partner exists: the halves share the staged rows of A, and the half on the
+                // diagonal reads them as its B as well
+                gram_all = (sh / bm) * (sh / bn);
+                for (int m0 = 0; m0 < sh; m0 += bm) {
+                    int n0 = m0;
+                    while (n0 < sh) {
+                        if (n0 + bn < sh) {
+                            gram_tiles_wide.push_back(GemmTile{pidx, m0, n0, GEMM_TILE_SYMMETRIC});
+                            n0 += 2 * bn;
+                            gram_used += 2;
+                        } else {
+                            gram_tiles_wide.push_back(GemmTile{pidx, m0, n0, GEMM_TILE_SYMMETRIC | GEMM_TILE_SINGLE});
+                            n0 += bn;
+                            gram_used += 1;
+                        }
+                    }
+                }
+            }
+            for (int m0 = 0; m0 < sh && !gram_wide; m0 += bm)
                 for (int n0 = 0; n0 < sh; n0 += bn) {
                     ++gram_all;
                     if (bm == bn && n0 < m0) continue;
@@ -1169,6 +1192,8 @@ int muon_init(vb_optimizer *opt)
         VB_TRY(upload(&s->d_tc_upd_tiles, upd_tiles, e->stream));
         VB_TRY(upload(&s->d_tc_upd_tiles_last, upd_tiles_last, e->stream));
         VB_TRY(upload(&s->d_tc_upd_tiles_wide, upd_tiles_wide, e->stream));
+        VB_TRY(upload(&s->d_tc_gram_tiles_wide, gram_tiles_wide, e->stream));
+        s->n_tc_gram_tiles_wide = (int)gram_tiles_wide.size();
         VB_TRY(upload(&s->d_tc_upd_tiles_last_wide, upd_tiles_last_wide, e->stream));
         s->n_tc_upd_tiles_wide = (int)upd_tiles_wide.size();
         s->n_tc_upd_tiles_last_wide = (int)upd_tiles_last_wide.size();
@@ -1266,10 +1291,13 @@ int muon_step(vb_optimizer *opt, uint32_t flags)
         prof_begin(e, VB_PHASE_MUON_NS);
         for (int it = 0; it < opt->ns_steps; ++it) {
             const int par = it & 1;
-            if (s->n_tc_gram_tiles > 0) {
+            if (s->n_tc_gram_tiles + s->n_tc_gram_tiles_wide > 0) {
                 const bool split = s->planes > 1;
                 VB_TRY(launch_ns_gemm_tc(s->d_tc_gram[(size_t)it], s->d_tc_gram_tiles, s->n_tc_gram_tiles,
                                          opt->d_present, s->d_error, e->sm_count, e->stream, gemm_wait_limit, split));
+                VB_TRY(launch_ns_gemm_tc(s->d_tc_gram[(size_t)it], s->d_tc_gram_tiles_wide, s->n_tc_gram_tiles_wide,
+                                         opt->d_present, s->d_error, e->sm_count, e->stream, gemm_wait_limit, split, nullptr,
+                                         /*wide=*/true));
                 const bool last_it = it == opt->ns_steps - 1;
                 TcApplyArgs ap{};
                 if (last_it && fuse_now) {
@@ -1285,6 +1313,8 @@ int muon_step(vb_optimizer *opt, uint32_t flags)
                     ap.keep_update = s->keep_update ? 1 : 0;
                     ap.lr = opt->lr;
                     ap.pt = xp.pt;
+                    // phase timing: this launch counts as Newton-Schulz and, on its own, as "apply"
+                    prof_begin(e, VB_PHASE_MUON_APPLY);
                 }
                 VB_TRY(launch_ns_gemm_tc(s->d_tc_upd[(size_t)it], last_it ? s->d_tc_upd_tiles_last : s->d_tc_upd_tiles,
                                          last_it ? s->n_tc_upd_tiles_last : s->n_tc_upd_tiles,
@@ -1295,7 +1325,9 @@ int muon_step(vb_optimizer *opt, uint32_t flags)
                                          last_it ? s->d_tc_upd_tiles_last_wide : s->d_tc_upd_tiles_wide, n_wide,
                                          opt->d_present, s->d_error, e->sm_count, e->stream, gemm_wait_limit, split,
                                          ap.enabled ? &ap : nullptr, /*wide=*/true));
-                e->launches += 1 + ((last_it ? s->n_tc_upd_tiles_last : s->n_tc_upd_tiles) > 0) + (n_wide > 0);
+                if (ap.enabled) prof_end(e, VB_PHASE_MUON_APPLY);
+                e->launches += (s->n_tc_gram_tiles > 0) + (s->n_tc_gram_tiles_wide > 0) +
+                               ((last_it ? s->n_tc_upd_tiles_last : s->n_tc_upd_tiles) > 0) + (n_wide > 0);
             }
             if (s->n_gram_tiles > 0) {
                 VB_TRY(launch_ns_gemm_f32(s->d_gram_prob[par], s->d_gram_tiles, s->n_gram_tiles, opt->d_present,
@@ -1307,7 +1339,7 @@ int muon_step(vb_optimizer *opt, uint32_t flags)
         }
         prof_end(e, VB_PHASE_MUON_NS);
         s->last_flops = s->flops_per_step;
-        if (s->n_tc_gram_tiles > 0)
+        if (s->n_tc_gram_tiles + s->n_tc_gram_tiles_wide > 0)
             VB_CUDA(cudaMemcpyAsync(s->h_error, s->d_error, sizeof(int), cudaMemcpyDeviceToHost, e->stream));
     }
     prof_end(e, VB_PHASE_MUON_PRE);  // no-op if already closed (no Newton-Schulz matrices)
@@ -1323,7 +1355,7 @@ int muon_step(vb_optimizer *opt, uint32_t flags)
     const ChunkDesc *apply_chunks = fuse_now ? s->d_chunks_apply : s->d_chunks;
     const int64_t n_apply_chunks = fuse_now ? s->n_chunks_apply : s->n_chunks;
     if (n_apply_chunks > 0 && compute) {
-        prof_begin(e, VB_PHASE_MUON_APPLY);
+        if (!fuse_now) prof_begin(e, VB_PHASE_MUON_APPLY);  // fused: the phase is the last GEMM launch
         const bool f32_peers = xp.pt.n > 0;
         const int half = xp.pt.half_local == nullptr ? 0 : xp.pt.n_half > 0 ? 2 : 1;
         const int apply_grid = (int)std::min<int64_t>(n_apply_chunks, (int64_t)e->sm_count * 8);
@@ -1339,7 +1371,7 @@ int muon_step(vb_optimizer *opt, uint32_t flags)
         }
 #undef VB_APPLY
         VB_CUDA(cudaGetLastError());
-        prof_end(e, VB_PHASE_MUON_APPLY);
+        if (!fuse_now) prof_end(e, VB_PHASE_MUON_APPLY);
         e->launches += 1;
     }
     VB_TRY(exchange_fence(opt, xp, 2));

@@ -54,7 +54,11 @@ __device__ __forceinline__ void split_f16(float xs, unsigned short &h0, unsigned
 
 enum GemmTileFlags {
     GEMM_TILE_MIRROR = 1,  // symmetric output: also store this tile transposed
-    GEMM_TILE_B_IS_A = 2   // diagonal tile of X^T X (or X X^T): the rows of B are the rows of A, staged once
+    GEMM_TILE_B_IS_A = 2,  // diagonal tile of X^T X (or X X^T): the rows of B are the rows of A, staged once
+    // 256 x 512 tiles (two 256-column halves at n0 and n0 + 256):
+    GEMM_TILE_SINGLE = 4,     // only the first half exists
+    GEMM_TILE_SYMMETRIC = 8   // tile of a symmetric product on or above the diagonal: a half right of the diagonal
+                              // is also stored transposed, the half on the diagonal reads A's rows as its B
 };
 
 struct GemmTile {
@@ -140,7 +144,8 @@ int launch_ns_gemm_tc(const TcGemmProblem *d_problems, const GemmTile *d_tiles, 
                       const uint8_t *d_present, int *d_error_flag, int sm_count, cudaStream_t stream,
                       uint32_t wait_limit = 0, bool split = false, const TcApplyArgs *apply = nullptr, bool wide = false);
 void tc_gemm_tile_shape(int *bm, int *bn);
-int tc_gemm_wide_cols();  // columns of the wide tile (512) of the update products, 0 if not in use
+int tc_gemm_wide_cols();       // columns of the wide tile (512) of the update products, 0 if not in use
+int tc_gemm_wide_gram_cols();  // the same for the Gram products
 int make_bf16_tensor_map(void *map_out, const void *base, int64_t inner, int64_t outer, int mode, int planes = 1,
                          int64_t plane_stride = 0);
 int tc_mn_major_mode(int64_t inner);

@@ -742,6 +742,8 @@ struct TileInfo {
     int m0, n0, k_blocks, a_mode, b_mode, n_terms;
     bool mirror;    // symmetric product: this off-diagonal tile is also stored transposed
     bool b_is_a;    // diagonal tile of a symmetric product: B's rows are A's rows, staged once
+    bool single;    // wide tile with one half only
+    bool symmetric; // wide tile of a symmetric product (mirror / operand sharing decided per half)
     bool skipped;   // gradient absent: nothing to do
     bool withhold;  // test hook (TcGemmProblem::withhold_loads): the producer stages nothing
 };
@@ -756,6 +758,8 @@ __device__ __forceinline__ TileInfo fetch_tile(const TcGemmProblem *problems, co
     ti.withhold = false;
     ti.mirror = false;
     ti.b_is_a = false;
+    ti.single = false;
+    ti.symmetric = false;
     if (t < n_tiles) {
         const GemmTile tile = tiles[t];
         const TcGemmProblem *p = problems + tile.problem;
@@ -764,6 +768,8 @@ __device__ __forceinline__ TileInfo fetch_tile(const TcGemmProblem *problems, co
         ti.n0 = tile.n0;
         ti.mirror = (tile.flags & GEMM_TILE_MIRROR) != 0;
         ti.b_is_a = (tile.flags & GEMM_TILE_B_IS_A) != 0;
+        ti.single = (tile.flags & GEMM_TILE_SINGLE) != 0;
+        ti.symmetric = (tile.flags & GEMM_TILE_SYMMETRIC) != 0;
         ti.k_blocks = (p->K + BK - 1) / BK;
         ti.a_mode = p->a_mode;
         ti.b_mode = p->b_mode;
@@ -849,7 +855,10 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
                 const int b_row0 = ti.n0 + (int)cta_rank * C::kBRows;  // this CTA's rows of B
                 // diagonal tile of a symmetric product (pair kernel, plain bf16): each CTA's 128 rows of
                 // B are its 128 rows of A, so they are fetched once and the MMA reads A's slot twice
-                const bool alias_b = kCtas == 2 && !kSplit && ti.b_is_a;
+                const bool alias_b = kCtas == 2 && !kSplit && !kWide && ti.b_is_a;
+                // wide tile: the half on the diagonal of a symmetric product reads A's rows as its B
+                const bool alias_h0 = kWide && ti.symmetric && ti.n0 == ti.m0;
+                const int wide_b_loads = (ti.single ? 1 : 2) - (alias_h0 ? 1 : 0);
                 constexpr int kRing = kSplit ? C::kSplitStages : C::kStages;
                 constexpr int kSlotBytes = kSplit ? C::kSplitStageBytes : C::kStageBytes;
                 const int n_slots = ti.k_blocks;  // one ring slot per k block
@@ -874,7 +883,9 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
                         // (and, a ring later, this thread's own) run out.  Used by the expiry test.
                     } else if (lane == 0) {
                         if (cta_rank == 0)
-                            mbar_expect_tx(&bars->full[stage], alias_b ? kCtas * kRows128Bytes : kCtas * kSlotBytes);
+                            mbar_expect_tx(&bars->full[stage], kWide     ? kCtas * kRows128Bytes * (1 + wide_b_loads)
+                                                               : alias_b ? kCtas * kRows128Bytes
+                                                                         : kCtas * kSlotBytes);
 #pragma unroll
                         for (int pl = 0; pl < (kSplit ? kSplitPlanes : 1); ++pl)
                             load_rows128<kCtas, kSplit>(sa + pl * C::kStageBytes, &ti.p->map_a, ti.a_mode, a_row0, k0, pl,
@@ -883,11 +894,13 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
 #pragma unroll
                         for (int pl = 0; pl < (kSplit ? kSplitPlanes : 1); ++pl)
 #pragma unroll
-                            for (int j = 0; j < C::kBRows / 128; ++j)  // wide tile: this CTA's 128 rows of each half
+                            for (int j = 0; j < C::kBRows / 128; ++j) {  // wide tile: this CTA's 128 rows of each half
+                                if (kWide && ((j == 1 && ti.single) || (j == 0 && alias_h0))) continue;
                                 load_rows128<kCtas, kSplit>(sb + pl * C::kStageBytes + j * kRows128Bytes, &ti.p->map_b,
                                                             ti.b_mode,
                                                             kWide ? ti.n0 + j * BN + (int)cta_rank * 128 : b_row0 + j * 128,
                                                             k0, pl, full_bar);
+                            }
                     }
                     if (++stage == kRing) {
                         stage = 0;
@@ -908,6 +921,7 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
             uint32_t phase = 0;
             int acc = 0;
             uint32_t acc_phase = 0;
+            uint32_t half_phase[2] = {0u, 0u};  // wide tile: each half's barriers advance only when the half is used
             bool ok = true;
             TileInfo next = fetch_tile(problems, tiles, n_tiles, present, group_id);
             for (int t = group_id; t < n_tiles && ok; t += n_groups) {
@@ -952,14 +966,16 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
                         // both halves of the 512 accumulator columns read the same staged rows of A
 #pragma unroll
                         for (int h = 0; h < 2; ++h) {
+                            if (h == 1 && ti.single) continue;
                             if (slot == 0) {  // this half must have been drained by the previous tile's epilogue
-                                if (!MBAR_WAIT(1, &bars->tmem_empty[h], acc_phase ^ 1u)) {
+                                if (!MBAR_WAIT(1, &bars->tmem_empty[h], half_phase[h] ^ 1u)) {
                                     ok = false;
                                     break;
                                 }
                                 tcgen05_fence_after();
                             }
-                            const uint32_t sb = base + kRows128Bytes + (uint32_t)(h * kRows128Bytes);
+                            const bool alias = h == 0 && ti.symmetric && ti.n0 == ti.m0;  // B's rows are A's
+                            const uint32_t sb = alias ? base : base + kRows128Bytes + (uint32_t)(h * kRows128Bytes);
 #pragma unroll
                             for (int kk = 0; kk < BK / UMMA_K; ++kk)
                                 tcgen05_mma_bf16<kCtas>(tmem_base + (uint32_t)(h * kAccCols), operand_desc(base, ti.a_mode, kk),
@@ -981,10 +997,13 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
                     }
                 }
                 if (!ok) break;
-                if (kWide) {  // both halves complete (in every CTA); every tile uses both barriers
+                if (kWide) {  // the halves this tile used are complete (in every CTA)
                     tcgen05_commit<kCtas>(&bars->tmem_full[0]);
-                    tcgen05_commit<kCtas>(&bars->tmem_full[1]);
-                    acc_phase ^= 1u;
+                    half_phase[0] ^= 1u;
+                    if (!ti.single) {
+                        tcgen05_commit<kCtas>(&bars->tmem_full[1]);
+                        half_phase[1] ^= 1u;
+                    }
                 } else {
                     tcgen05_commit<kCtas>(&bars->tmem_full[acc]);  // accumulator complete (in every CTA)
                     if (++acc == 2) {
@@ -1006,6 +1025,7 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
         const uint32_t my_stage = smem_u32(epi_stage) + (uint32_t)((warp - 2) * kStageWarpBytes);  // plain kernel only
         int acc = 0;
         uint32_t acc_phase = 0;
+        uint32_t half_phase[2] = {0u, 0u};
         bool ok = true;
         TileInfo next = fetch_tile(problems, tiles, n_tiles, present, group_id);
         for (int t = group_id; t < n_tiles && ok; t += n_groups) {
@@ -1046,10 +1066,13 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
             // (wide tile) both buffers in every tile, as the two halves of its 512 columns.
 #pragma unroll 1
             for (int h = 0; h < C::kHalves && ok; ++h) {
+            if (kWide && h == 1 && ti.single) break;
             const int buf = kWide ? h : acc;
+            // a half of a symmetric wide tile is mirrored when it lies right of the diagonal
+            const bool mirror = (kWide && ti.symmetric) ? (ti.n0 + h * BN > ti.m0) : ti.mirror;
             // warp-uniform: near expiry some lanes could see the barrier flip and others give up;
             // the whole warp must take the same branch before the aligned tcgen05.ld below
-            if (!__all_sync(0xffffffffu, MBAR_WAIT(3, &bars->tmem_full[buf], acc_phase))) {
+            if (!__all_sync(0xffffffffu, MBAR_WAIT(3, &bars->tmem_full[buf], kWide ? half_phase[h] : acc_phase))) {
                 ok = false;
                 break;
             }
@@ -1071,20 +1094,20 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
                 // (a * s) * 0.5 == a * (s * 0.5) and -(a * s) == a * (-s) exactly
                 if (epi == TC_EPI_HALF)
                     drain_fast<TC_EPI_HALF>(taddr, row - lane, tile_col0, M, 0.5f * acc_scale, lane, out_bf16, out_f32,
-                                            ti.mirror, transpose, ld, apply_w, apply_pos, ap, my_stage);
+                                            mirror, transpose, ld, apply_w, apply_pos, ap, my_stage);
                 else if (epi == TC_EPI_THREE_I_MINUS)
                     drain_fast<TC_EPI_THREE_I_MINUS>(taddr, row - lane, tile_col0, M, -acc_scale, lane, out_bf16,
-                                                     out_f32, ti.mirror, transpose, ld, nullptr, 0, ap, my_stage);
+                                                     out_f32, mirror, transpose, ld, nullptr, 0, ap, my_stage);
                 else
                     drain_fast<TC_EPI_IDENTITY>(taddr, row - lane, tile_col0, M, acc_scale, lane, out_bf16, out_f32,
-                                                ti.mirror, transpose, ld, nullptr, 0, ap, my_stage);
+                                                mirror, transpose, ld, nullptr, 0, ap, my_stage);
             }
             if (!fast) {
                 DrainArgs da;
                 da.taddr = taddr; da.row = row; da.tile_col0 = tile_col0; da.M = M; da.N = N; da.epi = epi;
                 da.lane = lane; da.acc_scale = acc_scale; da.split_e = split_e; da.ld = ld; da.plane_stride = plane_stride;
                 da.out_planes = out_planes; da.out_planes_in = out_planes_in; da.bf16_rows_32b = bf16_rows_32b;
-                da.mirror = ti.mirror; da.transpose = transpose; da.out_bf16 = out_bf16; da.out_f32 = out_f32; da.in_bf16 = in_bf16;
+                da.mirror = mirror; da.transpose = transpose; da.out_bf16 = out_bf16; da.out_f32 = out_f32; da.in_bf16 = in_bf16;
                 da.apply_w = apply_w; da.apply_pos = apply_pos; da.ap = &ap;
                 drain_generic<kSplit>(da);
             }
@@ -1100,10 +1123,9 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
                 if (kCtas == 2) mbar_remote_arrive(map_to_cta(smem_u32(&bars->tmem_empty[buf]), 0));
                 else mbar_arrive(&bars->tmem_empty[buf]);
             }
+            if (kWide) half_phase[h] ^= 1u;
             }  // halves
-            if (kWide) {
-                acc_phase ^= 1u;
-            } else if (++acc == 2) {
+            if (!kWide && ++acc == 2) {
                 acc = 0;
                 acc_phase ^= 1u;
             }
@@ -1297,6 +1319,20 @@ int tc_gemm_wide_cols()
     static int v = -1;
     if (v < 0) {
         const char *e = getenv("VB_TC_WIDE");
+        v = (tc_use_pair() && e && *e == '1') ? 2 * BN : 0;
+    }
+    return v;
+}
+
+// The same tile for the Gram products: rows of tiles on and above the diagonal, one or two halves
+// each.  Off unless VB_TC_WIDE_GRAM=1: although the contraction is four times longer (the exposed
+// drain weighs less) and a quarter less is fetched from L2, the mixed tile costs balance worse over
+// the 74 CTA pairs and the chain measured 5.12 ms against 4.88 ms per step.
+int tc_gemm_wide_gram_cols()
+{
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("VB_TC_WIDE_GRAM");
         v = (tc_use_pair() && e && *e == '1') ? 2 * BN : 0;
     }
     return v;
