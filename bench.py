@@ -506,7 +506,7 @@ def run_ours(args):
     e2e = None
     if not args.skip_e2e:
         e2e_steps = args.steps
-        pieces = max(4, 32 // world)   # ~14 MB per piece
+        pieces = max(4, 24 // world)   # ~18 MB per piece: 20-24 pieces measured best at N=1 (9.85 ms; 9.95 with 32, 10.3 with 12)
         restart()
         for _ in range(2):
             opt.step_host(grads_pinned.array, params_pinned.array, pieces=pieces)
