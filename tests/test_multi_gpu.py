@@ -321,3 +321,113 @@ def test_two_gpu_gradient_reduction_fused_into_the_update(oracle, kind, transpor
     for a, b, r in zip(res["params0"], res["params1"], ref):
         assert np.array_equal(a.view(np.uint32), r.view(np.uint32))
         assert np.array_equal(b.view(np.uint32), r.view(np.uint32))
+
+
+def _worker_absent_rank(rank, world, shared):
+    """Rank 1 takes part in the first step and then stops stepping (it stays alive and idle: nothing
+    of it is in flight).  Rank 0's next step must give up its wait in bounded time, and rank 1, when
+    it steps again later, must fail as well: no rank goes on alone."""
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    sys.path.insert(0, ROOT)
+    import time
+
+    import workloads
+    from volta_b200 import VB_STEP_NO_EXCHANGE, Adam, Engine, Tensor, VoltaB200Error
+    eng = Engine(rank)
+    if rank == 0:
+        shared["id"] = Engine.unique_id()
+    while "id" not in shared:
+        time.sleep(0.01)
+    eng.init_comm(shared["id"], rank, world)
+    eng.set_wait_limit_ms(300)
+    wl = workloads.c5_ragged_adam(n_tensors=32, max_log2=14, seed=3)
+    h = wl.hyper
+
+    def make():
+        ts = [Tensor(p, p.shape) for p in wl.make_params()]
+        return ts, Adam(ts, h["lr"], h["betas"], h["eps"], h["weight_decay"], engine=eng)
+
+    tensors, opt = make()
+    shared[f"ipc{rank}"] = opt.ipc_handle()
+    while any(f"ipc{r}" not in shared for r in range(world)):
+        time.sleep(0.01)
+    opt.open_peers([shared[f"ipc{r}"] for r in range(world)])
+    for t, g in zip(tensors, wl.make_grads(1)):
+        t.grad = g
+    opt.step()                       # both ranks: an ordinary sharded step
+    eng.synchronize()
+    shared[f"stepped{rank}"] = True
+    while any(f"stepped{r}" not in shared for r in range(world)):
+        time.sleep(0.01)
+    out = {}
+    if rank == 0:
+        t0 = time.perf_counter()
+        opt.step()                   # rank 1 never comes: the fence's bounded wait runs out
+        try:
+            eng.synchronize()
+            out["status"] = 0
+        except VoltaB200Error as exc:
+            out["status"], out["message"] = exc.status, exc.message
+        out["seconds"] = time.perf_counter() - t0
+        shared["rank0_reported"] = True
+    else:
+        while "rank0_reported" not in shared:
+            time.sleep(0.01)
+        opt.step()                   # late, after rank 0 gave up: must not go on alone
+        try:
+            eng.synchronize()
+            out["status"] = 0
+        except VoltaB200Error as exc:
+            out["status"], out["message"] = exc.status, exc.message
+    try:                             # fail-stop: the optimizer refuses further steps ...
+        opt.step()
+        out["again"] = 0
+    except VoltaB200Error as exc:
+        out["again"] = exc.status
+    shared[f"late{rank}"] = True     # nobody frees an arena a peer's kernels may still write flags into
+    while any(f"late{r}" not in shared for r in range(world)):
+        time.sleep(0.01)
+    import ctypes as C
+    from volta_b200 import _lib
+    _lib.load().vb_optimizer_destroy(opt._h)
+    opt._h = C.c_void_p()
+    # ... while the engine and its context are intact: a new optimizer works (no exchange asked for)
+    tensors2, opt2 = make()
+    for t, g in zip(tensors2, wl.make_grads(2)):
+        t.grad = g
+    opt2.step(VB_STEP_NO_EXCHANGE)
+    eng.synchronize()
+    lo, hi = opt2.owned_range()
+    out["alive"] = bool(hi > lo and all(np.all(np.isfinite(t.data)) for t in tensors2))
+    shared[f"out{rank}"] = out
+    shared[f"finished{rank}"] = True
+    while any(f"finished{r}" not in shared for r in range(world)):   # leave together: peers' memory stays mapped
+        time.sleep(0.01)
+    _lib.load().vb_optimizer_destroy(opt2._h)
+    opt2._h = C.c_void_p()
+    eng.close()
+
+
+def test_a_rank_that_stops_stepping_ends_the_step_on_every_rank():
+    """Failure detection between ranks on real GPUs, without faulting anything: the absent rank is
+    alive and idle, the others' waits are bounded (300 ms here), every rank gets VB_ERR_TIMEOUT, the
+    optimizer is fail-stop and the CUDA context stays usable."""
+    if _gpu_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    with ctx.Manager() as mgr:
+        shared = mgr.dict()
+        procs = [ctx.Process(target=_worker_absent_rank, args=(r, 2, shared)) for r in range(2)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(120)
+            assert p.exitcode == 0
+        res = dict(shared)
+    r0, r1 = res["out0"], res["out1"]
+    assert r0["status"] == 4 and "did not reach" in r0["message"], r0
+    assert 0.25 <= r0["seconds"] < 10.0, r0
+    assert r1["status"] == 4, r1
+    assert r0["again"] == 4 and r1["again"] == 4
+    assert r0["alive"] and r1["alive"]

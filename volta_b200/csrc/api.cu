@@ -428,6 +428,7 @@ int plan_exchange(vb_optimizer *opt, uint32_t flags, ExchangePlan *plan)
                 f.peer[r] = reinterpret_cast<uint32_t *>(const_cast<float *>(xp.pt.grad_base[r]) + arena);
         }
         f.host_error = opt->d_fence_error;
+        xp.pt.fence_error = f.local + kSyncError;
         f.rank = e->rank;
         f.wait_ns = (uint64_t)e->wait_limit_ms * 1000000ull;
         static const bool nccl_fence = [] {

@@ -71,6 +71,14 @@ __global__ void __launch_bounds__(32) exchange_fence_kernel(const FenceArgs a, i
     // One lane giving up ends the step for the whole rank: every peer is told, not only the one
     // that was waited for, so that all ranks stop together.
     if (a.local_error != nullptr && *reinterpret_cast<const volatile int *>(a.local_error) != 0) ok = false;
+    // A rank that gave up earlier has written its error word here: this rank fails with it even if
+    // the flags it was waiting for are all there (the failed rank publishes its flags before it
+    // waits), so that no rank goes on alone.
+    if (j == 0) {
+#pragma unroll
+        for (int r = 0; r <= kMaxPeers; ++r)
+            if (ld_acquire_sys(a.local + kSyncError + r) != 0u) ok = false;
+    }
     const bool bad = __any_sync(0xffffffffu, !ok);
     if (bad) {
         const uint32_t code = (uint32_t)phase;  // names the phase that ran out

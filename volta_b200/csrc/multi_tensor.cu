@@ -310,6 +310,7 @@ multi_tensor_update_kernel(const FatChunk *__restrict__ chunks, int64_t n_chunks
 {
     int64_t c = blockIdx.x;
     if (c >= n_chunks) return;
+    if ((PEERS || HALF == 2 || GSUM) && fence_failed(pt.fence_error)) return;  // the fence before this launch gave up
     FatChunk cur = load_chunk(chunks + c);
     for (;;) {
         const int64_t cn = c + gridDim.x;

@@ -41,6 +41,7 @@ struct GradPeers {
     const float *local_base;       // this rank's gradient arena
     int n, rank;
     float scale;
+    const uint32_t *fence_error;   // see PeerTable::fence_error
 };
 __device__ __forceinline__ const float *grad_source(const GradPeers &gp, const float *local, ptrdiff_t pos, int k)
 {
@@ -86,6 +87,7 @@ momentum_kernel(const TensorDesc *__restrict__ tensors, const ChunkDesc *__restr
                 const GradPeers gp)
 {
     __shared__ float warp_sums[kEwThreads / 32];
+    if (GSUM && fence_failed(gp.fence_error)) return;  // the peers' gradients may not be there
     for (int64_t c = blockIdx.x; c < n_chunks; c += gridDim.x) {
         const ChunkDesc ch = chunks[c];
         if (present[ch.tensor] == 0) continue;
@@ -606,6 +608,7 @@ apply_kernel(const TensorDesc *__restrict__ tensors, const ChunkDesc *__restrict
     // A Newton-Schulz kernel of this step gave up a wait: its update buffers are half written.
     // Nothing is applied, so the weights (here and on the peers) keep their pre-step values.
     if (error_flag != nullptr && *reinterpret_cast<const volatile int *>(error_flag) != 0) return;
+    if ((PEERS || HALF == 2) && fence_failed(pt.fence_error)) return;  // the fence before this launch gave up
     for (int64_t c = blockIdx.x; c < n_chunks; c += gridDim.x) {
         const ChunkDesc ch = chunks[c];
         if (present[ch.tensor] == 0) continue;
@@ -1246,6 +1249,7 @@ int muon_step(vb_optimizer *opt, uint32_t flags)
         gp.n = xp.pt.n_grad;
         gp.rank = xp.pt.rank;
         gp.scale = xp.pt.grad_scale;
+        gp.fence_error = xp.pt.fence_error;
         for (int r = 0; r < gp.n; ++r) gp.base[r] = xp.pt.grad_base[r];
         // a one-rank engine asked for the mean or the sum of gradients: scale 1, nothing to add
 #define VB_MOMENTUM(P, G)                                                                                      \

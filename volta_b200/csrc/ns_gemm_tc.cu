@@ -814,6 +814,8 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
         // An earlier kernel of the chain gave up a wait: its output is half written, so this
         // launch computes and stores nothing (read once per CTA: every role sees the same value).
         bars->skip = *reinterpret_cast<const volatile int *>(error_flag) != 0 ? 1u : 0u;
+        // a launch that stores into peer GPUs also stays idle when the fence before it gave up
+        if (ap.enabled && (ap.pt.n > 0 || ap.pt.n_half > 0) && fence_failed(ap.pt.fence_error)) bars->skip = 1u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {  // TMEM allocation is warp-wide; with two CTAs the same warp of both allocates

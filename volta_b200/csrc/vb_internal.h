@@ -77,7 +77,22 @@ struct PeerTable {
     int n_grad;        // > 0: the gradient of an element is the sum over all ranks, in rank order
     int rank;          // this rank's place in that order
     float grad_scale;  // the sum is multiplied by this (1, or 1 / world for the mean)
+    // The error words of this rank's fence block (kSyncError, one per rank), or null when the step
+    // touches no peer memory.  A kernel that finds one set does nothing: the fence before it gave
+    // up (a peer never reached the step, or failed), so peers must not be written to or read from.
+    const uint32_t *fence_error;
 };
+
+#ifdef __CUDACC__
+__device__ __forceinline__ bool fence_failed(const uint32_t *fence_error)
+{
+    if (fence_error == nullptr) return false;
+    uint32_t any = 0;
+#pragma unroll
+    for (int r = 0; r <= 7; ++r) any |= reinterpret_cast<const volatile uint32_t *>(fence_error)[r];
+    return any != 0u;
+}
+#endif
 
 // Flag words that order the ranks around a step that touches peer memory.  Every arena that can
 // be opened by the peers (parameters, bf16 copies, gradients) carries one block of kSyncWords
