@@ -156,7 +156,9 @@ int vb_engine_synchronize_deadline(vb_engine *engine, double timeout_ms);
 /* Bound, in milliseconds of device wall time, of every wait of this engine's kernels on another
  * rank (the flag barrier around sharded steps).  Default 5000.  A wait that runs out ends the
  * step on every rank: each rank's next call on the optimizer (or synchronize) returns
- * VB_ERR_TIMEOUT, the optimizer is fail-stop from then on, the CUDA context stays usable. */
+ * VB_ERR_TIMEOUT, the optimizer is fail-stop from then on, the CUDA context stays usable.
+ * No counterpart in the reference (single process; its own waits are bounded by
+ * sync_checked(), src/gpu/context.rs:448-505). */
 int vb_engine_set_wait_limit_ms(vb_engine *engine, uint32_t milliseconds);
 /* The engine's cudaStream_t, for callers that enqueue their own producers of gradients. */
 int vb_engine_stream(vb_engine *engine, void **cuda_stream);
@@ -345,7 +347,7 @@ int vb_optimizer_open_peers(vb_optimizer *opt, const void *handles, int n_handle
  * after a step, so the parameters are unchanged.  *ms_per_rep is this rank's device time per
  * repetition; bytes in and out per repetition are (world - 1) slices each.  Needs
  * vb_optimizer_open_peers; all ranks must call it together.  Benchmarks use the result as the
- * measured ceiling of a sharded step's exchange. */
+ * measured ceiling of a sharded step's exchange.  No counterpart in the reference. */
 int vb_optimizer_peer_copy_probe(vb_optimizer *opt, int reps, double *ms_per_rep);
 
 /* Data-parallel gradients (no counterpart in the reference, which has one process and one

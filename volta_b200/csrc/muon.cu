@@ -1228,7 +1228,7 @@ int muon_step(vb_optimizer *opt, uint32_t flags)
     // The last update launch applies its result itself (and stores the new weights into the peers
     // when their arenas are open: measured at 2 GPUs 3.37 ms per step against 3.57 ms with the
     // separate apply pass, since the NVLink stores then overlap the launch's tensor work).
-    const bool fuse_now = s->fuse_apply;
+    const bool fuse_now = s->fuse_apply && s->n_tc_upd_tiles_last + s->n_tc_upd_tiles_last_wide > 0;
     s->last_step_fused = fuse_now;
     bool fence1_done = false;
     if (gsum) {
