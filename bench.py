@@ -731,6 +731,49 @@ def time_cpu_muon_sample(ns_steps=5):
     return time.perf_counter() - t0, 4.0 * 1024 ** 3 * ns_steps
 
 
+def time_library_chain(shapes, ns_steps, dev, min_seconds):
+    """The Newton-Schulz chain's products alone through torch.bmm (cuBLAS, bf16): the library baseline.
+
+    Same matrices per shape batched into one call, the short-side Gram as in the product path, but
+    whole products (no symmetry), no polynomial pieces, no normalisation and no apply: what a
+    chain of library GEMMs costs before anything is fused into it.  Returns (ms, flops) per chain."""
+    import torch
+
+    by_shape = {}
+    for r, c in shapes:
+        by_shape[(r, c)] = by_shape.get((r, c), 0) + 1
+    gen = torch.Generator(device=dev).manual_seed(7)
+    xs = [torch.randn(n, r, c, device=dev, dtype=torch.bfloat16, generator=gen) * 0.01 for (r, c), n in by_shape.items()]
+
+    def chain():
+        flops = 0.0
+        for x in xs:
+            n, r, c = x.shape
+            y = x
+            for _ in range(ns_steps):
+                if r >= c:
+                    y = torch.bmm(y, torch.bmm(y.transpose(1, 2), y))
+                else:
+                    y = torch.bmm(torch.bmm(y, y.transpose(1, 2)), y)
+                flops += 4.0 * n * min(r, c) ** 2 * max(r, c)
+        return flops
+
+    for _ in range(3):
+        flops = chain()
+    torch.cuda.synchronize(dev)
+    blocks = []
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    while len(blocks) < 3 or (time.perf_counter() - t0 < min_seconds and len(blocks) < 40):
+        e0.record()
+        for _ in range(10):
+            chain()
+        e1.record()
+        e1.synchronize()
+        blocks.append(e0.elapsed_time(e1) / 10)
+    return statistics.median(blocks), flops
+
+
 def run_muon(args, eng, world, rank, dev, barrier, max_over_ranks, peaks):
     """Muon on the 96 matrices of the 24-layer d=1024 configuration: NS TFLOP/s."""
     import torch
@@ -848,6 +891,15 @@ def run_muon(args, eng, world, rank, dev, barrier, max_over_ranks, peaks):
     out["config"] = {"workload": f"c4_muon: {len(wl.shapes)} matrices ({args.muon_layers} x {{3072x1024, 1024x1024, "
                                  f"4096x1024, 1024x4096}}), {wl.total} f32 params, lr=0.1 momentum=0.9 nesterov "
                                  "ns_steps=5"}
+    if world == 1 and not args.no_library_baseline and "bf16" in out:
+        lib_ms, lib_flops = time_library_chain(wl.shapes, h["ns_steps"], dev, timed_blocks.cap_seconds)
+        out["bf16"]["library_baseline"] = {
+            "ms_per_chain": lib_ms, "tflops": lib_flops / (lib_ms * 1e-3) / 1e12, "flops_per_chain": lib_flops,
+            "ours_ms": out["bf16"]["ns_ms_per_step"],
+            "ours_tflops_on_whole_products": lib_flops / (out["bf16"]["ns_ms_per_step"] * 1e-3) / 1e12,
+            "note": "the same ten products per matrix through torch.bmm (cuBLAS bf16, one batched call per shape), "
+                    "whole products, nothing fused: no polynomial pieces, normalisation or apply, which "
+                    "ns_ms_per_step includes"}
     if world == 1 and not args.no_cpu_baseline and "bf16" in out:
         sec, fl = time_cpu_muon_sample(h["ns_steps"])
         ref_flops = out["bf16"]["reference_formulation_flops_per_step"]
@@ -881,6 +933,8 @@ def main():
     ap.add_argument("--skip-muon", action="store_true", help="Adam only")
     ap.add_argument("--skip-muon-f32", action="store_true", help="skip the (slow) f32 Newton-Schulz timing")
     ap.add_argument("--only-muon", action="store_true", help="profiling runs: Muon bf16 only")
+    ap.add_argument("--no-library-baseline", action="store_true",
+                    help="skip timing the Newton-Schulz products through torch.bmm beside the Muon numbers")
     ap.add_argument("--skip-c5", action="store_true", help="skip the ragged 4096-tensor Adam section")
     ap.add_argument("--skip-parity", action="store_true", help="profiling runs: skip the parity block")
     ap.add_argument("--min-seconds", type=float, default=MIN_TIMED_SECONDS,
