@@ -133,6 +133,32 @@ def test_ordered_sum_adversarial_values(oracle, engine):
         opt.close()
 
 
+@pytest.mark.gpu
+def test_ordered_sum_ties_on_large_matrices(oracle, engine):
+    """4 M addends drawn from a few powers of two: once the running sum passes 1 the smallest square
+    (2^-24) is exactly half an ulp of it, so about a third of the additions are ties whose rounding
+    depends on the parity of the running sum; the blocks then run under guessed binades.  A second
+    matrix mixes such values with ordinary ones so that ties and inexact addends alternate."""
+    from volta_b200 import VB_NS_F32, Muon, Tensor
+    rng = np.random.default_rng(11)
+    n_r, n_c = 2048, 2048
+    cases = [np.exp2(-rng.integers(10, 13, (n_r, n_c))).astype(np.float32)]
+    x = (rng.standard_normal((n_r, n_c)) * 6e-4).astype(np.float32)
+    pick = rng.random((n_r, n_c)) < 0.5
+    x[pick] = np.exp2(-rng.integers(11, 14, int(pick.sum()))).astype(np.float32)
+    cases.append(x)
+    for g in cases:
+        w = Tensor(np.zeros((n_r, n_c), np.float32))
+        opt = Muon([w], 0.1, 0.0, False, 0, ns_mode=VB_NS_F32, engine=engine, keep_update=True)
+        w.grad = g
+        opt.step()
+        wr = np.zeros((n_r, n_c), np.float32)
+        ref = oracle.Muon([wr], 0.1, 0.0, False, 0)
+        ref.step([g])
+        assert bits_equal(opt.last_update(0), ref.last_update[0])
+        opt.close()
+
+
 # ---- bf16 tensor-core path (tcgen05) ----------------------------------------------------------
 
 def _bf16_round(x):

@@ -187,7 +187,7 @@ __global__ void reduce_partials_kernel(const float *__restrict__ partials, const
 // k in one go.  If the result would leave the binade (k + inc >= 2^24), or s is not a normal
 // number yet, one thread walks the elements with real f32 additions until the exponent of s
 // changes and the block resumes from there; this happens about once per doubling of s.  The
-// per-warp maps localise the crossing to one warp's span (512 elements), so a walk is short.
+// per-warp and per-thread maps localise the crossing to one thread's 16 elements, so a walk is short.
 struct IncMap {
     uint32_t even;  // increment (in ulps) when k is even
     uint32_t odd;   // increment when k is odd
@@ -204,31 +204,55 @@ __device__ __forceinline__ IncMap compose(IncMap a, IncMap b)  // a first, then 
     return c;
 }
 
-__device__ __forceinline__ IncMap element_map(float a, float inv_ulp)  // inv_ulp = 2^(23 - e), a normal float
+// Map of one addend a >= 0: x = a / ulp = q + f is exact (power-of-two scaling; inv_ulp =
+// 2^(23 - e)).  Unless f is exactly 1/2 the increment is rne(x) whatever the parity of k, read
+// off the low bits of x + 2^23; x is clamped to 2^23, an increment that leaves the binade for
+// certain (k >= 2^23), which also catches inf and NaN.  On a tie the even-k increment is the even
+// one of {q, q + 1} (what the addition above rounds to) and the odd-k increment the other one.
+struct ElementInc {
+    uint32_t r;  // rne(x), ties to even; 2^23 when x was clamped
+    float d;     // x - rne(x), exact: +-0.5 on a tie
+};
+__device__ __forceinline__ ElementInc element_inc(float a, float inv_ulp)
 {
-    // x = a / ulp = q + f, exact (power-of-two scaling).  q and the comparison of f with 1/2 are
-    // read off the bits of x with integer operations (no float->int conversions, which run at a
-    // quarter of the ALU rate): x = M * 2^(E - 150) with M the 24-bit significand.
-    IncMap m;
-    const uint32_t xb = __float_as_uint(__fmul_rn(a, inv_ulp));
-    const uint32_t E = xb >> 23;  // a >= 0: no sign bit (NaN/inf give E = 255)
-    if (E >= 151u) {              // x >= 2^24 (or inf/NaN): leaves the binade for certain
-        m.even = m.odd = kIncSat;
-        return m;
+    ElementInc e;
+    const float x = fminf(__fmul_rn(a, inv_ulp), 8388608.0f);
+    const float y = __fadd_rn(x, 8388608.0f);
+    e.r = __float_as_uint(y) - 0x4B000000u;
+    e.d = __fsub_rn(x, __fsub_rn(y, 8388608.0f));
+    return e;
+}
+// Composed map of 16 consecutive addends (not saturated: below 2^28).  Ties are rare (the addend
+// must end exactly half an ulp of the running sum), so the sixteen increments are simply added and
+// the parity-dependent composition is only run when one of them was a tie.
+__device__ __forceinline__ IncMap compose16(const float *a, float inv_ulp)
+{
+    uint32_t sum = 0u;
+    bool any_tie = false;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const ElementInc e = element_inc(a[i], inv_ulp);
+        sum += e.r;
+        any_tie |= fabsf(e.d) == 0.5f;
     }
-    if (E <= 125u) {              // x < 1/2 (including 0 and subnormal results): no change
+    IncMap m = {sum, sum};
+    if (any_tie) {
         m.even = m.odd = 0u;
-        return m;
+#pragma unroll 1
+        for (int i = 0; i < 16; ++i) {
+            const ElementInc e = element_inc(a[i], inv_ulp);
+            const uint32_t k_odd_even = m.even & 1u, k_odd_odd = (m.odd & 1u) ^ 1u;  // parity of k + increment so far
+            m.even += e.r;
+            m.odd += e.r;
+            if (fabsf(e.d) == 0.5f) {
+                const uint32_t other = e.d > 0.0f ? 1u : 0xffffffffu;  // the odd neighbour is r + 1 or r - 1
+                if (k_odd_even) m.even += other;
+                if (k_odd_odd) m.odd += other;
+            }
+        }
     }
-    const uint32_t M = (xb & 0x7fffffu) | 0x800000u;
-    const uint32_t sh = 150u - E;                 // 0 .. 24 fractional bits
-    const uint32_t qi = sh >= 24u ? 0u : (M >> sh);
-    const uint32_t rem = M & ((1u << sh) - 1u);   // sh <= 24 < 32
-    const uint32_t half = sh ? (1u << (sh - 1u)) : 0u;
-    const uint32_t up = (sh && rem > half) ? 1u : 0u;
-    const uint32_t tie = (sh && rem == half) ? 1u : 0u;
-    m.even = qi + up + (tie & (qi & 1u));          // k even: k+q odd iff q odd -> round up to even
-    m.odd = qi + up + (tie & ((qi & 1u) ^ 1u));    // k odd:  k+q odd iff q even
+    m.even = min(m.even, kIncSat);
+    m.odd = min(m.odd, kIncSat);
     return m;
 }
 
@@ -241,7 +265,7 @@ __device__ __forceinline__ bool binade_ok(float s)
 }
 
 constexpr int kSeqThreads = 512;
-constexpr int kSeqPerThread = 16;
+constexpr int kSeqPerThread = 16;  // compose16 and load_block16 take sixteen elements per thread
 constexpr int kSeqChunk = kSeqThreads * kSeqPerThread;       // 8192 elements per pass
 constexpr int kSeqWarpSpan = 32 * kSeqPerThread;             // elements one warp covers
 
@@ -254,7 +278,8 @@ __device__ __forceinline__ float float_from_k(uint32_t bits_of_s, uint32_t k)
 // in parallel.  A block of 8192 consecutive elements is one composed map once the binade of the
 // running sum at the block's start is known, and that binade can be guessed from an ordinary
 // (tree) prefix sum, which differs from the sequential sum by parts in 10^3 only:
-//   1. block_sumsq_kernel       tree sum of squares of every block            (parallel)
+//   1. momentum_kernel          also leaves the tree sum of squares of every block (its chunks are
+//                               these blocks when the ordered sum is in use)   (parallel)
 //   2. block_guess_kernel       prefix over a matrix's blocks -> guessed exponent per block
 //   3. block_map_kernel         composed map of every block under its guess   (parallel)
 //   4. sumsq_ordered_kernel     walks the blocks: a guessed map is used when the running sum
@@ -282,36 +307,11 @@ __device__ __forceinline__ void load_block16(const float *__restrict__ x, int64_
     }
 }
 
-__global__ void __launch_bounds__(512)
-block_sumsq_kernel(const TensorDesc *__restrict__ tensors, const SeqBlock *__restrict__ blocks, int n_blocks,
-                   const int64_t *__restrict__ sizes, const uint8_t *__restrict__ present,
-                   float *__restrict__ block_sum)
-{
-    __shared__ float warp_sums[16];
-    for (int b = blockIdx.x; b < n_blocks; b += gridDim.x) {
-        const SeqBlock sb = blocks[b];
-        if (present[sb.tensor] == 0) continue;
-        float v[16];
-        load_block16(tensors[sb.tensor].s2, sizes[sb.tensor], (int64_t)sb.index * 8192, threadIdx.x, v);
-        float acc = 0.0f;
-#pragma unroll
-        for (int i = 0; i < 16; ++i) acc += v[i] * v[i];
-#pragma unroll
-        for (int d = 16; d > 0; d >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, d);
-        if ((threadIdx.x & 31) == 0) warp_sums[threadIdx.x >> 5] = acc;
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            float t = 0.0f;
-#pragma unroll
-            for (int w = 0; w < 16; ++w) t += warp_sums[w];
-            block_sum[b] = t;
-        }
-        __syncthreads();
-    }
-}
-
 // One warp per matrix: biased exponent of the (approximate) sum of everything before each block.
-__global__ void block_guess_kernel(const float *__restrict__ block_sum, const int64_t *__restrict__ first_block,
+// The block sums are the momentum kernel's per-chunk sums: with the ordered sum in use the
+// element-wise chunks are the 8192-element blocks (block b of a tensor is its chunk b).
+__global__ void block_guess_kernel(const float *__restrict__ chunk_sum, const int64_t *__restrict__ first_chunk,
+                                   const int64_t *__restrict__ first_block,
                                    const int32_t *__restrict__ ns_tensors, int n_ns,
                                    const uint8_t *__restrict__ present, int32_t *__restrict__ guess)
 {
@@ -320,6 +320,7 @@ __global__ void block_guess_kernel(const float *__restrict__ block_sum, const in
     if (present[ns_tensors[w]] == 0) return;
     const int lane = threadIdx.x & 31;
     const int64_t lo = first_block[w], hi = first_block[w + 1];
+    const float *__restrict__ block_sum = chunk_sum + first_chunk[ns_tensors[w]] - lo;
     double carry = 0.0;
     for (int64_t base = lo; base < hi; base += 32) {
         const int64_t i = base + lane;
@@ -352,9 +353,9 @@ block_map_kernel(const TensorDesc *__restrict__ tensors, const SeqBlock *__restr
         float v[16];
         load_block16(tensors[sb.tensor].s2, sizes[sb.tensor], (int64_t)sb.index * 8192, threadIdx.x, v);
         const float inv_ulp = __uint_as_float((277u - biased) << 23);
-        IncMap m = {0u, 0u};
 #pragma unroll
-        for (int i = 0; i < 16; ++i) m = compose(m, element_map(__fmul_rn(v[i], v[i]), inv_ulp));
+        for (int i = 0; i < 16; ++i) v[i] = __fmul_rn(v[i], v[i]);
+        IncMap m = compose16(v, inv_ulp);
         const int lane = threadIdx.x & 31;
 #pragma unroll
         for (int d = 1; d < 32; d <<= 1) {
@@ -384,6 +385,7 @@ sumsq_ordered_kernel(const TensorDesc *__restrict__ tensors, const int32_t *__re
     constexpr int kWindow = 512;  // blocks whose guessed maps are staged in shared memory at a time
     __shared__ float sq[kSeqChunk];
     __shared__ IncMap warp_maps[kSeqThreads / 32];
+    __shared__ IncMap thread_maps[kSeqThreads];
     __shared__ IncMap win_map[kWindow];
     __shared__ int32_t win_guess[kWindow];
     __shared__ float sh_s;
@@ -454,12 +456,11 @@ sumsq_ordered_kernel(const TensorDesc *__restrict__ tensors, const int32_t *__re
                     // 1/ulp(s) = 2^(23 - e) with e the unbiased exponent of s: biased exponent 150 - e - 127 + 127
                     const uint32_t biased = (__float_as_uint(s) >> 23) & 0xffu;
                     const float inv_ulp = __uint_as_float((277u - biased) << 23);
-                    IncMap m = {0u, 0u};
+                    float rest[kSeqPerThread];  // the addends from `start` on (past cnt: squares of the zero padding)
 #pragma unroll
-                    for (int i = 0; i < kSeqPerThread; ++i) {
-                        const int idx = tid * kSeqPerThread + i;
-                        if (idx >= start && idx < cnt) m = compose(m, element_map(a[i], inv_ulp));
-                    }
+                    for (int i = 0; i < kSeqPerThread; ++i) rest[i] = tid * kSeqPerThread + i >= start ? a[i] : 0.0f;
+                    IncMap m = compose16(rest, inv_ulp);
+                    thread_maps[tid] = m;
 #pragma unroll
                     for (int d = 1; d < 32; d <<= 1) {
                         IncMap o;
@@ -491,7 +492,17 @@ sumsq_ordered_kernel(const TensorDesc *__restrict__ tensors, const int32_t *__re
                             sh_start = cnt;
                             done = true;
                         } else {
-                            walk_from = max(start, w * kSeqWarpSpan);  // the crossing is inside warp w's span
+                            // the crossing is inside warp w's span: take its threads' maps up to the one that crosses
+                            int th = max(start / kSeqPerThread, w * 32);
+                            const int th_end = (w + 1) * 32;
+                            for (; th < th_end; ++th) {
+                                const IncMap tm = thread_maps[th];
+                                const uint32_t inc = (k & 1u) ? tm.odd : tm.even;
+                                if (k + inc >= (1u << 24)) break;
+                                k += inc;
+                            }
+                            s_new = float_from_k(bits, k);
+                            walk_from = max(start, min(th, th_end - 1) * kSeqPerThread);
                         }
                     }
                     if (!done) {
@@ -697,7 +708,7 @@ struct MuonState {
     __nv_bfloat16 *d_xb[2] = {nullptr, nullptr};  // bf16 path: X ping-pong
     __nv_bfloat16 *d_cb = nullptr;                // bf16 path: C = 3I - Gram per matrix (short side squared)
     float *d_sumsq = nullptr;         // per tensor
-    float *d_partials = nullptr;      // per chunk (bf16 mode)
+    float *d_partials = nullptr;      // per chunk: sum of squares of the update (tree order)
     uint8_t *d_ns_kind = nullptr;
     int64_t *d_sizes = nullptr;
     int32_t *d_ns_tensors = nullptr;  // owned tensors that run Newton-Schulz
@@ -707,7 +718,6 @@ struct MuonState {
     // tree sums, guessed exponents and guessed maps (see block_map_kernel)
     SeqBlock *d_seq_blocks = nullptr;
     int64_t *d_first_block = nullptr;  // per Newton-Schulz tensor (n_ns + 1)
-    float *d_block_sum = nullptr;
     int32_t *d_block_guess = nullptr;
     IncMap *d_block_map = nullptr;
     int n_seq_blocks = 0;
@@ -767,7 +777,6 @@ void destroy_muon_state(MuonState *s)
     cudaFree(s->d_first_chunk);
     cudaFree(s->d_seq_blocks);
     cudaFree(s->d_first_block);
-    cudaFree(s->d_block_sum);
     cudaFree(s->d_block_guess);
     cudaFree(s->d_block_map);
     cudaFree(s->d_desc);
@@ -909,7 +918,9 @@ int muon_init(vb_optimizer *opt)
     *s->h_error = 0;
 
     // element-wise chunk table over owned tensors
-    const int64_t chunk_len = pick_chunk_len(off, e->sm_count);
+    // with the ordered sum of squares in use a chunk is one of its 8192-element blocks, so that the
+    // momentum kernel's chunk sums serve as the block sums of the binade guess
+    const int64_t chunk_len = opt->ns_mode != VB_NS_BF16 ? (int64_t)kSeqChunk : pick_chunk_len(off, e->sm_count);
     std::vector<TensorDesc> desc((size_t)std::max<int64_t>(nt, 1));
     std::vector<ChunkDesc> chunks;
     std::vector<int64_t> first_chunk((size_t)nt + 1, 0);
@@ -966,7 +977,6 @@ int muon_init(vb_optimizer *opt)
                 VB_TRY(upload(&s->d_seq_blocks, blocks, e->stream));
                 VB_TRY(upload(&s->d_first_block, first_block, e->stream));
                 const size_t nb = std::max<size_t>(blocks.size(), 1);
-                VB_CUDA(cudaMalloc(&s->d_block_sum, nb * sizeof(float)));
                 VB_CUDA(cudaMalloc(&s->d_block_guess, nb * sizeof(int32_t)));
                 VB_CUDA(cudaMalloc(&s->d_block_map, nb * sizeof(IncMap)));
             }
@@ -1256,7 +1266,7 @@ int muon_step(vb_optimizer *opt, uint32_t flags)
     momentum_kernel<P, G><<<ew_grid, kEwThreads, 0, e->stream>>>(s->d_desc, s->d_chunks, s->n_chunks,      \
                                                                 opt->d_present, opt->momentum, opt->nesterov, \
                                                                 s->d_partials, direct, s->d_upd, s->d_xb[0], gp)
-        if (fast_norm) {
+        if (fast_norm || s->n_seq_blocks > 0) {  // chunk sums: the sum itself (bf16 mode) or the binade guesses
             if (gsum) VB_MOMENTUM(true, true); else VB_MOMENTUM(true, false);
         } else {
             if (gsum) VB_MOMENTUM(false, true); else VB_MOMENTUM(false, false);
@@ -1272,14 +1282,12 @@ int muon_step(vb_optimizer *opt, uint32_t flags)
         else {
             if (s->n_seq_blocks > 0) {
                 const int grid = std::min(s->n_seq_blocks, e->sm_count * 4);
-                block_sumsq_kernel<<<grid, 512, 0, e->stream>>>(s->d_desc, s->d_seq_blocks, s->n_seq_blocks, s->d_sizes,
-                                                                opt->d_present, s->d_block_sum);
-                block_guess_kernel<<<(s->n_ns + 3) / 4, 128, 0, e->stream>>>(s->d_block_sum, s->d_first_block,
-                                                                            s->d_ns_tensors, s->n_ns, opt->d_present,
-                                                                            s->d_block_guess);
+                block_guess_kernel<<<(s->n_ns + 3) / 4, 128, 0, e->stream>>>(s->d_partials, s->d_first_chunk,
+                                                                            s->d_first_block, s->d_ns_tensors, s->n_ns,
+                                                                            opt->d_present, s->d_block_guess);
                 block_map_kernel<<<grid, 512, 0, e->stream>>>(s->d_desc, s->d_seq_blocks, s->n_seq_blocks, s->d_sizes,
                                                               opt->d_present, s->d_block_guess, s->d_block_map);
-                e->launches += 3;
+                e->launches += 2;
             }
             sumsq_ordered_kernel<<<s->n_ns, kSeqThreads, 0, e->stream>>>(
                 s->d_desc, s->d_ns_tensors, s->d_sizes, opt->d_present, s->d_sumsq, s->d_first_block,
