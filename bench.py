@@ -154,7 +154,7 @@ def bench_config(n_gpus: int):
     """The workload description both arms print (identical for the same N)."""
     return {"workload": C3_WORKLOAD,
             "inputs_vs_l2": "inputs larger than L2 (1.75 GB of theta/g/m/v per step vs 126 MB): no flush needed",
-            "sharding": "single GPU" if n_gpus == 1 else f"parameter arena in {n_gpus} equal slices (ZeRO-1), one rank per GPU"}
+            "sharding": "single GPU" if n_gpus == 1 else f"parameter arena sharded by ownership over {n_gpus} ranks (ZeRO-1), one rank per GPU"}
 
 
 def run_reference(args):
@@ -268,13 +268,17 @@ def run_parity(eng, world, rank, dev, exchange):
     cases = [("adam", workloads.c5_ragged_adam(n_tensors=96, max_log2=16, seed=11), None),
              ("sgd", workloads.c2_cnn_sgd(), None),
              ("muon_f32", muon_wl, VB_NS_F32), ("muon_bf16", muon_wl, VB_NS_BF16)]
+    if world > 1:  # the same Adam list with 45 % of the arena updated by every rank itself instead of exchanged
+        cases.insert(1, ("adam_replicated_tail", workloads.c5_ragged_adam(n_tensors=96, max_log2=16, seed=11), None))
     out = {"n_ranks": world, "steps": 3, "exchange": exchange if world > 1 else "none"}
     all_equal = True
     for name, wl, mode in cases:
         h = wl.hyper
         tensors = [Tensor(p, p.shape) for p in wl.make_params()]
-        if name == "adam":
+        if name.startswith("adam"):
+            eng.set_replicated_fraction(0.45 if name == "adam_replicated_tail" else 0.0)
             opt = Adam(tensors, h["lr"], h["betas"], h["eps"], h["weight_decay"], engine=eng)
+            eng.set_replicated_fraction(0.0)
         elif name == "sgd":
             opt = SGD(tensors, h["lr"], h["momentum"], h["weight_decay"], engine=eng)
         else:
@@ -299,7 +303,7 @@ def run_parity(eng, world, rank, dev, exchange):
         if rank == 0:
             oracle.build()
             ref = wl.make_params()
-            if name == "adam":
+            if name.startswith("adam"):
                 o = oracle.Adam(ref, h["lr"], h["betas"], h["eps"], h["weight_decay"])
             elif name == "sgd":
                 o = oracle.SGD(ref, h["lr"], h["momentum"], h["weight_decay"])
@@ -330,6 +334,7 @@ def run_parity(eng, world, rank, dev, exchange):
             out[f"{name}_bit_identical"] = bool(stats[0].item() == 1.0)
     out["all_ranks_equal"] = all_equal
     out["ok"] = bool(out["adam_bit_identical"] and out["sgd_bit_identical"] and out["muon_f32_bit_identical"]
+                     and out.get("adam_replicated_tail_bit_identical", True)
                      and out["muon_bf16_rel_fro_max"] <= 2e-2 and all_equal)
     return out
 
@@ -437,26 +442,28 @@ def run_ours(args):
     params0_pinned = PinnedBuffer(arena)
     opt.download_arena(0, params0_pinned.array)
 
-    def restart():
+    def restart(o=None):
         """Back to the start of the configuration (seeded parameters, zero moments, t = 0), outside every
         timed region.  The configuration is 50 steps; replaying one resident gradient for thousands of steps
         instead would train every parameter to the fixed point g + wd * theta = 0, where parameters' effective
         gradients and moments underflow -- values no 50-step run ever sees."""
-        opt.reset_state()
-        opt.upload_arena(0, params0_pinned.array)
+        o = opt if o is None else o
+        o.reset_state()
+        o.upload_arena(0, params0_pinned.array)
         eng.synchronize()
 
-    def make_block(flags=0):
+    def make_block(flags=0, o=None):
         def run_block():
-            restart()
+            target = opt if o is None else o
+            restart(target)
             for _ in range(args.warmup):
-                opt.step(flags)
+                target.step(flags)
             barrier()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             lc0 = eng.launch_count
             e0.record(stream)
             for _ in range(args.steps):
-                opt.step(flags)
+                target.step(flags)
             e1.record(stream)
             eng.synchronize()
             timed_launches[0] += eng.launch_count - lc0
@@ -479,8 +486,88 @@ def run_ours(args):
         kernel_blocks = timed_blocks(make_block(VB_STEP_NO_EXCHANGE), barrier, max_over_ranks, min_seconds=0.3)
     else:
         kernel_blocks = blocks
-    clocks = sampler.stop() if rank == 0 else None
     per_rank_update_ms = [statistics.median(timed_blocks.last_local) / args.steps]
+
+    # ---- N > 1: part of the arena replicated instead of exchanged ----
+    # When everything is exchanged the step is bound by NVLink while HBM idles; with the last fraction f of
+    # the arena updated by every rank itself the same launch mixes link-bound and HBM-bound chunks.  f comes
+    # from the two rates just measured (vb_plan_replicated_fraction), the result must equal the plain one.
+    tail = None
+    if world > 1 and args.exchange == "peer" and args.replicated_fraction != 0.0:
+        try:
+            k_ms = statistics.median(kernel_blocks) / args.steps
+            hbm_gbs = ADAM_BYTES_PER_PARAM * (wl.total / world) / (k_ms * 1e-3) / 1e9
+            # the update launch with its peer stores, apart from the fences around it: a short profiled pass
+            restart(opt)
+            for _ in range(args.warmup):
+                opt.step()
+            barrier()
+            eng.set_profiling(True)
+            for ph in ("update", "exchange"):
+                eng.profile(ph)
+            for _ in range(args.steps):
+                opt.step()
+            eng.synchronize()
+            upd_ms = max_over_ranks(eng.profile("update")[0] / args.steps)
+            fence_ms = max_over_ranks(eng.profile("exchange")[0] / args.steps)
+            eng.set_profiling(False)
+            link_gbs = 4.0 * arena * (world - 1) / world / (upd_ms * 1e-3) / 1e9
+            frac = args.replicated_fraction if args.replicated_fraction > 0.0 else \
+                volta_b200.plan_replicated_fraction(ADAM_BYTES_PER_PARAM, world, hbm_gbs, link_gbs)
+            ft = torch.tensor([frac], dtype=torch.float64, device=dev)
+            dist.broadcast(ft, 0)    # one value on every rank
+            frac = float(ft.item())
+            if frac > 0.0:
+                eng.set_replicated_fraction(frac)
+                tensors_t = [Tensor(p, p.shape) for p in params]
+                opt_t = Adam(tensors_t, h["lr"], h["betas"], h["eps"], h["weight_decay"], engine=eng)
+                eng.set_replicated_fraction(0.0)
+                fps = torch.zeros(world, dtype=torch.int64, device=dev)
+                dist.all_gather_into_tensor(fps, torch.tensor([opt_t.plan_fingerprint() & 0x7fffffffffffffff],
+                                                              dtype=torch.int64, device=dev))
+                volta_b200.verify_plan([int(x) for x in fps.cpu().tolist()])
+                opt_t.open_peers(gather_handles(opt_t.ipc_handle(), world, dev))
+                opt_t.upload_arena(1, grads_pinned.array)
+                eng.synchronize()
+                launches_before = timed_launches[0]
+                tail_blocks = timed_blocks(make_block(0, opt_t), barrier, max_over_ranks)
+                tail_launches = timed_launches[0] - launches_before
+                timed_launches[0] = launches_before
+                # same number of steps from the same start on both optimizers: the parameters must agree bit for bit
+                restart(opt)
+                restart(opt_t)
+                for _ in range(args.steps):
+                    opt.step()
+                    opt_t.step()
+                eng.synchronize()
+                opt.download_arena(0, params_pinned.array)
+                plain_bits = params_pinned.array.view(np.uint32).copy()
+                opt_t.download_arena(0, params_pinned.array)
+                same = bool(np.array_equal(plain_bits, params_pinned.array.view(np.uint32)))
+                del plain_bits
+                st = torch.tensor([1.0 if same else 0.0], dtype=torch.float64, device=dev)
+                dist.all_reduce(st, op=dist.ReduceOp.MIN)
+                t_lo, t_hi = opt_t.replicated_range()
+                tail_ms = statistics.median(tail_blocks) / args.steps
+                tail = {"fraction": frac, "replicated_elements": t_hi - t_lo, "ms_per_step": tail_ms,
+                        "value": wl.total / (tail_ms * 1e-3), "unit": "params/s",
+                        "blocks": block_stats(tail_blocks, args.steps), "launches": int(tail_launches),
+                        "equals_the_fully_exchanged_result_bit_for_bit": bool(st.item() == 1.0),
+                        "rates_used": {"hbm_gbs": hbm_gbs, "nvlink_gbs_per_direction": link_gbs,
+                                       "all_exchanged_update_launch_ms": upd_ms, "fences_ms_per_step": fence_ms,
+                                       "how": "HBM: the update kernel alone on a slice (update_only); NVLink: bytes into "
+                                              "a GPU over the duration of the update launch that stores every parameter "
+                                              "to every peer (CUDA events around the launch, a separate pass)"},
+                        "extra_state_bytes_per_gpu": 8 * (t_hi - t_lo),
+                        "note": "the last `fraction` of the arena is updated by every rank itself (its moments live "
+                                "on every rank; every rank holds the complete gradients) and never crosses NVLink; "
+                                "the rest is sliced ZeRO-1 style and exchanged by the same launch"}
+                opt_t.close()
+                del tensors_t
+        except volta_b200.VoltaB200Error as exc:
+            tail = {"error": str(exc)}
+            eng.set_replicated_fraction(0.0)
+    clocks = sampler.stop() if rank == 0 else None
     if world > 1:
         t = torch.zeros(world, dtype=torch.float64, device=dev)
         dist.all_gather_into_tensor(t, torch.tensor(per_rank_update_ms, dtype=torch.float64, device=dev))
@@ -488,6 +575,19 @@ def run_ours(args):
 
     ms_per_step = statistics.median(blocks) / args.steps
     kernel_avg_ms = statistics.median(kernel_blocks) / args.steps
+    all_exchanged = None
+    if tail is not None and tail.get("equals_the_fully_exchanged_result_bit_for_bit") and tail["ms_per_step"] < ms_per_step:
+        # the headline is the faster of the two shardings of the same step; the other one stays in the line
+        all_exchanged = {"ms_per_step": ms_per_step, "value": wl.total / (ms_per_step * 1e-3), "unit": "params/s",
+                         "blocks": block_stats(blocks, args.steps),
+                         "note": "plain ZeRO-1: every parameter is updated by one rank and sent to all others"}
+        zero1_ms_per_step = ms_per_step
+        ms_per_step = tail["ms_per_step"]
+        headline_blocks = tail_blocks
+        launches = tail["launches"]
+    else:
+        zero1_ms_per_step = ms_per_step
+        headline_blocks = blocks
     value = wl.total / (ms_per_step * 1e-3)
 
     # ---- the fabric's own rate for the exchange, measured in this run (N > 1, peer exchange) ----
@@ -606,11 +706,15 @@ def run_ours(args):
                      "restarts from the seeded parameters with zero moments and t = 0, runs the warm-up steps and "
                      "then exactly `steps` timed steps (the configuration itself is 50 steps)",
         "config": config,
-        "arm_details": {"exchange": ("none" if world == 1 else
+        "arm_details": {"sharding": ("none" if world == 1 else
+                                     f"ZeRO-1 slices of the first {1.0 - tail['fraction']:.3f} of the arena, the rest updated "
+                                     "by every rank (replicated_tail)" if all_exchanged is not None else
+                                     "ZeRO-1 slices of the whole arena"),
+                        "exchange": ("none" if world == 1 else
                                      "peer stores over NVLink fused into the update kernel, fenced by a flag barrier in "
                                      "peer-mapped memory" if args.exchange == "peer" else
                                      "nccl all-gather of updated params after the update kernel")},
-        "blocks": block_stats(blocks, args.steps),
+        "blocks": block_stats(headline_blocks, args.steps),
         "update_only": {"value": wl.total / (kernel_avg_ms * 1e-3), "unit": "params/s",
                         "ms_per_step": kernel_avg_ms, "blocks": block_stats(kernel_blocks, args.steps),
                         "per_rank_ms_per_step": per_rank_update_ms,
@@ -625,8 +729,8 @@ def run_ours(args):
                      "algorithmic_bytes_per_launch": ADAM_BYTES_PER_PARAM * (wl.total // world),
                      "launch_ms": kernel_avg_ms},
         "gpu_launches": int(launches),
-        "gpu_launches_note": f"update and fence kernels launched inside the timed regions of the {len(blocks)} blocks "
-                             f"({launches // max(len(blocks) * args.steps, 1)} per step)",
+        "gpu_launches_note": f"update and fence kernels launched inside the timed regions of the {len(headline_blocks)} blocks "
+                             f"({launches // max(len(headline_blocks) * args.steps, 1)} per step)",
         "clocks": clocks,
     }
     if clocks and clocks.get("sm_mhz"):
@@ -656,14 +760,19 @@ def run_ours(args):
         floor_ms = ingress / (peak * 1e9) * 1e3
         line["exchange_roofline"] = {"bound": "nvlink ingress per GPU", "bytes_in_per_gpu": ingress, "peak": peak,
                                      "peak_source": src, "unit": "GB/s", "floor_ms": floor_ms,
-                                     "achieved": ingress / (ms_per_step * 1e-3) / 1e9,
-                                     "frac": floor_ms / ms_per_step,
+                                     "achieved": ingress / (zero1_ms_per_step * 1e-3) / 1e9,
+                                     "frac": floor_ms / zero1_ms_per_step,
                                      "strong_scaling_efficiency_bound": (wl.total / (floor_ms * 1e-3)) / world,
-                                     "note": "strong scaling of the whole step is capped by this floor; the update "
-                                             "kernel itself scales with 1/N (update_only); "
+                                     "note": "for the step that exchanges every parameter (all_exchanged when the headline "
+                                             "is the replicated-tail sharding): its strong scaling is capped by "
+                                             "this floor; the update kernel itself scales with 1/N (update_only); "
                                              "strong_scaling_efficiency_bound is params/s per GPU at the floor"}
         if nvlink is not None:
             line["exchange_roofline"]["probe"] = nvlink
+    if tail is not None:
+        line["replicated_tail"] = tail
+    if all_exchanged is not None:
+        line["all_exchanged"] = all_exchanged
     if dp_step is not None:
         line["data_parallel_step"] = dp_step
     if bf16_exchange is not None:
@@ -932,6 +1041,9 @@ def main():
     ap.add_argument("--skip-e2e", action="store_true", help="profiling runs: device-resident timing only")
     ap.add_argument("--skip-muon", action="store_true", help="Adam only")
     ap.add_argument("--skip-muon-f32", action="store_true", help="skip the (slow) f32 Newton-Schulz timing")
+    ap.add_argument("--replicated-fraction", type=float, default=-1.0,
+                    help="N > 1: share of the arena every rank updates itself instead of receiving it "
+                         "(-1 = from the measured HBM and NVLink rates, 0 = off)")
     ap.add_argument("--only-muon", action="store_true", help="profiling runs: Muon bf16 only")
     ap.add_argument("--no-library-baseline", action="store_true",
                     help="skip timing the Newton-Schulz products through torch.bmm beside the Muon numbers")

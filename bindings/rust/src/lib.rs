@@ -62,6 +62,7 @@ pub mod ffi {
         pub fn vb_engine_synchronize(engine: *mut vb_engine) -> c_int;
         pub fn vb_engine_synchronize_deadline(engine: *mut vb_engine, timeout_ms: f64) -> c_int;
         pub fn vb_engine_set_wait_limit_ms(engine: *mut vb_engine, milliseconds: u32) -> c_int;
+        pub fn vb_engine_set_replicated_fraction(engine: *mut vb_engine, fraction: f64) -> c_int;
         pub fn vb_adam_create(
             engine: *mut vb_engine, n_tensors: i64, sizes: *const i64, lr: f32, beta1: f32, beta2: f32,
             eps: f32, weight_decay: f32, out: *mut *mut vb_optimizer,

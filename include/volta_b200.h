@@ -110,6 +110,22 @@ int vb_plan_layout(int64_t n_tensors, const int64_t *sizes, int world_size, int 
                    int64_t *offsets_out, int64_t *arena_elements, int64_t *shard_begin,
                    int64_t *shard_end, int64_t *n_chunks, int64_t chunk_capacity,
                    int64_t *chunk_tensor, int64_t *chunk_offset, int64_t *chunk_len);
+/* The same plan with a replicated tail (see vb_engine_set_replicated_fraction): the positions
+ * [0, *tail_begin) are cut into the ranks' slices, [*tail_begin, *arena_elements) is updated by
+ * every rank; chunk_local_only[c] = 1 marks the chunks of the tail, which the table interleaves
+ * with those of the slice.  replicated_fraction = 0 gives vb_plan_layout's plan. */
+int vb_plan_layout_replicated(int64_t n_tensors, const int64_t *sizes, int world_size, int rank, int sm_count,
+                              double replicated_fraction, int64_t *offsets_out, int64_t *arena_elements,
+                              int64_t *shard_begin, int64_t *shard_end, int64_t *tail_begin,
+                              int64_t *n_chunks, int64_t chunk_capacity, int64_t *chunk_tensor,
+                              int64_t *chunk_offset, int64_t *chunk_len, int32_t *chunk_local_only);
+/* The replicated fraction at which a sharded step's HBM time and NVLink time are equal, from
+ * the bytes one element's update moves through HBM (Adam 28, SGD with momentum 20, plain SGD
+ * 12), the HBM rate of the update kernel and the NVLink rate per direction of the fused exchange
+ * with both directions busy (GB/s; measure them, e.g. from a step with VB_STEP_NO_EXCHANGE and a
+ * whole step without replication).  0 when exchanging everything is not the bottleneck. */
+int vb_plan_replicated_fraction(double bytes_per_element, int world_size, double hbm_gb_per_s,
+                                double link_gb_per_s, double *fraction);
 
 /* Pure host planning, no CUDA call: which rank owns each Muon tensor.  Whole tensors are
  * taken in order of decreasing estimated cost per step under the arithmetic `ns_mode` really
@@ -160,6 +176,19 @@ int vb_engine_synchronize_deadline(vb_engine *engine, double timeout_ms);
  * No counterpart in the reference (single process; its own waits are bounded by
  * sync_checked(), src/gpu/context.rs:448-505). */
 int vb_engine_set_wait_limit_ms(vb_engine *engine, uint32_t milliseconds);
+/* Sharded engines, Adam and SGD optimizers created after the call: the last `fraction` of the
+ * arena is not sharded.  Every rank keeps optimizer state for that tail and updates it itself in
+ * the same launch that updates (and sends to the peers) its slice of the rest, so that part of
+ * the parameters never crosses NVLink: when the exchange bounds the step (it does from two B200s
+ * on: 4 B/param into every GPU against 28 B/param of HBM traffic shared by N GPUs) the launch
+ * overlaps link-bound and HBM-bound work, see vb_plan_replicated_fraction.  The price: state
+ * memory for the tail on every rank, and every rank needs the complete, identical gradients of
+ * the tail (the default when gradients were all-reduced; with VB_STEP_REDUCE_GRADS every rank
+ * sums the tail's gradients itself, which multiplies that NVLink traffic).  Results are
+ * unchanged: all ranks run the same arithmetic on the same inputs.  All ranks must set the same
+ * fraction (vb_optimizer_plan_fingerprint covers it).  Default 0: plain ZeRO-1 slices.  No
+ * counterpart in the reference (single device). */
+int vb_engine_set_replicated_fraction(vb_engine *engine, double fraction);
 /* The engine's cudaStream_t, for callers that enqueue their own producers of gradients. */
 int vb_engine_stream(vb_engine *engine, void **cuda_stream);
 /* Kernels launched by this engine since creation (bookkeeping for benchmarks). */
@@ -293,6 +322,9 @@ int vb_optimizer_upload_arena_range(vb_optimizer *opt, int which, const float *h
 int vb_optimizer_download_arena_range(vb_optimizer *opt, int which, float *host, int64_t begin, int64_t n);
 /* The slice of the arena whose state this rank owns (Adam/SGD; the whole arena for Muon). */
 int vb_optimizer_owned_range(vb_optimizer *opt, int64_t *begin, int64_t *end);
+/* The tail of the arena every rank updates itself (empty, begin == end == arena size, unless
+ * vb_engine_set_replicated_fraction was set when the optimizer was created). */
+int vb_optimizer_replicated_range(vb_optimizer *opt, int64_t *begin, int64_t *end);
 
 /* Presence of a gradient: step() skips tensors whose gradient is absent
  * (src/nn/optim/adam.rs:81-84, sgd.rs:75-78, muon.rs:110). */
@@ -392,7 +424,10 @@ int vb_optimizer_open_peers_bf16(vb_optimizer *opt, const void *handles, int n_h
 
 /* which: 0 = first state (Adam m, SGD velocity, Muon velocity), 1 = Adam v.
  * On a sharded engine only the owning rank holds a tensor's state: export returns the
- * owned elements and zeros elsewhere, and reports the owned range. */
+ * owned elements and zeros elsewhere, and reports the owned range.  Every element is reported
+ * by exactly one rank: the state of a replicated tail (vb_engine_set_replicated_fraction),
+ * identical on all ranks, by the last rank, whose slice the tail follows.  Import takes the whole
+ * tensor and keeps every element whose state the rank holds, the tail's on every rank. */
 int vb_optimizer_export_state(vb_optimizer *opt, int64_t tensor, int which, float *host, int64_t n,
                               int64_t *owned_begin, int64_t *owned_end);
 int vb_optimizer_import_state(vb_optimizer *opt, int64_t tensor, int which, const float *host,

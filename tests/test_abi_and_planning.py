@@ -27,7 +27,7 @@ def test_library_exports_every_declared_symbol():
         assert hasattr(lib, name), f"{name} is declared in include/volta_b200.h but not exported"
     bound = set(_lib.SIGNATURES) | set(_lib.OTHER_SYMBOLS)
     assert set(names) == bound, set(names) ^ bound
-    assert lib.vb_abi_version() == 1001
+    assert lib.vb_abi_version() == 1002
 
 
 def test_python_constants_match_the_header():
@@ -115,6 +115,85 @@ def test_plan_covers_every_element_exactly_once(world):
     assert cover.sum() == total and cover.max() == 1
     for o, s in zip(offsets, sizes):
         assert np.all(cover[o:o + s] == 1)
+
+
+def plan_replicated(sizes, world, rank, fraction, sm=148):
+    from volta_b200 import _lib
+    n = len(sizes)
+    arr = (C.c_int64 * max(n, 1))(*sizes)
+    offs = (C.c_int64 * max(n, 1))()
+    arena, lo, hi, tail, nch = C.c_int64(), C.c_int64(), C.c_int64(), C.c_int64(), C.c_int64()
+    _lib.call("vb_plan_layout_replicated", n, arr, world, rank, sm, fraction, offs, C.byref(arena), C.byref(lo),
+              C.byref(hi), C.byref(tail), C.byref(nch), 0, None, None, None, None)
+    k = nch.value
+    ct, co, cl = (C.c_int64 * max(k, 1))(), (C.c_int64 * max(k, 1))(), (C.c_int64 * max(k, 1))()
+    local = (C.c_int32 * max(k, 1))()
+    _lib.call("vb_plan_layout_replicated", n, arr, world, rank, sm, fraction, offs, C.byref(arena), C.byref(lo),
+              C.byref(hi), C.byref(tail), C.byref(nch), k, ct, co, cl, local)
+    return dict(offsets=[offs[i] for i in range(n)], arena=arena.value, lo=lo.value, hi=hi.value, tail=tail.value,
+                chunks=[(ct[i], co[i], cl[i], local[i]) for i in range(k)])
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("fraction", [0.0, 0.2, 0.55, 1.0])
+def test_plan_with_a_replicated_tail(world, fraction):
+    """[0, tail) is cut into the ranks' slices, [tail, arena) belongs to every rank; a rank's chunks
+    cover its slice and the tail exactly once, flagged by part and mixed in proportion."""
+    rng = np.random.default_rng(world)
+    sizes = [int(s) for s in np.floor(np.exp2(18 * rng.random(150))).astype(np.int64)] + [1 << 21, 0, 1, 33]
+    plain = [plan(sizes, world, r) for r in range(world)]
+    cover_slices = None
+    prev_hi = 0
+    for rank in range(world):
+        p = plan_replicated(sizes, world, rank, fraction)
+        if fraction == 0.0:
+            assert p["tail"] == p["arena"] and (p["lo"], p["hi"]) == (plain[rank]["lo"], plain[rank]["hi"])
+            assert [c[:3] for c in p["chunks"]] == plain[rank]["chunks"] and not any(c[3] for c in p["chunks"])
+        if cover_slices is None:
+            cover_slices = np.zeros(p["arena"], np.int32)
+            tail = p["tail"]
+            offsets = p["offsets"]
+            assert tail % (256 * world) == 0 and 0 <= tail <= p["arena"]
+            assert abs((p["arena"] - tail) - fraction * p["arena"]) <= 256 * world
+        assert p["tail"] == tail and p["offsets"] == offsets
+        assert p["lo"] == prev_hi and (p["hi"] - p["lo"]) * world == tail
+        prev_hi = p["hi"]
+        cover_tail = np.zeros(p["arena"], np.int32)
+        for t, off, ln, local in p["chunks"]:
+            assert ln > 0 and off + ln <= sizes[t]
+            a = offsets[t] + off
+            assert a % 4 == 0
+            if local:
+                assert tail <= a and a + ln <= p["arena"]
+                cover_tail[a:a + ln] += 1
+            else:
+                assert p["lo"] <= a and a + ln <= p["hi"]
+                cover_slices[a:a + ln] += 1
+        for o, s in zip(offsets, sizes):  # every rank covers the whole tail once
+            assert np.all(cover_tail[max(o, tail):max(o + s, tail)] == 1)
+        assert cover_tail[:tail].sum() == 0
+        flags = np.array([c[3] for c in p["chunks"]], np.int64)
+        if 0 < flags.sum() < flags.size:  # the two kinds are spread evenly over the table
+            share = flags.mean()
+            running = np.cumsum(flags) - share * np.arange(1, flags.size + 1)
+            assert np.abs(running).max() <= 2.0
+    assert prev_hi == tail
+    for o, s in zip(offsets, sizes):
+        assert np.all(cover_slices[o:min(o + s, max(o, tail))] == 1)
+    assert cover_slices[tail:].sum() == 0 and cover_slices.max() <= 1
+
+
+def test_replicated_fraction_balances_hbm_and_link_time():
+    from volta_b200 import plan_replicated_fraction
+    assert plan_replicated_fraction(28, 1, 6700, 630) == 0.0
+    for world in (2, 4, 8):
+        f = plan_replicated_fraction(28, world, 6700, 630)
+        assert 0.0 < f < 1.0
+        hbm = 28 / 6700 * ((1 - f) / world + f)
+        link = 4 * (world - 1) / world / 630 * (1 - f)
+        assert abs(hbm - link) < 1e-9 * hbm + 1e-15
+    # a link as fast as needed: nothing to replicate
+    assert plan_replicated_fraction(28, 2, 1000, 1e6) == 0.0
 
 
 def test_plan_chunk_lengths_scale_with_problem_size():

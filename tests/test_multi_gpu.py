@@ -35,6 +35,9 @@ def _worker(rank, world, shared, kind):
     assert (eng.rank, eng.world_size) == (rank, world)
     peer = kind.endswith("_peer")  # exchange fused into the update kernel (NVLink peer stores)
     kind = kind.replace("_peer", "")
+    if kind.endswith("_tail"):     # part of the arena is updated by every rank itself and never exchanged
+        eng.set_replicated_fraction(0.45)
+        kind = kind.replace("_tail", "")
     if kind == "adam":
         wl = workloads.c5_ragged_adam(n_tensors=96, max_log2=16, seed=11)
     elif kind == "sgd":
@@ -68,13 +71,16 @@ def _worker(rank, world, shared, kind):
         owned += hi - lo
     shared[f"params{rank}"] = [t.data.copy() for t in tensors]
     shared[f"owned{rank}"] = owned
+    shared[f"ranges{rank}"] = (opt.owned_range(), opt.replicated_range()) if kind in ("adam", "sgd") else None
     opt.close()
     eng.close()
 
 
 @pytest.mark.parametrize("world,kind", [(2, k) for k in ("adam", "sgd", "adam_peer", "sgd_peer", "muon_f32", "muon_bf16",
                                                          "muon_f32_peer", "muon_bf16_peer")] +
-                         [(4, k) for k in ("adam", "adam_peer", "sgd_peer", "muon_f32_peer", "muon_bf16_peer")])
+                         [(2, k) for k in ("adam_tail", "adam_tail_peer", "sgd_tail_peer")] +
+                         [(4, k) for k in ("adam", "adam_peer", "sgd_peer", "muon_f32_peer", "muon_bf16_peer",
+                                           "adam_tail_peer")])
 def test_sharded_step_matches_oracle(oracle, world, kind):
     if _gpu_count() < world:
         pytest.skip(f"needs {world} GPUs")
@@ -92,6 +98,12 @@ def test_sharded_step_matches_oracle(oracle, world, kind):
             assert p.exitcode == 0
         res = dict(shared)
     kind = kind.replace("_peer", "")
+    tail = kind.endswith("_tail")
+    kind = kind.replace("_tail", "")
+    if kind in ("adam", "sgd"):
+        (lo0, hi0), (t_lo, t_hi) = res["ranges0"]
+        assert (t_hi - t_lo > 0) == tail and all(res[f"ranges{r}"][1] == (t_lo, t_hi) for r in range(world))
+        assert (hi0 - lo0) * world == t_lo  # the slices cut up what the tail leaves
     if kind == "adam":
         wl = workloads.c5_ragged_adam(n_tensors=96, max_log2=16, seed=11)
     elif kind == "sgd":
@@ -121,6 +133,100 @@ def test_sharded_step_matches_oracle(oracle, world, kind):
     # state is partitioned: the ranks' owned element counts add up to the whole
     owned = [res[f"owned{rank}"] for rank in range(world)]
     assert sum(owned) == wl.total and min(owned) > 0
+
+
+def _worker_tail_resume(rank, world, shared):
+    """Two steps, export the state, a new optimizer with the merged state, a third step on both."""
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import time
+
+    import workloads
+    from volta_b200 import Adam, Engine, Tensor
+    eng = Engine(rank)
+    if rank == 0:
+        shared["id"] = Engine.unique_id()
+    while "id" not in shared:
+        time.sleep(0.01)
+    eng.init_comm(shared["id"], rank, world)
+    eng.set_replicated_fraction(0.45)
+    wl = workloads.c5_ragged_adam(n_tensors=96, max_log2=16, seed=11)
+    h = wl.hyper
+
+    def gather(key, value):
+        shared[f"{key}{rank}"] = value
+        while any(f"{key}{r}" not in shared for r in range(world)):
+            time.sleep(0.01)
+        return [shared[f"{key}{r}"] for r in range(world)]
+
+    def make():
+        tensors = [Tensor(p, p.shape) for p in wl.make_params()]
+        return tensors, Adam(tensors, h["lr"], h["betas"], h["eps"], h["weight_decay"], engine=eng)
+
+    def step(tensors, opt, s):
+        opt.zero_grad()
+        for t, g in zip(tensors, wl.make_grads(s)):
+            t.grad = g
+        opt.step()
+
+    tensors, opt = make()
+    opt.open_peers(gather("ipc_a", opt.ipc_handle()))
+    for s in (1, 2):
+        step(tensors, opt, s)
+    # every element of the state is reported by exactly one rank
+    mine = [[(opt.state(i, w), opt.state_owned_range(i, w)) for i in range(len(tensors))] for w in (0, 1)]
+    everyone = gather("state", mine)
+    tensors2, opt2 = make()
+    opt2.open_peers(gather("ipc_b", opt2.ipc_handle()))
+    covered = 0
+    for w in (0, 1):
+        for i in range(len(tensors)):
+            full = np.zeros(tensors[i].data.size, np.float32)
+            for r in range(world):
+                arr, (lo, hi) = everyone[r][w][i]
+                assert not full[lo:hi].any()
+                full[lo:hi] = arr[lo:hi]
+                covered += (hi - lo) if w == 0 else 0
+            opt2.load_state(i, w, full)
+    assert covered == wl.total
+    for t2, t1 in zip(tensors2, tensors):
+        t2.data = t1.data.copy()
+    opt2.t = opt.t
+    step(tensors, opt, 3)
+    step(tensors2, opt2, 3)
+    shared[f"a{rank}"] = [t.data.copy() for t in tensors]
+    shared[f"b{rank}"] = [t.data.copy() for t in tensors2]
+    gather("done", 1)
+    opt.close()
+    opt2.close()
+    eng.close()
+
+
+def test_state_round_trip_with_a_replicated_tail(oracle):
+    if _gpu_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+
+    import workloads
+    ctx = mp.get_context("spawn")
+    with ctx.Manager() as mgr:
+        shared = mgr.dict()
+        procs = [ctx.Process(target=_worker_tail_resume, args=(r, 2, shared)) for r in range(2)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(300)
+            assert p.exitcode == 0
+        res = dict(shared)
+    wl = workloads.c5_ragged_adam(n_tensors=96, max_log2=16, seed=11)
+    h = wl.hyper
+    ref = wl.make_params()
+    o = oracle.Adam(ref, h["lr"], h["betas"], h["eps"], h["weight_decay"])
+    for s in (1, 2, 3):
+        o.step(wl.make_grads(s))
+    for i, r in enumerate(ref):
+        for key in ("a0", "a1", "b0", "b1"):
+            assert np.array_equal(res[key][i].view(np.uint32), r.view(np.uint32)), (key, i)
 
 
 def _bf16_rne(x):

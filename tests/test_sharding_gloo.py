@@ -56,6 +56,42 @@ def _adam_worker(rank, world, port, ret):
         dist.destroy_process_group()
 
 
+def _adam_tail_worker(rank, world, port, ret, fraction):
+    """ZeRO-1 slices of [0, tail) plus a tail every rank updates itself from its own gradients."""
+    sys.path.insert(0, ROOT)
+    import oracle
+    import workloads
+    from volta_b200 import _lib
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        wl = workloads.c5_ragged_adam(n_tensors=64, max_log2=14, seed=7)
+        h = wl.hyper
+        n = len(wl.sizes)
+        arr = (C.c_int64 * n)(*wl.sizes)
+        offs = (C.c_int64 * n)()
+        arena, lo, hi, tail, nch = C.c_int64(), C.c_int64(), C.c_int64(), C.c_int64(), C.c_int64()
+        _lib.call("vb_plan_layout_replicated", n, arr, world, rank, 148, fraction, offs, C.byref(arena), C.byref(lo),
+                  C.byref(hi), C.byref(tail), C.byref(nch), 0, None, None, None, None)
+        offsets, arena, lo, hi, tail = [offs[i] for i in range(n)], arena.value, lo.value, hi.value, tail.value
+        assert 0 < tail < arena
+        theta = np.zeros(arena, np.float32)
+        for o, p in zip(offsets, wl.make_params()):
+            theta[o:o + p.size] = p.reshape(-1)
+        mine, shared = theta[lo:hi], theta[tail:]
+        opt = oracle.Adam([mine, shared], h["lr"], h["betas"], h["eps"], h["weight_decay"])
+        for s in (1, 2, 3):
+            g = np.zeros(arena, np.float32)
+            for o, gi in zip(offsets, wl.make_grads(s)):
+                g[o:o + gi.size] = gi.reshape(-1)
+            opt.step([np.ascontiguousarray(g[lo:hi]), np.ascontiguousarray(g[tail:])])
+            t = torch.from_numpy(theta)
+            dist.all_gather_into_tensor(t[:tail], t[lo:hi].clone())  # only the sliced part is exchanged
+        ret[rank] = theta.copy()
+    finally:
+        dist.destroy_process_group()
+
+
 def _free_port():
     import socket
     s = socket.socket()
@@ -83,6 +119,22 @@ def test_zero1_adam_two_ranks_matches_unsharded():
     import oracle
     import workloads
     res = _spawn(_adam_worker, 2)
+    wl = workloads.c5_ragged_adam(n_tensors=64, max_log2=14, seed=7)
+    h = wl.hyper
+    params = wl.make_params()
+    opt = oracle.Adam(params, h["lr"], h["betas"], h["eps"], h["weight_decay"])
+    for s in (1, 2, 3):
+        opt.step(wl.make_grads(s))
+    offsets, arena, _, _ = _plan(wl.sizes, 2, 0)
+    assert np.array_equal(res[0], res[1])
+    for o, p in zip(offsets, params):
+        assert np.array_equal(res[0][o:o + p.size].view(np.uint32), p.reshape(-1).view(np.uint32))
+
+
+def test_adam_with_a_replicated_tail_two_ranks_matches_unsharded():
+    import oracle
+    import workloads
+    res = _spawn(_adam_tail_worker, 2, 0.4)
     wl = workloads.c5_ragged_adam(n_tensors=64, max_log2=14, seed=7)
     h = wl.hyper
     params = wl.make_params()

@@ -54,6 +54,9 @@ SIGNATURES = {
     "vb_device_count": [C.POINTER(C.c_int)],
     "vb_plan_layout": [_i64, _i64p, C.c_int, C.c_int, C.c_int, _i64p, _i64p, _i64p, _i64p, _i64p, _i64,
                        _i64p, _i64p, _i64p],
+    "vb_plan_layout_replicated": [_i64, _i64p, C.c_int, C.c_int, C.c_int, C.c_double, _i64p, _i64p, _i64p, _i64p, _i64p,
+                                  _i64p, _i64, _i64p, _i64p, _i64p, C.POINTER(C.c_int32)],
+    "vb_plan_replicated_fraction": [C.c_double, C.c_int, C.c_double, C.c_double, C.POINTER(C.c_double)],
     "vb_plan_muon_owners": [_i64, _i64p, _i64p, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int32),
                             C.POINTER(C.c_double)],
     "vb_plan_fingerprint": [C.c_int, _i64, _i64p, _i64p, _f32p, C.c_int, C.POINTER(C.c_int32), C.c_int, C.c_int,
@@ -62,6 +65,7 @@ SIGNATURES = {
     "vb_optimizer_plan_fingerprint": [_vp, C.POINTER(C.c_uint64)],
     "vb_engine_synchronize_deadline": [_vp, C.c_double],
     "vb_engine_set_wait_limit_ms": [_vp, C.c_uint32],
+    "vb_engine_set_replicated_fraction": [_vp, C.c_double],
     "vb_debug_muon_withhold_loads": [_vp, C.c_uint32],
     "vb_debug_fence_wait_expiry": [_vp, C.c_uint32, C.c_int, C.POINTER(C.c_int)],
     "vb_engine_create": [C.c_int, _vpp],
@@ -98,6 +102,7 @@ SIGNATURES = {
     "vb_optimizer_upload_arena_range": [_vp, C.c_int, _vp, _i64, _i64],
     "vb_optimizer_download_arena_range": [_vp, C.c_int, _vp, _i64, _i64],
     "vb_optimizer_owned_range": [_vp, _i64p, _i64p],
+    "vb_optimizer_replicated_range": [_vp, _i64p, _i64p],
     "vb_optimizer_set_grad_present": [_vp, _i64, C.c_int],
     "vb_optimizer_step": [_vp],
     "vb_optimizer_step_ex": [_vp, C.c_uint32],

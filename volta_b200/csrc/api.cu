@@ -109,11 +109,18 @@ static int set_device(const vb_engine *e)
 struct Layout {
     std::vector<int64_t> offsets;
     int64_t total = 0, arena = 0, shard_begin = 0, shard_end = 0, chunk_len = 0;
+    int64_t tail_begin = 0;  // [tail_begin, arena) is updated by every rank itself and never exchanged
     std::vector<ChunkDesc> chunks;
+    std::vector<uint8_t> chunk_local;  // per chunk: 1 = part of the replicated tail
 };
 
+// Sharded engines: the arena positions [0, tail_begin) are cut into one slice per rank (updated by
+// its owner, exchanged afterwards); with replicated_fraction > 0 the last part of the arena,
+// [tail_begin, arena), is instead updated by every rank from its own copy of the gradients and
+// never crosses NVLink.  The chunks of the two parts are interleaved in the table so that a launch
+// mixes link-bound and HBM-bound work all along.
 static void plan_layout(int64_t n_tensors, const int64_t *sizes, int world, int rank, int sm_count,
-                        bool shard, Layout *L)
+                        bool shard, double replicated_fraction, Layout *L)
 {
     L->offsets.resize((size_t)n_tensors);
     int64_t off = 0;
@@ -124,33 +131,57 @@ static void plan_layout(int64_t n_tensors, const int64_t *sizes, int world, int 
         L->total += sizes[i];
     }
     L->arena = round_up(std::max<int64_t>(off, 1), kShardAlign * world);
+    L->tail_begin = L->arena;
     if (shard) {
-        const int64_t per = L->arena / world;
+        if (world > 1 && replicated_fraction > 0.0) {
+            const double keep = replicated_fraction >= 1.0 ? 0.0 : 1.0 - replicated_fraction;
+            L->tail_begin = std::min(L->arena, round_up((int64_t)((double)L->arena * keep), kShardAlign * world));
+        }
+        const int64_t per = L->tail_begin / world;
         L->shard_begin = per * rank;
         L->shard_end = L->shard_begin + per;
     } else {
         L->shard_begin = 0;
         L->shard_end = L->arena;
     }
+    // the two owned ranges of this rank: its slice and the tail
+    const int64_t range_lo[2] = {L->shard_begin, L->tail_begin};
+    const int64_t range_hi[2] = {L->shard_end, L->arena};
     int64_t owned = 0;
-    for (int64_t i = 0; i < n_tensors; ++i) {
-        const int64_t lo = std::max(L->offsets[(size_t)i], L->shard_begin);
-        const int64_t hi = std::min(L->offsets[(size_t)i] + sizes[i], L->shard_end);
-        if (hi > lo) owned += hi - lo;
-    }
-    L->chunk_len = pick_chunk_len(owned, sm_count);
-    L->chunks.clear();
-    for (int64_t i = 0; i < n_tensors; ++i) {
-        const int64_t o = L->offsets[(size_t)i];
-        const int64_t lo = std::max(o, L->shard_begin);
-        const int64_t hi = std::min(o + sizes[i], L->shard_end);
-        for (int64_t b = lo; b < hi; b += L->chunk_len) {
-            ChunkDesc c;
-            c.offset = b - o;
-            c.tensor = (uint32_t)i;
-            c.len = (uint32_t)std::min(L->chunk_len, hi - b);
-            L->chunks.push_back(c);
+    for (int part = 0; part < 2; ++part)
+        for (int64_t i = 0; i < n_tensors; ++i) {
+            const int64_t lo = std::max(L->offsets[(size_t)i], range_lo[part]);
+            const int64_t hi = std::min(L->offsets[(size_t)i] + sizes[i], range_hi[part]);
+            if (hi > lo) owned += hi - lo;
         }
+    L->chunk_len = pick_chunk_len(owned, sm_count);
+    std::vector<ChunkDesc> part_chunks[2];
+    for (int part = 0; part < 2; ++part)
+        for (int64_t i = 0; i < n_tensors; ++i) {
+            const int64_t o = L->offsets[(size_t)i];
+            const int64_t lo = std::max(o, range_lo[part]);
+            const int64_t hi = std::min(o + sizes[i], range_hi[part]);
+            for (int64_t b = lo; b < hi; b += L->chunk_len) {
+                ChunkDesc c;
+                c.offset = b - o;
+                c.tensor = (uint32_t)i;
+                c.len = (uint32_t)std::min(L->chunk_len, hi - b);
+                part_chunks[part].push_back(c);
+            }
+        }
+    // merge in proportion (each part keeps its order): position k of the table is a tail chunk
+    // whenever the tail is behind its share of the first k chunks
+    const size_t n_s = part_chunks[0].size(), n_t = part_chunks[1].size();
+    L->chunks.clear();
+    L->chunk_local.clear();
+    L->chunks.reserve(n_s + n_t);
+    L->chunk_local.reserve(n_s + n_t);
+    size_t i_s = 0, i_t = 0;
+    while (i_s < n_s || i_t < n_t) {
+        const bool take_tail = i_s == n_s || (i_t < n_t && (i_t + 1) * n_s <= (i_s + 1) * n_t);
+        if (take_tail) L->chunks.push_back(part_chunks[1][i_t++]);
+        else L->chunks.push_back(part_chunks[0][i_s++]);
+        L->chunk_local.push_back(take_tail ? 1 : 0);
     }
 }
 
@@ -159,12 +190,14 @@ static int build_arena(vb_optimizer *opt, int n_state_buffers, bool shard_states
 {
     vb_engine *e = opt->eng;
     VB_TRY(set_device(e));
-    plan_layout(opt->n_tensors, opt->sizes.data(), e->world, e->rank, e->sm_count, shard_states, L);
+    plan_layout(opt->n_tensors, opt->sizes.data(), e->world, e->rank, e->sm_count, shard_states,
+                shard_states ? e->replicated_fraction : 0.0, L);
     opt->offsets = L->offsets;
     opt->total = L->total;
     opt->arena = L->arena;
     opt->shard_begin = L->shard_begin;
     opt->shard_end = L->shard_end;
+    opt->tail_begin = L->tail_begin;
     // each arena a peer can map ends with the flag block of the exchange fence (vb_internal.h)
     const size_t arena_bytes = (size_t)opt->arena * sizeof(float) + kSyncWords * sizeof(uint32_t);
     VB_CUDA(cudaMalloc(&opt->d_param, arena_bytes));
@@ -174,8 +207,9 @@ static int build_arena(vb_optimizer *opt, int n_state_buffers, bool shard_states
     VB_CUDA(cudaHostAlloc((void **)&opt->h_fence_error, sizeof(uint32_t), cudaHostAllocMapped));
     *opt->h_fence_error = 0;
     VB_CUDA(cudaHostGetDevicePointer((void **)&opt->d_fence_error, opt->h_fence_error, 0));
-    opt->state_elems = opt->shard_end - opt->shard_begin;
-    const size_t state_bytes = (size_t)opt->state_elems * sizeof(float);
+    // state: this rank's slice, then the replicated tail
+    opt->state_elems = (opt->shard_end - opt->shard_begin) + (opt->arena - opt->tail_begin);
+    const size_t state_bytes = (size_t)std::max<int64_t>(opt->state_elems, 1) * sizeof(float);
     if (n_state_buffers >= 1) {  // Storage::new_zeros, adam.rs:26-47 / sgd.rs:30-41
         VB_CUDA(cudaMalloc(&opt->d_s1, state_bytes));
         VB_CUDA(cudaMemsetAsync(opt->d_s1, 0, state_bytes, e->stream));
@@ -201,12 +235,12 @@ static int build_chunk_table(vb_optimizer *opt, const Layout &L)
         FatChunk &f = fat[c];
         f.p = opt->d_param + pos;
         f.g = opt->d_grad + pos;
-        // state arrays cover only this rank's slice [shard_begin, shard_end)
-        f.s1 = opt->d_s1 ? opt->d_s1 + (pos - opt->shard_begin) : nullptr;
-        f.s2 = opt->d_s2 ? opt->d_s2 + (pos - opt->shard_begin) : nullptr;
+        // state arrays cover only what this rank updates: its slice, then the replicated tail
+        f.s1 = opt->d_s1 ? opt->d_s1 + opt->state_pos(pos) : nullptr;
+        f.s2 = opt->d_s2 ? opt->d_s2 + opt->state_pos(pos) : nullptr;
         f.len = ch.len;
         f.tensor = ch.tensor;
-        f.pad = 0;
+        f.local_only = L.chunk_local[c];
     }
     opt->n_chunks = (int64_t)fat.size();
     opt->chunk_pos.resize(L.chunks.size());
@@ -478,7 +512,7 @@ int fence_check_error(vb_optimizer *opt)
 
 extern "C" {
 
-int vb_abi_version(void) { return 1001; }
+int vb_abi_version(void) { return 1002; }
 
 const char *vb_last_error(void) { return g_err; }
 
@@ -495,20 +529,34 @@ int vb_plan_layout(int64_t n_tensors, const int64_t *sizes, int world_size, int 
                    int64_t *n_chunks, int64_t chunk_capacity, int64_t *chunk_tensor, int64_t *chunk_offset,
                    int64_t *chunk_len)
 {
+    return vb_plan_layout_replicated(n_tensors, sizes, world_size, rank, sm_count, 0.0, offsets_out, arena_elements,
+                                     shard_begin, shard_end, nullptr, n_chunks, chunk_capacity, chunk_tensor,
+                                     chunk_offset, chunk_len, nullptr);
+}
+
+int vb_plan_layout_replicated(int64_t n_tensors, const int64_t *sizes, int world_size, int rank, int sm_count,
+                              double replicated_fraction, int64_t *offsets_out, int64_t *arena_elements,
+                              int64_t *shard_begin, int64_t *shard_end, int64_t *tail_begin, int64_t *n_chunks,
+                              int64_t chunk_capacity, int64_t *chunk_tensor, int64_t *chunk_offset,
+                              int64_t *chunk_len, int32_t *chunk_local_only)
+{
     VB_API_BEGIN
     VB_TRY(validate_sizes(n_tensors, sizes));
     if (world_size < 1 || rank < 0 || rank >= world_size || sm_count < 1)
         return fail(VB_ERR_INVALID_ARG, "rank %d / world_size %d / sm_count %d is not valid", rank, world_size,
                     sm_count);
+    if (!(replicated_fraction >= 0.0 && replicated_fraction <= 1.0))
+        return fail(VB_ERR_INVALID_ARG, "the replicated fraction must be in [0, 1]");
     Layout L;
-    plan_layout(n_tensors, sizes, world_size, rank, sm_count, true, &L);
+    plan_layout(n_tensors, sizes, world_size, rank, sm_count, true, replicated_fraction, &L);
+    if (tail_begin) *tail_begin = L.tail_begin;
     if (offsets_out)
         for (int64_t i = 0; i < n_tensors; ++i) offsets_out[i] = L.offsets[(size_t)i];
     if (arena_elements) *arena_elements = L.arena;
     if (shard_begin) *shard_begin = L.shard_begin;
     if (shard_end) *shard_end = L.shard_end;
     if (n_chunks) *n_chunks = (int64_t)L.chunks.size();
-    if (chunk_tensor || chunk_offset || chunk_len) {
+    if (chunk_tensor || chunk_offset || chunk_len || chunk_local_only) {
         if (chunk_capacity < (int64_t)L.chunks.size())
             return fail(VB_ERR_INVALID_ARG, "chunk_capacity %lld is less than the %lld chunks of the plan",
                         (long long)chunk_capacity, (long long)L.chunks.size());
@@ -516,6 +564,7 @@ int vb_plan_layout(int64_t n_tensors, const int64_t *sizes, int world_size, int 
             if (chunk_tensor) chunk_tensor[c] = L.chunks[c].tensor;
             if (chunk_offset) chunk_offset[c] = L.chunks[c].offset;
             if (chunk_len) chunk_len[c] = L.chunks[c].len;
+            if (chunk_local_only) chunk_local_only[c] = L.chunk_local[c];
         }
     }
     return VB_OK;
@@ -575,10 +624,13 @@ int vb_optimizer_plan_fingerprint(vb_optimizer *opt, uint64_t *fingerprint)
     VB_TRY(check_opt(opt));
     if (!fingerprint) return fail(VB_ERR_INVALID_ARG, "fingerprint is null");
     const float hyper[6] = {opt->lr, opt->beta1, opt->beta2, opt->eps, opt->weight_decay, opt->momentum};
-    const int32_t ints[4] = {opt->nesterov, opt->ns_steps, opt->ns_mode, opt->d_param_bf16 ? 1 : 0};
+    // a replicated tail is part of the plan: ranks that cut the arena differently must not step together
+    const bool tail = opt->kind != KIND_MUON && opt->tail_begin < opt->arena;
+    const int32_t ints[6] = {opt->nesterov, opt->ns_steps, opt->ns_mode, opt->d_param_bf16 ? 1 : 0,
+                             (int32_t)(opt->tail_begin & 0x7fffffff), (int32_t)(opt->tail_begin >> 31)};
     const bool muon = opt->kind == KIND_MUON;
     *fingerprint = plan_hash(opt->kind, opt->n_tensors, muon ? opt->rows.data() : opt->sizes.data(),
-                             muon ? opt->cols.data() : nullptr, hyper, 6, ints, 4, opt->eng->world);
+                             muon ? opt->cols.data() : nullptr, hyper, 6, ints, tail ? 6 : 4, opt->eng->world);
     return VB_OK;
 }
 
@@ -706,6 +758,34 @@ int vb_engine_set_wait_limit_ms(vb_engine *e, uint32_t ms)
     if (!e) return fail(VB_ERR_INVALID_ARG, "engine is null");
     if (ms == 0) return fail(VB_ERR_INVALID_ARG, "the wait limit must be at least 1 ms");
     e->wait_limit_ms = ms;
+    return VB_OK;
+}
+
+int vb_engine_set_replicated_fraction(vb_engine *e, double fraction)
+{
+    if (!e) return fail(VB_ERR_INVALID_ARG, "engine is null");
+    if (!(fraction >= 0.0 && fraction <= 1.0)) return fail(VB_ERR_INVALID_ARG, "the replicated fraction must be in [0, 1]");
+    e->replicated_fraction = fraction;
+    return VB_OK;
+}
+
+int vb_plan_replicated_fraction(double bytes_per_element, int world_size, double hbm_gb_per_s, double link_gb_per_s,
+                                double *fraction)
+{
+    if (!fraction) return fail(VB_ERR_INVALID_ARG, "fraction is null");
+    if (!(bytes_per_element > 0.0) || world_size < 1 || !(hbm_gb_per_s > 0.0) || !(link_gb_per_s > 0.0))
+        return fail(VB_ERR_INVALID_ARG, "bytes_per_element, world_size and both rates must be positive");
+    *fraction = 0.0;
+    if (world_size == 1) return VB_OK;
+    // per arena element: t_local = time to update it here, t_link = time its 4 bytes take into every GPU
+    // when everything is exchanged.  With a fraction f replicated the launch moves
+    //     HBM:  t_local * ((1 - f) / N + f)        NVLink:  t_link * (1 - f)
+    // at the same time; the two are equal at the fraction returned.
+    const double n = (double)world_size;
+    const double t_local = bytes_per_element / hbm_gb_per_s;
+    const double t_link = 4.0 * (n - 1.0) / n / link_gb_per_s;
+    const double exchanged = t_local / (t_link + t_local * (1.0 - 1.0 / n));
+    *fraction = exchanged >= 1.0 ? 0.0 : 1.0 - exchanged;
     return VB_OK;
 }
 
@@ -1182,6 +1262,14 @@ int vb_optimizer_owned_range(vb_optimizer *opt, int64_t *begin, int64_t *end)
     return VB_OK;
 }
 
+int vb_optimizer_replicated_range(vb_optimizer *opt, int64_t *begin, int64_t *end)
+{
+    VB_TRY(check_opt(opt));
+    if (begin) *begin = opt->kind == KIND_MUON ? opt->arena : opt->tail_begin;
+    if (end) *end = opt->arena;
+    return VB_OK;
+}
+
 int vb_optimizer_set_grad_present(vb_optimizer *opt, int64_t tensor, int present)
 {
     VB_TRY(check_tensor(opt, tensor, 0, false));
@@ -1245,9 +1333,9 @@ int vb_optimizer_step_ex(vb_optimizer *opt, uint32_t flags)
     VB_TRY(exchange_fence(opt, xp, 2));
     if (xp.nccl_f32 || xp.nccl_half) {
         prof_begin(e, VB_PHASE_EXCHANGE);
-        if (xp.nccl_f32) VB_TRY(comm_all_gather_inplace(e, opt->d_param, opt->arena / e->world));
+        if (xp.nccl_f32) VB_TRY(comm_all_gather_inplace(e, opt->d_param, opt->tail_begin / e->world));
         if (xp.nccl_half)
-            VB_TRY(comm_all_gather_inplace_bytes(e, opt->d_param_bf16, opt->arena / e->world * (int64_t)sizeof(uint16_t)));
+            VB_TRY(comm_all_gather_inplace_bytes(e, opt->d_param_bf16, opt->tail_begin / e->world * (int64_t)sizeof(uint16_t)));
         prof_end(e, VB_PHASE_EXCHANGE);
     }
     return VB_OK;
@@ -1263,6 +1351,9 @@ int vb_optimizer_step_host(vb_optimizer *opt, const float *grads_host, float *pa
     vb_engine *e = opt->eng;
     if (opt->kind == KIND_MUON) return fail(VB_ERR_UNSUPPORTED, "the pipelined host step is implemented for Adam and SGD");
     if (!grads_host || !params_host) return fail(VB_ERR_INVALID_ARG, "host arena pointer is null");
+    if (opt->tail_begin < opt->arena)
+        return fail(VB_ERR_UNSUPPORTED, "the pipelined host step moves one contiguous owned range: create the optimizer "
+                                        "with no replicated part (vb_engine_set_replicated_fraction 0)");
     if (pieces < 1) pieces = 1;
     if (pieces > 64) pieces = 64;
     VB_TRY(set_device(e));
@@ -1321,9 +1412,9 @@ int vb_optimizer_step_host(vb_optimizer *opt, const float *grads_host, float *pa
     prof_end(e, VB_PHASE_UPDATE);
     prof_end(e, VB_PHASE_HOST_D2H, e->d2h_stream);
     VB_TRY(exchange_fence(opt, xp, 2));
-    if (xp.nccl_f32) VB_TRY(comm_all_gather_inplace(e, opt->d_param, opt->arena / e->world));
+    if (xp.nccl_f32) VB_TRY(comm_all_gather_inplace(e, opt->d_param, opt->tail_begin / e->world));
     if (xp.nccl_half)
-        VB_TRY(comm_all_gather_inplace_bytes(e, opt->d_param_bf16, opt->arena / e->world * (int64_t)sizeof(uint16_t)));
+        VB_TRY(comm_all_gather_inplace_bytes(e, opt->d_param_bf16, opt->tail_begin / e->world * (int64_t)sizeof(uint16_t)));
     VB_CUDA(cudaStreamSynchronize(e->d2h_stream));
     VB_CUDA(cudaStreamSynchronize(e->stream));
     return fence_check_error(opt);
@@ -1344,20 +1435,33 @@ int vb_optimizer_export_state(vb_optimizer *opt, int64_t tensor, int which, floa
         if (which != 0) return fail(VB_ERR_INVALID_ARG, "Muon has one state buffer (velocity)");
         if (muon_owner(opt, tensor) == opt->eng->rank) hi = n;
     } else {
+        // Every element is reported by exactly one rank: its slice by its owner, the replicated tail
+        // (identical on all ranks) by the last rank, whose slice ends where the tail begins, so
+        // that the reported range stays one interval.
         const int64_t off = opt->offsets[tensor];
+        const bool with_tail = opt->eng->rank == opt->eng->world - 1;
         lo = std::max(off, opt->shard_begin) - off;
-        hi = std::min(off + n, opt->shard_end) - off;
+        hi = std::min(off + n, with_tail ? opt->arena : opt->shard_end) - off;
         if (hi < lo) lo = hi = 0;
     }
     if (!state && hi > lo)
         return fail(VB_ERR_STATE, "this optimizer has no state buffer %d (e.g. SGD without momentum)", which);
     if (n > 0) memset(host, 0, (size_t)n * sizeof(float));
     if (hi > lo) {
-        const float *src = opt->kind == KIND_MUON
-                               ? muon_velocity_ptr(opt, tensor) + lo
-                               : state + (opt->offsets[tensor] + lo - opt->shard_begin);
-        VB_CUDA(cudaMemcpyAsync(host + lo, src, (size_t)(hi - lo) * sizeof(float), cudaMemcpyDeviceToHost,
-                                opt->eng->stream));
+        if (opt->kind == KIND_MUON) {
+            VB_CUDA(cudaMemcpyAsync(host + lo, muon_velocity_ptr(opt, tensor) + lo, (size_t)(hi - lo) * sizeof(float),
+                                    cudaMemcpyDeviceToHost, opt->eng->stream));
+        } else {
+            // the slice part and the tail part are two runs of the state arrays
+            const int64_t off = opt->offsets[tensor];
+            const int64_t mid = std::min(std::max(opt->tail_begin - off, lo), hi);
+            if (mid > lo)
+                VB_CUDA(cudaMemcpyAsync(host + lo, state + opt->state_pos(off + lo), (size_t)(mid - lo) * sizeof(float),
+                                        cudaMemcpyDeviceToHost, opt->eng->stream));
+            if (hi > mid)
+                VB_CUDA(cudaMemcpyAsync(host + mid, state + opt->state_pos(off + mid), (size_t)(hi - mid) * sizeof(float),
+                                        cudaMemcpyDeviceToHost, opt->eng->stream));
+        }
         VB_CUDA(cudaStreamSynchronize(opt->eng->stream));
     }
     if (owned_begin) *owned_begin = lo;
@@ -1384,14 +1488,25 @@ int vb_optimizer_import_state(vb_optimizer *opt, int64_t tensor, int which, cons
         hi = std::min(off + n, opt->shard_end) - off;
         if (hi < lo) lo = hi = 0;
     }
-    if (!state && hi > lo) return fail(VB_ERR_STATE, "this optimizer has no state buffer %d", which);
+    // every rank keeps the part of the replicated tail this tensor reaches into as well
+    int64_t t_lo = 0, t_hi = 0;
+    if (opt->kind != KIND_MUON) {
+        const int64_t off = opt->offsets[tensor];
+        t_lo = std::max(off, opt->tail_begin) - off;
+        t_hi = std::min(off + n, opt->arena) - off;
+        if (t_hi < t_lo) t_lo = t_hi = 0;
+    }
+    if (!state && (hi > lo || t_hi > t_lo)) return fail(VB_ERR_STATE, "this optimizer has no state buffer %d", which);
     if (hi > lo) {
         float *dst = opt->kind == KIND_MUON ? muon_velocity_ptr(opt, tensor) + lo
-                                            : state + (opt->offsets[tensor] + lo - opt->shard_begin);
+                                            : state + opt->state_pos(opt->offsets[tensor] + lo);
         VB_CUDA(cudaMemcpyAsync(dst, host + lo, (size_t)(hi - lo) * sizeof(float), cudaMemcpyHostToDevice,
                                 opt->eng->stream));
-        VB_CUDA(cudaStreamSynchronize(opt->eng->stream));
     }
+    if (t_hi > t_lo)
+        VB_CUDA(cudaMemcpyAsync(state + opt->state_pos(opt->offsets[tensor] + t_lo), host + t_lo,
+                                (size_t)(t_hi - t_lo) * sizeof(float), cudaMemcpyHostToDevice, opt->eng->stream));
+    if (hi > lo || t_hi > t_lo) VB_CUDA(cudaStreamSynchronize(opt->eng->stream));
     return VB_OK;
     VB_API_END
 }
@@ -1701,7 +1816,7 @@ int vb_multi_tensor_step(vb_engine *e, const vb_optimizer_step_params *hp, int64
             f.s2 = (state2 && state2[i]) ? (float *)state2[i] + b : nullptr;
             f.len = (uint32_t)std::min(chunk_len, sizes[i] - b);
             f.tensor = (uint32_t)i;
-            f.pad = 0;
+            f.local_only = 0;
         }
     }
     FatChunk *d = (FatChunk *)e->d_stage[slot];

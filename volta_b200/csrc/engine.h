@@ -42,6 +42,7 @@ struct vb_engine {
     std::vector<vb_optimizer *> optimizers;  // alive optimizers of this engine (their error words are read on synchronize)
     cudaEvent_t deadline_event = nullptr;  // vb_engine_synchronize_deadline
     uint32_t wait_limit_ms = 5000;         // bound of every device-side wait on another rank
+    double replicated_fraction = 0.0;      // Adam/SGD optimizers created from now on: share of the arena every rank updates itself
     // optional phase timing (vb_engine_set_profiling): event pairs per phase, summed on query
     bool profiling = false;
     std::vector<std::pair<cudaEvent_t, cudaEvent_t>> prof_pairs[VB_PHASE_COUNT];
@@ -62,6 +63,12 @@ struct vb_optimizer {
     int64_t arena = 0;             // arena length in elements (padded)
     // this rank's slice of the arena (Adam/SGD state lives only here)
     int64_t shard_begin = 0, shard_end = 0;
+    int64_t tail_begin = 0;  // [tail_begin, arena): updated by every rank itself, never exchanged (== arena: none)
+    // index into the state arrays of an arena position this rank updates (slice first, then the tail)
+    int64_t state_pos(int64_t pos) const
+    {
+        return pos < tail_begin ? pos - shard_begin : (shard_end - shard_begin) + (pos - tail_begin);
+    }
 
     float *d_param = nullptr;
     float *d_grad = nullptr;

@@ -193,6 +193,9 @@ __device__ __forceinline__ void update_chunk(const FatChunk &ch, const StepScala
     const uint32_t n = ch.len;
 
     const ptrdiff_t arena_pos = (PEERS || HALF || GSUM) ? (p - pt.local_base) : 0;  // element offset inside the arena
+    // peers to store to: none for a chunk of the replicated tail, which every rank computes itself
+    const int n_peers = (PEERS && ch.local_only == 0) ? pt.n : 0;
+    const int n_half_peers = (HALF == 2 && ch.local_only == 0) ? pt.n_half : 0;
     const float *g_arena = g - arena_pos;  // this rank's gradient arena (same layout as the parameters)
 
     uintptr_t align_bits = reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g);
@@ -217,7 +220,7 @@ __device__ __forceinline__ void update_chunk(const FatChunk &ch, const StepScala
             if (PEERS) {
 #pragma unroll
                 for (int r = 0; r < kMaxPeers; ++r)  // unrolled: the table stays in the constant bank
-                    if (r < pt.n) st_vec8(reinterpret_cast<Vec8 *>(pt.base[r] + arena_pos) + i, vp);
+                    if (r < n_peers) st_vec8(reinterpret_cast<Vec8 *>(pt.base[r] + arena_pos) + i, vp);
             }
             if (HALF) {  // arena_pos is a multiple of 8 here: 16-byte aligned bf16 octets
                 const uint4 h = make_uint4(pack_bf16x2(vp.lo.x, vp.lo.y), pack_bf16x2(vp.lo.z, vp.lo.w),
@@ -226,7 +229,7 @@ __device__ __forceinline__ void update_chunk(const FatChunk &ch, const StepScala
                 if (HALF == 2) {
 #pragma unroll
                     for (int r = 0; r < kMaxPeers; ++r)
-                        if (r < pt.n_half) reinterpret_cast<uint4 *>(pt.half_base[r] + arena_pos)[i] = h;
+                        if (r < n_half_peers) reinterpret_cast<uint4 *>(pt.half_base[r] + arena_pos)[i] = h;
                 }
             }
             if (kHasS1) st_vec8(a8 + i, va);
@@ -257,7 +260,7 @@ __device__ __forceinline__ void update_chunk(const FatChunk &ch, const StepScala
             if (PEERS) {
 #pragma unroll
                 for (int r = 0; r < kMaxPeers; ++r)
-                    if (r < pt.n) reinterpret_cast<float4 *>(pt.base[r] + arena_pos)[i] = vp;
+                    if (r < n_peers) reinterpret_cast<float4 *>(pt.base[r] + arena_pos)[i] = vp;
             }
             if (HALF) {
                 const uint2 h = make_uint2(pack_bf16x2(vp.x, vp.y), pack_bf16x2(vp.z, vp.w));
@@ -265,7 +268,7 @@ __device__ __forceinline__ void update_chunk(const FatChunk &ch, const StepScala
                 if (HALF == 2) {
 #pragma unroll
                     for (int r = 0; r < kMaxPeers; ++r)
-                        if (r < pt.n_half) reinterpret_cast<uint2 *>(pt.half_base[r] + arena_pos)[i] = h;
+                        if (r < n_half_peers) reinterpret_cast<uint2 *>(pt.half_base[r] + arena_pos)[i] = h;
                 }
             }
             if (kHasS1) __stcs(a4 + i, va);
@@ -284,7 +287,7 @@ __device__ __forceinline__ void update_chunk(const FatChunk &ch, const StepScala
         if (PEERS) {
 #pragma unroll
             for (int r = 0; r < kMaxPeers; ++r)
-                if (r < pt.n) pt.base[r][arena_pos + i] = vp;
+                if (r < n_peers) pt.base[r][arena_pos + i] = vp;
         }
         if (HALF) {
             const uint16_t h = bf16_bits(vp);
@@ -292,7 +295,7 @@ __device__ __forceinline__ void update_chunk(const FatChunk &ch, const StepScala
             if (HALF == 2) {
 #pragma unroll
                 for (int r = 0; r < kMaxPeers; ++r)
-                    if (r < pt.n_half) pt.half_base[r][arena_pos + i] = h;
+                    if (r < n_half_peers) pt.half_base[r][arena_pos + i] = h;
             }
         }
         if (kHasS1) s1[i] = va;
@@ -626,7 +629,7 @@ extern "C" int vb_multi_tensor_step_static(vb_engine *engine, const vb_optimizer
             f.s2 = (state2 && state2[i]) ? (float *)state2[i] + b : nullptr;
             f.len = (uint32_t)(sizes[i] - b < chunk_len ? sizes[i] - b : chunk_len);
             f.tensor = (uint32_t)i;
-            f.pad = 0;
+            f.local_only = 0;
         }
     }
     // The used prefix of the device table is rewritten on every call; nothing in it has to

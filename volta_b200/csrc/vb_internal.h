@@ -57,7 +57,8 @@ struct alignas(16) FatChunk {
     float *s2;
     uint32_t len;
     uint32_t tensor;
-    uint64_t pad;
+    uint32_t local_only;  // 1: a chunk of the replicated tail: the new values stay on this GPU
+    uint32_t pad;
 };
 static_assert(sizeof(FatChunk) == 48, "FatChunk is fetched as three 16-byte words");
 

@@ -24,7 +24,7 @@ from ._lib import (VB_NS_BF16, VB_NS_F32, VB_NS_F32_TC, VB_STEP_DEFAULT, VB_STEP
                    VB_STEP_NO_EXCHANGE, VB_STEP_REDUCE_GRADS,
                    VoltaB200Error, call)
 
-__all__ = ["Engine", "Tensor", "Adam", "SGD", "Muon", "default_engine", "multi_tensor_step", "accumulate_grad",
+__all__ = ["Engine", "Tensor", "Adam", "SGD", "Muon", "default_engine", "multi_tensor_step", "accumulate_grad", "plan_replicated_fraction",
            "verify_plan", "plan_fingerprint",
            "VoltaB200Error", "VB_NS_F32", "VB_NS_BF16", "VB_NS_F32_TC", "VB_STEP_NO_EXCHANGE", "VB_STEP_EXCHANGE_BF16", "VB_STEP_REDUCE_GRADS", "VB_STEP_MEAN_GRADS"]
 
@@ -59,6 +59,12 @@ class Engine:
     def set_wait_limit_ms(self, ms: int) -> None:
         """Bound of every device-side wait on another rank (default 5000 ms)."""
         call("vb_engine_set_wait_limit_ms", self._h, int(ms))
+
+    def set_replicated_fraction(self, fraction: float) -> None:
+        """Adam/SGD optimizers created from now on keep the last ``fraction`` of their arena out of
+        the sharding: every rank updates that tail itself (state for it on every rank, complete
+        gradients needed on every rank) and it never crosses NVLink.  0 = plain ZeRO-1 slices."""
+        call("vb_engine_set_replicated_fraction", self._h, float(fraction))
 
     @property
     def stream(self) -> int:
@@ -422,6 +428,13 @@ class _Optimizer:
         call("vb_optimizer_owned_range", self._h, C.byref(lo), C.byref(hi))
         return int(lo.value), int(hi.value)
 
+    def replicated_range(self):
+        """[begin, end) of the arena every rank updates itself (empty unless the engine had a
+        replicated fraction set when the optimizer was created)."""
+        lo, hi = C.c_int64(), C.c_int64()
+        call("vb_optimizer_replicated_range", self._h, C.byref(lo), C.byref(hi))
+        return int(lo.value), int(hi.value)
+
     def upload_arena_range(self, which: int, host: np.ndarray, begin: int) -> None:
         assert host.dtype == np.float32 and host.flags.c_contiguous
         call("vb_optimizer_upload_arena_range", self._h, which, host.ctypes.data_as(C.c_void_p), int(begin), host.size)
@@ -517,6 +530,17 @@ def verify_plan(fingerprints: Sequence[int]) -> None:
     arr = (C.c_uint64 * max(n, 1))(*[int(f) for f in fingerprints])
     bad = C.c_int(-1)
     call("vb_plan_fingerprints_agree", arr, n, C.byref(bad))
+
+
+def plan_replicated_fraction(bytes_per_element: float, world_size: int, hbm_gb_per_s: float,
+                             link_gb_per_s: float) -> float:
+    """The replicated fraction at which a sharded step's HBM time and NVLink time are equal
+    (``vb_plan_replicated_fraction``): Adam moves 28 B per element through HBM, SGD with momentum
+    20, plain SGD 12; the rates are those of the update kernel and of the fused exchange."""
+    out = C.c_double()
+    call("vb_plan_replicated_fraction", float(bytes_per_element), int(world_size), float(hbm_gb_per_s),
+         float(link_gb_per_s), C.byref(out))
+    return float(out.value)
 
 
 def plan_fingerprint(kind: str, sizes_or_shapes, hyper: Sequence[float], ints: Sequence[int] = (),
