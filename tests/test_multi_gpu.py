@@ -142,7 +142,7 @@ def _worker_tail_resume(rank, world, shared):
     import time
 
     import workloads
-    from volta_b200 import Adam, Engine, Tensor
+    from volta_b200 import Adam, Engine, Tensor, VoltaB200Error
     eng = Engine(rank)
     if rank == 0:
         shared["id"] = Engine.unique_id()
@@ -171,6 +171,13 @@ def _worker_tail_resume(rank, world, shared):
 
     tensors, opt = make()
     opt.open_peers(gather("ipc_a", opt.ipc_handle()))
+    # the pipelined host step moves one contiguous owned range: refused (before anything is enqueued)
+    _, _, arena, _ = opt.arena_layout()
+    try:
+        opt.step_host(np.zeros(arena, np.float32), np.zeros(arena, np.float32), pieces=2)
+        raise AssertionError("step_host accepted an optimizer with a replicated tail")
+    except VoltaB200Error as exc:
+        assert "replicated" in str(exc)
     for s in (1, 2):
         step(tensors, opt, s)
     # every element of the state is reported by exactly one rank
