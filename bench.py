@@ -517,8 +517,8 @@ def run_ours(args):
             ft = torch.tensor([frac], dtype=torch.float64, device=dev)
             dist.broadcast(ft, 0)    # one value on every rank
             frac = float(ft.item())
-            if frac > 0.0:
-                eng.set_replicated_fraction(frac)
+            def measure_tail(fr):
+                eng.set_replicated_fraction(fr)
                 tensors_t = [Tensor(p, p.shape) for p in params]
                 opt_t = Adam(tensors_t, h["lr"], h["betas"], h["eps"], h["weight_decay"], engine=eng)
                 eng.set_replicated_fraction(0.0)
@@ -530,8 +530,8 @@ def run_ours(args):
                 opt_t.upload_arena(1, grads_pinned.array)
                 eng.synchronize()
                 launches_before = timed_launches[0]
-                tail_blocks = timed_blocks(make_block(0, opt_t), barrier, max_over_ranks)
-                tail_launches = timed_launches[0] - launches_before
+                t_blocks = timed_blocks(make_block(0, opt_t), barrier, max_over_ranks)
+                t_launches = timed_launches[0] - launches_before
                 timed_launches[0] = launches_before
                 # same number of steps from the same start on both optimizers: the parameters must agree bit for bit
                 restart(opt)
@@ -548,22 +548,39 @@ def run_ours(args):
                 st = torch.tensor([1.0 if same else 0.0], dtype=torch.float64, device=dev)
                 dist.all_reduce(st, op=dist.ReduceOp.MIN)
                 t_lo, t_hi = opt_t.replicated_range()
-                tail_ms = statistics.median(tail_blocks) / args.steps
-                tail = {"fraction": frac, "replicated_elements": t_hi - t_lo, "ms_per_step": tail_ms,
-                        "value": wl.total / (tail_ms * 1e-3), "unit": "params/s",
-                        "blocks": block_stats(tail_blocks, args.steps), "launches": int(tail_launches),
-                        "equals_the_fully_exchanged_result_bit_for_bit": bool(st.item() == 1.0),
-                        "rates_used": {"hbm_gbs": hbm_gbs, "nvlink_gbs_per_direction": link_gbs,
-                                       "all_exchanged_update_launch_ms": upd_ms, "fences_ms_per_step": fence_ms,
-                                       "how": "HBM: the update kernel alone on a slice (update_only); NVLink: bytes into "
-                                              "a GPU over the duration of the update launch that stores every parameter "
-                                              "to every peer (CUDA events around the launch, a separate pass)"},
-                        "extra_state_bytes_per_gpu": 8 * (t_hi - t_lo),
-                        "note": "the last `fraction` of the arena is updated by every rank itself (its moments live "
-                                "on every rank; every rank holds the complete gradients) and never crosses NVLink; "
-                                "the rest is sliced ZeRO-1 style and exchanged by the same launch"}
+                t_ms = statistics.median(t_blocks) / args.steps
                 opt_t.close()
                 del tensors_t
+                return {"fraction": fr, "replicated_elements": t_hi - t_lo, "ms_per_step": t_ms,
+                        "value": wl.total / (t_ms * 1e-3), "unit": "params/s",
+                        "blocks": block_stats(t_blocks, args.steps), "launches": int(t_launches),
+                        "equals_the_fully_exchanged_result_bit_for_bit": bool(st.item() == 1.0),
+                        "extra_state_bytes_per_gpu": 8 * (t_hi - t_lo)}, t_blocks
+
+            if frac > 0.0:
+                # the model assumes the two kinds of traffic overlap perfectly; they do not quite, and the best
+                # cut lies a little to either side of the model's (below at N = 2, above at N = 4): three
+                # fractions around it are measured and the fastest kept
+                candidates = [frac] if args.replicated_fraction > 0.0 else [frac, 0.8 * frac, min(1.15 * frac, 0.95)]
+                tried = []
+                for fr in candidates:
+                    res, res_blocks = measure_tail(fr)
+                    tried.append({"fraction": fr, "ms_per_step": res["ms_per_step"]})
+                    if res["equals_the_fully_exchanged_result_bit_for_bit"] and \
+                            (tail is None or res["ms_per_step"] < tail["ms_per_step"]):
+                        tail, tail_blocks = res, res_blocks
+                if tail is None:
+                    tail, tail_blocks = res, res_blocks
+                tail["fractions_tried"] = tried
+                tail["rates_used"] = {"hbm_gbs": hbm_gbs, "nvlink_gbs_per_direction": link_gbs,
+                                      "all_exchanged_update_launch_ms": upd_ms, "fences_ms_per_step": fence_ms,
+                                      "model_fraction": frac,
+                                      "how": "HBM: the update kernel alone on a slice (update_only); NVLink: bytes into "
+                                             "a GPU over the duration of the update launch that stores every parameter "
+                                             "to every peer (CUDA events around the launch, a separate pass)"}
+                tail["note"] = ("the last `fraction` of the arena is updated by every rank itself (its moments live "
+                                "on every rank; every rank holds the complete gradients) and never crosses NVLink; "
+                                "the rest is sliced ZeRO-1 style and exchanged by the same launch")
         except volta_b200.VoltaB200Error as exc:
             tail = {"error": str(exc)}
             eng.set_replicated_fraction(0.0)
