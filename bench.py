@@ -707,7 +707,8 @@ def run_ours(args):
     # ---- Muon (second headline: Newton-Schulz tensor TFLOP/s), on every rank ----
     muon = None if args.skip_muon else run_muon(args, eng, world, rank, dev, barrier, max_over_ranks, peaks)
 
-    c5 = None if args.skip_c5 else run_c5(args, eng, world, rank, dev, barrier, max_over_ranks, peaks)
+    c5 = None if args.skip_c5 else run_c5(args, eng, world, rank, dev, barrier, max_over_ranks, peaks,
+                                          tail["fraction"] if tail and "fraction" in tail else 0.0)
 
     if rank != 0:
         return 0
@@ -802,9 +803,11 @@ def run_ours(args):
     return 0
 
 
-def run_c5(args, eng, world, rank, dev, barrier, max_over_ranks, peaks):
+def run_c5(args, eng, world, rank, dev, barrier, max_over_ranks, peaks, replicated_fraction=0.0):
     """Ragged multi-tensor Adam (4096 tensors, sizes log-uniform in [1, 2^22], ~1.13e9 params):
-    the same kernel must hold its HBM fraction when the tensor list is ragged."""
+    the same kernel must hold its HBM fraction when the tensor list is ragged.  At N > 1 also the
+    whole step with the fused exchange, every parameter exchanged and with the replicated tail the
+    C3 measurement chose."""
     import torch
 
     from volta_b200 import VB_STEP_NO_EXCHANGE, Adam, Tensor
@@ -812,18 +815,43 @@ def run_c5(args, eng, world, rank, dev, barrier, max_over_ranks, peaks):
 
     wl = workloads.c5_ragged_adam()
     h = wl.hyper
-    tensors = [Tensor(np.zeros(n, np.float32)) for n in wl.sizes]
-    opt = Adam(tensors, h["lr"], h["betas"], h["eps"], h["weight_decay"], engine=eng)
-    p_ptr, g_ptr, arena, offsets = opt.arena_layout()
-    theta = torch.as_tensor(device_array(p_ptr, arena, opt), device=dev)
-    grad = torch.as_tensor(device_array(g_ptr, arena, opt), device=dev)
-    gen = torch.Generator(device=dev)
-    gen.manual_seed(1234)
-    theta.normal_(0.0, 1.0, generator=gen)
-    grad.normal_(0.0, 1e-3, generator=gen)
-    opt.mark_all_grads_present()
-    torch.cuda.synchronize()
     steps = max(3, min(args.steps, 10))
+
+    def build(fraction):
+        eng.set_replicated_fraction(fraction)
+        tensors = [Tensor(np.zeros(n, np.float32)) for n in wl.sizes]
+        opt = Adam(tensors, h["lr"], h["betas"], h["eps"], h["weight_decay"], engine=eng)
+        eng.set_replicated_fraction(0.0)
+        p_ptr, g_ptr, arena, _ = opt.arena_layout()
+        theta = torch.as_tensor(device_array(p_ptr, arena, opt), device=dev)
+        grad = torch.as_tensor(device_array(g_ptr, arena, opt), device=dev)
+        gen = torch.Generator(device=dev)
+        gen.manual_seed(1234)   # the same values on every rank
+        theta.normal_(0.0, 1.0, generator=gen)
+        grad.normal_(0.0, 1e-3, generator=gen)
+        opt.mark_all_grads_present()
+        torch.cuda.synchronize()
+        del theta, grad
+        return opt, tensors
+
+    def whole_steps(opt):
+        stream = torch.cuda.ExternalStream(eng.stream, device=dev)
+        for _ in range(2):
+            opt.step()
+        times = []
+        for _ in range(3):
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(steps):
+                opt.step()
+            e1.record(stream)
+            eng.synchronize()
+            times.append(max_over_ranks(e0.elapsed_time(e1) / steps))
+        barrier()
+        return statistics.median(times)
+
+    opt, tensors = build(0.0)
     for _ in range(3):
         opt.step(VB_STEP_NO_EXCHANGE)
     barrier()
@@ -834,13 +862,33 @@ def run_c5(args, eng, world, rank, dev, barrier, max_over_ranks, peaks):
     ms = max_over_ranks(eng.profile("update")[0] / steps)
     eng.set_profiling(False)
     barrier()
-    del theta, grad
-    opt.close()
     gbs = ADAM_BYTES_PER_PARAM * (wl.total / world) / (ms * 1e-3) / 1e9
-    return {"workload": f"c5_ragged_adam: {len(wl.sizes)} tensors, {wl.total} f32 params, sizes in "
-                        f"[{min(wl.sizes)}, {max(wl.sizes)}], lr=3e-4 wd=0.1", "steps": steps,
-            "update_ms_per_step": ms, "params_per_s": wl.total / (ms * 1e-3), "achieved_gbs_per_gpu": gbs,
-            "frac_of_measured_hbm_peak": gbs / peaks["hbm_gbs"], "note": "update kernel only (no exchange)"}
+    out = {"workload": f"c5_ragged_adam: {len(wl.sizes)} tensors, {wl.total} f32 params, sizes in "
+                       f"[{min(wl.sizes)}, {max(wl.sizes)}], lr=3e-4 wd=0.1", "steps": steps,
+           "update_ms_per_step": ms, "params_per_s": wl.total / (ms * 1e-3), "achieved_gbs_per_gpu": gbs,
+           "frac_of_measured_hbm_peak": gbs / peaks["hbm_gbs"], "note": "update kernel only (no exchange)"}
+    if world > 1 and args.exchange == "peer":
+        try:
+            import volta_b200
+            opt.open_peers(gather_handles(opt.ipc_handle(), world, dev))
+            full_ms = whole_steps(opt)
+            out["whole_step"] = {"ms_per_step": full_ms, "params_per_s": wl.total / (full_ms * 1e-3),
+                                 "note": "fused peer exchange of every parameter"}
+            opt.close()
+            del tensors
+            opt = None
+            if replicated_fraction > 0.0:
+                opt, tensors = build(replicated_fraction)
+                opt.open_peers(gather_handles(opt.ipc_handle(), world, dev))
+                tail_ms = whole_steps(opt)
+                out["whole_step_replicated_tail"] = {"fraction": replicated_fraction, "ms_per_step": tail_ms,
+                                                     "params_per_s": wl.total / (tail_ms * 1e-3)}
+        except volta_b200.VoltaB200Error as exc:
+            out["whole_step_error"] = str(exc)
+            eng.set_replicated_fraction(0.0)
+    if opt is not None:
+        opt.close()
+    return out
 
 
 def time_cpu_muon_sample(ns_steps=5):
