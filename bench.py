@@ -1026,7 +1026,10 @@ def run_muon(args, eng, world, rank, dev, barrier, max_over_ranks, peaks):
             "apply_note": "apply_ms is the last update launch, which applies its result to the weights in its epilogue "
                           "(8 B/param of HBM traffic on top of the product); it is part of ns_ms_per_step as well"
                           if mode_name != "f32" else "separate apply pass",
-            "note": {"bf16": "tcgen05 bf16, short-side Gram, symmetric Gram computed on and above the diagonal only", "f32": "CUDA-core FFMA, bit-identical to the CPU arithmetic",
+            "note": {"bf16": "tcgen05 bf16, chain form: one long-side Gram, 3 (K - 1) short-side symmetric squares (computed "
+                             "on and above the diagonal) and one long-side product per matrix instead of K Gram and K "
+                             "update products; same result within the bf16 bound (VB_NS_CHAIN=0 selects the "
+                             "per-iteration form)", "f32": "CUDA-core FFMA, bit-identical to the CPU arithmetic",
                      "f32_tc": "tcgen05, operands held as two f16 planes (three products per product); "
                                "ns_tflops counts executed f16 tensor FLOPs"}[mode_name],
             "reference_formulation_flops_per_step": sum(4.0 * r * c * c * h["ns_steps"] for r, c in wl.shapes),
@@ -1071,9 +1074,9 @@ def run_muon(args, eng, world, rank, dev, barrier, max_over_ranks, peaks):
             "ms_per_chain": lib_ms, "tflops": lib_flops / (lib_ms * 1e-3) / 1e12, "flops_per_chain": lib_flops,
             "ours_ms": out["bf16"]["ns_ms_per_step"],
             "ours_tflops_on_whole_products": lib_flops / (out["bf16"]["ns_ms_per_step"] * 1e-3) / 1e12,
-            "note": "the same ten products per matrix through torch.bmm (cuBLAS bf16, one batched call per shape), "
-                    "whole products, nothing fused: no polynomial pieces, normalisation or apply, which "
-                    "ns_ms_per_step includes"}
+            "note": "the reference's ten products per matrix (a Gram and an update product per iteration) through "
+                    "torch.bmm (cuBLAS bf16, one batched call per shape), whole products, nothing fused: no "
+                    "polynomial pieces, normalisation or apply, which ns_ms_per_step includes"}
     if world == 1 and not args.no_cpu_baseline and "bf16" in out:
         sec, fl = time_cpu_muon_sample(h["ns_steps"])
         ref_flops = out["bf16"]["reference_formulation_flops_per_step"]

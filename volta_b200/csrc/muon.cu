@@ -744,6 +744,20 @@ struct MuonState {
     // less operand traffic from L2); the lists above then hold only the other matrices
     GemmTile *d_tc_upd_tiles_wide = nullptr, *d_tc_upd_tiles_last_wide = nullptr, *d_tc_gram_tiles_wide = nullptr;
     int n_tc_upd_tiles_wide = 0, n_tc_upd_tiles_last_wide = 0, n_tc_gram_tiles_wide = 0;
+    // The chain form of the plain bf16 path (see build of chain_launches): launches in order, the
+    // last one is the product that yields the update
+    struct TcLaunch {
+        TcGemmProblem *d_problems = nullptr;
+        const GemmTile *d_tiles = nullptr;
+        int n_tiles = 0;
+        bool final_product = false;
+        bool dual = false;  // its problems store G beside 3I - G
+    };
+    bool chain = false;
+    std::vector<TcLaunch> chain_launches;
+    __nv_bfloat16 *d_chain = nullptr;    // per matrix six short-side squares: G, T, C'[2], P'[2]
+    GemmTile *d_small_tiles = nullptr, *d_small_tiles2 = nullptr;
+    int n_small_tiles = 0, n_small_tiles2 = 0;
     int *d_error = nullptr;
     int *h_error = nullptr;              // pinned mirror of d_error, refreshed after every step
     // The last update launch applies its result to the weights itself (tensor-core matrices); the
@@ -769,6 +783,10 @@ void destroy_muon_state(MuonState *s)
     cudaFree(s->d_xb[0]);
     cudaFree(s->d_xb[1]);
     cudaFree(s->d_cb);
+    cudaFree(s->d_chain);
+    cudaFree(s->d_small_tiles);
+    cudaFree(s->d_small_tiles2);
+    for (auto &l : s->chain_launches) cudaFree(l.d_problems);
     cudaFree(s->d_sumsq);
     cudaFree(s->d_partials);
     cudaFree(s->d_ns_kind);
@@ -819,6 +837,11 @@ double muon_tensor_cost(int64_t rows, int64_t cols, int ns_mode, int ns_steps)
     const double L = std::max(r, c), S = std::min(r, c);
     const double t = std::ceil(S / 256.0);                  // 256 x 256 tiles per side of the Gram
     const double upper = (t * (t + 1.0) / 2.0) / (t * t);   // share of the Gram that is computed
+    if (ns_mode == VB_NS_BF16) {
+        // the chain form: the first Gram (upper tiles), 3 (K - 1) short-side squares (upper tiles), the last product
+        const double work = 2.0 * L * S * S * (1.0 + upper) + 3.0 * (double)(ns_steps - 1) * 2.0 * S * S * S * upper;
+        return elementwise + work / 0.8e15;
+    }
     const double planes = ns_mode == VB_NS_F32_TC ? 3.0 : 1.0;
     return elementwise + planes * (double)ns_steps * 2.0 * L * S * S * (1.0 + upper) / 1.15e15;
 }
@@ -998,6 +1021,15 @@ int muon_init(vb_optimizer *opt)
         }
         VB_CUDA(cudaMalloc(&s->d_cb, (size_t)s->planes * (size_t)std::max<int64_t>(cb_elems, 1) *
                                          sizeof(__nv_bfloat16)));
+        // plain bf16 path: the chain form (below) unless VB_NS_CHAIN=0 asks for one Gram and one update
+        // product per iteration
+        const char *chain_env = getenv("VB_NS_CHAIN");
+        s->chain = s->planes == 1 && opt->ns_steps >= 1 && !(chain_env && *chain_env == '0');
+        if (s->chain) {
+            const size_t chain_bytes = 6 * (size_t)std::max<int64_t>(cb_elems, 1) * sizeof(__nv_bfloat16);
+            VB_CUDA(cudaMalloc(&s->d_chain, chain_bytes));
+            VB_CUDA(cudaMemsetAsync(s->d_chain, 0, chain_bytes, e->stream));
+        }
     }
     // where the final update of each tensor lives after a step
     std::vector<TensorDesc> desc_apply = desc;
@@ -1058,8 +1090,23 @@ int muon_init(vb_optimizer *opt)
         const int iters = opt->ns_steps;
         std::vector<std::vector<TcGemmProblem>> gram((size_t)iters), upd((size_t)iters);
         std::vector<GemmTile> gram_tiles, upd_tiles, upd_tiles_last, upd_tiles_wide, upd_tiles_last_wide, gram_tiles_wide;
-        const int wide_cols = s->planes == 1 ? tc_gemm_wide_cols() : 0;
-        const int wide_gram_cols = s->planes == 1 ? tc_gemm_wide_gram_cols() : 0;
+        const int wide_cols = (s->planes == 1 && !s->chain) ? tc_gemm_wide_cols() : 0;  // the chain form keeps to square tiles
+        const int wide_gram_cols = (s->planes == 1 && !s->chain) ? tc_gemm_wide_gram_cols() : 0;
+        // The chain form.  With C' = 3I - G every iterate is X_k = X_0 P_k with P_k a polynomial in
+        // G_0 = X_0^T X_0, and all of G_k, C'_k, P_k commute and are symmetric:
+        //     T_k = G_k C'_k,   G_{k+1} = C'_k T_k / 4,   C'_{k+1} = 3I - G_{k+1},   P'_{k+1} = P'_k C'_k  (P'_1 = C'_0)
+        //     X_K = 2^-K X_0 P'_K
+        // so only the first Gram and the last product touch the long side of the matrix; everything
+        // in between is short-side squares, computed on and above the diagonal and mirrored.  Per
+        // matrix that is three long-side products' worth of work (the Gram counts half) plus
+        // 3 (K - 1) half squares, instead of 3 K long-side products (4096 x 1024, K = 5: 24 n^3
+        // multiply-adds against 60 n^3).  In exact arithmetic the result is the reference's; in bf16 the distance
+        // from the f32 oracle stays what the per-iteration form has (a few 1e-3, bound 2e-2).
+        const int n_chain_mid = std::max(iters - 1, 0);
+        std::vector<TcGemmProblem> chain_l0, chain_final;
+        std::vector<std::vector<TcGemmProblem>> chain_a((size_t)n_chain_mid), chain_b((size_t)n_chain_mid),
+            chain_c((size_t)iters);  // chain_c[k], k = 1 .. iters - 1
+        std::vector<GemmTile> small_tiles;
         std::stable_sort(tc_tensors.begin(), tc_tensors.end(), by_size);
         // plain bf16 path: the momentum kernel writes the unnormalised bf16 operand and the first
         // iteration's epilogues apply 1/norm; the split path keeps the reference's true division
@@ -1141,6 +1188,61 @@ int muon_init(vb_optimizer *opt)
                 }
                 upd[(size_t)it].push_back(u);
             }
+            if (s->chain) {
+                __nv_bfloat16 *sq[6];  // G, T, C'[0], C'[1], P'[0], P'[1]
+                CUtensorMap sq_k[6], sq_mn[6];
+                for (int b = 0; b < 6; ++b) {
+                    sq[b] = s->d_chain + (int64_t)b * cb_elems + cb_off[(size_t)t];
+                    VB_TRY(make_bf16_tensor_map(&sq_k[b], sq[b], sh, sh, TC_OP_K_MAJOR, 1, 0));
+                    VB_TRY(make_bf16_tensor_map(&sq_mn[b], sq[b], sh, sh, c_mn_mode, 1, 0));
+                }
+                enum { kG = 0, kT = 1, kC0 = 2, kP0 = 4 };
+                auto small = [&](int a, int b, int out, int epi) {
+                    TcGemmProblem q{};
+                    q.map_a = sq_mn[a]; q.map_b = sq_k[b];  // both symmetric: A staged MN-major (the faster way)
+                    q.M = sh; q.N = sh; q.K = sh;
+                    q.a_mode = c_mn_mode; q.b_mode = TC_OP_K_MAJOR;
+                    q.epilogue = epi; q.ld_out = sh; q.tensor = t;
+                    q.n_terms = 1; q.n_out_planes = 1; q.out_plane_stride = 0;
+                    q.out_bf16 = sq[out];
+                    return q;
+                };
+                TcGemmProblem l0 = gram[0].back();  // G_0 = (u^T u) / norm^2 and C'_0 = 3I - G_0
+                l0.out_bf16 = sq[kC0];
+                l0.out2_bf16 = sq[kG];
+                chain_l0.push_back(l0);
+                for (int k = 0; k + 1 < iters; ++k) {
+                    const int c_now = kC0 + (k & 1), c_next = kC0 + ((k + 1) & 1);
+                    chain_a[(size_t)k].push_back(small(kG, c_now, kT, TC_EPI_IDENTITY));            // T_k = G_k C'_k
+                    TcGemmProblem lb = small(c_now, kT, c_next, TC_EPI_THREE_I_MINUS);              // C'_{k+1} = 3I - C'_k T_k / 4
+                    lb.extra_scale = 0.25f;
+                    lb.out2_bf16 = sq[kG];                                                          // G_{k+1}
+                    chain_b[(size_t)k].push_back(lb);
+                }
+                // P'_1 = C'_0 lives in C'[0]; P'_j (j >= 2) in P'[j & 1]
+                auto p_buf = [&](int j) { return j == 1 ? (int)kC0 : kP0 + (j & 1); };
+                for (int k = 1; k < iters; ++k)
+                    chain_c[(size_t)k].push_back(small(p_buf(k), kC0 + (k & 1), p_buf(k + 1), TC_EPI_IDENTITY));
+                // X_K = 2^-K (u P'_K) / norm, in the direct form of the last update product
+                TcGemmProblem fin = upd[(size_t)iters - 1].back();
+                const int pk = p_buf(iters);
+                if (tall) {
+                    fin.map_a = map_x_k[0];
+                    fin.map_b = sq_k[pk];
+                } else {
+                    fin.map_a = sq_mn[pk];
+                    fin.map_b = map_x_mn[0];
+                }
+                fin.in_bf16 = nullptr;
+                fin.epilogue = TC_EPI_HALF;  // 0.5 * 2^(1 - K) = 2^-K
+                fin.scale_sumsq = s->d_sumsq + t;
+                fin.scale_power = 1;
+                fin.extra_scale = ldexpf(1.0f, 1 - iters);
+                chain_final.push_back(fin);
+                for (int m0 = 0; m0 < sh; m0 += bm)
+                    for (int n0 = m0; n0 < sh; n0 += bn)
+                        small_tiles.push_back(GemmTile{pidx, m0, n0, n0 > m0 ? GEMM_TILE_MIRROR : 0});
+            }
             // The Gram is symmetric: with square tiles only those on or above the diagonal are
             // computed; off-diagonal ones are also stored transposed by the epilogue.
             int gram_all = 0, gram_used = 0;
@@ -1192,8 +1294,47 @@ int muon_init(vb_optimizer *opt)
             // executed tensor-core FLOPs: three plane products per product on the split path; the
             // Gram counts only the tiles that are computed
             const double prod = 2.0 * (double)std::max(r, c) * (double)sh * (double)sh;
-            s->flops_per_step += (double)n_terms * (double)opt->ns_steps *
-                                 (prod * (double)gram_used / (double)gram_all + prod);
+            if (s->chain) {
+                const double upper = (double)gram_used / (double)gram_all;
+                const double square = 2.0 * (double)sh * (double)sh * (double)sh * upper;
+                s->flops_per_step += prod * upper + 3.0 * (double)(iters - 1) * square + prod;
+            } else {
+                s->flops_per_step += (double)n_terms * (double)opt->ns_steps *
+                                     (prod * (double)gram_used / (double)gram_all + prod);
+            }
+        }
+        if (s->chain) {
+            if (bm != bn) return fail(VB_ERR_STATE, "the chain form needs square tiles");
+            const int n_tc = (int)chain_l0.size();
+            std::vector<GemmTile> small_tiles2 = small_tiles;  // two problem sets in one launch
+            for (const GemmTile &tl : small_tiles) small_tiles2.push_back(GemmTile{tl.problem + n_tc, tl.m0, tl.n0, tl.flags});
+            VB_TRY(upload(&s->d_small_tiles, small_tiles, e->stream));
+            VB_TRY(upload(&s->d_small_tiles2, small_tiles2, e->stream));
+            s->n_small_tiles = (int)small_tiles.size();
+            s->n_small_tiles2 = (int)small_tiles2.size();
+            auto add = [&](const std::vector<TcGemmProblem> &probs, const GemmTile *tiles, int n_tiles, bool fin,
+                           bool dual = false) -> int {
+                MuonState::TcLaunch l;
+                VB_TRY(upload(&l.d_problems, probs, e->stream));
+                l.d_tiles = tiles;
+                l.n_tiles = n_tiles;
+                l.final_product = fin;
+                l.dual = dual;
+                s->chain_launches.push_back(l);
+                return VB_OK;
+            };
+            // the tile lists of the first Gram and of the last product are uploaded below; their
+            // pointers are filled in once they exist
+            VB_TRY(add(chain_l0, nullptr, 0, false, /*dual=*/true));
+            for (int k = 0; k + 1 < iters; ++k) {
+                std::vector<TcGemmProblem> both = chain_a[(size_t)k];
+                if (k >= 1) both.insert(both.end(), chain_c[(size_t)k].begin(), chain_c[(size_t)k].end());
+                VB_TRY(add(both, k >= 1 ? s->d_small_tiles2 : s->d_small_tiles,
+                           k >= 1 ? s->n_small_tiles2 : s->n_small_tiles, false));
+                VB_TRY(add(chain_b[(size_t)k], s->d_small_tiles, s->n_small_tiles, false, /*dual=*/true));
+            }
+            if (iters >= 2) VB_TRY(add(chain_c[(size_t)iters - 1], s->d_small_tiles, s->n_small_tiles, false));
+            VB_TRY(add(chain_final, nullptr, 0, true));
         }
         s->d_tc_gram.assign((size_t)iters, nullptr);
         s->d_tc_upd.assign((size_t)iters, nullptr);
@@ -1213,6 +1354,12 @@ int muon_init(vb_optimizer *opt)
         s->n_tc_upd_tiles_last = (int)upd_tiles_last.size();
         s->n_tc_gram_tiles = (int)gram_tiles.size();
         s->n_tc_upd_tiles = (int)upd_tiles.size();
+        if (s->chain) {
+            s->chain_launches.front().d_tiles = s->d_tc_gram_tiles;
+            s->chain_launches.front().n_tiles = s->n_tc_gram_tiles;
+            s->chain_launches.back().d_tiles = s->d_tc_upd_tiles_last;
+            s->chain_launches.back().n_tiles = s->n_tc_upd_tiles_last;
+        }
     }
     VB_CUDA(cudaStreamSynchronize(e->stream));
     return VB_OK;
@@ -1246,9 +1393,11 @@ int muon_step(vb_optimizer *opt, uint32_t flags)
         fence1_done = true;
     }
     const uint32_t gemm_wait_limit = s->debug_wait_limit;  // 0 = the default; set by the expiry test hook
-    if (s->debug_withhold && compute && !s->d_tc_gram.empty()) {
+    TcGemmProblem *first_tc_problems = s->chain ? s->chain_launches.front().d_problems
+                                                : (s->d_tc_gram.empty() ? nullptr : s->d_tc_gram[0]);
+    if (s->debug_withhold && compute && first_tc_problems != nullptr) {
         const int32_t one = 1;
-        VB_CUDA(cudaMemcpyAsync(reinterpret_cast<char *>(s->d_tc_gram[0]) + offsetof(TcGemmProblem, withhold_loads), &one,
+        VB_CUDA(cudaMemcpyAsync(reinterpret_cast<char *>(first_tc_problems) + offsetof(TcGemmProblem, withhold_loads), &one,
                                 sizeof(one), cudaMemcpyHostToDevice, e->stream));
     }
     prof_begin(e, VB_PHASE_MUON_PRE);
@@ -1301,9 +1450,38 @@ int muon_step(vb_optimizer *opt, uint32_t flags)
         e->launches += 2;
         prof_end(e, VB_PHASE_MUON_PRE);
         prof_begin(e, VB_PHASE_MUON_NS);
+        // the launch that yields the update applies it itself when fused (see TcApplyArgs)
+        auto final_apply_args = [&](TcApplyArgs &ap) -> int {
+            if (!fuse_now) return VB_OK;
+            // this launch writes the new weights (also into the peers): nobody is written to
+            // before it has reached its step
+            if (!fence1_done) {
+                prof_end(e, VB_PHASE_MUON_NS);
+                VB_TRY(exchange_fence(opt, xp, 1));
+                prof_begin(e, VB_PHASE_MUON_NS);
+                fence1_done = true;
+            }
+            ap.enabled = 1;
+            ap.keep_update = s->keep_update ? 1 : 0;
+            ap.lr = opt->lr;
+            ap.pt = xp.pt;
+            // phase timing: this launch counts as Newton-Schulz and, on its own, as "apply"
+            prof_begin(e, VB_PHASE_MUON_APPLY);
+            return VB_OK;
+        };
+        if (s->chain) {
+            for (const MuonState::TcLaunch &l : s->chain_launches) {
+                TcApplyArgs ap{};
+                if (l.final_product) VB_TRY(final_apply_args(ap));
+                VB_TRY(launch_ns_gemm_tc(l.d_problems, l.d_tiles, l.n_tiles, opt->d_present, s->d_error, e->sm_count,
+                                         e->stream, gemm_wait_limit, false, ap.enabled ? &ap : nullptr, false, l.dual));
+                if (ap.enabled) prof_end(e, VB_PHASE_MUON_APPLY);
+                e->launches += l.n_tiles > 0;
+            }
+        }
         for (int it = 0; it < opt->ns_steps; ++it) {
             const int par = it & 1;
-            if (s->n_tc_gram_tiles + s->n_tc_gram_tiles_wide > 0) {
+            if (!s->chain && s->n_tc_gram_tiles + s->n_tc_gram_tiles_wide > 0) {
                 const bool split = s->planes > 1;
                 VB_TRY(launch_ns_gemm_tc(s->d_tc_gram[(size_t)it], s->d_tc_gram_tiles, s->n_tc_gram_tiles,
                                          opt->d_present, s->d_error, e->sm_count, e->stream, gemm_wait_limit, split));
@@ -1312,22 +1490,7 @@ int muon_step(vb_optimizer *opt, uint32_t flags)
                                          /*wide=*/true));
                 const bool last_it = it == opt->ns_steps - 1;
                 TcApplyArgs ap{};
-                if (last_it && fuse_now) {
-                    // this launch writes the new weights (also into the peers): nobody is written to
-                    // before it has reached its step
-                    if (!fence1_done) {
-                        prof_end(e, VB_PHASE_MUON_NS);
-                        VB_TRY(exchange_fence(opt, xp, 1));
-                        prof_begin(e, VB_PHASE_MUON_NS);
-                        fence1_done = true;
-                    }
-                    ap.enabled = 1;
-                    ap.keep_update = s->keep_update ? 1 : 0;
-                    ap.lr = opt->lr;
-                    ap.pt = xp.pt;
-                    // phase timing: this launch counts as Newton-Schulz and, on its own, as "apply"
-                    prof_begin(e, VB_PHASE_MUON_APPLY);
-                }
+                if (last_it) VB_TRY(final_apply_args(ap));
                 VB_TRY(launch_ns_gemm_tc(s->d_tc_upd[(size_t)it], last_it ? s->d_tc_upd_tiles_last : s->d_tc_upd_tiles,
                                          last_it ? s->n_tc_upd_tiles_last : s->n_tc_upd_tiles,
                                          opt->d_present, s->d_error, e->sm_count, e->stream, gemm_wait_limit, split,
@@ -1355,9 +1518,9 @@ int muon_step(vb_optimizer *opt, uint32_t flags)
             VB_CUDA(cudaMemcpyAsync(s->h_error, s->d_error, sizeof(int), cudaMemcpyDeviceToHost, e->stream));
     }
     prof_end(e, VB_PHASE_MUON_PRE);  // no-op if already closed (no Newton-Schulz matrices)
-    if (s->debug_withhold && compute && !s->d_tc_gram.empty()) {
+    if (s->debug_withhold && compute && first_tc_problems != nullptr) {
         const int32_t zero = 0;
-        VB_CUDA(cudaMemcpyAsync(reinterpret_cast<char *>(s->d_tc_gram[0]) + offsetof(TcGemmProblem, withhold_loads), &zero,
+        VB_CUDA(cudaMemcpyAsync(reinterpret_cast<char *>(first_tc_problems) + offsetof(TcGemmProblem, withhold_loads), &zero,
                                 sizeof(zero), cudaMemcpyHostToDevice, e->stream));
         s->debug_withhold = false;
         s->debug_wait_limit = 0;

@@ -117,9 +117,12 @@ struct alignas(128) TcGemmProblem {
     const float *scale_sumsq;      // if set: the accumulator is scaled by s^scale_power, s = 1/sqrt(*scale_sumsq + 1e-8)
                                    // (the Frobenius normalisation of muon.rs:59-64 folded into the first iteration)
     int32_t scale_power;           // 1 or 2
-    int32_t pad0;
+    float extra_scale;             // plain kernel: a further factor on the accumulator (0 = none)
     const __nv_bfloat16 *in_bf16;  // TC_EPI_NS_COMBINE only: planes of X (same ld and plane stride as the output)
     __nv_bfloat16 *out_bf16; // may be null
+    // plain kernel, TC_EPI_THREE_I_MINUS only: if set, the scaled accumulator itself (G, where out_bf16
+    // receives 3I - G), same leading dimension
+    __nv_bfloat16 *out2_bf16;
     float *out_f32;          // may be null
     // Launches with TcApplyArgs::enabled: the weights of this matrix (row-major, ld_out) and the
     // arena position of their first element; the epilogue applies the update to them in place.
@@ -142,7 +145,8 @@ struct TcApplyArgs {
 // wait_limit: mbarrier polls before a role gives up (0 = the default, about a second).
 int launch_ns_gemm_tc(const TcGemmProblem *d_problems, const GemmTile *d_tiles, int n_tiles,
                       const uint8_t *d_present, int *d_error_flag, int sm_count, cudaStream_t stream,
-                      uint32_t wait_limit = 0, bool split = false, const TcApplyArgs *apply = nullptr, bool wide = false);
+                      uint32_t wait_limit = 0, bool split = false, const TcApplyArgs *apply = nullptr, bool wide = false,
+                      bool dual = false);  // dual: the launch's 3I - G problems also store G (out2_bf16)
 void tc_gemm_tile_shape(int *bm, int *bn);
 int tc_gemm_wide_cols();       // columns of the wide tile (512) of the update products, 0 if not in use
 int tc_gemm_wide_gram_cols();  // the same for the Gram products

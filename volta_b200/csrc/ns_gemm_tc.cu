@@ -782,7 +782,10 @@ __device__ __forceinline__ TileInfo fetch_tile(const TcGemmProblem *problems, co
 
 // kSplit: the operands are two f16 planes (f32-accurate path); the plain bf16 instantiation
 // carries none of that code.
-template <int kCtas, bool kSplit, bool kWide>
+// kDual: launches whose 3I - G problems also store G itself (TcGemmProblem::out2_bf16) drain every
+// accumulator twice; the code for that lives in an instantiation of its own so that the register
+// allocation of every other launch is not touched by it.
+template <int kCtas, bool kSplit, bool kWide, bool kDual>
 __global__ void __launch_bounds__(kThreads, 1)
 ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__restrict__ tiles, int n_tiles,
                   const uint8_t *__restrict__ present, int *__restrict__ error_flag, uint32_t wait_limit,
@@ -1058,6 +1061,9 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
                 const float inv = norm > 1e-8f ? 1.0f / norm : 1.0f;  // muon.rs:60
                 acc_scale = p->scale_power == 2 ? inv * inv : inv;
             }
+            if (!kSplit && p->extra_scale != 0.0f) acc_scale *= p->extra_scale;
+            // a second output of a 3I - G launch: G itself (drained by a second pass over the accumulator)
+            __nv_bfloat16 *out2_bf16 = (kDual && !kSplit && epi == TC_EPI_THREE_I_MINUS) ? p->out2_bf16 : nullptr;
             const int64_t ld = p->ld_out;
             const int out_planes = kSplit ? p->n_out_planes : 1;  // 1: bf16 rounding; 2: the two f16 planes
             const int out_planes_in = kSplit ? kSplitPlanes : 1;  // planes of the operands (and of in_bf16)
@@ -1092,26 +1098,32 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
             const bool fast = !kSplit && tile_col0 + BN / 2 <= N && bf16_rows_32b &&
                               (out_bf16 == nullptr || transpose || (out_f32 == nullptr && apply_w == nullptr)) &&
                               (epi == TC_EPI_HALF || epi == TC_EPI_THREE_I_MINUS || epi == TC_EPI_IDENTITY);
-            if (fast) {
-                // (a * s) * 0.5 == a * (s * 0.5) and -(a * s) == a * (-s) exactly
-                if (epi == TC_EPI_HALF)
-                    drain_fast<TC_EPI_HALF>(taddr, row - lane, tile_col0, M, 0.5f * acc_scale, lane, out_bf16, out_f32,
-                                            mirror, transpose, ld, apply_w, apply_pos, ap, my_stage);
-                else if (epi == TC_EPI_THREE_I_MINUS)
-                    drain_fast<TC_EPI_THREE_I_MINUS>(taddr, row - lane, tile_col0, M, -acc_scale, lane, out_bf16,
-                                                     out_f32, mirror, transpose, ld, nullptr, 0, ap, my_stage);
-                else
-                    drain_fast<TC_EPI_IDENTITY>(taddr, row - lane, tile_col0, M, acc_scale, lane, out_bf16, out_f32,
-                                                mirror, transpose, ld, nullptr, 0, ap, my_stage);
-            }
-            if (!fast) {
-                DrainArgs da;
-                da.taddr = taddr; da.row = row; da.tile_col0 = tile_col0; da.M = M; da.N = N; da.epi = epi;
-                da.lane = lane; da.acc_scale = acc_scale; da.split_e = split_e; da.ld = ld; da.plane_stride = plane_stride;
-                da.out_planes = out_planes; da.out_planes_in = out_planes_in; da.bf16_rows_32b = bf16_rows_32b;
-                da.mirror = mirror; da.transpose = transpose; da.out_bf16 = out_bf16; da.out_f32 = out_f32; da.in_bf16 = in_bf16;
-                da.apply_w = apply_w; da.apply_pos = apply_pos; da.ap = &ap;
-                drain_generic<kSplit>(da);
+            // one pass over the accumulator per output: 3I - G, then (if asked for) G itself
+            const int n_pass = (kDual && out2_bf16 != nullptr) ? 2 : 1;
+#pragma unroll 1
+            for (int pass = 0; pass < n_pass; ++pass) {
+                const int epi_p = pass == 0 ? epi : (int)TC_EPI_IDENTITY;
+                __nv_bfloat16 *const out_p = pass == 0 ? out_bf16 : out2_bf16;
+                if (fast) {
+                    // (a * s) * 0.5 == a * (s * 0.5) and -(a * s) == a * (-s) exactly
+                    if (epi_p == TC_EPI_HALF)
+                        drain_fast<TC_EPI_HALF>(taddr, row - lane, tile_col0, M, 0.5f * acc_scale, lane, out_p, out_f32,
+                                                mirror, transpose, ld, apply_w, apply_pos, ap, my_stage);
+                    else if (epi_p == TC_EPI_THREE_I_MINUS)
+                        drain_fast<TC_EPI_THREE_I_MINUS>(taddr, row - lane, tile_col0, M, -acc_scale, lane, out_p,
+                                                         out_f32, mirror, transpose, ld, nullptr, 0, ap, my_stage);
+                    else
+                        drain_fast<TC_EPI_IDENTITY>(taddr, row - lane, tile_col0, M, acc_scale, lane, out_p, out_f32,
+                                                    mirror, transpose, ld, nullptr, 0, ap, my_stage);
+                } else {
+                    DrainArgs da;
+                    da.taddr = taddr; da.row = row; da.tile_col0 = tile_col0; da.M = M; da.N = N; da.epi = epi_p;
+                    da.lane = lane; da.acc_scale = acc_scale; da.split_e = split_e; da.ld = ld; da.plane_stride = plane_stride;
+                    da.out_planes = out_planes; da.out_planes_in = out_planes_in; da.bf16_rows_32b = bf16_rows_32b;
+                    da.mirror = mirror; da.transpose = transpose; da.out_bf16 = out_p; da.out_f32 = out_f32; da.in_bf16 = in_bf16;
+                    da.apply_w = apply_w; da.apply_pos = apply_pos; da.ap = &ap;
+                    drain_generic<kSplit>(da);
+                }
             }
             tcgen05_fence_before();
             __syncwarp();
@@ -1240,21 +1252,21 @@ int make_bf16_tensor_map(void *map_out, const void *base, int64_t inner, int64_t
     return VB_OK;
 }
 
-template <int kCtas, bool kSplit, bool kWide>
+template <int kCtas, bool kSplit, bool kWide, bool kDual = false>
 static int launch_variant(const TcGemmProblem *d_problems, const GemmTile *d_tiles, int n_tiles,
                           const uint8_t *d_present, int *d_error_flag, int sm_count, cudaStream_t stream,
                           uint32_t wait_limit, const TcApplyArgs &ap)
 {
     static bool attr_set = false;
     if (!attr_set) {
-        VB_CUDA(cudaFuncSetAttribute(ns_gemm_tc_kernel<kCtas, kSplit, kWide>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        VB_CUDA(cudaFuncSetAttribute(ns_gemm_tc_kernel<kCtas, kSplit, kWide, kDual>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      (int)smem_bytes<kCtas, kSplit, kWide>()));
         attr_set = true;
     }
     if (kCtas == 1) {
         int grid = sm_count;  // one persistent CTA per SM (it owns all 512 TMEM columns)
         if (grid > n_tiles) grid = n_tiles;
-        ns_gemm_tc_kernel<kCtas, kSplit, kWide><<<grid, kThreads, smem_bytes<kCtas, kSplit, kWide>(), stream>>>(
+        ns_gemm_tc_kernel<kCtas, kSplit, kWide, kDual><<<grid, kThreads, smem_bytes<kCtas, kSplit, kWide>(), stream>>>(
             d_problems, d_tiles, n_tiles, d_present, d_error_flag, wait_limit, ap);
         VB_CUDA(cudaGetLastError());
         return VB_OK;
@@ -1275,14 +1287,14 @@ static int launch_variant(const TcGemmProblem *d_problems, const GemmTile *d_til
     if (max_clusters == 0) {
         cfg.gridDim = dim3((unsigned)(sm_count / 2 * 2));
         int n = 0;
-        VB_CUDA(cudaOccupancyMaxActiveClusters(&n, ns_gemm_tc_kernel<kCtas, kSplit, kWide>, &cfg));
+        VB_CUDA(cudaOccupancyMaxActiveClusters(&n, ns_gemm_tc_kernel<kCtas, kSplit, kWide, kDual>, &cfg));
         if (n < 1) return fail(VB_ERR_CUDA, "the device cannot hold a 2-CTA cluster of the GEMM kernel");
         max_clusters = n;
     }
     int clusters = max_clusters;
     if (clusters > n_tiles) clusters = n_tiles;
     cfg.gridDim = dim3((unsigned)(clusters * 2));
-    VB_CUDA(cudaLaunchKernelEx(&cfg, ns_gemm_tc_kernel<kCtas, kSplit, kWide>, d_problems, d_tiles, n_tiles, d_present,
+    VB_CUDA(cudaLaunchKernelEx(&cfg, ns_gemm_tc_kernel<kCtas, kSplit, kWide, kDual>, d_problems, d_tiles, n_tiles, d_present,
                                d_error_flag, wait_limit, ap));
     return VB_OK;
 }
@@ -1290,11 +1302,18 @@ static int launch_variant(const TcGemmProblem *d_problems, const GemmTile *d_til
 // split: the problems' operands are two f16 planes (all problems of a launch are alike).
 int launch_ns_gemm_tc(const TcGemmProblem *d_problems, const GemmTile *d_tiles, int n_tiles,
                       const uint8_t *d_present, int *d_error_flag, int sm_count, cudaStream_t stream,
-                      uint32_t wait_limit, bool split, const TcApplyArgs *apply, bool wide)
+                      uint32_t wait_limit, bool split, const TcApplyArgs *apply, bool wide, bool dual)
 {
     if (n_tiles <= 0) return VB_OK;
     if (wait_limit == 0) wait_limit = kDefaultWaitLimit;
     const TcApplyArgs ap = apply ? *apply : TcApplyArgs{};
+    if (dual) {
+        if (split || wide) return fail(VB_ERR_INVALID_ARG, "a second output exists for the plain kernel");
+        return tc_use_pair() ? launch_variant<2, false, false, true>(d_problems, d_tiles, n_tiles, d_present, d_error_flag,
+                                                                     sm_count, stream, wait_limit, ap)
+                             : launch_variant<1, false, false, true>(d_problems, d_tiles, n_tiles, d_present, d_error_flag,
+                                                                     sm_count, stream, wait_limit, ap);
+    }
     if (wide) {
         if (split || !tc_use_pair()) return fail(VB_ERR_INVALID_ARG, "the wide tile exists for the plain pair kernel");
         return launch_variant<2, false, true>(d_problems, d_tiles, n_tiles, d_present, d_error_flag, sm_count, stream,
