@@ -1061,9 +1061,9 @@ def run_muon(args, eng, world, rank, dev, barrier, max_over_ranks, peaks):
                 "frac_of_burst_peak": tflops / (peaks["bf16_tflops"] * world),
                 "frac_of_nominal_2250": tflops / (2250.0 * world),
                 "traffic": NCU_MUON_4LAYER_DRAM_BYTES_PER_LAUNCH * args.muon_layers / 4.0 / world,
-                "traffic_note": "ncu capture of the 4-layer case (mean of a Gram and an update launch), scaled by "
+                "traffic_note": "ncu capture of the 4-layer case (mean over the eleven launches of a step), scaled by "
                                 "layers / 4: per-launch traffic grows with the number of matrices",
-                "kernel": "ns_gemm_tc_kernel (tcgen05 bf16, 10 launches per step)"}
+                "kernel": "ns_gemm_tc_kernel (tcgen05 bf16, 11 launches per step in the chain form)"}
         opt.close()
     out["config"] = {"workload": f"c4_muon: {len(wl.shapes)} matrices ({args.muon_layers} x {{3072x1024, 1024x1024, "
                                  f"4096x1024, 1024x4096}}), {wl.total} f32 params, lr=0.1 momentum=0.9 nesterov "
@@ -1093,10 +1093,10 @@ def run_muon(args, eng, world, rank, dev, barrier, max_over_ranks, peaks):
 NCU_ADAM_C3_DRAM_BYTES_PER_LAUNCH = 3.0164e9
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of ns_gemm_tc_kernel<2, 0> on 4 layers of the Muon
-# workload (16 matrices): mean of a Gram launch (110.4 MB) and an update launch (206.8 MB), from the ncu
-# capture summarised in profiles/muon_c4_ns_gemm_tc.md
-NCU_MUON_4LAYER_DRAM_BYTES_PER_LAUNCH = 158.6e6
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of ns_gemm_tc_kernel on 4 layers of the Muon workload
+# (16 matrices): mean over the eleven launches of one step of the chain form (133, 71, 4 x 89, 3 x 158, 71 and
+# 488 MB), from the ncu capture summarised in profiles/muon_c4_ns_gemm_tc.md
+NCU_MUON_4LAYER_DRAM_BYTES_PER_LAUNCH = 144.8e6
 
 
 def main():
