@@ -959,14 +959,28 @@ def run_muon(args, eng, world, rank, dev, barrier, max_over_ranks, peaks):
     params = wl.make_params()
     grads = wl.make_grads(1)
     out = {}
+    # "bf16" is the library's default (the chain form of Newton-Schulz); "bf16_per_iteration_form" runs the
+    # same kernel on one Gram and one update product per iteration (VB_NS_CHAIN=0): twice the FLOPs in long
+    # main loops, the like-for-like measure of the kernel against the dense-GEMM peak
     for mode_name, mode, steps in (("bf16", VB_NS_BF16, max(3, min(args.steps, 20))),
+                                   ("bf16_per_iteration_form", VB_NS_BF16, max(3, min(args.steps, 20))),
                                    ("f32_tc", VB_NS_F32_TC, max(3, min(args.steps, 5))), ("f32", VB_NS_F32, 2)):
         if mode_name == "f32" and (args.skip_muon_f32 or (args.only_muon and not args.muon_f32)):
             continue
         if mode_name == "f32_tc" and args.only_muon and not args.muon_f32_tc:
             continue
         tensors = [Tensor(p, p.shape) for p in params]
-        opt = Muon(tensors, h["lr"], h["momentum"], h["nesterov"], h["ns_steps"], ns_mode=mode, engine=eng)
+        chain_env = os.environ.get("VB_NS_CHAIN")
+        if mode_name == "bf16_per_iteration_form":
+            os.environ["VB_NS_CHAIN"] = "0"   # read when the optimizer is created
+        try:
+            opt = Muon(tensors, h["lr"], h["momentum"], h["nesterov"], h["ns_steps"], ns_mode=mode, engine=eng)
+        finally:
+            if mode_name == "bf16_per_iteration_form":
+                if chain_env is None:
+                    del os.environ["VB_NS_CHAIN"]
+                else:
+                    os.environ["VB_NS_CHAIN"] = chain_env
         if world > 1 and args.exchange == "peer":
             opt.open_peers(gather_handles(opt.ipc_handle(), world, dev))
         _, _, arena, offsets = opt.arena_layout()
@@ -999,7 +1013,8 @@ def run_muon(args, eng, world, rank, dev, barrier, max_over_ranks, peaks):
         # blocks of `steps` steps until the timed region is long enough for the clocks to settle
         # (the bit-faithful f32 mode is slow enough as it is)
         blocks = timed_blocks(run_block, barrier, max_over_ranks,
-                              min_seconds=MIN_TIMED_SECONDS if mode_name == "bf16" else 0.25 if mode_name == "f32_tc" else 0.0,
+                              min_seconds=MIN_TIMED_SECONDS if mode_name == "bf16" else
+                              0.25 if mode_name in ("f32_tc", "bf16_per_iteration_form") else 0.0,
                               max_blocks=40)
         muon_clocks = sampler.stop() if sampler is not None else None
         n_steps_total = steps * len(blocks)
@@ -1026,7 +1041,10 @@ def run_muon(args, eng, world, rank, dev, barrier, max_over_ranks, peaks):
             "apply_note": "apply_ms is the last update launch, which applies its result to the weights in its epilogue "
                           "(8 B/param of HBM traffic on top of the product); it is part of ns_ms_per_step as well"
                           if mode_name != "f32" else "separate apply pass",
-            "note": {"bf16": "tcgen05 bf16, chain form: one long-side Gram, 3 (K - 1) short-side symmetric squares (computed "
+            "note": {"bf16_per_iteration_form": "tcgen05 bf16, one short-side Gram (computed on and above the diagonal) "
+                                                "and one update product per iteration (VB_NS_CHAIN=0): the form whose "
+                                                "launches are long dense products",
+                     "bf16": "tcgen05 bf16, chain form: one long-side Gram, 3 (K - 1) short-side symmetric squares (computed "
                              "on and above the diagonal) and one long-side product per matrix instead of K Gram and K "
                              "update products; same result within the bf16 bound (VB_NS_CHAIN=0 selects the "
                              "per-iteration form)", "f32": "CUDA-core FFMA, bit-identical to the CPU arithmetic",
@@ -1054,7 +1072,7 @@ def run_muon(args, eng, world, rank, dev, barrier, max_over_ranks, peaks):
             half_ms = max_over_ranks(e0.elapsed_time(e1) / steps)
             out[mode_name]["bf16_exchange"] = {"ms_per_step": half_ms, "params_per_s": wl.total / (half_ms * 1e-3),
                                                "note": "step(VB_STEP_EXCHANGE_BF16): owners send bf16 copies only"}
-        if mode_name == "bf16":
+        if mode_name in ("bf16", "bf16_per_iteration_form"):
             out[mode_name]["roofline"] = {
                 "bound": "tensor", "achieved": tflops, "peak": peak, "unit": "TFLOP/s", "frac": tflops / peak,
                 "peak_source": peaks["source"] + " (cuBLAS bf16 sustained)",
@@ -1063,7 +1081,18 @@ def run_muon(args, eng, world, rank, dev, barrier, max_over_ranks, peaks):
                 "traffic": NCU_MUON_4LAYER_DRAM_BYTES_PER_LAUNCH * args.muon_layers / 4.0 / world,
                 "traffic_note": "ncu capture of the 4-layer case (mean over the eleven launches of a step), scaled by "
                                 "layers / 4: per-launch traffic grows with the number of matrices",
-                "kernel": "ns_gemm_tc_kernel (tcgen05 bf16, 11 launches per step in the chain form)"}
+                "kernel": "ns_gemm_tc_kernel (tcgen05 bf16, 11 launches per step in the chain form)"
+                          if mode_name == "bf16" else "ns_gemm_tc_kernel (tcgen05 bf16, 10 launches per step)"}
+            if mode_name == "bf16_per_iteration_form":
+                out[mode_name]["roofline"]["traffic"] = 158.6e6 * args.muon_layers / 4.0 / world
+                out[mode_name]["roofline"]["traffic_note"] = ("ncu capture of the 4-layer case (mean of a Gram and an "
+                                                              "update launch), scaled by layers / 4")
+                if "bf16" in out:
+                    out["bf16"]["roofline"]["note"] = (
+                        "the chain form executes about half the FLOPs of the per-iteration form, in short (k = S) "
+                        "symmetric squares that run at a lower rate, and ends sooner: "
+                        f"{out['bf16']['ns_ms_per_step']:.3f} ms against {ns_ms:.3f} ms for the GEMM launches of a step; "
+                        "the kernel's rate on long dense products is bf16_per_iteration_form.roofline")
         opt.close()
     out["config"] = {"workload": f"c4_muon: {len(wl.shapes)} matrices ({args.muon_layers} x {{3072x1024, 1024x1024, "
                                  f"4096x1024, 1024x4096}}), {wl.total} f32 params, lr=0.1 momentum=0.9 nesterov "
