@@ -306,12 +306,16 @@ def test_bf16_path_c4_layer_shapes(oracle, engine):
 
 # ---- f32-accurate tensor-core path (two f16 planes per operand) ----------------------------------
 
+@pytest.mark.parametrize("form", ["chain", "per_iteration"])
 @pytest.mark.parametrize("shapes", [[(256, 128)], [(128, 384), (512, 512)], [(200, 72), (64, 36), (50,)], [(1032, 264)]])
-def test_f32_tc_path_meets_f32_tolerance(oracle, engine, shapes):
+def test_f32_tc_path_meets_f32_tolerance(oracle, engine, shapes, form, monkeypatch):
     """VB_NS_F32_TC: operands held as two f16 planes, three tensor-core products per product,
     ordered sum of squares.  Same 1e-5 bound as the bit-faithful path (shapes whose rows are
-    not 16-byte aligned in bf16 run the bit-faithful kernels inside the same optimizer)."""
+    not 16-byte aligned in bf16 run the bit-faithful kernels inside the same optimizer).  Both
+    forms: the chain of short-side squares (default) and one Gram and one update product per
+    iteration (VB_NS_CHAIN=0)."""
     from volta_b200 import VB_NS_F32_TC
+    monkeypatch.setenv("VB_NS_CHAIN", "1" if form == "chain" else "0")
     res = _run(oracle, engine, shapes, 3, VB_NS_F32_TC)
     for r in res:
         assert r["update"] <= TOL_F32, res

@@ -173,6 +173,14 @@ __global__ void reduce_partials_kernel(const float *__restrict__ partials, const
 }
 
 // ---- K3s: order-faithful sum of squares ------------------------------------------------------
+// The identity as two f16 planes of I * 2^scale_log2 (chain form of the f32-accurate path: P_0 = I).
+__global__ void set_identity_planes_kernel(__nv_bfloat16 *__restrict__ plane0, int n, int scale_log2)
+{
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n)
+        reinterpret_cast<unsigned short *>(plane0)[(int64_t)i * n + i] = __half_as_ushort(__float2half_rn(ldexpf(1.0f, scale_log2)));
+}
+
 // The reference adds x*x left to right in f32 (muon.rs:58).  With millions of addends that
 // differs from the exact sum by up to a few 1e-3 relative, far more than the 1e-5 parity
 // bound of the f32 path, so the GPU must reproduce the *sequence of roundings*.
@@ -837,13 +845,12 @@ double muon_tensor_cost(int64_t rows, int64_t cols, int ns_mode, int ns_steps)
     const double L = std::max(r, c), S = std::min(r, c);
     const double t = std::ceil(S / 256.0);                  // 256 x 256 tiles per side of the Gram
     const double upper = (t * (t + 1.0) / 2.0) / (t * t);   // share of the Gram that is computed
-    if (ns_mode == VB_NS_BF16) {
-        // the chain form: the first Gram (upper tiles), 3 (K - 1) short-side squares (upper tiles), the last product
-        const double work = 2.0 * L * S * S * (1.0 + upper) + 3.0 * (double)(ns_steps - 1) * 2.0 * S * S * S * upper;
-        return elementwise + work / 0.8e15;
-    }
-    const double planes = ns_mode == VB_NS_F32_TC ? 3.0 : 1.0;
-    return elementwise + planes * (double)ns_steps * 2.0 * L * S * S * (1.0 + upper) / 1.15e15;
+    // the chain form: the first Gram (upper tiles), the short-side squares (upper tiles), the last product;
+    // three plane products per product on the f32-accurate path, which also forms P_1 by a product
+    const bool split = ns_mode == VB_NS_F32_TC;
+    const double squares = split ? 3.0 * (double)ns_steps - 2.0 : 3.0 * (double)(ns_steps - 1);
+    const double work = 2.0 * L * S * S * (1.0 + upper) + squares * 2.0 * S * S * S * upper;
+    return elementwise + (split ? 3.0 * work / 0.95e15 : work / 0.8e15);
 }
 
 // Whole matrices are owned by one rank: tensors are taken in order of decreasing estimated
@@ -1024,9 +1031,10 @@ int muon_init(vb_optimizer *opt)
         // plain bf16 path: the chain form (below) unless VB_NS_CHAIN=0 asks for one Gram and one update
         // product per iteration
         const char *chain_env = getenv("VB_NS_CHAIN");
-        s->chain = s->planes == 1 && opt->ns_steps >= 1 && !(chain_env && *chain_env == '0');
+        s->chain = opt->ns_steps >= 1 && !(chain_env && *chain_env == '0');
         if (s->chain) {
-            const size_t chain_bytes = 6 * (size_t)std::max<int64_t>(cb_elems, 1) * sizeof(__nv_bfloat16);
+            // six short-side squares per matrix (of `planes` planes each)
+            const size_t chain_bytes = 6 * (size_t)s->planes * (size_t)std::max<int64_t>(cb_elems, 1) * sizeof(__nv_bfloat16);
             VB_CUDA(cudaMalloc(&s->d_chain, chain_bytes));
             VB_CUDA(cudaMemsetAsync(s->d_chain, 0, chain_bytes, e->stream));
         }
@@ -1106,6 +1114,7 @@ int muon_init(vb_optimizer *opt)
         std::vector<TcGemmProblem> chain_l0, chain_final;
         std::vector<std::vector<TcGemmProblem>> chain_a((size_t)n_chain_mid), chain_b((size_t)n_chain_mid),
             chain_c((size_t)iters);  // chain_c[k], k = 1 .. iters - 1
+        std::vector<std::vector<TcGemmProblem>> split_p((size_t)iters);  // f32-accurate path: the P products
         std::vector<GemmTile> small_tiles;
         std::stable_sort(tc_tensors.begin(), tc_tensors.end(), by_size);
         // plain bf16 path: the momentum kernel writes the unnormalised bf16 operand and the first
@@ -1188,7 +1197,70 @@ int muon_init(vb_optimizer *opt)
                 }
                 upd[(size_t)it].push_back(u);
             }
-            if (s->chain) {
+            if (s->chain && planes > 1) {
+                // f32-accurate path: the chain with only G, T and P stored (two f16 planes each) and
+                // C = 1.5 I - 0.5 G applied in the epilogues, which all have the form 1.5 Y - 0.5 (Y G)
+                // of the per-iteration update (TC_EPI_NS_COMBINE):
+                //     T_k = 1.5 G_k - 0.5 G_k G_k,   G_{k+1} = 1.5 T_k - 0.5 G_k T_k,   P_{k+1} = 1.5 P_k - 0.5 P_k G_k  (P_0 = I)
+                //     X_K = X_0 P_K
+                // G and T carry the scale of the Gram (2^(15 - 2e), see split_exponent), P is held at
+                // 2^p_log2 with 1.5^K 2^p_log2 inside the f16 range; every product has G as one operand, so
+                // the accumulator returns to the scale of Y by the same factor as in the update product.
+                const int p_log2 = std::min(15, (int)std::floor(std::log2(60000.0 / std::pow(1.5, (double)iters))));
+                enum { kG0 = 0, kG1 = 1, kT = 2, kPI = 3, kPa = 4, kPb = 5 };
+                __nv_bfloat16 *sq[6];
+                CUtensorMap sq_k[6], sq_mn[6];
+                const int64_t buf_stride = (int64_t)planes * cb_elems;
+                for (int b = 0; b < 6; ++b) {
+                    sq[b] = s->d_chain + (int64_t)b * buf_stride + cb_off[(size_t)t];
+                    VB_TRY(make_bf16_tensor_map(&sq_k[b], sq[b], sh, sh, TC_OP_K_MAJOR, planes, cb_elems));
+                    VB_TRY(make_bf16_tensor_map(&sq_mn[b], sq[b], sh, sh, c_mn_mode, planes, cb_elems));
+                }
+                set_identity_planes_kernel<<<(sh + 255) / 256, 256, 0, e->stream>>>(sq[kPI], sh, p_log2);
+                VB_CUDA(cudaGetLastError());
+                auto combine = [&](int y, int g, int out) {  // out = 1.5 Y - 0.5 (Y G)
+                    TcGemmProblem q{};
+                    q.map_a = sq_mn[y]; q.map_b = sq_k[g];
+                    q.M = sh; q.N = sh; q.K = sh;
+                    q.a_mode = c_mn_mode; q.b_mode = TC_OP_K_MAJOR;
+                    q.epilogue = TC_EPI_NS_COMBINE; q.ld_out = sh; q.tensor = t;
+                    q.n_terms = n_terms; q.n_out_planes = planes; q.out_plane_stride = cb_elems;
+                    q.in_bf16 = sq[y];
+                    q.split_sumsq = s->d_sumsq + t;
+                    q.out_bf16 = sq[out];
+                    return q;
+                };
+                TcGemmProblem l0 = gram[0].back();  // G_0 = X_0^T X_0 (two planes)
+                l0.out_bf16 = sq[kG0];
+                chain_l0.push_back(l0);
+                auto p_buf = [&](int j) { return j == 0 ? (int)kPI : (j & 1) ? (int)kPa : (int)kPb; };
+                for (int k = 0; k < iters; ++k) {
+                    const int g_now = kG0 + (k & 1), g_next = kG0 + ((k + 1) & 1);
+                    if (k + 1 < iters) {
+                        chain_a[(size_t)k].push_back(combine(g_now, g_now, kT));   // T_k
+                        chain_b[(size_t)k].push_back(combine(kT, g_now, g_next));  // G_{k+1}
+                    }
+                    split_p[(size_t)k].push_back(combine(p_buf(k), g_now, p_buf(k + 1)));  // P_{k+1}
+                }
+                TcGemmProblem fin = upd[(size_t)iters - 1].back();  // X_K = X_0 P_K, in the direct form of the update product
+                const int pk = p_buf(iters);
+                if (tall) {
+                    fin.map_a = map_x_k[0];
+                    fin.map_b = sq_k[pk];
+                } else {
+                    fin.map_a = sq_mn[pk];
+                    fin.map_b = map_x_mn[0];
+                }
+                fin.in_bf16 = nullptr;
+                fin.epilogue = TC_EPI_IDENTITY;  // the accumulator is X_K 2^(15 - e + p_log2)
+                fin.split_sumsq = s->d_sumsq + t;
+                fin.extra_scale = ldexpf(1.0f, 15 - p_log2);
+                chain_final.push_back(fin);
+                for (int m0 = 0; m0 < sh; m0 += bm)
+                    for (int n0 = m0; n0 < sh; n0 += bn)
+                        small_tiles.push_back(GemmTile{pidx, m0, n0, n0 > m0 ? GEMM_TILE_MIRROR : 0});
+            }
+            if (s->chain && planes == 1) {
                 __nv_bfloat16 *sq[6];  // G, T, C'[0], C'[1], P'[0], P'[1]
                 CUtensorMap sq_k[6], sq_mn[6];
                 for (int b = 0; b < 6; ++b) {
@@ -1297,7 +1369,8 @@ int muon_init(vb_optimizer *opt)
             if (s->chain) {
                 const double upper = (double)gram_used / (double)gram_all;
                 const double square = 2.0 * (double)sh * (double)sh * (double)sh * upper;
-                s->flops_per_step += prod * upper + 3.0 * (double)(iters - 1) * square + prod;
+                const double n_squares = s->planes > 1 ? 3.0 * (double)iters - 2.0 : 3.0 * (double)(iters - 1);
+                s->flops_per_step += (double)n_terms * (prod * upper + n_squares * square + prod);
             } else {
                 s->flops_per_step += (double)n_terms * (double)opt->ns_steps *
                                      (prod * (double)gram_used / (double)gram_all + prod);
@@ -1325,16 +1398,29 @@ int muon_init(vb_optimizer *opt)
             };
             // the tile lists of the first Gram and of the last product are uploaded below; their
             // pointers are filled in once they exist
-            VB_TRY(add(chain_l0, nullptr, 0, false, /*dual=*/true));
-            for (int k = 0; k + 1 < iters; ++k) {
+            if (s->planes > 1) {
+                VB_TRY(add(chain_l0, nullptr, 0, false));
+                for (int k = 0; k + 1 < iters; ++k) {  // T_k and P_{k+1} need only G_k: one launch
+                    std::vector<TcGemmProblem> both = chain_a[(size_t)k];
+                    both.insert(both.end(), split_p[(size_t)k].begin(), split_p[(size_t)k].end());
+                    VB_TRY(add(both, s->d_small_tiles2, s->n_small_tiles2, false));
+                    VB_TRY(add(chain_b[(size_t)k], s->d_small_tiles, s->n_small_tiles, false));
+                }
+                VB_TRY(add(split_p[(size_t)iters - 1], s->d_small_tiles, s->n_small_tiles, false));
+                VB_TRY(add(chain_final, nullptr, 0, true));
+            }
+            if (s->planes == 1) VB_TRY(add(chain_l0, nullptr, 0, false, /*dual=*/true));
+            for (int k = 0; s->planes == 1 && k + 1 < iters; ++k) {
                 std::vector<TcGemmProblem> both = chain_a[(size_t)k];
                 if (k >= 1) both.insert(both.end(), chain_c[(size_t)k].begin(), chain_c[(size_t)k].end());
                 VB_TRY(add(both, k >= 1 ? s->d_small_tiles2 : s->d_small_tiles,
                            k >= 1 ? s->n_small_tiles2 : s->n_small_tiles, false));
                 VB_TRY(add(chain_b[(size_t)k], s->d_small_tiles, s->n_small_tiles, false, /*dual=*/true));
             }
-            if (iters >= 2) VB_TRY(add(chain_c[(size_t)iters - 1], s->d_small_tiles, s->n_small_tiles, false));
-            VB_TRY(add(chain_final, nullptr, 0, true));
+            if (s->planes == 1) {
+                if (iters >= 2) VB_TRY(add(chain_c[(size_t)iters - 1], s->d_small_tiles, s->n_small_tiles, false));
+                VB_TRY(add(chain_final, nullptr, 0, true));
+            }
         }
         s->d_tc_gram.assign((size_t)iters, nullptr);
         s->d_tc_upd.assign((size_t)iters, nullptr);
@@ -1474,7 +1560,7 @@ int muon_step(vb_optimizer *opt, uint32_t flags)
                 TcApplyArgs ap{};
                 if (l.final_product) VB_TRY(final_apply_args(ap));
                 VB_TRY(launch_ns_gemm_tc(l.d_problems, l.d_tiles, l.n_tiles, opt->d_present, s->d_error, e->sm_count,
-                                         e->stream, gemm_wait_limit, false, ap.enabled ? &ap : nullptr, false, l.dual));
+                                         e->stream, gemm_wait_limit, s->planes > 1, ap.enabled ? &ap : nullptr, false, l.dual));
                 if (ap.enabled) prof_end(e, VB_PHASE_MUON_APPLY);
                 e->launches += l.n_tiles > 0;
             }

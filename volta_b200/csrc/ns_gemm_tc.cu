@@ -1061,7 +1061,13 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
                 const float inv = norm > 1e-8f ? 1.0f / norm : 1.0f;  // muon.rs:60
                 acc_scale = p->scale_power == 2 ? inv * inv : inv;
             }
-            if (!kSplit && p->extra_scale != 0.0f) acc_scale *= p->extra_scale;
+            if (kSplit && epi == TC_EPI_IDENTITY && p->split_sumsq) {
+                // the last product of the chain form: one operand is X_0 at 2^(15 - e), the other a square
+                // whose power-of-two scale the host folded into extra_scale
+                split_e = split_exponent(*p->split_sumsq);
+                acc_scale = ldexpf(acc_scale, split_e);
+            }
+            if (p->extra_scale != 0.0f) acc_scale *= p->extra_scale;
             // a second output of a 3I - G launch: G itself (drained by a second pass over the accumulator)
             __nv_bfloat16 *out2_bf16 = (kDual && !kSplit && epi == TC_EPI_THREE_I_MINUS) ? p->out2_bf16 : nullptr;
             const int64_t ld = p->ld_out;
