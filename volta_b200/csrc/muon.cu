@@ -173,12 +173,14 @@ __global__ void reduce_partials_kernel(const float *__restrict__ partials, const
 }
 
 // ---- K3s: order-faithful sum of squares ------------------------------------------------------
-// The identity as two f16 planes of I * 2^scale_log2 (chain form of the f32-accurate path: P_0 = I).
-__global__ void set_identity_planes_kernel(__nv_bfloat16 *__restrict__ plane0, int n, int scale_log2)
+// The identity times 2^scale_log2 as the first of two f16 planes, or as bf16 (chain forms that start from P_0 = I).
+__global__ void set_identity_planes_kernel(__nv_bfloat16 *__restrict__ plane0, int n, int scale_log2, int as_bf16)
 {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n)
-        reinterpret_cast<unsigned short *>(plane0)[(int64_t)i * n + i] = __half_as_ushort(__float2half_rn(ldexpf(1.0f, scale_log2)));
+    if (i >= n) return;
+    const float v = ldexpf(1.0f, scale_log2);
+    reinterpret_cast<unsigned short *>(plane0)[(int64_t)i * n + i] =
+        as_bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(v)) : __half_as_ushort(__float2half_rn(v));
 }
 
 // The reference adds x*x left to right in f32 (muon.rs:58).  With millions of addends that
@@ -762,6 +764,7 @@ struct MuonState {
         bool dual = false;  // its problems store G beside 3I - G
     };
     bool chain = false;
+    bool chain_g_only = false;  // only G, T, P are stored; C = 1.5 I - 0.5 G is applied in the epilogues
     std::vector<TcLaunch> chain_launches;
     __nv_bfloat16 *d_chain = nullptr;    // per matrix six short-side squares: G, T, C'[2], P'[2]
     GemmTile *d_small_tiles = nullptr, *d_small_tiles2 = nullptr;
@@ -1032,6 +1035,8 @@ int muon_init(vb_optimizer *opt)
         // product per iteration
         const char *chain_env = getenv("VB_NS_CHAIN");
         s->chain = opt->ns_steps >= 1 && !(chain_env && *chain_env == '0');
+        // VB_NS_CHAIN=2: the plain bf16 path also keeps only G, T and P (as the f32-accurate path does)
+        s->chain_g_only = s->planes > 1 || (chain_env && *chain_env == '2');
         if (s->chain) {
             // six short-side squares per matrix (of `planes` planes each)
             const size_t chain_bytes = 6 * (size_t)s->planes * (size_t)std::max<int64_t>(cb_elems, 1) * sizeof(__nv_bfloat16);
@@ -1197,7 +1202,7 @@ int muon_init(vb_optimizer *opt)
                 }
                 upd[(size_t)it].push_back(u);
             }
-            if (s->chain && planes > 1) {
+            if (s->chain && s->chain_g_only) {
                 // f32-accurate path: the chain with only G, T and P stored (two f16 planes each) and
                 // C = 1.5 I - 0.5 G applied in the epilogues, which all have the form 1.5 Y - 0.5 (Y G)
                 // of the per-iteration update (TC_EPI_NS_COMBINE):
@@ -1206,7 +1211,7 @@ int muon_init(vb_optimizer *opt)
                 // G and T carry the scale of the Gram (2^(15 - 2e), see split_exponent), P is held at
                 // 2^p_log2 with 1.5^K 2^p_log2 inside the f16 range; every product has G as one operand, so
                 // the accumulator returns to the scale of Y by the same factor as in the update product.
-                const int p_log2 = std::min(15, (int)std::floor(std::log2(60000.0 / std::pow(1.5, (double)iters))));
+                const int p_log2 = planes > 1 ? std::min(15, (int)std::floor(std::log2(60000.0 / std::pow(1.5, (double)iters)))) : 0;
                 enum { kG0 = 0, kG1 = 1, kT = 2, kPI = 3, kPa = 4, kPb = 5 };
                 __nv_bfloat16 *sq[6];
                 CUtensorMap sq_k[6], sq_mn[6];
@@ -1216,7 +1221,7 @@ int muon_init(vb_optimizer *opt)
                     VB_TRY(make_bf16_tensor_map(&sq_k[b], sq[b], sh, sh, TC_OP_K_MAJOR, planes, cb_elems));
                     VB_TRY(make_bf16_tensor_map(&sq_mn[b], sq[b], sh, sh, c_mn_mode, planes, cb_elems));
                 }
-                set_identity_planes_kernel<<<(sh + 255) / 256, 256, 0, e->stream>>>(sq[kPI], sh, p_log2);
+                set_identity_planes_kernel<<<(sh + 255) / 256, 256, 0, e->stream>>>(sq[kPI], sh, p_log2, planes == 1);
                 VB_CUDA(cudaGetLastError());
                 auto combine = [&](int y, int g, int out) {  // out = 1.5 Y - 0.5 (Y G)
                     TcGemmProblem q{};
@@ -1230,7 +1235,8 @@ int muon_init(vb_optimizer *opt)
                     q.out_bf16 = sq[out];
                     return q;
                 };
-                TcGemmProblem l0 = gram[0].back();  // G_0 = X_0^T X_0 (two planes)
+                TcGemmProblem l0 = gram[0].back();  // G_0 = X_0^T X_0 (plain path: of u, scaled by 1 / norm^2)
+                l0.epilogue = TC_EPI_IDENTITY;
                 l0.out_bf16 = sq[kG0];
                 chain_l0.push_back(l0);
                 auto p_buf = [&](int j) { return j == 0 ? (int)kPI : (j & 1) ? (int)kPa : (int)kPb; };
@@ -1252,15 +1258,22 @@ int muon_init(vb_optimizer *opt)
                     fin.map_b = map_x_mn[0];
                 }
                 fin.in_bf16 = nullptr;
-                fin.epilogue = TC_EPI_IDENTITY;  // the accumulator is X_K 2^(15 - e + p_log2)
-                fin.split_sumsq = s->d_sumsq + t;
-                fin.extra_scale = ldexpf(1.0f, 15 - p_log2);
+                if (planes > 1) {
+                    fin.epilogue = TC_EPI_IDENTITY;  // the accumulator is X_K 2^(15 - e + p_log2)
+                    fin.split_sumsq = s->d_sumsq + t;
+                    fin.extra_scale = ldexpf(1.0f, 15 - p_log2);
+                } else {
+                    fin.epilogue = TC_EPI_HALF;  // X_K = (u P_K) / norm: 0.5 * 2
+                    fin.scale_sumsq = s->d_sumsq + t;
+                    fin.scale_power = 1;
+                    fin.extra_scale = 2.0f;
+                }
                 chain_final.push_back(fin);
                 for (int m0 = 0; m0 < sh; m0 += bm)
                     for (int n0 = m0; n0 < sh; n0 += bn)
                         small_tiles.push_back(GemmTile{pidx, m0, n0, n0 > m0 ? GEMM_TILE_MIRROR : 0});
             }
-            if (s->chain && planes == 1) {
+            if (s->chain && !s->chain_g_only) {
                 __nv_bfloat16 *sq[6];  // G, T, C'[0], C'[1], P'[0], P'[1]
                 CUtensorMap sq_k[6], sq_mn[6];
                 for (int b = 0; b < 6; ++b) {
@@ -1369,7 +1382,7 @@ int muon_init(vb_optimizer *opt)
             if (s->chain) {
                 const double upper = (double)gram_used / (double)gram_all;
                 const double square = 2.0 * (double)sh * (double)sh * (double)sh * upper;
-                const double n_squares = s->planes > 1 ? 3.0 * (double)iters - 2.0 : 3.0 * (double)(iters - 1);
+                const double n_squares = s->chain_g_only ? 3.0 * (double)iters - 2.0 : 3.0 * (double)(iters - 1);
                 s->flops_per_step += (double)n_terms * (prod * upper + n_squares * square + prod);
             } else {
                 s->flops_per_step += (double)n_terms * (double)opt->ns_steps *
@@ -1398,26 +1411,28 @@ int muon_init(vb_optimizer *opt)
             };
             // the tile lists of the first Gram and of the last product are uploaded below; their
             // pointers are filled in once they exist
-            if (s->planes > 1) {
+            if (s->chain_g_only) {
+                // on the plain path the epilogue that reads a tile back lives in the kernel's second instantiation
+                const bool aux = s->planes == 1;
                 VB_TRY(add(chain_l0, nullptr, 0, false));
                 for (int k = 0; k + 1 < iters; ++k) {  // T_k and P_{k+1} need only G_k: one launch
                     std::vector<TcGemmProblem> both = chain_a[(size_t)k];
                     both.insert(both.end(), split_p[(size_t)k].begin(), split_p[(size_t)k].end());
-                    VB_TRY(add(both, s->d_small_tiles2, s->n_small_tiles2, false));
-                    VB_TRY(add(chain_b[(size_t)k], s->d_small_tiles, s->n_small_tiles, false));
+                    VB_TRY(add(both, s->d_small_tiles2, s->n_small_tiles2, false, aux));
+                    VB_TRY(add(chain_b[(size_t)k], s->d_small_tiles, s->n_small_tiles, false, aux));
                 }
-                VB_TRY(add(split_p[(size_t)iters - 1], s->d_small_tiles, s->n_small_tiles, false));
+                VB_TRY(add(split_p[(size_t)iters - 1], s->d_small_tiles, s->n_small_tiles, false, aux));
                 VB_TRY(add(chain_final, nullptr, 0, true));
             }
-            if (s->planes == 1) VB_TRY(add(chain_l0, nullptr, 0, false, /*dual=*/true));
-            for (int k = 0; s->planes == 1 && k + 1 < iters; ++k) {
+            if (!s->chain_g_only) VB_TRY(add(chain_l0, nullptr, 0, false, /*dual=*/true));
+            for (int k = 0; !s->chain_g_only && k + 1 < iters; ++k) {
                 std::vector<TcGemmProblem> both = chain_a[(size_t)k];
                 if (k >= 1) both.insert(both.end(), chain_c[(size_t)k].begin(), chain_c[(size_t)k].end());
                 VB_TRY(add(both, k >= 1 ? s->d_small_tiles2 : s->d_small_tiles,
                            k >= 1 ? s->n_small_tiles2 : s->n_small_tiles, false));
                 VB_TRY(add(chain_b[(size_t)k], s->d_small_tiles, s->n_small_tiles, false, /*dual=*/true));
             }
-            if (s->planes == 1) {
+            if (!s->chain_g_only) {
                 if (iters >= 2) VB_TRY(add(chain_c[(size_t)iters - 1], s->d_small_tiles, s->n_small_tiles, false));
                 VB_TRY(add(chain_final, nullptr, 0, true));
             }

@@ -594,7 +594,9 @@ __device__ __forceinline__ float rounded16(float a)
     return __bfloat162float(__float2bfloat16_rn(a));
 }
 
-template <bool kSplit>
+// kInRead: TC_EPI_NS_COMBINE (the output position of `in_bf16` enters the result) is compiled in; always
+// on the split path, on the plain path only in the instantiation kept for the rarer launches.
+template <bool kSplit, bool kInRead>
 __device__ __forceinline__ void drain_generic(const DrainArgs &a)
 {
     constexpr int kChunks = (BN / 2) / 32;
@@ -626,7 +628,7 @@ __device__ __forceinline__ void drain_generic(const DrainArgs &a)
                 else if (epi == TC_EPI_HALF) f[j] = 0.5f * a;                               // muon.rs:95-99
                 else f[j] = a;  // TC_EPI_IDENTITY, or TC_EPI_NS_COMBINE (finished below)
             }
-            if (kSplit && epi == TC_EPI_NS_COMBINE) {
+            if (kInRead && epi == TC_EPI_NS_COMBINE) {
                 // X' = 0.5 X (3I - G) evaluated as 1.5 X - 0.5 (X G): the accumulator holds only
                 // the small product X G, so the tensor core's truncating f32 accumulation acts on
                 // a term that is a few percent of the result instead of on the result itself.
@@ -642,8 +644,13 @@ __device__ __forceinline__ void drain_generic(const DrainArgs &a)
                             const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
                             for (int h = 0; h < 4; ++h) {
-                                x[g8 * 8 + 2 * h] += f16_bits_to_float(w[h] & 0xffffu);
-                                x[g8 * 8 + 2 * h + 1] += f16_bits_to_float(w[h] >> 16);
+                                if (kSplit) {
+                                    x[g8 * 8 + 2 * h] += f16_bits_to_float(w[h] & 0xffffu);
+                                    x[g8 * 8 + 2 * h + 1] += f16_bits_to_float(w[h] >> 16);
+                                } else {  // bf16: the upper half of an f32
+                                    x[g8 * 8 + 2 * h] += __uint_as_float(w[h] << 16);
+                                    x[g8 * 8 + 2 * h + 1] += __uint_as_float(w[h] & 0xffff0000u);
+                                }
                             }
                         }
                     }
@@ -1128,7 +1135,7 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
                     da.out_planes = out_planes; da.out_planes_in = out_planes_in; da.bf16_rows_32b = bf16_rows_32b;
                     da.mirror = mirror; da.transpose = transpose; da.out_bf16 = out_p; da.out_f32 = out_f32; da.in_bf16 = in_bf16;
                     da.apply_w = apply_w; da.apply_pos = apply_pos; da.ap = &ap;
-                    drain_generic<kSplit>(da);
+                    drain_generic<kSplit, kSplit || kDual>(da);
                 }
             }
             tcgen05_fence_before();
