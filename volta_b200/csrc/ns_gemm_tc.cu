@@ -461,11 +461,13 @@ __device__ __forceinline__ void ld_shared_128(uint32_t addr, uint32_t &a, uint32
     asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "r"(addr) : "memory");
 }
 
-template <int EPI>
+// kIn: the bf16 tile of `in_bf16` at the output position enters the result, f = 1.5 in + mult acc
+// (TC_EPI_NS_COMBINE on the plain path, with mult = -0.5 times the accumulator's scale).
+template <int EPI, bool kIn = false>
 __device__ __forceinline__ void drain_fast(uint32_t taddr, int row0, int tile_col0, int M, float mult, int lane,
                                            __nv_bfloat16 *out_bf16, float *out_f32, bool mirror, bool transpose,
                                            int64_t ld, float *apply_w, int64_t apply_pos, const TcApplyArgs &ap,
-                                           uint32_t stage)
+                                           uint32_t stage, const __nv_bfloat16 *in_bf16 = nullptr)
 {
     constexpr int kPieces = (BN / 2) / 32;
     const int row = row0 + lane;  // the accumulator row this lane holds
@@ -488,6 +490,19 @@ __device__ __forceinline__ void drain_fast(uint32_t taddr, int row0, int tile_co
         float f[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[cc & 1][j]) * mult;
+        if (kIn && row_ok) {  // the lane's 32 bf16 of the input tile: four 16-byte loads (rows start on 32-byte boundaries)
+            const uint4 *src = reinterpret_cast<const uint4 *>(in_bf16 + (int64_t)row * ld + col0);
+#pragma unroll
+            for (int g8 = 0; g8 < 4; ++g8) {
+                const uint4 q = src[g8];
+                const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                for (int h = 0; h < 4; ++h) {
+                    f[g8 * 8 + 2 * h] = fmaf(1.5f, __uint_as_float(w[h] << 16), f[g8 * 8 + 2 * h]);
+                    f[g8 * 8 + 2 * h + 1] = fmaf(1.5f, __uint_as_float(w[h] & 0xffff0000u), f[g8 * 8 + 2 * h + 1]);
+                }
+            }
+        }
         if (EPI == TC_EPI_THREE_I_MINUS && row - col0 == lane) {  // warp-uniform: the piece that holds the diagonal
 #pragma unroll
             for (int j = 0; j < 32; ++j) f[j] = (j == lane) ? 3.0f + f[j] : f[j];
@@ -1110,7 +1125,8 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
             // (one staging buffer per warp: a launch writes its result row-major either as bf16 or as f32)
             const bool fast = !kSplit && tile_col0 + BN / 2 <= N && bf16_rows_32b &&
                               (out_bf16 == nullptr || transpose || (out_f32 == nullptr && apply_w == nullptr)) &&
-                              (epi == TC_EPI_HALF || epi == TC_EPI_THREE_I_MINUS || epi == TC_EPI_IDENTITY);
+                              (epi == TC_EPI_HALF || epi == TC_EPI_THREE_I_MINUS || epi == TC_EPI_IDENTITY ||
+                               (kDual && epi == TC_EPI_NS_COMBINE));
             // one pass over the accumulator per output: 3I - G, then (if asked for) G itself
             const int n_pass = (kDual && out2_bf16 != nullptr) ? 2 : 1;
 #pragma unroll 1
@@ -1125,6 +1141,9 @@ ns_gemm_tc_kernel(const TcGemmProblem *__restrict__ problems, const GemmTile *__
                     else if (epi_p == TC_EPI_THREE_I_MINUS)
                         drain_fast<TC_EPI_THREE_I_MINUS>(taddr, row - lane, tile_col0, M, -acc_scale, lane, out_p,
                                                          out_f32, mirror, transpose, ld, nullptr, 0, ap, my_stage);
+                    else if (kDual && epi_p == TC_EPI_NS_COMBINE)
+                        drain_fast<TC_EPI_IDENTITY, kDual>(taddr, row - lane, tile_col0, M, -0.5f * acc_scale, lane, out_p,
+                                                           nullptr, mirror, false, ld, nullptr, 0, ap, my_stage, in_bf16);
                     else
                         drain_fast<TC_EPI_IDENTITY>(taddr, row - lane, tile_col0, M, acc_scale, lane, out_p, out_f32,
                                                     mirror, transpose, ld, nullptr, 0, ap, my_stage);
