@@ -66,7 +66,12 @@ typedef enum vb_ns_mode {
      * reference's order.  Target: relative Frobenius error <= 1e-5 per matrix. */
     VB_NS_F32 = 0,
     /* bf16 operands on the tcgen05 tensor cores, f32 accumulation in TMEM.
-     * Target: relative Frobenius error <= 2e-2 per matrix. */
+     * Target: relative Frobenius error <= 2e-2 per matrix.
+     * Both tensor-core modes evaluate the iteration (src/nn/optim/muon.rs:67-100) in an
+     * algebraically equal chain form: every Gram matrix of the iteration is a polynomial in the
+     * first one, so one Gram and one product on the long side of the matrix frame a chain of
+     * short-side symmetric squares.  VB_NS_CHAIN=0 in the environment at creation selects one
+     * Gram and one update product per iteration instead; the targets hold for both. */
     VB_NS_BF16 = 1,
     /* f32-accurate on the tensor cores: every operand is held as two f16 pieces of the value
      * scaled by 2^15 (22 significand bits; Newton-Schulz operands are bounded by 1 once the
@@ -132,8 +137,9 @@ int vb_plan_replicated_fraction(double bytes_per_element, int world_size, double
  * executes and given to the least-loaded rank; this is the assignment vb_muon_create uses.
  * Cost: VB_NS_F32 runs the reference's formulation, 4 * rows * cols^2 FLOPs per iteration
  * whatever the orientation (src/nn/optim/muon.rs:73 forms cols x cols), on the CUDA cores; the
- * tensor-core modes run the short-side form, 2 * long * short^2 for the update plus the tiles on
- * and above the diagonal of the symmetric Gram (three plane products each in VB_NS_F32_TC);
+ * tensor-core modes run the chain form: the first Gram (tiles on and above the diagonal) and the
+ * last product on the long side, 2 * long * short^2 each in full, and 3 K - 3 (VB_NS_F32_TC:
+ * 3 K - 2) short-side squares on their upper tiles (three plane products each in VB_NS_F32_TC);
  * shapes that a tensor-core mode hands to the f32 kernels (a side not a multiple of 8) are
  * charged as such; every tensor also pays its element-wise passes.  rank_cost_out (world_size
  * entries, may be NULL) receives each rank's summed estimate in seconds.  No counterpart in the
