@@ -1110,11 +1110,13 @@ int muon_init(vb_optimizer *opt)
         //     T_k = G_k C'_k,   G_{k+1} = C'_k T_k / 4,   C'_{k+1} = 3I - G_{k+1},   P'_{k+1} = P'_k C'_k  (P'_1 = C'_0)
         //     X_K = 2^-K X_0 P'_K
         // so only the first Gram and the last product touch the long side of the matrix; everything
-        // in between is short-side squares, computed on and above the diagonal and mirrored.  Per
-        // matrix that is three long-side products' worth of work (the Gram counts half) plus
-        // 3 (K - 1) half squares, instead of 3 K long-side products (4096 x 1024, K = 5: 24 n^3
-        // multiply-adds against 60 n^3).  In exact arithmetic the result is the reference's; in bf16 the distance
-        // from the f32 oracle stays what the per-iteration form has (a few 1e-3, bound 2e-2).
+        // in between is short-side squares, computed on and above the diagonal and mirrored.  For a
+        // 4096 x 1024 matrix (n = 1024) and K = 5 that is 4 n^3 (Gram, half) + 8 n^3 (last product)
+        // + 12 half squares of n^3 = 24 n^3 multiply-adds against 5 (4 + 8) n^3 = 60 n^3.  In exact
+        // arithmetic the result is the reference's (tests/test_ns_chain_identity.py); in bf16 the
+        // distance from the f32 oracle stays what the per-iteration form has (a few 1e-3, bound 2e-2).
+        // G is stored from the accumulator itself, beside 3I - G (out2_bf16): deriving it from the
+        // rounded C' loses its diagonal as G approaches I, and the chain diverges.
         const int n_chain_mid = std::max(iters - 1, 0);
         std::vector<TcGemmProblem> chain_l0, chain_final;
         std::vector<std::vector<TcGemmProblem>> chain_a((size_t)n_chain_mid), chain_b((size_t)n_chain_mid),
