@@ -1111,8 +1111,9 @@ int muon_init(vb_optimizer *opt)
         //     X_K = 2^-K X_0 P'_K
         // so only the first Gram and the last product touch the long side of the matrix; everything
         // in between is short-side squares, computed on and above the diagonal and mirrored.  For a
-        // 4096 x 1024 matrix (n = 1024) and K = 5 that is 4 n^3 (Gram, half) + 8 n^3 (last product)
-        // + 12 half squares of n^3 = 24 n^3 multiply-adds against 5 (4 + 8) n^3 = 60 n^3.  In exact
+        // 4096 x 1024 matrix (n = 1024, 10 of 16 tiles on or above the diagonal) and K = 5 that is
+        // 5 n^3 (first Gram) + 8 n^3 (last product) + 12 x 1.25 n^3 (squares) = 28 n^3 FLOP against
+        // 5 x (5 + 8) n^3 = 65 n^3 for one Gram and one update product per iteration.  In exact
         // arithmetic the result is the reference's (tests/test_ns_chain_identity.py); in bf16 the
         // distance from the f32 oracle stays what the per-iteration form has (a few 1e-3, bound 2e-2).
         // G is stored from the accumulator itself, beside 3I - G (out2_bf16): deriving it from the
